@@ -1,0 +1,335 @@
+/*
+ * CPU oracle for the mshadow lazy-evaluation hot path -- TEST INFRASTRUCTURE ONLY.
+ * See oracle.h for the role of this file and for how it is pinned to the reference.
+ *
+ * Build: gcc -O2 -std=c11 -fopenmp -ffp-contract=off -fPIC -shared oracle.c -lm
+ * (-ffp-contract=off is mandatory: a fused multiply-add changes result bits, and the
+ *  reference CPU build uses plain SSE arithmetic.)
+ *
+ * Each function names the reference lines it restates.  Loops run in the reference's
+ * order wherever order affects floating-point results; OpenMP is only ever applied to
+ * loops whose iterations produce disjoint outputs, exactly as the reference does.
+ */
+#define _GNU_SOURCE
+#include "oracle.h"
+
+#include <float.h>
+#include <math.h>
+#include <stdlib.h>
+#include <string.h>
+#ifdef _OPENMP
+#include <omp.h>
+#endif
+
+/* sv::saveto / plusto / minusto / multo / divto  (mshadow/base.h:539-602) */
+static inline void save(float *a, float b, int saver) {
+  switch (saver) {
+    case 0: *a = b; break;
+    case 1: *a += b; break;
+    case 2: *a -= b; break;
+    case 3: *a *= b; break;
+    default: *a /= b; break;
+  }
+}
+
+/* red::sum / maximum / minimum ::Reduce  (mshadow/base.h:692-862) */
+static inline float reduce(float acc, float v, int reducer) {
+  switch (reducer) {
+    case 0: return acc + v;
+    case 1: return acc < v ? v : acc;  /* std::max(acc, v) */
+    default: return v < acc ? v : acc; /* std::min(acc, v) */
+  }
+}
+
+/* Reducer::SetInitValue  (mshadow/base.h:742-749, 795-797, 857-860) */
+static inline float reduce_init(int reducer) {
+  switch (reducer) {
+    case 0: return 0.0f;
+    case 1: return -FLT_MAX;
+    default: return FLT_MAX;
+  }
+}
+
+/* Reducer::PartialGrad  (mshadow/base.h:736-739, 787-790) */
+static inline float partial_grad(float redres, float redsrc, int reducer) {
+  if (reducer == 0) return 1.0f;
+  return redres == redsrc ? 1.0f : 0.0f;
+}
+
+/* ---- elementwise: scalar MapPlan, y outer / x inner (tensor_cpu-inl.h:143-159) ---- */
+
+static inline float sigmoid(float a) { return 1.0f / (1.0f + expf(-a)); }
+
+void ORC(expr_case)(int id, float *dst, const float *A, const float *B, const float *C,
+                    const float *bias, int64_t rows, int64_t cols, int64_t ld_dst,
+                    int64_t ld_a, int64_t ld_b, int64_t ld_c) {
+#pragma omp parallel for
+  for (int64_t y = 0; y < rows; ++y) {
+    float *d = dst + y * ld_dst;
+    const float *a = A + y * ld_a, *b = B + y * ld_b, *c = C + y * ld_c;
+    for (int64_t x = 0; x < cols; ++x) {
+      switch (id) {
+        case 0: {
+          /* repmat plan reads src(0, x): extension/broadcast.h:137-148 */
+          float t = a[x] * b[x];
+          float u = 0.5f * c[x];
+          d[x] = sigmoid(t + u) + bias[x];
+          break;
+        }
+        case 1: {
+          float t = a[x] * 2.0f;
+          float u = b[x] / c[x];
+          d[x] += t - u;
+          break;
+        }
+        case 2: {
+          float m = a[x] > b[x] ? a[x] * b[x] : b[x];
+          d[x] = m * c[x];
+          break;
+        }
+        case 3: d[x] *= a[x] + 1.5f; break;
+        case 4: d[x] -= a[x] * b[x]; break;
+        case 5: {
+          float t = c[x] * c[x];
+          d[x] /= t + 1.0f;
+          break;
+        }
+        case 6: d[x] = 3.25f; break;
+        case 7: {
+          float t = a[x] * b[x];
+          d[x] = t + c[x];
+          break;
+        }
+        case 8: {
+          /* general broadcast plan reads src(0, (y / ystride) % length), with
+             ystride = 1 and length = rows for dimcast 0 of a matrix:
+             extension/broadcast.h:116-135 */
+          float t = bias[y] * a[x];
+          d[x] = t + b[x];
+          break;
+        }
+        default: {
+          float s = a[x] - 1.0f;
+          float num = s * s;
+          float t = b[x] * b[x];
+          float q = num / (t + 2.0f);
+          d[x] = q + c[x];
+          break;
+        }
+      }
+    }
+  }
+}
+
+/* ---- reductions ---- */
+
+/* tensor_cpu-inl.h:221-227: seed from row 0, fold rows 1.. in order, scale, save */
+void ORC(reduce_keep_lowest)(float *dst, const float *src, int64_t rows, int64_t cols,
+                             int64_t ld, float scale, int saver, int reducer) {
+#pragma omp parallel for
+  for (int64_t x = 0; x < cols; ++x) {
+    float res = src[x];
+    for (int64_t y = 1; y < rows; ++y) res = reduce(res, src[y * ld + x], reducer);
+    save(dst + x, res * scale, saver);
+  }
+}
+
+/* tensor_cpu-inl.h:254-267: per-n partial from the init value, then folded into res */
+void ORC(reduce_keep_highdim)(float *dst, const float *src, int64_t n, int64_t c, int64_t h,
+                              int64_t w, int64_t ld, float scale, int saver, int reducer) {
+#pragma omp parallel for
+  for (int64_t ci = 0; ci < c; ++ci) {
+    float res = reduce_init(reducer);
+    for (int64_t ni = 0; ni < n; ++ni) {
+      float tres = reduce_init(reducer);
+      for (int64_t y = 0; y < h; ++y) {
+        const float *row = src + ((ni * c + ci) * h + y) * ld;
+        for (int64_t x = 0; x < w; ++x) tres = reduce(tres, row[x], reducer);
+      }
+      res = reduce(res, tres, reducer);
+    }
+    save(dst + ci, res * scale, saver);
+  }
+}
+
+/* ---- softmax ---- */
+
+/* tensor_cpu-inl.h:270-285 applied per row by :464-472 */
+void ORC(softmax)(float *dst, const float *src, int64_t rows, int64_t cols, int64_t ld_dst,
+                  int64_t ld_src) {
+#pragma omp parallel for
+  for (int64_t y = 0; y < rows; ++y) {
+    const float *e = src + y * ld_src;
+    float *d = dst + y * ld_dst;
+    float mmax = e[0];
+    for (int64_t x = 1; x < cols; ++x)
+      if (mmax < e[x]) mmax = e[x];
+    float sum = 0.0f;
+    for (int64_t x = 0; x < cols; ++x) {
+      d[x] = expf(e[x] - mmax);
+      sum += d[x];
+    }
+    for (int64_t x = 0; x < cols; ++x) d[x] /= sum;
+  }
+}
+
+/* tensor_cpu-inl.h:287-302 (plain), :304-321 (smooth), :324-344 (ignore), :346-368 (both) */
+void ORC(softmax_grad)(float *dst, const float *src, const float *label, int64_t rows,
+                       int64_t cols, int64_t ld_dst, int64_t ld_src, int mode,
+                       float ignore_label, float alpha) {
+  const int smooth = mode & 1, ignore = mode & 2;
+  const float smooth_grad = alpha / (float)(cols - 1);
+#pragma omp parallel for
+  for (int64_t y = 0; y < rows; ++y) {
+    const int k = (int)label[y];
+    const float *s = src + y * ld_src;
+    float *d = dst + y * ld_dst;
+    for (int64_t x = 0; x < cols; ++x) {
+      if (ignore && (int)ignore_label == k) {
+        d[x] = 0.0f;
+      } else if (x == k) {
+        d[x] = smooth ? s[x] - 1.0f + alpha : s[x] - 1.0f;
+      } else {
+        d[x] = smooth ? s[x] - smooth_grad : s[x];
+      }
+    }
+  }
+}
+
+/* ---- pooling ---- */
+
+static inline int64_t imin(int64_t a, int64_t b) { return a < b ? a : b; }
+
+/* extension/spatial_pool.h:39-51 (output size) and :125-142 (window walk) */
+void ORC(pool)(float *dst, const float *src, int64_t planes, int64_t h, int64_t w, int ky,
+               int kx, int sy, int sx, int64_t ld_src, int64_t ld_dst, int reducer) {
+  const int64_t ph = (h - ky) / sy + 1, pw = (w - kx) / sx + 1;
+#pragma omp parallel for
+  for (int64_t i = 0; i < planes * ph; ++i) {
+    const int64_t py = i % ph, c = i / ph;
+    const int64_t y0 = py * sy, y1 = imin(y0 + ky, h);
+    for (int64_t px = 0; px < pw; ++px) {
+      const int64_t x0 = px * sx, x1 = imin(x0 + kx, w);
+      float res = reduce_init(reducer);
+      for (int64_t y = y0; y < y1; ++y)
+        for (int64_t x = x0; x < x1; ++x)
+          res = reduce(res, src[(c * h + y) * ld_src + x], reducer);
+      dst[i * ld_dst + px] = res;
+    }
+  }
+}
+
+/* extension/spatial_unpool.h:102-125 */
+void ORC(unpool)(float *dst, const float *src, const float *pooled, const float *gpooled,
+                 int64_t planes, int64_t h, int64_t w, int64_t ph, int64_t pw, int ky, int kx,
+                 int sy, int sx, int64_t ld_src, int64_t ld_pooled, int64_t ld_dst,
+                 int reducer) {
+#pragma omp parallel for
+  for (int64_t i = 0; i < planes * h; ++i) {
+    const int64_t y = i % h, c = i / h;
+    const int64_t py_min = y < ky ? 0 : (y - ky + sy) / sy;
+    const int64_t py_max = imin((y + sy) / sy, ph);
+    for (int64_t x = 0; x < w; ++x) {
+      const float vsrc = src[i * ld_src + x];
+      const int64_t px_min = x < kx ? 0 : (x - kx + sx) / sx;
+      const int64_t px_max = imin((x + sx) / sx, pw);
+      float val = 0.0f;
+      for (int64_t py = py_min; py < py_max; ++py)
+        for (int64_t px = px_min; px < px_max; ++px) {
+          const int64_t o = (c * ph + py) * ld_pooled + px;
+          val += partial_grad(vsrc, pooled[o], reducer) * gpooled[o];
+        }
+      dst[i * ld_dst + x] = val;
+    }
+  }
+}
+
+/* extension/channel_pool.h:35-42 (output channels) and :85-99 (window walk; note that
+   the upper clamp uses the OUTPUT channel count, as the reference does) */
+void ORC(chpool)(float *dst, const float *src, int64_t n, int64_t c, int64_t h, int64_t w,
+                 int nsize, int stride, int pad, int64_t ld_src, int64_t ld_dst, int reducer) {
+  const int64_t co = (c - nsize + pad * 2 + 1) / stride;
+#pragma omp parallel for
+  for (int64_t i = 0; i < n * co * h; ++i) {
+    const int64_t y = i % h, oc = (i / h) % co, ni = i / h / co;
+    const int64_t cstart = oc * stride < pad ? 0 : oc * stride - pad;
+    const int64_t cend = imin(oc * stride - pad + nsize, co);
+    for (int64_t x = 0; x < w; ++x) {
+      float res = reduce_init(reducer);
+      for (int64_t cc = cstart; cc < cend; ++cc)
+        res = reduce(res, src[((ni * c + cc) * h + y) * ld_src + x], reducer);
+      dst[i * ld_dst + x] = res;
+    }
+  }
+}
+
+/* ---- embedding backward ---- */
+
+/* tensor_cpu-inl.h:497-508: serial over the batch, index clipped into [0, K-1] */
+void ORC(addtakegrad)(float *dst, const int32_t *index, const float *src, int64_t k,
+                      int64_t d, int64_t nidx, int64_t ld_dst, int64_t ld_src) {
+  for (int64_t y = 0; y < nidx; ++y) {
+    int64_t j = index[y];
+    if (j <= 0) j = 0;
+    else if (j >= k) j = k - 1;
+    float *row = dst + j * ld_dst;
+    const float *s = src + y * ld_src;
+    for (int64_t x = 0; x < d; ++x) row[x] += s[x];
+  }
+}
+
+/* tensor_cpu-inl.h:510-518: serial over the sorted list, no clipping */
+void ORC(addtakegrad_largebatch)(float *dst, const int32_t *sorted, const int32_t *index,
+                                 const float *src, int64_t k, int64_t d, int64_t nidx) {
+  (void)k;
+  for (int64_t y = 0; y < nidx; ++y) {
+    float *row = dst + (int64_t)sorted[y] * d;
+    const float *s = src + (int64_t)index[y] * d;
+    for (int64_t x = 0; x < d; ++x) row[x] += s[x];
+  }
+}
+
+/* ---- SortByKey: stable permutation sort, then gather (tensor_cpu-inl.h:531-560) ---- */
+
+static void merge_sort_perm(int64_t *perm, int64_t *tmp, const int32_t *keys, int64_t lo,
+                            int64_t hi, int ascend) {
+  if (hi - lo < 2) return;
+  const int64_t mid = lo + (hi - lo) / 2;
+  merge_sort_perm(perm, tmp, keys, lo, mid, ascend);
+  merge_sort_perm(perm, tmp, keys, mid, hi, ascend);
+  int64_t i = lo, j = mid, o = lo;
+  while (i < mid && j < hi) {
+    /* take from the right run only when it is strictly "before" the left head */
+    const int right_first =
+        ascend ? keys[perm[j]] < keys[perm[i]] : keys[perm[j]] > keys[perm[i]];
+    tmp[o++] = right_first ? perm[j++] : perm[i++];
+  }
+  while (i < mid) tmp[o++] = perm[i++];
+  while (j < hi) tmp[o++] = perm[j++];
+  memcpy(perm + lo, tmp + lo, (size_t)(hi - lo) * sizeof(int64_t));
+}
+
+void ORC(sort_by_key)(int32_t *keys, int32_t *values, int64_t n, int ascend) {
+  if (n <= 0) return;
+  int64_t *perm = (int64_t *)malloc((size_t)n * sizeof(int64_t));
+  int64_t *tmp = (int64_t *)malloc((size_t)n * sizeof(int64_t));
+  int32_t *k2 = (int32_t *)malloc((size_t)n * sizeof(int32_t));
+  int32_t *v2 = (int32_t *)malloc((size_t)n * sizeof(int32_t));
+  for (int64_t i = 0; i < n; ++i) perm[i] = i;
+  merge_sort_perm(perm, tmp, keys, 0, n, ascend);
+  for (int64_t i = 0; i < n; ++i) {
+    k2[i] = keys[perm[i]];
+    v2[i] = values[perm[i]];
+  }
+  memcpy(keys, k2, (size_t)n * sizeof(int32_t));
+  memcpy(values, v2, (size_t)n * sizeof(int32_t));
+  free(perm); free(tmp); free(k2); free(v2);
+}
+
+int ORC(num_threads)(void) {
+#ifdef _OPENMP
+  return omp_get_max_threads();
+#else
+  return 1;
+#endif
+}

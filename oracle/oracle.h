@@ -1,0 +1,110 @@
+/*
+ * CPU oracle for the mshadow lazy-evaluation hot path -- TEST INFRASTRUCTURE ONLY.
+ *
+ * A plain-C restatement of what mshadow's CPU evaluator (mshadow/tensor_cpu-inl.h and
+ * the extension Plan::Eval bodies) computes for the operators that the CUDA library
+ * accelerates.  It exists so that parity tests have something to compare against on a
+ * machine that has no copy of the reference tree.  It is never linked into, loaded by,
+ * or called from the product library; only the test-suite, the smoke check and the
+ * benchmark's cpu_baseline leg may use it.
+ *
+ * Parity pinning: every function below is checked bit-for-bit against the unmodified
+ * reference headers compiled into oracle/_ref/libmshadow_ref.so (see ref_shim.cc and
+ * the Makefile) and against the fixtures in tests/golden/ that were produced by that
+ * reference build.
+ *
+ * Conventions shared with ref_shim.cc (which exports the same entry points with a
+ * ref_ prefix):  all matrices are row-major fp32 with an explicit leading dimension
+ * `ld` counted in elements (mshadow's Tensor::stride_);  `saver` picks mshadow's
+ * sv::saveto/plusto/minusto/multo/divto as 0..4;  `reducer` picks red::sum (0),
+ * red::maximum (1) or red::minimum (2).
+ */
+#ifndef MSHADOW_B200_ORACLE_H_
+#define MSHADOW_B200_ORACLE_H_
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#ifndef ORC_PREFIX
+#define ORC_PREFIX orc_
+#endif
+#define ORC_CAT2(a, b) a##b
+#define ORC_CAT(a, b) ORC_CAT2(a, b)
+#define ORC(name) ORC_CAT(ORC_PREFIX, name)
+
+/* Number of elementwise expression cases understood by expr_case(). */
+#define ORC_NUM_EXPR_CASES 10
+
+/*
+ * Elementwise expression cases evaluated through MapExp (tensor_cpu-inl.h:143-201).
+ *   0  dst  = F<sigmoid>(A*B + 0.5f*C) + repmat(bias, rows)     sigmoid(a)=1.0f/(1.0f+expf(-a))
+ *   1  dst += A*2.0f - B/C
+ *   2  dst  = F<clip_mul>(A, B) * C          clip_mul(a,b) = a > b ? a*b : b
+ *   3  dst *= A + 1.5f
+ *   4  dst -= A * B
+ *   5  dst /= C*C + 1.0f
+ *   6  dst  = 3.25f                          (scalar broadcast, all-zero shape sentinel)
+ *   7  dst  = F<fma3>(A, B, C)               fma3(a,b,c) = a*b + c   (ternary map)
+ *   8  dst  = broadcast<0>(bias_rows, shape) * A + B   bias_rows has `rows` entries
+ *   9  dst  = F<square>(A - 1.0f) / (B*B + 2.0f) + C   square(a) = a*a
+ * `bias` holds max(rows, cols) floats.
+ */
+void ORC(expr_case)(int id, float *dst, const float *A, const float *B, const float *C,
+                    const float *bias, int64_t rows, int64_t cols, int64_t ld_dst,
+                    int64_t ld_a, int64_t ld_b, int64_t ld_c);
+
+/* dst[x] <saver>= scale * Reduce_y src(y,x)     (tensor_cpu-inl.h:203-228) */
+void ORC(reduce_keep_lowest)(float *dst, const float *src, int64_t rows, int64_t cols,
+                             int64_t ld, float scale, int saver, int reducer);
+
+/* dst[c] <saver>= scale * Reduce_{n,y,x} src((n*C+c)*H+y, x)   (tensor_cpu-inl.h:230-268) */
+void ORC(reduce_keep_highdim)(float *dst, const float *src, int64_t n, int64_t c, int64_t h,
+                              int64_t w, int64_t ld, float scale, int saver, int reducer);
+
+/* row softmax (tensor_cpu-inl.h:270-285, 464-472) */
+void ORC(softmax)(float *dst, const float *src, int64_t rows, int64_t cols, int64_t ld_dst,
+                  int64_t ld_src);
+
+/*
+ * SoftmaxGrad family (tensor_cpu-inl.h:287-368).  mode bit0 = label smoothing with
+ * `alpha`, bit1 = rows whose label equals `ignore_label` are zero-filled.
+ */
+void ORC(softmax_grad)(float *dst, const float *src, const float *label, int64_t rows,
+                       int64_t cols, int64_t ld_dst, int64_t ld_src, int mode,
+                       float ignore_label, float alpha);
+
+/* pool<Reducer>(src, ky, kx, sy, sx) on `planes` images of h x w (extension/spatial_pool.h:116-149) */
+void ORC(pool)(float *dst, const float *src, int64_t planes, int64_t h, int64_t w, int ky,
+               int kx, int sy, int sx, int64_t ld_src, int64_t ld_dst, int reducer);
+
+/* unpool<Reducer>(src, pooled, grad_pooled, ...) (extension/spatial_unpool.h:93-132) */
+void ORC(unpool)(float *dst, const float *src, const float *pooled, const float *gpooled,
+                 int64_t planes, int64_t h, int64_t w, int64_t ph, int64_t pw, int ky, int kx,
+                 int sy, int sx, int64_t ld_src, int64_t ld_pooled, int64_t ld_dst,
+                 int reducer);
+
+/* chpool<Reducer>(src, nsize, stride, pad) on (n, c, h, w) (extension/channel_pool.h:21-104) */
+void ORC(chpool)(float *dst, const float *src, int64_t n, int64_t c, int64_t h, int64_t w,
+                 int nsize, int stride, int pad, int64_t ld_src, int64_t ld_dst, int reducer);
+
+/* dst[clip(index[y])] += src[y]  (tensor_cpu-inl.h:497-508) */
+void ORC(addtakegrad)(float *dst, const int32_t *index, const float *src, int64_t k,
+                      int64_t d, int64_t nidx, int64_t ld_dst, int64_t ld_src);
+
+/* dst[sorted[y]] += src[index[y]]  (tensor_cpu-inl.h:510-518) */
+void ORC(addtakegrad_largebatch)(float *dst, const int32_t *sorted, const int32_t *index,
+                                 const float *src, int64_t k, int64_t d, int64_t nidx);
+
+/* stable key/value sort, ascending or descending (tensor_cpu-inl.h:531-560) */
+void ORC(sort_by_key)(int32_t *keys, int32_t *values, int64_t n, int ascend);
+
+/* number of OpenMP threads the library will use (for cpu_baseline.cores) */
+int ORC(num_threads)(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif  /* MSHADOW_B200_ORACLE_H_ */

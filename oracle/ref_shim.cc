@@ -1,0 +1,193 @@
+/*
+ * C entry points around the UNMODIFIED reference CPU evaluator -- TEST INFRASTRUCTURE ONLY.
+ *
+ * This file contains no arithmetic of its own: every function wraps caller memory in
+ * mshadow::Tensor<cpu,...> handles and calls the reference's public API, so that the
+ * results are, by construction, what dmlc/mshadow computes on the CPU.  It is compiled
+ * against the reference headers where they lie (include path only; see the Makefile)
+ * into oracle/_ref/libmshadow_ref.so, which is used to pin oracle.c, to generate the
+ * fixtures under tests/golden/, and as the timed CPU baseline of the benchmark.
+ *
+ * The exported names are those of oracle.h with a ref_ prefix.
+ */
+#define ORC_PREFIX ref_
+#include "oracle.h"
+
+#include <cmath>
+#include <vector>
+#ifdef _OPENMP
+#include <omp.h>
+#endif
+
+#include "mshadow/tensor.h"
+
+using namespace mshadow;
+using namespace mshadow::expr;
+
+namespace {
+
+typedef Tensor<cpu, 1, float> T1;
+typedef Tensor<cpu, 2, float> T2;
+typedef Tensor<cpu, 4, float> T4;
+
+inline T2 mat(const float *p, int64_t rows, int64_t cols, int64_t ld) {
+  return T2(const_cast<float *>(p), Shape2(rows, cols), static_cast<index_t>(ld), NULL);
+}
+inline T1 vec(const float *p, int64_t n) {
+  return T1(const_cast<float *>(p), Shape1(n), static_cast<index_t>(n), NULL);
+}
+inline T4 img(const float *p, int64_t n, int64_t c, int64_t h, int64_t w, int64_t ld) {
+  return T4(const_cast<float *>(p), Shape4(n, c, h, w), static_cast<index_t>(ld), NULL);
+}
+
+/* user-defined operators in the style of guide/defop.cpp and guide/README.md:152-157 */
+struct sigmoid {
+  MSHADOW_XINLINE static float Map(float a) { return 1.0f / (1.0f + expf(-a)); }
+};
+struct clip_mul {
+  MSHADOW_XINLINE static float Map(float a, float b) { return a > b ? a * b : b; }
+};
+struct fma3 {
+  MSHADOW_XINLINE static float Map(float a, float b, float c) { return a * b + c; }
+};
+struct square {
+  MSHADOW_XINLINE static float Map(float a) { return a * a; }
+};
+
+template <typename Reducer>
+void keep_lowest(T1 d, const T2 &s, float scale, int saver) {
+  switch (saver) {
+    case 0: MapReduceKeepLowest<sv::saveto, Reducer>(&d, s, scale); break;
+    case 1: MapReduceKeepLowest<sv::plusto, Reducer>(&d, s, scale); break;
+    case 2: MapReduceKeepLowest<sv::minusto, Reducer>(&d, s, scale); break;
+    case 3: MapReduceKeepLowest<sv::multo, Reducer>(&d, s, scale); break;
+    default: MapReduceKeepLowest<sv::divto, Reducer>(&d, s, scale); break;
+  }
+}
+
+template <typename Reducer>
+void keep_dim1(T1 d, const T4 &s, float scale, int saver) {
+  switch (saver) {
+    case 0: MapReduceKeepHighDim<sv::saveto, Reducer, 1>(&d, s, scale); break;
+    case 1: MapReduceKeepHighDim<sv::plusto, Reducer, 1>(&d, s, scale); break;
+    case 2: MapReduceKeepHighDim<sv::minusto, Reducer, 1>(&d, s, scale); break;
+    case 3: MapReduceKeepHighDim<sv::multo, Reducer, 1>(&d, s, scale); break;
+    default: MapReduceKeepHighDim<sv::divto, Reducer, 1>(&d, s, scale); break;
+  }
+}
+
+}  // namespace
+
+extern "C" {
+
+void ref_expr_case(int id, float *dst, const float *A, const float *B, const float *C,
+                   const float *bias, int64_t rows, int64_t cols, int64_t ld_dst, int64_t ld_a,
+                   int64_t ld_b, int64_t ld_c) {
+  T2 d = mat(dst, rows, cols, ld_dst);
+  T2 a = mat(A, rows, cols, ld_a), b = mat(B, rows, cols, ld_b), c = mat(C, rows, cols, ld_c);
+  switch (id) {
+    case 0: d = F<sigmoid>(a * b + 0.5f * c) + repmat(vec(bias, cols), rows); break;
+    case 1: d += a * 2.0f - b / c; break;
+    case 2: d = F<clip_mul>(a, b) * c; break;
+    case 3: d *= a + 1.5f; break;
+    case 4: d -= a * b; break;
+    case 5: d /= c * c + 1.0f; break;
+    case 6: d = 3.25f; break;
+    case 7: d = F<fma3>(a, b, c); break;
+    case 8: d = broadcast<0>(vec(bias, rows), d.shape_) * a + b; break;
+    default: d = F<square>(a - 1.0f) / (b * b + 2.0f) + c; break;
+  }
+}
+
+void ref_reduce_keep_lowest(float *dst, const float *src, int64_t rows, int64_t cols,
+                            int64_t ld, float scale, int saver, int reducer) {
+  T1 d = vec(dst, cols);
+  T2 s = mat(src, rows, cols, ld);
+  if (reducer == 0) keep_lowest<red::sum>(d, s, scale, saver);
+  else if (reducer == 1) keep_lowest<red::maximum>(d, s, scale, saver);
+  else keep_lowest<red::minimum>(d, s, scale, saver);
+}
+
+void ref_reduce_keep_highdim(float *dst, const float *src, int64_t n, int64_t c, int64_t h,
+                             int64_t w, int64_t ld, float scale, int saver, int reducer) {
+  T1 d = vec(dst, c);
+  T4 s = img(src, n, c, h, w, ld);
+  if (reducer == 0) keep_dim1<red::sum>(d, s, scale, saver);
+  else if (reducer == 1) keep_dim1<red::maximum>(d, s, scale, saver);
+  else keep_dim1<red::minimum>(d, s, scale, saver);
+}
+
+void ref_softmax(float *dst, const float *src, int64_t rows, int64_t cols, int64_t ld_dst,
+                 int64_t ld_src) {
+  Softmax(mat(dst, rows, cols, ld_dst), mat(src, rows, cols, ld_src));
+}
+
+void ref_softmax_grad(float *dst, const float *src, const float *label, int64_t rows,
+                      int64_t cols, int64_t ld_dst, int64_t ld_src, int mode,
+                      float ignore_label, float alpha) {
+  T2 d = mat(dst, rows, cols, ld_dst), s = mat(src, rows, cols, ld_src);
+  T1 l = vec(label, rows);
+  switch (mode & 3) {
+    case 0: SoftmaxGrad(d, s, l); break;
+    case 1: SmoothSoftmaxGrad(d, s, l, alpha); break;
+    case 2: SoftmaxGrad(d, s, l, ignore_label); break;
+    default: SmoothSoftmaxGrad(d, s, l, ignore_label, alpha); break;
+  }
+}
+
+void ref_pool(float *dst, const float *src, int64_t planes, int64_t h, int64_t w, int ky,
+              int kx, int sy, int sx, int64_t ld_src, int64_t ld_dst, int reducer) {
+  const int64_t ph = (h - ky) / sy + 1, pw = (w - kx) / sx + 1;
+  T4 s = img(src, 1, planes, h, w, ld_src), d = img(dst, 1, planes, ph, pw, ld_dst);
+  if (reducer == 0) d = pool<red::sum>(s, ky, kx, sy, sx);
+  else if (reducer == 1) d = pool<red::maximum>(s, ky, kx, sy, sx);
+  else d = pool<red::minimum>(s, ky, kx, sy, sx);
+}
+
+void ref_unpool(float *dst, const float *src, const float *pooled, const float *gpooled,
+                int64_t planes, int64_t h, int64_t w, int64_t ph, int64_t pw, int ky, int kx,
+                int sy, int sx, int64_t ld_src, int64_t ld_pooled, int64_t ld_dst,
+                int reducer) {
+  T4 s = img(src, 1, planes, h, w, ld_src), d = img(dst, 1, planes, h, w, ld_dst);
+  T4 p = img(pooled, 1, planes, ph, pw, ld_pooled), g = img(gpooled, 1, planes, ph, pw, ld_pooled);
+  if (reducer == 0) d = unpool<red::sum>(s, p, g, ky, kx, sy, sx);
+  else if (reducer == 1) d = unpool<red::maximum>(s, p, g, ky, kx, sy, sx);
+  else d = unpool<red::minimum>(s, p, g, ky, kx, sy, sx);
+}
+
+void ref_chpool(float *dst, const float *src, int64_t n, int64_t c, int64_t h, int64_t w,
+                int nsize, int stride, int pad, int64_t ld_src, int64_t ld_dst, int reducer) {
+  const int64_t co = (c - nsize + pad * 2 + 1) / stride;
+  T4 s = img(src, n, c, h, w, ld_src), d = img(dst, n, co, h, w, ld_dst);
+  if (reducer == 0) d = chpool<red::sum>(s, nsize, stride, pad);
+  else if (reducer == 1) d = chpool<red::maximum>(s, nsize, stride, pad);
+  else d = chpool<red::minimum>(s, nsize, stride, pad);
+}
+
+void ref_addtakegrad(float *dst, const int32_t *index, const float *src, int64_t k, int64_t d,
+                     int64_t nidx, int64_t ld_dst, int64_t ld_src) {
+  Tensor<cpu, 1, int32_t> idx(const_cast<int32_t *>(index), Shape1(nidx), nidx, NULL);
+  AddTakeGrad(mat(dst, k, d, ld_dst), idx, mat(src, nidx, d, ld_src));
+}
+
+void ref_addtakegrad_largebatch(float *dst, const int32_t *sorted, const int32_t *index,
+                                const float *src, int64_t k, int64_t d, int64_t nidx) {
+  Tensor<cpu, 1, int32_t> s(const_cast<int32_t *>(sorted), Shape1(nidx), nidx, NULL);
+  Tensor<cpu, 1, int32_t> i(const_cast<int32_t *>(index), Shape1(nidx), nidx, NULL);
+  AddTakeGradLargeBatch(mat(dst, k, d, d), s, i, mat(src, nidx, d, d));
+}
+
+void ref_sort_by_key(int32_t *keys, int32_t *values, int64_t n, int ascend) {
+  Tensor<cpu, 1, int32_t> k(keys, Shape1(n), n, NULL), v(values, Shape1(n), n, NULL);
+  SortByKey(k, v, ascend != 0);
+}
+
+int ref_num_threads(void) {
+#ifdef _OPENMP
+  return omp_get_max_threads();
+#else
+  return 1;
+#endif
+}
+
+}  // extern "C"

@@ -1,0 +1,155 @@
+"""ctypes bindings for the two CPU checkers under oracle/ (test infrastructure).
+
+`load("orc")` binds oracle/liboracle.so (the plain-C restatement); `load("ref")` binds
+oracle/_ref/libmshadow_ref.so (the unmodified reference headers behind a C shim) and
+returns None when that file has not been built.  Both expose the same numpy-level API,
+so a test can run the same call against either one.
+"""
+import ctypes as C
+import os
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+PATHS = {
+    "orc": os.path.join(ROOT, "oracle", "liboracle.so"),
+    "ref": os.path.join(ROOT, "oracle", "_ref", "libmshadow_ref.so"),
+}
+
+_f32p = C.POINTER(C.c_float)
+_i32p = C.POINTER(C.c_int32)
+i64 = C.c_int64
+
+
+def _fp(a):
+    assert a.dtype == np.float32
+    return a.ctypes.data_as(_f32p)
+
+
+def _ip(a):
+    assert a.dtype == np.int32 and a.flags.c_contiguous
+    return a.ctypes.data_as(_i32p)
+
+
+def _ld(a):
+    """Leading dimension (elements) of a 2-D+ array whose last axis is dense."""
+    assert a.strides[-1] == 4
+    return a.strides[-2] // 4 if a.ndim >= 2 else a.shape[0]
+
+
+class Checker:
+    def __init__(self, kind):
+        self.kind = kind
+        self.lib = C.CDLL(PATHS[kind])
+        self.p = kind + "_"
+        self.lib[self.p + "num_threads"].restype = C.c_int
+
+    def _fn(self, name):
+        f = self.lib[self.p + name]
+        f.restype = None
+        return f
+
+    def num_threads(self):
+        return int(self.lib[self.p + "num_threads"]())
+
+    # ---- elementwise -------------------------------------------------------------
+    def expr_case(self, cid, dst, A, B, Cm, bias):
+        rows, cols = dst.shape
+        self._fn("expr_case")(C.c_int(cid), _fp(dst), _fp(A), _fp(B), _fp(Cm), _fp(bias),
+                              i64(rows), i64(cols), i64(_ld(dst)), i64(_ld(A)), i64(_ld(B)),
+                              i64(_ld(Cm)))
+        return dst
+
+    # ---- reductions --------------------------------------------------------------
+    def reduce_keep_lowest(self, dst, src, scale=1.0, saver=0, reducer=0):
+        rows, cols = src.shape
+        self._fn("reduce_keep_lowest")(_fp(dst), _fp(src), i64(rows), i64(cols), i64(_ld(src)),
+                                       C.c_float(scale), C.c_int(saver), C.c_int(reducer))
+        return dst
+
+    def reduce_keep_highdim(self, dst, src, scale=1.0, saver=0, reducer=0):
+        n, c, h, w = src.shape
+        self._fn("reduce_keep_highdim")(_fp(dst), _fp(src), i64(n), i64(c), i64(h), i64(w),
+                                        i64(_ld(src)), C.c_float(scale), C.c_int(saver),
+                                        C.c_int(reducer))
+        return dst
+
+    # ---- softmax -----------------------------------------------------------------
+    def softmax(self, dst, src):
+        rows, cols = src.shape
+        self._fn("softmax")(_fp(dst), _fp(src), i64(rows), i64(cols), i64(_ld(dst)),
+                            i64(_ld(src)))
+        return dst
+
+    def softmax_grad(self, dst, src, label, mode=0, ignore_label=0.0, alpha=0.0):
+        rows, cols = src.shape
+        self._fn("softmax_grad")(_fp(dst), _fp(src), _fp(label), i64(rows), i64(cols),
+                                 i64(_ld(dst)), i64(_ld(src)), C.c_int(mode),
+                                 C.c_float(ignore_label), C.c_float(alpha))
+        return dst
+
+    # ---- pooling -----------------------------------------------------------------
+    def pool(self, dst, src, ky, kx, sy, sx, reducer=1):
+        planes, h, w = src.shape
+        self._fn("pool")(_fp(dst), _fp(src), i64(planes), i64(h), i64(w), C.c_int(ky),
+                         C.c_int(kx), C.c_int(sy), C.c_int(sx), i64(_ld(src)), i64(_ld(dst)),
+                         C.c_int(reducer))
+        return dst
+
+    def unpool(self, dst, src, pooled, gpooled, ky, kx, sy, sx, reducer=1):
+        planes, h, w = src.shape
+        _, ph, pw = pooled.shape
+        assert _ld(pooled) == _ld(gpooled)
+        self._fn("unpool")(_fp(dst), _fp(src), _fp(pooled), _fp(gpooled), i64(planes), i64(h),
+                           i64(w), i64(ph), i64(pw), C.c_int(ky), C.c_int(kx), C.c_int(sy),
+                           C.c_int(sx), i64(_ld(src)), i64(_ld(pooled)), i64(_ld(dst)),
+                           C.c_int(reducer))
+        return dst
+
+    def chpool(self, dst, src, nsize, stride=1, pad=None, reducer=0):
+        n, c, h, w = src.shape
+        pad = nsize // 2 if pad is None else pad
+        self._fn("chpool")(_fp(dst), _fp(src), i64(n), i64(c), i64(h), i64(w), C.c_int(nsize),
+                           C.c_int(stride), C.c_int(pad), i64(_ld(src)), i64(_ld(dst)),
+                           C.c_int(reducer))
+        return dst
+
+    # ---- embedding backward ------------------------------------------------------
+    def addtakegrad(self, dst, index, src):
+        k, d = dst.shape
+        self._fn("addtakegrad")(_fp(dst), _ip(index), _fp(src), i64(k), i64(d),
+                                i64(index.shape[0]), i64(_ld(dst)), i64(_ld(src)))
+        return dst
+
+    def addtakegrad_largebatch(self, dst, sorted_, index, src):
+        k, d = dst.shape
+        assert dst.flags.c_contiguous and src.flags.c_contiguous
+        self._fn("addtakegrad_largebatch")(_fp(dst), _ip(sorted_), _ip(index), _fp(src), i64(k),
+                                           i64(d), i64(index.shape[0]))
+        return dst
+
+    def sort_by_key(self, keys, values, ascend=True):
+        self._fn("sort_by_key")(_ip(keys), _ip(values), i64(keys.shape[0]),
+                                C.c_int(1 if ascend else 0))
+        return keys, values
+
+
+_cache = {}
+
+
+def load(kind):
+    if kind not in _cache:
+        _cache[kind] = Checker(kind) if os.path.exists(PATHS[kind]) else None
+    return _cache[kind]
+
+
+def pool_out(h, k, s):
+    return (h - k) // s + 1
+
+
+def pitched(rng_array, pad):
+    """Return a view of a copy of `rng_array` whose rows are `pad` elements apart wider."""
+    shape = rng_array.shape
+    buf = np.full(shape[:-1] + (shape[-1] + pad,), np.float32(7.5), dtype=np.float32)
+    buf[..., : shape[-1]] = rng_array
+    return buf[..., : shape[-1]]

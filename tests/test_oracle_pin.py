@@ -1,0 +1,247 @@
+"""Pins the plain-C oracle to the reference.
+
+Two anchors: (1) bit-for-bit agreement with the unmodified reference headers compiled
+into oracle/_ref/libmshadow_ref.so (skipped where that library was never built), and
+(2) the known-answer cases the reference's own tests and guides describe
+(test/test.cu ramp tensor, test/pairtest.cu 6x6 ramp pooling, all-ones pooling cases).
+The committed fixtures under tests/golden/ are covered by test_golden.py.
+"""
+import numpy as np
+import pytest
+
+import cpu_checkers as cc
+from cpu_checkers import pitched, pool_out
+
+orc = cc.load("orc")
+ref = cc.load("ref")
+needs_ref = pytest.mark.skipif(ref is None, reason="reference build (oracle/_ref) not present")
+
+NUM_EXPR_CASES = 10
+
+
+def bits(a):
+    return np.ascontiguousarray(a).view(np.uint32)
+
+
+def same_bits(a, b):
+    return np.array_equal(bits(a), bits(b))
+
+
+def rnd(rng, shape, lo=-1.0, hi=1.0):
+    return rng.uniform(lo, hi, size=shape).astype(np.float32)
+
+
+# ---------------------------------------------------------------- reference pins
+@needs_ref
+@pytest.mark.parametrize("cid", range(NUM_EXPR_CASES))
+@pytest.mark.parametrize("shape,pad", [((7, 13), 0), ((33, 64), 0), ((5, 100), 4), ((3, 31), 1),
+                                       ((64, 257), 7)])
+def test_expr_cases_match_reference(cid, shape, pad):
+    rng = np.random.default_rng(100 + cid)
+    A, B, Cm = (pitched(rnd(rng, shape), pad) for _ in range(3))
+    Cm = pitched(rnd(rng, shape, 0.5, 1.5), pad)
+    bias = rng.standard_normal(max(shape)).astype(np.float32)
+    d0 = rnd(rng, shape, 0.5, 2.0)
+    outs = []
+    for lib in (orc, ref):
+        d = pitched(d0, pad)
+        lib.expr_case(cid, d, A, B, Cm, bias)
+        outs.append(np.array(d))
+    assert same_bits(*outs)
+
+
+@needs_ref
+@pytest.mark.parametrize("reducer", [0, 1, 2])
+@pytest.mark.parametrize("saver", [0, 1, 2, 3, 4])
+def test_reductions_match_reference(reducer, saver):
+    rng = np.random.default_rng(7 * reducer + saver)
+    src = pitched(rng.standard_normal((67, 45)).astype(np.float32), 3)
+    t4 = pitched(rng.standard_normal((5, 6, 7, 9)).astype(np.float32), 2)
+    for fn, s, n in (("reduce_keep_lowest", src, 45), ("reduce_keep_highdim", t4, 6)):
+        d0 = rnd(rng, (n,), 1.0, 2.0)
+        outs = []
+        for lib in (orc, ref):
+            d = d0.copy()
+            getattr(lib, fn)(d, s, scale=0.75, saver=saver, reducer=reducer)
+            outs.append(d)
+        assert same_bits(*outs), fn
+
+
+@needs_ref
+@pytest.mark.parametrize("rows,cols,pad", [(1, 1, 0), (4, 8, 0), (9, 1000, 0), (3, 33, 5)])
+def test_softmax_family_matches_reference(rows, cols, pad):
+    rng = np.random.default_rng(rows * 1000 + cols)
+    src = pitched((2.0 * rng.standard_normal((rows, cols))).astype(np.float32), pad)
+    outs = []
+    for lib in (orc, ref):
+        d = pitched(np.zeros((rows, cols), np.float32), pad)
+        lib.softmax(d, src)
+        outs.append(np.array(d))
+    assert same_bits(*outs)
+    prob = outs[0]
+    label = rng.integers(0, cols, size=rows).astype(np.float32)
+    label[0] = cols - 1
+    if cols == 1:
+        return  # smooth variants divide by cols-1
+    for mode in range(4):
+        res = []
+        for lib in (orc, ref):
+            d = np.full((rows, cols), 9.0, np.float32)
+            lib.softmax_grad(d, prob, label, mode=mode, ignore_label=float(label[-1]),
+                             alpha=0.1)
+            res.append(d)
+        assert same_bits(*res), mode
+
+
+@needs_ref
+@pytest.mark.parametrize("reducer", [0, 1, 2])
+@pytest.mark.parametrize("h,w,ky,kx,sy,sx,pad", [(6, 6, 2, 2, 2, 2, 0), (13, 11, 3, 3, 2, 2, 0),
+                                                 (8, 9, 3, 2, 1, 3, 3), (7, 7, 7, 7, 1, 1, 0),
+                                                 (10, 10, 2, 2, 3, 3, 0)])
+def test_pool_unpool_match_reference(reducer, h, w, ky, kx, sy, sx, pad):
+    rng = np.random.default_rng(h * w + reducer)
+    # quantised values force ties, which exercise the equality mask of unpool
+    src = pitched((rng.integers(0, 4, size=(5, h, w)) * 0.25).astype(np.float32), pad)
+    ph, pw = pool_out(h, ky, sy), pool_out(w, kx, sx)
+    res = []
+    for lib in (orc, ref):
+        p = np.zeros((5, ph, pw), np.float32)
+        lib.pool(p, src, ky, kx, sy, sx, reducer=reducer)
+        g = rnd(np.random.default_rng(3), (5, ph, pw), 0.0, 1.0)
+        u = pitched(np.zeros((5, h, w), np.float32), pad)
+        lib.unpool(u, src, p, g, ky, kx, sy, sx, reducer=reducer)
+        res.append((p, np.array(u)))
+    assert same_bits(res[0][0], res[1][0])
+    assert same_bits(res[0][1], res[1][1])
+
+
+@needs_ref
+@pytest.mark.parametrize("reducer", [0, 1])
+@pytest.mark.parametrize("c,nsize,stride,pad", [(8, 5, 1, 2), (7, 3, 1, 1), (9, 3, 2, 1),
+                                                (5, 5, 1, 2), (6, 1, 1, 0)])
+def test_chpool_matches_reference(reducer, c, nsize, stride, pad):
+    rng = np.random.default_rng(c + nsize)
+    src = pitched(rnd(rng, (3, c, 4, 6)), 2)
+    co = (c - nsize + 2 * pad + 1) // stride
+    res = []
+    for lib in (orc, ref):
+        d = np.zeros((3, co, 4, 6), np.float32)
+        lib.chpool(d, src, nsize, stride, pad, reducer=reducer)
+        res.append(d)
+    assert same_bits(*res)
+
+
+@needs_ref
+def test_addtakegrad_matches_reference():
+    rng = np.random.default_rng(5)
+    k, d, n = 11, 20, 300
+    src = rnd(rng, (n, d))
+    idx = rng.integers(-3, k + 3, size=n).astype(np.int32)  # AddTakeGrad clips
+    res = []
+    for lib in (orc, ref):
+        t = rnd(np.random.default_rng(1), (k, d))
+        lib.addtakegrad(t, idx, src)
+        res.append(t)
+    assert same_bits(*res)
+    inb = np.clip(idx, 0, k - 1).astype(np.int32)
+    res = []
+    for lib in (orc, ref):
+        keys, vals = inb.copy(), np.arange(n, dtype=np.int32)
+        lib.sort_by_key(keys, vals, True)
+        t = rnd(np.random.default_rng(1), (k, d))
+        lib.addtakegrad_largebatch(t, keys, vals, src)
+        res.append((keys, vals, t))
+    assert np.array_equal(res[0][0], res[1][0]) and np.array_equal(res[0][1], res[1][1])
+    assert same_bits(res[0][2], res[1][2])
+    for asc in (True, False):
+        pair = []
+        for lib in (orc, ref):
+            keys, vals = inb.copy(), np.arange(n, dtype=np.int32)
+            lib.sort_by_key(keys, vals, asc)
+            pair.append((keys, vals))
+        assert np.array_equal(pair[0][0], pair[1][0]) and np.array_equal(pair[0][1], pair[1][1])
+
+
+# ---------------------------------------------------------------- known answers
+def test_ramp_tensor_known_answers():
+    """test/test.cu:12-18 fills (3,2,4) with i*0.1+j*0.2+k*0.1 and reduces batch 0."""
+    t = np.zeros((3, 2, 4), np.float32)
+    for i in range(3):
+        for j in range(2):
+            for k in range(4):
+                t[i, j, k] = np.float32(i * np.float32(0.1) + j * np.float32(0.2)) + \
+                    np.float32(k * np.float32(0.1))
+    d = np.zeros(4, np.float32)
+    orc.reduce_keep_lowest(d, t[0])
+    assert np.allclose(d, [0.2, 0.4, 0.6, 0.8], atol=1e-6)
+    d3 = np.zeros(3, np.float32)
+    # sumall_except_dim<0> of a 3-D tensor == keep-high-dim with n=1, c=3
+    orc.reduce_keep_highdim(d3, t.reshape(1, 3, 2, 4))
+    assert np.allclose(d3, [2.0, 2.8, 3.6], atol=1e-5)
+    sm = np.zeros((2, 4), np.float32)
+    orc.softmax(sm, t[0])
+    assert np.allclose(sm.sum(axis=1), 1.0, atol=1e-6)
+    e = np.exp(t[0].astype(np.float64))
+    assert np.allclose(sm, e / e.sum(axis=1, keepdims=True), atol=1e-6)
+
+
+def test_pairtest_ramp_pooling_known_answers():
+    """test/pairtest.cu:34-39,52-76: 6x6 ramp, max pool K=2 stride 2, unpool of grad 0.1."""
+    src = np.arange(36, dtype=np.float32).reshape(1, 6, 6)
+    p = np.zeros((1, 3, 3), np.float32)
+    orc.pool(p, src, 2, 2, 2, 2, reducer=1)
+    assert np.array_equal(p[0], [[7, 9, 11], [19, 21, 23], [31, 33, 35]])
+    g = np.full((1, 3, 3), 0.1, np.float32)
+    u = np.zeros((1, 6, 6), np.float32)
+    orc.unpool(u, src, p, g, 2, 2, 2, 2, reducer=1)
+    want = np.zeros((6, 6), np.float32)
+    want[1::2, 1::2] = np.float32(0.1)
+    assert np.array_equal(u[0], want)
+    s = np.zeros((1, 3, 3), np.float32)
+    orc.pool(s, src, 2, 2, 2, 2, reducer=0)
+    assert np.array_equal(s[0], [[14, 22, 30], [62, 70, 78], [110, 118, 126]])
+
+
+def test_all_ones_known_answers():
+    """Constant planes: every tied position receives the gradient; chpool clamps."""
+    x = np.ones((2 * 3, 6, 6), np.float32)
+    p = np.zeros((6, 2, 2), np.float32)
+    orc.pool(p, x, 3, 3, 2, 2, reducer=1)
+    assert np.all(p == 1.0)
+    u = np.zeros_like(x)
+    orc.unpool(u, x, p, p, 3, 3, 2, 2, reducer=1)
+    assert u[0, 2, 2] == 4.0 and u[0, 0, 0] == 1.0 and u[0, 5, 5] == 0.0
+    x4 = np.ones((2, 3, 6, 6), np.float32)
+    c = np.zeros_like(x4)
+    orc.chpool(c, x4, 3)
+    assert np.all(c[:, 0] == 2.0) and np.all(c[:, 1] == 3.0) and np.all(c[:, 2] == 2.0)
+    d = np.zeros(3, np.float32)
+    orc.reduce_keep_highdim(d, x4)
+    assert np.all(d == 72.0)
+    sm = np.zeros((1, 8), np.float32)
+    orc.softmax(sm, np.full((1, 8), 3.0, np.float32))
+    assert np.all(sm == 0.125)
+
+
+def test_softmax_grad_label_edges():
+    prob = np.full((3, 5), 0.2, np.float32)
+    label = np.array([0, 4, 2], np.float32)
+    d = np.zeros_like(prob)
+    orc.softmax_grad(d, prob, label)
+    want = prob.copy()
+    want[0, 0] -= 1
+    want[1, 4] -= 1
+    want[2, 2] -= 1
+    assert np.array_equal(d, want)
+    orc.softmax_grad(d, prob, label, mode=2, ignore_label=4.0)
+    assert np.all(d[1] == 0.0) and np.array_equal(d[0], want[0])
+
+
+def test_addtakegrad_clips_and_sort_is_stable():
+    t = np.zeros((3, 2), np.float32)
+    orc.addtakegrad(t, np.array([-5, 7, 1, 1], np.int32), np.ones((4, 2), np.float32))
+    assert np.array_equal(t[:, 0], [1, 2, 1])
+    keys = np.array([2, 0, 2, 1, 0], np.int32)
+    vals = np.arange(5, dtype=np.int32)
+    orc.sort_by_key(keys, vals, True)
+    assert list(keys) == [0, 0, 1, 2, 2] and list(vals) == [1, 4, 3, 0, 2]
