@@ -1,0 +1,165 @@
+/*
+ * C ABI of the B200 evaluation engine for the mshadow lazy-evaluation path.
+ *
+ * dmlc/mshadow has no FFI of its own: its public interface is a C++ template header API
+ * (mshadow/tensor.h).  The template part of that interface (expression plans) cannot cross
+ * a C boundary and stays in headers (mshadow_b200/include/mshadow/); everything that is not
+ * a template -- the function-form operators, memory, streams, and fp32 instantiations of
+ * the reductions and pooling expressions -- is exported here with plain pointers and
+ * sizes.  Each entry names the reference interface it stands for (file:line within
+ * dmlc/mshadow).
+ *
+ * Conventions
+ *   - every function returns an msb_status; 0 is success.  Nothing throws or aborts.
+ *     msb_last_error() returns a thread-local, human-readable description of the last
+ *     failure on the calling thread.
+ *   - device pointers are raw CUDA device addresses; `ld_*` are leading dimensions counted
+ *     in elements (mshadow's Tensor::stride_); sizes are int64_t.
+ *   - work is enqueued on `stream` (a cudaStream_t passed as void*; NULL = the legacy
+ *     default stream) and is asynchronous, like every mshadow GPU operation
+ *     (mshadow/tensor_gpu-inl.h:101-156).  The caller synchronises.
+ *   - `saver` selects mshadow's sv::saveto/plusto/minusto/multo/divto as 0..4
+ *     (mshadow/base.h:539-602); `reducer` selects red::sum / maximum / minimum as 0..2
+ *     (mshadow/base.h:604-862).
+ *   - operators may use a library-owned scratch buffer that is cached per (device, stream)
+ *     and released by msb_shutdown(); callers never see it, in keeping with mshadow's
+ *     "no temporary allocation" contract (README.md:19-20 of the reference).
+ */
+#ifndef MSHADOW_B200_C_API_H_
+#define MSHADOW_B200_C_API_H_
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef enum {
+  MSB_OK = 0,
+  MSB_ERR_ARGUMENT = 1,  /* null pointer, negative size, unknown selector */
+  MSB_ERR_SHAPE = 2,     /* shapes of the operands do not agree */
+  MSB_ERR_LAYOUT = 3,    /* operand must be contiguous / sufficiently aligned */
+  MSB_ERR_CUDA = 4,      /* a CUDA runtime call or kernel launch failed */
+  MSB_ERR_MEMORY = 5,    /* allocation failed */
+  MSB_ERR_TIMEOUT = 6    /* a bounded device-side wait gave up */
+} msb_status;
+
+typedef void *msb_stream_t; /* cudaStream_t */
+
+const char *msb_last_error(void);
+int msb_version(void);
+
+/* ---- engine life cycle and streams ------------------------------------------------- */
+
+/* InitTensorEngine<gpu>(dev) / SetDevice<gpu>(dev): mshadow/tensor_gpu-inl.h:14-36 */
+int msb_init(int device);
+int msb_set_device(int device);
+/* ShutdownTensorEngine<gpu>(): additionally frees every cached scratch buffer */
+int msb_shutdown(void);
+/* NewStream<gpu> / DeleteStream / Stream<gpu>::Wait / CheckIdle: mshadow/stream_gpu-inl.h:18-211 */
+int msb_stream_create(msb_stream_t *out);
+int msb_stream_destroy(msb_stream_t stream);
+int msb_stream_wait(msb_stream_t stream);
+int msb_stream_idle(msb_stream_t stream, int *idle);
+
+/* ---- memory ------------------------------------------------------------------------ */
+
+/* AllocSpace(Tensor<gpu,...>*, pad) / FreeSpace: mshadow/tensor_gpu-inl.h:37-56.
+   rows = product of all but the last extent, cols = last extent.  With pad != 0 and
+   cols >= 64 the rows are pitched; *ld_out receives the resulting stride in elements. */
+int msb_alloc_space(void **dptr_out, int64_t *ld_out, int64_t rows, int64_t cols,
+                    int64_t elem_size, int pad);
+int msb_free_space(void *dptr);
+/* AllocHost<gpu> / FreeHost<gpu> (page-locked host memory): mshadow/tensor_cpu-inl.h:60-92 */
+int msb_alloc_host(void **ptr_out, int64_t bytes);
+int msb_free_host(void *ptr);
+/* Copy(dst, src, stream) in its host->device (1), device->host (2) and device->device (3)
+   forms: mshadow/tensor_gpu-inl.h:57-92.  Honours both strides. */
+int msb_copy_2d(void *dst, int64_t ld_dst, const void *src, int64_t ld_src, int64_t rows,
+                int64_t cols, int64_t elem_size, int kind, msb_stream_t stream);
+/* Scratch buffer of at least `bytes` for work on `stream`; owned by the library. */
+int msb_workspace(msb_stream_t stream, int64_t bytes, void **out);
+
+/* ---- element-wise expressions (MapExp): mshadow/tensor_gpu-inl.h:101-116 -------------
+   Expression plans are C++ templates; these are fixed fp32 instantiations compiled from the
+   header API, exported so that non-C++ callers and the parity tests can reach the fused
+   map kernel.  `id`:
+     0  dst  = F<sigmoid>(A*B + 0.5f*C) + repmat(bias, rows)   sigmoid(a) = 1/(1+exp(-a))
+     1  dst += A*2.0f - B/C
+     2  dst  = F<clip_mul>(A, B) * C          clip_mul(a,b) = a > b ? a*b : b
+     3  dst *= A + 1.5f
+     4  dst -= A * B
+     5  dst /= C*C + 1.0f
+     6  dst  = 3.25f
+     7  dst  = F<fma3>(A, B, C)               fma3(a,b,c) = a*b + c, two roundings
+     8  dst  = broadcast<0>(bias, shape) * A + B      (bias has `rows` entries)
+     9  dst  = F<square>(A - 1.0f) / (B*B + 2.0f) + C
+   `bias` must hold max(rows, cols) floats. */
+int msb_expr_case_f32(int id, float *dst, const float *A, const float *B, const float *C,
+                      const float *bias, int64_t rows, int64_t cols, int64_t ld_dst,
+                      int64_t ld_a, int64_t ld_b, int64_t ld_c, msb_stream_t stream);
+
+/* ---- reductions --------------------------------------------------------------------- */
+
+/* MapReduceKeepLowest<Saver,Reducer>(dst, src, scale) -- e.g. dst = sum_rows(src):
+   mshadow/tensor_gpu-inl.h:118-133, mshadow/extension/reduceto1d.h:77-101 */
+int msb_reduce_keep_lowest_f32(float *dst, const float *src, int64_t rows, int64_t cols,
+                               int64_t ld, float scale, int saver, int reducer,
+                               msb_stream_t stream);
+/* MapReduceKeepHighDim<Saver,Reducer,1>(dst, src(n,c,h,w), scale) -- e.g.
+   dst = sumall_except_dim<1>(src): mshadow/tensor_gpu-inl.h:135-156 */
+int msb_reduce_keep_highdim_f32(float *dst, const float *src, int64_t n, int64_t c, int64_t h,
+                                int64_t w, int64_t ld, float scale, int saver, int reducer,
+                                msb_stream_t stream);
+
+/* ---- softmax family ----------------------------------------------------------------- */
+
+/* Softmax(Tensor<gpu,2>, Tensor<gpu,2>): mshadow/tensor_gpu-inl.h:157-161 */
+int msb_softmax_f32(float *dst, const float *src, int64_t rows, int64_t cols, int64_t ld_dst,
+                    int64_t ld_src, msb_stream_t stream);
+/* SoftmaxGrad / SmoothSoftmaxGrad, with and without ignore_label:
+   mshadow/tensor_gpu-inl.h:169-214.  mode bit0 = smoothing by `alpha`, bit1 = rows whose
+   label equals `ignore_label` become zero.  Labels are floats holding integers. */
+int msb_softmax_grad_f32(float *dst, const float *src, const float *label, int64_t rows,
+                         int64_t cols, int64_t ld_dst, int64_t ld_src, int mode,
+                         float ignore_label, float alpha, msb_stream_t stream);
+
+/* ---- pooling expressions (fp32 instantiations over plain tensors) -------------------- */
+
+/* dst = pool<Reducer>(src, ky, kx, sy, sx) on `planes` images of h x w; output
+   ((h-ky)/sy+1) x ((w-kx)/sx+1): mshadow/extension/spatial_pool.h:20-149 */
+int msb_pool_f32(float *dst, const float *src, int64_t planes, int64_t h, int64_t w, int ky,
+                 int kx, int sy, int sx, int64_t ld_src, int64_t ld_dst, int reducer,
+                 msb_stream_t stream);
+/* dst = unpool<Reducer>(src, pooled, grad_pooled, ky, kx, sy, sx):
+   mshadow/extension/spatial_unpool.h:20-132 */
+int msb_unpool_f32(float *dst, const float *src, const float *pooled, const float *gpooled,
+                   int64_t planes, int64_t h, int64_t w, int64_t ph, int64_t pw, int ky, int kx,
+                   int sy, int sx, int64_t ld_src, int64_t ld_pooled, int64_t ld_dst,
+                   int reducer, msb_stream_t stream);
+/* dst = chpool<Reducer>(src, nsize, stride, pad) on (n, c, h, w):
+   mshadow/extension/channel_pool.h:21-104 */
+int msb_chpool_f32(float *dst, const float *src, int64_t n, int64_t c, int64_t h, int64_t w,
+                   int nsize, int stride, int pad, int64_t ld_src, int64_t ld_dst, int reducer,
+                   msb_stream_t stream);
+
+/* ---- embedding backward --------------------------------------------------------------- */
+
+/* AddTakeGrad(dst, index, src): dst[clip(index[y])] += src[y]:
+   mshadow/tensor_gpu-inl.h:216-221 */
+int msb_addtakegrad_f32_i32(float *dst, const int32_t *index, const float *src, int64_t k,
+                            int64_t d, int64_t nidx, int64_t ld_dst, int64_t ld_src,
+                            msb_stream_t stream);
+/* AddTakeGradLargeBatch(dst, sorted, index, src): dst[sorted[y]] += src[index[y]], all
+   operands contiguous, `sorted` ascending: mshadow/tensor_gpu-inl.h:223-229 */
+int msb_addtakegrad_largebatch_f32_i32(float *dst, const int32_t *sorted, const int32_t *index,
+                                       const float *src, int64_t k, int64_t d, int64_t nidx,
+                                       msb_stream_t stream);
+/* SortByKey(keys, values, is_ascend), stable: mshadow/tensor_gpu-inl.h:231-235 */
+int msb_sort_by_key_i32(int32_t *keys, int32_t *values, int64_t n, int ascend,
+                        msb_stream_t stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* MSHADOW_B200_C_API_H_ */

@@ -1,0 +1,220 @@
+"""ctypes binding of the C ABI in include/mshadow_b200.h.
+
+The shared library is the product; this module only marshals arguments.  Device memory is
+passed as raw addresses, so any owner of CUDA memory works: the helpers below accept objects
+with a ``data_ptr()`` method (torch tensors) and take shapes and strides from them.  There is
+no host fallback: if the library is missing, loading raises; if a call fails, ``MsbError``
+carries the library's own message.
+"""
+import ctypes as C
+import os
+import re
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_HERE, "libmshadow_b200.so")
+HEADER_PATH = os.path.join(os.path.dirname(_HERE), "include", "mshadow_b200.h")
+
+STATUS_NAMES = {0: "MSB_OK", 1: "MSB_ERR_ARGUMENT", 2: "MSB_ERR_SHAPE", 3: "MSB_ERR_LAYOUT",
+                4: "MSB_ERR_CUDA", 5: "MSB_ERR_MEMORY", 6: "MSB_ERR_TIMEOUT"}
+
+SAVETO, PLUSTO, MINUSTO, MULTO, DIVTO = range(5)
+RED_SUM, RED_MAX, RED_MIN = range(3)
+H2D, D2H, D2D = 1, 2, 3
+
+
+class MsbError(RuntimeError):
+    def __init__(self, status, message):
+        super().__init__("%s: %s" % (STATUS_NAMES.get(status, status), message))
+        self.status = status
+
+
+def declared_symbols(header_path=HEADER_PATH):
+    """Names of every function the C header declares."""
+    text = open(header_path).read()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    return sorted(set(re.findall(r"\b(msb_[a-z0-9_]+)\s*\(", text)))
+
+
+i64, f32, cint, vp = C.c_int64, C.c_float, C.c_int, C.c_void_p
+
+_SIGNATURES = {
+    "msb_init": [cint],
+    "msb_set_device": [cint],
+    "msb_shutdown": [],
+    "msb_stream_create": [C.POINTER(vp)],
+    "msb_stream_destroy": [vp],
+    "msb_stream_wait": [vp],
+    "msb_stream_idle": [vp, C.POINTER(cint)],
+    "msb_alloc_space": [C.POINTER(vp), C.POINTER(i64), i64, i64, i64, cint],
+    "msb_free_space": [vp],
+    "msb_alloc_host": [C.POINTER(vp), i64],
+    "msb_free_host": [vp],
+    "msb_copy_2d": [vp, i64, vp, i64, i64, i64, i64, cint, vp],
+    "msb_workspace": [vp, i64, C.POINTER(vp)],
+    "msb_expr_case_f32": [cint, vp, vp, vp, vp, vp, i64, i64, i64, i64, i64, i64, vp],
+    "msb_reduce_keep_lowest_f32": [vp, vp, i64, i64, i64, f32, cint, cint, vp],
+    "msb_reduce_keep_highdim_f32": [vp, vp, i64, i64, i64, i64, i64, f32, cint, cint, vp],
+    "msb_softmax_f32": [vp, vp, i64, i64, i64, i64, vp],
+    "msb_softmax_grad_f32": [vp, vp, vp, i64, i64, i64, i64, cint, f32, f32, vp],
+    "msb_pool_f32": [vp, vp, i64, i64, i64, cint, cint, cint, cint, i64, i64, cint, vp],
+    "msb_unpool_f32": [vp, vp, vp, vp, i64, i64, i64, i64, i64, cint, cint, cint, cint, i64, i64, i64,
+                       cint, vp],
+    "msb_chpool_f32": [vp, vp, i64, i64, i64, i64, cint, cint, cint, i64, i64, cint, vp],
+    "msb_addtakegrad_f32_i32": [vp, vp, vp, i64, i64, i64, i64, i64, vp],
+    "msb_addtakegrad_largebatch_f32_i32": [vp, vp, vp, vp, i64, i64, i64, vp],
+    "msb_sort_by_key_i32": [vp, vp, i64, cint, vp],
+}
+
+
+def _ptr(t):
+    return vp(t.data_ptr() if hasattr(t, "data_ptr") else int(t))
+
+
+def _ld(t):
+    """Leading dimension in elements: distance between consecutive rows of the last axis."""
+    assert t.stride(-1) == 1 or t.shape[-1] <= 1, "last axis must be dense"
+    if t.dim() < 2:
+        return t.shape[0]
+    return t.stride(-2)
+
+
+class Library:
+    """The loaded shared object with typed entry points and status checking."""
+
+    def __init__(self, path=LIB_PATH):
+        if not os.path.exists(path):
+            raise FileNotFoundError(
+                "%s not found: build it with `python -c 'import __graft_entry__ as g; g.build()'`; "
+                "there is no fallback implementation" % path)
+        self.path = path
+        self.dll = C.CDLL(path)
+        self.dll.msb_last_error.restype = C.c_char_p
+        self.dll.msb_version.restype = cint
+        for name, argtypes in _SIGNATURES.items():
+            fn = getattr(self.dll, name)
+            fn.argtypes = argtypes
+            fn.restype = cint
+
+    def call(self, name, *args):
+        status = getattr(self.dll, name)(*args)
+        if status != 0:
+            raise MsbError(status, self.dll.msb_last_error().decode("utf-8", "replace"))
+
+    def status(self, name, *args):
+        """Raw status code without raising (for tests of error behaviour)."""
+        return getattr(self.dll, name)(*args), self.dll.msb_last_error().decode("utf-8", "replace")
+
+    # ---- engine ---------------------------------------------------------------------
+    def init(self, device=0):
+        self.call("msb_init", device)
+
+    def shutdown(self):
+        self.call("msb_shutdown")
+
+    def stream_create(self):
+        s = vp()
+        self.call("msb_stream_create", C.byref(s))
+        return s
+
+    def stream_destroy(self, s):
+        self.call("msb_stream_destroy", s)
+
+    def stream_wait(self, s=None):
+        self.call("msb_stream_wait", s)
+
+    def alloc_space(self, rows, cols, elem_size=4, pad=True):
+        p, ld = vp(), i64()
+        self.call("msb_alloc_space", C.byref(p), C.byref(ld), rows, cols, elem_size, int(pad))
+        return p.value, ld.value
+
+    def free_space(self, p):
+        self.call("msb_free_space", vp(p))
+
+    def alloc_host(self, nbytes):
+        p = vp()
+        self.call("msb_alloc_host", C.byref(p), nbytes)
+        return p.value
+
+    def free_host(self, p):
+        self.call("msb_free_host", vp(p))
+
+    def copy_2d(self, dst, ld_dst, src, ld_src, rows, cols, kind, elem_size=4, stream=None):
+        self.call("msb_copy_2d", _ptr(dst), ld_dst, _ptr(src), ld_src, rows, cols, elem_size, kind, stream)
+
+    # ---- operators (tensor-like arguments) ---------------------------------------------
+    def expr_case(self, cid, dst, A, B, Cm, bias, stream=None):
+        rows, cols = dst.shape
+        self.call("msb_expr_case_f32", cid, _ptr(dst), _ptr(A), _ptr(B), _ptr(Cm), _ptr(bias), rows, cols,
+                  _ld(dst), _ld(A), _ld(B), _ld(Cm), stream)
+        return dst
+
+    def reduce_keep_lowest(self, dst, src, scale=1.0, saver=0, reducer=0, stream=None):
+        rows, cols = src.shape
+        self.call("msb_reduce_keep_lowest_f32", _ptr(dst), _ptr(src), rows, cols, _ld(src), scale, saver,
+                  reducer, stream)
+        return dst
+
+    def reduce_keep_highdim(self, dst, src, scale=1.0, saver=0, reducer=0, stream=None):
+        n, c, h, w = src.shape
+        self.call("msb_reduce_keep_highdim_f32", _ptr(dst), _ptr(src), n, c, h, w, _ld(src), scale, saver,
+                  reducer, stream)
+        return dst
+
+    def softmax(self, dst, src, stream=None):
+        rows, cols = src.shape
+        self.call("msb_softmax_f32", _ptr(dst), _ptr(src), rows, cols, _ld(dst), _ld(src), stream)
+        return dst
+
+    def softmax_grad(self, dst, src, label, mode=0, ignore_label=0.0, alpha=0.0, stream=None):
+        rows, cols = src.shape
+        self.call("msb_softmax_grad_f32", _ptr(dst), _ptr(src), _ptr(label), rows, cols, _ld(dst), _ld(src),
+                  mode, ignore_label, alpha, stream)
+        return dst
+
+    def pool(self, dst, src, ky, kx, sy, sx, reducer=1, stream=None):
+        planes, h, w = src.shape
+        self.call("msb_pool_f32", _ptr(dst), _ptr(src), planes, h, w, ky, kx, sy, sx, _ld(src), _ld(dst),
+                  reducer, stream)
+        return dst
+
+    def unpool(self, dst, src, pooled, gpooled, ky, kx, sy, sx, reducer=1, stream=None):
+        planes, h, w = src.shape
+        _, ph, pw = pooled.shape
+        assert _ld(pooled) == _ld(gpooled)
+        self.call("msb_unpool_f32", _ptr(dst), _ptr(src), _ptr(pooled), _ptr(gpooled), planes, h, w, ph, pw,
+                  ky, kx, sy, sx, _ld(src), _ld(pooled), _ld(dst), reducer, stream)
+        return dst
+
+    def chpool(self, dst, src, nsize, stride=1, pad=None, reducer=0, stream=None):
+        n, c, h, w = src.shape
+        pad = nsize // 2 if pad is None else pad
+        self.call("msb_chpool_f32", _ptr(dst), _ptr(src), n, c, h, w, nsize, stride, pad, _ld(src), _ld(dst),
+                  reducer, stream)
+        return dst
+
+    def addtakegrad(self, dst, index, src, stream=None):
+        k, d = dst.shape
+        self.call("msb_addtakegrad_f32_i32", _ptr(dst), _ptr(index), _ptr(src), k, d, index.shape[0],
+                  _ld(dst), _ld(src), stream)
+        return dst
+
+    def addtakegrad_largebatch(self, dst, sorted_, index, src, stream=None):
+        k, d = dst.shape
+        self.call("msb_addtakegrad_largebatch_f32_i32", _ptr(dst), _ptr(sorted_), _ptr(index), _ptr(src), k,
+                  d, index.shape[0], stream)
+        return dst
+
+    def sort_by_key(self, keys, values, ascend=True, stream=None):
+        self.call("msb_sort_by_key_i32", _ptr(keys), _ptr(values), keys.shape[0], int(ascend), stream)
+        return keys, values
+
+
+_lib = None
+
+
+def load():
+    """The process-wide Library instance."""
+    global _lib
+    if _lib is None:
+        _lib = Library()
+    return _lib

@@ -1,0 +1,419 @@
+/*
+ * extern "C" layer of the B200 mshadow engine (declared in include/mshadow_b200.h).
+ *
+ * Every entry point validates its arguments, wraps the raw pointers in mshadow::Tensor
+ * handles and calls the header-level C++ API, which holds all kernels.  The translation
+ * unit is compiled with DMLC_LOG_FATAL_THROW=1, so a failed CHECK inside the C++ API
+ * surfaces here as a dmlc::Error; it is turned into a status code and a thread-local
+ * message.  Nothing in this file computes on the host and there is no fallback path: if
+ * the CUDA runtime or the device is unusable the call fails with MSB_ERR_CUDA.
+ */
+#include "mshadow_b200.h"
+
+#include <string>
+
+#include "mshadow/tensor.h"
+#include "mshadow/gpu/math.h"
+
+using namespace mshadow;        // NOLINT(*)
+using namespace mshadow::expr;  // NOLINT(*)
+
+namespace {
+
+thread_local std::string g_last_error;
+
+int Fail(int code, const std::string &msg) {
+  g_last_error = msg;
+  return code;
+}
+
+/*! \brief a Stream<gpu> that wraps a caller-owned cudaStream_t for the duration of one call */
+struct BorrowedStream {
+  Stream<gpu> s;
+  explicit BorrowedStream(msb_stream_t raw) { s.stream_ = static_cast<cudaStream_t>(raw); }
+  Stream<gpu> *get() { return &s; }
+};
+
+typedef Tensor<gpu, 1, float> G1;
+typedef Tensor<gpu, 2, float> G2;
+typedef Tensor<gpu, 3, float> G3;
+typedef Tensor<gpu, 4, float> G4;
+
+inline G2 Mat(const float *p, int64_t r, int64_t c, int64_t ld, Stream<gpu> *s) {
+  return G2(const_cast<float *>(p), Shape2(r, c), static_cast<index_t>(ld), s);
+}
+inline G1 Vec(const float *p, int64_t n, Stream<gpu> *s) {
+  return G1(const_cast<float *>(p), Shape1(n), static_cast<index_t>(n), s);
+}
+inline G4 Img(const float *p, int64_t n, int64_t c, int64_t h, int64_t w, int64_t ld, Stream<gpu> *s) {
+  return G4(const_cast<float *>(p), Shape4(n, c, h, w), static_cast<index_t>(ld), s);
+}
+inline G3 Planes(const float *p, int64_t n, int64_t h, int64_t w, int64_t ld, Stream<gpu> *s) {
+  return G3(const_cast<float *>(p), Shape3(n, h, w), static_cast<index_t>(ld), s);
+}
+
+inline bool FitsIndex(int64_t v) { return v >= 0 && v <= 0x7fffffffLL; }
+
+// user-style functors for the exported expression cases (cf. guide/defop.cpp of the reference)
+struct clip_mul {
+  MSHADOW_XINLINE static float Map(float a, float b) { return a > b ? a * b : b; }
+};
+struct fma3 {
+  MSHADOW_XINLINE static float Map(float a, float b, float c) { return a * b + c; }
+};
+struct square {
+  MSHADOW_XINLINE static float Map(float a) { return a * a; }
+};
+
+template <typename Reducer>
+void KeepLowest(G1 d, const G2 &s, float scale, int saver) {
+  switch (saver) {
+    case 0: MapReduceKeepLowest<sv::saveto, Reducer>(&d, s, scale); break;
+    case 1: MapReduceKeepLowest<sv::plusto, Reducer>(&d, s, scale); break;
+    case 2: MapReduceKeepLowest<sv::minusto, Reducer>(&d, s, scale); break;
+    case 3: MapReduceKeepLowest<sv::multo, Reducer>(&d, s, scale); break;
+    default: MapReduceKeepLowest<sv::divto, Reducer>(&d, s, scale); break;
+  }
+}
+template <typename Reducer>
+void KeepDim1(G1 d, const G4 &s, float scale, int saver) {
+  switch (saver) {
+    case 0: MapReduceKeepHighDim<sv::saveto, Reducer, 1>(&d, s, scale); break;
+    case 1: MapReduceKeepHighDim<sv::plusto, Reducer, 1>(&d, s, scale); break;
+    case 2: MapReduceKeepHighDim<sv::minusto, Reducer, 1>(&d, s, scale); break;
+    case 3: MapReduceKeepHighDim<sv::multo, Reducer, 1>(&d, s, scale); break;
+    default: MapReduceKeepHighDim<sv::divto, Reducer, 1>(&d, s, scale); break;
+  }
+}
+
+}  // namespace
+
+#define MSB_GUARD_BEGIN try {
+#define MSB_GUARD_END                                        \
+  }                                                          \
+  catch (const dmlc::Error &e) {                             \
+    const std::string what = e.what();                       \
+    const bool cuda = what.find("CUDA") != std::string::npos || what.find("ErrStr") != std::string::npos; \
+    return Fail(cuda ? MSB_ERR_CUDA : MSB_ERR_SHAPE, what);  \
+  }                                                          \
+  catch (const std::exception &e) {                          \
+    return Fail(MSB_ERR_MEMORY, e.what());                   \
+  }                                                          \
+  return MSB_OK;
+
+#define MSB_REQUIRE(cond, code, msg) \
+  if (!(cond)) return Fail(code, std::string(__func__) + ": " + msg)
+
+extern "C" {
+
+const char *msb_last_error(void) { return g_last_error.c_str(); }
+int msb_version(void) { return 100; }
+
+int msb_init(int device) {
+  MSB_GUARD_BEGIN
+  InitTensorEngine<gpu>(device);
+  MSB_GUARD_END
+}
+int msb_set_device(int device) {
+  MSB_GUARD_BEGIN
+  SetDevice<gpu>(device);
+  MSB_GUARD_END
+}
+int msb_shutdown(void) {
+  MSB_GUARD_BEGIN
+  ShutdownTensorEngine<gpu>();
+  MSB_GUARD_END
+}
+int msb_stream_create(msb_stream_t *out) {
+  MSB_REQUIRE(out != nullptr, MSB_ERR_ARGUMENT, "null output");
+  cudaStream_t s;
+  const cudaError_t err = cudaStreamCreate(&s);
+  if (err != cudaSuccess) return Fail(MSB_ERR_CUDA, cudaGetErrorString(err));
+  *out = s;
+  return MSB_OK;
+}
+int msb_stream_destroy(msb_stream_t stream) {
+  MSB_GUARD_BEGIN
+  gpu_rt::Scratch::Release(false, static_cast<cudaStream_t>(stream));
+  MSHADOW_CUDA_CALL(cudaStreamDestroy(static_cast<cudaStream_t>(stream)));
+  MSB_GUARD_END
+}
+int msb_stream_wait(msb_stream_t stream) {
+  const cudaError_t err = cudaStreamSynchronize(static_cast<cudaStream_t>(stream));
+  if (err != cudaSuccess) return Fail(MSB_ERR_CUDA, cudaGetErrorString(err));
+  // a kernel whose bounded wait ran out leaves a mark in the device status word
+  int flag = 0;
+  int *word = mshadow::cuda::pooldetail::StatusWord();
+  if (cudaMemcpy(&flag, word, sizeof(int), cudaMemcpyDeviceToHost) != cudaSuccess)
+    return Fail(MSB_ERR_CUDA, "cannot read device status word");
+  if (flag != 0) {
+    cudaMemset(word, 0, sizeof(int));
+    return Fail(MSB_ERR_TIMEOUT, "a device-side bounded wait gave up (status " + std::to_string(flag) + ")");
+  }
+  return MSB_OK;
+}
+int msb_stream_idle(msb_stream_t stream, int *idle) {
+  MSB_REQUIRE(idle != nullptr, MSB_ERR_ARGUMENT, "null output");
+  const cudaError_t err = cudaStreamQuery(static_cast<cudaStream_t>(stream));
+  if (err != cudaSuccess && err != cudaErrorNotReady) return Fail(MSB_ERR_CUDA, cudaGetErrorString(err));
+  *idle = err == cudaSuccess;
+  return MSB_OK;
+}
+
+int msb_alloc_space(void **dptr_out, int64_t *ld_out, int64_t rows, int64_t cols, int64_t elem_size, int pad) {
+  MSB_REQUIRE(dptr_out != nullptr && ld_out != nullptr, MSB_ERR_ARGUMENT, "null output");
+  MSB_REQUIRE(rows >= 0 && cols >= 0 && elem_size > 0, MSB_ERR_ARGUMENT, "negative size");
+  void *p = nullptr;
+  size_t pitch = 0;
+  cudaError_t err;
+  if (pad && cols >= MSHADOW_MIN_PAD_RATIO * 32) {
+    err = cudaMallocPitch(&p, &pitch, cols * elem_size, rows);
+    *ld_out = static_cast<int64_t>(pitch / elem_size);
+  } else {
+    const size_t bytes = static_cast<size_t>(rows) * cols * elem_size;
+    err = cudaMalloc(&p, bytes == 0 ? 1 : bytes);
+    *ld_out = cols;
+  }
+  if (err != cudaSuccess) return Fail(MSB_ERR_MEMORY, cudaGetErrorString(err));
+  *dptr_out = p;
+  return MSB_OK;
+}
+int msb_free_space(void *dptr) {
+  const cudaError_t err = cudaFree(dptr);
+  return err == cudaSuccess ? MSB_OK : Fail(MSB_ERR_CUDA, cudaGetErrorString(err));
+}
+int msb_alloc_host(void **ptr_out, int64_t bytes) {
+  MSB_REQUIRE(ptr_out != nullptr && bytes >= 0, MSB_ERR_ARGUMENT, "bad argument");
+  const cudaError_t err = cudaMallocHost(ptr_out, bytes == 0 ? 1 : bytes, cudaHostAllocPortable);
+  return err == cudaSuccess ? MSB_OK : Fail(MSB_ERR_MEMORY, cudaGetErrorString(err));
+}
+int msb_free_host(void *ptr) {
+  const cudaError_t err = cudaFreeHost(ptr);
+  return err == cudaSuccess ? MSB_OK : Fail(MSB_ERR_CUDA, cudaGetErrorString(err));
+}
+int msb_copy_2d(void *dst, int64_t ld_dst, const void *src, int64_t ld_src, int64_t rows, int64_t cols,
+                int64_t elem_size, int kind, msb_stream_t stream) {
+  MSB_REQUIRE(kind >= 1 && kind <= 3, MSB_ERR_ARGUMENT, "kind must be 1 (h2d), 2 (d2h) or 3 (d2d)");
+  MSB_REQUIRE(rows >= 0 && cols >= 0 && ld_dst >= cols && ld_src >= cols, MSB_ERR_SHAPE, "bad extents");
+  if (rows == 0 || cols == 0) return MSB_OK;
+  MSB_REQUIRE(dst != nullptr && src != nullptr, MSB_ERR_ARGUMENT, "null pointer");
+  const cudaMemcpyKind k =
+      kind == 1 ? cudaMemcpyHostToDevice : (kind == 2 ? cudaMemcpyDeviceToHost : cudaMemcpyDeviceToDevice);
+  const cudaStream_t s = static_cast<cudaStream_t>(stream);
+  cudaError_t err;
+  if (ld_dst == cols && ld_src == cols) {
+    err = cudaMemcpyAsync(dst, src, static_cast<size_t>(rows) * cols * elem_size, k, s);
+  } else {
+    err = cudaMemcpy2DAsync(dst, ld_dst * elem_size, src, ld_src * elem_size, cols * elem_size, rows, k, s);
+  }
+  return err == cudaSuccess ? MSB_OK : Fail(MSB_ERR_CUDA, cudaGetErrorString(err));
+}
+int msb_workspace(msb_stream_t stream, int64_t bytes, void **out) {
+  MSB_REQUIRE(out != nullptr && bytes >= 0, MSB_ERR_ARGUMENT, "bad argument");
+  MSB_GUARD_BEGIN
+  *out = gpu_rt::Scratch::Get(static_cast<cudaStream_t>(stream), static_cast<size_t>(bytes));
+  MSB_GUARD_END
+}
+
+int msb_expr_case_f32(int id, float *dst, const float *A, const float *B, const float *C, const float *bias,
+                      int64_t rows, int64_t cols, int64_t ld_dst, int64_t ld_a, int64_t ld_b, int64_t ld_c,
+                      msb_stream_t stream) {
+  MSB_REQUIRE(id >= 0 && id <= 9, MSB_ERR_ARGUMENT, "unknown expression id");
+  MSB_REQUIRE(FitsIndex(rows) && FitsIndex(cols) && FitsIndex(rows * cols), MSB_ERR_SHAPE, "extent out of range");
+  MSB_REQUIRE(ld_dst >= cols && ld_a >= cols && ld_b >= cols && ld_c >= cols, MSB_ERR_SHAPE, "stride < width");
+  if (rows == 0 || cols == 0) return MSB_OK;
+  MSB_REQUIRE(dst && A && B && C && bias, MSB_ERR_ARGUMENT, "null pointer");
+  MSB_GUARD_BEGIN
+  BorrowedStream st(stream);
+  G2 d = Mat(dst, rows, cols, ld_dst, st.get());
+  const G2 a = Mat(A, rows, cols, ld_a, st.get()), b = Mat(B, rows, cols, ld_b, st.get()),
+           c = Mat(C, rows, cols, ld_c, st.get());
+  switch (id) {
+    case 0: d = F<b200::sigmoid>(a * b + 0.5f * c) + repmat(Vec(bias, cols, st.get()), rows); break;
+    case 1: d += a * 2.0f - b / c; break;
+    case 2: d = F<clip_mul>(a, b) * c; break;
+    case 3: d *= a + 1.5f; break;
+    case 4: d -= a * b; break;
+    case 5: d /= c * c + 1.0f; break;
+    case 6: d = 3.25f; break;
+    case 7: d = F<fma3>(a, b, c); break;
+    case 8: d = broadcast<0>(Vec(bias, rows, st.get()), d.shape_) * a + b; break;
+    default: d = F<square>(a - 1.0f) / (b * b + 2.0f) + c; break;
+  }
+  MSB_GUARD_END
+}
+
+int msb_reduce_keep_lowest_f32(float *dst, const float *src, int64_t rows, int64_t cols, int64_t ld, float scale,
+                               int saver, int reducer, msb_stream_t stream) {
+  MSB_REQUIRE(saver >= 0 && saver <= 4 && reducer >= 0 && reducer <= 2, MSB_ERR_ARGUMENT, "unknown selector");
+  MSB_REQUIRE(FitsIndex(rows) && FitsIndex(cols) && FitsIndex(rows * cols) && ld >= cols, MSB_ERR_SHAPE,
+              "extent out of range");
+  MSB_REQUIRE(rows > 0, MSB_ERR_SHAPE, "can not reduce over empty tensor");
+  if (cols == 0) return MSB_OK;
+  MSB_REQUIRE(dst && src, MSB_ERR_ARGUMENT, "null pointer");
+  MSB_GUARD_BEGIN
+  BorrowedStream st(stream);
+  const G1 d = Vec(dst, cols, st.get());
+  const G2 s = Mat(src, rows, cols, ld, st.get());
+  if (reducer == 0) KeepLowest<red::sum>(d, s, scale, saver);
+  else if (reducer == 1) KeepLowest<red::maximum>(d, s, scale, saver);
+  else KeepLowest<red::minimum>(d, s, scale, saver);
+  MSB_GUARD_END
+}
+
+int msb_reduce_keep_highdim_f32(float *dst, const float *src, int64_t n, int64_t c, int64_t h, int64_t w, int64_t ld,
+                                float scale, int saver, int reducer, msb_stream_t stream) {
+  MSB_REQUIRE(saver >= 0 && saver <= 4 && reducer >= 0 && reducer <= 2, MSB_ERR_ARGUMENT, "unknown selector");
+  MSB_REQUIRE(FitsIndex(n) && FitsIndex(c) && FitsIndex(h) && FitsIndex(w) && ld >= w, MSB_ERR_SHAPE,
+              "extent out of range");
+  MSB_REQUIRE(FitsIndex(n * c) && FitsIndex(n * c * h) && FitsIndex(n * c * h * w), MSB_ERR_SHAPE, "tensor too large");
+  if (c == 0) return MSB_OK;
+  MSB_REQUIRE(dst && (src || n * h * w == 0), MSB_ERR_ARGUMENT, "null pointer");
+  MSB_GUARD_BEGIN
+  BorrowedStream st(stream);
+  const G1 d = Vec(dst, c, st.get());
+  const G4 s = Img(src, n, c, h, w, ld, st.get());
+  if (reducer == 0) KeepDim1<red::sum>(d, s, scale, saver);
+  else if (reducer == 1) KeepDim1<red::maximum>(d, s, scale, saver);
+  else KeepDim1<red::minimum>(d, s, scale, saver);
+  MSB_GUARD_END
+}
+
+int msb_softmax_f32(float *dst, const float *src, int64_t rows, int64_t cols, int64_t ld_dst, int64_t ld_src,
+                    msb_stream_t stream) {
+  MSB_REQUIRE(FitsIndex(rows) && FitsIndex(cols) && ld_dst >= cols && ld_src >= cols, MSB_ERR_SHAPE,
+              "extent out of range");
+  if (rows == 0 || cols == 0) return MSB_OK;
+  MSB_REQUIRE(dst && src, MSB_ERR_ARGUMENT, "null pointer");
+  MSB_GUARD_BEGIN
+  BorrowedStream st(stream);
+  Softmax(Mat(dst, rows, cols, ld_dst, st.get()), Mat(src, rows, cols, ld_src, st.get()));
+  MSB_GUARD_END
+}
+
+int msb_softmax_grad_f32(float *dst, const float *src, const float *label, int64_t rows, int64_t cols,
+                         int64_t ld_dst, int64_t ld_src, int mode, float ignore_label, float alpha,
+                         msb_stream_t stream) {
+  MSB_REQUIRE(mode >= 0 && mode <= 3, MSB_ERR_ARGUMENT, "mode must be 0..3");
+  MSB_REQUIRE(FitsIndex(rows) && FitsIndex(cols) && FitsIndex(rows * cols) && ld_dst >= cols && ld_src >= cols,
+              MSB_ERR_SHAPE, "extent out of range");
+  if (rows == 0 || cols == 0) return MSB_OK;
+  MSB_REQUIRE(dst && src && label, MSB_ERR_ARGUMENT, "null pointer");
+  MSB_GUARD_BEGIN
+  BorrowedStream st(stream);
+  G2 d = Mat(dst, rows, cols, ld_dst, st.get());
+  const G2 s = Mat(src, rows, cols, ld_src, st.get());
+  const G1 l = Vec(label, rows, st.get());
+  switch (mode) {
+    case 0: SoftmaxGrad(d, s, l); break;
+    case 1: SmoothSoftmaxGrad(d, s, l, alpha); break;
+    case 2: SoftmaxGrad(d, s, l, ignore_label); break;
+    default: SmoothSoftmaxGrad(d, s, l, ignore_label, alpha); break;
+  }
+  MSB_GUARD_END
+}
+
+int msb_pool_f32(float *dst, const float *src, int64_t planes, int64_t h, int64_t w, int ky, int kx, int sy, int sx,
+                 int64_t ld_src, int64_t ld_dst, int reducer, msb_stream_t stream) {
+  MSB_REQUIRE(reducer >= 0 && reducer <= 2, MSB_ERR_ARGUMENT, "unknown reducer");
+  MSB_REQUIRE(ky > 0 && kx > 0 && sy > 0 && sx > 0, MSB_ERR_ARGUMENT, "window and stride must be positive");
+  MSB_REQUIRE(FitsIndex(planes) && FitsIndex(h) && FitsIndex(w) && FitsIndex(planes * h) && FitsIndex(planes * h * w),
+              MSB_ERR_SHAPE, "extent out of range");
+  MSB_REQUIRE(h >= ky && w >= kx, MSB_ERR_SHAPE, "PoolingExp: kernel must be smaller than image");
+  const int64_t ph = (h - ky) / sy + 1, pw = (w - kx) / sx + 1;
+  MSB_REQUIRE(ld_src >= w && ld_dst >= pw, MSB_ERR_SHAPE, "stride < width");
+  if (planes == 0) return MSB_OK;
+  MSB_REQUIRE(dst && src, MSB_ERR_ARGUMENT, "null pointer");
+  MSB_GUARD_BEGIN
+  BorrowedStream st(stream);
+  G3 d = Planes(dst, planes, ph, pw, ld_dst, st.get());
+  const G3 s = Planes(src, planes, h, w, ld_src, st.get());
+  if (reducer == 0) d = pool<red::sum>(s, ky, kx, sy, sx);
+  else if (reducer == 1) d = pool<red::maximum>(s, ky, kx, sy, sx);
+  else d = pool<red::minimum>(s, ky, kx, sy, sx);
+  MSB_GUARD_END
+}
+
+int msb_unpool_f32(float *dst, const float *src, const float *pooled, const float *gpooled, int64_t planes, int64_t h,
+                   int64_t w, int64_t ph, int64_t pw, int ky, int kx, int sy, int sx, int64_t ld_src,
+                   int64_t ld_pooled, int64_t ld_dst, int reducer, msb_stream_t stream) {
+  MSB_REQUIRE(reducer >= 0 && reducer <= 2, MSB_ERR_ARGUMENT, "unknown reducer");
+  MSB_REQUIRE(ky > 0 && kx > 0 && sy > 0 && sx > 0, MSB_ERR_ARGUMENT, "window and stride must be positive");
+  MSB_REQUIRE(FitsIndex(planes) && FitsIndex(h) && FitsIndex(w) && FitsIndex(planes * h) && FitsIndex(planes * h * w) &&
+                  FitsIndex(ph) && FitsIndex(pw),
+              MSB_ERR_SHAPE, "extent out of range");
+  MSB_REQUIRE(ld_src >= w && ld_dst >= w && ld_pooled >= pw, MSB_ERR_SHAPE, "stride < width");
+  if (planes == 0 || h * w == 0) return MSB_OK;
+  MSB_REQUIRE(dst && src && (ph * pw == 0 || (pooled && gpooled)), MSB_ERR_ARGUMENT, "null pointer");
+  MSB_GUARD_BEGIN
+  BorrowedStream st(stream);
+  G3 d = Planes(dst, planes, h, w, ld_dst, st.get());
+  const G3 s = Planes(src, planes, h, w, ld_src, st.get());
+  const G3 p = Planes(pooled, planes, ph, pw, ld_pooled, st.get()), g = Planes(gpooled, planes, ph, pw, ld_pooled, st.get());
+  if (reducer == 0) d = unpool<red::sum>(s, p, g, ky, kx, sy, sx);
+  else if (reducer == 1) d = unpool<red::maximum>(s, p, g, ky, kx, sy, sx);
+  else d = unpool<red::minimum>(s, p, g, ky, kx, sy, sx);
+  MSB_GUARD_END
+}
+
+int msb_chpool_f32(float *dst, const float *src, int64_t n, int64_t c, int64_t h, int64_t w, int nsize, int stride,
+                   int pad, int64_t ld_src, int64_t ld_dst, int reducer, msb_stream_t stream) {
+  MSB_REQUIRE(reducer >= 0 && reducer <= 2, MSB_ERR_ARGUMENT, "unknown reducer");
+  MSB_REQUIRE(nsize > 0 && stride > 0 && pad >= 0, MSB_ERR_ARGUMENT, "bad window");
+  MSB_REQUIRE(FitsIndex(n) && FitsIndex(c) && FitsIndex(h) && FitsIndex(w) && FitsIndex(n * c * h) &&
+                  FitsIndex(n * c * h * w),
+              MSB_ERR_SHAPE, "extent out of range");
+  MSB_REQUIRE(c >= nsize, MSB_ERR_SHAPE, "chpool: local size must be smaller than nchannels");
+  MSB_REQUIRE(ld_src >= w && ld_dst >= w, MSB_ERR_SHAPE, "stride < width");
+  const int64_t co = (c - nsize + pad * 2 + 1) / stride;
+  if (n * co * h * w == 0) return MSB_OK;
+  MSB_REQUIRE(dst && src, MSB_ERR_ARGUMENT, "null pointer");
+  MSB_GUARD_BEGIN
+  BorrowedStream st(stream);
+  G4 d = Img(dst, n, co, h, w, ld_dst, st.get());
+  const G4 s = Img(src, n, c, h, w, ld_src, st.get());
+  if (reducer == 0) d = chpool<red::sum>(s, nsize, stride, pad);
+  else if (reducer == 1) d = chpool<red::maximum>(s, nsize, stride, pad);
+  else d = chpool<red::minimum>(s, nsize, stride, pad);
+  MSB_GUARD_END
+}
+
+int msb_addtakegrad_f32_i32(float *dst, const int32_t *index, const float *src, int64_t k, int64_t d, int64_t nidx,
+                            int64_t ld_dst, int64_t ld_src, msb_stream_t stream) {
+  MSB_REQUIRE(FitsIndex(k) && FitsIndex(d) && FitsIndex(nidx) && ld_dst >= d && ld_src >= d, MSB_ERR_SHAPE,
+              "extent out of range");
+  MSB_REQUIRE(k > 0 || nidx == 0, MSB_ERR_SHAPE, "empty table");
+  if (nidx == 0 || d == 0) return MSB_OK;
+  MSB_REQUIRE(dst && index && src, MSB_ERR_ARGUMENT, "null pointer");
+  MSB_GUARD_BEGIN
+  BorrowedStream st(stream);
+  const Tensor<gpu, 1, int32_t> idx(const_cast<int32_t *>(index), Shape1(nidx), nidx, st.get());
+  AddTakeGrad(Mat(dst, k, d, ld_dst, st.get()), idx, Mat(src, nidx, d, ld_src, st.get()));
+  MSB_GUARD_END
+}
+
+int msb_addtakegrad_largebatch_f32_i32(float *dst, const int32_t *sorted, const int32_t *index, const float *src,
+                                       int64_t k, int64_t d, int64_t nidx, msb_stream_t stream) {
+  MSB_REQUIRE(FitsIndex(k) && FitsIndex(d) && FitsIndex(nidx), MSB_ERR_SHAPE, "extent out of range");
+  if (nidx == 0 || d == 0) return MSB_OK;
+  MSB_REQUIRE(dst && sorted && index && src, MSB_ERR_ARGUMENT, "null pointer");
+  MSB_GUARD_BEGIN
+  BorrowedStream st(stream);
+  const Tensor<gpu, 1, int32_t> s(const_cast<int32_t *>(sorted), Shape1(nidx), nidx, st.get());
+  const Tensor<gpu, 1, int32_t> i(const_cast<int32_t *>(index), Shape1(nidx), nidx, st.get());
+  AddTakeGradLargeBatch(Mat(dst, k, d, d, st.get()), s, i, Mat(src, nidx, d, d, st.get()));
+  MSB_GUARD_END
+}
+
+int msb_sort_by_key_i32(int32_t *keys, int32_t *values, int64_t n, int ascend, msb_stream_t stream) {
+  MSB_REQUIRE(FitsIndex(n), MSB_ERR_SHAPE, "extent out of range");
+  if (n == 0) return MSB_OK;
+  MSB_REQUIRE(keys && values, MSB_ERR_ARGUMENT, "null pointer");
+  MSB_GUARD_BEGIN
+  BorrowedStream st(stream);
+  Tensor<gpu, 1, int32_t> k(keys, Shape1(n), n, st.get()), v(values, Shape1(n), n, st.get());
+  SortByKey(k, v, ascend != 0);
+  MSB_GUARD_END
+}
+
+}  // extern "C"

@@ -1,0 +1,301 @@
+/*
+ * Embedding backward: AddTakeGradLargeBatch (dst[sorted[y]] += src[index[y]]), AddTakeGrad
+ * (dst[clip(index[y])] += src[y]) and SortByKey.
+ *
+ * The reference's large-batch kernel (mshadow/cuda/tensor_gpu-inl.cuh:619-672) lets the
+ * warp that sits on the first entry of a run of equal indices walk the whole run while all
+ * other warps exit, so a frequent index (a Zipf head holds an eighth of a million-entry
+ * batch) is accumulated serially by one warp per 128 features; its small-batch kernel
+ * (:599-617) is serial over the entire batch.
+ *
+ * Here the sorted list is cut into fixed chunks of kSegChunk entries, one CTA per chunk and
+ * per 1024-feature slab.  A thread owns four adjacent features and streams the source rows
+ * of its chunk with 128-bit loads, eight rows in flight, accumulating in registers while
+ * the key stays the same.  A run that lies wholly inside one chunk is added to its table
+ * row directly.  A run that crosses a chunk boundary leaves one partial row per chunk in a
+ * scratch matrix; those partial rows, keyed by table row and still in sorted order, are the
+ * input of the same kernel one level up.  Levels shrink by a factor of kSegChunk / 2, so a
+ * million entries take four launches, the last three tiny.  No atomics are used and every
+ * addition order is fixed by the chunk geometry, so results are reproducible.
+ *
+ * Traffic: each source row is read once (4*N*D bytes), each touched table row is read and
+ * written once, partial rows add a few percent.  The kernel is bound by HBM bandwidth.
+ */
+#ifndef MSHADOW_GPU_EMBED_CUH_
+#define MSHADOW_GPU_EMBED_CUH_
+
+#include <cub/device/device_radix_sort.cuh>
+
+#include "./runtime.h"
+
+namespace mshadow {
+namespace cuda {
+
+const uint32_t kSegChunk = 128;
+const int kSegDepth = 8;
+
+/*!
+ * \brief one level of the chunked segmented sum.
+ *  keys[n] ascending; rows[n] (or identity when null) names the source row of each entry, a
+ *  negative row contributes nothing.  part_keys / part_rows / partials receive two slots per
+ *  chunk for the next level.  grid = (chunks, feature slabs).
+ */
+template <int kLanes>
+__global__ void __launch_bounds__(256)
+SegmentSumKernel(float *dst, int64_t ld_dst, const int32_t *keys, const int32_t *rows, const float *src,
+                 int64_t ld_src, uint32_t n, uint32_t width, int32_t *part_keys, int32_t *part_rows,
+                 float *partials) {
+  const uint32_t chunk = blockIdx.x;
+  const uint32_t begin = chunk * kSegChunk;
+  const uint32_t end = min(n, begin + kSegChunk);
+  const uint32_t col = (blockIdx.y * blockDim.x + threadIdx.x) * kLanes;
+  const bool active = col < width;
+  const bool lead = blockIdx.y == 0 && threadIdx.x == 0;
+  const bool joins_prev = chunk > 0 && keys[begin - 1] == keys[begin];
+  const bool joins_next = end < n && keys[end] == keys[end - 1];
+  if (lead && part_rows != nullptr) {
+    part_keys[2 * chunk] = keys[begin];
+    part_keys[2 * chunk + 1] = keys[end - 1];
+    part_rows[2 * chunk] = -1;
+    part_rows[2 * chunk + 1] = -1;
+  }
+  int32_t cur = keys[begin];
+  bool first_run = true, any = false;
+  float acc[kLanes];
+#pragma unroll
+  for (int l = 0; l < kLanes; ++l) acc[l] = 0.0f;
+
+  // add a finished run to its table row, or park it in the scratch matrix if it continues
+  // in a neighbouring chunk
+  auto flush = [&](bool last_run) {
+    const bool spans = (first_run && joins_prev) || (last_run && joins_next);
+    if (!spans) {
+      if (any && active) {
+        float *row = dst + static_cast<int64_t>(cur) * ld_dst + col;
+        if (kLanes == 4) {
+          float4 d = *reinterpret_cast<float4 *>(row);
+          d.x = __fadd_rn(d.x, acc[0]);
+          d.y = __fadd_rn(d.y, acc[1 % kLanes]);
+          d.z = __fadd_rn(d.z, acc[2 % kLanes]);
+          d.w = __fadd_rn(d.w, acc[3 % kLanes]);
+          *reinterpret_cast<float4 *>(row) = d;
+        } else {
+          row[0] = __fadd_rn(row[0], acc[0]);
+        }
+      }
+    } else if (any) {
+      const uint32_t slot = 2 * chunk + (first_run ? 0 : 1);
+      if (active) {
+        float *row = partials + static_cast<int64_t>(slot) * width + col;
+        if (kLanes == 4) {
+          *reinterpret_cast<float4 *>(row) = make_float4(acc[0], acc[1 % kLanes], acc[2 % kLanes], acc[3 % kLanes]);
+        } else {
+          row[0] = acc[0];
+        }
+      }
+      if (lead) part_rows[slot] = static_cast<int32_t>(slot);
+    }
+  };
+
+  for (uint32_t i = begin; i < end; i += kSegDepth) {
+    int32_t k[kSegDepth], r[kSegDepth];
+    float v[kSegDepth][kLanes];
+#pragma unroll
+    for (int u = 0; u < kSegDepth; ++u) {
+      const uint32_t e = i + u;
+      const bool in = e < end;
+      k[u] = in ? keys[e] : 0;
+      r[u] = in ? (rows != nullptr ? rows[e] : static_cast<int32_t>(e)) : -1;
+    }
+#pragma unroll
+    for (int u = 0; u < kSegDepth; ++u) {
+      if (r[u] >= 0 && active) {
+        const float *p = src + static_cast<int64_t>(r[u]) * ld_src + col;
+        if (kLanes == 4) {
+          const float4 q = __ldcs(reinterpret_cast<const float4 *>(p));
+          v[u][0] = q.x;
+          v[u][1 % kLanes] = q.y;
+          v[u][2 % kLanes] = q.z;
+          v[u][3 % kLanes] = q.w;
+        } else {
+          v[u][0] = __ldcs(p);
+        }
+      } else {
+#pragma unroll
+        for (int l = 0; l < kLanes; ++l) v[u][l] = 0.0f;
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < kSegDepth; ++u) {
+      if (i + u < end) {
+        if (k[u] != cur) {
+          flush(false);
+          cur = k[u];
+          first_run = false;
+          any = false;
+#pragma unroll
+          for (int l = 0; l < kLanes; ++l) acc[l] = 0.0f;
+        }
+        if (r[u] >= 0) {
+          any = true;
+#pragma unroll
+          for (int l = 0; l < kLanes; ++l) acc[l] = __fadd_rn(acc[l], v[u][l]);
+        }
+      }
+    }
+  }
+  flush(true);
+}
+
+/*! \brief keys[i] = clip(index[i], 0, k-1), vals[i] = i */
+__global__ void ClipIotaKernel(int32_t *keys, int32_t *vals, const int32_t *index, uint32_t n, int32_t k) {
+  const uint32_t i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  int32_t j = index[i];
+  j = j <= 0 ? 0 : (j >= k ? k - 1 : j);
+  keys[i] = j;
+  vals[i] = static_cast<int32_t>(i);
+}
+
+namespace embeddetail {
+inline size_t Align256(size_t b) { return (b + 255) / 256 * 256; }
+
+/*! \brief chunk counts of every level until one chunk remains */
+inline int Levels(uint32_t n, uint32_t (&entries)[8], uint32_t (&chunks)[8]) {
+  int levels = 0;
+  uint32_t cur = n;
+  while (levels < 8) {
+    entries[levels] = cur;
+    chunks[levels] = (cur + kSegChunk - 1) / kSegChunk;
+    ++levels;
+    if (chunks[levels - 1] <= 1) break;
+    cur = 2 * chunks[levels - 1];
+  }
+  return levels;
+}
+
+/*! \brief bytes of scratch the levels below need (partial rows + their keys and row ids) */
+inline size_t SegmentScratchBytes(uint32_t n, uint32_t width) {
+  uint32_t entries[8], chunks[8];
+  const int levels = Levels(n, entries, chunks);
+  size_t bytes = 0;
+  for (int l = 0; l + 1 < levels; ++l) {
+    bytes += Align256(2ull * chunks[l] * width * sizeof(float));
+    bytes += 2 * Align256(2ull * chunks[l] * sizeof(int32_t));
+  }
+  return bytes;
+}
+
+/*! \brief run all levels; `scratch` must hold SegmentScratchBytes(n, width) */
+inline void SegmentSumRun(float *dst, int64_t ld_dst, const int32_t *keys, const int32_t *rows, const float *src,
+                          int64_t ld_src, uint32_t n, uint32_t width, char *scratch, cudaStream_t stream) {
+  if (n == 0 || width == 0) return;
+  uint32_t entries[8], chunks[8];
+  const int levels = Levels(n, entries, chunks);
+  const int32_t *lkeys = keys, *lrows = rows;
+  const float *lsrc = src;
+  int64_t lld = ld_src;
+  for (int l = 0; l < levels; ++l) {
+    int32_t *pk = nullptr, *pr = nullptr;
+    float *pp = nullptr;
+    if (l + 1 < levels) {
+      pp = reinterpret_cast<float *>(scratch);
+      scratch += Align256(2ull * chunks[l] * width * sizeof(float));
+      pk = reinterpret_cast<int32_t *>(scratch);
+      scratch += Align256(2ull * chunks[l] * sizeof(int32_t));
+      pr = reinterpret_cast<int32_t *>(scratch);
+      scratch += Align256(2ull * chunks[l] * sizeof(int32_t));
+    }
+    const bool vec = width % 4 == 0 && lld % 4 == 0 && ld_dst % 4 == 0 &&
+                     reinterpret_cast<uintptr_t>(lsrc) % 16 == 0 && reinterpret_cast<uintptr_t>(dst) % 16 == 0;
+    const uint32_t items = vec ? width / 4 : width;
+    uint32_t threads = (items + 31) / 32 * 32;
+    if (threads > 256) threads = 256;
+    const dim3 grid(chunks[l], (items + threads - 1) / threads);
+    if (vec) {
+      SegmentSumKernel<4><<<grid, threads, 0, stream>>>(dst, ld_dst, lkeys, lrows, lsrc, lld, entries[l], width, pk,
+                                                       pr, pp);
+    } else {
+      SegmentSumKernel<1><<<grid, threads, 0, stream>>>(dst, ld_dst, lkeys, lrows, lsrc, lld, entries[l], width, pk,
+                                                       pr, pp);
+    }
+    MSHADOW_CUDA_POST_KERNEL_CHECK(SegmentSumKernel);
+    lkeys = pk;
+    lrows = pr;
+    lsrc = pp;
+    lld = width;
+  }
+}
+}  // namespace embeddetail
+
+/*! \brief dst[sorted[y]] += src[index[y]]; `sorted` ascending */
+inline void AddTakeGradLargeBatchLaunch(float *dst, int64_t ld_dst, const int32_t *sorted, const int32_t *index,
+                                        const float *src, int64_t ld_src, int64_t n, int64_t width,
+                                        cudaStream_t stream) {
+  if (n == 0 || width == 0) return;
+  CHECK_LT(n, (int64_t(1) << 31));
+  const size_t bytes = embeddetail::SegmentScratchBytes(static_cast<uint32_t>(n), static_cast<uint32_t>(width));
+  char *scratch = bytes == 0 ? nullptr : static_cast<char *>(gpu_rt::Scratch::Get(stream, bytes));
+  embeddetail::SegmentSumRun(dst, ld_dst, sorted, index, src, ld_src, static_cast<uint32_t>(n),
+                             static_cast<uint32_t>(width), scratch, stream);
+}
+
+/*! \brief stable key/value sort of 32-bit pairs, in place from the caller's point of view */
+template <typename KDType, typename VDType>
+inline void SortPairsLaunch(KDType *keys, VDType *values, int64_t n, bool ascend, cudaStream_t stream) {
+  if (n <= 1) return;
+  CHECK_LT(n, (int64_t(1) << 31));
+  size_t temp = 0;
+  if (ascend) {
+    MSHADOW_CUDA_CALL((cub::DeviceRadixSort::SortPairs<KDType, VDType>(nullptr, temp, keys, keys, values, values,
+                                                                       static_cast<int>(n), 0, sizeof(KDType) * 8,
+                                                                       stream)));
+  } else {
+    MSHADOW_CUDA_CALL((cub::DeviceRadixSort::SortPairsDescending<KDType, VDType>(
+        nullptr, temp, keys, keys, values, values, static_cast<int>(n), 0, sizeof(KDType) * 8, stream)));
+  }
+  const size_t kb = embeddetail::Align256(n * sizeof(KDType)), vb = embeddetail::Align256(n * sizeof(VDType));
+  char *base = static_cast<char *>(gpu_rt::Scratch::Get(stream, kb + vb + temp));
+  KDType *k2 = reinterpret_cast<KDType *>(base);
+  VDType *v2 = reinterpret_cast<VDType *>(base + kb);
+  void *work = base + kb + vb;
+  if (ascend) {
+    MSHADOW_CUDA_CALL((cub::DeviceRadixSort::SortPairs<KDType, VDType>(work, temp, keys, k2, values, v2,
+                                                                       static_cast<int>(n), 0, sizeof(KDType) * 8,
+                                                                       stream)));
+  } else {
+    MSHADOW_CUDA_CALL((cub::DeviceRadixSort::SortPairsDescending<KDType, VDType>(
+        work, temp, keys, k2, values, v2, static_cast<int>(n), 0, sizeof(KDType) * 8, stream)));
+  }
+  MSHADOW_CUDA_CALL(cudaMemcpyAsync(keys, k2, n * sizeof(KDType), cudaMemcpyDeviceToDevice, stream));
+  MSHADOW_CUDA_CALL(cudaMemcpyAsync(values, v2, n * sizeof(VDType), cudaMemcpyDeviceToDevice, stream));
+}
+
+/*! \brief dst[clip(index[y], 0, k-1)] += src[y], contributions to a row added in batch order */
+inline void AddTakeGradLaunch(float *dst, int64_t ld_dst, const int32_t *index, const float *src, int64_t ld_src,
+                              int64_t k, int64_t n, int64_t width, cudaStream_t stream) {
+  if (n == 0 || width == 0) return;
+  CHECK_LT(n, (int64_t(1) << 31));
+  using embeddetail::Align256;
+  const uint32_t un = static_cast<uint32_t>(n);
+  size_t temp = 0;
+  MSHADOW_CUDA_CALL((cub::DeviceRadixSort::SortPairs<int32_t, int32_t>(nullptr, temp, nullptr, nullptr, nullptr,
+                                                                       nullptr, static_cast<int>(n), 0, 32, stream)));
+  const size_t ib = Align256(n * sizeof(int32_t));
+  const size_t seg = embeddetail::SegmentScratchBytes(un, static_cast<uint32_t>(width));
+  char *base = static_cast<char *>(gpu_rt::Scratch::Get(stream, 4 * ib + Align256(temp) + seg));
+  int32_t *k_in = reinterpret_cast<int32_t *>(base), *v_in = reinterpret_cast<int32_t *>(base + ib);
+  int32_t *k_out = reinterpret_cast<int32_t *>(base + 2 * ib), *v_out = reinterpret_cast<int32_t *>(base + 3 * ib);
+  void *work = base + 4 * ib;
+  char *seg_scratch = base + 4 * ib + Align256(temp);
+  ClipIotaKernel<<<gpu_rt::CeilDiv(n, 256), 256, 0, stream>>>(k_in, v_in, index, un, static_cast<int32_t>(k));
+  MSHADOW_CUDA_POST_KERNEL_CHECK(ClipIotaKernel);
+  MSHADOW_CUDA_CALL((cub::DeviceRadixSort::SortPairs<int32_t, int32_t>(work, temp, k_in, k_out, v_in, v_out,
+                                                                       static_cast<int>(n), 0, 32, stream)));
+  embeddetail::SegmentSumRun(dst, ld_dst, k_out, v_out, src, ld_src, un, static_cast<uint32_t>(width), seg_scratch,
+                             stream);
+}
+
+}  // namespace cuda
+}  // namespace mshadow
+#endif  // MSHADOW_GPU_EMBED_CUH_

@@ -1,0 +1,422 @@
+/*
+ * Dedicated kernels for the pooling expressions over plain tensors:
+ *   PoolPlanes     out = pool<Reducer>(src, ky, kx, sy, sx)
+ *   UnpoolPlanes   out = unpool<Reducer>(src, pooled, grad_pooled, ky, kx, sy, sx)
+ *   ChannelPool    out = chpool<Reducer>(src, nsize)            (stride 1, pad nsize/2)
+ * In the reference these have no kernels of their own: the window loop sits inside
+ * Plan::Eval (mshadow/extension/spatial_pool.h:125-142, spatial_unpool.h:102-125,
+ * channel_pool.h:85-99) and runs in the generic one-thread-per-output map kernel, so each
+ * output re-reads its window from global memory with stride-2, 4-byte accesses.
+ *
+ * Spatial kernels: a CTA takes a group of consecutive image planes, brings them into shared
+ * memory with one bulk asynchronous copy per operand (plain 128-bit loads when the group is
+ * not 16-byte sized/aligned or rows are pitched), evaluates the windows out of shared
+ * memory and writes the result coalesced.  HBM traffic is one read of every input and one
+ * write of the output.
+ *
+ * Arithmetic is the reference's, operation for operation: windows are walked y-outer /
+ * x-inner from Reducer::SetInitValue; unpool adds PartialGrad(src, pooled) * grad for the
+ * covering windows in py-outer / px-inner order starting from zero, so tied maxima all
+ * receive the gradient; chpool adds its channels in ascending order starting from zero.
+ * Results are therefore bit-identical to the CPU evaluation.
+ */
+#ifndef MSHADOW_GPU_POOL_CUH_
+#define MSHADOW_GPU_POOL_CUH_
+
+#include "./runtime.h"
+#include "./tma.cuh"
+
+namespace mshadow {
+namespace cuda {
+
+const int kPoolThreads = 256;
+
+/*! \brief window geometry; a template value of 0 means "read the run-time field" */
+struct PoolGeom {
+  int ky, kx, sy, sx;
+};
+
+namespace pooldetail {
+
+/*!
+ * \brief bring `count` floats that start at `src` into shared memory.  Uses the bulk copy
+ *  when the byte range is 16-byte aligned and sized, otherwise plain loads by all threads.
+ *  Must be called by every thread of the CTA.  Returns false after a copy timeout.
+ */
+__device__ __forceinline__ bool StageDense(float *smem, const float *src, uint32_t count, uint64_t *bar,
+                                           bool *used_bulk) {
+  const bool bulk = (reinterpret_cast<uintptr_t>(src) % 16 == 0) && (count % 4 == 0);
+  *used_bulk = bulk;
+  if (bulk) {
+    if (threadIdx.x == 0) {
+      tma::BarrierExpect(bar, count * 4u);
+      tma::BulkLoad(smem, src, count * 4u, bar);
+    }
+    return true;
+  }
+  for (uint32_t i = threadIdx.x; i < count; i += blockDim.x) smem[i] = src[i];
+  return true;
+}
+
+/*! \brief rows of `w` floats, `ld` apart in global memory, packed densely into shared memory */
+__device__ __forceinline__ void StagePitched(float *smem, const float *src, uint32_t nrows, uint32_t w, int64_t ld) {
+  const uint32_t count = nrows * w;
+  for (uint32_t i = threadIdx.x; i < count; i += blockDim.x) {
+    const uint32_t r = i / w;
+    smem[i] = src[r * ld + (i - r * w)];
+  }
+}
+
+}  // namespace pooldetail
+
+/*!
+ * \brief spatial pooling of groups of `gplanes` planes.  Shared memory: gplanes*h*w floats.
+ *  KY/KX/SY/SX > 0 fix the window at compile time.
+ */
+template <typename Reducer, int KY, int KX, int SY, int SX>
+__global__ void __launch_bounds__(kPoolThreads)
+PoolPlanesKernel(float *dst, const float *src, uint32_t planes, uint32_t h, uint32_t w, uint32_t ph, uint32_t pw,
+                 PoolGeom g, int64_t ld_src, int64_t ld_dst, uint32_t gplanes, gpu_rt::FastDiv div_pw,
+                 gpu_rt::FastDiv div_ph, int *status) {
+  extern __shared__ __align__(16) float tile[];
+  __shared__ uint64_t bar;
+  const int ky = KY > 0 ? KY : g.ky, kx = KX > 0 ? KX : g.kx;
+  const int sy = SY > 0 ? SY : g.sy, sx = SX > 0 ? SX : g.sx;
+  if (threadIdx.x == 0) tma::BarrierInit(&bar, 1);
+  __syncthreads();
+  uint32_t phase = 0;
+  const bool dense_in = ld_src == static_cast<int64_t>(w);
+  for (uint32_t first = blockIdx.x * gplanes; first < planes; first += gridDim.x * gplanes) {
+    const uint32_t np = min(gplanes, planes - first);
+    bool bulk = false;
+    if (dense_in) {
+      pooldetail::StageDense(tile, src + static_cast<int64_t>(first) * h * w, np * h * w, &bar, &bulk);
+    } else {
+      pooldetail::StagePitched(tile, src + static_cast<int64_t>(first) * h * ld_src, np * h, w, ld_src);
+    }
+    if (bulk) {
+      if (!tma::WaitBounded(&bar, phase)) {
+        if (threadIdx.x == 0) atomicExch(status, tma::kStatusBulkCopyTimeout);
+        tma::WaitBounded(&bar, phase);
+        return;
+      }
+      phase ^= 1;
+    } else {
+      __syncthreads();
+    }
+    const uint32_t nout = np * ph * pw;
+    for (uint32_t o = threadIdx.x; o < nout; o += kPoolThreads) {
+      const uint32_t row = div_pw.Quot(o);  // plane-local output row index: p * ph + py
+      const uint32_t px = o - row * pw;
+      const uint32_t p = div_ph.Quot(row);
+      const uint32_t py = row - p * ph;
+      const uint32_t y0 = py * sy, x0 = px * sx;
+      const uint32_t y1 = min(y0 + ky, h), x1 = min(x0 + kx, w);
+      const float *plane = tile + p * h * w;
+      float res;
+      Reducer::SetInitValue(res);
+      if (KY > 0 && y0 + KY <= h && x0 + KX <= w) {
+#pragma unroll
+        for (int dy = 0; dy < (KY > 0 ? KY : 1); ++dy)
+#pragma unroll
+          for (int dx = 0; dx < (KX > 0 ? KX : 1); ++dx) Reducer::Reduce(res, plane[(y0 + dy) * w + x0 + dx]);
+      } else {
+        for (uint32_t y = y0; y < y1; ++y)
+          for (uint32_t x = x0; x < x1; ++x) Reducer::Reduce(res, plane[y * w + x]);
+      }
+      dst[(static_cast<int64_t>(first) * ph + row) * ld_dst + px] = res;
+    }
+    // all reads of the tile are done before the next group overwrites it
+    tma::FenceAsyncShared();
+    __syncthreads();
+  }
+}
+
+/*!
+ * \brief backward of spatial pooling for groups of `gplanes` planes.
+ *  Shared memory: gplanes * (h*w + 2*ph*pw) floats (source, pooled, pooled gradient).
+ */
+template <typename Reducer, int KY, int KX, int SY, int SX>
+__global__ void __launch_bounds__(kPoolThreads)
+UnpoolPlanesKernel(float *dst, const float *src, const float *pooled, const float *gpooled, uint32_t planes,
+                   uint32_t h, uint32_t w, uint32_t ph, uint32_t pw, PoolGeom g, int64_t ld_src, int64_t ld_pooled,
+                   int64_t ld_dst, uint32_t gplanes, gpu_rt::FastDiv div_w, gpu_rt::FastDiv div_h,
+                   gpu_rt::FastDiv div_sy, gpu_rt::FastDiv div_sx, int *status) {
+  extern __shared__ __align__(16) float tile[];
+  __shared__ uint64_t bar;
+  const uint32_t ky = KY > 0 ? KY : g.ky, kx = KX > 0 ? KX : g.kx;
+  const uint32_t sy = SY > 0 ? SY : g.sy, sx = SX > 0 ? SX : g.sx;
+  // group sizes are padded to multiples of 4 floats so that every region starts 16-byte aligned
+  const uint32_t src_cap = (gplanes * h * w + 3) & ~3u, pool_cap = (gplanes * ph * pw + 3) & ~3u;
+  float *s_src = tile, *s_pool = tile + src_cap, *s_grad = s_pool + pool_cap;
+  if (threadIdx.x == 0) tma::BarrierInit(&bar, 1);
+  __syncthreads();
+  uint32_t phase = 0;
+  const bool dense = ld_src == static_cast<int64_t>(w) && ld_pooled == static_cast<int64_t>(pw);
+  for (uint32_t first = blockIdx.x * gplanes; first < planes; first += gridDim.x * gplanes) {
+    const uint32_t np = min(gplanes, planes - first);
+    const uint32_t n_src = np * h * w, n_pool = np * ph * pw;
+    const float *g_src = src + static_cast<int64_t>(first) * h * ld_src;
+    const float *g_pool = pooled + static_cast<int64_t>(first) * ph * ld_pooled;
+    const float *g_grad = gpooled + static_cast<int64_t>(first) * ph * ld_pooled;
+    const bool bulk = dense && n_src % 4 == 0 && n_pool % 4 == 0 && reinterpret_cast<uintptr_t>(g_src) % 16 == 0 &&
+                      reinterpret_cast<uintptr_t>(g_pool) % 16 == 0 && reinterpret_cast<uintptr_t>(g_grad) % 16 == 0;
+    if (bulk) {
+      if (threadIdx.x == 0) {
+        tma::BarrierExpect(&bar, (n_src + 2 * n_pool) * 4u);
+        tma::BulkLoad(s_src, g_src, n_src * 4u, &bar);
+        tma::BulkLoad(s_pool, g_pool, n_pool * 4u, &bar);
+        tma::BulkLoad(s_grad, g_grad, n_pool * 4u, &bar);
+      }
+      if (!tma::WaitBounded(&bar, phase)) {
+        if (threadIdx.x == 0) atomicExch(status, tma::kStatusBulkCopyTimeout);
+        tma::WaitBounded(&bar, phase);
+        return;
+      }
+      phase ^= 1;
+    } else {
+      pooldetail::StagePitched(s_src, g_src, np * h, w, ld_src);
+      pooldetail::StagePitched(s_pool, g_pool, np * ph, pw, ld_pooled);
+      pooldetail::StagePitched(s_grad, g_grad, np * ph, pw, ld_pooled);
+      __syncthreads();
+    }
+    for (uint32_t o = threadIdx.x; o < n_src; o += kPoolThreads) {
+      const uint32_t row = div_w.Quot(o);  // p * h + y
+      const uint32_t x = o - row * w;
+      const uint32_t p = div_h.Quot(row);
+      const uint32_t y = row - p * h;
+      const float vsrc = s_src[o];
+      const uint32_t py_min = y < ky ? 0 : (SY > 0 ? (y - ky + sy) / sy : div_sy.Quot(y - ky + sy));
+      const uint32_t px_min = x < kx ? 0 : (SX > 0 ? (x - kx + sx) / sx : div_sx.Quot(x - kx + sx));
+      const uint32_t py_max = min(SY > 0 ? (y + sy) / sy : div_sy.Quot(y + sy), ph);
+      const uint32_t px_max = min(SX > 0 ? (x + sx) / sx : div_sx.Quot(x + sx), pw);
+      const float *pp = s_pool + p * ph * pw;
+      const float *gp = s_grad + p * ph * pw;
+      float val = 0.0f;
+      for (uint32_t py = py_min; py < py_max; ++py)
+        for (uint32_t px = px_min; px < px_max; ++px) {
+          const float pg = Reducer::PartialGrad(vsrc, pp[py * pw + px]);
+          val = __fadd_rn(val, __fmul_rn(pg, gp[py * pw + px]));
+        }
+      dst[(static_cast<int64_t>(first) * h + row) * ld_dst + x] = val;
+    }
+    tma::FenceAsyncShared();
+    __syncthreads();
+  }
+}
+
+/*!
+ * \brief channel-window pooling with stride 1 and pad NSIZE/2 (the chpool(src, nsize) form).
+ *  A thread owns kLanes adjacent pixels of one image and marches over the channels with the
+ *  last NSIZE values in registers, so every input element is read from HBM once.
+ *  grid = (pixel tiles, images); `plane` = h*w elements per channel, dense.
+ */
+template <typename Reducer, int NSIZE, int kLanes>
+__global__ void __launch_bounds__(kPoolThreads)
+ChannelPoolKernel(float *dst, const float *src, uint32_t channels, uint32_t plane) {
+  constexpr int kPad = NSIZE / 2;
+  constexpr int kAhead = 4;          // loads issued this many channels before they are needed
+  constexpr int kRing = NSIZE + kAhead;
+  const uint32_t pix = (blockIdx.x * kPoolThreads + threadIdx.x) * kLanes;
+  if (pix >= plane) return;
+  const int64_t image = static_cast<int64_t>(blockIdx.y) * channels * plane;
+  const float *in = src + image + pix;
+  float *out = dst + image + pix;
+  float ring[kRing][kLanes];
+  float init;
+  Reducer::SetInitValue(init);
+  auto load = [&](int slot, int64_t c) {
+    if (c >= 0 && c < static_cast<int64_t>(channels)) {
+      if (kLanes == 4) {
+        const float4 p = __ldcs(reinterpret_cast<const float4 *>(in + c * plane));
+        ring[slot][0] = p.x;
+        ring[slot][1 % kLanes] = p.y;
+        ring[slot][2 % kLanes] = p.z;
+        ring[slot][3 % kLanes] = p.w;
+      } else {
+        ring[slot][0] = __ldcs(in + c * plane);
+      }
+    } else {
+#pragma unroll
+      for (int l = 0; l < kLanes; ++l) ring[slot][l] = init;
+    }
+  };
+  // ring slot of channel c is (c + kPad) mod kRing; preload channels -kPad .. kPad + kAhead - 1
+#pragma unroll
+  for (int s = 0; s < kRing; ++s) load(s, static_cast<int64_t>(s) - kPad);
+  for (uint32_t c0 = 0; c0 < channels; c0 += kRing) {
+#pragma unroll
+    for (int j = 0; j < kRing; ++j) {
+      const uint32_t c = c0 + j;
+      if (c < channels) {
+        // window of channel c: slots j .. j + NSIZE - 1 (mod kRing), ascending channel order
+        float res[kLanes];
+#pragma unroll
+        for (int l = 0; l < kLanes; ++l) res[l] = init;
+#pragma unroll
+        for (int t = 0; t < NSIZE; ++t)
+#pragma unroll
+          for (int l = 0; l < kLanes; ++l) Reducer::Reduce(res[l], ring[(j + t) % kRing][l]);
+        if (kLanes == 4) {
+          float4 p;
+          p.x = res[0];
+          p.y = res[1 % kLanes];
+          p.z = res[2 % kLanes];
+          p.w = res[3 % kLanes];
+          __stcs(reinterpret_cast<float4 *>(out + static_cast<int64_t>(c) * plane), p);
+        } else {
+          __stcs(out + static_cast<int64_t>(c) * plane, res[0]);
+        }
+        // slot j held channel c - kPad, which no later window needs: refill it with the
+        // channel kRing further on
+        load(j, static_cast<int64_t>(c) - kPad + kRing);
+      }
+    }
+  }
+}
+
+// ------------------------------- host side ----------------------------------------------
+
+namespace pooldetail {
+/*! \brief device status word (see tma.cuh); lives as long as the process */
+inline int *StatusWord() {
+  static std::mutex mu;
+  static std::map<int, int *> words;
+  int dev = 0;
+  MSHADOW_CUDA_CALL(cudaGetDevice(&dev));
+  std::lock_guard<std::mutex> lock(mu);
+  auto it = words.find(dev);
+  if (it == words.end()) {
+    int *p = nullptr;
+    MSHADOW_CUDA_CALL(cudaMalloc(&p, sizeof(int)));
+    MSHADOW_CUDA_CALL(cudaMemset(p, 0, sizeof(int)));
+    it = words.insert(std::make_pair(dev, p)).first;
+  }
+  return it->second;
+}
+
+/*! \brief planes per CTA: as many as fit `budget` bytes, in multiples of `quantum` */
+inline uint32_t GroupSize(uint64_t bytes_per_plane, uint32_t quantum, uint64_t budget, uint32_t planes) {
+  uint64_t g = budget / bytes_per_plane;
+  if (g >= quantum) g -= g % quantum;
+  if (g < 1) g = 1;
+  if (g > planes) g = planes;
+  if (g > 64) g = 64;
+  return static_cast<uint32_t>(g);
+}
+
+inline uint32_t Gcd(uint32_t a, uint32_t b) { return b == 0 ? a : Gcd(b, a % b); }
+}  // namespace pooldetail
+
+/*! \brief dynamic shared memory per CTA: forward leaves room for 4 CTAs per SM, backward for 3 */
+const uint64_t kPoolSmemBudget = 56 * 1024;
+const uint64_t kUnpoolSmemBudget = 74 * 1024;
+
+/*! \brief true when the plane kernels can run: at least one plane has to fit the budget */
+inline bool PoolPlanesFit(int64_t h, int64_t w, int64_t ph, int64_t pw, bool backward) {
+  const uint64_t per_plane = static_cast<uint64_t>(h) * w * 4 + (backward ? 2ull * ph * pw * 4 : 0ull);
+  return per_plane + 32 <= (backward ? kUnpoolSmemBudget : kPoolSmemBudget) && static_cast<int64_t>(h) * w < (1 << 24);
+}
+
+template <typename Reducer>
+inline void PoolPlanesLaunch(float *dst, const float *src, int64_t planes, int64_t h, int64_t w, int ky, int kx,
+                             int sy, int sx, int64_t ld_src, int64_t ld_dst, cudaStream_t stream) {
+  const uint32_t ph = static_cast<uint32_t>((h - ky) / sy + 1), pw = static_cast<uint32_t>((w - kx) / sx + 1);
+  if (planes == 0) return;
+  const uint32_t hw = static_cast<uint32_t>(h * w);
+  // groups start 16-byte aligned when their plane count is a multiple of 4 / gcd(h*w, 4)
+  const uint32_t quantum = 4 / pooldetail::Gcd(hw, 4);
+  const uint32_t gp = pooldetail::GroupSize(hw * 4ull, quantum, kPoolSmemBudget, static_cast<uint32_t>(planes));
+  const size_t smem = static_cast<size_t>(gp) * hw * 4;
+  const int groups = gpu_rt::CeilDiv(planes, gp);
+  const int cap = gpu_rt::CurrentDevice().sm_count * 16;
+  const int grid = groups < cap ? groups : cap;
+  const PoolGeom g = {ky, kx, sy, sx};
+  int *status = pooldetail::StatusWord();
+#define MSHADOW_B200_POOL_LAUNCH_(KY, KX, SY, SX)                                                                 \
+  {                                                                                                               \
+    auto kernel = PoolPlanesKernel<Reducer, KY, KX, SY, SX>;                                                      \
+    MSHADOW_CUDA_CALL(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,                   \
+                                           static_cast<int>(kPoolSmemBudget)));                                   \
+    kernel<<<grid, kPoolThreads, smem, stream>>>(dst, src, static_cast<uint32_t>(planes), static_cast<uint32_t>(h), \
+                                                static_cast<uint32_t>(w), ph, pw, g, ld_src, ld_dst, gp,          \
+                                                gpu_rt::FastDiv(pw), gpu_rt::FastDiv(ph), status);                \
+  }
+  if (ky == 3 && kx == 3 && sy == 2 && sx == 2) MSHADOW_B200_POOL_LAUNCH_(3, 3, 2, 2)
+  else if (ky == 2 && kx == 2 && sy == 2 && sx == 2) MSHADOW_B200_POOL_LAUNCH_(2, 2, 2, 2)
+  else MSHADOW_B200_POOL_LAUNCH_(0, 0, 0, 0)
+#undef MSHADOW_B200_POOL_LAUNCH_
+  MSHADOW_CUDA_POST_KERNEL_CHECK(PoolPlanesKernel);
+}
+
+template <typename Reducer>
+inline void UnpoolPlanesLaunch(float *dst, const float *src, const float *pooled, const float *gpooled,
+                               int64_t planes, int64_t h, int64_t w, int64_t ph, int64_t pw, int ky, int kx, int sy,
+                               int sx, int64_t ld_src, int64_t ld_pooled, int64_t ld_dst, cudaStream_t stream) {
+  if (planes == 0) return;
+  const uint32_t hw = static_cast<uint32_t>(h * w), phw = static_cast<uint32_t>(ph * pw);
+  const uint32_t q1 = 4 / pooldetail::Gcd(hw, 4), q2 = 4 / pooldetail::Gcd(phw, 4);
+  const uint32_t quantum = q1 > q2 ? q1 : q2;
+  const uint32_t gp = pooldetail::GroupSize((hw + 2ull * phw) * 4, quantum, kUnpoolSmemBudget - 32,
+                                            static_cast<uint32_t>(planes));
+  const size_t smem = (((static_cast<size_t>(gp) * hw + 3) & ~size_t(3)) +
+                       2 * ((static_cast<size_t>(gp) * phw + 3) & ~size_t(3))) * 4;
+  const int groups = gpu_rt::CeilDiv(planes, gp);
+  const int cap = gpu_rt::CurrentDevice().sm_count * 16;
+  const int grid = groups < cap ? groups : cap;
+  const PoolGeom g = {ky, kx, sy, sx};
+  int *status = pooldetail::StatusWord();
+#define MSHADOW_B200_UNPOOL_LAUNCH_(KY, KX, SY, SX)                                                               \
+  {                                                                                                               \
+    auto kernel = UnpoolPlanesKernel<Reducer, KY, KX, SY, SX>;                                                    \
+    MSHADOW_CUDA_CALL(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,                   \
+                                           static_cast<int>(kUnpoolSmemBudget)));                                 \
+    kernel<<<grid, kPoolThreads, smem, stream>>>(                                                                 \
+        dst, src, pooled, gpooled, static_cast<uint32_t>(planes), static_cast<uint32_t>(h),                       \
+        static_cast<uint32_t>(w), static_cast<uint32_t>(ph), static_cast<uint32_t>(pw), g, ld_src, ld_pooled,     \
+        ld_dst, gp, gpu_rt::FastDiv(static_cast<uint32_t>(w)), gpu_rt::FastDiv(static_cast<uint32_t>(h)),         \
+        gpu_rt::FastDiv(static_cast<uint32_t>(sy)), gpu_rt::FastDiv(static_cast<uint32_t>(sx)), status);          \
+  }
+  if (ky == 3 && kx == 3 && sy == 2 && sx == 2) MSHADOW_B200_UNPOOL_LAUNCH_(3, 3, 2, 2)
+  else if (ky == 2 && kx == 2 && sy == 2 && sx == 2) MSHADOW_B200_UNPOOL_LAUNCH_(2, 2, 2, 2)
+  else MSHADOW_B200_UNPOOL_LAUNCH_(0, 0, 0, 0)
+#undef MSHADOW_B200_UNPOOL_LAUNCH_
+  MSHADOW_CUDA_POST_KERNEL_CHECK(UnpoolPlanesKernel);
+}
+
+/*! \brief window sizes the register-ring channel kernel is instantiated for */
+inline bool ChannelPoolSupported(int nsize, int stride, int pad) {
+  return stride == 1 && pad == nsize / 2 && (nsize == 1 || nsize == 3 || nsize == 5 || nsize == 7 || nsize == 9);
+}
+
+/*! \brief dense (n, c, h, w) in and out; requires ChannelPoolSupported */
+template <typename Reducer>
+inline void ChannelPoolLaunch(float *dst, const float *src, int64_t n, int64_t c, int64_t h, int64_t w, int nsize,
+                              cudaStream_t stream) {
+  if (n == 0 || c == 0 || h * w == 0) return;
+  const uint32_t plane = static_cast<uint32_t>(h * w);
+  const bool vec = plane % 4 == 0 && reinterpret_cast<uintptr_t>(dst) % 16 == 0 &&
+                   reinterpret_cast<uintptr_t>(src) % 16 == 0;
+  CHECK_LT(n, 65536) << "chpool: too many images for one launch";
+#define MSHADOW_B200_CHPOOL_LAUNCH_(NS)                                                                        \
+  if (vec) {                                                                                                   \
+    ChannelPoolKernel<Reducer, NS, 4><<<dim3(gpu_rt::CeilDiv(plane / 4, kPoolThreads), n), kPoolThreads, 0,    \
+                                       stream>>>(dst, src, static_cast<uint32_t>(c), plane);                   \
+  } else {                                                                                                     \
+    ChannelPoolKernel<Reducer, NS, 1><<<dim3(gpu_rt::CeilDiv(plane, kPoolThreads), n), kPoolThreads, 0,        \
+                                       stream>>>(dst, src, static_cast<uint32_t>(c), plane);                   \
+  }
+  switch (nsize) {
+    case 1: MSHADOW_B200_CHPOOL_LAUNCH_(1) break;
+    case 3: MSHADOW_B200_CHPOOL_LAUNCH_(3) break;
+    case 5: MSHADOW_B200_CHPOOL_LAUNCH_(5) break;
+    case 7: MSHADOW_B200_CHPOOL_LAUNCH_(7) break;
+    default: MSHADOW_B200_CHPOOL_LAUNCH_(9) break;
+  }
+#undef MSHADOW_B200_CHPOOL_LAUNCH_
+  MSHADOW_CUDA_POST_KERNEL_CHECK(ChannelPoolKernel);
+}
+
+}  // namespace cuda
+}  // namespace mshadow
+#endif  // MSHADOW_GPU_POOL_CUH_

@@ -1,0 +1,337 @@
+/*
+ * Reductions of a matrix-viewed expression to a vector:
+ *   KeepLowest   dst[x] <Saver>= scale * Reduce_y plan(y, x)               (column reduce)
+ *   KeepHighDim  dst[c] <Saver>= scale * Reduce_{n,y,x} plan((n*C+c)*H+y, x) (channel reduce)
+ * They replace MapRedKeepLowestKernel / MapReduceKeepDim1Kernel and the shared-memory tree
+ * of the reference (mshadow/cuda/tensor_gpu-inl.cuh:122-215, mshadow/cuda/reduce.cuh:42-116),
+ * which give each output column strip / channel to a single CTA -- 128 CTAs for a 4096-wide
+ * matrix, each walking all 65536 rows -- and so cannot fill a 148-SM device.
+ *
+ * Here the reduced extent is split over many CTAs.  Each thread accumulates 16-byte groups
+ * in registers; inside a CTA values meet through warp shuffles and a small shared buffer;
+ * the CTAs of a thread-block cluster (up to 8, laid along the reduced extent) meet through
+ * distributed shared memory, read by the cluster's first CTA in rank order; and if more
+ * than one cluster covers an output, cluster results go to a scratch matrix that a small
+ * second kernel folds in a fixed order.  Every combine order is fixed by the launch
+ * geometry, so results are reproducible run to run.  Both kernels are bound by HBM
+ * bandwidth: 4 bytes read per input element, nothing else of size.
+ */
+#ifndef MSHADOW_GPU_REDUCE_CUH_
+#define MSHADOW_GPU_REDUCE_CUH_
+
+#include <cooperative_groups.h>
+
+#include "./runtime.h"
+
+namespace mshadow {
+namespace cuda {
+
+namespace cg = cooperative_groups;
+
+const int kRedLowThreads = 128;
+const int kRedHighThreads = 256;
+const int kRedMaxCluster = 8;
+
+namespace reddetail {
+
+/*! \brief kLanes consecutive elements of a plan row, by one 128-bit access when kLanes > 1 */
+template <int kLanes, typename DType, typename SPlan>
+__device__ __forceinline__ void LoadLanes(const SPlan &plan, index_t y, index_t x, DType (&out)[kLanes]) {
+  if constexpr (kLanes == 1) {
+    out[0] = plan.Eval(y, x);
+  } else {
+    const expr::Pack<DType> p = plan.EvalPack(y, x);
+#pragma unroll
+    for (int l = 0; l < kLanes; ++l) out[l] = p.v[l];
+  }
+}
+
+template <typename DType>
+__device__ __forceinline__ DType ShflDown(DType v, int delta) {
+  if constexpr (sizeof(DType) == 8) {
+    const unsigned long long b = __shfl_down_sync(0xffffffffu, *reinterpret_cast<unsigned long long *>(&v), delta);
+    return *reinterpret_cast<const DType *>(&b);
+  } else {
+    static_assert(sizeof(DType) <= 4, "unsupported element size");
+    unsigned int raw = 0;
+    memcpy(&raw, &v, sizeof(DType));
+    raw = __shfl_down_sync(0xffffffffu, raw, delta);
+    DType r;
+    memcpy(&r, &raw, sizeof(DType));
+    return r;
+  }
+}
+
+/*! \brief fold the values of a CTA into thread 0; `buf` holds one element per warp */
+template <typename Reducer, typename DType, int kThreads>
+__device__ __forceinline__ DType BlockReduce(DType v, DType *buf) {
+#pragma unroll
+  for (int d = 16; d > 0; d >>= 1) {
+    DType o = ShflDown(v, d);
+    Reducer::Reduce(v, o);
+  }
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (lane == 0) buf[warp] = v;
+  __syncthreads();
+  if (warp == 0) {
+    DType init;
+    Reducer::SetInitValue(init);
+    v = lane < kThreads / 32 ? buf[lane] : init;
+#pragma unroll
+    for (int d = 16; d > 0; d >>= 1) {
+      DType o = ShflDown(v, d);
+      Reducer::Reduce(v, o);
+    }
+  }
+  return v;
+}
+
+}  // namespace reddetail
+
+/*!
+ * \brief column reduce.  grid = (column tiles, row chunks); a cluster spans row chunks.
+ *  Each thread owns kLanes adjacent columns and the rows of its chunk.
+ *  If `partial` is null the grid has a single cluster per column tile and results go
+ *  straight to `dst`; otherwise cluster c writes row c of the `partial` matrix.
+ */
+template <typename Saver, typename Reducer, int kLanes, typename DType, typename DPlan, typename SPlan>
+__global__ void __launch_bounds__(kRedLowThreads)
+ReduceKeepLowestKernel(DPlan dst, const SPlan src, uint32_t rows, uint32_t cols, uint32_t rows_per_chunk,
+                       DType scale, DType *partial) {
+  __shared__ __align__(16) DType stage[kRedLowThreads * kLanes];
+  cg::cluster_group cluster = cg::this_cluster();
+  const uint32_t x = (blockIdx.x * kRedLowThreads + threadIdx.x) * kLanes;
+  const uint32_t y0 = blockIdx.y * rows_per_chunk;
+  uint32_t y1 = y0 + rows_per_chunk;
+  if (y1 > rows) y1 = rows;
+  const bool live = x < cols && y0 < y1;
+  DType acc[kLanes];
+  if (live) {
+    reddetail::LoadLanes<kLanes>(src, y0, x, acc);
+    uint32_t y = y0 + 1;
+    constexpr int kDepth = 8;
+    for (; y + kDepth <= y1; y += kDepth) {
+      DType v[kDepth][kLanes];
+#pragma unroll
+      for (int k = 0; k < kDepth; ++k) reddetail::LoadLanes<kLanes>(src, y + k, x, v[k]);
+#pragma unroll
+      for (int k = 0; k < kDepth; ++k)
+#pragma unroll
+        for (int l = 0; l < kLanes; ++l) Reducer::Reduce(acc[l], v[k][l]);
+    }
+    for (; y < y1; ++y) {
+      DType v[kLanes];
+      reddetail::LoadLanes<kLanes>(src, y, x, v);
+#pragma unroll
+      for (int l = 0; l < kLanes; ++l) Reducer::Reduce(acc[l], v[l]);
+    }
+  }
+  const unsigned csize = cluster.num_blocks();
+  if (csize > 1) {
+    // meet the other row chunks of this cluster through distributed shared memory
+    const unsigned crank = cluster.block_rank();
+    if (crank != 0 && live) {
+#pragma unroll
+      for (int l = 0; l < kLanes; ++l) stage[threadIdx.x * kLanes + l] = acc[l];
+    }
+    cluster.sync();
+    if (crank == 0 && live) {
+      for (unsigned r = 1; r < csize; ++r) {
+        // a later chunk may lie wholly past the last row; it then holds nothing
+        if ((blockIdx.y + r) * rows_per_chunk >= rows) break;
+        const DType *remote = cluster.map_shared_rank(stage, r);
+#pragma unroll
+        for (int l = 0; l < kLanes; ++l) Reducer::Reduce(acc[l], remote[threadIdx.x * kLanes + l]);
+      }
+    }
+    cluster.sync();  // keep every CTA's shared memory alive until the first CTA has read it
+    if (crank != 0) return;
+  }
+  if (!live) return;
+  if (partial == nullptr) {
+#pragma unroll
+    for (int l = 0; l < kLanes; ++l) {
+      if (x + l < cols) Saver::Save(dst.REval(0, x + l), DType(acc[l] * scale));
+    }
+  } else {
+    DType *row = partial + static_cast<size_t>(blockIdx.y / csize) * cols;
+#pragma unroll
+    for (int l = 0; l < kLanes; ++l) {
+      if (x + l < cols) row[x + l] = acc[l];
+    }
+  }
+}
+
+/*! \brief fold `nparts` rows of the scratch matrix, in row order, into dst */
+template <typename Saver, typename Reducer, typename DType, typename DPlan>
+__global__ void ReduceFinishKernel(DPlan dst, const DType *partial, uint32_t nparts, uint32_t cols,
+                                   DType scale) {
+  const uint32_t x = blockIdx.x * blockDim.x + threadIdx.x;
+  if (x >= cols) return;
+  DType acc = partial[x];
+  for (uint32_t k = 1; k < nparts; ++k) Reducer::Reduce(acc, partial[static_cast<size_t>(k) * cols + x]);
+  Saver::Save(dst.REval(0, x), DType(acc * scale));
+}
+
+/*!
+ * \brief channel reduce.  grid = (channels, n chunks); a cluster spans n chunks.
+ *  The (inner_rows x width) plane of every (n, c) is walked as packs_per_row groups per
+ *  row; `width` must be a multiple of kLanes.
+ */
+template <typename Saver, typename Reducer, int kLanes, typename DType, typename DPlan, typename SPlan>
+__global__ void __launch_bounds__(kRedHighThreads)
+ReduceKeepHighDimKernel(DPlan dst, const SPlan src, uint32_t outer, uint32_t channels, uint32_t inner_rows,
+                        uint32_t packs_per_row, gpu_rt::FastDiv row_of_pack, uint32_t outer_per_chunk,
+                        DType scale, DType *partial) {
+  __shared__ DType warp_buf[kRedHighThreads / 32];
+  __shared__ DType cta_val;
+  cg::cluster_group cluster = cg::this_cluster();
+  const uint32_t c = blockIdx.x;
+  const uint32_t n0 = blockIdx.y * outer_per_chunk;
+  uint32_t n1 = n0 + outer_per_chunk;
+  if (n1 > outer) n1 = outer;
+  const uint32_t per_plane = inner_rows * packs_per_row;
+  DType acc[kLanes];
+#pragma unroll
+  for (int l = 0; l < kLanes; ++l) Reducer::SetInitValue(acc[l]);
+  constexpr int kDepth = 4;
+  for (uint32_t n = n0; n < n1; ++n) {
+    const uint32_t row0 = (n * channels + c) * inner_rows;
+    for (uint32_t base = threadIdx.x; base < per_plane; base += kRedHighThreads * kDepth) {
+      DType v[kDepth][kLanes];
+#pragma unroll
+      for (int k = 0; k < kDepth; ++k) {
+        const uint32_t i = base + k * kRedHighThreads;
+        if (i < per_plane) {
+          const uint32_t y = inner_rows == 1 ? 0 : row_of_pack.Quot(i);
+          reddetail::LoadLanes<kLanes>(src, row0 + y, (i - y * packs_per_row) * kLanes, v[k]);
+        } else {
+#pragma unroll
+          for (int l = 0; l < kLanes; ++l) Reducer::SetInitValue(v[k][l]);
+        }
+      }
+#pragma unroll
+      for (int k = 0; k < kDepth; ++k)
+#pragma unroll
+        for (int l = 0; l < kLanes; ++l) Reducer::Reduce(acc[l], v[k][l]);
+    }
+  }
+#pragma unroll
+  for (int l = 1; l < kLanes; ++l) Reducer::Reduce(acc[0], acc[l]);
+  DType total = reddetail::BlockReduce<Reducer, DType, kRedHighThreads>(acc[0], warp_buf);
+  const unsigned csize = cluster.num_blocks();
+  if (csize > 1) {
+    const unsigned crank = cluster.block_rank();
+    if (threadIdx.x == 0) cta_val = total;
+    cluster.sync();
+    if (crank == 0 && threadIdx.x == 0) {
+      for (unsigned r = 1; r < csize; ++r) {
+        const DType *remote = cluster.map_shared_rank(&cta_val, r);
+        Reducer::Reduce(total, *remote);
+      }
+    }
+    cluster.sync();
+    if (crank != 0) return;
+  }
+  if (threadIdx.x != 0) return;
+  if (partial == nullptr) {
+    Saver::Save(dst.REval(0, c), DType(total * scale));
+  } else {
+    partial[static_cast<size_t>(blockIdx.y / csize) * channels + c] = total;
+  }
+}
+
+namespace reddetail {
+/*! \brief launch with a (1, cluster_y, 1) thread-block cluster */
+template <typename Kernel, typename... Args>
+inline void LaunchClustered(Kernel kernel, dim3 grid, dim3 block, unsigned cluster_y, cudaStream_t stream,
+                            Args... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = 0;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 1;
+  attr[0].val.clusterDim.y = cluster_y;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  MSHADOW_CUDA_CALL(cudaLaunchKernelEx(&cfg, kernel, args...));
+}
+
+/*! \brief split `extent` into chunks: about `want` of them, a multiple of the cluster size */
+struct Split {
+  uint32_t per_chunk, chunks, cluster, clusters;
+};
+inline Split PlanSplit(uint32_t extent, uint32_t want, uint32_t min_per_chunk) {
+  Split s;
+  uint32_t chunks = want < 1 ? 1 : want;
+  const uint32_t max_chunks = (extent + min_per_chunk - 1) / min_per_chunk;
+  if (chunks > max_chunks) chunks = max_chunks;
+  if (chunks < 1) chunks = 1;
+  s.per_chunk = (extent + chunks - 1) / chunks;
+  chunks = (extent + s.per_chunk - 1) / s.per_chunk;  // drop chunks that would be empty
+  s.cluster = chunks < static_cast<uint32_t>(kRedMaxCluster) ? chunks : kRedMaxCluster;
+  s.clusters = (chunks + s.cluster - 1) / s.cluster;
+  s.chunks = s.clusters * s.cluster;  // trailing chunks of the last cluster may be empty
+  return s;
+}
+}  // namespace reddetail
+
+/*! \brief host side of the column reduce */
+template <typename Saver, typename Reducer, int kLanes, typename DType, typename DPlan, typename SPlan>
+inline void ReduceKeepLowestLaunch(DPlan dplan, const SPlan &splan, Shape<2> eshape, DType scale,
+                                   cudaStream_t stream) {
+  const uint32_t rows = eshape[0], cols = eshape[1];
+  const int sms = gpu_rt::CurrentDevice().sm_count;
+  const uint32_t col_tiles = gpu_rt::CeilDiv(cols, kRedLowThreads * kLanes);
+  // aim at 16 CTAs of 128 threads per SM; at least 32 rows per chunk
+  const reddetail::Split sp = reddetail::PlanSplit(rows, (sms * 16 + col_tiles - 1) / col_tiles, 32);
+  DType *partial = nullptr;
+  if (sp.clusters > 1) {
+    partial = static_cast<DType *>(
+        gpu_rt::Scratch::Get(stream, static_cast<size_t>(sp.clusters) * cols * sizeof(DType)));
+  }
+  auto kernel = ReduceKeepLowestKernel<Saver, Reducer, kLanes, DType, DPlan, SPlan>;
+  reddetail::LaunchClustered(kernel, dim3(col_tiles, sp.chunks), dim3(kRedLowThreads), sp.cluster, stream,
+                             dplan, splan, rows, cols, sp.per_chunk, scale, partial);
+  MSHADOW_CUDA_POST_KERNEL_CHECK(ReduceKeepLowestKernel);
+  if (partial != nullptr) {
+    ReduceFinishKernel<Saver, Reducer, DType, DPlan>
+        <<<gpu_rt::CeilDiv(cols, 256), 256, 0, stream>>>(dplan, partial, sp.clusters, cols, scale);
+    MSHADOW_CUDA_POST_KERNEL_CHECK(ReduceFinishKernel);
+  }
+}
+
+/*! \brief host side of the channel reduce; pshape = (outer, channels, inner rows, width) */
+template <typename Saver, typename Reducer, int kLanes, typename DType, typename DPlan, typename SPlan>
+inline void ReduceKeepHighDimLaunch(DPlan dplan, const SPlan &splan, Shape<4> pshape, DType scale,
+                                    cudaStream_t stream) {
+  const uint32_t outer = pshape[0], channels = pshape[1], inner_rows = pshape[2], width = pshape[3];
+  CHECK_EQ(width % kLanes, 0U);
+  const uint32_t ppr = width / kLanes;
+  const int sms = gpu_rt::CurrentDevice().sm_count;
+  // aim at 8 CTAs of 256 threads per SM
+  const reddetail::Split sp = reddetail::PlanSplit(outer, (sms * 8 + channels - 1) / channels, 1);
+  DType *partial = nullptr;
+  if (sp.clusters > 1) {
+    partial = static_cast<DType *>(
+        gpu_rt::Scratch::Get(stream, static_cast<size_t>(sp.clusters) * channels * sizeof(DType)));
+  }
+  auto kernel = ReduceKeepHighDimKernel<Saver, Reducer, kLanes, DType, DPlan, SPlan>;
+  reddetail::LaunchClustered(kernel, dim3(channels, sp.chunks), dim3(kRedHighThreads), sp.cluster, stream,
+                             dplan, splan, outer, channels, inner_rows, ppr, gpu_rt::FastDiv(ppr),
+                             sp.per_chunk, scale, partial);
+  MSHADOW_CUDA_POST_KERNEL_CHECK(ReduceKeepHighDimKernel);
+  if (partial != nullptr) {
+    ReduceFinishKernel<Saver, Reducer, DType, DPlan>
+        <<<gpu_rt::CeilDiv(channels, 256), 256, 0, stream>>>(dplan, partial, sp.clusters, channels, scale);
+    MSHADOW_CUDA_POST_KERNEL_CHECK(ReduceFinishKernel);
+  }
+}
+
+}  // namespace cuda
+}  // namespace mshadow
+#endif  // MSHADOW_GPU_REDUCE_CUH_

@@ -1,0 +1,264 @@
+/*
+ * Host-side GPU runtime of the engine: Stream<gpu>, engine life cycle, device memory,
+ * copies, launch-geometry helpers and the library-owned scratch buffers.
+ *
+ * The API follows dmlc/mshadow's mshadow/stream_gpu-inl.h (:18-211) and
+ * mshadow/tensor_gpu-inl.h (:14-92).  Differences: there is no BLAS / cuDNN / cuSOLVER
+ * handle (matrix products are outside this engine; the creation flags are accepted and
+ * ignored), and kernels that need scratch memory obtain it from a per-(device, stream)
+ * cache kept here, so that the "operators allocate no temporaries" contract of the
+ * reference (README.md:19-20) still holds from the caller's point of view.
+ */
+#ifndef MSHADOW_GPU_RUNTIME_H_
+#define MSHADOW_GPU_RUNTIME_H_
+
+#include <cuda_runtime.h>
+
+#include <map>
+#include <mutex>
+#include <utility>
+
+#include "../tensor.h"
+
+/*! \brief check that the launch just issued was accepted by the driver */
+#define MSHADOW_CUDA_POST_KERNEL_CHECK(name)                                              \
+  {                                                                                       \
+    cudaError_t msh_err_ = cudaPeekAtLastError();                                         \
+    CHECK_EQ(msh_err_, cudaSuccess) << "Name: " << #name << " ErrStr:" << cudaGetErrorString(msh_err_); \
+  }
+
+namespace mshadow {
+
+/*! \brief execution queue of a CUDA device */
+template <>
+struct Stream<gpu> {
+  cudaStream_t stream_;
+  int dev_id;
+  Stream() : stream_(0), dev_id(0) {}
+  inline void Wait() { MSHADOW_CUDA_CALL(cudaStreamSynchronize(stream_)); }
+  inline bool CheckIdle() {
+    const cudaError_t err = cudaStreamQuery(stream_);
+    if (err == cudaSuccess) return true;
+    if (err == cudaErrorNotReady) return false;
+    LOG(FATAL) << cudaGetErrorString(err);
+    return false;
+  }
+  inline void CreateBlasHandle() {}
+  /*! \brief raw stream of a possibly-null Stream pointer; null is fatal under MSHADOW_FORCE_STREAM */
+  inline static cudaStream_t GetStream(Stream<gpu> *stream) {
+    if (stream == NULL) {
+#if MSHADOW_FORCE_STREAM
+      LOG(FATAL) << "Default GPU stream was used when MSHADOW_FORCE_STREAM was on";
+#endif
+      return 0;
+    }
+    return stream->stream_;
+  }
+};
+
+namespace gpu_rt {
+
+/*! \brief properties of the current device that launch heuristics need; queried once per device */
+struct DeviceInfo {
+  int sm_count;
+  int max_smem_optin;
+  int l2_bytes;
+};
+
+inline const DeviceInfo &CurrentDevice() {
+  static std::mutex mu;
+  static std::map<int, DeviceInfo> cache;
+  int dev = 0;
+  MSHADOW_CUDA_CALL(cudaGetDevice(&dev));
+  std::lock_guard<std::mutex> lock(mu);
+  auto it = cache.find(dev);
+  if (it == cache.end()) {
+    DeviceInfo info;
+    MSHADOW_CUDA_CALL(cudaDeviceGetAttribute(&info.sm_count, cudaDevAttrMultiProcessorCount, dev));
+    MSHADOW_CUDA_CALL(
+        cudaDeviceGetAttribute(&info.max_smem_optin, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev));
+    MSHADOW_CUDA_CALL(cudaDeviceGetAttribute(&info.l2_bytes, cudaDevAttrL2CacheSize, dev));
+    it = cache.insert(std::make_pair(dev, info)).first;
+  }
+  return it->second;
+}
+
+/*!
+ * \brief scratch buffers, one per (device, stream), grown on demand and never shrunk.
+ *  Work that uses a buffer is ordered on its stream, so one buffer per stream is race-free;
+ *  growing synchronises that stream before the old buffer is released.
+ */
+class Scratch {
+ public:
+  static void *Get(cudaStream_t stream, size_t bytes) {
+    int dev = 0;
+    MSHADOW_CUDA_CALL(cudaGetDevice(&dev));
+    std::lock_guard<std::mutex> lock(Mutex());
+    Slot &slot = Table()[std::make_pair(dev, stream)];
+    if (slot.bytes < bytes) {
+      if (slot.ptr != nullptr) {
+        MSHADOW_CUDA_CALL(cudaStreamSynchronize(stream));
+        MSHADOW_CUDA_CALL(cudaFree(slot.ptr));
+        slot.ptr = nullptr;
+        slot.bytes = 0;
+      }
+      size_t want = bytes + bytes / 2;
+      want = (want + 255) / 256 * 256;
+      MSHADOW_CUDA_CALL(cudaMalloc(&slot.ptr, want));
+      slot.bytes = want;
+    }
+    return slot.ptr;
+  }
+  /*! \brief release the buffers of one stream on the current device (stream == all: every buffer) */
+  static void Release(bool all, cudaStream_t stream) {
+    int dev = 0;
+    if (!all) MSHADOW_CUDA_CALL(cudaGetDevice(&dev));
+    std::lock_guard<std::mutex> lock(Mutex());
+    auto &table = Table();
+    for (auto it = table.begin(); it != table.end();) {
+      if (all || (it->first.first == dev && it->first.second == stream)) {
+        if (it->second.ptr != nullptr) {
+          int cur = 0;
+          cudaGetDevice(&cur);
+          cudaSetDevice(it->first.first);
+          cudaFree(it->second.ptr);
+          cudaSetDevice(cur);
+        }
+        it = table.erase(it);
+      } else {
+        ++it;
+      }
+    }
+  }
+
+ private:
+  struct Slot {
+    void *ptr = nullptr;
+    size_t bytes = 0;
+  };
+  static std::mutex &Mutex() {
+    static std::mutex mu;
+    return mu;
+  }
+  static std::map<std::pair<int, cudaStream_t>, Slot> &Table() {
+    static std::map<std::pair<int, cudaStream_t>, Slot> table;
+    return table;
+  }
+};
+
+/*! \brief exact division of a non-negative 31-bit number by a fixed divisor, without a divide */
+struct FastDiv {
+  uint32_t mul;
+  uint32_t shift;
+  uint32_t div;
+  FastDiv() : mul(0), shift(0), div(1) {}
+  explicit FastDiv(uint32_t d) : div(d) {
+    // q = (n * mul) >> (31 + ceil(log2 d)) is exact for all n < 2^31 (round-up method)
+    uint32_t lg = 0;
+    while ((1ull << lg) < d) ++lg;
+    shift = 31 + lg;
+    mul = static_cast<uint32_t>(((1ull << shift) + d - 1) / d);
+  }
+  MSHADOW_XINLINE uint32_t Quot(uint32_t n) const {
+    return div == 1 ? n : static_cast<uint32_t>((static_cast<uint64_t>(n) * mul) >> shift);
+  }
+};
+
+inline int CeilDiv(int64_t a, int64_t b) { return static_cast<int>((a + b - 1) / b); }
+
+}  // namespace gpu_rt
+
+template <>
+inline void InitTensorEngine<gpu>(int dev_id) {
+  int device_count = 0;
+  cudaGetDeviceCount(&device_count);
+  CHECK_GT(device_count, 0) << "Cannot find CUDA device. Please check CUDA-Configuration";
+  const int device_id = dev_id < 0 ? 0 : dev_id;
+  CHECK_LT(device_id, device_count) << "Incorrect Device ID";
+  MSHADOW_CUDA_CALL(cudaSetDevice(device_id));
+  gpu_rt::CurrentDevice();
+}
+template <>
+inline void ShutdownTensorEngine<gpu>() {
+  gpu_rt::Scratch::Release(true, 0);
+}
+template <>
+inline void SetDevice<gpu>(int devid) {
+  MSHADOW_CUDA_CALL(cudaSetDevice(devid));
+}
+template <>
+inline Stream<gpu> *NewStream<gpu>(bool, bool, int dev_id) {
+  Stream<gpu> *st = new Stream<gpu>();
+  MSHADOW_CUDA_CALL(cudaStreamCreate(&st->stream_));
+  if (dev_id < 0) {
+    MSHADOW_CUDA_CALL(cudaGetDevice(&st->dev_id));
+  } else {
+    st->dev_id = dev_id;
+  }
+  return st;
+}
+template <>
+inline void DeleteStream<gpu>(Stream<gpu> *stream) {
+  if (stream == NULL) return;
+  gpu_rt::Scratch::Release(false, stream->stream_);
+  MSHADOW_CUDA_CALL(cudaStreamDestroy(stream->stream_));
+  delete stream;
+}
+
+template <int dim, typename DType>
+inline void AllocSpace(Tensor<gpu, dim, DType> *obj, bool pad) {
+  size_t pitch = 0;
+  const Shape<2> flat = obj->shape_.FlatTo2D();
+  if (pad && obj->size(dim - 1) >= MSHADOW_MIN_PAD_RATIO * 32) {
+    MSHADOW_CUDA_CALL(cudaMallocPitch(reinterpret_cast<void **>(&obj->dptr_), &pitch,
+                                      flat[1] * sizeof(DType), flat[0]));
+    obj->stride_ = static_cast<index_t>(pitch / sizeof(DType));
+  } else {
+    obj->stride_ = obj->size(dim - 1);
+    MSHADOW_CUDA_CALL(cudaMalloc(reinterpret_cast<void **>(&obj->dptr_),
+                                 static_cast<size_t>(flat[0]) * flat[1] * sizeof(DType)));
+  }
+}
+template <int dim, typename DType>
+inline void FreeSpace(Tensor<gpu, dim, DType> *obj) {
+  MSHADOW_CUDA_CALL(cudaFree(obj->dptr_));
+  obj->dptr_ = NULL;
+}
+
+namespace gpu_rt {
+template <typename A, typename B, int dim, typename DType>
+inline void CopyRows(Tensor<A, dim, DType> dst_nd, Tensor<B, dim, DType> src_nd, cudaMemcpyKind kind,
+                     Stream<gpu> *stream) {
+  CHECK_EQ(dst_nd.shape_, src_nd.shape_) << "Copy:shape mismatch";
+  const Tensor<A, 2, DType> dst = dst_nd.FlatTo2D();
+  const Tensor<B, 2, DType> src = src_nd.FlatTo2D();
+  const cudaStream_t s = Stream<gpu>::GetStream(stream);
+  if (dst.CheckContiguous() && src.CheckContiguous()) {
+    MSHADOW_CUDA_CALL(cudaMemcpyAsync(dst.dptr_, src.dptr_,
+                                      static_cast<size_t>(dst.size(0)) * dst.size(1) * sizeof(DType),
+                                      kind, s));
+  } else {
+    MSHADOW_CUDA_CALL(cudaMemcpy2DAsync(dst.dptr_, dst.stride_ * sizeof(DType), src.dptr_,
+                                        src.stride_ * sizeof(DType), dst.size(1) * sizeof(DType),
+                                        dst.size(0), kind, s));
+  }
+  // a copy issued without a stream behaves synchronously, as in the reference
+  if (stream == NULL) MSHADOW_CUDA_CALL(cudaStreamSynchronize(0));
+}
+}  // namespace gpu_rt
+
+template <int dim, typename DType>
+inline void Copy(Tensor<cpu, dim, DType> dst, const Tensor<gpu, dim, DType> &src, Stream<gpu> *stream) {
+  gpu_rt::CopyRows(dst, src, cudaMemcpyDeviceToHost, stream);
+}
+template <int dim, typename DType>
+inline void Copy(Tensor<gpu, dim, DType> dst, const Tensor<cpu, dim, DType> &src, Stream<gpu> *stream) {
+  gpu_rt::CopyRows(dst, src, cudaMemcpyHostToDevice, stream);
+}
+template <int dim, typename DType>
+inline void Copy(Tensor<gpu, dim, DType> dst, const Tensor<gpu, dim, DType> &src, Stream<gpu> *stream) {
+  gpu_rt::CopyRows(dst, src, cudaMemcpyDeviceToDevice, stream);
+}
+
+}  // namespace mshadow
+#endif  // MSHADOW_GPU_RUNTIME_H_

@@ -1,0 +1,286 @@
+/*
+ * Row softmax and the SoftmaxGrad family on the GPU.
+ *
+ * Softmax replaces the reference's SoftmaxKernel (mshadow/cuda/tensor_gpu-inl.cuh:330-393),
+ * which walks each row three times through global memory (20 bytes of traffic per element)
+ * with 256 threads.  Here a CTA loads its row once into registers (up to 32 floats per
+ * thread), finds the maximum, exponentiates and sums in registers, and writes the
+ * normalised row once: 8 bytes per element, the algorithmic minimum.  Rows that do not fit
+ * the register budget (more than 32768 columns) fall back to a three-sweep kernel whose
+ * second and third sweeps mostly hit the L2 cache.
+ *
+ * The arithmetic follows the reference's CPU definition (mshadow/tensor_cpu-inl.h:270-285):
+ * exp(x - max) with true division by the sum.  The sum is formed pairwise (registers, warp
+ * shuffles, shared memory) instead of left to right, which changes results by rounding only.
+ *
+ * SoftmaxGrad and its smooth / ignore-label variants (reference kernels :239-328) are
+ * element-wise copies with a per-row fix-up; they run as a 128-bit grid-stride sweep.
+ */
+#ifndef MSHADOW_GPU_SOFTMAX_CUH_
+#define MSHADOW_GPU_SOFTMAX_CUH_
+
+#include "./reduce.cuh"
+
+namespace mshadow {
+namespace cuda {
+
+namespace smdetail {
+struct MaxOp {
+  __device__ __forceinline__ static void Reduce(float &a, float b) { a = a < b ? b : a; }  // NOLINT(*)
+  __device__ __forceinline__ static void SetInitValue(float &a) { a = -FLT_MAX; }          // NOLINT(*)
+};
+struct SumOp {
+  __device__ __forceinline__ static void Reduce(float &a, float b) { a = __fadd_rn(a, b); }  // NOLINT(*)
+  __device__ __forceinline__ static void SetInitValue(float &a) { a = 0.0f; }                // NOLINT(*)
+};
+
+/*! \brief value of a CTA-wide reduction, broadcast to every thread */
+template <typename Op, int kThreads>
+__device__ __forceinline__ float BlockAll(float v, float *buf) {
+#pragma unroll
+  for (int d = 16; d > 0; d >>= 1) Op::Reduce(v, __shfl_xor_sync(0xffffffffu, v, d));
+  if (kThreads == 32) return v;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  __syncthreads();  // buf may still be read from a previous call
+  if (lane == 0) buf[warp] = v;
+  __syncthreads();
+  float init;
+  Op::SetInitValue(init);
+  v = lane < kThreads / 32 ? buf[lane] : init;
+#pragma unroll
+  for (int d = 16; d > 0; d >>= 1) Op::Reduce(v, __shfl_xor_sync(0xffffffffu, v, d));
+  return v;
+}
+}  // namespace smdetail
+
+/*!
+ * \brief one CTA per row, row resident in registers.  Thread t owns items t, t+kThreads, ...
+ *  (kItems of them), an item being kLanes adjacent floats.
+ */
+template <int kThreads, int kItems, int kLanes>
+__global__ void __launch_bounds__(kThreads)
+SoftmaxRowKernel(float *dst, const float *src, uint32_t rows, uint32_t cols, int64_t ld_dst, int64_t ld_src) {
+  __shared__ float buf[32];
+  const uint32_t nitems = (cols + kLanes - 1) / kLanes;
+  for (uint32_t y = blockIdx.x; y < rows; y += gridDim.x) {
+    const float *in = src + y * ld_src;
+    float *out = dst + y * ld_dst;
+    float v[kItems][kLanes];
+#pragma unroll
+    for (int k = 0; k < kItems; ++k) {
+      const uint32_t item = threadIdx.x + k * kThreads;
+      if (item < nitems) {
+        if (kLanes == 4) {
+          const float4 p = __ldcs(reinterpret_cast<const float4 *>(in) + item);
+          v[k][0] = p.x;
+          v[k][1 % kLanes] = p.y;
+          v[k][2 % kLanes] = p.z;
+          v[k][3 % kLanes] = p.w;
+        } else {
+          v[k][0] = __ldcs(in + item);
+        }
+      } else {
+#pragma unroll
+        for (int l = 0; l < kLanes; ++l) v[k][l] = -FLT_MAX;
+      }
+    }
+    float m = -FLT_MAX;
+#pragma unroll
+    for (int k = 0; k < kItems; ++k)
+#pragma unroll
+      for (int l = 0; l < kLanes; ++l) m = m < v[k][l] ? v[k][l] : m;
+    m = smdetail::BlockAll<smdetail::MaxOp, kThreads>(m, buf);
+    float s = 0.0f;
+#pragma unroll
+    for (int k = 0; k < kItems; ++k) {
+      const bool in_row = threadIdx.x + k * kThreads < nitems;
+#pragma unroll
+      for (int l = 0; l < kLanes; ++l) {
+        v[k][l] = in_row ? expf(__fsub_rn(v[k][l], m)) : 0.0f;
+        s = __fadd_rn(s, v[k][l]);
+      }
+    }
+    s = smdetail::BlockAll<smdetail::SumOp, kThreads>(s, buf);
+#pragma unroll
+    for (int k = 0; k < kItems; ++k) {
+      const uint32_t item = threadIdx.x + k * kThreads;
+      if (item < nitems) {
+        if (kLanes == 4) {
+          float4 p;
+          p.x = __fdiv_rn(v[k][0], s);
+          p.y = __fdiv_rn(v[k][1 % kLanes], s);
+          p.z = __fdiv_rn(v[k][2 % kLanes], s);
+          p.w = __fdiv_rn(v[k][3 % kLanes], s);
+          __stcs(reinterpret_cast<float4 *>(out) + item, p);
+        } else {
+          __stcs(out + item, __fdiv_rn(v[k][0], s));
+        }
+      }
+    }
+  }
+}
+
+/*! \brief any row length: three sweeps over global memory, one CTA per row */
+template <int kThreads>
+__global__ void __launch_bounds__(kThreads)
+SoftmaxSweepKernel(float *dst, const float *src, uint32_t rows, uint32_t cols, int64_t ld_dst, int64_t ld_src) {
+  __shared__ float buf[32];
+  for (uint32_t y = blockIdx.x; y < rows; y += gridDim.x) {
+    const float *in = src + y * ld_src;
+    float *out = dst + y * ld_dst;
+    float m = -FLT_MAX;
+    for (uint32_t x = threadIdx.x; x < cols; x += kThreads) m = m < in[x] ? in[x] : m;
+    m = smdetail::BlockAll<smdetail::MaxOp, kThreads>(m, buf);
+    float s = 0.0f;
+    for (uint32_t x = threadIdx.x; x < cols; x += kThreads) {
+      const float e = expf(__fsub_rn(in[x], m));
+      out[x] = e;
+      s = __fadd_rn(s, e);
+    }
+    s = smdetail::BlockAll<smdetail::SumOp, kThreads>(s, buf);
+    for (uint32_t x = threadIdx.x; x < cols; x += kThreads) out[x] = __fdiv_rn(out[x], s);
+  }
+}
+
+namespace smdetail {
+template <int kThreads, int kItems, int kLanes>
+inline void LaunchRow(float *dst, const float *src, uint32_t rows, uint32_t cols, int64_t ld_dst, int64_t ld_src,
+                      cudaStream_t stream) {
+  // persistent over rows only when there are more rows than a generous grid
+  const uint32_t cap = static_cast<uint32_t>(gpu_rt::CurrentDevice().sm_count) * 64u;
+  const uint32_t grid = rows < cap ? rows : cap;
+  SoftmaxRowKernel<kThreads, kItems, kLanes><<<grid, kThreads, 0, stream>>>(dst, src, rows, cols, ld_dst, ld_src);
+}
+}  // namespace smdetail
+
+/*! \brief dst = softmax(src) row by row; fp32 */
+inline void SoftmaxLaunch(float *dst, const float *src, int64_t rows, int64_t cols, int64_t ld_dst, int64_t ld_src,
+                          cudaStream_t stream) {
+  if (rows == 0 || cols == 0) return;
+  CHECK_LT(rows, (int64_t(1) << 31));
+  CHECK_LT(cols, (int64_t(1) << 31));
+  const uint32_t r = static_cast<uint32_t>(rows), c = static_cast<uint32_t>(cols);
+  const bool vec = cols % 4 == 0 && reinterpret_cast<uintptr_t>(dst) % 16 == 0 &&
+                   reinterpret_cast<uintptr_t>(src) % 16 == 0 && (rows == 1 || (ld_dst % 4 == 0 && ld_src % 4 == 0));
+  using smdetail::LaunchRow;
+  if (vec && cols <= 32768) {
+    const uint32_t n = c / 4;  // 16-byte items per row
+    if (n <= 32) LaunchRow<32, 1, 4>(dst, src, r, c, ld_dst, ld_src, stream);
+    else if (n <= 128) LaunchRow<128, 1, 4>(dst, src, r, c, ld_dst, ld_src, stream);
+    else if (n <= 256) LaunchRow<256, 1, 4>(dst, src, r, c, ld_dst, ld_src, stream);
+    else if (n <= 512) LaunchRow<256, 2, 4>(dst, src, r, c, ld_dst, ld_src, stream);
+    else if (n <= 1024) LaunchRow<256, 4, 4>(dst, src, r, c, ld_dst, ld_src, stream);
+    else if (n <= 2048) LaunchRow<512, 4, 4>(dst, src, r, c, ld_dst, ld_src, stream);
+    else if (n <= 4096) LaunchRow<1024, 4, 4>(dst, src, r, c, ld_dst, ld_src, stream);
+    else LaunchRow<1024, 8, 4>(dst, src, r, c, ld_dst, ld_src, stream);
+  } else if (cols <= 8192) {
+    if (c <= 32) LaunchRow<32, 1, 1>(dst, src, r, c, ld_dst, ld_src, stream);
+    else if (c <= 128) LaunchRow<128, 1, 1>(dst, src, r, c, ld_dst, ld_src, stream);
+    else if (c <= 512) LaunchRow<256, 2, 1>(dst, src, r, c, ld_dst, ld_src, stream);
+    else if (c <= 2048) LaunchRow<256, 8, 1>(dst, src, r, c, ld_dst, ld_src, stream);
+    else LaunchRow<512, 16, 1>(dst, src, r, c, ld_dst, ld_src, stream);
+  } else {
+    const uint32_t cap = static_cast<uint32_t>(gpu_rt::CurrentDevice().sm_count) * 16u;
+    SoftmaxSweepKernel<512><<<r < cap ? r : cap, 512, 0, stream>>>(dst, src, r, c, ld_dst, ld_src);
+  }
+  MSHADOW_CUDA_POST_KERNEL_CHECK(Softmax);
+}
+
+/*!
+ * \brief dst = src - onehot(label) with optional label smoothing (mode bit 0) and row
+ *  zeroing for ignored labels (mode bit 1); arithmetic as mshadow/tensor_cpu-inl.h:287-368.
+ */
+template <int kLanes>
+__global__ void __launch_bounds__(256)
+SoftmaxGradKernel(float *dst, const float *src, const float *label, uint32_t rows, uint32_t cols,
+                  uint32_t items_per_row, gpu_rt::FastDiv row_of_item, int64_t ld_dst, int64_t ld_src, int mode,
+                  int ignore_label, float alpha, float smooth_grad) {
+  const uint32_t total = rows * items_per_row;
+  const uint32_t step = gridDim.x * 256;
+  constexpr int kUnroll = 4;
+  for (uint32_t base = blockIdx.x * 256 + threadIdx.x; base < total; base += step * kUnroll) {
+    float v[kUnroll][kLanes];
+    int kk[kUnroll];
+#pragma unroll
+    for (int u = 0; u < kUnroll; ++u) {
+      const uint32_t i = base + u * step;
+      if (i < total) {
+        const uint32_t y = row_of_item.Quot(i);
+        const uint32_t x = (i - y * items_per_row) * kLanes;
+        const int k = static_cast<int>(label[y]);
+        kk[u] = k;
+        const bool zero_row = (mode & 2) && k == ignore_label;
+        if (zero_row) {
+#pragma unroll
+          for (int l = 0; l < kLanes; ++l) v[u][l] = 0.0f;
+        } else if (kLanes == 4) {
+          const float4 p = __ldcs(reinterpret_cast<const float4 *>(src + y * ld_src + x));
+          v[u][0] = p.x;
+          v[u][1 % kLanes] = p.y;
+          v[u][2 % kLanes] = p.z;
+          v[u][3 % kLanes] = p.w;
+        } else {
+          v[u][0] = __ldcs(src + y * ld_src + x);
+        }
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < kUnroll; ++u) {
+      const uint32_t i = base + u * step;
+      if (i < total) {
+        const uint32_t y = row_of_item.Quot(i);
+        const uint32_t x = (i - y * items_per_row) * kLanes;
+        const bool zero_row = (mode & 2) && kk[u] == ignore_label;
+        if (!zero_row) {
+#pragma unroll
+          for (int l = 0; l < kLanes; ++l) {
+            const bool hit = static_cast<int>(x) + l == kk[u];
+            if (mode & 1) {
+              v[u][l] = hit ? __fadd_rn(__fsub_rn(v[u][l], 1.0f), alpha) : __fsub_rn(v[u][l], smooth_grad);
+            } else if (hit) {
+              v[u][l] = __fsub_rn(v[u][l], 1.0f);
+            }
+          }
+        }
+        if (kLanes == 4) {
+          float4 p;
+          p.x = v[u][0];
+          p.y = v[u][1 % kLanes];
+          p.z = v[u][2 % kLanes];
+          p.w = v[u][3 % kLanes];
+          __stcs(reinterpret_cast<float4 *>(dst + y * ld_dst + x), p);
+        } else {
+          __stcs(dst + y * ld_dst + x, v[u][0]);
+        }
+      }
+    }
+  }
+}
+
+inline void SoftmaxGradLaunch(float *dst, const float *src, const float *label, int64_t rows, int64_t cols,
+                              int64_t ld_dst, int64_t ld_src, int mode, float ignore_label, float alpha,
+                              cudaStream_t stream) {
+  if (rows == 0 || cols == 0) return;
+  CHECK_LT(rows * cols, (int64_t(1) << 31)) << "SoftmaxGrad: tensor too large for 32-bit indexing";
+  const float smooth_grad = alpha / static_cast<float>(static_cast<index_t>(cols) - 1);
+  const bool vec = cols % 4 == 0 && reinterpret_cast<uintptr_t>(dst) % 16 == 0 &&
+                   reinterpret_cast<uintptr_t>(src) % 16 == 0 && (rows == 1 || (ld_dst % 4 == 0 && ld_src % 4 == 0));
+  const uint32_t r = static_cast<uint32_t>(rows), c = static_cast<uint32_t>(cols);
+  const uint32_t ipr = vec ? c / 4 : c;
+  const int64_t work = static_cast<int64_t>(r) * ipr;
+  int grid = gpu_rt::CeilDiv(work, 256 * 4);
+  const int cap = gpu_rt::CurrentDevice().sm_count * 8;
+  if (grid > cap) grid = cap;
+  if (vec) {
+    SoftmaxGradKernel<4><<<grid, 256, 0, stream>>>(dst, src, label, r, c, ipr, gpu_rt::FastDiv(ipr), ld_dst, ld_src,
+                                                  mode, static_cast<int>(ignore_label), alpha, smooth_grad);
+  } else {
+    SoftmaxGradKernel<1><<<grid, 256, 0, stream>>>(dst, src, label, r, c, ipr, gpu_rt::FastDiv(ipr), ld_dst, ld_src,
+                                                  mode, static_cast<int>(ignore_label), alpha, smooth_grad);
+  }
+  MSHADOW_CUDA_POST_KERNEL_CHECK(SoftmaxGrad);
+}
+
+}  // namespace cuda
+}  // namespace mshadow
+#endif  // MSHADOW_GPU_SOFTMAX_CUH_

@@ -1,0 +1,308 @@
+"""GPU parity: every C-ABI operator against the CPU oracle on the same seeded inputs.
+
+Tolerances (stated by the task for this path):
+  * bit-exact  pooling / unpooling / channel pooling, SoftmaxGrad, sorting, and every
+               element-wise expression built from + - * / and comparisons;
+  * <= 1 ulp   the sigmoid expression (its exp is evaluated to the host library's rounding);
+  * 1e-5       relative, for fp32 sums: reductions, softmax, AddTakeGrad.  For sums the
+               error is measured against max(|reference|, RMS of the reference output), since
+               an element-wise relative error is meaningless next to a zero crossing.
+"""
+import numpy as np
+import pytest
+
+import cpu_checkers as cc
+from cpu_checkers import pool_out
+
+torch = pytest.importorskip("torch")
+pytestmark = pytest.mark.gpu
+
+orc = cc.load("orc")
+
+
+@pytest.fixture(scope="module")
+def lib():
+    if not torch.cuda.is_available():
+        pytest.skip("no CUDA device")
+    import mshadow_b200
+    L = mshadow_b200.load()
+    L.init(0)
+    return L
+
+
+def dev(a, pad=0, fill=7.5):
+    """Copy a numpy array to the GPU, optionally with `pad` extra elements per row."""
+    a = np.asarray(a)
+    if pad == 0:
+        return torch.from_numpy(np.ascontiguousarray(a)).cuda()
+    buf = torch.full(a.shape[:-1] + (a.shape[-1] + pad,), fill, dtype=torch.from_numpy(a[..., :1].copy()).dtype,
+                     device="cuda")
+    view = buf[..., : a.shape[-1]]
+    view.copy_(torch.from_numpy(np.ascontiguousarray(a)))
+    return view
+
+
+def host(t):
+    return t.cpu().numpy()
+
+
+def ulp_diff(a, b):
+    ia = np.ascontiguousarray(a).view(np.int32).astype(np.int64)
+    ib = np.ascontiguousarray(b).view(np.int32).astype(np.int64)
+    # map the sign-magnitude float order onto a monotone integer line
+    ia = np.where(ia < 0, -(ia & 0x7FFFFFFF), ia)
+    ib = np.where(ib < 0, -(ib & 0x7FFFFFFF), ib)
+    return np.abs(ia - ib)
+
+
+def assert_bits(got, want):
+    got, want = np.ascontiguousarray(got), np.ascontiguousarray(want)
+    same = got.view(np.uint32) == want.view(np.uint32)
+    assert same.all(), "%d of %d elements differ; first at %s" % (
+        (~same).sum(), same.size, np.argwhere(~same)[0])
+
+
+def assert_sum_close(got, want, tol=1e-5):
+    scale = np.maximum(np.abs(want), np.sqrt(np.mean(want.astype(np.float64) ** 2)))
+    err = np.abs(got.astype(np.float64) - want) / np.maximum(scale, 1e-30)
+    assert err.max() <= tol, "max scaled error %.3g" % err.max()
+
+
+SHAPES = [((1, 1), 0), ((7, 13), 0), ((33, 64), 0), ((5, 100), 4), ((3, 31), 1), ((64, 257), 7),
+          ((16, 1024), 0), ((9, 1000), 24), ((300, 5), 0), ((2, 4099), 0)]
+
+
+@pytest.mark.parametrize("cid", range(10))
+@pytest.mark.parametrize("shape,pad", SHAPES)
+def test_expression_cases(lib, cid, shape, pad):
+    rng = np.random.default_rng(100 * cid + shape[0] + shape[1])
+    A = rng.uniform(-1, 1, shape).astype(np.float32)
+    B = rng.uniform(-1, 1, shape).astype(np.float32)
+    Cm = rng.uniform(0.5, 1.5, shape).astype(np.float32)
+    bias = rng.standard_normal(max(shape)).astype(np.float32)
+    d0 = rng.uniform(0.5, 2.0, shape).astype(np.float32)
+    want = orc.expr_case(cid, d0.copy(), A, B, Cm, bias)
+    d = dev(d0, pad)
+    lib.expr_case(cid, d, dev(A, pad), dev(B, pad), dev(Cm, pad), dev(bias))
+    got = host(d)
+    if cid == 0:
+        assert ulp_diff(got, want).max() <= 1
+    else:
+        assert_bits(got, want)
+
+
+def test_expression_in_place_and_padding_untouched(lib):
+    rng = np.random.default_rng(3)
+    A = rng.uniform(-1, 1, (17, 100)).astype(np.float32)
+    buf = torch.full((17, 104), 7.5, device="cuda")
+    view = buf[:, :100]
+    view.copy_(torch.from_numpy(A))
+    # dst aliases A: d *= A + 1.5
+    want = orc.expr_case(3, A.copy(), A, A, A, A[0])
+    lib.expr_case(3, view, view, view, view, dev(A[0]))
+    assert_bits(host(view), want)
+    assert bool((buf[:, 100:] == 7.5).all()), "row padding was overwritten"
+
+
+@pytest.mark.parametrize("reducer", [0, 1, 2])
+@pytest.mark.parametrize("saver", [0, 1, 2, 3, 4])
+@pytest.mark.parametrize("rows,cols,pad", [(1, 1, 0), (67, 45, 3), (1000, 128, 0), (4097, 260, 0), (33, 1030, 2),
+                                           (5000, 8, 0)])
+def test_reduce_keep_lowest(lib, reducer, saver, rows, cols, pad):
+    rng = np.random.default_rng(rows + cols + reducer)
+    src = rng.standard_normal((rows, cols)).astype(np.float32)
+    d0 = rng.uniform(1, 2, cols).astype(np.float32)
+    want = orc.reduce_keep_lowest(d0.copy(), src, scale=0.75, saver=saver, reducer=reducer)
+    got = host(lib.reduce_keep_lowest(dev(d0), dev(src, pad), scale=0.75, saver=saver, reducer=reducer))
+    if reducer == 0:
+        assert_sum_close(got, want)
+    else:
+        assert_bits(got, want)
+
+
+@pytest.mark.parametrize("reducer", [0, 1, 2])
+@pytest.mark.parametrize("saver", [0, 1, 4])
+@pytest.mark.parametrize("shape,pad", [((1, 1, 1, 1), 0), ((5, 6, 7, 9), 2), ((16, 32, 28, 28), 0),
+                                       ((3, 1030, 2, 4), 0), ((600, 3, 5, 8), 0), ((2, 7, 27, 27), 0)])
+def test_reduce_keep_highdim(lib, reducer, saver, shape, pad):
+    rng = np.random.default_rng(sum(shape) + reducer)
+    src = rng.standard_normal(shape).astype(np.float32)
+    d0 = rng.uniform(1, 2, shape[1]).astype(np.float32)
+    want = orc.reduce_keep_highdim(d0.copy(), src, scale=0.5, saver=saver, reducer=reducer)
+    got = host(lib.reduce_keep_highdim(dev(d0), dev(src, pad), scale=0.5, saver=saver, reducer=reducer))
+    if reducer == 0:
+        assert_sum_close(got, want)
+    else:
+        assert_bits(got, want)
+
+
+@pytest.mark.parametrize("rows,cols,pad", [(1, 1, 0), (4, 8, 0), (9, 1000, 0), (3, 33, 5), (5, 4096, 0),
+                                           (4, 32000, 0), (3, 31999, 0), (2, 8193, 0), (2, 40000, 0), (70, 513, 3),
+                                           (300, 128, 0)])
+def test_softmax(lib, rows, cols, pad):
+    rng = np.random.default_rng(rows * 1000 + cols)
+    src = (2.0 * rng.standard_normal((rows, cols))).astype(np.float32)
+    want = orc.softmax(np.zeros_like(src), src)
+    d = dev(np.zeros_like(src), pad)
+    lib.softmax(d, dev(src, pad))
+    got = host(d)
+    rel = np.abs(got.astype(np.float64) - want) / np.maximum(want, 1e-37)
+    assert rel[want > 0].max() <= 1e-5
+    assert np.all(got[want == 0] <= 1e-37)
+    # in place, as in Softmax(out, out)
+    s = dev(src, pad)
+    lib.softmax(s, s)
+    assert_bits(host(s), got)
+
+
+@pytest.mark.parametrize("mode", [0, 1, 2, 3])
+@pytest.mark.parametrize("rows,cols,pad", [(3, 5, 0), (9, 1000, 0), (4, 33, 3), (6, 32000, 0), (64, 260, 4)])
+def test_softmax_grad(lib, mode, rows, cols, pad):
+    rng = np.random.default_rng(rows + cols + mode)
+    prob = rng.uniform(0, 1, (rows, cols)).astype(np.float32)
+    label = rng.integers(0, cols, rows).astype(np.float32)
+    label[0], label[-1] = 0, cols - 1
+    ignore = float(label[1])
+    want = orc.softmax_grad(np.zeros_like(prob), prob, label, mode=mode, ignore_label=ignore, alpha=0.1)
+    d = dev(np.full_like(prob, 9.0), pad)
+    lib.softmax_grad(d, dev(prob, pad), dev(label), mode=mode, ignore_label=ignore, alpha=0.1)
+    assert_bits(host(d), want)
+
+
+POOL_CASES = [(5, 6, 6, 2, 2, 2, 2, 0), (5, 13, 11, 3, 3, 2, 2, 0), (3, 8, 9, 3, 2, 1, 3, 3), (2, 7, 7, 7, 7, 1, 1, 0),
+              (4, 10, 10, 2, 2, 3, 3, 0), (9, 56, 56, 3, 3, 2, 2, 0), (8, 27, 27, 3, 3, 2, 2, 0),
+              (70, 12, 12, 2, 2, 2, 2, 0), (3, 130, 120, 5, 4, 3, 2, 0)]
+
+
+@pytest.mark.parametrize("reducer", [0, 1, 2])
+@pytest.mark.parametrize("planes,h,w,ky,kx,sy,sx,pad", POOL_CASES)
+def test_pool_unpool(lib, reducer, planes, h, w, ky, kx, sy, sx, pad):
+    rng = np.random.default_rng(h * w + reducer + planes)
+    # values on a coarse grid produce many tied maxima
+    src = (rng.integers(0, 8, size=(planes, h, w)) * 0.125).astype(np.float32)
+    ph, pw = pool_out(h, ky, sy), pool_out(w, kx, sx)
+    g = rng.uniform(0, 1, (planes, ph, pw)).astype(np.float32)
+    wp = orc.pool(np.zeros((planes, ph, pw), np.float32), src, ky, kx, sy, sx, reducer=reducer)
+    wu = orc.unpool(np.zeros_like(src), src, wp, g, ky, kx, sy, sx, reducer=reducer)
+    dsrc = dev(src, pad)
+    dp = lib.pool(torch.zeros(planes, ph, pw, device="cuda"), dsrc, ky, kx, sy, sx, reducer=reducer)
+    assert_bits(host(dp), wp)
+    du = dev(np.zeros_like(src), pad)
+    lib.unpool(du, dsrc, dp, dev(g), ky, kx, sy, sx, reducer=reducer)
+    assert_bits(host(du), wu)
+
+
+def test_unpool_all_tied(lib):
+    x = np.ones((6, 6, 6), np.float32)
+    p = host(lib.pool(torch.zeros(6, 2, 2, device="cuda"), dev(x), 3, 3, 2, 2))
+    assert np.all(p == 1.0)
+    u = host(lib.unpool(torch.zeros(6, 6, 6, device="cuda"), dev(x), dev(p), dev(p), 3, 3, 2, 2))
+    assert u[0, 2, 2] == 4.0 and u[0, 0, 0] == 1.0 and u[0, 5, 5] == 0.0
+
+
+@pytest.mark.parametrize("reducer", [0, 1])
+@pytest.mark.parametrize("shape,nsize,stride,pad", [((3, 8, 4, 6), 5, 1, 2), ((2, 7, 5, 5), 3, 1, 1),
+                                                    ((2, 9, 4, 4), 3, 2, 1), ((1, 5, 2, 2), 5, 1, 2),
+                                                    ((2, 6, 3, 4), 1, 1, 0), ((2, 40, 14, 14), 5, 1, 2),
+                                                    ((2, 20, 7, 9), 7, 1, 3), ((1, 12, 8, 8), 9, 1, 4),
+                                                    ((2, 10, 6, 6), 5, 1, 0)])
+def test_chpool(lib, reducer, shape, nsize, stride, pad):
+    rng = np.random.default_rng(sum(shape) + nsize)
+    src = rng.uniform(-1, 1, shape).astype(np.float32)
+    co = (shape[1] - nsize + 2 * pad + 1) // stride
+    out_shape = (shape[0], co, shape[2], shape[3])
+    want = orc.chpool(np.zeros(out_shape, np.float32), src, nsize, stride, pad, reducer=reducer)
+    got = lib.chpool(torch.zeros(out_shape, device="cuda"), dev(src), nsize, stride, pad, reducer=reducer)
+    assert_bits(host(got), want)
+
+
+def zipf_indices(rng, n, k, s=1.1):
+    p = (np.arange(k) + 1.0) ** (-s)
+    return rng.choice(k, size=n, p=p / p.sum()).astype(np.int32)
+
+
+@pytest.mark.parametrize("k,d,n,kind", [(11, 20, 300, "uniform"), (50, 64, 600, "uniform"), (1, 8, 1000, "uniform"),
+                                        (4000, 128, 3000, "distinct"), (300, 1024, 5000, "zipf"),
+                                        (64, 1028, 700, "zipf"), (200, 4, 40000, "zipf"), (7, 33, 1, "uniform")])
+def test_addtakegrad_largebatch(lib, k, d, n, kind):
+    rng = np.random.default_rng(k + d + n)
+    if kind == "uniform":
+        idx = rng.integers(0, k, n).astype(np.int32)
+    elif kind == "distinct":
+        idx = rng.permutation(k)[:n].astype(np.int32)
+    else:
+        idx = zipf_indices(rng, n, k)
+    src = rng.standard_normal((n, d)).astype(np.float32)
+    keys, vals = idx.copy(), np.arange(n, dtype=np.int32)
+    orc.sort_by_key(keys, vals, True)
+    t0 = rng.standard_normal((k, d)).astype(np.float32)
+    want = orc.addtakegrad_largebatch(t0.copy(), keys, vals, src)
+    got = lib.addtakegrad_largebatch(dev(t0), dev(keys), dev(vals), dev(src))
+    assert_sum_close(host(got), want)
+    # untouched rows stay bit-identical
+    untouched = np.setdiff1d(np.arange(k), idx)
+    assert_bits(host(got)[untouched], t0[untouched])
+
+
+@pytest.mark.parametrize("k,d,n", [(11, 20, 300), (128, 256, 4096), (5, 1024, 513)])
+def test_addtakegrad_unsorted_clips(lib, k, d, n):
+    rng = np.random.default_rng(k * d + n)
+    idx = rng.integers(-3, k + 3, n).astype(np.int32)
+    src = rng.standard_normal((n, d)).astype(np.float32)
+    t0 = rng.standard_normal((k, d)).astype(np.float32)
+    want = orc.addtakegrad(t0.copy(), idx, src)
+    got = lib.addtakegrad(dev(t0, 4), dev(idx), dev(src, 4))
+    assert_sum_close(host(got), want)
+
+
+@pytest.mark.parametrize("n", [1, 2, 1000, 70000])
+@pytest.mark.parametrize("ascend", [True, False])
+def test_sort_by_key(lib, n, ascend):
+    rng = np.random.default_rng(n)
+    keys = rng.integers(-50, 50, n).astype(np.int32)
+    vals = np.arange(n, dtype=np.int32)
+    wk, wv = orc.sort_by_key(keys.copy(), vals.copy(), ascend)
+    gk, gv = lib.sort_by_key(dev(keys), dev(vals), ascend)
+    assert np.array_equal(host(gk), wk) and np.array_equal(host(gv), wv)
+
+
+def test_errors_are_status_codes(lib):
+    import ctypes as C
+    z = torch.zeros(4, 4, device="cuda")
+    st, msg = lib.status("msb_softmax_f32", C.c_void_p(z.data_ptr()), C.c_void_p(z.data_ptr()), 4, 4, 2, 4, None)
+    assert st == 2 and "extent" in msg
+    st, _ = lib.status("msb_reduce_keep_lowest_f32", C.c_void_p(z.data_ptr()), C.c_void_p(z.data_ptr()), 0, 4, 4,
+                       C.c_float(1.0), 0, 0, None)
+    assert st == 2
+    st, _ = lib.status("msb_pool_f32", C.c_void_p(z.data_ptr()), C.c_void_p(z.data_ptr()), 1, 2, 2, 3, 3, 1, 1, 2, 1,
+                       1, None)
+    assert st == 2
+    st, _ = lib.status("msb_expr_case_f32", 99, None, None, None, None, None, 1, 1, 1, 1, 1, 1, None)
+    assert st == 1
+    # empty inputs are accepted and do nothing
+    lib.softmax(torch.zeros(0, 8, device="cuda"), torch.zeros(0, 8, device="cuda"))
+    lib.addtakegrad_largebatch(z, torch.zeros(0, dtype=torch.int32, device="cuda"),
+                               torch.zeros(0, dtype=torch.int32, device="cuda"), torch.zeros(0, 4, device="cuda"))
+    lib.stream_wait(None)
+
+
+def test_memory_and_streams(lib):
+    p, ld = lib.alloc_space(10, 100, 4, True)
+    assert ld >= 100 and ld % 4 == 0
+    q, ld2 = lib.alloc_space(10, 27, 4, True)
+    assert ld2 == 27  # narrow rows are never pitched
+    hbuf = lib.alloc_host(4000)
+    s = lib.stream_create()
+    import ctypes as C
+    src = (C.c_float * 1000).from_address(hbuf)
+    for i in range(1000):
+        src[i] = float(i)
+    lib.copy_2d(p, ld, hbuf, 100, 10, 100, 1, stream=s)
+    out = torch.zeros(10, 100, device="cuda")
+    lib.copy_2d(out, 100, p, ld, 10, 100, 3, stream=s)
+    lib.stream_wait(s)
+    assert np.array_equal(host(out).ravel(), np.arange(1000, dtype=np.float32))
+    lib.stream_destroy(s)
+    lib.free_host(hbuf)
+    lib.free_space(p)
+    lib.free_space(q)
