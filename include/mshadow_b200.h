@@ -48,6 +48,10 @@ typedef void *msb_stream_t; /* cudaStream_t */
 
 const char *msb_last_error(void);
 int msb_version(void);
+/* Number of kernels the library has launched so far in this process (its own kernels only;
+   library sorts and memory copies are not counted).  No counterpart in the reference;
+   benchmarks use the difference across a timed region. */
+int64_t msb_launch_count(void);
 
 /* ---- engine life cycle and streams ------------------------------------------------- */
 

@@ -90,6 +90,7 @@ class Library:
         self.dll = C.CDLL(path)
         self.dll.msb_last_error.restype = C.c_char_p
         self.dll.msb_version.restype = cint
+        self.dll.msb_launch_count.restype = i64
         for name, argtypes in _SIGNATURES.items():
             fn = getattr(self.dll, name)
             fn.argtypes = argtypes
@@ -105,6 +106,9 @@ class Library:
         return getattr(self.dll, name)(*args), self.dll.msb_last_error().decode("utf-8", "replace")
 
     # ---- engine ---------------------------------------------------------------------
+    def launch_count(self):
+        return int(self.dll.msb_launch_count())
+
     def init(self, device=0):
         self.call("msb_init", device)
 

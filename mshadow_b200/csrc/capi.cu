@@ -108,6 +108,7 @@ extern "C" {
 
 const char *msb_last_error(void) { return g_last_error.c_str(); }
 int msb_version(void) { return 100; }
+int64_t msb_launch_count(void) { return gpu_rt::LaunchCounter().load(); }
 
 int msb_init(int device) {
   MSB_GUARD_BEGIN

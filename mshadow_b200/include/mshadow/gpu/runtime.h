@@ -14,17 +14,29 @@
 
 #include <cuda_runtime.h>
 
+#include <atomic>
 #include <map>
 #include <mutex>
 #include <utility>
 
 #include "../tensor.h"
 
-/*! \brief check that the launch just issued was accepted by the driver */
+namespace mshadow {
+namespace gpu_rt {
+/*! \brief number of kernels this engine has launched in the process (all threads, all devices) */
+inline std::atomic<long long> &LaunchCounter() {
+  static std::atomic<long long> count(0);
+  return count;
+}
+}  // namespace gpu_rt
+}  // namespace mshadow
+
+/*! \brief check that the launch just issued was accepted by the driver, and count it */
 #define MSHADOW_CUDA_POST_KERNEL_CHECK(name)                                              \
   {                                                                                       \
     cudaError_t msh_err_ = cudaPeekAtLastError();                                         \
     CHECK_EQ(msh_err_, cudaSuccess) << "Name: " << #name << " ErrStr:" << cudaGetErrorString(msh_err_); \
+    ::mshadow::gpu_rt::LaunchCounter().fetch_add(1, std::memory_order_relaxed);           \
   }
 
 namespace mshadow {
