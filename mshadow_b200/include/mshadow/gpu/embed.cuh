@@ -148,10 +148,11 @@ SegmentSumKernel(float *dst, int64_t ld_dst, const int32_t *keys, const int32_t 
 }
 
 /*! \brief keys[i] = clip(index[i], 0, k-1), vals[i] = i */
-__global__ void ClipIotaKernel(int32_t *keys, int32_t *vals, const int32_t *index, uint32_t n, int32_t k) {
+template <typename IndexType>
+__global__ void ClipIotaKernel(IndexType *keys, IndexType *vals, const IndexType *index, uint32_t n, IndexType k) {
   const uint32_t i = blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= n) return;
-  int32_t j = index[i];
+  IndexType j = index[i];
   j = j <= 0 ? 0 : (j >= k ? k - 1 : j);
   keys[i] = j;
   vals[i] = static_cast<int32_t>(i);
@@ -288,7 +289,7 @@ inline void AddTakeGradLaunch(float *dst, int64_t ld_dst, const int32_t *index, 
   int32_t *k_out = reinterpret_cast<int32_t *>(base + 2 * ib), *v_out = reinterpret_cast<int32_t *>(base + 3 * ib);
   void *work = base + 4 * ib;
   char *seg_scratch = base + 4 * ib + Align256(temp);
-  ClipIotaKernel<<<gpu_rt::CeilDiv(n, 256), 256, 0, stream>>>(k_in, v_in, index, un, static_cast<int32_t>(k));
+  ClipIotaKernel<int32_t><<<gpu_rt::CeilDiv(n, 256), 256, 0, stream>>>(k_in, v_in, index, un, static_cast<int32_t>(k));
   MSHADOW_CUDA_POST_KERNEL_CHECK(ClipIotaKernel);
   MSHADOW_CUDA_CALL((cub::DeviceRadixSort::SortPairs<int32_t, int32_t>(work, temp, k_in, k_out, v_in, v_out,
                                                                        static_cast<int>(n), 0, 32, stream)));
