@@ -110,6 +110,22 @@ int msb_expr_case_f32(int id, float *dst, const float *A, const float *B, const 
 int msb_reduce_keep_lowest_f32(float *dst, const float *src, int64_t rows, int64_t cols,
                                int64_t ld, float scale, int saver, int reducer,
                                msb_stream_t stream);
+/* dst[x] = scale * sum over rows of src(y, x), computed exactly as by
+   msb_reduce_keep_lowest_f32 with saver 0 / reducer 0, but WITHOUT allocating anything.
+   This entry point has no counterpart in the reference.  It is for callers that must not
+   cause a cudaMalloc at call time (frozen memory pools, real-time paths that cannot take
+   cudaMalloc's implicit device synchronisation, processes whose device memory is already
+   fully assigned).  Its cross-cluster scratch is a fixed 1 MiB array inside the library's
+   device image, resident on every GPU that loads the library.  Limits and rules:
+     - inputs whose partial rows (clusters x cols floats) exceed 1 MiB are rejected with
+       MSB_ERR_SHAPE and nothing is launched;
+     - the first call on a device resolves the array's address; make that call before any
+       stream capture begins;
+     - all calls share the array, so calls that can overlap on the GPU (different streams
+       without ordering) race and must be serialised by the caller. */
+int msb_reduce_keep_lowest_sum_f32_noalloc(float *dst, const float *src, int64_t rows,
+                                           int64_t cols, int64_t ld, float scale,
+                                           msb_stream_t stream);
 /* MapReduceKeepHighDim<Saver,Reducer,1>(dst, src(n,c,h,w), scale) -- e.g.
    dst = sumall_except_dim<1>(src): mshadow/tensor_gpu-inl.h:135-156 */
 int msb_reduce_keep_highdim_f32(float *dst, const float *src, int64_t n, int64_t c, int64_t h,

@@ -19,7 +19,8 @@ NVCC_FLAGS = [
 ]
 
 TARGETS = [
-    (os.path.join(HERE, "libmshadow_b200.so"), [os.path.join(HERE, "csrc", "capi.cu")]),
+    (os.path.join(HERE, "libmshadow_b200.so"),
+     [os.path.join(HERE, "csrc", "capi.cu"), os.path.join(HERE, "csrc", "noalloc.cu")]),
     (os.path.join(ROOT, "tests", "cxx", "libmsb_api_suite.so"),
      [os.path.join(ROOT, "tests", "cxx", "api_suite.cu")]),
 ]

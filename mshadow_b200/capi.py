@@ -53,6 +53,7 @@ _SIGNATURES = {
     "msb_workspace": [vp, i64, C.POINTER(vp)],
     "msb_expr_case_f32": [cint, vp, vp, vp, vp, vp, i64, i64, i64, i64, i64, i64, vp],
     "msb_reduce_keep_lowest_f32": [vp, vp, i64, i64, i64, f32, cint, cint, vp],
+    "msb_reduce_keep_lowest_sum_f32_noalloc": [vp, vp, i64, i64, i64, f32, vp],
     "msb_reduce_keep_highdim_f32": [vp, vp, i64, i64, i64, i64, i64, f32, cint, cint, vp],
     "msb_softmax_f32": [vp, vp, i64, i64, i64, i64, vp],
     "msb_softmax_grad_f32": [vp, vp, vp, i64, i64, i64, i64, cint, f32, f32, vp],
@@ -156,6 +157,13 @@ class Library:
         rows, cols = src.shape
         self.call("msb_reduce_keep_lowest_f32", _ptr(dst), _ptr(src), rows, cols, _ld(src), scale, saver,
                   reducer, stream)
+        return dst
+
+    def reduce_keep_lowest_sum_noalloc(self, dst, src, scale=1.0, stream=None):
+        """Column sum through the entry point that allocates nothing (fixed in-library scratch)."""
+        rows, cols = src.shape
+        self.call("msb_reduce_keep_lowest_sum_f32_noalloc", _ptr(dst), _ptr(src), rows, cols, _ld(src), scale,
+                  stream)
         return dst
 
     def reduce_keep_highdim(self, dst, src, scale=1.0, saver=0, reducer=0, stream=None):

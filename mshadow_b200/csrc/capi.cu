@@ -88,6 +88,11 @@ void KeepDim1(G1 d, const G4 &s, float scale, int saver) {
 
 }  // namespace
 
+namespace msb_internal {
+/*! \brief lets the library's other translation units report through msb_last_error() */
+void SetLastError(const char *message) { g_last_error = message; }
+}  // namespace msb_internal
+
 #define MSB_GUARD_BEGIN try {
 #define MSB_GUARD_END                                        \
   }                                                          \
