@@ -207,61 +207,59 @@ def time_kernel(torch, fn, iters=20, warm=5):
     return float(np.median(times)) * 1e-3
 
 
-def kernel_table(lib, torch, peak):
-    """Algorithmic GB/s of every kernel of the path at its BASELINE config (one GPU)."""
+def kernel_cases(lib, torch, small=False):
+    """Yields (key, label, algorithmic bytes, elements, callable, iterations) for every kernel
+    of the path, at its BASELINE config or, with small=True, at a reduced size that still
+    exceeds the L2 cache (for profiler captures).  Tensors of a case die when the next starts."""
     dev = torch.device("cuda")
-    rows = []
-
-    def add(name, nbytes, elems, seconds):
-        gbs = nbytes / seconds / 1e9
-        rows.append({"kernel": name, "ms": seconds * 1e3, "GBps": round(gbs, 1),
-                     "frac_of_measured_peak": round(gbs / peak, 3), "frac_of_8TBps": round(gbs / NOMINAL_HBM_GBS, 3),
-                     "Gelem_per_s": round(elems / seconds / 1e9, 2)})
-
     g = torch.Generator(device=dev)
     g.manual_seed(1)
     # C1: fused element-wise, 16 B/elem
-    n = 8192
-    A, B, Cm = (torch.rand(n, n, device=dev, generator=g) * 2 - 1 for _ in range(3))
+    rows, n = (2048, 8192) if small else (8192, 8192)
+    A, B, Cm = (torch.rand(rows, n, device=dev, generator=g) * 2 - 1 for _ in range(3))
     bias = torch.randn(n, device=dev, generator=g)
-    D = torch.empty(n, n, device=dev)
-    add("C1 map: sigmoid(A*B+0.5*C)+repmat(bias)", 16 * n * n + 4 * n, n * n,
-        time_kernel(torch, lambda: lib.expr_case(0, D, A, B, Cm, bias)))
+    D = torch.empty(rows, n, device=dev)
+    yield ("map", "C1 map: sigmoid(A*B+0.5*C)+repmat(bias) %dx%d" % (rows, n), 16 * rows * n + 4 * n, rows * n,
+           lambda: lib.expr_case(0, D, A, B, Cm, bias), 20)
     del A, B, Cm, D
     # C2: reductions, 4 B/elem
-    T = torch.randn(C2A_SHAPE, device=dev, generator=g)
-    o = torch.zeros(C2A_SHAPE[1], device=dev)
-    add("C2a sumall_except_dim<1> (256,512,28,28)", 4 * T.numel() + 4 * o.numel(), T.numel(),
-        time_kernel(torch, lambda: lib.reduce_keep_highdim(o, T)))
+    shape = (64,) + C2A_SHAPE[1:] if small else C2A_SHAPE
+    T = torch.randn(shape, device=dev, generator=g)
+    o = torch.zeros(shape[1], device=dev)
+    yield ("keep_highdim", "C2a sumall_except_dim<1> %s" % (shape,), 4 * T.numel() + 4 * o.numel(), T.numel(),
+           lambda: lib.reduce_keep_highdim(o, T), 20)
     del T
-    M = torch.randn(C2B_SHAPE, device=dev, generator=g)
-    o2 = torch.zeros(C2B_SHAPE[1], device=dev)
-    add("C2b sum_rows 65536x4096", 4 * M.numel() + 4 * o2.numel(), M.numel(),
-        time_kernel(torch, lambda: lib.reduce_keep_lowest(o2, M)))
+    shape = (16384, 4096) if small else C2B_SHAPE
+    M = torch.randn(shape, device=dev, generator=g)
+    o2 = torch.zeros(shape[1], device=dev)
+    yield ("keep_lowest", "C2b sum_rows %dx%d" % shape, 4 * M.numel() + 4 * o2.numel(), M.numel(),
+           lambda: lib.reduce_keep_lowest(o2, M), 20)
     del M
     # C3: softmax + grad, 8 B/elem each
-    r, c = 32768, 32000
+    r, c = (2048, 32000) if small else (32768, 32000)
     L = torch.randn(r, c, device=dev, generator=g) * 2
     P = torch.empty(r, c, device=dev)
-    add("C3 Softmax 32768x32000", 8 * r * c, r * c, time_kernel(torch, lambda: lib.softmax(P, L), iters=10, warm=3))
+    yield ("softmax", "C3 Softmax %dx%d" % (r, c), 8 * r * c, r * c, lambda: lib.softmax(P, L), 10)
     lab = torch.randint(0, c, (r,), device=dev, generator=g).float()
-    add("C3 SoftmaxGrad 32768x32000", 8 * r * c + 4 * r, r * c,
-        time_kernel(torch, lambda: lib.softmax_grad(L, P, lab), iters=10, warm=3))
+    yield ("softmax_grad", "C3 SoftmaxGrad %dx%d" % (r, c), 8 * r * c + 4 * r, r * c,
+           lambda: lib.softmax_grad(L, P, lab), 10)
     del L, P
     # C4: pooling
-    X = torch.rand(256 * 256, 56, 56, device=dev, generator=g)
-    Pm = torch.empty(256 * 256, 27, 27, device=dev)
-    add("C4 pool<max> 3x3/2 (256,256,56,56)", 4 * X.numel() + 4 * Pm.numel(), X.numel(),
-        time_kernel(torch, lambda: lib.pool(Pm, X, 3, 3, 2, 2)))
-    gP = torch.rand(256 * 256, 27, 27, device=dev, generator=g)
+    imgs = 32 if small else 256
+    X = torch.rand(imgs * 256, 56, 56, device=dev, generator=g)
+    Pm = torch.empty(imgs * 256, 27, 27, device=dev)
+    yield ("pool", "C4 pool<max> 3x3/2 (%d,256,56,56)" % imgs, 4 * X.numel() + 4 * Pm.numel(), X.numel(),
+           lambda: lib.pool(Pm, X, 3, 3, 2, 2), 20)
+    gP = torch.rand(imgs * 256, 27, 27, device=dev, generator=g)
     G = torch.empty_like(X)
-    add("C4 unpool<max> 3x3/2", 8 * X.numel() + 8 * Pm.numel(), X.numel(),
-        time_kernel(torch, lambda: lib.unpool(G, X, Pm, gP, 3, 3, 2, 2)))
-    X4, G4 = X.view(256, 256, 56, 56), G.view(256, 256, 56, 56)
-    add("C4 chpool<sum> nsize 5", 8 * X.numel(), X.numel(), time_kernel(torch, lambda: lib.chpool(G4, X4, 5)))
+    yield ("unpool", "C4 unpool<max> 3x3/2 (%d,256,56,56)" % imgs, 8 * X.numel() + 8 * Pm.numel(), X.numel(),
+           lambda: lib.unpool(G, X, Pm, gP, 3, 3, 2, 2), 20)
+    X4, G4 = X.view(imgs, 256, 56, 56), G.view(imgs, 256, 56, 56)
+    yield ("chpool", "C4 chpool<sum> nsize 5 (%d,256,56,56)" % imgs, 8 * X.numel(), X.numel(),
+           lambda: lib.chpool(G4, X4, 5), 20)
     del X, Pm, gP, G, X4, G4
     # C5: embedding backward
-    k, d, nidx = 262144, 1024, 1 << 20
+    k, d, nidx = (262144, 1024, 1 << 17) if small else (262144, 1024, 1 << 20)
     p = (np.arange(k) + 1.0) ** -1.1
     idx = np.random.default_rng(5).choice(k, size=nidx, p=p / p.sum()).astype(np.int32)
     uniq = int(np.unique(idx).size)
@@ -270,10 +268,24 @@ def kernel_table(lib, torch, peak):
     lib.sort_by_key(keys, vals, True)
     src = torch.randn(nidx, d, device=dev, generator=g)
     table = torch.zeros(k, d, device=dev)
-    add("C5 AddTakeGradLargeBatch 262144x1024, 1Mi Zipf(1.1)", 4 * nidx * d + 8 * nidx + 8 * uniq * d, nidx * d,
-        time_kernel(torch, lambda: lib.addtakegrad_largebatch(table, keys, vals, src), iters=10, warm=3))
+    yield ("addtakegrad", "C5 AddTakeGradLargeBatch 262144x1024, %d Zipf(1.1) indices" % nidx,
+           4 * nidx * d + 8 * nidx + 8 * uniq * d, nidx * d,
+           lambda: lib.addtakegrad_largebatch(table, keys, vals, src), 10)
     del src, table
     torch.cuda.empty_cache()
+
+
+def kernel_table(lib, torch, peak, only=None, small=False, iters=None, warm=None):
+    """Algorithmic GB/s of every kernel of the path (one GPU)."""
+    rows = []
+    for key, label, nbytes, elems, fn, n_it in kernel_cases(lib, torch, small):
+        if only is not None and key != only:
+            continue
+        seconds = time_kernel(torch, fn, iters=iters or n_it, warm=warm if warm is not None else 3)
+        gbs = nbytes / seconds / 1e9
+        rows.append({"kernel": label, "key": key, "ms": seconds * 1e3, "GBps": round(gbs, 1),
+                     "frac_of_measured_peak": round(gbs / peak, 3), "frac_of_8TBps": round(gbs / NOMINAL_HBM_GBS, 3),
+                     "Gelem_per_s": round(elems / seconds / 1e9, 2)})
     return rows
 
 
@@ -289,7 +301,21 @@ def main():
     ap.add_argument("--no-table", action="store_true", help="skip the per-kernel table")
     ap.add_argument("--e2e-steps", type=int, default=10)
     ap.add_argument("--cpu-reps", type=int, default=5)
+    ap.add_argument("--only", default=None,
+                    help="run one kernel of the table alone (map, keep_highdim, keep_lowest, softmax, softmax_grad, "
+                         "pool, unpool, chpool, addtakegrad) for --steps launches after --warmup; for profiling")
+    ap.add_argument("--small", action="store_true", help="with --only: reduced size that still exceeds L2")
     args = ap.parse_args()
+    if args.only is not None:
+        import torch
+        import mshadow_b200
+        lib = mshadow_b200.load()
+        lib.init(0)
+        peak, _ = measured_peak()
+        print(json.dumps({"only": args.only, "small": args.small,
+                          "kernels": kernel_table(lib, torch, peak, only=args.only, small=args.small,
+                                                  iters=args.steps, warm=args.warmup)}), flush=True)
+        return
     args.warmup = max(args.warmup, 3)
 
     if args.impl == "reference":
