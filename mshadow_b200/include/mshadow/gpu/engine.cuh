@@ -53,6 +53,18 @@ struct MapDispatch {
   }
 };
 
+/*!
+ * \brief an assignment sees an extension expression through its MakeTensorExp base (that is
+ *  the type `dst = pool<...>(...)` deduces); dispatch on the real expression type
+ */
+template <typename Saver, typename R, typename T, typename SrcExp, int dim, typename DType>
+struct MapDispatch<Saver, R, expr::MakeTensorExp<T, SrcExp, dim, DType>, DType, dim> {
+  inline static void Run(R *dst, const expr::MakeTensorExp<T, SrcExp, dim, DType> &exp, Shape<dim> dshape,
+                         cudaStream_t stream) {
+    MapDispatch<Saver, R, T, DType, dim>::Run(dst, exp.real_self(), dshape, stream);
+  }
+};
+
 }  // namespace cuda
 
 template <typename Saver, typename R, int dim, typename DType, typename E, int etype>
