@@ -41,7 +41,7 @@ const int kSegDepth = 8;
  *  chunk for the next level.  grid = (chunks, feature slabs).
  */
 template <int kLanes>
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(256, 3)
 SegmentSumKernel(float *dst, int64_t ld_dst, const int32_t *keys, const int32_t *rows, const float *src,
                  int64_t ld_src, uint32_t n, uint32_t width, int32_t *part_keys, int32_t *part_rows,
                  float *partials) {

@@ -105,10 +105,23 @@ MapScalarKernel(DPlan dst, const SPlan src, uint32_t rows, uint32_t cols, gpu_rt
   }
 }
 
-inline int MapGridSize(int64_t work_items) {
+/*!
+ * \brief grid for a grid-stride kernel: enough CTAs for the work, but never more than the
+ *  device keeps resident at once for this kernel (registers decide), so that no partly
+ *  filled second wave trails behind
+ */
+template <typename Kernel>
+inline int MapGridSize(int64_t work_items, Kernel kernel) {
+  static int resident = 0;  // per kernel instantiation; the engine targets one device model
+  if (resident == 0) {
+    int per_sm = 0;
+    MSHADOW_CUDA_CALL(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, kMapThreads, 0));
+    if (per_sm < 1) per_sm = 1;
+    if (per_sm > kMapCtasPerSM) per_sm = kMapCtasPerSM;
+    resident = per_sm * gpu_rt::CurrentDevice().sm_count;
+  }
   const int want = gpu_rt::CeilDiv(work_items, static_cast<int64_t>(kMapThreads) * kMapUnroll);
-  const int cap = gpu_rt::CurrentDevice().sm_count * kMapCtasPerSM;
-  return want < 1 ? 1 : (want < cap ? want : cap);
+  return want < 1 ? 1 : (want < resident ? want : resident);
 }
 
 /*!
@@ -129,9 +142,9 @@ inline void MapPlanPacked(DPlan dplan, const SPlan &splan, Shape<2> dshape, bool
   }
   const uint32_t ppr = cols / kLanes;
   const int64_t work = static_cast<int64_t>(rows) * (ppr == 0 ? 1 : ppr);
-  MapPackKernel<Saver, DPlan, SPlan, DType>
-      <<<MapGridSize(work), kMapThreads, 0, stream>>>(dplan, splan, rows, cols, ppr,
-                                                      gpu_rt::FastDiv(ppr == 0 ? 1 : ppr));
+  auto kernel = MapPackKernel<Saver, DPlan, SPlan, DType>;
+  kernel<<<MapGridSize(work, kernel), kMapThreads, 0, stream>>>(dplan, splan, rows, cols, ppr,
+                                                                gpu_rt::FastDiv(ppr == 0 ? 1 : ppr));
   MSHADOW_CUDA_POST_KERNEL_CHECK(MapPackKernel);
 }
 
@@ -141,7 +154,8 @@ inline void MapPlanScalar(DPlan dplan, const SPlan &splan, Shape<2> dshape, cuda
   const int64_t count = static_cast<int64_t>(dshape[0]) * dshape[1];
   if (count == 0) return;
   CHECK_LT(count, (int64_t(1) << 31)) << "MapExp: tensor too large for 32-bit indexing";
-  MapScalarKernel<Saver, DPlan, SPlan, DType><<<MapGridSize(count), kMapThreads, 0, stream>>>(
+  auto kernel = MapScalarKernel<Saver, DPlan, SPlan, DType>;
+  kernel<<<MapGridSize(count, kernel), kMapThreads, 0, stream>>>(
       dplan, splan, static_cast<uint32_t>(dshape[0]), static_cast<uint32_t>(dshape[1]),
       gpu_rt::FastDiv(static_cast<uint32_t>(dshape[1])));
   MSHADOW_CUDA_POST_KERNEL_CHECK(MapScalarKernel);

@@ -209,24 +209,34 @@ UnpoolPlanesKernel(float *dst, const float *src, const float *pooled, const floa
  * \brief channel-window pooling with stride 1 and pad NSIZE/2 (the chpool(src, nsize) form).
  *  A thread owns kLanes adjacent pixels of one image and marches over the channels with the
  *  last NSIZE values in registers, so every input element is read from HBM once.
- *  grid = (pixel tiles, images); `plane` = h*w elements per channel, dense.
+ *  Work item = (image, pixel group), numbered across all images so that no lane idles at
+ *  image borders; blockIdx.y selects a segment of `seg_len` output channels, which lets the
+ *  host cut the march into as many equal pieces as fill whole waves of resident CTAs (a
+ *  segment re-reads NSIZE-1 halo channels).  `plane` = h*w elements per channel, dense.
  */
 template <typename Reducer, int NSIZE, int kLanes>
 __global__ void __launch_bounds__(kPoolThreads)
-ChannelPoolKernel(float *dst, const float *src, uint32_t channels, uint32_t plane) {
+ChannelPoolKernel(float *dst, const float *src, uint32_t channels, uint32_t plane, uint32_t groups_per_image,
+                  uint32_t total_items, gpu_rt::FastDiv image_of_item, uint32_t seg_len) {
   constexpr int kPad = NSIZE / 2;
   constexpr int kAhead = 4;          // loads issued this many channels before they are needed
   constexpr int kRing = NSIZE + kAhead;
-  const uint32_t pix = (blockIdx.x * kPoolThreads + threadIdx.x) * kLanes;
-  if (pix >= plane) return;
-  const int64_t image = static_cast<int64_t>(blockIdx.y) * channels * plane;
+  const uint32_t item = blockIdx.x * kPoolThreads + threadIdx.x;
+  if (item >= total_items) return;
+  const uint32_t image_idx = image_of_item.Quot(item);
+  const uint32_t pix = (item - image_idx * groups_per_image) * kLanes;
+  const uint32_t c_begin = blockIdx.y * seg_len;
+  const uint32_t c_end = min(channels, c_begin + seg_len);
+  const int64_t image = static_cast<int64_t>(image_idx) * channels * plane;
   const float *in = src + image + pix;
   float *out = dst + image + pix;
   float ring[kRing][kLanes];
   float init;
   Reducer::SetInitValue(init);
+  // channels a segment may touch: its own plus the halo, clipped to the tensor
+  const int64_t load_end = min(static_cast<int64_t>(channels), static_cast<int64_t>(c_end) + kPad);
   auto load = [&](int slot, int64_t c) {
-    if (c >= 0 && c < static_cast<int64_t>(channels)) {
+    if (c >= 0 && c < load_end) {
       if (kLanes == 4) {
         const float4 p = __ldcs(reinterpret_cast<const float4 *>(in + c * plane));
         ring[slot][0] = p.x;
@@ -241,14 +251,15 @@ ChannelPoolKernel(float *dst, const float *src, uint32_t channels, uint32_t plan
       for (int l = 0; l < kLanes; ++l) ring[slot][l] = init;
     }
   };
-  // ring slot of channel c is (c + kPad) mod kRing; preload channels -kPad .. kPad + kAhead - 1
+  // ring slot of channel c is (c - c_begin + kPad) mod kRing; preload the first window and
+  // kAhead channels beyond it
 #pragma unroll
-  for (int s = 0; s < kRing; ++s) load(s, static_cast<int64_t>(s) - kPad);
-  for (uint32_t c0 = 0; c0 < channels; c0 += kRing) {
+  for (int s = 0; s < kRing; ++s) load(s, static_cast<int64_t>(c_begin) + s - kPad);
+  for (uint32_t c0 = c_begin; c0 < c_end; c0 += kRing) {
 #pragma unroll
     for (int j = 0; j < kRing; ++j) {
       const uint32_t c = c0 + j;
-      if (c < channels) {
+      if (c < c_end) {
         // window of channel c: slots j .. j + NSIZE - 1 (mod kRing), ascending channel order
         float res[kLanes];
 #pragma unroll
@@ -306,6 +317,27 @@ inline uint32_t GroupSize(uint64_t bytes_per_plane, uint32_t quantum, uint64_t b
 }
 
 inline uint32_t Gcd(uint32_t a, uint32_t b) { return b == 0 ? a : Gcd(b, a % b); }
+
+/*!
+ * \brief how many equal segments (1..kmax) to cut each of `fixed` CTA columns into so that the
+ *  grid of fixed*k CTAs fills whole waves of `slots` resident CTAs; the smallest k reaching
+ *  95 %, else the best one
+ */
+inline uint32_t WaveFriendlySegments(uint32_t fixed, uint32_t kmax, uint32_t slots) {
+  uint32_t best = 1;
+  double best_eff = 0.0;
+  for (uint32_t k = 1; k <= kmax; ++k) {
+    const uint64_t ctas = static_cast<uint64_t>(fixed) * k;
+    const uint64_t waves = (ctas + slots - 1) / slots;
+    const double eff = static_cast<double>(ctas) / static_cast<double>(waves * slots);
+    if (eff > best_eff + 1e-9) {
+      best_eff = eff;
+      best = k;
+    }
+    if (eff >= 0.95) return k;
+  }
+  return best;
+}
 }  // namespace pooldetail
 
 /*! \brief dynamic shared memory per CTA: forward leaves room for 4 CTAs per SM, backward for 3 */
@@ -397,22 +429,42 @@ inline void ChannelPoolLaunch(float *dst, const float *src, int64_t n, int64_t c
   const uint32_t plane = static_cast<uint32_t>(h * w);
   const bool vec = plane % 4 == 0 && reinterpret_cast<uintptr_t>(dst) % 16 == 0 &&
                    reinterpret_cast<uintptr_t>(src) % 16 == 0;
-  CHECK_LT(n, 65536) << "chpool: too many images for one launch";
-#define MSHADOW_B200_CHPOOL_LAUNCH_(NS)                                                                        \
-  if (vec) {                                                                                                   \
-    ChannelPoolKernel<Reducer, NS, 4><<<dim3(gpu_rt::CeilDiv(plane / 4, kPoolThreads), n), kPoolThreads, 0,    \
-                                       stream>>>(dst, src, static_cast<uint32_t>(c), plane);                   \
-  } else {                                                                                                     \
-    ChannelPoolKernel<Reducer, NS, 1><<<dim3(gpu_rt::CeilDiv(plane, kPoolThreads), n), kPoolThreads, 0,        \
-                                       stream>>>(dst, src, static_cast<uint32_t>(c), plane);                   \
+  const int lanes = vec ? 4 : 1;
+  const uint32_t groups = plane / lanes;
+  const int64_t items64 = n * static_cast<int64_t>(groups);
+  CHECK_LT(items64, (int64_t(1) << 31)) << "chpool: tensor too large for 32-bit indexing";
+  const uint32_t items = static_cast<uint32_t>(items64);
+  const uint32_t tiles = static_cast<uint32_t>(gpu_rt::CeilDiv(items, kPoolThreads));
+#define MSHADOW_B200_CHPOOL_LAUNCH_(NS, LANES)                                                                 \
+  {                                                                                                            \
+    auto kernel = ChannelPoolKernel<Reducer, NS, LANES>;                                                       \
+    /* cut the channel march into the number of segments that fills whole waves of resident CTAs; every      \
+       segment costs NS-1 halo channels, so segments stay at least 8 windows long */                          \
+    static uint32_t slots = 0;                                                                                 \
+    if (slots == 0) {                                                                                          \
+      int per_sm = 0;                                                                                          \
+      MSHADOW_CUDA_CALL(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, kPoolThreads, 0));      \
+      slots = static_cast<uint32_t>(per_sm < 1 ? 1 : per_sm) * gpu_rt::CurrentDevice().sm_count;               \
+    }                                                                                                          \
+    uint32_t max_seg = static_cast<uint32_t>(c) / (8 * NS);                                                    \
+    if (max_seg < 1) max_seg = 1;                                                                              \
+    if (max_seg > 16) max_seg = 16;                                                                            \
+    const uint32_t segs = pooldetail::WaveFriendlySegments(tiles, max_seg, slots);                            \
+    const uint32_t seg_len = (static_cast<uint32_t>(c) + segs - 1) / segs;                                     \
+    const uint32_t nseg = (static_cast<uint32_t>(c) + seg_len - 1) / seg_len;                                  \
+    kernel<<<dim3(tiles, nseg), kPoolThreads, 0, stream>>>(dst, src, static_cast<uint32_t>(c), plane, groups,  \
+                                                            items, gpu_rt::FastDiv(groups), seg_len);          \
   }
+#define MSHADOW_B200_CHPOOL_PICK_(NS) \
+  if (vec) MSHADOW_B200_CHPOOL_LAUNCH_(NS, 4) else MSHADOW_B200_CHPOOL_LAUNCH_(NS, 1)
   switch (nsize) {
-    case 1: MSHADOW_B200_CHPOOL_LAUNCH_(1) break;
-    case 3: MSHADOW_B200_CHPOOL_LAUNCH_(3) break;
-    case 5: MSHADOW_B200_CHPOOL_LAUNCH_(5) break;
-    case 7: MSHADOW_B200_CHPOOL_LAUNCH_(7) break;
-    default: MSHADOW_B200_CHPOOL_LAUNCH_(9) break;
+    case 1: MSHADOW_B200_CHPOOL_PICK_(1) break;
+    case 3: MSHADOW_B200_CHPOOL_PICK_(3) break;
+    case 5: MSHADOW_B200_CHPOOL_PICK_(5) break;
+    case 7: MSHADOW_B200_CHPOOL_PICK_(7) break;
+    default: MSHADOW_B200_CHPOOL_PICK_(9) break;
   }
+#undef MSHADOW_B200_CHPOOL_PICK_
 #undef MSHADOW_B200_CHPOOL_LAUNCH_
   MSHADOW_CUDA_POST_KERNEL_CHECK(ChannelPoolKernel);
 }

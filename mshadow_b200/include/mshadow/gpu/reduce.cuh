@@ -181,8 +181,8 @@ __global__ void ReduceFinishKernel(DPlan dst, const DType *partial, uint32_t npa
 template <typename Saver, typename Reducer, int kLanes, typename DType, typename DPlan, typename SPlan>
 __global__ void __launch_bounds__(kRedHighThreads)
 ReduceKeepHighDimKernel(DPlan dst, const SPlan src, uint32_t outer, uint32_t channels, uint32_t inner_rows,
-                        uint32_t packs_per_row, gpu_rt::FastDiv row_of_pack, uint32_t outer_per_chunk,
-                        DType scale, DType *partial) {
+                        uint32_t packs_per_row, gpu_rt::FastDiv row_of_pack, gpu_rt::FastDiv plane_of_pack,
+                        uint32_t outer_per_chunk, DType scale, DType *partial) {
   __shared__ DType warp_buf[kRedHighThreads / 32];
   __shared__ DType cta_val;
   cg::cluster_group cluster = cg::this_cluster();
@@ -194,27 +194,30 @@ ReduceKeepHighDimKernel(DPlan dst, const SPlan src, uint32_t outer, uint32_t cha
   DType acc[kLanes];
 #pragma unroll
   for (int l = 0; l < kLanes; ++l) Reducer::SetInitValue(acc[l]);
+  // the chunk's planes are walked as one list of 16-byte groups, so that every thread always
+  // has kDepth independent loads in flight whatever the plane size
   constexpr int kDepth = 4;
-  for (uint32_t n = n0; n < n1; ++n) {
-    const uint32_t row0 = (n * channels + c) * inner_rows;
-    for (uint32_t base = threadIdx.x; base < per_plane; base += kRedHighThreads * kDepth) {
-      DType v[kDepth][kLanes];
+  const uint32_t npacks = (n1 > n0 ? n1 - n0 : 0) * per_plane;
+  for (uint32_t base = threadIdx.x; base < npacks; base += kRedHighThreads * kDepth) {
+    DType v[kDepth][kLanes];
 #pragma unroll
-      for (int k = 0; k < kDepth; ++k) {
-        const uint32_t i = base + k * kRedHighThreads;
-        if (i < per_plane) {
-          const uint32_t y = inner_rows == 1 ? 0 : row_of_pack.Quot(i);
-          reddetail::LoadLanes<kLanes>(src, row0 + y, (i - y * packs_per_row) * kLanes, v[k]);
-        } else {
+    for (int k = 0; k < kDepth; ++k) {
+      const uint32_t i = base + k * kRedHighThreads;
+      if (i < npacks) {
+        const uint32_t dn = plane_of_pack.Quot(i);
+        const uint32_t r = i - dn * per_plane;
+        const uint32_t y = inner_rows == 1 ? 0 : row_of_pack.Quot(r);
+        reddetail::LoadLanes<kLanes>(src, ((n0 + dn) * channels + c) * inner_rows + y,
+                                     (r - y * packs_per_row) * kLanes, v[k]);
+      } else {
 #pragma unroll
-          for (int l = 0; l < kLanes; ++l) Reducer::SetInitValue(v[k][l]);
-        }
+        for (int l = 0; l < kLanes; ++l) Reducer::SetInitValue(v[k][l]);
       }
-#pragma unroll
-      for (int k = 0; k < kDepth; ++k)
-#pragma unroll
-        for (int l = 0; l < kLanes; ++l) Reducer::Reduce(acc[l], v[k][l]);
     }
+#pragma unroll
+    for (int k = 0; k < kDepth; ++k)
+#pragma unroll
+      for (int l = 0; l < kLanes; ++l) Reducer::Reduce(acc[l], v[k][l]);
   }
 #pragma unroll
   for (int l = 1; l < kLanes; ++l) Reducer::Reduce(acc[0], acc[l]);
@@ -278,6 +281,63 @@ inline Split PlanSplit(uint32_t extent, uint32_t want, uint32_t min_per_chunk) {
   s.chunks = s.clusters * s.cluster;  // trailing chunks of the last cluster may be empty
   return s;
 }
+
+/*!
+ * \brief number of chunks k (1..kmax) for a grid of fixed*k CTAs on a device that keeps
+ *  `slots` CTAs resident: the smallest k that fills whole waves to at least 95 %, or the
+ *  best-filling k if none does.  A partly filled last wave is pure loss for kernels whose
+ *  CTAs all run equally long.
+ */
+inline uint32_t WaveFriendlyChunks(uint32_t fixed, uint32_t kmax, uint32_t slots) {
+  if (kmax < 1) kmax = 1;
+  if (static_cast<uint64_t>(fixed) * kmax <= slots) return kmax;  // cannot even fill one wave
+  uint32_t best = 1;
+  double best_eff = 0.0;
+  for (uint32_t k = 1; k <= kmax; ++k) {
+    const uint64_t ctas = static_cast<uint64_t>(fixed) * k;
+    if (ctas < slots) continue;
+    const uint64_t waves = (ctas + slots - 1) / slots;
+    const double eff = static_cast<double>(ctas) / static_cast<double>(waves * slots);
+    if (eff > best_eff + 1e-9) {
+      best_eff = eff;
+      best = k;
+    }
+    if (eff >= 0.95) return k;
+  }
+  return best;
+}
+
+/*! \brief split `extent` into exactly-planned chunks; the cluster size is the largest divisor <= 8 */
+inline Split PlanSplitWaves(uint32_t extent, uint32_t fixed, uint32_t slots, uint32_t max_chunks) {
+  Split s;
+  if (extent == 0) {  // nothing to walk: one CTA per output stores the reducer's initial value
+    s.per_chunk = s.chunks = s.cluster = s.clusters = 1;
+    return s;
+  }
+  if (max_chunks > extent) max_chunks = extent;
+  uint32_t chunks = WaveFriendlyChunks(fixed, max_chunks, slots);
+  s.per_chunk = (extent + chunks - 1) / chunks;
+  chunks = (extent + s.per_chunk - 1) / s.per_chunk;
+  s.cluster = 1;
+  for (uint32_t d = kRedMaxCluster; d >= 1; --d) {
+    if (chunks % d == 0) {
+      s.cluster = d;
+      break;
+    }
+  }
+  s.clusters = chunks / s.cluster;
+  s.chunks = chunks;
+  return s;
+}
+
+/*! \brief CTAs of `kernel` that the current device keeps resident at once */
+template <typename Kernel>
+inline uint32_t ResidentCtas(Kernel kernel, int threads) {
+  int per_sm = 0;
+  MSHADOW_CUDA_CALL(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, threads, 0));
+  if (per_sm < 1) per_sm = 1;
+  return static_cast<uint32_t>(per_sm) * static_cast<uint32_t>(gpu_rt::CurrentDevice().sm_count);
+}
 }  // namespace reddetail
 
 /*! \brief host side of the column reduce */
@@ -312,18 +372,20 @@ inline void ReduceKeepHighDimLaunch(DPlan dplan, const SPlan &splan, Shape<4> ps
   const uint32_t outer = pshape[0], channels = pshape[1], inner_rows = pshape[2], width = pshape[3];
   CHECK_EQ(width % kLanes, 0U);
   const uint32_t ppr = width / kLanes;
-  const int sms = gpu_rt::CurrentDevice().sm_count;
-  // aim at 8 CTAs of 256 threads per SM
-  const reddetail::Split sp = reddetail::PlanSplit(outer, (sms * 8 + channels - 1) / channels, 1);
+  auto kernel = ReduceKeepHighDimKernel<Saver, Reducer, kLanes, DType, DPlan, SPlan>;
+  // whole waves of resident CTAs; at most 64 chunks, each at least one outer index
+  static uint32_t slots = 0;  // per instantiation; the engine targets one device model
+  if (slots == 0) slots = reddetail::ResidentCtas(kernel, kRedHighThreads);
+  const reddetail::Split sp = reddetail::PlanSplitWaves(outer, channels, slots, 64);
   DType *partial = nullptr;
   if (sp.clusters > 1) {
     partial = static_cast<DType *>(
         gpu_rt::Scratch::Get(stream, static_cast<size_t>(sp.clusters) * channels * sizeof(DType)));
   }
-  auto kernel = ReduceKeepHighDimKernel<Saver, Reducer, kLanes, DType, DPlan, SPlan>;
+  const uint32_t per_plane = inner_rows * ppr;
   reddetail::LaunchClustered(kernel, dim3(channels, sp.chunks), dim3(kRedHighThreads), sp.cluster, stream,
                              dplan, splan, outer, channels, inner_rows, ppr, gpu_rt::FastDiv(ppr),
-                             sp.per_chunk, scale, partial);
+                             gpu_rt::FastDiv(per_plane == 0 ? 1 : per_plane), sp.per_chunk, scale, partial);
   MSHADOW_CUDA_POST_KERNEL_CHECK(ReduceKeepHighDimKernel);
   if (partial != nullptr) {
     ReduceFinishKernel<Saver, Reducer, DType, DPlan>
