@@ -38,6 +38,9 @@ struct PoolGeom {
 
 namespace pooldetail {
 
+/*! \brief floor(a / b) for b > 0, also for negative a */
+__host__ __device__ constexpr int FloorDiv(int a, int b) { return a >= 0 ? a / b : -((-a + b - 1) / b); }
+
 /*!
  * \brief bring `count` floats that start at `src` into shared memory.  Uses the bulk copy
  *  when the byte range is 16-byte aligned and sized, otherwise plain loads by all threads.
@@ -141,7 +144,7 @@ __global__ void __launch_bounds__(kPoolThreads)
 UnpoolPlanesKernel(float *dst, const float *src, const float *pooled, const float *gpooled, uint32_t planes,
                    uint32_t h, uint32_t w, uint32_t ph, uint32_t pw, PoolGeom g, int64_t ld_src, int64_t ld_pooled,
                    int64_t ld_dst, uint32_t gplanes, gpu_rt::FastDiv div_w, gpu_rt::FastDiv div_h,
-                   gpu_rt::FastDiv div_sy, gpu_rt::FastDiv div_sx, int *status) {
+                   gpu_rt::FastDiv div_sy, gpu_rt::FastDiv div_sx, gpu_rt::FastDiv div_wq, int *status) {
   extern __shared__ __align__(16) float tile[];
   __shared__ uint64_t bar;
   const uint32_t ky = KY > 0 ? KY : g.ky, kx = KX > 0 ? KX : g.kx;
@@ -153,6 +156,11 @@ UnpoolPlanesKernel(float *dst, const float *src, const float *pooled, const floa
   __syncthreads();
   uint32_t phase = 0;
   const bool dense = ld_src == static_cast<int64_t>(w) && ld_pooled == static_cast<int64_t>(pw);
+  // the four-pixels-per-thread path needs a compile-time window, a stride dividing 4 and rows
+  // that are whole groups of four
+  constexpr bool kQuad = KY > 0 && KX > 0 && SY > 0 && SX > 0 && (4 % (SX > 0 ? SX : 1) == 0);
+  const bool quad_ok = (w & 3u) == 0;
+  const bool vec_out = (ld_dst & 3) == 0 && reinterpret_cast<uintptr_t>(dst) % 16 == 0;
   for (uint32_t first = blockIdx.x * gplanes; first < planes; first += gridDim.x * gplanes) {
     const uint32_t np = min(gplanes, planes - first);
     const uint32_t n_src = np * h * w, n_pool = np * ph * pw;
@@ -180,25 +188,85 @@ UnpoolPlanesKernel(float *dst, const float *src, const float *pooled, const floa
       pooldetail::StagePitched(s_grad, g_grad, np * ph, pw, ld_pooled);
       __syncthreads();
     }
-    for (uint32_t o = threadIdx.x; o < n_src; o += kPoolThreads) {
-      const uint32_t row = div_w.Quot(o);  // p * h + y
-      const uint32_t x = o - row * w;
-      const uint32_t p = div_h.Quot(row);
-      const uint32_t y = row - p * h;
-      const float vsrc = s_src[o];
-      const uint32_t py_min = y < ky ? 0 : (SY > 0 ? (y - ky + sy) / sy : div_sy.Quot(y - ky + sy));
-      const uint32_t px_min = x < kx ? 0 : (SX > 0 ? (x - kx + sx) / sx : div_sx.Quot(x - kx + sx));
-      const uint32_t py_max = min(SY > 0 ? (y + sy) / sy : div_sy.Quot(y + sy), ph);
-      const uint32_t px_max = min(SX > 0 ? (x + sx) / sx : div_sx.Quot(x + sx), pw);
-      const float *pp = s_pool + p * ph * pw;
-      const float *gp = s_grad + p * ph * pw;
-      float val = 0.0f;
-      for (uint32_t py = py_min; py < py_max; ++py)
-        for (uint32_t px = px_min; px < px_max; ++px) {
-          const float pg = Reducer::PartialGrad(vsrc, pp[py * pw + px]);
-          val = __fadd_rn(val, __fmul_rn(pg, gp[py * pw + px]));
+    if (kQuad && quad_ok) {
+      // Four adjacent outputs per thread.  With the window fixed at compile time and a stride
+      // that divides 4, which pooled columns cover which of the four pixels is a compile-time
+      // pattern relative to the first candidate column pxb; only the image borders need
+      // run-time checks.  Windows are visited row-major, as the reference does.
+      constexpr int kSXs = SX > 0 ? SX : 1, kSYs = SY > 0 ? SY : 1;
+      constexpr int kOff = pooldetail::FloorDiv(kSXs - KX, kSXs);
+      constexpr int kCols = (3 / kSXs + 1) - kOff;
+      constexpr int kRows = (KY - 1) / kSYs + 1;
+      const uint32_t wq = w >> 2;
+      const uint32_t nq = np * h * wq;
+      for (uint32_t it = threadIdx.x; it < nq; it += kPoolThreads) {
+        const uint32_t row = div_wq.Quot(it);  // p * h + y
+        const uint32_t xq = it - row * wq;
+        const uint32_t p = div_h.Quot(row);
+        const uint32_t y = row - p * h;
+        const float4 sv4 = *reinterpret_cast<const float4 *>(s_src + row * w + 4 * xq);
+        const float sv[4] = {sv4.x, sv4.y, sv4.z, sv4.w};
+        constexpr uint32_t kKYs = KY > 0 ? KY : 1;
+        const int py_lo = y < kKYs ? 0 : static_cast<int>((y - kKYs + kSYs) / kSYs);
+        const int py_hi = min(static_cast<int>((y + kSYs) / kSYs), static_cast<int>(ph));
+        const int pxb = static_cast<int>(xq) * (4 / kSXs) + kOff;
+        const float *pp = s_pool + p * ph * pw;
+        const float *gp = s_grad + p * ph * pw;
+        float val[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+#pragma unroll
+        for (int r = 0; r < kRows; ++r) {
+          const int py = py_lo + r;
+          if (py < py_hi) {
+#pragma unroll
+            for (int cc = 0; cc < kCols; ++cc) {
+              const int px = pxb + cc;
+              if (px >= 0 && px < static_cast<int>(pw)) {
+                const float pv = pp[py * pw + px];
+                const float gv = gp[py * pw + px];
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                  // pixel 4*xq+i is covered by pooled columns [lo, hi) relative to pxb
+                  const int lo = pooldetail::FloorDiv(i - KX + kSXs, kSXs) - kOff;
+                  const int hi = i / kSXs + 1 - kOff;
+                  if (cc >= lo && cc < hi) {
+                    val[i] = __fadd_rn(val[i], __fmul_rn(Reducer::PartialGrad(sv[i], pv), gv));
+                  }
+                }
+              }
+            }
+          }
         }
-      dst[(static_cast<int64_t>(first) * h + row) * ld_dst + x] = val;
+        float *out = dst + (static_cast<int64_t>(first) * h + row) * ld_dst + 4 * xq;
+        if (vec_out) {
+          __stcs(reinterpret_cast<float4 *>(out), make_float4(val[0], val[1], val[2], val[3]));
+        } else {
+          out[0] = val[0];
+          out[1] = val[1];
+          out[2] = val[2];
+          out[3] = val[3];
+        }
+      }
+    } else {
+      for (uint32_t o = threadIdx.x; o < n_src; o += kPoolThreads) {
+        const uint32_t row = div_w.Quot(o);  // p * h + y
+        const uint32_t x = o - row * w;
+        const uint32_t p = div_h.Quot(row);
+        const uint32_t y = row - p * h;
+        const float vsrc = s_src[o];
+        const uint32_t py_min = y < ky ? 0 : (SY > 0 ? (y - ky + sy) / sy : div_sy.Quot(y - ky + sy));
+        const uint32_t px_min = x < kx ? 0 : (SX > 0 ? (x - kx + sx) / sx : div_sx.Quot(x - kx + sx));
+        const uint32_t py_max = min(SY > 0 ? (y + sy) / sy : div_sy.Quot(y + sy), ph);
+        const uint32_t px_max = min(SX > 0 ? (x + sx) / sx : div_sx.Quot(x + sx), pw);
+        const float *pp = s_pool + p * ph * pw;
+        const float *gp = s_grad + p * ph * pw;
+        float val = 0.0f;
+        for (uint32_t py = py_min; py < py_max; ++py)
+          for (uint32_t px = px_min; px < px_max; ++px) {
+            const float pg = Reducer::PartialGrad(vsrc, pp[py * pw + px]);
+            val = __fadd_rn(val, __fmul_rn(pg, gp[py * pw + px]));
+          }
+        dst[(static_cast<int64_t>(first) * h + row) * ld_dst + x] = val;
+      }
     }
     tma::FenceAsyncShared();
     __syncthreads();
@@ -407,7 +475,8 @@ inline void UnpoolPlanesLaunch(float *dst, const float *src, const float *pooled
         dst, src, pooled, gpooled, static_cast<uint32_t>(planes), static_cast<uint32_t>(h),                       \
         static_cast<uint32_t>(w), static_cast<uint32_t>(ph), static_cast<uint32_t>(pw), g, ld_src, ld_pooled,     \
         ld_dst, gp, gpu_rt::FastDiv(static_cast<uint32_t>(w)), gpu_rt::FastDiv(static_cast<uint32_t>(h)),         \
-        gpu_rt::FastDiv(static_cast<uint32_t>(sy)), gpu_rt::FastDiv(static_cast<uint32_t>(sx)), status);          \
+        gpu_rt::FastDiv(static_cast<uint32_t>(sy)), gpu_rt::FastDiv(static_cast<uint32_t>(sx)),                   \
+        gpu_rt::FastDiv(static_cast<uint32_t>(w / 4 > 0 ? w / 4 : 1)), status);                                   \
   }
   if (ky == 3 && kx == 3 && sy == 2 && sx == 2) MSHADOW_B200_UNPOOL_LAUNCH_(3, 3, 2, 2)
   else if (ky == 2 && kx == 2 && sy == 2 && sx == 2) MSHADOW_B200_UNPOOL_LAUNCH_(2, 2, 2, 2)
