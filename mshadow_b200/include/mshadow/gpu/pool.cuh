@@ -358,21 +358,7 @@ ChannelPoolKernel(float *dst, const float *src, uint32_t channels, uint32_t plan
 
 namespace pooldetail {
 /*! \brief device status word (see tma.cuh); lives as long as the process */
-inline int *StatusWord() {
-  static std::mutex mu;
-  static std::map<int, int *> words;
-  int dev = 0;
-  MSHADOW_CUDA_CALL(cudaGetDevice(&dev));
-  std::lock_guard<std::mutex> lock(mu);
-  auto it = words.find(dev);
-  if (it == words.end()) {
-    int *p = nullptr;
-    MSHADOW_CUDA_CALL(cudaMalloc(&p, sizeof(int)));
-    MSHADOW_CUDA_CALL(cudaMemset(p, 0, sizeof(int)));
-    it = words.insert(std::make_pair(dev, p)).first;
-  }
-  return it->second;
-}
+inline int *StatusWord() { return gpu_rt::StatusWord(); }
 
 /*! \brief planes per CTA: as many as fit `budget` bytes, in multiples of `quantum` */
 inline uint32_t GroupSize(uint64_t bytes_per_plane, uint32_t quantum, uint64_t budget, uint32_t planes) {

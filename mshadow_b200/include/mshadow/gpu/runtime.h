@@ -158,6 +158,26 @@ class Scratch {
   }
 };
 
+/*!
+ * \brief one int per device in which a kernel records that a bounded wait gave up
+ *  (see gpu/tma.cuh); allocated on first use, lives as long as the process
+ */
+inline int *StatusWord() {
+  static std::mutex mu;
+  static std::map<int, int *> words;
+  int dev = 0;
+  MSHADOW_CUDA_CALL(cudaGetDevice(&dev));
+  std::lock_guard<std::mutex> lock(mu);
+  auto it = words.find(dev);
+  if (it == words.end()) {
+    int *p = nullptr;
+    MSHADOW_CUDA_CALL(cudaMalloc(&p, sizeof(int)));
+    MSHADOW_CUDA_CALL(cudaMemset(p, 0, sizeof(int)));
+    it = words.insert(std::make_pair(dev, p)).first;
+  }
+  return it->second;
+}
+
 /*! \brief exact division of a non-negative 31-bit number by a fixed divisor, without a divide */
 struct FastDiv {
   uint32_t mul;

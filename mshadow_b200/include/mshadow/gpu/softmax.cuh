@@ -20,6 +20,7 @@
 #define MSHADOW_GPU_SOFTMAX_CUH_
 
 #include "./reduce.cuh"
+#include "./tma.cuh"
 
 namespace mshadow {
 namespace cuda {
@@ -120,6 +121,99 @@ SoftmaxRowKernel(float *dst, const float *src, uint32_t rows, uint32_t cols, int
   }
 }
 
+/*!
+ * \brief long rows: one persistent CTA of 1024 threads per SM.  While the CTA works on row y
+ *  out of registers (max, exp, sum, normalise, store), a bulk asynchronous copy already
+ *  brings row y + gridDim.x into shared memory, so the read of the next row overlaps the
+ *  arithmetic and the write of the current one; with a whole row per CTA and the register
+ *  file full, no second CTA could provide that overlap.  Dynamic shared memory: one row.
+ *  The quotient v / s is formed as v * (1/s) with one fused correction step, which equals
+ *  IEEE division except for rare last-bit cases.
+ */
+template <int kItems>
+__global__ void __launch_bounds__(1024, 1)
+SoftmaxStagedKernel(float *dst, const float *src, uint32_t rows, uint32_t cols, int64_t ld_dst, int64_t ld_src,
+                    int *status) {
+  constexpr int kThreads = 1024;
+  extern __shared__ __align__(16) float4 staged_row[];
+  __shared__ uint64_t bar;
+  __shared__ float buf[32];
+  const uint32_t nitems = cols >> 2;
+  const uint32_t row_bytes = cols * 4u;
+  uint32_t y = blockIdx.x;
+  if (y >= rows) return;
+  if (threadIdx.x == 0) {
+    tma::BarrierInit(&bar, 1);
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    tma::BarrierExpect(&bar, row_bytes);
+    tma::BulkLoad(staged_row, src + y * ld_src, row_bytes, &bar);
+  }
+  uint32_t phase = 0;
+  for (; y < rows; y += gridDim.x) {
+    if (!tma::WaitBounded(&bar, phase)) {
+      if (threadIdx.x == 0) atomicExch(status, tma::kStatusBulkCopyTimeout);
+      tma::WaitBounded(&bar, phase);
+      return;
+    }
+    phase ^= 1;
+    float v[kItems][4];
+#pragma unroll
+    for (int k = 0; k < kItems; ++k) {
+      const uint32_t item = threadIdx.x + k * kThreads;
+      if (item < nitems) {
+        const float4 p = staged_row[item];
+        v[k][0] = p.x;
+        v[k][1] = p.y;
+        v[k][2] = p.z;
+        v[k][3] = p.w;
+      } else {
+        v[k][0] = v[k][1] = v[k][2] = v[k][3] = -FLT_MAX;
+      }
+    }
+    __syncthreads();  // every thread holds its part of the row: the buffer may be refilled
+    const uint32_t ynext = y + gridDim.x;
+    if (threadIdx.x == 0 && ynext < rows) {
+      tma::FenceAsyncShared();
+      tma::BarrierExpect(&bar, row_bytes);
+      tma::BulkLoad(staged_row, src + ynext * ld_src, row_bytes, &bar);
+    }
+    float m = -FLT_MAX;
+#pragma unroll
+    for (int k = 0; k < kItems; ++k)
+#pragma unroll
+      for (int l = 0; l < 4; ++l) m = m < v[k][l] ? v[k][l] : m;
+    m = smdetail::BlockAll<smdetail::MaxOp, kThreads>(m, buf);
+    float s = 0.0f;
+#pragma unroll
+    for (int k = 0; k < kItems; ++k) {
+      const bool in_row = threadIdx.x + k * kThreads < nitems;
+#pragma unroll
+      for (int l = 0; l < 4; ++l) {
+        v[k][l] = in_row ? expf(__fsub_rn(v[k][l], m)) : 0.0f;
+        s = __fadd_rn(s, v[k][l]);
+      }
+    }
+    s = smdetail::BlockAll<smdetail::SumOp, kThreads>(s, buf);
+    const float r = __frcp_rn(s);
+    float4 *out = reinterpret_cast<float4 *>(dst + y * ld_dst);
+#pragma unroll
+    for (int k = 0; k < kItems; ++k) {
+      const uint32_t item = threadIdx.x + k * kThreads;
+      if (item < nitems) {
+        float q[4];
+#pragma unroll
+        for (int l = 0; l < 4; ++l) {
+          const float q0 = __fmul_rn(v[k][l], r);
+          q[l] = __fmaf_rn(__fmaf_rn(-q0, s, v[k][l]), r, q0);
+        }
+        __stcs(out + item, make_float4(q[0], q[1], q[2], q[3]));
+      }
+    }
+  }
+}
+
 /*! \brief any row length: three sweeps over global memory, one CTA per row */
 template <int kThreads>
 __global__ void __launch_bounds__(kThreads)
@@ -163,7 +257,24 @@ inline void SoftmaxLaunch(float *dst, const float *src, int64_t rows, int64_t co
   const bool vec = cols % 4 == 0 && reinterpret_cast<uintptr_t>(dst) % 16 == 0 &&
                    reinterpret_cast<uintptr_t>(src) % 16 == 0 && (rows == 1 || (ld_dst % 4 == 0 && ld_src % 4 == 0));
   using smdetail::LaunchRow;
-  if (vec && cols <= 32768) {
+  const int sms = gpu_rt::CurrentDevice().sm_count;
+  if (vec && cols >= 4096 && cols <= 32768 && rows >= sms) {
+    // long rows, enough of them to keep one persistent CTA per SM busy
+    const uint32_t n = c / 4;
+    const size_t smem = static_cast<size_t>(c) * 4;
+    int *status = gpu_rt::StatusWord();
+#define MSHADOW_B200_SOFTMAX_STAGED_(ITEMS)                                                                       \
+  {                                                                                                               \
+    auto kernel = SoftmaxStagedKernel<ITEMS>;                                                                     \
+    MSHADOW_CUDA_CALL(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 128 * 1024));     \
+    kernel<<<sms, 1024, smem, stream>>>(dst, src, r, c, ld_dst, ld_src, status);                                  \
+  }
+    if (n <= 1024) MSHADOW_B200_SOFTMAX_STAGED_(1)
+    else if (n <= 2048) MSHADOW_B200_SOFTMAX_STAGED_(2)
+    else if (n <= 4096) MSHADOW_B200_SOFTMAX_STAGED_(4)
+    else MSHADOW_B200_SOFTMAX_STAGED_(8)
+#undef MSHADOW_B200_SOFTMAX_STAGED_
+  } else if (vec && cols <= 32768) {
     const uint32_t n = c / 4;  // 16-byte items per row
     if (n <= 32) LaunchRow<32, 1, 4>(dst, src, r, c, ld_dst, ld_src, stream);
     else if (n <= 128) LaunchRow<128, 1, 4>(dst, src, r, c, ld_dst, ld_src, stream);

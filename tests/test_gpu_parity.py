@@ -157,7 +157,10 @@ def test_reduce_keep_highdim(lib, reducer, saver, shape, pad):
 
 @pytest.mark.parametrize("rows,cols,pad", [(1, 1, 0), (4, 8, 0), (9, 1000, 0), (3, 33, 5), (5, 4096, 0),
                                            (4, 32000, 0), (3, 31999, 0), (2, 8193, 0), (2, 40000, 0), (70, 513, 3),
-                                           (300, 128, 0)])
+                                           (300, 128, 0),
+                                           # many long rows: the persistent, bulk-copy staged kernel
+                                           (200, 4096, 0), (333, 12000, 0), (150, 32000, 0), (149, 32768, 0),
+                                           (450, 6000, 8)])
 def test_softmax(lib, rows, cols, pad):
     rng = np.random.default_rng(rows * 1000 + cols)
     src = (2.0 * rng.standard_normal((rows, cols))).astype(np.float32)
