@@ -14,7 +14,7 @@
  * What callers need to know:
  *   - the array holds kNoAllocScratchFloats floats (1 MiB).  Every GPU that loads the
  *     library carries it from load to exit, used or not.  A call whose partial rows would
- *     not fit (clusters x columns floats; at most about 300 thousand floats on a 148-SM B200, for inputs around 150 thousand columns wide) is
+ *     not fit (clusters x columns floats; a few hundred thousand floats at most on a 148-SM B200, reached by inputs over a hundred thousand columns wide) is
  *     rejected with MSB_ERR_SHAPE before anything is launched.
  *   - the first call on each device looks up the array's device address
  *     (cudaGetSymbolAddress) and the SM count.  That first call is a set-up call: make it
@@ -51,8 +51,14 @@ static __device__ __align__(256) float g_noalloc_scratch[kNoAllocScratchFloats];
 struct PerDevice {
   bool ready;
   float *scratch;
-  int sm_count;
+  uint32_t slots_vec;     // resident CTAs of the 128-bit kernel on this device
+  uint32_t slots_scalar;  // ... and of the element-at-a-time kernel
 };
+
+typedef mshadow::expr::Plan<mshadow::Tensor<mshadow::gpu, 1, float>, float> DPlan;
+typedef mshadow::expr::Plan<mshadow::Tensor<mshadow::gpu, 2, float>, float> SPlan;
+#define MSB_NOALLOC_KERNEL(LANES) \
+  mshadow::cuda::ReduceKeepLowestKernel<mshadow::sv::saveto, mshadow::red::sum, LANES, float, DPlan, SPlan>
 PerDevice g_dev[kMaxDevices];
 std::mutex g_dev_mutex;
 
@@ -70,11 +76,19 @@ int SetUpDevice(int dev, PerDevice *out) {
     float *ptr = nullptr;
     cudaError_t err = cudaGetSymbolAddress(reinterpret_cast<void **>(&ptr), g_noalloc_scratch);
     if (err != cudaSuccess || ptr == nullptr) return FailNoAlloc(MSB_ERR_CUDA, cudaGetErrorString(err));
-    int sms = 0;
+    int sms = 0, per_sm_vec = 0, per_sm_scalar = 0;
     err = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
     if (err != cudaSuccess || sms <= 0) return FailNoAlloc(MSB_ERR_CUDA, cudaGetErrorString(err));
+    // the same occupancy figures the allocating entry point plans its grid with
+    err = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm_vec, MSB_NOALLOC_KERNEL(4),
+                                                        mshadow::cuda::kRedLowThreads, 0);
+    if (err == cudaSuccess)
+      err = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm_scalar, MSB_NOALLOC_KERNEL(1),
+                                                          mshadow::cuda::kRedLowThreads, 0);
+    if (err != cudaSuccess) return FailNoAlloc(MSB_ERR_CUDA, cudaGetErrorString(err));
     g_dev[dev].scratch = ptr;
-    g_dev[dev].sm_count = sms;
+    g_dev[dev].slots_vec = static_cast<uint32_t>(per_sm_vec < 1 ? 1 : per_sm_vec) * sms;
+    g_dev[dev].slots_scalar = static_cast<uint32_t>(per_sm_scalar < 1 ? 1 : per_sm_scalar) * sms;
     g_dev[dev].ready = true;
   }
   *out = g_dev[dev];
@@ -103,8 +117,8 @@ extern "C" int msb_reduce_keep_lowest_sum_f32_noalloc(float *dst, const float *s
   const int lanes = vec ? 4 : 1;
   const uint32_t col_tiles = static_cast<uint32_t>((cols + mshadow::cuda::kRedLowThreads * lanes - 1) /
                                                    (mshadow::cuda::kRedLowThreads * lanes));
-  const mshadow::cuda::reddetail::Split sp = mshadow::cuda::reddetail::PlanSplit(
-      static_cast<uint32_t>(rows), (pd.sm_count * 16 + col_tiles - 1) / col_tiles, 32);
+  const mshadow::cuda::reddetail::Split sp = mshadow::cuda::reddetail::PlanKeepLowest(
+      static_cast<uint32_t>(rows), col_tiles, vec ? pd.slots_vec : pd.slots_scalar);
   float *partial = nullptr;
   if (sp.clusters > 1) {
     if (static_cast<size_t>(sp.clusters) * static_cast<size_t>(cols) > kNoAllocScratchFloats)
@@ -115,8 +129,6 @@ extern "C" int msb_reduce_keep_lowest_sum_f32_noalloc(float *dst, const float *s
   st.stream_ = static_cast<cudaStream_t>(stream);
   const Tensor<gpu, 1, float> d(dst, Shape1(cols), static_cast<index_t>(cols), &st);
   const Tensor<gpu, 2, float> s(const_cast<float *>(src), Shape2(rows, cols), static_cast<index_t>(ld), &st);
-  typedef expr::Plan<Tensor<gpu, 1, float>, float> DPlan;
-  typedef expr::Plan<Tensor<gpu, 2, float>, float> SPlan;
   const DPlan dplan = expr::MakePlan(d);
   const SPlan splan = expr::MakePlan(s);
   const dim3 grid(col_tiles, sp.chunks), block(mshadow::cuda::kRedLowThreads);
@@ -134,11 +146,9 @@ extern "C" int msb_reduce_keep_lowest_sum_f32_noalloc(float *dst, const float *s
   const uint32_t urows = static_cast<uint32_t>(rows), ucols = static_cast<uint32_t>(cols);
   cudaError_t err;
   if (vec) {
-    err = cudaLaunchKernelEx(&cfg, mshadow::cuda::ReduceKeepLowestKernel<sv::saveto, red::sum, 4, float, DPlan, SPlan>, dplan,
-                             splan, urows, ucols, sp.per_chunk, scale, partial);
+    err = cudaLaunchKernelEx(&cfg, MSB_NOALLOC_KERNEL(4), dplan, splan, urows, ucols, sp.per_chunk, scale, partial);
   } else {
-    err = cudaLaunchKernelEx(&cfg, mshadow::cuda::ReduceKeepLowestKernel<sv::saveto, red::sum, 1, float, DPlan, SPlan>, dplan,
-                             splan, urows, ucols, sp.per_chunk, scale, partial);
+    err = cudaLaunchKernelEx(&cfg, MSB_NOALLOC_KERNEL(1), dplan, splan, urows, ucols, sp.per_chunk, scale, partial);
   }
   if (err != cudaSuccess) return FailNoAlloc(MSB_ERR_CUDA, cudaGetErrorString(err));
   if (partial != nullptr) {

@@ -330,6 +330,41 @@ inline Split PlanSplitWaves(uint32_t extent, uint32_t fixed, uint32_t slots, uin
   return s;
 }
 
+/*!
+ * \brief row split of the column reduce: `col_tiles` CTA columns times k row chunks, at least
+ *  32 rows per chunk.  Prefers the smallest k that is a multiple of the cluster size and fills
+ *  whole waves of `slots` resident CTAs to 95 %; otherwise the best-filling k of any kind.
+ *  Shared by the allocating and the allocation-free entry points, which must agree.
+ */
+inline Split PlanKeepLowest(uint32_t rows, uint32_t col_tiles, uint32_t slots) {
+  uint32_t kmax = rows / 32;
+  if (kmax < 1) kmax = 1;
+  if (kmax > 4096) kmax = 4096;
+  uint32_t pick = 0;
+  if (static_cast<uint64_t>(col_tiles) * kmax > slots) {
+    for (uint32_t k = kRedMaxCluster; k <= kmax && pick == 0; k += kRedMaxCluster) {
+      const uint64_t ctas = static_cast<uint64_t>(col_tiles) * k;
+      if (ctas * 20 < static_cast<uint64_t>(slots) * 19) continue;  // under 95 % of one wave
+      const uint64_t waves = (ctas + slots - 1) / slots;
+      if (ctas * 20 >= waves * slots * 19) pick = k;
+    }
+  }
+  if (pick == 0) pick = WaveFriendlyChunks(col_tiles, kmax, slots);
+  Split s;
+  s.per_chunk = (rows + pick - 1) / pick;
+  uint32_t chunks = (rows + s.per_chunk - 1) / s.per_chunk;
+  s.cluster = 1;
+  for (uint32_t d = kRedMaxCluster; d >= 1; --d) {
+    if (chunks % d == 0) {
+      s.cluster = d;
+      break;
+    }
+  }
+  s.clusters = chunks / s.cluster;
+  s.chunks = chunks;
+  return s;
+}
+
 /*! \brief CTAs of `kernel` that the current device keeps resident at once */
 template <typename Kernel>
 inline uint32_t ResidentCtas(Kernel kernel, int threads) {
@@ -345,16 +380,16 @@ template <typename Saver, typename Reducer, int kLanes, typename DType, typename
 inline void ReduceKeepLowestLaunch(DPlan dplan, const SPlan &splan, Shape<2> eshape, DType scale,
                                    cudaStream_t stream) {
   const uint32_t rows = eshape[0], cols = eshape[1];
-  const int sms = gpu_rt::CurrentDevice().sm_count;
   const uint32_t col_tiles = gpu_rt::CeilDiv(cols, kRedLowThreads * kLanes);
-  // aim at 16 CTAs of 128 threads per SM; at least 32 rows per chunk
-  const reddetail::Split sp = reddetail::PlanSplit(rows, (sms * 16 + col_tiles - 1) / col_tiles, 32);
+  auto kernel = ReduceKeepLowestKernel<Saver, Reducer, kLanes, DType, DPlan, SPlan>;
+  static uint32_t slots = 0;  // per instantiation; the engine targets one device model
+  if (slots == 0) slots = reddetail::ResidentCtas(kernel, kRedLowThreads);
+  const reddetail::Split sp = reddetail::PlanKeepLowest(rows, col_tiles, slots);
   DType *partial = nullptr;
   if (sp.clusters > 1) {
     partial = static_cast<DType *>(
         gpu_rt::Scratch::Get(stream, static_cast<size_t>(sp.clusters) * cols * sizeof(DType)));
   }
-  auto kernel = ReduceKeepLowestKernel<Saver, Reducer, kLanes, DType, DPlan, SPlan>;
   reddetail::LaunchClustered(kernel, dim3(col_tiles, sp.chunks), dim3(kRedLowThreads), sp.cluster, stream,
                              dplan, splan, rows, cols, sp.per_chunk, scale, partial);
   MSHADOW_CUDA_POST_KERNEL_CHECK(ReduceKeepLowestKernel);
