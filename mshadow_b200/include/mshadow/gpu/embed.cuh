@@ -31,8 +31,8 @@
 namespace mshadow {
 namespace cuda {
 
-const uint32_t kSegChunk = 128;
-const int kSegDepth = 8;
+const uint32_t kSegChunk = MSHADOW_B200_SEG_CHUNK;
+const int kSegDepth = MSHADOW_B200_SEG_DEPTH;
 
 /*!
  * \brief one level of the chunked segmented sum.
@@ -41,7 +41,7 @@ const int kSegDepth = 8;
  *  chunk for the next level.  grid = (chunks, feature slabs).
  */
 template <int kLanes>
-__global__ void __launch_bounds__(256, 3)
+__global__ void __launch_bounds__(256, MSHADOW_B200_SEG_MIN_CTAS)
 SegmentSumKernel(float *dst, int64_t ld_dst, const int32_t *keys, const int32_t *rows, const float *src,
                  int64_t ld_src, uint32_t n, uint32_t width, int32_t *part_keys, int32_t *part_rows,
                  float *partials) {

@@ -27,8 +27,8 @@
 namespace mshadow {
 namespace cuda {
 
-const int kMapThreads = 256;
-const int kMapUnroll = 4;
+const int kMapThreads = MSHADOW_B200_MAP_THREADS;
+const int kMapUnroll = MSHADOW_B200_MAP_UNROLL;
 /*! \brief resident CTAs per SM that the grid is sized for */
 const int kMapCtasPerSM = 8;
 

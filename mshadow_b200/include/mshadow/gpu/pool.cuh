@@ -283,11 +283,11 @@ UnpoolPlanesKernel(float *dst, const float *src, const float *pooled, const floa
  *  segment re-reads NSIZE-1 halo channels).  `plane` = h*w elements per channel, dense.
  */
 template <typename Reducer, int NSIZE, int kLanes>
-__global__ void __launch_bounds__(kPoolThreads)
+__global__ void __launch_bounds__(kPoolThreads, MSHADOW_B200_CHPOOL_MIN_CTAS)
 ChannelPoolKernel(float *dst, const float *src, uint32_t channels, uint32_t plane, uint32_t groups_per_image,
                   uint32_t total_items, gpu_rt::FastDiv image_of_item, uint32_t seg_len) {
   constexpr int kPad = NSIZE / 2;
-  constexpr int kAhead = 4;          // loads issued this many channels before they are needed
+  constexpr int kAhead = MSHADOW_B200_CHPOOL_AHEAD;  // loads issued this many channels before they are needed
   constexpr int kRing = NSIZE + kAhead;
   const uint32_t item = blockIdx.x * kPoolThreads + threadIdx.x;
   if (item >= total_items) return;
@@ -395,8 +395,8 @@ inline uint32_t WaveFriendlySegments(uint32_t fixed, uint32_t kmax, uint32_t slo
 }  // namespace pooldetail
 
 /*! \brief dynamic shared memory per CTA: forward leaves room for 4 CTAs per SM, backward for 3 */
-const uint64_t kPoolSmemBudget = 56 * 1024;
-const uint64_t kUnpoolSmemBudget = 74 * 1024;
+const uint64_t kPoolSmemBudget = MSHADOW_B200_POOL_SMEM_KB * 1024;
+const uint64_t kUnpoolSmemBudget = MSHADOW_B200_UNPOOL_SMEM_KB * 1024;
 
 /*! \brief true when the plane kernels can run: at least one plane has to fit the budget */
 inline bool PoolPlanesFit(int64_t h, int64_t w, int64_t ph, int64_t pw, bool backward) {

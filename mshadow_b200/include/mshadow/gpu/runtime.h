@@ -20,6 +20,7 @@
 #include <utility>
 
 #include "../tensor.h"
+#include "./tuning.h"
 
 namespace mshadow {
 namespace gpu_rt {

@@ -308,7 +308,7 @@ SoftmaxGradKernel(float *dst, const float *src, const float *label, uint32_t row
                   int ignore_label, float alpha, float smooth_grad) {
   const uint32_t total = rows * items_per_row;
   const uint32_t step = gridDim.x * 256;
-  constexpr int kUnroll = 4;
+  constexpr int kUnroll = MSHADOW_B200_SMGRAD_UNROLL;
   for (uint32_t base = blockIdx.x * 256 + threadIdx.x; base < total; base += step * kUnroll) {
     float v[kUnroll][kLanes];
     int kk[kUnroll];
@@ -379,7 +379,7 @@ inline void SoftmaxGradLaunch(float *dst, const float *src, const float *label, 
   const uint32_t r = static_cast<uint32_t>(rows), c = static_cast<uint32_t>(cols);
   const uint32_t ipr = vec ? c / 4 : c;
   const int64_t work = static_cast<int64_t>(r) * ipr;
-  int grid = gpu_rt::CeilDiv(work, 256 * 4);
+  int grid = gpu_rt::CeilDiv(work, 256 * MSHADOW_B200_SMGRAD_UNROLL);
   const int cap = gpu_rt::CurrentDevice().sm_count * 8;
   if (grid > cap) grid = cap;
   if (vec) {
