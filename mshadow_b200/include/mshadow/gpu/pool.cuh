@@ -354,6 +354,97 @@ ChannelPoolKernel(float *dst, const float *src, uint32_t channels, uint32_t plan
   }
 }
 
+/*!
+ * \brief channel-window pooling with the channel planes staged through shared memory.
+ *  Same arithmetic as ChannelPoolKernel (window kept in registers, channels added in
+ *  ascending order), but the thread no longer waits on its own global loads: one thread
+ *  issues a bulk asynchronous copy per channel plane (or plane tile) into a ring of `ring`
+ *  shared-memory slots, `ring` channels ahead of the march, so a CTA keeps ring * tile bytes
+ *  in flight at no register cost and reads memory in long contiguous pieces.
+ *  CTA = (image, pixel tile) x channel segment; thread = 4 adjacent pixels.
+ *  Dynamic shared memory: ring * tile_px floats.
+ */
+template <typename Reducer, int NSIZE>
+__global__ void __launch_bounds__(1024, 1)
+ChannelPoolStagedKernel(float *dst, const float *src, uint32_t channels, uint32_t plane, uint32_t tile_px,
+                        uint32_t tiles_per_plane, uint32_t seg_len, uint32_t ring, int *status) {
+  constexpr int kPad = NSIZE / 2;
+  constexpr uint32_t kMaxRing = 16;
+  extern __shared__ __align__(16) float slots[];
+  __shared__ uint64_t bars[kMaxRing];
+  const uint32_t image_idx = blockIdx.x / tiles_per_plane;
+  const uint32_t tile_idx = blockIdx.x - image_idx * tiles_per_plane;
+  const uint32_t px0 = tile_idx * tile_px;
+  const uint32_t len = min(tile_px, plane - px0);  // pixels of this tile, a multiple of 4
+  const uint32_t c_begin = blockIdx.y * seg_len;
+  const uint32_t c_end = min(channels, c_begin + seg_len);
+  const int64_t base = static_cast<int64_t>(image_idx) * channels * plane + px0;
+  const float *in = src + base;
+  float *out = dst + base;
+  const uint32_t nsteps = (c_end - c_begin) + 2 * kPad;  // channels c_begin-kPad .. c_end-1+kPad
+  const bool mine = threadIdx.x * 4 < len;
+  if (threadIdx.x == 0) {
+    for (uint32_t j = 0; j < ring; ++j) tma::BarrierInit(&bars[j], 1);
+  }
+  __syncthreads();
+  auto issue = [&](uint32_t step) {  // called by thread 0 only
+    const int64_t ch = static_cast<int64_t>(c_begin) - kPad + step;
+    if (step < nsteps && ch >= 0 && ch < static_cast<int64_t>(channels)) {
+      const uint32_t slot = step % ring;
+      tma::BarrierExpect(&bars[slot], len * 4u);
+      tma::BulkLoad(slots + static_cast<size_t>(slot) * tile_px, in + ch * plane, len * 4u, &bars[slot]);
+    }
+  };
+  if (threadIdx.x == 0) {
+    for (uint32_t j = 0; j < ring; ++j) issue(j);
+  }
+  float init;
+  Reducer::SetInitValue(init);
+  float win[NSIZE][4];
+#pragma unroll
+  for (int j = 0; j < NSIZE; ++j) win[j][0] = win[j][1] = win[j][2] = win[j][3] = init;
+  uint32_t phase_bits = 0;  // expected parity per ring slot; identical in every thread
+  for (uint32_t s0 = 0; s0 < nsteps; s0 += NSIZE) {
+#pragma unroll
+    for (int j = 0; j < NSIZE; ++j) {
+      const uint32_t s = s0 + j;
+      if (s < nsteps) {
+        const int64_t ch = static_cast<int64_t>(c_begin) - kPad + s;
+        const uint32_t slot = s % ring;
+        float4 v = make_float4(init, init, init, init);
+        if (ch >= 0 && ch < static_cast<int64_t>(channels)) {
+          if (!tma::WaitBounded(&bars[slot], (phase_bits >> slot) & 1u)) {
+            if (threadIdx.x == 0) atomicExch(status, tma::kStatusBulkCopyTimeout);
+            tma::WaitBounded(&bars[slot], (phase_bits >> slot) & 1u);
+            return;
+          }
+          phase_bits ^= 1u << slot;
+          if (mine) v = *reinterpret_cast<const float4 *>(slots + static_cast<size_t>(slot) * tile_px + threadIdx.x * 4);
+        }
+        __syncthreads();  // the slot has been read by everyone: refill it `ring` channels ahead
+        if (threadIdx.x == 0) {
+          tma::FenceAsyncShared();
+          issue(s + ring);
+        }
+        win[j][0] = v.x;
+        win[j][1] = v.y;
+        win[j][2] = v.z;
+        win[j][3] = v.w;
+        if (s >= 2 * kPad && mine) {
+          // window of output channel ch - kPad: the last NSIZE loaded channels, oldest first
+          float res[4] = {init, init, init, init};
+#pragma unroll
+          for (int t = 1; t <= NSIZE; ++t)
+#pragma unroll
+            for (int l = 0; l < 4; ++l) Reducer::Reduce(res[l], win[(j + t) % NSIZE][l]);
+          __stcs(reinterpret_cast<float4 *>(out + (ch - kPad) * plane + threadIdx.x * 4),
+                 make_float4(res[0], res[1], res[2], res[3]));
+        }
+      }
+    }
+  }
+}
+
 // ------------------------------- host side ----------------------------------------------
 
 namespace pooldetail {
@@ -510,8 +601,46 @@ inline void ChannelPoolLaunch(float *dst, const float *src, int64_t n, int64_t c
     kernel<<<dim3(tiles, nseg), kPoolThreads, 0, stream>>>(dst, src, static_cast<uint32_t>(c), plane, groups,  \
                                                             items, gpu_rt::FastDiv(groups), seg_len);          \
   }
-#define MSHADOW_B200_CHPOOL_PICK_(NS) \
-  if (vec) MSHADOW_B200_CHPOOL_LAUNCH_(NS, 4) else MSHADOW_B200_CHPOOL_LAUNCH_(NS, 1)
+  // staged variant: planes (or plane tiles of at most 4096 pixels) ride through a shared-memory ring
+  const uint32_t tiles_per_plane = (plane + 4095) / 4096;
+  const uint32_t tile_px = ((plane + tiles_per_plane - 1) / tiles_per_plane + 3) & ~3u;
+  const uint32_t st_threads = ((tile_px / 4) + 31) & ~31u;
+  const bool staged = vec && MSHADOW_B200_CHPOOL_STAGED && c >= 2 * nsize &&
+                      n * static_cast<int64_t>(tiles_per_plane) < (int64_t(1) << 31);
+#define MSHADOW_B200_CHPOOL_STAGED_LAUNCH_(NS)                                                                 \
+  {                                                                                                            \
+    auto kernel = ChannelPoolStagedKernel<Reducer, NS>;                                                        \
+    uint32_t ring = static_cast<uint32_t>((MSHADOW_B200_CHPOOL_RING_KB * 1024) / (tile_px * 4));               \
+    if (ring < NS + 2) ring = NS + 2;                                                                          \
+    if (ring > 16) ring = 16;                                                                                  \
+    const size_t smem = static_cast<size_t>(ring) * tile_px * 4;                                               \
+    MSHADOW_CUDA_CALL(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));  \
+    int per_sm = 0;                                                                                            \
+    MSHADOW_CUDA_CALL(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, st_threads, smem));       \
+    const uint32_t slots = static_cast<uint32_t>(per_sm < 1 ? 1 : per_sm) * gpu_rt::CurrentDevice().sm_count;  \
+    const uint32_t fixed = static_cast<uint32_t>(n) * tiles_per_plane;                                         \
+    /* segments: whole waves of resident CTAs, weighed against the NS-1 halo channels each one re-reads */    \
+    uint32_t segs = 1;                                                                                         \
+    double best = 0.0;                                                                                         \
+    for (uint32_t k = 1; k <= 16 && k * 2 * NS <= static_cast<uint32_t>(c); ++k) {                             \
+      const uint64_t ctas = static_cast<uint64_t>(fixed) * k;                                                  \
+      const uint64_t waves = (ctas + slots - 1) / slots;                                                       \
+      const double eff = static_cast<double>(ctas) / static_cast<double>(waves * slots) /                     \
+                         (1.0 + static_cast<double>((NS - 1) * k) / static_cast<double>(c));                   \
+      if (eff > best + 1e-9) {                                                                                 \
+        best = eff;                                                                                            \
+        segs = k;                                                                                              \
+      }                                                                                                        \
+    }                                                                                                          \
+    const uint32_t seg_len = (static_cast<uint32_t>(c) + segs - 1) / segs;                                     \
+    const uint32_t nseg = (static_cast<uint32_t>(c) + seg_len - 1) / seg_len;                                  \
+    kernel<<<dim3(fixed, nseg), st_threads, smem, stream>>>(dst, src, static_cast<uint32_t>(c), plane, tile_px, \
+                                                             tiles_per_plane, seg_len, ring,                   \
+                                                             gpu_rt::StatusWord());                            \
+  }
+#define MSHADOW_B200_CHPOOL_PICK_(NS)                \
+  if (staged) MSHADOW_B200_CHPOOL_STAGED_LAUNCH_(NS) \
+  else if (vec) MSHADOW_B200_CHPOOL_LAUNCH_(NS, 4) else MSHADOW_B200_CHPOOL_LAUNCH_(NS, 1)
   switch (nsize) {
     case 1: MSHADOW_B200_CHPOOL_PICK_(1) break;
     case 3: MSHADOW_B200_CHPOOL_PICK_(3) break;
@@ -520,6 +649,7 @@ inline void ChannelPoolLaunch(float *dst, const float *src, int64_t n, int64_t c
     default: MSHADOW_B200_CHPOOL_PICK_(9) break;
   }
 #undef MSHADOW_B200_CHPOOL_PICK_
+#undef MSHADOW_B200_CHPOOL_STAGED_LAUNCH_
 #undef MSHADOW_B200_CHPOOL_LAUNCH_
   MSHADOW_CUDA_POST_KERNEL_CHECK(ChannelPoolKernel);
 }

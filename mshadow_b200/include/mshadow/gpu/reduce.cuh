@@ -28,8 +28,8 @@ namespace cuda {
 
 namespace cg = cooperative_groups;
 
-const int kRedLowThreads = 128;
-const int kRedHighThreads = 256;
+const int kRedLowThreads = MSHADOW_B200_REDLOW_THREADS;
+const int kRedHighThreads = MSHADOW_B200_REDHIGH_THREADS;
 const int kRedMaxCluster = 8;
 
 namespace reddetail {
@@ -109,7 +109,7 @@ ReduceKeepLowestKernel(DPlan dst, const SPlan src, uint32_t rows, uint32_t cols,
   if (live) {
     reddetail::LoadLanes<kLanes>(src, y0, x, acc);
     uint32_t y = y0 + 1;
-    constexpr int kDepth = 8;
+    constexpr int kDepth = MSHADOW_B200_REDLOW_DEPTH;
     for (; y + kDepth <= y1; y += kDepth) {
       DType v[kDepth][kLanes];
 #pragma unroll
@@ -196,7 +196,7 @@ ReduceKeepHighDimKernel(DPlan dst, const SPlan src, uint32_t outer, uint32_t cha
   for (int l = 0; l < kLanes; ++l) Reducer::SetInitValue(acc[l]);
   // the chunk's planes are walked as one list of 16-byte groups, so that every thread always
   // has kDepth independent loads in flight whatever the plane size
-  constexpr int kDepth = 4;
+  constexpr int kDepth = MSHADOW_B200_REDHIGH_DEPTH;
   const uint32_t npacks = (n1 > n0 ? n1 - n0 : 0) * per_plane;
   for (uint32_t base = threadIdx.x; base < npacks; base += kRedHighThreads * kDepth) {
     DType v[kDepth][kLanes];

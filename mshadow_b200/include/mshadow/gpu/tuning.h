@@ -28,6 +28,12 @@
 #ifndef MSHADOW_B200_CHPOOL_MIN_CTAS
 #define MSHADOW_B200_CHPOOL_MIN_CTAS 1
 #endif
+#ifndef MSHADOW_B200_CHPOOL_STAGED
+#define MSHADOW_B200_CHPOOL_STAGED 1  // route dense 16-byte-aligned inputs through the shared-memory ring kernel
+#endif
+#ifndef MSHADOW_B200_CHPOOL_RING_KB
+#define MSHADOW_B200_CHPOOL_RING_KB 100  // shared memory of the ring per CTA (two CTAs per SM)
+#endif
 #ifndef MSHADOW_B200_POOL_SMEM_KB
 #define MSHADOW_B200_POOL_SMEM_KB 28  // staged planes per CTA, forward pooling (14: 78 %, 28: 86 %, 56: 83 %)
 #endif
@@ -36,6 +42,19 @@
 #endif
 #ifndef MSHADOW_B200_SMGRAD_UNROLL
 #define MSHADOW_B200_SMGRAD_UNROLL 1  // as for the map kernel: 1 -> 102 %, 2 -> 95-97 %, 4 -> 94 % of copy bandwidth
+#endif
+
+#ifndef MSHADOW_B200_REDLOW_THREADS
+#define MSHADOW_B200_REDLOW_THREADS 128  // column reduce: threads per CTA (4 columns each)
+#endif
+#ifndef MSHADOW_B200_REDLOW_DEPTH
+#define MSHADOW_B200_REDLOW_DEPTH 8  // column reduce: rows in flight per thread
+#endif
+#ifndef MSHADOW_B200_REDHIGH_THREADS
+#define MSHADOW_B200_REDHIGH_THREADS 256  // channel reduce: threads per CTA
+#endif
+#ifndef MSHADOW_B200_REDHIGH_DEPTH
+#define MSHADOW_B200_REDHIGH_DEPTH 4  // channel reduce: 16-byte groups in flight per thread
 #endif
 
 #endif  // MSHADOW_GPU_TUNING_H_

@@ -227,7 +227,12 @@ def test_unpool_all_tied(lib):
                                                     ((2, 9, 4, 4), 3, 2, 1), ((1, 5, 2, 2), 5, 1, 2),
                                                     ((2, 6, 3, 4), 1, 1, 0), ((2, 40, 14, 14), 5, 1, 2),
                                                     ((2, 20, 7, 9), 7, 1, 3), ((1, 12, 8, 8), 9, 1, 4),
-                                                    ((2, 10, 6, 6), 5, 1, 0)])
+                                                    ((2, 10, 6, 6), 5, 1, 0),
+                                                    # shared-memory ring kernel: whole planes, plane tiles,
+                                                    # several channel segments
+                                                    ((3, 33, 56, 56), 3, 1, 1), ((2, 24, 80, 80), 5, 1, 2),
+                                                    ((40, 64, 28, 28), 5, 1, 2), ((1, 19, 4, 4), 9, 1, 4),
+                                                    ((2, 300, 12, 12), 7, 1, 3)])
 def test_chpool(lib, reducer, shape, nsize, stride, pad):
     rng = np.random.default_rng(sum(shape) + nsize)
     src = rng.uniform(-1, 1, shape).astype(np.float32)
