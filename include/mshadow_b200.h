@@ -163,6 +163,15 @@ int msb_chpool_f32(float *dst, const float *src, int64_t n, int64_t c, int64_t h
                    int nsize, int stride, int pad, int64_t ld_src, int64_t ld_dst, int reducer,
                    msb_stream_t stream);
 
+/* dst = ch_unpool<Reducer>(src, pooled, grad_pooled, nsize, stride, pad), the gradient of
+   chpool; src and dst are (n, c, h, w), pooled and grad_pooled (n, pc, h, w):
+   mshadow/extension/channel_unpool.h:20-133.  Shapes for which the reference's window would
+   run past the pooled channels (it clamps with c, not pc) are refused with MSB_ERR_SHAPE. */
+int msb_ch_unpool_f32(float *dst, const float *src, const float *pooled, const float *gpooled,
+                      int64_t n, int64_t c, int64_t pc, int64_t h, int64_t w, int nsize, int stride,
+                      int pad, int64_t ld_src, int64_t ld_pooled, int64_t ld_dst, int reducer,
+                      msb_stream_t stream);
+
 /* ---- embedding backward --------------------------------------------------------------- */
 
 /* AddTakeGrad(dst, index, src): dst[clip(index[y])] += src[y]:

@@ -61,6 +61,7 @@ _SIGNATURES = {
     "msb_unpool_f32": [vp, vp, vp, vp, i64, i64, i64, i64, i64, cint, cint, cint, cint, i64, i64, i64,
                        cint, vp],
     "msb_chpool_f32": [vp, vp, i64, i64, i64, i64, cint, cint, cint, i64, i64, cint, vp],
+    "msb_ch_unpool_f32": [vp, vp, vp, vp, i64, i64, i64, i64, i64, cint, cint, cint, i64, i64, i64, cint, vp],
     "msb_addtakegrad_f32_i32": [vp, vp, vp, i64, i64, i64, i64, i64, vp],
     "msb_addtakegrad_largebatch_f32_i32": [vp, vp, vp, vp, i64, i64, i64, vp],
     "msb_sort_by_key_i32": [vp, vp, i64, cint, vp],
@@ -202,6 +203,14 @@ class Library:
         pad = nsize // 2 if pad is None else pad
         self.call("msb_chpool_f32", _ptr(dst), _ptr(src), n, c, h, w, nsize, stride, pad, _ld(src), _ld(dst),
                   reducer, stream)
+        return dst
+
+    def ch_unpool(self, dst, src, pooled, gpooled, nsize, stride=1, pad=None, reducer=0, stream=None):
+        n, c, h, w = src.shape
+        pad = nsize // 2 if pad is None else pad
+        assert _ld(pooled) == _ld(gpooled)
+        self.call("msb_ch_unpool_f32", _ptr(dst), _ptr(src), _ptr(pooled), _ptr(gpooled), n, c, pooled.shape[1], h,
+                  w, nsize, stride, pad, _ld(src), _ld(pooled), _ld(dst), reducer, stream)
         return dst
 
     def addtakegrad(self, dst, index, src, stream=None):

@@ -384,6 +384,32 @@ int msb_chpool_f32(float *dst, const float *src, int64_t n, int64_t c, int64_t h
   MSB_GUARD_END
 }
 
+int msb_ch_unpool_f32(float *dst, const float *src, const float *pooled, const float *gpooled, int64_t n, int64_t c,
+                      int64_t pc, int64_t h, int64_t w, int nsize, int stride, int pad, int64_t ld_src,
+                      int64_t ld_pooled, int64_t ld_dst, int reducer, msb_stream_t stream) {
+  MSB_REQUIRE(reducer >= 0 && reducer <= 2, MSB_ERR_ARGUMENT, "unknown reducer");
+  MSB_REQUIRE(nsize > 0 && stride > 0 && pad >= 0, MSB_ERR_ARGUMENT, "bad window");
+  MSB_REQUIRE(FitsIndex(n) && FitsIndex(c) && FitsIndex(pc) && FitsIndex(h) && FitsIndex(w) && FitsIndex(n * c * h) &&
+                  FitsIndex(n * c * h * w) && FitsIndex(n * pc * h * w),
+              MSB_ERR_SHAPE, "extent out of range");
+  MSB_REQUIRE(ld_src >= w && ld_dst >= w && ld_pooled >= w, MSB_ERR_SHAPE, "stride < width");
+  if (n * c * h * w == 0) return MSB_OK;
+  {
+    const int64_t top = (c - 1 + pad + stride) / stride;
+    MSB_REQUIRE((top < c ? top : c) <= pc, MSB_ERR_SHAPE, "window reaches past the pooled channels");
+  }
+  MSB_REQUIRE(dst && src && pooled && gpooled, MSB_ERR_ARGUMENT, "null pointer");
+  MSB_GUARD_BEGIN
+  BorrowedStream st(stream);
+  G4 d = Img(dst, n, c, h, w, ld_dst, st.get());
+  const G4 s = Img(src, n, c, h, w, ld_src, st.get());
+  const G4 p = Img(pooled, n, pc, h, w, ld_pooled, st.get()), g = Img(gpooled, n, pc, h, w, ld_pooled, st.get());
+  if (reducer == 0) d = ch_unpool<red::sum>(s, p, g, nsize, stride, pad);
+  else if (reducer == 1) d = ch_unpool<red::maximum>(s, p, g, nsize, stride, pad);
+  else d = ch_unpool<red::minimum>(s, p, g, nsize, stride, pad);
+  MSB_GUARD_END
+}
+
 int msb_addtakegrad_f32_i32(float *dst, const int32_t *index, const float *src, int64_t k, int64_t d, int64_t nidx,
                             int64_t ld_dst, int64_t ld_src, msb_stream_t stream) {
   MSB_REQUIRE(FitsIndex(k) && FitsIndex(d) && FitsIndex(nidx) && ld_dst >= d && ld_src >= d, MSB_ERR_SHAPE,

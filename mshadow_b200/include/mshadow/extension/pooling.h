@@ -234,6 +234,82 @@ class Plan<ChannelPoolingExp<Reducer, SrcExp, DType, srcdim>, DType> {
   const index_t out_c_, h_, nsize_, stride_, pad_, in_c_;
 };
 
+// ------------------------------------------------------------------------------------------
+// gradient of channel pooling (dmlc/mshadow: mshadow/extension/channel_unpool.h:20-133)
+// ------------------------------------------------------------------------------------------
+template <typename Reducer, typename SrcExp, typename DType, int srcdim>
+struct ChannelUnpoolingExp
+    : public MakeTensorExp<ChannelUnpoolingExp<Reducer, SrcExp, DType, srcdim>, SrcExp, srcdim, DType> {
+  const SrcExp &data_src_;
+  const SrcExp &data_pooled_;
+  const SrcExp &grad_pooled_;
+  index_t pchannel_, nsize_, kstride_, pad_;
+  ChannelUnpoolingExp(const SrcExp &data_src, const SrcExp &data_pooled, const SrcExp &grad_pooled, index_t nsize,
+                      index_t kstride, index_t pad)
+      : data_src_(data_src), data_pooled_(data_pooled), grad_pooled_(grad_pooled), nsize_(nsize), kstride_(kstride),
+        pad_(pad) {
+    typedef ShapeCheck<srcdim, SrcExp> Check;
+    const Shape<srcdim> pshape = Check::Check(grad_pooled);
+    CHECK_EQ(pshape, Check::Check(data_pooled)) << "ChannelUnPoolingExp: data and grad shape mismatch";
+    const Shape<srcdim> sshape = Check::Check(data_src);
+    for (int k = 0; k < srcdim; ++k) {
+      if (k == 1) continue;  // the channel extent is the one that pooling changes
+      CHECK_EQ(pshape[k], sshape[k]) << "ChannelUnPoolingExp: pooled tensor and src tensor shape mismatch"
+                                     << pshape[k] << " vs " << sshape[k];
+    }
+    pchannel_ = pshape[1];
+    this->shape_ = sshape;
+  }
+};
+
+template <typename Reducer, typename SrcExp, typename DType, int etype>
+inline ChannelUnpoolingExp<Reducer, SrcExp, DType, ExpInfo<SrcExp>::kDim> ch_unpool(
+    const Exp<SrcExp, DType, etype> &data_src, const Exp<SrcExp, DType, etype> &data_pooled,
+    const Exp<SrcExp, DType, etype> &grad_pooled, index_t nsize, index_t stride, index_t pad) {
+  TypeCheckPass<ExpInfo<SrcExp>::kDim >= 3>::Error_Expression_Does_Not_Meet_Dimension_Req();
+  return ChannelUnpoolingExp<Reducer, SrcExp, DType, ExpInfo<SrcExp>::kDim>(data_src.self(), data_pooled.self(),
+                                                                            grad_pooled.self(), nsize, stride, pad);
+}
+template <typename Reducer, typename SrcExp, typename DType, int etype>
+inline ChannelUnpoolingExp<Reducer, SrcExp, DType, ExpInfo<SrcExp>::kDim> ch_unpool(
+    const Exp<SrcExp, DType, etype> &data_src, const Exp<SrcExp, DType, etype> &data_pooled,
+    const Exp<SrcExp, DType, etype> &grad_pooled, index_t nsize) {
+  return ch_unpool<Reducer>(data_src, data_pooled, grad_pooled, nsize, 1, nsize / 2);
+}
+
+template <typename Reducer, typename SrcExp, typename DType, int srcdim>
+class Plan<ChannelUnpoolingExp<Reducer, SrcExp, DType, srcdim>, DType> {
+ public:
+  explicit Plan(const ChannelUnpoolingExp<Reducer, SrcExp, DType, srcdim> &e)
+      : src_(MakePlan(e.data_src_)), pooled_(MakePlan(e.data_pooled_)), grad_(MakePlan(e.grad_pooled_)),
+        c_(e.shape_[srcdim - 3]), h_(e.shape_[srcdim - 2]), pc_(e.pchannel_), nsize_(e.nsize_), stride_(e.kstride_),
+        pad_(e.pad_) {}
+  /*!
+   * \brief sum over the pooled channels whose window contains source channel c, in ascending
+   *  order from zero, of PartialGrad(src, pooled) * grad; the upper clamp is the SOURCE
+   *  channel count, as in the reference
+   */
+  MSHADOW_XINLINE DType Eval(index_t i, index_t j) const {
+    const DType v = src_.Eval(i, j);
+    const index_t t = i / h_, y = i - t * h_;
+    const index_t n = t / c_, c = t - n * c_;
+    const index_t lo = c < nsize_ - pad_ ? 0 : (c - (nsize_ - pad_) + stride_) / stride_;
+    index_t hi = (c + pad_ + stride_) / stride_;
+    if (hi > c_) hi = c_;
+    DType val = static_cast<DType>(0);
+    for (index_t cc = lo; cc < hi; ++cc) {
+      const index_t row = (n * pc_ + cc) * h_ + y;
+      val = detail::AddRN<DType>(
+          val, detail::MulRN<DType>(Reducer::PartialGrad(v, pooled_.Eval(row, j)), grad_.Eval(row, j)));
+    }
+    return val;
+  }
+
+ private:
+  Plan<SrcExp, DType> src_, pooled_, grad_;
+  const index_t c_, h_, pc_, nsize_, stride_, pad_;
+};
+
 }  // namespace expr
 
 #if MSHADOW_USE_CUDA && defined(__CUDACC__)

@@ -263,6 +263,28 @@ void ORC(chpool)(float *dst, const float *src, int64_t n, int64_t c, int64_t h, 
   }
 }
 
+/* extension/channel_unpool.h:108-126: pooled channels [cstart, cend) cover source channel c;
+   the upper clamp uses the SOURCE channel count, as the reference does */
+void ORC(ch_unpool)(float *dst, const float *src, const float *pooled, const float *gpooled, int64_t n,
+                    int64_t c, int64_t pc, int64_t h, int64_t w, int nsize, int stride, int pad,
+                    int64_t ld_src, int64_t ld_pooled, int64_t ld_dst, int reducer) {
+#pragma omp parallel for
+  for (int64_t i = 0; i < n * c * h; ++i) {
+    const int64_t y = i % h, ci = (i / h) % c, ni = i / h / c;
+    const int64_t cstart = ci < nsize - pad ? 0 : (ci - (nsize - pad) + stride) / stride;
+    const int64_t cend = imin((ci + pad + stride) / stride, c);
+    for (int64_t x = 0; x < w; ++x) {
+      const float vsrc = src[i * ld_src + x];
+      float val = 0.0f;
+      for (int64_t cc = cstart; cc < cend; ++cc) {
+        const int64_t o = ((ni * pc + cc) * h + y) * ld_pooled + x;
+        val += partial_grad(vsrc, pooled[o], reducer) * gpooled[o];
+      }
+      dst[i * ld_dst + x] = val;
+    }
+  }
+}
+
 /* ---- embedding backward ---- */
 
 /* tensor_cpu-inl.h:497-508: serial over the batch, index clipped into [0, K-1] */

@@ -90,6 +90,12 @@ void ORC(unpool)(float *dst, const float *src, const float *pooled, const float 
 void ORC(chpool)(float *dst, const float *src, int64_t n, int64_t c, int64_t h, int64_t w,
                  int nsize, int stride, int pad, int64_t ld_src, int64_t ld_dst, int reducer);
 
+/* ch_unpool<Reducer>(src, pooled, grad_pooled, nsize, stride, pad): gradient of chpool;
+   src is (n, c, h, w), pooled and grad_pooled are (n, pc, h, w) (extension/channel_unpool.h:102-133) */
+void ORC(ch_unpool)(float *dst, const float *src, const float *pooled, const float *gpooled, int64_t n,
+                    int64_t c, int64_t pc, int64_t h, int64_t w, int nsize, int stride, int pad,
+                    int64_t ld_src, int64_t ld_pooled, int64_t ld_dst, int reducer);
+
 /* dst[clip(index[y])] += src[y]  (tensor_cpu-inl.h:497-508) */
 void ORC(addtakegrad)(float *dst, const int32_t *index, const float *src, int64_t k,
                       int64_t d, int64_t nidx, int64_t ld_dst, int64_t ld_src);

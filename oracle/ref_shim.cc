@@ -164,6 +164,16 @@ void ref_chpool(float *dst, const float *src, int64_t n, int64_t c, int64_t h, i
   else d = chpool<red::minimum>(s, nsize, stride, pad);
 }
 
+void ref_ch_unpool(float *dst, const float *src, const float *pooled, const float *gpooled, int64_t n,
+                   int64_t c, int64_t pc, int64_t h, int64_t w, int nsize, int stride, int pad, int64_t ld_src,
+                   int64_t ld_pooled, int64_t ld_dst, int reducer) {
+  T4 s = img(src, n, c, h, w, ld_src), d = img(dst, n, c, h, w, ld_dst);
+  T4 p = img(pooled, n, pc, h, w, ld_pooled), g = img(gpooled, n, pc, h, w, ld_pooled);
+  if (reducer == 0) d = ch_unpool<red::sum>(s, p, g, nsize, stride, pad);
+  else if (reducer == 1) d = ch_unpool<red::maximum>(s, p, g, nsize, stride, pad);
+  else d = ch_unpool<red::minimum>(s, p, g, nsize, stride, pad);
+}
+
 void ref_addtakegrad(float *dst, const int32_t *index, const float *src, int64_t k, int64_t d,
                      int64_t nidx, int64_t ld_dst, int64_t ld_src) {
   Tensor<cpu, 1, int32_t> idx(const_cast<int32_t *>(index), Shape1(nidx), nidx, NULL);

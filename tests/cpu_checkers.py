@@ -114,6 +114,16 @@ class Checker:
                            C.c_int(reducer))
         return dst
 
+    def ch_unpool(self, dst, src, pooled, gpooled, nsize, stride=1, pad=None, reducer=0):
+        n, c, h, w = src.shape
+        pc = pooled.shape[1]
+        pad = nsize // 2 if pad is None else pad
+        assert _ld(pooled) == _ld(gpooled)
+        self._fn("ch_unpool")(_fp(dst), _fp(src), _fp(pooled), _fp(gpooled), i64(n), i64(c), i64(pc), i64(h),
+                              i64(w), C.c_int(nsize), C.c_int(stride), C.c_int(pad), i64(_ld(src)),
+                              i64(_ld(pooled)), i64(_ld(dst)), C.c_int(reducer))
+        return dst
+
     # ---- embedding backward ------------------------------------------------------
     def addtakegrad(self, dst, index, src):
         k, d = dst.shape

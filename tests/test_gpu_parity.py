@@ -243,6 +243,21 @@ def test_chpool(lib, reducer, shape, nsize, stride, pad):
     assert_bits(host(got), want)
 
 
+@pytest.mark.parametrize("reducer", [0, 1, 2])
+@pytest.mark.parametrize("shape,nsize,pad", [((2, 8, 3, 5), 5, 0), ((2, 7, 4, 4), 3, 0), ((3, 16, 6, 6), 5, 2),
+                                             ((1, 12, 5, 8), 7, 0), ((2, 6, 3, 3), 1, 3)])
+def test_ch_unpool(lib, reducer, shape, nsize, pad):
+    """Gradient of chpool(src, nsize): pooled has as many channels as the source."""
+    rng = np.random.default_rng(sum(shape) + nsize + reducer)
+    src = (rng.integers(0, 4, shape) / 4.0).astype(np.float32)  # coarse values: ties
+    pooled = orc.chpool(np.zeros(shape, np.float32), src, nsize, reducer=reducer)
+    g = rng.uniform(0, 1, shape).astype(np.float32)
+    want = orc.ch_unpool(np.zeros(shape, np.float32), src, pooled, g, nsize, reducer=reducer)
+    got = lib.ch_unpool(dev(np.zeros(shape, np.float32), pad), dev(src, pad), dev(pooled), dev(g), nsize,
+                        reducer=reducer)
+    assert_bits(host(got), want)
+
+
 def zipf_indices(rng, n, k, s=1.1):
     p = (np.arange(k) + 1.0) ** (-s)
     return rng.choice(k, size=n, p=p / p.sum()).astype(np.int32)

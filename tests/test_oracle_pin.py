@@ -132,6 +132,19 @@ def test_chpool_matches_reference(reducer, c, nsize, stride, pad):
 
 
 @needs_ref
+@pytest.mark.parametrize("reducer", [0, 1, 2])
+@pytest.mark.parametrize("c,nsize", [(8, 5), (7, 3), (6, 1), (12, 7)])
+def test_ch_unpool_matches_reference(reducer, c, nsize):
+    rng = np.random.default_rng(c * nsize + reducer)
+    shape = (2, c, 3, 5)
+    src = pitched((rng.integers(0, 4, shape) / 4.0).astype(np.float32), 1)
+    pooled = orc.chpool(np.zeros(shape, np.float32), src, nsize, reducer=reducer)
+    g = rnd(rng, shape, 0.0, 1.0)
+    res = [lib.ch_unpool(np.zeros(shape, np.float32), src, pooled, g, nsize, reducer=reducer) for lib in (orc, ref)]
+    assert same_bits(*res)
+
+
+@needs_ref
 def test_addtakegrad_matches_reference():
     rng = np.random.default_rng(5)
     k, d, n = 11, 20, 300
