@@ -244,7 +244,11 @@ def kernel_cases(lib, torch, small=False):
     lab = torch.randint(0, c, (r,), device=dev, generator=g).float()
     yield ("softmax_grad", "C3 SoftmaxGrad %dx%d" % (r, c), 8 * r * c + 4 * r, r * c,
            lambda: lib.softmax_grad(L, P, lab), 10)
-    del L, P
+    # beyond the reference API: both in one pass (reads the logits, writes the gradient)
+    Gd = P
+    yield ("softmax_grad_fused", "Softmax+SoftmaxGrad fused %dx%d" % (r, c), 8 * r * c + 4 * r, r * c,
+           lambda: lib.softmax_grad_fused(Gd, L, lab), 10)
+    del L, P, Gd
     # C4: pooling
     imgs = 32 if small else 256
     X = torch.rand(imgs * 256, 56, 56, device=dev, generator=g)
@@ -272,7 +276,25 @@ def kernel_cases(lib, torch, small=False):
     yield ("addtakegrad", "C5 AddTakeGradLargeBatch 262144x1024, %d Zipf(1.1) indices" % nidx,
            4 * nidx * d + 8 * nidx + 8 * uniq * d, nidx * d,
            lambda: lib.addtakegrad_largebatch(table, keys, vals, src), 10)
+    # the step before it: unsorted indices in, clip + stable radix sort + segmented sum in one call
+    raw = torch.from_numpy(idx).to(dev)
+    yield ("addtakegrad_unsorted", "C5 AddTakeGrad (unsorted, clipped) 262144x1024, %d Zipf(1.1) indices" % nidx,
+           4 * nidx * d + 12 * nidx + 8 * uniq * d, nidx * d,
+           lambda: lib.addtakegrad(table, raw, src), 10)
+    k2, v2 = raw.clone(), vals.clone()
+    yield ("sort_by_key", "SortByKey %d int32 pairs" % nidx, 16 * nidx, nidx,
+           lambda: lib.sort_by_key(k2, v2, True), 10)
     del src, table
+    # gradient of the channel pooling (generic map kernel, window loop inside the plan)
+    imgs = 32 if small else 256
+    X4 = torch.rand(imgs, 256, 56, 56, device=dev, generator=g)
+    P4 = torch.empty_like(X4)
+    lib.chpool(P4, X4, 5)
+    gP4 = torch.rand(imgs, 256, 56, 56, device=dev, generator=g)
+    G4 = torch.empty_like(X4)
+    yield ("ch_unpool", "ch_unpool<sum> nsize 5 (%d,256,56,56)" % imgs, 16 * X4.numel(), X4.numel(),
+           lambda: lib.ch_unpool(G4, X4, P4, gP4, 5), 10)
+    del X4, P4, gP4, G4
     torch.cuda.empty_cache()
 
 

@@ -144,6 +144,12 @@ int msb_softmax_grad_f32(float *dst, const float *src, const float *label, int64
                          int64_t cols, int64_t ld_dst, int64_t ld_src, int mode,
                          float ignore_label, float alpha, msb_stream_t stream);
 
+/* dst = Softmax(logits) - onehot(label) in ONE pass: the result of msb_softmax_f32 followed
+   by msb_softmax_grad_f32 (mode 0) without storing the probabilities.  No counterpart in the
+   reference; for loss layers that need only the gradient (8 instead of 16 bytes per element). */
+int msb_softmax_grad_fused_f32(float *dst, const float *logits, const float *label, int64_t rows,
+                               int64_t cols, int64_t ld_dst, int64_t ld_src, msb_stream_t stream);
+
 /* ---- pooling expressions (fp32 instantiations over plain tensors) -------------------- */
 
 /* dst = pool<Reducer>(src, ky, kx, sy, sx) on `planes` images of h x w; output

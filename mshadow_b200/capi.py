@@ -57,6 +57,7 @@ _SIGNATURES = {
     "msb_reduce_keep_highdim_f32": [vp, vp, i64, i64, i64, i64, i64, f32, cint, cint, vp],
     "msb_softmax_f32": [vp, vp, i64, i64, i64, i64, vp],
     "msb_softmax_grad_f32": [vp, vp, vp, i64, i64, i64, i64, cint, f32, f32, vp],
+    "msb_softmax_grad_fused_f32": [vp, vp, vp, i64, i64, i64, i64, vp],
     "msb_pool_f32": [vp, vp, i64, i64, i64, cint, cint, cint, cint, i64, i64, cint, vp],
     "msb_unpool_f32": [vp, vp, vp, vp, i64, i64, i64, i64, i64, cint, cint, cint, cint, i64, i64, i64,
                        cint, vp],
@@ -182,6 +183,12 @@ class Library:
         rows, cols = src.shape
         self.call("msb_softmax_grad_f32", _ptr(dst), _ptr(src), _ptr(label), rows, cols, _ld(dst), _ld(src),
                   mode, ignore_label, alpha, stream)
+        return dst
+
+    def softmax_grad_fused(self, dst, logits, label, stream=None):
+        rows, cols = logits.shape
+        self.call("msb_softmax_grad_fused_f32", _ptr(dst), _ptr(logits), _ptr(label), rows, cols, _ld(dst),
+                  _ld(logits), stream)
         return dst
 
     def pool(self, dst, src, ky, kx, sy, sx, reducer=1, stream=None):

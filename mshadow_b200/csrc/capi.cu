@@ -319,6 +319,19 @@ int msb_softmax_grad_f32(float *dst, const float *src, const float *label, int64
   MSB_GUARD_END
 }
 
+int msb_softmax_grad_fused_f32(float *dst, const float *logits, const float *label, int64_t rows, int64_t cols,
+                               int64_t ld_dst, int64_t ld_src, msb_stream_t stream) {
+  MSB_REQUIRE(FitsIndex(rows) && FitsIndex(cols) && ld_dst >= cols && ld_src >= cols, MSB_ERR_SHAPE,
+              "extent out of range");
+  if (rows == 0 || cols == 0) return MSB_OK;
+  MSB_REQUIRE(dst && logits && label, MSB_ERR_ARGUMENT, "null pointer");
+  MSB_GUARD_BEGIN
+  BorrowedStream st(stream);
+  SoftmaxGradFused(Mat(dst, rows, cols, ld_dst, st.get()), Mat(logits, rows, cols, ld_src, st.get()),
+                   Vec(label, rows, st.get()));
+  MSB_GUARD_END
+}
+
 int msb_pool_f32(float *dst, const float *src, int64_t planes, int64_t h, int64_t w, int ky, int kx, int sy, int sx,
                  int64_t ld_src, int64_t ld_dst, int reducer, msb_stream_t stream) {
   MSB_REQUIRE(reducer >= 0 && reducer <= 2, MSB_ERR_ARGUMENT, "unknown reducer");

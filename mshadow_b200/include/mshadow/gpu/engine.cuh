@@ -188,6 +188,18 @@ inline void SmoothSoftmaxGrad(const Tensor<gpu, 2, float> &dst, const Tensor<gpu
                           ignore_label, alpha, Stream<gpu>::GetStream(dst.stream_));
 }
 
+/*!
+ * \brief dst = Softmax(logits) - onehot(label) in one pass over memory: what
+ *  `Softmax(p, logits); SoftmaxGrad(dst, p, label);` computes, for loss layers that only
+ *  need the gradient.  Not part of the reference API; it saves the write and re-read of p.
+ */
+inline void SoftmaxGradFused(Tensor<gpu, 2, float> dst, const Tensor<gpu, 2, float> &logits,
+                             const Tensor<gpu, 1, float> &label) {
+  cuda::SoftmaxGradCheck(dst, logits, label);
+  cuda::SoftmaxLaunch(dst.dptr_, logits.dptr_, dst.size(0), dst.size(1), dst.stride_, logits.stride_,
+                      Stream<gpu>::GetStream(dst.stream_), label.dptr_);
+}
+
 inline void AddTakeGrad(Tensor<gpu, 2, float> dst, const Tensor<gpu, 1, int32_t> &index,
                         const Tensor<gpu, 2, float> &src) {
   CHECK_EQ(dst.size(1), src.size(1)) << "AddTakeGrad: shape of src mismatch";

@@ -60,7 +60,8 @@ __device__ __forceinline__ float BlockAll(float v, float *buf) {
  */
 template <int kThreads, int kItems, int kLanes>
 __global__ void __launch_bounds__(kThreads)
-SoftmaxRowKernel(float *dst, const float *src, uint32_t rows, uint32_t cols, int64_t ld_dst, int64_t ld_src) {
+SoftmaxRowKernel(float *dst, const float *src, const float *label, uint32_t rows, uint32_t cols, int64_t ld_dst,
+                 int64_t ld_src) {
   __shared__ float buf[32];
   const uint32_t nitems = (cols + kLanes - 1) / kLanes;
   for (uint32_t y = blockIdx.x; y < rows; y += gridDim.x) {
@@ -102,19 +103,22 @@ SoftmaxRowKernel(float *dst, const float *src, uint32_t rows, uint32_t cols, int
       }
     }
     s = smdetail::BlockAll<smdetail::SumOp, kThreads>(s, buf);
+    // fused gradient: subtract one at the label's column (label == nullptr: plain softmax)
+    const int hot = label != nullptr ? static_cast<int>(label[y]) : -1;
 #pragma unroll
     for (int k = 0; k < kItems; ++k) {
       const uint32_t item = threadIdx.x + k * kThreads;
       if (item < nitems) {
+        float q[kLanes];
+#pragma unroll
+        for (int l = 0; l < kLanes; ++l) {
+          q[l] = __fdiv_rn(v[k][l], s);
+          if (static_cast<int>(item * kLanes + l) == hot) q[l] = __fsub_rn(q[l], 1.0f);
+        }
         if (kLanes == 4) {
-          float4 p;
-          p.x = __fdiv_rn(v[k][0], s);
-          p.y = __fdiv_rn(v[k][1 % kLanes], s);
-          p.z = __fdiv_rn(v[k][2 % kLanes], s);
-          p.w = __fdiv_rn(v[k][3 % kLanes], s);
-          __stcs(reinterpret_cast<float4 *>(out) + item, p);
+          __stcs(reinterpret_cast<float4 *>(out) + item, make_float4(q[0], q[1 % kLanes], q[2 % kLanes], q[3 % kLanes]));
         } else {
-          __stcs(out + item, __fdiv_rn(v[k][0], s));
+          __stcs(out + item, q[0]);
         }
       }
     }
@@ -132,8 +136,8 @@ SoftmaxRowKernel(float *dst, const float *src, uint32_t rows, uint32_t cols, int
  */
 template <int kItems>
 __global__ void __launch_bounds__(1024, 1)
-SoftmaxStagedKernel(float *dst, const float *src, uint32_t rows, uint32_t cols, int64_t ld_dst, int64_t ld_src,
-                    int *status) {
+SoftmaxStagedKernel(float *dst, const float *src, const float *label, uint32_t rows, uint32_t cols, int64_t ld_dst,
+                    int64_t ld_src, int *status) {
   constexpr int kThreads = 1024;
   extern __shared__ __align__(16) float4 staged_row[];
   __shared__ uint64_t bar;
@@ -197,6 +201,8 @@ SoftmaxStagedKernel(float *dst, const float *src, uint32_t rows, uint32_t cols, 
     }
     s = smdetail::BlockAll<smdetail::SumOp, kThreads>(s, buf);
     const float r = __frcp_rn(s);
+    const int hot = label != nullptr ? static_cast<int>(label[y]) : -1;
+    const int hot_item = hot >= 0 ? hot >> 2 : -1, hot_lane = hot & 3;
     float4 *out = reinterpret_cast<float4 *>(dst + y * ld_dst);
 #pragma unroll
     for (int k = 0; k < kItems; ++k) {
@@ -208,6 +214,12 @@ SoftmaxStagedKernel(float *dst, const float *src, uint32_t rows, uint32_t cols, 
           const float q0 = __fmul_rn(v[k][l], r);
           q[l] = __fmaf_rn(__fmaf_rn(-q0, s, v[k][l]), r, q0);
         }
+        if (static_cast<int>(item) == hot_item) {  // one group per row holds the label's column
+          q[0] = hot_lane == 0 ? __fsub_rn(q[0], 1.0f) : q[0];
+          q[1] = hot_lane == 1 ? __fsub_rn(q[1], 1.0f) : q[1];
+          q[2] = hot_lane == 2 ? __fsub_rn(q[2], 1.0f) : q[2];
+          q[3] = hot_lane == 3 ? __fsub_rn(q[3], 1.0f) : q[3];
+        }
         __stcs(out + item, make_float4(q[0], q[1], q[2], q[3]));
       }
     }
@@ -217,7 +229,8 @@ SoftmaxStagedKernel(float *dst, const float *src, uint32_t rows, uint32_t cols, 
 /*! \brief any row length: three sweeps over global memory, one CTA per row */
 template <int kThreads>
 __global__ void __launch_bounds__(kThreads)
-SoftmaxSweepKernel(float *dst, const float *src, uint32_t rows, uint32_t cols, int64_t ld_dst, int64_t ld_src) {
+SoftmaxSweepKernel(float *dst, const float *src, const float *label, uint32_t rows, uint32_t cols, int64_t ld_dst,
+                   int64_t ld_src) {
   __shared__ float buf[32];
   for (uint32_t y = blockIdx.x; y < rows; y += gridDim.x) {
     const float *in = src + y * ld_src;
@@ -232,24 +245,34 @@ SoftmaxSweepKernel(float *dst, const float *src, uint32_t rows, uint32_t cols, i
       s = __fadd_rn(s, e);
     }
     s = smdetail::BlockAll<smdetail::SumOp, kThreads>(s, buf);
-    for (uint32_t x = threadIdx.x; x < cols; x += kThreads) out[x] = __fdiv_rn(out[x], s);
+    const int hot = label != nullptr ? static_cast<int>(label[y]) : -1;
+    for (uint32_t x = threadIdx.x; x < cols; x += kThreads) {
+      const float q = __fdiv_rn(out[x], s);
+      out[x] = static_cast<int>(x) == hot ? __fsub_rn(q, 1.0f) : q;
+    }
   }
 }
 
 namespace smdetail {
 template <int kThreads, int kItems, int kLanes>
-inline void LaunchRow(float *dst, const float *src, uint32_t rows, uint32_t cols, int64_t ld_dst, int64_t ld_src,
-                      cudaStream_t stream) {
+inline void LaunchRow(float *dst, const float *src, const float *label, uint32_t rows, uint32_t cols, int64_t ld_dst,
+                      int64_t ld_src, cudaStream_t stream) {
   // persistent over rows only when there are more rows than a generous grid
   const uint32_t cap = static_cast<uint32_t>(gpu_rt::CurrentDevice().sm_count) * 64u;
   const uint32_t grid = rows < cap ? rows : cap;
-  SoftmaxRowKernel<kThreads, kItems, kLanes><<<grid, kThreads, 0, stream>>>(dst, src, rows, cols, ld_dst, ld_src);
+  SoftmaxRowKernel<kThreads, kItems, kLanes><<<grid, kThreads, 0, stream>>>(dst, src, label, rows, cols, ld_dst,
+                                                                            ld_src);
 }
 }  // namespace smdetail
 
-/*! \brief dst = softmax(src) row by row; fp32 */
+/*!
+ * \brief dst = softmax(src) row by row, fp32.  With `label` (one float per row holding a column
+ *  index) the gradient of the cross-entropy loss is produced in the same pass instead:
+ *  dst = softmax(src) - onehot(label), i.e. SoftmaxGrad(Softmax(src)) without writing and
+ *  re-reading the probabilities.
+ */
 inline void SoftmaxLaunch(float *dst, const float *src, int64_t rows, int64_t cols, int64_t ld_dst, int64_t ld_src,
-                          cudaStream_t stream) {
+                          cudaStream_t stream, const float *label = nullptr) {
   if (rows == 0 || cols == 0) return;
   CHECK_LT(rows, (int64_t(1) << 31));
   CHECK_LT(cols, (int64_t(1) << 31));
@@ -267,7 +290,7 @@ inline void SoftmaxLaunch(float *dst, const float *src, int64_t rows, int64_t co
   {                                                                                                               \
     auto kernel = SoftmaxStagedKernel<ITEMS>;                                                                     \
     MSHADOW_CUDA_CALL(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 128 * 1024));     \
-    kernel<<<sms, 1024, smem, stream>>>(dst, src, r, c, ld_dst, ld_src, status);                                  \
+    kernel<<<sms, 1024, smem, stream>>>(dst, src, label, r, c, ld_dst, ld_src, status);                                  \
   }
     if (n <= 1024) MSHADOW_B200_SOFTMAX_STAGED_(1)
     else if (n <= 2048) MSHADOW_B200_SOFTMAX_STAGED_(2)
@@ -276,23 +299,23 @@ inline void SoftmaxLaunch(float *dst, const float *src, int64_t rows, int64_t co
 #undef MSHADOW_B200_SOFTMAX_STAGED_
   } else if (vec && cols <= 32768) {
     const uint32_t n = c / 4;  // 16-byte items per row
-    if (n <= 32) LaunchRow<32, 1, 4>(dst, src, r, c, ld_dst, ld_src, stream);
-    else if (n <= 128) LaunchRow<128, 1, 4>(dst, src, r, c, ld_dst, ld_src, stream);
-    else if (n <= 256) LaunchRow<256, 1, 4>(dst, src, r, c, ld_dst, ld_src, stream);
-    else if (n <= 512) LaunchRow<256, 2, 4>(dst, src, r, c, ld_dst, ld_src, stream);
-    else if (n <= 1024) LaunchRow<256, 4, 4>(dst, src, r, c, ld_dst, ld_src, stream);
-    else if (n <= 2048) LaunchRow<512, 4, 4>(dst, src, r, c, ld_dst, ld_src, stream);
-    else if (n <= 4096) LaunchRow<1024, 4, 4>(dst, src, r, c, ld_dst, ld_src, stream);
-    else LaunchRow<1024, 8, 4>(dst, src, r, c, ld_dst, ld_src, stream);
+    if (n <= 32) LaunchRow<32, 1, 4>(dst, src, label, r, c, ld_dst, ld_src, stream);
+    else if (n <= 128) LaunchRow<128, 1, 4>(dst, src, label, r, c, ld_dst, ld_src, stream);
+    else if (n <= 256) LaunchRow<256, 1, 4>(dst, src, label, r, c, ld_dst, ld_src, stream);
+    else if (n <= 512) LaunchRow<256, 2, 4>(dst, src, label, r, c, ld_dst, ld_src, stream);
+    else if (n <= 1024) LaunchRow<256, 4, 4>(dst, src, label, r, c, ld_dst, ld_src, stream);
+    else if (n <= 2048) LaunchRow<512, 4, 4>(dst, src, label, r, c, ld_dst, ld_src, stream);
+    else if (n <= 4096) LaunchRow<1024, 4, 4>(dst, src, label, r, c, ld_dst, ld_src, stream);
+    else LaunchRow<1024, 8, 4>(dst, src, label, r, c, ld_dst, ld_src, stream);
   } else if (cols <= 8192) {
-    if (c <= 32) LaunchRow<32, 1, 1>(dst, src, r, c, ld_dst, ld_src, stream);
-    else if (c <= 128) LaunchRow<128, 1, 1>(dst, src, r, c, ld_dst, ld_src, stream);
-    else if (c <= 512) LaunchRow<256, 2, 1>(dst, src, r, c, ld_dst, ld_src, stream);
-    else if (c <= 2048) LaunchRow<256, 8, 1>(dst, src, r, c, ld_dst, ld_src, stream);
-    else LaunchRow<512, 16, 1>(dst, src, r, c, ld_dst, ld_src, stream);
+    if (c <= 32) LaunchRow<32, 1, 1>(dst, src, label, r, c, ld_dst, ld_src, stream);
+    else if (c <= 128) LaunchRow<128, 1, 1>(dst, src, label, r, c, ld_dst, ld_src, stream);
+    else if (c <= 512) LaunchRow<256, 2, 1>(dst, src, label, r, c, ld_dst, ld_src, stream);
+    else if (c <= 2048) LaunchRow<256, 8, 1>(dst, src, label, r, c, ld_dst, ld_src, stream);
+    else LaunchRow<512, 16, 1>(dst, src, label, r, c, ld_dst, ld_src, stream);
   } else {
     const uint32_t cap = static_cast<uint32_t>(gpu_rt::CurrentDevice().sm_count) * 16u;
-    SoftmaxSweepKernel<512><<<r < cap ? r : cap, 512, 0, stream>>>(dst, src, r, c, ld_dst, ld_src);
+    SoftmaxSweepKernel<512><<<r < cap ? r : cap, 512, 0, stream>>>(dst, src, label, r, c, ld_dst, ld_src);
   }
   MSHADOW_CUDA_POST_KERNEL_CHECK(Softmax);
 }

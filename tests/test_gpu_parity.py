@@ -177,6 +177,29 @@ def test_softmax(lib, rows, cols, pad):
     assert_bits(host(s), got)
 
 
+@pytest.mark.parametrize("rows,cols,pad", [(3, 5, 0), (9, 1000, 0), (4, 33, 3), (160, 8000, 0), (2, 40000, 0)])
+def test_softmax_grad_fused(lib, rows, cols, pad):
+    """One pass Softmax + SoftmaxGrad must equal the two library calls it replaces, exactly,
+    and the CPU composition within the softmax tolerance."""
+    rng = np.random.default_rng(rows + cols)
+    logits = (2.0 * rng.standard_normal((rows, cols))).astype(np.float32)
+    label = rng.integers(0, cols, rows).astype(np.float32)
+    label[0], label[-1] = 0, cols - 1
+    fused = dev(np.zeros_like(logits), pad)
+    lib.softmax_grad_fused(fused, dev(logits, pad), dev(label))
+    prob = dev(np.zeros_like(logits), pad)
+    lib.softmax(prob, dev(logits, pad))
+    two = dev(np.zeros_like(logits), pad)
+    lib.softmax_grad(two, prob, dev(label))
+    assert_bits(host(fused), host(two))
+    want = orc.softmax_grad(np.zeros_like(logits), orc.softmax(np.zeros_like(logits), logits), label)
+    err = np.abs(host(fused).astype(np.float64) - want) / np.maximum(np.abs(want), 1e-30)
+    hit = np.zeros(want.shape, bool)
+    hit[np.arange(rows), label.astype(int)] = True
+    assert err[~hit & (want > 0)].max() <= 1e-5 if (~hit & (want > 0)).any() else True
+    assert np.abs(host(fused)[hit] - want[hit]).max() <= 1e-5  # p - 1: absolute, the scale is 1
+
+
 @pytest.mark.parametrize("mode", [0, 1, 2, 3])
 @pytest.mark.parametrize("rows,cols,pad", [(3, 5, 0), (9, 1000, 0), (4, 33, 3), (6, 32000, 0), (64, 260, 4)])
 def test_softmax_grad(lib, mode, rows, cols, pad):
