@@ -146,6 +146,97 @@ def cpu_step(chk, t4, m, out512, out4096):
     chk.reduce_keep_lowest(out4096, m)
 
 
+def reference_gpu_table(peak):
+    """The reference's OWN CUDA kernels (oracle/_ref/libmshadow_ref_gpu.so: the unmodified
+    mshadow headers recompiled for sm_100a) timed on this GPU at the BASELINE configs, with the
+    same algorithmic byte counts as the `kernels` table of the other arm.  Returns None where
+    there is no GPU or the library was not built.  None of this repository's kernels run here:
+    inputs come from torch, the sorted index list from torch.sort."""
+    import ctypes as C
+    path = os.path.join(ROOT, "oracle", "_ref", "libmshadow_ref_gpu.so")
+    try:
+        import torch
+    except Exception:
+        return None
+    if not os.path.exists(path) or not torch.cuda.is_available():
+        return None
+    dll = C.CDLL(path)
+    dll.refgpu_last_error.restype = C.c_char_p
+    vp, i64 = C.c_void_p, C.c_int64
+
+    def call(name, *args):
+        conv = [vp(a.data_ptr()) if hasattr(a, "data_ptr") else a for a in args]
+        if getattr(dll, name)(*conv, None) != 0:
+            raise RuntimeError(dll.refgpu_last_error().decode("utf-8", "replace"))
+
+    for name, types in {
+        "refgpu_expr_case0": [vp] * 5 + [i64] * 2, "refgpu_sum_rows": [vp] * 2 + [i64] * 2,
+        "refgpu_sumall_except_dim1": [vp] * 2 + [i64] * 4, "refgpu_softmax": [vp] * 2 + [i64] * 2,
+        "refgpu_softmax_grad": [vp] * 3 + [i64] * 2, "refgpu_pool_max": [vp] * 2 + [i64] * 3 + [C.c_int] * 4,
+        "refgpu_unpool_max": [vp] * 4 + [i64] * 3 + [C.c_int] * 4, "refgpu_chpool_sum": [vp] * 2 + [i64] * 4 + [C.c_int],
+        "refgpu_addtakegrad_largebatch": [vp] * 4 + [i64] * 3,
+    }.items():
+        getattr(dll, name).argtypes = types + [vp]
+        getattr(dll, name).restype = C.c_int
+    dev = torch.device("cuda")
+    g = torch.Generator(device=dev)
+    g.manual_seed(1)
+    rows = []
+
+    def run(key, label, nbytes, fn, iters):
+        try:
+            seconds = time_kernel(torch, fn, iters=iters, warm=2)
+            gbs = nbytes / seconds / 1e9
+            rows.append({"key": key, "kernel": label, "ms": seconds * 1e3, "GBps": round(gbs, 1),
+                         "frac_of_measured_peak": round(gbs / peak, 3)})
+        except Exception as e:  # the reference refused the shape (its CHECKs throw)
+            rows.append({"key": key, "kernel": label, "error": str(e)[:200]})
+
+    n = 8192
+    A, B, Cm = (torch.rand(n, n, device=dev, generator=g) * 2 - 1 for _ in range(3))
+    bias, D = torch.randn(n, device=dev, generator=g), torch.empty(n, n, device=dev)
+    run("map", "C1 map", 16 * n * n + 4 * n, lambda: call("refgpu_expr_case0", D, A, B, Cm, bias, n, n), 10)
+    del A, B, Cm, D
+    T = torch.randn(C2A_SHAPE, device=dev, generator=g)
+    o = torch.zeros(C2A_SHAPE[1], device=dev)
+    run("keep_highdim", "C2a sumall_except_dim<1>", 4 * T.numel(),
+        lambda: call("refgpu_sumall_except_dim1", o, T, *C2A_SHAPE), 10)
+    del T
+    M = torch.randn(C2B_SHAPE, device=dev, generator=g)
+    o2 = torch.zeros(C2B_SHAPE[1], device=dev)
+    run("keep_lowest", "C2b sum_rows", 4 * M.numel(), lambda: call("refgpu_sum_rows", o2, M, *C2B_SHAPE), 10)
+    del M
+    r, c = 32768, 32000
+    L = torch.randn(r, c, device=dev, generator=g) * 2
+    P = torch.empty(r, c, device=dev)
+    run("softmax", "C3 Softmax", 8 * r * c, lambda: call("refgpu_softmax", P, L, r, c), 5)
+    lab = torch.randint(0, c, (r,), device=dev, generator=g).float()
+    run("softmax_grad", "C3 SoftmaxGrad", 8 * r * c, lambda: call("refgpu_softmax_grad", L, P, lab, r, c), 5)
+    del L, P
+    planes = 256 * 256
+    X = torch.rand(planes, 56, 56, device=dev, generator=g)
+    Pm = torch.empty(planes, 27, 27, device=dev)
+    run("pool", "C4 pool<max> 3x3/2", 4 * X.numel() + 4 * Pm.numel(),
+        lambda: call("refgpu_pool_max", Pm, X, planes, 56, 56, 3, 3, 2, 2), 5)
+    gP = torch.rand(planes, 27, 27, device=dev, generator=g)
+    G = torch.empty_like(X)
+    run("unpool", "C4 unpool<max> 3x3/2", 8 * X.numel() + 8 * Pm.numel(),
+        lambda: call("refgpu_unpool_max", G, X, Pm, gP, planes, 56, 56, 3, 3, 2, 2), 5)
+    run("chpool", "C4 chpool<sum> 5", 8 * X.numel(), lambda: call("refgpu_chpool_sum", G, X, 256, 256, 56, 56, 5), 5)
+    del X, Pm, gP, G
+    k, d, nidx = 262144, 1024, 1 << 20
+    p = (np.arange(k) + 1.0) ** -1.1
+    idx = np.random.default_rng(5).choice(k, size=nidx, p=p / p.sum()).astype(np.int32)
+    uniq = int(np.unique(idx).size)
+    keys, order = torch.sort(torch.from_numpy(idx).to(dev), stable=True)
+    keys, order = keys.contiguous(), order.to(torch.int32).contiguous()
+    src = torch.randn(nidx, d, device=dev, generator=g)
+    table = torch.zeros(k, d, device=dev)
+    run("addtakegrad", "C5 AddTakeGradLargeBatch", 4 * nidx * d + 8 * nidx + 8 * uniq * d,
+        lambda: call("refgpu_addtakegrad_largebatch", table, keys, order, src, k, d, nidx), 3)
+    return rows
+
+
 def cpu_reference_arm(args):
     """Times sumall_except_dim<1> + sum_rows of the reference CPU path on the host cores.
 
@@ -188,6 +279,12 @@ def cpu_reference_arm(args):
         "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
+    if not args.no_table:
+        # second baseline: the reference's own CUDA kernels recompiled for this GPU (not part of `value`)
+        peak, _ = measured_peak()
+        table = reference_gpu_table(peak)
+        if table is not None:
+            line["reference_gpu_kernels"] = table
     print(json.dumps(line), flush=True)
 
 
@@ -285,16 +382,38 @@ def kernel_cases(lib, torch, small=False):
     yield ("sort_by_key", "SortByKey %d int32 pairs" % nidx, 16 * nidx, nidx,
            lambda: lib.sort_by_key(k2, v2, True), 10)
     del src, table
-    # gradient of the channel pooling (generic map kernel, window loop inside the plan)
+    # gradient of the channel pooling.  For red::sum the mask PartialGrad is the constant 1, so only
+    # the pooled gradient is read (8 B/elem); for red::maximum src and pooled are compared as well.
     imgs = 32 if small else 256
     X4 = torch.rand(imgs, 256, 56, 56, device=dev, generator=g)
     P4 = torch.empty_like(X4)
     lib.chpool(P4, X4, 5)
     gP4 = torch.rand(imgs, 256, 56, 56, device=dev, generator=g)
     G4 = torch.empty_like(X4)
-    yield ("ch_unpool", "ch_unpool<sum> nsize 5 (%d,256,56,56)" % imgs, 16 * X4.numel(), X4.numel(),
+    yield ("ch_unpool", "ch_unpool<sum> nsize 5 (%d,256,56,56)" % imgs, 8 * X4.numel(), X4.numel(),
            lambda: lib.ch_unpool(G4, X4, P4, gP4, 5), 10)
+    lib.chpool(P4, X4, 5, reducer=1)
+    yield ("ch_unpool_max", "ch_unpool<max> nsize 5 (%d,256,56,56)" % imgs, 16 * X4.numel(), X4.numel(),
+           lambda: lib.ch_unpool(G4, X4, P4, gP4, 5, reducer=1), 10)
     del X4, P4, gP4, G4
+    # softmax over the middle axis (per-pixel classification shape: 21 classes, 256x256 positions)
+    b3, c3, n3 = (16 if small else 64), 21, 256 * 256
+    L3 = torch.randn(b3, c3, n3, device=dev, generator=g) * 2
+    P3 = torch.empty_like(L3)
+    yield ("softmax3d", "Softmax 3-D (%d,%d,%d)" % (b3, c3, n3), 8 * L3.numel(), L3.numel(),
+           lambda: lib.softmax3d(P3, L3), 10)
+    lab3 = torch.randint(0, c3, (b3, n3), device=dev, generator=g).float()
+    yield ("softmax_grad3d", "SoftmaxGrad 3-D (%d,%d,%d)" % (b3, c3, n3), 8 * L3.numel() + 4 * lab3.numel(),
+           L3.numel(), lambda: lib.softmax_grad3d(L3, P3, lab3), 10)
+    del L3, P3, lab3
+    # IndexFill: 2^18 distinct rows of 1024 floats written into a 262144-row table
+    kf, df, nf = 262144, 1024, (1 << 16 if small else 1 << 18)
+    fidx = torch.randperm(kf, device=dev, generator=g)[:nf].to(torch.int32)
+    fsrc = torch.randn(nf, df, device=dev, generator=g)
+    ftab = torch.zeros(kf, df, device=dev)
+    yield ("index_fill", "IndexFill %d rows of %d into %dx%d" % (nf, df, kf, df), 8 * nf * df + 8 * nf + 4 * kf,
+           nf * df, lambda: lib.index_fill(ftab, fidx, fsrc), 10)
+    del fidx, fsrc, ftab
     torch.cuda.empty_cache()
 
 

@@ -193,6 +193,28 @@ int msb_addtakegrad_largebatch_f32_i32(float *dst, const int32_t *sorted, const 
 /* SortByKey(keys, values, is_ascend), stable: mshadow/tensor_gpu-inl.h:231-235 */
 int msb_sort_by_key_i32(int32_t *keys, int32_t *values, int64_t n, int ascend,
                         msb_stream_t stream);
+/* VectorizedSort(values, segments): values sorted ascending inside each run of equal
+   `segments` (ascending on entry), two stable pair sorts: mshadow/tensor.h:905-915,
+   mshadow/tensor_cpu-inl.h:562-567 */
+int msb_vectorized_sort_f32_i32(float *values, int32_t *segments, int64_t n, msb_stream_t stream);
+/* IndexFill(dst, index, src): dst[index[y]] = src[y], dst is k x d and src nidx x d, both
+   contiguous: mshadow/tensor_gpu-inl.h:237-242.  A row named by several entries keeps the last
+   one (the CPU evaluator's outcome, mshadow/tensor_cpu-inl.h:520-529); entries outside [0, k)
+   are skipped. */
+int msb_index_fill_f32_i32(float *dst, const int32_t *index, const float *src, int64_t k,
+                           int64_t d, int64_t nidx, msb_stream_t stream);
+
+/* Softmax(Tensor<gpu,3>): softmax over the middle axis of (batch, classes, positions);
+   ld_* = pitch of the last axis: mshadow/tensor_gpu-inl.h:163-167 */
+int msb_softmax3d_f32(float *dst, const float *src, int64_t batch, int64_t classes, int64_t npos,
+                      int64_t ld_dst, int64_t ld_src, msb_stream_t stream);
+/* SoftmaxGrad / SmoothSoftmaxGrad on (batch, classes, positions) with label (batch, positions);
+   mode as for msb_softmax_grad_f32: mshadow/tensor_gpu-inl.h:201-214,
+   mshadow/tensor_cpu-inl.h:370-462 */
+int msb_softmax_grad3d_f32(float *dst, const float *src, const float *label, int64_t batch,
+                           int64_t classes, int64_t npos, int64_t ld_dst, int64_t ld_src,
+                           int64_t ld_label, int mode, float ignore_label, float alpha,
+                           msb_stream_t stream);
 
 #ifdef __cplusplus
 }

@@ -66,6 +66,10 @@ _SIGNATURES = {
     "msb_addtakegrad_f32_i32": [vp, vp, vp, i64, i64, i64, i64, i64, vp],
     "msb_addtakegrad_largebatch_f32_i32": [vp, vp, vp, vp, i64, i64, i64, vp],
     "msb_sort_by_key_i32": [vp, vp, i64, cint, vp],
+    "msb_vectorized_sort_f32_i32": [vp, vp, i64, vp],
+    "msb_index_fill_f32_i32": [vp, vp, vp, i64, i64, i64, vp],
+    "msb_softmax3d_f32": [vp, vp, i64, i64, i64, i64, i64, vp],
+    "msb_softmax_grad3d_f32": [vp, vp, vp, i64, i64, i64, i64, i64, i64, cint, f32, f32, vp],
 }
 
 
@@ -235,6 +239,26 @@ class Library:
     def sort_by_key(self, keys, values, ascend=True, stream=None):
         self.call("msb_sort_by_key_i32", _ptr(keys), _ptr(values), keys.shape[0], int(ascend), stream)
         return keys, values
+
+    def vectorized_sort(self, values, segments, stream=None):
+        self.call("msb_vectorized_sort_f32_i32", _ptr(values), _ptr(segments), values.shape[0], stream)
+        return values, segments
+
+    def index_fill(self, dst, index, src, stream=None):
+        k, d = dst.shape
+        self.call("msb_index_fill_f32_i32", _ptr(dst), _ptr(index), _ptr(src), k, d, index.shape[0], stream)
+        return dst
+
+    def softmax3d(self, dst, src, stream=None):
+        batch, classes, npos = src.shape
+        self.call("msb_softmax3d_f32", _ptr(dst), _ptr(src), batch, classes, npos, _ld(dst), _ld(src), stream)
+        return dst
+
+    def softmax_grad3d(self, dst, src, label, mode=0, ignore_label=0.0, alpha=0.0, stream=None):
+        batch, classes, npos = src.shape
+        self.call("msb_softmax_grad3d_f32", _ptr(dst), _ptr(src), _ptr(label), batch, classes, npos, _ld(dst),
+                  _ld(src), _ld(label), mode, ignore_label, alpha, stream)
+        return dst
 
 
 _lib = None

@@ -461,4 +461,69 @@ int msb_sort_by_key_i32(int32_t *keys, int32_t *values, int64_t n, int ascend, m
   MSB_GUARD_END
 }
 
+int msb_softmax3d_f32(float *dst, const float *src, int64_t batch, int64_t classes, int64_t npos, int64_t ld_dst,
+                      int64_t ld_src, msb_stream_t stream) {
+  MSB_REQUIRE(FitsIndex(batch) && FitsIndex(classes) && FitsIndex(npos) && FitsIndex(batch * classes) &&
+                  FitsIndex(batch * classes * npos) && ld_dst >= npos && ld_src >= npos,
+              MSB_ERR_SHAPE, "extent out of range");
+  if (batch == 0 || classes == 0 || npos == 0) return MSB_OK;
+  MSB_REQUIRE(dst && src, MSB_ERR_ARGUMENT, "null pointer");
+  MSB_GUARD_BEGIN
+  BorrowedStream st(stream);
+  Tensor<gpu, 3, float> d(dst, Shape3(batch, classes, npos), static_cast<index_t>(ld_dst), st.get());
+  const Tensor<gpu, 3, float> s(const_cast<float *>(src), Shape3(batch, classes, npos), static_cast<index_t>(ld_src),
+                                st.get());
+  Softmax(d, s);
+  MSB_GUARD_END
+}
+
+int msb_softmax_grad3d_f32(float *dst, const float *src, const float *label, int64_t batch, int64_t classes,
+                           int64_t npos, int64_t ld_dst, int64_t ld_src, int64_t ld_label, int mode,
+                           float ignore_label, float alpha, msb_stream_t stream) {
+  MSB_REQUIRE(mode >= 0 && mode <= 3, MSB_ERR_ARGUMENT, "mode must be 0..3");
+  MSB_REQUIRE(FitsIndex(batch) && FitsIndex(classes) && FitsIndex(npos) && FitsIndex(batch * classes) &&
+                  FitsIndex(batch * classes * npos) && ld_dst >= npos && ld_src >= npos && ld_label >= npos,
+              MSB_ERR_SHAPE, "extent out of range");
+  if (batch == 0 || classes == 0 || npos == 0) return MSB_OK;
+  MSB_REQUIRE(dst && src && label, MSB_ERR_ARGUMENT, "null pointer");
+  MSB_GUARD_BEGIN
+  BorrowedStream st(stream);
+  const Tensor<gpu, 3, float> d(dst, Shape3(batch, classes, npos), static_cast<index_t>(ld_dst), st.get());
+  const Tensor<gpu, 3, float> s(const_cast<float *>(src), Shape3(batch, classes, npos), static_cast<index_t>(ld_src),
+                                st.get());
+  const G2 l = Mat(label, batch, npos, ld_label, st.get());
+  switch (mode) {
+    case 0: SoftmaxGrad(d, s, l); break;
+    case 1: SmoothSoftmaxGrad(d, s, l, alpha); break;
+    case 2: SoftmaxGrad(d, s, l, ignore_label); break;
+    default: SmoothSoftmaxGrad(d, s, l, ignore_label, alpha); break;
+  }
+  MSB_GUARD_END
+}
+
+int msb_index_fill_f32_i32(float *dst, const int32_t *index, const float *src, int64_t k, int64_t d, int64_t nidx,
+                           msb_stream_t stream) {
+  MSB_REQUIRE(FitsIndex(k) && FitsIndex(d) && FitsIndex(nidx) && FitsIndex(k * d) && FitsIndex(nidx * d),
+              MSB_ERR_SHAPE, "extent out of range");
+  if (nidx == 0 || d == 0 || k == 0) return MSB_OK;
+  MSB_REQUIRE(dst && index && src, MSB_ERR_ARGUMENT, "null pointer");
+  MSB_GUARD_BEGIN
+  BorrowedStream st(stream);
+  const Tensor<gpu, 1, int32_t> idx(const_cast<int32_t *>(index), Shape1(nidx), nidx, st.get());
+  IndexFill(Mat(dst, k, d, d, st.get()), idx, Mat(src, nidx, d, d, st.get()));
+  MSB_GUARD_END
+}
+
+int msb_vectorized_sort_f32_i32(float *values, int32_t *segments, int64_t n, msb_stream_t stream) {
+  MSB_REQUIRE(FitsIndex(n), MSB_ERR_SHAPE, "extent out of range");
+  if (n == 0) return MSB_OK;
+  MSB_REQUIRE(values && segments, MSB_ERR_ARGUMENT, "null pointer");
+  MSB_GUARD_BEGIN
+  BorrowedStream st(stream);
+  Tensor<gpu, 1, float> v(values, Shape1(n), n, st.get());
+  Tensor<gpu, 1, int32_t> s(segments, Shape1(n), n, st.get());
+  VectorizedSort(v, s);
+  MSB_GUARD_END
+}
+
 }  // extern "C"

@@ -370,6 +370,25 @@ struct MapDispatch<sv::saveto, Tensor<gpu, dim, float>,
   }
 };
 
+// `dst = ch_unpool<Reducer>(src, pooled, grad, nsize)` on dense fp32 GPU tensors
+template <typename Reducer, int dim>
+struct MapDispatch<sv::saveto, Tensor<gpu, dim, float>,
+                   expr::ChannelUnpoolingExp<Reducer, Tensor<gpu, dim, float>, float, dim>, float, dim> {
+  typedef expr::ChannelUnpoolingExp<Reducer, Tensor<gpu, dim, float>, float, dim> E;
+  inline static void Run(Tensor<gpu, dim, float> *dst, const E &e, Shape<dim> dshape, cudaStream_t stream) {
+    const Tensor<gpu, dim, float> &src = e.data_src_, &pooled = e.data_pooled_, &grad = e.grad_pooled_;
+    const index_t images = dshape.ProdShape(0, dim - 3);
+    if (ChannelUnpoolSupported(e.nsize_, e.kstride_, e.pad_) && e.pchannel_ == dshape[dim - 3] &&
+        src.CheckContiguous() && pooled.CheckContiguous() && grad.CheckContiguous() && dst->CheckContiguous() &&
+        images < 65536) {
+      ChannelUnpoolLaunch<Reducer>(dst->dptr_, src.dptr_, pooled.dptr_, grad.dptr_, images, dshape[dim - 3],
+                                   dshape[dim - 2], dshape[dim - 1], e.nsize_, stream);
+    } else {
+      MapGeneric<sv::saveto, float>(dst, e, dshape, stream);
+    }
+  }
+};
+
 }  // namespace cuda
 #endif  // MSHADOW_USE_CUDA && __CUDACC__
 

@@ -297,6 +297,69 @@ inline void AddTakeGradLaunch(float *dst, int64_t ld_dst, const int32_t *index, 
                              stream);
 }
 
+// ----------------------------------------------------------------------------------------
+// IndexFill: dst[index[y]] = src[y].  The reference's kernel (mshadow/cuda/tensor_gpu-inl.cuh:
+// 736-782) lets all batch entries write at once, so a row named twice ends up with either
+// source.  Here the CPU's outcome (mshadow/tensor_cpu-inl.h:520-529: entries in batch order,
+// the later one stays) is reproduced: a first pass records, per table row, the last batch entry
+// that names it; the second pass copies only those entries.
+// ----------------------------------------------------------------------------------------
+
+/*! \brief last[index[y]] = max(last[index[y]], y); `last` starts at -1; rows outside the table are skipped */
+template <typename IndexType>
+__global__ void __launch_bounds__(256)
+IndexFillOwnerKernel(int32_t *last, const IndexType *index, uint32_t n, int32_t k) {
+  const uint32_t y = blockIdx.x * 256 + threadIdx.x;
+  if (y >= n) return;
+  const int32_t j = static_cast<int32_t>(index[y]);
+  if (j >= 0 && j < k) atomicMax(last + j, static_cast<int32_t>(y));
+}
+
+/*! \brief one CTA row per batch entry (grid-stride); the entry copies its source row if it is the last one naming that table row */
+template <int kLanes>
+__global__ void __launch_bounds__(256)
+IndexFillCopyKernel(float *dst, int64_t ld_dst, const int32_t *last, const int32_t *index, const float *src,
+                    int64_t ld_src, uint32_t n, uint32_t items, int32_t k) {
+  for (uint32_t y = blockIdx.x; y < n; y += gridDim.x) {
+    const int32_t j = index[y];
+    if (j < 0 || j >= k || last[j] != static_cast<int32_t>(y)) continue;
+    const float *in = src + y * ld_src;
+    float *out = dst + j * ld_dst;
+    for (uint32_t i = threadIdx.x; i < items; i += 256) {
+      if (kLanes == 4) {
+        reinterpret_cast<float4 *>(out)[i] = __ldcs(reinterpret_cast<const float4 *>(in) + i);
+      } else {
+        out[i] = __ldcs(in + i);
+      }
+    }
+  }
+}
+
+/*! \brief dst[index[y]] = src[y] with the outcome of a serial walk over y; indices outside [0, k) are ignored */
+inline void IndexFillLaunch(float *dst, int64_t ld_dst, const int32_t *index, const float *src, int64_t ld_src,
+                            int64_t k, int64_t n, int64_t width, cudaStream_t stream) {
+  if (n == 0 || width == 0 || k == 0) return;
+  CHECK_LT(n, (int64_t(1) << 31));
+  CHECK_LT(k, (int64_t(1) << 31));
+  int32_t *last = static_cast<int32_t *>(gpu_rt::Scratch::Get(stream, k * sizeof(int32_t)));
+  MSHADOW_CUDA_CALL(cudaMemsetAsync(last, 0xff, k * sizeof(int32_t), stream));  // every entry -1
+  const uint32_t un = static_cast<uint32_t>(n);
+  IndexFillOwnerKernel<int32_t><<<gpu_rt::CeilDiv(n, 256), 256, 0, stream>>>(last, index, un, static_cast<int32_t>(k));
+  MSHADOW_CUDA_POST_KERNEL_CHECK(IndexFillOwnerKernel);
+  const bool vec = width % 4 == 0 && ld_src % 4 == 0 && ld_dst % 4 == 0 &&
+                   reinterpret_cast<uintptr_t>(src) % 16 == 0 && reinterpret_cast<uintptr_t>(dst) % 16 == 0;
+  const int cap = gpu_rt::CurrentDevice().sm_count * 8;
+  const int grid = n < cap ? static_cast<int>(n) : cap;
+  if (vec) {
+    IndexFillCopyKernel<4><<<grid, 256, 0, stream>>>(dst, ld_dst, last, index, src, ld_src, un,
+                                                    static_cast<uint32_t>(width / 4), static_cast<int32_t>(k));
+  } else {
+    IndexFillCopyKernel<1><<<grid, 256, 0, stream>>>(dst, ld_dst, last, index, src, ld_src, un,
+                                                    static_cast<uint32_t>(width), static_cast<int32_t>(k));
+  }
+  MSHADOW_CUDA_POST_KERNEL_CHECK(IndexFillCopyKernel);
+}
+
 }  // namespace cuda
 }  // namespace mshadow
 #endif  // MSHADOW_GPU_EMBED_CUH_

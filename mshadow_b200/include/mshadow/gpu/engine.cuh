@@ -188,6 +188,40 @@ inline void SmoothSoftmaxGrad(const Tensor<gpu, 2, float> &dst, const Tensor<gpu
                           ignore_label, alpha, Stream<gpu>::GetStream(dst.stream_));
 }
 
+/*! \brief softmax over the middle axis of (batch, classes, positions); mshadow/tensor_gpu-inl.h:163-167 */
+inline void Softmax(Tensor<gpu, 3, float> dst, const Tensor<gpu, 3, float> &src) {
+  CHECK_EQ(dst.shape_, src.shape_) << "Softmax: shape mismatch";
+  cuda::Softmax3DLaunch(dst.dptr_, src.dptr_, dst.size(0), dst.size(1), dst.size(2), dst.stride_, src.stride_,
+                        Stream<gpu>::GetStream(dst.stream_));
+}
+namespace cuda {
+inline void SoftmaxGrad3DGo(const Tensor<gpu, 3, float> &dst, const Tensor<gpu, 3, float> &src,
+                            const Tensor<gpu, 2, float> &label, int mode, float ignore_label, float alpha) {
+  CHECK_EQ(dst.shape_, src.shape_) << "SoftmaxGrad: shape mismatch";
+  CHECK_EQ(dst.size(0), label.size(0)) << "SoftmaxGrad: label shape mismatch";
+  CHECK_EQ(dst.size(2), label.size(1)) << "SoftmaxGrad: label shape mismatch";
+  SoftmaxGrad3DLaunch(dst.dptr_, src.dptr_, label.dptr_, dst.size(0), dst.size(1), dst.size(2), dst.stride_,
+                      src.stride_, label.stride_, mode, ignore_label, alpha, Stream<gpu>::GetStream(dst.stream_));
+}
+}  // namespace cuda
+/*! \brief 3-D gradient forms, label(y, n) per position; mshadow/tensor_gpu-inl.h:201-214, tensor_cpu-inl.h:370-462 */
+inline void SoftmaxGrad(const Tensor<gpu, 3, float> &dst, const Tensor<gpu, 3, float> &src,
+                        const Tensor<gpu, 2, float> &label) {
+  cuda::SoftmaxGrad3DGo(dst, src, label, 0, 0.0f, 0.0f);
+}
+inline void SoftmaxGrad(const Tensor<gpu, 3, float> &dst, const Tensor<gpu, 3, float> &src,
+                        const Tensor<gpu, 2, float> &label, const float &ignore_label) {
+  cuda::SoftmaxGrad3DGo(dst, src, label, 2, ignore_label, 0.0f);
+}
+inline void SmoothSoftmaxGrad(const Tensor<gpu, 3, float> &dst, const Tensor<gpu, 3, float> &src,
+                              const Tensor<gpu, 2, float> &label, const float alpha) {
+  cuda::SoftmaxGrad3DGo(dst, src, label, 1, 0.0f, alpha);
+}
+inline void SmoothSoftmaxGrad(const Tensor<gpu, 3, float> &dst, const Tensor<gpu, 3, float> &src,
+                              const Tensor<gpu, 2, float> &label, const float &ignore_label, const float alpha) {
+  cuda::SoftmaxGrad3DGo(dst, src, label, 3, ignore_label, alpha);
+}
+
 /*!
  * \brief dst = Softmax(logits) - onehot(label) in one pass over memory: what
  *  `Softmax(p, logits); SoftmaxGrad(dst, p, label);` computes, for loss layers that only
@@ -221,12 +255,37 @@ inline void AddTakeGradLargeBatch(Tensor<gpu, 2, float> dst, const Tensor<gpu, 1
 }
 
 template <typename KDType, typename VDType>
-inline void SortByKey(Tensor<gpu, 1, KDType> keys, Tensor<gpu, 1, VDType> values, bool is_ascend) {
+inline void SortByKey(Tensor<gpu, 1, KDType> keys, Tensor<gpu, 1, VDType> values, bool is_ascend = true) {
   CHECK_EQ(keys.CheckContiguous(), true);
   CHECK_EQ(values.CheckContiguous(), true);
   CHECK_EQ(keys.size(0), values.size(0)) << "The sizes of key/value are not equal! keys_size: " << keys.size(0)
                                          << "values_size: " << values.size(0);
   cuda::SortPairsLaunch(keys.dptr_, values.dptr_, keys.size(0), is_ascend, Stream<gpu>::GetStream(keys.stream_));
+}
+
+/*!
+ * \brief dst[index[y]] = src[y] (mshadow/tensor_gpu-inl.h:237-242).  Where several entries name one
+ *  row the result is the CPU's (the last entry stays), not the reference kernel's race.
+ */
+inline void IndexFill(Tensor<gpu, 2, float> dst, const Tensor<gpu, 1, int32_t> &index,
+                      const Tensor<gpu, 2, float> &src) {
+  CHECK_EQ(dst.CheckContiguous(), true);
+  CHECK_EQ(index.CheckContiguous(), true);
+  CHECK_EQ(src.CheckContiguous(), true);
+  CHECK_EQ(dst.size(1), src.size(1)) << "IndexFill: shape mismatch";
+  CHECK_EQ(index.size(0), src.size(0)) << "IndexFill: shape mismatch";
+  cuda::IndexFillLaunch(dst.dptr_, dst.stride_, index.dptr_, src.dptr_, src.stride_, dst.size(0), index.size(0),
+                        dst.size(1), Stream<gpu>::GetStream(dst.stream_));
+}
+
+/*!
+ * \brief sort `values` inside each run of equal `segments` (ascending on entry) by two stable
+ *  pair sorts, as mshadow/tensor_cpu-inl.h:562-567 does on either device
+ */
+template <typename VDType, typename SDType>
+inline void VectorizedSort(Tensor<gpu, 1, VDType> values, Tensor<gpu, 1, SDType> segments) {
+  SortByKey(values, segments, true);
+  SortByKey(segments, values, true);
 }
 
 }  // namespace mshadow

@@ -355,6 +355,89 @@ ChannelPoolKernel(float *dst, const float *src, uint32_t channels, uint32_t plan
 }
 
 /*!
+ * \brief gradient of the channel-window pooling above (ch_unpool(src, pooled, grad, nsize): stride
+ *  1, pad NSIZE/2, pooled tensor with as many channels as src).  Source channel c collects
+ *  PartialGrad(src(c), pooled(cc)) * grad(cc) over cc = c - pad .. c + pad inside the tensor, in
+ *  ascending cc from zero, with one rounding per product and per sum, as the window loop of
+ *  mshadow/extension/channel_unpool.h:102-133 does.  Same march as ChannelPoolKernel: a thread
+ *  owns kLanes adjacent pixels, keeps the last NSIZE pooled and gradient values (and the source
+ *  values on their way) in registers, and reads every element from HBM once apart from the
+ *  NSIZE-1 halo channels per segment.  Channels outside the tensor enter as gradient +0, which
+ *  adds nothing.
+ */
+template <typename Reducer, int NSIZE, int kLanes>
+__global__ void __launch_bounds__(kPoolThreads, 2)
+ChannelUnpoolKernel(float *dst, const float *src, const float *pooled, const float *gpooled, uint32_t channels,
+                    uint32_t plane, uint32_t groups_per_image, uint32_t total_items, gpu_rt::FastDiv image_of_item,
+                    uint32_t seg_len) {
+  constexpr int kPad = NSIZE / 2;
+  // loads are issued this many channels before they are needed (for red::sum PartialGrad is the
+  // constant 1, so the compiler drops the source and pooled rings and only the gradient is read)
+  constexpr int kAhead = MSHADOW_B200_CHPOOL_AHEAD;
+  constexpr int kRing = NSIZE + kAhead;
+  const uint32_t item = blockIdx.x * kPoolThreads + threadIdx.x;
+  if (item >= total_items) return;
+  const uint32_t image_idx = image_of_item.Quot(item);
+  const uint32_t pix = (item - image_idx * groups_per_image) * kLanes;
+  const uint32_t c_begin = blockIdx.y * seg_len;
+  const uint32_t c_end = min(channels, c_begin + seg_len);
+  const int64_t image = static_cast<int64_t>(image_idx) * channels * plane + pix;
+  const float *in = src + image, *pin = pooled + image, *gin = gpooled + image;
+  float *out = dst + image;
+  float rs[kRing][kLanes], rp[kRing][kLanes], rg[kRing][kLanes];
+  const int64_t load_end = min(static_cast<int64_t>(channels), static_cast<int64_t>(c_end) + kPad);
+  auto load = [&](int slot, int64_t c) {
+    if (c >= 0 && c < load_end) {
+      // a halo channel contributes its pooled value and gradient only: its source value is not read
+      const bool own = c >= static_cast<int64_t>(c_begin) && c < static_cast<int64_t>(c_end);
+      if (kLanes == 4) {
+        const float4 s = own ? __ldcs(reinterpret_cast<const float4 *>(in + c * plane)) : make_float4(0, 0, 0, 0);
+        const float4 p = __ldcs(reinterpret_cast<const float4 *>(pin + c * plane));
+        const float4 g = __ldcs(reinterpret_cast<const float4 *>(gin + c * plane));
+        rs[slot][0] = s.x, rs[slot][1 % kLanes] = s.y, rs[slot][2 % kLanes] = s.z, rs[slot][3 % kLanes] = s.w;
+        rp[slot][0] = p.x, rp[slot][1 % kLanes] = p.y, rp[slot][2 % kLanes] = p.z, rp[slot][3 % kLanes] = p.w;
+        rg[slot][0] = g.x, rg[slot][1 % kLanes] = g.y, rg[slot][2 % kLanes] = g.z, rg[slot][3 % kLanes] = g.w;
+      } else {
+        rs[slot][0] = own ? __ldcs(in + c * plane) : 0.0f;
+        rp[slot][0] = __ldcs(pin + c * plane);
+        rg[slot][0] = __ldcs(gin + c * plane);
+      }
+    } else {
+#pragma unroll
+      for (int l = 0; l < kLanes; ++l) rs[slot][l] = 0.0f, rp[slot][l] = 0.0f, rg[slot][l] = 0.0f;
+    }
+  };
+  // ring slot of channel c is (c - c_begin + kPad) mod kRing
+#pragma unroll
+  for (int s = 0; s < kRing; ++s) load(s, static_cast<int64_t>(c_begin) + s - kPad);
+  for (uint32_t c0 = c_begin; c0 < c_end; c0 += kRing) {
+#pragma unroll
+    for (int j = 0; j < kRing; ++j) {
+      const uint32_t c = c0 + j;
+      if (c < c_end) {
+        float val[kLanes];
+#pragma unroll
+        for (int l = 0; l < kLanes; ++l) val[l] = 0.0f;
+#pragma unroll
+        for (int t = 0; t < NSIZE; ++t)
+#pragma unroll
+          for (int l = 0; l < kLanes; ++l) {
+            const float pg = Reducer::PartialGrad(rs[(j + kPad) % kRing][l], rp[(j + t) % kRing][l]);
+            val[l] = __fadd_rn(val[l], __fmul_rn(pg, rg[(j + t) % kRing][l]));
+          }
+        if (kLanes == 4) {
+          __stcs(reinterpret_cast<float4 *>(out + static_cast<int64_t>(c) * plane),
+                 make_float4(val[0], val[1 % kLanes], val[2 % kLanes], val[3 % kLanes]));
+        } else {
+          __stcs(out + static_cast<int64_t>(c) * plane, val[0]);
+        }
+        load(j, static_cast<int64_t>(c) - kPad + kRing);
+      }
+    }
+  }
+}
+
+/*!
  * \brief channel-window pooling with the channel planes staged through shared memory.
  *  Same arithmetic as ChannelPoolKernel (window kept in registers, channels added in
  *  ascending order), but the thread no longer waits on its own global loads: one thread
@@ -652,6 +735,58 @@ inline void ChannelPoolLaunch(float *dst, const float *src, int64_t n, int64_t c
 #undef MSHADOW_B200_CHPOOL_STAGED_LAUNCH_
 #undef MSHADOW_B200_CHPOOL_LAUNCH_
   MSHADOW_CUDA_POST_KERNEL_CHECK(ChannelPoolKernel);
+}
+
+/*! \brief window sizes ChannelUnpoolKernel is instantiated for (stride 1, pad nsize/2) */
+inline bool ChannelUnpoolSupported(int nsize, int stride, int pad) {
+  return stride == 1 && pad == nsize / 2 && (nsize == 1 || nsize == 3 || nsize == 5 || nsize == 7);
+}
+
+/*! \brief dense (n, c, h, w) src, pooled, pooled gradient and dst; requires ChannelUnpoolSupported */
+template <typename Reducer>
+inline void ChannelUnpoolLaunch(float *dst, const float *src, const float *pooled, const float *gpooled, int64_t n,
+                                int64_t c, int64_t h, int64_t w, int nsize, cudaStream_t stream) {
+  if (n == 0 || c == 0 || h * w == 0) return;
+  const uint32_t plane = static_cast<uint32_t>(h * w);
+  const bool vec = plane % 4 == 0 && reinterpret_cast<uintptr_t>(dst) % 16 == 0 &&
+                   reinterpret_cast<uintptr_t>(src) % 16 == 0 && reinterpret_cast<uintptr_t>(pooled) % 16 == 0 &&
+                   reinterpret_cast<uintptr_t>(gpooled) % 16 == 0;
+  const uint32_t groups = plane / (vec ? 4 : 1);
+  const int64_t items64 = n * static_cast<int64_t>(groups);
+  CHECK_LT(items64, (int64_t(1) << 31)) << "ch_unpool: tensor too large for 32-bit indexing";
+  const uint32_t items = static_cast<uint32_t>(items64);
+  const uint32_t tiles = static_cast<uint32_t>(gpu_rt::CeilDiv(items, kPoolThreads));
+#define MSHADOW_B200_CHUNPOOL_LAUNCH_(NS, LANES)                                                               \
+  {                                                                                                            \
+    auto kernel = ChannelUnpoolKernel<Reducer, NS, LANES>;                                                     \
+    static uint32_t slots = 0; /* resident CTAs of this instantiation */                                      \
+    if (slots == 0) {                                                                                          \
+      int per_sm = 0;                                                                                          \
+      MSHADOW_CUDA_CALL(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, kPoolThreads, 0));      \
+      slots = static_cast<uint32_t>(per_sm < 1 ? 1 : per_sm) * gpu_rt::CurrentDevice().sm_count;               \
+    }                                                                                                          \
+    /* channel segments that fill whole waves; each re-reads NS-1 halo channels of two tensors */            \
+    uint32_t max_seg = static_cast<uint32_t>(c) / (8 * NS);                                                    \
+    if (max_seg < 1) max_seg = 1;                                                                              \
+    if (max_seg > 16) max_seg = 16;                                                                            \
+    const uint32_t segs = pooldetail::WaveFriendlySegments(tiles, max_seg, slots);                            \
+    const uint32_t seg_len = (static_cast<uint32_t>(c) + segs - 1) / segs;                                     \
+    const uint32_t nseg = (static_cast<uint32_t>(c) + seg_len - 1) / seg_len;                                  \
+    kernel<<<dim3(tiles, nseg), kPoolThreads, 0, stream>>>(dst, src, pooled, gpooled, static_cast<uint32_t>(c), \
+                                                            plane, groups, items, gpu_rt::FastDiv(groups),     \
+                                                            seg_len);                                          \
+  }
+#define MSHADOW_B200_CHUNPOOL_PICK_(NS) \
+  if (vec) MSHADOW_B200_CHUNPOOL_LAUNCH_(NS, 4) else MSHADOW_B200_CHUNPOOL_LAUNCH_(NS, 1)
+  switch (nsize) {
+    case 1: MSHADOW_B200_CHUNPOOL_PICK_(1) break;
+    case 3: MSHADOW_B200_CHUNPOOL_PICK_(3) break;
+    case 5: MSHADOW_B200_CHUNPOOL_PICK_(5) break;
+    default: MSHADOW_B200_CHUNPOOL_PICK_(7) break;
+  }
+#undef MSHADOW_B200_CHUNPOOL_PICK_
+#undef MSHADOW_B200_CHUNPOOL_LAUNCH_
+  MSHADOW_CUDA_POST_KERNEL_CHECK(ChannelUnpoolKernel);
 }
 
 }  // namespace cuda

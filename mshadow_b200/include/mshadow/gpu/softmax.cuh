@@ -415,6 +415,215 @@ inline void SoftmaxGradLaunch(float *dst, const float *src, const float *label, 
   MSHADOW_CUDA_POST_KERNEL_CHECK(SoftmaxGrad);
 }
 
+// ----------------------------------------------------------------------------------------
+// (batch, classes, positions) tensors: softmax over the middle axis.  Element (y, x, n) lives
+// at (y * classes + x) * ld + n, so the classes of one position are `ld` floats apart and
+// neighbouring threads take neighbouring positions.
+// ----------------------------------------------------------------------------------------
+
+const int kSoftmax3DThreads = 128;
+
+/*!
+ * \brief one CTA = one image y and a tile of kThreads * kLanes positions; thread t owns kLanes
+ *  adjacent positions and walks the classes.  With kStaged the tile (classes x positions) is
+ *  parked in shared memory between the three passes, so global memory sees one read and one
+ *  write per element; without it (more classes than shared memory holds) the exponentials are
+ *  parked in dst and read back, mostly from L2.  Each column is summed by one thread in class
+ *  order, as mshadow/tensor_cpu-inl.h:474-495 does.
+ */
+template <int kLanes, bool kStaged>
+__global__ void __launch_bounds__(kSoftmax3DThreads)
+Softmax3DKernel(float *dst, const float *src, uint32_t classes, uint32_t npos, uint32_t tiles, int64_t ld_dst,
+                int64_t ld_src) {
+  extern __shared__ __align__(16) float tile[];  // [classes][kThreads * kLanes]
+  constexpr int kWidth = kSoftmax3DThreads * kLanes;
+  const uint32_t y = blockIdx.x / tiles;
+  const uint32_t n = (blockIdx.x - y * tiles) * kWidth + threadIdx.x * kLanes;
+  if (n >= npos) return;  // no CTA-wide barrier below: every thread works on its own columns
+  const float *in = src + static_cast<int64_t>(y) * classes * ld_src + n;
+  float *out = dst + static_cast<int64_t>(y) * classes * ld_dst + n;
+  float *mine = tile + threadIdx.x * kLanes;
+  float m[kLanes], s[kLanes];
+#pragma unroll
+  for (int l = 0; l < kLanes; ++l) m[l] = -FLT_MAX, s[l] = 0.0f;
+#pragma unroll 4
+  for (uint32_t x = 0; x < classes; ++x) {
+    float v[kLanes];
+    if (kLanes == 4) {
+      const float4 p = __ldcs(reinterpret_cast<const float4 *>(in + x * ld_src));
+      v[0] = p.x, v[1 % kLanes] = p.y, v[2 % kLanes] = p.z, v[3 % kLanes] = p.w;
+      if (kStaged) *reinterpret_cast<float4 *>(mine + x * kWidth) = p;
+    } else {
+      v[0] = __ldcs(in + x * ld_src);
+      if (kStaged) mine[x * kWidth] = v[0];
+    }
+#pragma unroll
+    for (int l = 0; l < kLanes; ++l) m[l] = m[l] < v[l] ? v[l] : m[l];
+  }
+#pragma unroll 4
+  for (uint32_t x = 0; x < classes; ++x) {
+    float v[kLanes];
+    if (kLanes == 4) {
+      const float4 p = kStaged ? *reinterpret_cast<const float4 *>(mine + x * kWidth)
+                               : __ldcg(reinterpret_cast<const float4 *>(in + x * ld_src));
+      v[0] = p.x, v[1 % kLanes] = p.y, v[2 % kLanes] = p.z, v[3 % kLanes] = p.w;
+    } else {
+      v[0] = kStaged ? mine[x * kWidth] : __ldcg(in + x * ld_src);
+    }
+#pragma unroll
+    for (int l = 0; l < kLanes; ++l) {
+      v[l] = expf(__fsub_rn(v[l], m[l]));
+      s[l] = __fadd_rn(s[l], v[l]);
+    }
+    if (kLanes == 4) {
+      const float4 p = make_float4(v[0], v[1 % kLanes], v[2 % kLanes], v[3 % kLanes]);
+      if (kStaged) *reinterpret_cast<float4 *>(mine + x * kWidth) = p;
+      else *reinterpret_cast<float4 *>(out + x * ld_dst) = p;
+    } else {
+      if (kStaged) mine[x * kWidth] = v[0];
+      else out[x * ld_dst] = v[0];
+    }
+  }
+#pragma unroll 4
+  for (uint32_t x = 0; x < classes; ++x) {
+    if (kLanes == 4) {
+      float4 p = kStaged ? *reinterpret_cast<const float4 *>(mine + x * kWidth)
+                         : *reinterpret_cast<const float4 *>(out + x * ld_dst);
+      p.x = __fdiv_rn(p.x, s[0]);
+      p.y = __fdiv_rn(p.y, s[1 % kLanes]);
+      p.z = __fdiv_rn(p.z, s[2 % kLanes]);
+      p.w = __fdiv_rn(p.w, s[3 % kLanes]);
+      __stcs(reinterpret_cast<float4 *>(out + x * ld_dst), p);
+    } else {
+      const float e = kStaged ? mine[x * kWidth] : out[x * ld_dst];
+      __stcs(out + x * ld_dst, __fdiv_rn(e, s[0]));
+    }
+  }
+}
+
+namespace smdetail {
+template <int kLanes>
+inline void LaunchSoftmax3D(float *dst, const float *src, uint32_t batch, uint32_t classes, uint32_t npos,
+                            int64_t ld_dst, int64_t ld_src, cudaStream_t stream) {
+  const uint32_t width = kSoftmax3DThreads * kLanes;
+  const uint32_t tiles = (npos + width - 1) / width;
+  const size_t smem = static_cast<size_t>(classes) * width * sizeof(float);
+  const size_t limit = static_cast<size_t>(gpu_rt::CurrentDevice().max_smem_optin);
+  const int64_t ctas = static_cast<int64_t>(batch) * tiles;
+  CHECK_LT(ctas, (int64_t(1) << 31)) << "Softmax: too many tiles for one launch";
+  if (smem <= limit) {
+    auto kernel = Softmax3DKernel<kLanes, true>;
+    if (smem > 48 * 1024) {
+      MSHADOW_CUDA_CALL(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                             static_cast<int>(limit)));
+    }
+    kernel<<<static_cast<unsigned>(ctas), kSoftmax3DThreads, smem, stream>>>(dst, src, classes, npos, tiles, ld_dst,
+                                                                            ld_src);
+  } else {
+    Softmax3DKernel<kLanes, false><<<static_cast<unsigned>(ctas), kSoftmax3DThreads, 0, stream>>>(
+        dst, src, classes, npos, tiles, ld_dst, ld_src);
+  }
+  MSHADOW_CUDA_POST_KERNEL_CHECK(Softmax3D);
+}
+}  // namespace smdetail
+
+/*! \brief softmax over the middle axis; dst may alias src */
+inline void Softmax3DLaunch(float *dst, const float *src, int64_t batch, int64_t classes, int64_t npos,
+                            int64_t ld_dst, int64_t ld_src, cudaStream_t stream) {
+  if (batch == 0 || classes == 0 || npos == 0) return;
+  CHECK_LT(batch * classes * std::max(ld_dst, ld_src), (int64_t(1) << 40)) << "Softmax: tensor too large";
+  const uint32_t b = static_cast<uint32_t>(batch), c = static_cast<uint32_t>(classes), p = static_cast<uint32_t>(npos);
+  const bool vec = npos % 4 == 0 && ld_dst % 4 == 0 && ld_src % 4 == 0 && reinterpret_cast<uintptr_t>(dst) % 16 == 0 &&
+                   reinterpret_cast<uintptr_t>(src) % 16 == 0;
+  // narrow position axes keep one position per thread so that a tile is not mostly idle threads;
+  // the same when only the one-lane tile of all classes fits shared memory
+  const size_t limit = static_cast<size_t>(gpu_rt::CurrentDevice().max_smem_optin);
+  const bool wide_fits = static_cast<size_t>(classes) * kSoftmax3DThreads * 4 * sizeof(float) <= limit;
+  const bool narrow_fits = static_cast<size_t>(classes) * kSoftmax3DThreads * sizeof(float) <= limit;
+  if (vec && npos >= 4 * kSoftmax3DThreads && (wide_fits || !narrow_fits)) {
+    smdetail::LaunchSoftmax3D<4>(dst, src, b, c, p, ld_dst, ld_src, stream);
+  } else {
+    smdetail::LaunchSoftmax3D<1>(dst, src, b, c, p, ld_dst, ld_src, stream);
+  }
+}
+
+/*!
+ * \brief dst(y,x,n) = src(y,x,n) - [x == label(y,n)], with the smoothing / ignore-label modes
+ *  of SoftmaxGradKernel; arithmetic as mshadow/tensor_cpu-inl.h:370-462
+ */
+template <int kLanes>
+__global__ void __launch_bounds__(256)
+SoftmaxGrad3DKernel(float *dst, const float *src, const float *label, uint32_t total, uint32_t items_per_row,
+                    gpu_rt::FastDiv row_of_item, gpu_rt::FastDiv image_of_row, int64_t ld_dst, int64_t ld_src,
+                    int64_t ld_label, int mode, int ignore_label, float alpha, float smooth_grad) {
+  const uint32_t step = gridDim.x * 256;
+  for (uint32_t i = blockIdx.x * 256 + threadIdx.x; i < total; i += step) {
+    const uint32_t row = row_of_item.Quot(i);  // row = y * classes + x
+    const uint32_t n = (i - row * items_per_row) * kLanes;
+    const uint32_t y = image_of_row.Quot(row);
+    const int x = static_cast<int>(row - y * image_of_row.div);
+    int k[kLanes];
+    bool any_live = false;
+#pragma unroll
+    for (int l = 0; l < kLanes; ++l) {
+      k[l] = static_cast<int>(__ldg(label + y * ld_label + n + l));
+      any_live |= !((mode & 2) && k[l] == ignore_label);
+    }
+    float v[kLanes];
+#pragma unroll
+    for (int l = 0; l < kLanes; ++l) v[l] = 0.0f;
+    if (any_live) {
+      if (kLanes == 4) {
+        const float4 p = __ldcs(reinterpret_cast<const float4 *>(src + row * ld_src + n));
+        v[0] = p.x, v[1 % kLanes] = p.y, v[2 % kLanes] = p.z, v[3 % kLanes] = p.w;
+      } else {
+        v[0] = __ldcs(src + row * ld_src + n);
+      }
+    }
+#pragma unroll
+    for (int l = 0; l < kLanes; ++l) {
+      if ((mode & 2) && k[l] == ignore_label) {
+        v[l] = 0.0f;
+      } else if (mode & 1) {
+        v[l] = x == k[l] ? __fadd_rn(__fsub_rn(v[l], 1.0f), alpha) : __fsub_rn(v[l], smooth_grad);
+      } else if (x == k[l]) {
+        v[l] = __fsub_rn(v[l], 1.0f);
+      }
+    }
+    if (kLanes == 4) {
+      __stcs(reinterpret_cast<float4 *>(dst + row * ld_dst + n),
+             make_float4(v[0], v[1 % kLanes], v[2 % kLanes], v[3 % kLanes]));
+    } else {
+      __stcs(dst + row * ld_dst + n, v[0]);
+    }
+  }
+}
+
+inline void SoftmaxGrad3DLaunch(float *dst, const float *src, const float *label, int64_t batch, int64_t classes,
+                                int64_t npos, int64_t ld_dst, int64_t ld_src, int64_t ld_label, int mode,
+                                float ignore_label, float alpha, cudaStream_t stream) {
+  if (batch == 0 || classes == 0 || npos == 0) return;
+  CHECK_LT(batch * classes * npos, (int64_t(1) << 31)) << "SoftmaxGrad: tensor too large for 32-bit indexing";
+  const float smooth_grad = alpha / static_cast<float>(static_cast<index_t>(classes) - 1);
+  const bool vec = npos % 4 == 0 && ld_dst % 4 == 0 && ld_src % 4 == 0 && reinterpret_cast<uintptr_t>(dst) % 16 == 0 &&
+                   reinterpret_cast<uintptr_t>(src) % 16 == 0;
+  const uint32_t rows = static_cast<uint32_t>(batch * classes);
+  const uint32_t ipr = static_cast<uint32_t>(vec ? npos / 4 : npos);
+  const uint32_t total = rows * ipr;
+  int grid = gpu_rt::CeilDiv(total, 256);
+  const int cap = gpu_rt::CurrentDevice().sm_count * 8;
+  if (grid > cap) grid = cap;
+  const gpu_rt::FastDiv by_items(ipr), by_classes(static_cast<uint32_t>(classes));
+  if (vec) {
+    SoftmaxGrad3DKernel<4><<<grid, 256, 0, stream>>>(dst, src, label, total, ipr, by_items, by_classes, ld_dst, ld_src,
+                                                    ld_label, mode, static_cast<int>(ignore_label), alpha, smooth_grad);
+  } else {
+    SoftmaxGrad3DKernel<1><<<grid, 256, 0, stream>>>(dst, src, label, total, ipr, by_items, by_classes, ld_dst, ld_src,
+                                                    ld_label, mode, static_cast<int>(ignore_label), alpha, smooth_grad);
+  }
+  MSHADOW_CUDA_POST_KERNEL_CHECK(SoftmaxGrad3D);
+}
+
 }  // namespace cuda
 }  // namespace mshadow
 #endif  // MSHADOW_GPU_SOFTMAX_CUH_

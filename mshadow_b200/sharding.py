@@ -30,6 +30,45 @@ def route_sorted_indices(sorted_keys, order, num_rows, rank, world):
     return local, np.ascontiguousarray(order[lo:hi]), row_begin, row_end
 
 
+def hot_rows(sorted_keys, count):
+    """The `count` table rows named most often in a sorted key list, ascending.
+
+    With Zipf-distributed indices a few rows receive a large share of the batch (the hottest
+    one about 13 % at exponent 1.1), so any ownership rule leaves the owner of those rows with
+    far more than 1/world of the work.  These rows are handled by every rank instead.
+    """
+    if count <= 0 or sorted_keys.size == 0:
+        return np.zeros(0, dtype=sorted_keys.dtype)
+    uniq, counts = np.unique(sorted_keys, return_counts=True)
+    take = np.argsort(-counts, kind="stable")[:count]
+    return np.sort(uniq[take]).astype(sorted_keys.dtype)
+
+
+def route_cyclic_with_hot_rows(sorted_keys, order, num_sources, rank, world, hot):
+    """Split a sorted (key, source-row) list for cyclic table ownership with replicated hot rows.
+
+    Table row r is owned by rank r % world and stored there as local row r // world.
+      tail  entries whose key is not hot go to the key's owner, keys rewritten to local rows;
+            the list stays sorted and every row keeps its accumulation order, so tail rows come
+            out bit-identical to the unsharded result.
+      hot   entries whose key is hot stay with the rank that owns their SOURCE row (sources are
+            sharded contiguously over the batch); their keys are rewritten to positions in
+            `hot`.  Each rank sums them into a len(hot) x D partial table; one all-reduce of that
+            small table follows, and owners add its rows to theirs.  This changes the order of
+            the additions for hot rows only (rounding-level differences).
+    Returns (tail_keys, tail_order, hot_keys, hot_order).
+    """
+    is_hot = np.isin(sorted_keys, hot)
+    mine = (~is_hot) & (sorted_keys % world == rank)
+    tail_keys = np.ascontiguousarray(sorted_keys[mine] // world, dtype=sorted_keys.dtype)
+    tail_order = np.ascontiguousarray(order[mine])
+    begin, end = shard_range(num_sources, rank, world)
+    local_src = is_hot & (order >= begin) & (order < end)
+    hot_keys = np.ascontiguousarray(np.searchsorted(hot, sorted_keys[local_src]), dtype=sorted_keys.dtype)
+    hot_order = np.ascontiguousarray(order[local_src])
+    return tail_keys, tail_order, hot_keys, hot_order
+
+
 def allreduce_sum(tensor):
     """In-place sum over all ranks of the default process group (NCCL on GPUs, gloo on CPU)."""
     import torch.distributed as dist

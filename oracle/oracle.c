@@ -348,6 +348,99 @@ void ORC(sort_by_key)(int32_t *keys, int32_t *values, int64_t n, int ascend) {
   free(perm); free(tmp); free(k2); free(v2);
 }
 
+/* ---- softmax over the middle axis (tensor_cpu-inl.h:474-495) ---- */
+
+void ORC(softmax3d)(float *dst, const float *src, int64_t batch, int64_t classes, int64_t npos,
+                    int64_t ld_dst, int64_t ld_src) {
+#pragma omp parallel for
+  for (int64_t y = 0; y < batch; ++y) {
+    for (int64_t n = 0; n < npos; ++n) {
+      const float *e = src + y * classes * ld_src + n;
+      float *d = dst + y * classes * ld_dst + n;
+      float mmax = e[0];
+      for (int64_t x = 1; x < classes; ++x)
+        if (mmax < e[x * ld_src]) mmax = e[x * ld_src];
+      float sum = 0.0f;
+      for (int64_t x = 0; x < classes; ++x) {
+        d[x * ld_dst] = expf(e[x * ld_src] - mmax);
+        sum += d[x * ld_dst];
+      }
+      for (int64_t x = 0; x < classes; ++x) d[x * ld_dst] /= sum;
+    }
+  }
+}
+
+/* tensor_cpu-inl.h:370-387 (plain), :389-408 (smooth), :410-434 (ignore), :436-462 (both) */
+void ORC(softmax_grad3d)(float *dst, const float *src, const float *label, int64_t batch,
+                         int64_t classes, int64_t npos, int64_t ld_dst, int64_t ld_src,
+                         int64_t ld_label, int mode, float ignore_label, float alpha) {
+  const int smooth = mode & 1, ignore = mode & 2;
+  const float smooth_grad = alpha / (float)(classes - 1);
+#pragma omp parallel for
+  for (int64_t n = 0; n < npos; ++n) {
+    for (int64_t y = 0; y < batch; ++y) {
+      const int k = (int)label[y * ld_label + n];
+      for (int64_t x = 0; x < classes; ++x) {
+        const float s = src[(y * classes + x) * ld_src + n];
+        float *d = dst + (y * classes + x) * ld_dst + n;
+        if (ignore && k == (int)ignore_label) {
+          *d = 0.0f;
+        } else if (x == k) {
+          *d = smooth ? s - 1.0f + alpha : s - 1.0f;
+        } else {
+          *d = smooth ? s - smooth_grad : s;
+        }
+      }
+    }
+  }
+}
+
+/* ---- IndexFill (tensor_cpu-inl.h:520-529): serial, so a row named twice keeps the later source ---- */
+
+void ORC(index_fill)(float *dst, const int32_t *index, const float *src, int64_t d, int64_t nidx,
+                     int64_t ld_dst, int64_t ld_src) {
+  for (int64_t y = 0; y < nidx; ++y) {
+    float *row = dst + (int64_t)index[y] * ld_dst;
+    const float *s = src + y * ld_src;
+    for (int64_t j = 0; j < d; ++j) row[j] = s[j];
+  }
+}
+
+/* ---- VectorizedSort (tensor_cpu-inl.h:562-567): SortByKey(values, segments), then
+        SortByKey(segments, values), both stable and ascending ---- */
+
+static void merge_sort_perm_f32(int64_t *perm, int64_t *tmp, const float *keys, int64_t lo, int64_t hi) {
+  if (hi - lo < 2) return;
+  const int64_t mid = lo + (hi - lo) / 2;
+  merge_sort_perm_f32(perm, tmp, keys, lo, mid);
+  merge_sort_perm_f32(perm, tmp, keys, mid, hi);
+  int64_t i = lo, j = mid, o = lo;
+  while (i < mid && j < hi) tmp[o++] = keys[perm[j]] < keys[perm[i]] ? perm[j++] : perm[i++];
+  while (i < mid) tmp[o++] = perm[i++];
+  while (j < hi) tmp[o++] = perm[j++];
+  memcpy(perm + lo, tmp + lo, (size_t)(hi - lo) * sizeof(int64_t));
+}
+
+void ORC(vectorized_sort)(float *values, int32_t *segments, int64_t n) {
+  if (n <= 0) return;
+  int64_t *perm = (int64_t *)malloc((size_t)n * sizeof(int64_t));
+  int64_t *tmp = (int64_t *)malloc((size_t)n * sizeof(int64_t));
+  float *v2 = (float *)malloc((size_t)n * sizeof(float));
+  int32_t *s2 = (int32_t *)malloc((size_t)n * sizeof(int32_t));
+  for (int pass = 0; pass < 2; ++pass) {
+    for (int64_t i = 0; i < n; ++i) perm[i] = i;
+    if (pass == 0) merge_sort_perm_f32(perm, tmp, values, 0, n);
+    else merge_sort_perm(perm, tmp, segments, 0, n, 1);
+    for (int64_t i = 0; i < n; ++i) {
+      v2[i] = values[perm[i]];
+      s2[i] = segments[perm[i]];
+    }
+    memcpy(values, v2, (size_t)n * sizeof(float));
+    memcpy(segments, s2, (size_t)n * sizeof(int32_t));
+  }
+  free(perm); free(tmp); free(v2); free(s2);
+}
+
 int ORC(num_threads)(void) {
 #ifdef _OPENMP
   return omp_get_max_threads();

@@ -107,6 +107,31 @@ void ORC(addtakegrad_largebatch)(float *dst, const int32_t *sorted, const int32_
 /* stable key/value sort, ascending or descending (tensor_cpu-inl.h:531-560) */
 void ORC(sort_by_key)(int32_t *keys, int32_t *values, int64_t n, int ascend);
 
+/*
+ * Softmax over the middle axis of a (batch, classes, positions) tensor
+ * (tensor_cpu-inl.h:474-495): for every (y, n) the column src[y][.][n] is normalised.
+ * `ld_*` is the pitch of the last axis.
+ */
+void ORC(softmax3d)(float *dst, const float *src, int64_t batch, int64_t classes, int64_t npos,
+                    int64_t ld_dst, int64_t ld_src);
+
+/*
+ * SoftmaxGrad family on (batch, classes, positions) with label (batch, positions)
+ * (tensor_cpu-inl.h:370-462); mode bits as for softmax_grad.
+ */
+void ORC(softmax_grad3d)(float *dst, const float *src, const float *label, int64_t batch,
+                         int64_t classes, int64_t npos, int64_t ld_dst, int64_t ld_src,
+                         int64_t ld_label, int mode, float ignore_label, float alpha);
+
+/* dst[index[y]][j] = src[y][j] for y ascending: the last writer of a row wins
+   (tensor_cpu-inl.h:520-529) */
+void ORC(index_fill)(float *dst, const int32_t *index, const float *src, int64_t d, int64_t nidx,
+                     int64_t ld_dst, int64_t ld_src);
+
+/* sort `values` ascending inside each run of equal `segments` (segments ascending on entry):
+   two stable pair sorts (tensor_cpu-inl.h:562-567) */
+void ORC(vectorized_sort)(float *values, int32_t *segments, int64_t n);
+
 /* number of OpenMP threads the library will use (for cpu_baseline.cores) */
 int ORC(num_threads)(void);
 

@@ -192,6 +192,44 @@ void ref_sort_by_key(int32_t *keys, int32_t *values, int64_t n, int ascend) {
   SortByKey(k, v, ascend != 0);
 }
 
+void ref_softmax3d(float *dst, const float *src, int64_t batch, int64_t classes, int64_t npos,
+                   int64_t ld_dst, int64_t ld_src) {
+  typedef Tensor<cpu, 3, float> T3;
+  T3 d(dst, Shape3(batch, classes, npos), static_cast<index_t>(ld_dst), NULL);
+  T3 s(const_cast<float *>(src), Shape3(batch, classes, npos), static_cast<index_t>(ld_src), NULL);
+  Softmax(d, s);
+}
+
+void ref_softmax_grad3d(float *dst, const float *src, const float *label, int64_t batch,
+                        int64_t classes, int64_t npos, int64_t ld_dst, int64_t ld_src,
+                        int64_t ld_label, int mode, float ignore_label, float alpha) {
+  typedef Tensor<cpu, 3, float> T3;
+  T3 d(dst, Shape3(batch, classes, npos), static_cast<index_t>(ld_dst), NULL);
+  T3 s(const_cast<float *>(src), Shape3(batch, classes, npos), static_cast<index_t>(ld_src), NULL);
+  T2 l = mat(label, batch, npos, ld_label);
+  switch (mode & 3) {
+    case 0: SoftmaxGrad(d, s, l); break;
+    case 1: SmoothSoftmaxGrad(d, s, l, alpha); break;
+    case 2: SoftmaxGrad(d, s, l, ignore_label); break;
+    default: SmoothSoftmaxGrad(d, s, l, ignore_label, alpha); break;
+  }
+}
+
+void ref_index_fill(float *dst, const int32_t *index, const float *src, int64_t d, int64_t nidx,
+                    int64_t ld_dst, int64_t ld_src) {
+  /* the destination's row count is not consulted by the reference; any bound >= max(index)+1 serves */
+  int64_t k = 1;
+  for (int64_t y = 0; y < nidx; ++y) k = index[y] + 1 > k ? index[y] + 1 : k;
+  Tensor<cpu, 1, int32_t> idx(const_cast<int32_t *>(index), Shape1(nidx), nidx, NULL);
+  IndexFill(mat(dst, k, d, ld_dst), idx, mat(src, nidx, d, ld_src));
+}
+
+void ref_vectorized_sort(float *values, int32_t *segments, int64_t n) {
+  Tensor<cpu, 1, float> v(values, Shape1(n), n, NULL);
+  Tensor<cpu, 1, int32_t> s(segments, Shape1(n), n, NULL);
+  VectorizedSort(v, s);
+}
+
 int ref_num_threads(void) {
 #ifdef _OPENMP
   return omp_get_max_threads();

@@ -143,6 +143,30 @@ class Checker:
                                 C.c_int(1 if ascend else 0))
         return keys, values
 
+    # ---- softmax over the middle axis, IndexFill, VectorizedSort -------------------
+    def softmax3d(self, dst, src):
+        batch, classes, npos = src.shape
+        self._fn("softmax3d")(_fp(dst), _fp(src), i64(batch), i64(classes), i64(npos), i64(_ld(dst)),
+                              i64(_ld(src)))
+        return dst
+
+    def softmax_grad3d(self, dst, src, label, mode=0, ignore_label=0.0, alpha=0.0):
+        batch, classes, npos = src.shape
+        self._fn("softmax_grad3d")(_fp(dst), _fp(src), _fp(label), i64(batch), i64(classes), i64(npos),
+                                   i64(_ld(dst)), i64(_ld(src)), i64(_ld(label)), C.c_int(mode),
+                                   C.c_float(ignore_label), C.c_float(alpha))
+        return dst
+
+    def index_fill(self, dst, index, src):
+        self._fn("index_fill")(_fp(dst), _ip(index), _fp(src), i64(src.shape[1]), i64(index.shape[0]),
+                               i64(_ld(dst)), i64(_ld(src)))
+        return dst
+
+    def vectorized_sort(self, values, segments):
+        assert values.flags.c_contiguous
+        self._fn("vectorized_sort")(_fp(values), _ip(segments), i64(values.shape[0]))
+        return values, segments
+
 
 _cache = {}
 

@@ -85,6 +85,24 @@ def main():
     ref.sort_by_key(kd, vd, False)
     out.update(emb_sorted_desc=kd, emb_order_desc=vd)
 
+    # softmax over the middle axis and its gradients, IndexFill, VectorizedSort
+    L3 = f32(rng.standard_normal((3, 7, 10)) * 2)
+    lab3 = f32(rng.integers(0, 7, size=(3, 10)))
+    P3 = ref.softmax3d(np.zeros_like(L3), L3)
+    out.update(sm3_logits=L3, sm3_label=lab3, sm3_prob=P3)
+    for mode in range(4):
+        out["sm3_grad_%d" % mode] = ref.softmax_grad3d(np.zeros_like(L3), P3, lab3, mode=mode,
+                                                       ignore_label=float(lab3[1, 2]), alpha=0.1)
+    fidx = rng.integers(0, 12, size=30).astype(np.int32)
+    fsrc = f32(rng.standard_normal((30, 6)))
+    ft0 = f32(rng.standard_normal((12, 6)))
+    out.update(fill_idx=fidx, fill_src=fsrc, fill_t0=ft0)
+    out["fill_out"] = ref.index_fill(ft0.copy(), fidx, fsrc)
+    seg = np.sort(rng.integers(0, 5, size=64)).astype(np.int32)
+    sval = f32(rng.integers(0, 16, size=64) / 4.0)
+    out.update(vsort_seg=seg, vsort_val=sval)
+    out["vsort_out"] = ref.vectorized_sort(sval.copy(), seg.copy())[0]
+
     path = os.path.join(HERE, "golden.npz")
     np.savez_compressed(path, **out)
     print("wrote %s (%d arrays, %d bytes)" % (path, len(out), os.path.getsize(path)))

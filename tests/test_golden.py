@@ -67,6 +67,18 @@ def test_oracle_embedding():
     assert np.array_equal(kd, G["emb_sorted_desc"]) and np.array_equal(vd, G["emb_order_desc"])
 
 
+def test_oracle_softmax3d_fill_and_segment_sort():
+    L3, lab3 = G["sm3_logits"], G["sm3_label"]
+    P3 = orc.softmax3d(np.zeros_like(L3), L3)
+    assert same_bits(P3, G["sm3_prob"])
+    for mode in range(4):
+        got = orc.softmax_grad3d(np.zeros_like(L3), P3, lab3, mode=mode, ignore_label=float(lab3[1, 2]), alpha=0.1)
+        assert same_bits(got, G["sm3_grad_%d" % mode])
+    assert same_bits(orc.index_fill(G["fill_t0"].copy(), G["fill_idx"], G["fill_src"]), G["fill_out"])
+    v, s = orc.vectorized_sort(G["vsort_val"].copy(), G["vsort_seg"].copy())
+    assert same_bits(v, G["vsort_out"]) and np.array_equal(s, G["vsort_seg"])
+
+
 # ----------------------------------------------------------------------------- CUDA path
 @pytest.fixture(scope="module")
 def gpu():
@@ -136,3 +148,13 @@ def test_gpu_matches_fixtures(gpu):
     assert sum_close(h(lib.addtakegrad_largebatch(d(t0), gk, gv, d(src))), G["emb_largebatch"], per_row=True)
     gk, gv = lib.sort_by_key(d(keys), d(vals), False)
     assert np.array_equal(h(gk), G["emb_sorted_desc"]) and np.array_equal(h(gv), G["emb_order_desc"])
+    L3, lab3, P3 = G["sm3_logits"], G["sm3_label"], G["sm3_prob"]
+    got = h(lib.softmax3d(torch.zeros(L3.shape, device="cuda"), d(L3)))
+    assert np.max(np.abs(got.astype(np.float64) - P3) / P3) <= 1e-5
+    for mode in range(4):
+        got = h(lib.softmax_grad3d(torch.zeros(L3.shape, device="cuda"), d(P3), d(lab3), mode=mode,
+                                   ignore_label=float(lab3[1, 2]), alpha=0.1))
+        assert same_bits(got, G["sm3_grad_%d" % mode])
+    assert same_bits(h(lib.index_fill(d(G["fill_t0"]), d(G["fill_idx"]), d(G["fill_src"]))), G["fill_out"])
+    gv, gs = lib.vectorized_sort(d(G["vsort_val"]), d(G["vsort_seg"]))
+    assert same_bits(h(gv), G["vsort_out"]) and np.array_equal(h(gs), G["vsort_seg"])

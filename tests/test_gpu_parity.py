@@ -268,7 +268,11 @@ def test_chpool(lib, reducer, shape, nsize, stride, pad):
 
 @pytest.mark.parametrize("reducer", [0, 1, 2])
 @pytest.mark.parametrize("shape,nsize,pad", [((2, 8, 3, 5), 5, 0), ((2, 7, 4, 4), 3, 0), ((3, 16, 6, 6), 5, 2),
-                                             ((1, 12, 5, 8), 7, 0), ((2, 6, 3, 3), 1, 3)])
+                                             ((1, 12, 5, 8), 7, 0), ((2, 6, 3, 3), 1, 3),
+                                             ((3, 200, 16, 24), 5, 0),   # channel march cut into segments
+                                             ((2, 130, 7, 9), 3, 0),     # segments, one pixel per thread
+                                             ((40, 9, 32, 32), 7, 0),    # many images, window wider than half the channels
+                                             ((2, 24, 4, 4), 9, 0)])     # window the ring kernel is not built for
 def test_ch_unpool(lib, reducer, shape, nsize, pad):
     """Gradient of chpool(src, nsize): pooled has as many channels as the source."""
     rng = np.random.default_rng(sum(shape) + nsize + reducer)
@@ -329,6 +333,60 @@ def test_sort_by_key(lib, n, ascend):
     wk, wv = orc.sort_by_key(keys.copy(), vals.copy(), ascend)
     gk, gv = lib.sort_by_key(dev(keys), dev(vals), ascend)
     assert np.array_equal(host(gk), wk) and np.array_equal(host(gv), wv)
+
+
+@pytest.mark.parametrize("batch,classes,npos,pad", [
+    (1, 1, 1, 0), (2, 5, 7, 0), (3, 21, 64, 0), (2, 9, 33, 3), (2, 21, 1024, 0), (1, 19, 4100, 4),
+    (2, 100, 512, 0),    # 128-bit tile too large for shared memory: one position per thread
+    (1, 600, 1024, 0),   # no tile fits: exponentials parked in dst
+    (1, 600, 130, 2),
+])
+def test_softmax3d_family(lib, batch, classes, npos, pad):
+    rng = np.random.default_rng(batch * 100000 + classes * 1000 + npos)
+    src = (rng.standard_normal((batch, classes, npos)) * 2).astype(np.float32)
+    want = orc.softmax3d(np.zeros_like(src), src)
+    got = lib.softmax3d(dev(np.zeros_like(src), pad), dev(src, pad))
+    rel = np.abs(host(got).astype(np.float64) - want) / np.maximum(np.abs(want), 1e-30)
+    assert rel.max() <= 1e-5, rel.max()
+    # in place, as the reference allows
+    buf = dev(src, pad)
+    lib.softmax3d(buf, buf)
+    assert_bits(host(buf), host(got))
+    label = rng.integers(0, classes, size=(batch, npos)).astype(np.float32)
+    ignore = float(label[0, 0])
+    for mode in range(4):
+        w = orc.softmax_grad3d(np.full_like(src, 9.0), want, label, mode, ignore, 0.125)
+        g = lib.softmax_grad3d(dev(np.full_like(src, 9.0), pad), dev(want, pad), dev(label, pad), mode, ignore, 0.125)
+        assert_bits(host(g), w)
+
+
+@pytest.mark.parametrize("k,d,n", [(13, 9, 40), (64, 1024, 5000), (1000, 256, 300), (7, 4, 1)])
+def test_index_fill_keeps_the_last_entry(lib, k, d, n):
+    rng = np.random.default_rng(k + d + n)
+    idx = rng.integers(0, k, n).astype(np.int32)
+    src = rng.standard_normal((n, d)).astype(np.float32)
+    t0 = rng.standard_normal((k, d)).astype(np.float32)
+    want = orc.index_fill(t0.copy(), idx, src)
+    got = lib.index_fill(dev(t0), dev(idx), dev(src))
+    assert_bits(host(got), want)
+    # entries outside the table are skipped, the rest behaves as before
+    idx2 = idx.copy()
+    idx2[::3] = np.where(np.arange(len(idx2[::3])) % 2 == 0, -1, k)
+    keep = (idx2 >= 0) & (idx2 < k)
+    want2 = orc.index_fill(t0.copy(), idx2[keep], np.ascontiguousarray(src[keep])) if keep.any() else t0
+    got2 = lib.index_fill(dev(t0), dev(idx2), dev(src))
+    assert_bits(host(got2), want2)
+
+
+@pytest.mark.parametrize("n,nseg", [(1, 1), (200, 6), (70000, 300)])
+def test_vectorized_sort(lib, n, nseg):
+    rng = np.random.default_rng(n)
+    seg = np.sort(rng.integers(0, nseg, size=n)).astype(np.int32)
+    vals = (rng.integers(-40, 40, size=n) / 4.0).astype(np.float32)
+    wv, ws = orc.vectorized_sort(vals.copy(), seg.copy())
+    gv, gs = lib.vectorized_sort(dev(vals), dev(seg))
+    assert_bits(host(gv), wv)
+    assert np.array_equal(host(gs), ws)
 
 
 def test_errors_are_status_codes(lib):

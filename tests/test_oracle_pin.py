@@ -175,6 +175,57 @@ def test_addtakegrad_matches_reference():
         assert np.array_equal(pair[0][0], pair[1][0]) and np.array_equal(pair[0][1], pair[1][1])
 
 
+@needs_ref
+@pytest.mark.parametrize("batch,classes,npos,pad", [(1, 1, 1, 0), (2, 5, 7, 0), (3, 21, 64, 0), (2, 9, 33, 3),
+                                                    (1, 300, 4, 0)])
+def test_softmax3d_family_matches_reference(batch, classes, npos, pad):
+    rng = np.random.default_rng(batch * 1000 + classes * 10 + npos)
+    src = pitched(rnd(rng, (batch, classes, npos), -4.0, 4.0), pad)
+    res = [lib.softmax3d(pitched(np.zeros((batch, classes, npos), np.float32), pad), src) for lib in (orc, ref)]
+    assert same_bits(*res)
+    label = pitched(rng.integers(0, classes, size=(batch, npos)).astype(np.float32), pad)
+    ignore = float(label[0, 0])
+    for mode in range(4):
+        out = [lib.softmax_grad3d(np.full((batch, classes, npos), 9.0, np.float32), res[0], label, mode, ignore,
+                                  0.125) for lib in (orc, ref)]
+        assert same_bits(*out), mode
+
+
+@needs_ref
+def test_index_fill_and_vectorized_sort_match_reference():
+    rng = np.random.default_rng(77)
+    k, d, n = 13, 9, 40
+    src = pitched(rnd(rng, (n, d)), 2)
+    idx = rng.integers(0, k, size=n).astype(np.int32)  # rows named several times: the later source wins
+    res = [lib.index_fill(pitched(np.full((k, d), 3.0, np.float32), 1), idx, src) for lib in (orc, ref)]
+    assert same_bits(*res)
+    seg = np.sort(rng.integers(0, 6, size=200)).astype(np.int32)
+    vals = (rng.integers(0, 20, size=200) / 4.0).astype(np.float32)  # ties inside segments
+    out = [lib.vectorized_sort(vals.copy(), seg.copy()) for lib in (orc, ref)]
+    assert same_bits(out[0][0], out[1][0]) and np.array_equal(out[0][1], out[1][1])
+    assert np.array_equal(out[0][1], seg)
+    for s in range(6):
+        assert np.array_equal(out[0][0][seg == s], np.sort(vals[seg == s]))
+
+
+def test_softmax3d_and_index_fill_known_answers():
+    # constant columns normalise to 1/classes; the gradient subtracts one at the label's class
+    p = orc.softmax3d(np.zeros((2, 8, 3), np.float32), np.full((2, 8, 3), 2.5, np.float32))
+    assert np.array_equal(p, np.full((2, 8, 3), 0.125, np.float32))
+    label = np.array([[0, 7, 3], [1, 1, 1]], np.float32)
+    g = orc.softmax_grad3d(np.zeros_like(p), p, label)
+    want = p.copy()
+    for y in range(2):
+        for n in range(3):
+            want[y, int(label[y, n]), n] -= 1.0
+    assert np.array_equal(g, want)
+    g = orc.softmax_grad3d(np.ones_like(p), p, label, mode=2, ignore_label=1.0)
+    assert np.array_equal(g[1], np.zeros((8, 3), np.float32)) and np.array_equal(g[0], want[0])
+    t = orc.index_fill(np.zeros((4, 2), np.float32), np.array([2, 0, 2], np.int32),
+                       np.array([[1, 1], [2, 2], [3, 3]], np.float32))
+    assert np.array_equal(t, np.array([[2, 2], [0, 0], [3, 3], [0, 0]], np.float32))
+
+
 # ---------------------------------------------------------------- known answers
 def test_ramp_tensor_known_answers():
     """test/test.cu:12-18 fills (3,2,4) with i*0.1+j*0.2+k*0.1 and reduces batch 0."""

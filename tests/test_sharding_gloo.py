@@ -50,8 +50,42 @@ def _worker(rank, world, port, tmpdir):
     counts = torch.tensor([lk.size], dtype=torch.int64)
     dist.all_reduce(counts)
     ok_cnt = int(counts.item()) == n
+    # cyclic ownership with replicated hot rows, on a skewed index list
+    k, d, n = 40, 8, 3000
+    p = (np.arange(k) + 1.0) ** -1.1
+    idx = rng.choice(k, size=n, p=p / p.sum()).astype(np.int32)
+    src = rng.standard_normal((n, d)).astype(np.float32)
+    t0 = rng.standard_normal((k, d)).astype(np.float32)
+    keys, order = idx.copy(), np.arange(n, dtype=np.int32)
+    orc.sort_by_key(keys, order, True)
+    want = orc.addtakegrad_largebatch(t0.copy(), keys, order, src)
+    hot = sharding.hot_rows(keys, 4)
+    tk, to, hk, ho = sharding.route_cyclic_with_hot_rows(keys, order, n, rank, world, hot)
+    mine = np.ascontiguousarray(t0[rank::world]).copy()
+    if tk.size:
+        orc.addtakegrad_largebatch(mine, tk, to, src)
+    partial = np.zeros((hot.size, d), np.float32)
+    if hk.size:
+        orc.addtakegrad_largebatch(partial, hk, ho, src)
+    partial = sharding.allreduce_sum(torch.from_numpy(partial)).numpy()
+    for i, r in enumerate(hot):
+        if r % world == rank:
+            mine[r // world] += partial[i]
+    ref_rows = want[rank::world]
+    cold = np.array([r not in set(hot.tolist()) for r in range(rank, k, world)])
+    ok_cold = bool(np.array_equal(mine[cold].view(np.uint32), ref_rows[cold].view(np.uint32)))
+    rms = np.sqrt(np.mean(ref_rows.astype(np.float64) ** 2, axis=1, keepdims=True))
+    err = np.abs(mine.astype(np.float64) - ref_rows) / np.maximum(np.abs(ref_rows), rms)
+    ok_hot = bool(err.max() <= 1e-5)
+    load = torch.tensor([float(tk.size + hk.size)])
+    total_load = load.clone()
+    dist.all_reduce(total_load)
+    peak = load.clone()
+    dist.all_reduce(peak, op=dist.ReduceOp.MAX)
+    # all entries are handled exactly once and no rank carries much more than its share
+    ok_bal = int(total_load.item()) == n and peak.item() <= 0.6 * n
     with open(os.path.join(tmpdir, "rank%d.txt" % rank), "w") as f:
-        f.write("%d %d %d" % (ok_red, ok_emb, ok_cnt))
+        f.write("%d %d %d %d %d %d" % (ok_red, ok_emb, ok_cnt, ok_cold, ok_hot, ok_bal))
     dist.destroy_process_group()
 
 
@@ -60,4 +94,25 @@ def test_two_ranks_reduce_and_route(tmp_path):
     port = 29600 + os.getpid() % 300
     mp.spawn(_worker, args=(2, port, str(tmp_path)), nprocs=2, join=True)
     for r in range(2):
-        assert open(tmp_path / ("rank%d.txt" % r)).read() == "1 1 1"
+        assert open(tmp_path / ("rank%d.txt" % r)).read() == "1 1 1 1 1 1"
+
+
+def test_hot_rows_balance_a_zipf_batch():
+    """Contiguous row ownership leaves one rank with almost everything; cyclic ownership plus a
+    handful of replicated hot rows brings every rank close to 1/world of the entries."""
+    rng = np.random.default_rng(3)
+    k, n, world = 262144, 1 << 18, 8
+    p = (np.arange(k) + 1.0) ** -1.1
+    keys = np.sort(rng.choice(k, size=n, p=p / p.sum()).astype(np.int32))
+    order = rng.permutation(n).astype(np.int32)
+    contiguous = [sharding.route_sorted_indices(keys, order, k, r, world)[0].size for r in range(world)]
+    assert max(contiguous) > 0.8 * n
+    hot = sharding.hot_rows(keys, 64)
+    loads, seen = [], 0
+    for r in range(world):
+        tk, to, hk, ho = sharding.route_cyclic_with_hot_rows(keys, order, n, r, world, hot)
+        assert np.all(np.diff(tk) >= 0) and np.all(np.diff(hk) >= 0)
+        loads.append(tk.size + hk.size)
+        seen += tk.size + hk.size
+    assert seen == n
+    assert max(loads) <= 1.1 * n / world
