@@ -414,6 +414,16 @@ def kernel_cases(lib, torch, small=False):
     yield ("index_fill", "IndexFill %d rows of %d into %dx%d" % (nf, df, kf, df), 8 * nf * df + 8 * nf + 4 * kf,
            nf * df, lambda: lib.index_fill(ftab, fidx, fsrc), 10)
     del fidx, fsrc, ftab
+    # index-remapping expressions: a permutation that keeps the last axis (128-bit path), one that
+    # moves it (element path), and a mirrored copy
+    rs = (32, 256, 56, 56) if small else (256, 256, 56, 56)
+    RA = torch.rand(rs, device=dev, generator=g)
+    RB = torch.empty_like(RA)
+    RD = torch.empty_like(RA)
+    for cid, name in ((7, "transpose(A,(0,2,1,3))"), (6, "swapaxis<3,1>(A)"), (12, "mirror(A)")):
+        yield ("remap_%d" % cid, "%s %s" % (name, rs), 8 * RA.numel(), RA.numel(),
+               lambda cid=cid: lib.remap_case(cid, RD, RA, RB), 10)
+    del RA, RB, RD
     torch.cuda.empty_cache()
 
 

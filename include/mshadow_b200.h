@@ -204,6 +204,35 @@ int msb_vectorized_sort_f32_i32(float *values, int32_t *segments, int64_t n, msb
 int msb_index_fill_f32_i32(float *dst, const int32_t *index, const float *src, int64_t k,
                            int64_t d, int64_t nidx, msb_stream_t stream);
 
+/*
+ * Index-remapping expressions (pure data movement) evaluated by MapExp on dense fp32 tensors A
+ * and B of shape (n, c, h, w); p0 and p1 are per-case parameters.  Expression plans cannot
+ * cross a C ABI, so a fixed set is exported, as for msb_expr_case_f32:
+ *    0  dst = reshape(A, Shape4(n, h, c, w))                 mshadow/extension/reshape.h
+ *    1  dst = slice<1>(A, p0, p1)                            mshadow/extension/slice.h
+ *    2  dst = slice<3>(A, p0, p1)
+ *    3  dst = concat<1>(A, B)                                mshadow/extension/concat.h
+ *    4  dst = concat<3>(A, B)
+ *    5  dst = swapaxis<2, 1>(A)                              mshadow/extension/swapaxis.h
+ *    6  dst = swapaxis<3, 1>(A)
+ *    7  dst = transpose(A, Shape4(0, 2, 1, 3))               mshadow/extension/transpose.h
+ *    8  dst = transpose(A, Shape4(3, 1, 0, 2))
+ *    9  dst = pad(A, p0, p1)                                 mshadow/extension/pad.h
+ *   10  dst = crop(A, Shape2(p0, p1))                        mshadow/extension/crop.h
+ *   11  dst = crop(A, Shape2(p0, p1), h - p0, w - p1)
+ *   12  dst = mirror(A)                                      mshadow/extension/mirror.h
+ *   13  dst = flip(A, 1)                                     mshadow/extension/flip.h
+ *   14  dst = B; slice<1>(dst, p0, p1) = slice<1>(A, p0, p1) + 1.0f
+ *   15  concat<1>(dst[0:n], dst[n:2n]) = F<op::identity>(concat<1>(B, A)), dst is (2n, c, h, w)
+ *   16  dst = crop(pad(A, p0, p1), Shape2(h, w)) + mirror(A)
+ * msb_remap_shape reports the (dense) shape dst must have.  Arguments the expressions' own
+ * checks reject (a slice out of range, a crop larger than the image) return MSB_ERR_SHAPE.
+ */
+int msb_remap_shape(int id, int64_t n, int64_t c, int64_t h, int64_t w, int64_t p0, int64_t p1,
+                    int64_t *out_shape);
+int msb_remap_case_f32(int id, float *dst, const float *A, const float *B, int64_t n, int64_t c,
+                       int64_t h, int64_t w, int64_t p0, int64_t p1, msb_stream_t stream);
+
 /* Softmax(Tensor<gpu,3>): softmax over the middle axis of (batch, classes, positions);
    ld_* = pitch of the last axis: mshadow/tensor_gpu-inl.h:163-167 */
 int msb_softmax3d_f32(float *dst, const float *src, int64_t batch, int64_t classes, int64_t npos,

@@ -68,6 +68,8 @@ _SIGNATURES = {
     "msb_sort_by_key_i32": [vp, vp, i64, cint, vp],
     "msb_vectorized_sort_f32_i32": [vp, vp, i64, vp],
     "msb_index_fill_f32_i32": [vp, vp, vp, i64, i64, i64, vp],
+    "msb_remap_shape": [cint, i64, i64, i64, i64, i64, i64, vp],
+    "msb_remap_case_f32": [cint, vp, vp, vp, i64, i64, i64, i64, i64, i64, vp],
     "msb_softmax3d_f32": [vp, vp, i64, i64, i64, i64, i64, vp],
     "msb_softmax_grad3d_f32": [vp, vp, vp, i64, i64, i64, i64, i64, i64, cint, f32, f32, vp],
 }
@@ -239,6 +241,17 @@ class Library:
     def sort_by_key(self, keys, values, ascend=True, stream=None):
         self.call("msb_sort_by_key_i32", _ptr(keys), _ptr(values), keys.shape[0], int(ascend), stream)
         return keys, values
+
+    def remap_shape(self, cid, shape, p0=0, p1=0):
+        out = (i64 * 4)()
+        n, c, h, w = shape
+        self.call("msb_remap_shape", cid, n, c, h, w, p0, p1, C.cast(out, vp))
+        return tuple(int(v) for v in out)
+
+    def remap_case(self, cid, dst, A, B, p0=0, p1=0, stream=None):
+        n, c, h, w = A.shape
+        self.call("msb_remap_case_f32", cid, _ptr(dst), _ptr(A), _ptr(B), n, c, h, w, p0, p1, stream)
+        return dst
 
     def vectorized_sort(self, values, segments, stream=None):
         self.call("msb_vectorized_sort_f32_i32", _ptr(values), _ptr(segments), values.shape[0], stream)

@@ -514,6 +514,87 @@ int msb_index_fill_f32_i32(float *dst, const int32_t *index, const float *src, i
   MSB_GUARD_END
 }
 
+namespace {
+typedef Tensor<gpu, 4, float> G4;
+inline G4 Img(const float *p, int64_t n, int64_t c, int64_t h, int64_t w, Stream<gpu> *s) {
+  return G4(const_cast<float *>(p), Shape4(n, c, h, w), static_cast<index_t>(w), s);
+}
+/*! \brief result shape of an index-remapping case, from the expression objects themselves */
+inline Shape<4> RemapShape(int id, int64_t n, int64_t c, int64_t h, int64_t w, int64_t p0, int64_t p1) {
+  const G4 a = Img(nullptr, n, c, h, w, nullptr);
+  switch (id) {
+    case 0: return reshape(a, Shape4(n, h, c, w)).shape_;
+    case 1: return slice<1>(a, p0, p1).shape_;
+    case 2: return slice<3>(a, p0, p1).shape_;
+    case 3: return concat<1>(a, a).shape_;
+    case 4: return concat<3>(a, a).shape_;
+    case 5: return swapaxis<2, 1>(a).shape_;
+    case 6: return swapaxis<3, 1>(a).shape_;
+    case 7: return transpose(a, Shape4(0, 2, 1, 3)).shape_;
+    case 8: return transpose(a, Shape4(3, 1, 0, 2)).shape_;
+    case 9: return pad(a, p0, p1).shape_;
+    case 10: return crop(a, Shape2(p0, p1)).shape_;
+    case 11: return crop(a, Shape2(p0, p1), h - p0, w - p1).shape_;
+    case 15: return Shape4(2 * n, c, h, w);
+    default: return a.shape_;
+  }
+}
+inline bool RemapArgsOk(int id, int64_t n, int64_t c, int64_t h, int64_t w, int64_t p0, int64_t p1) {
+  if (n <= 0 || c <= 0 || h <= 0 || w <= 0 || p0 < 0 || p1 < 0) return false;
+  if (!FitsIndex(n * c) || !FitsIndex(n * c * h) || !FitsIndex(2 * n * c * h * w)) return false;
+  if (id == 9 || id == 16) return FitsIndex(n * c * (h + 2 * p0) * (w + 2 * p1));
+  return true;
+}
+}  // namespace
+
+int msb_remap_shape(int id, int64_t n, int64_t c, int64_t h, int64_t w, int64_t p0, int64_t p1, int64_t *out_shape) {
+  MSB_REQUIRE(id >= 0 && id <= 16, MSB_ERR_ARGUMENT, "unknown expression id");
+  MSB_REQUIRE(RemapArgsOk(id, n, c, h, w, p0, p1), MSB_ERR_SHAPE, "extent out of range");
+  MSB_REQUIRE(out_shape != nullptr, MSB_ERR_ARGUMENT, "null pointer");
+  MSB_GUARD_BEGIN
+  const Shape<4> s = RemapShape(id, n, c, h, w, p0, p1);
+  for (int i = 0; i < 4; ++i) out_shape[i] = s[i];
+  MSB_GUARD_END
+}
+
+int msb_remap_case_f32(int id, float *dst, const float *A, const float *B, int64_t n, int64_t c, int64_t h, int64_t w,
+                       int64_t p0, int64_t p1, msb_stream_t stream) {
+  MSB_REQUIRE(id >= 0 && id <= 16, MSB_ERR_ARGUMENT, "unknown expression id");
+  MSB_REQUIRE(RemapArgsOk(id, n, c, h, w, p0, p1), MSB_ERR_SHAPE, "extent out of range");
+  MSB_REQUIRE(dst && A && B, MSB_ERR_ARGUMENT, "null pointer");
+  MSB_GUARD_BEGIN
+  BorrowedStream st(stream);
+  const Shape<4> o = RemapShape(id, n, c, h, w, p0, p1);
+  const G4 a = Img(A, n, c, h, w, st.get()), b = Img(B, n, c, h, w, st.get());
+  G4 d = Img(dst, o[0], o[1], o[2], o[3], st.get());
+  switch (id) {
+    case 0: d = reshape(a, Shape4(n, h, c, w)); break;
+    case 1: d = slice<1>(a, p0, p1); break;
+    case 2: d = slice<3>(a, p0, p1); break;
+    case 3: d = concat<1>(a, b); break;
+    case 4: d = concat<3>(a, b); break;
+    case 5: d = swapaxis<2, 1>(a); break;
+    case 6: d = swapaxis<3, 1>(a); break;
+    case 7: d = transpose(a, Shape4(0, 2, 1, 3)); break;
+    case 8: d = transpose(a, Shape4(3, 1, 0, 2)); break;
+    case 9: d = pad(a, p0, p1); break;
+    case 10: d = crop(a, Shape2(p0, p1)); break;
+    case 11: d = crop(a, Shape2(p0, p1), h - p0, w - p1); break;
+    case 12: d = mirror(a); break;
+    case 13: d = flip(a, 1); break;
+    case 14:
+      Copy(d, b, st.get());
+      slice<1>(d, p0, p1) = slice<1>(a, p0, p1) + 1.0f;
+      break;
+    case 15: {
+      G4 d1 = Img(dst, n, c, h, w, st.get()), d2 = Img(dst + n * c * h * w, n, c, h, w, st.get());
+      concat<1>(d1, d2) = F<op::identity>(concat<1>(b, a));
+    } break;
+    default: d = crop(pad(a, p0, p1), Shape2(h, w)) + mirror(a); break;
+  }
+  MSB_GUARD_END
+}
+
 int msb_vectorized_sort_f32_i32(float *values, int32_t *segments, int64_t n, msb_stream_t stream) {
   MSB_REQUIRE(FitsIndex(n), MSB_ERR_SHAPE, "extent out of range");
   if (n == 0) return MSB_OK;

@@ -8,4 +8,5 @@
 #include "./extension/broadcast.h"
 #include "./extension/reduceto1d.h"
 #include "./extension/pooling.h"
+#include "./extension/remap.h"
 #endif  // MSHADOW_EXTENSION_H_

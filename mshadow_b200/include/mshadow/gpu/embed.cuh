@@ -315,21 +315,43 @@ IndexFillOwnerKernel(int32_t *last, const IndexType *index, uint32_t n, int32_t 
   if (j >= 0 && j < k) atomicMax(last + j, static_cast<int32_t>(y));
 }
 
-/*! \brief one CTA row per batch entry (grid-stride); the entry copies its source row if it is the last one naming that table row */
+/*! \brief a CTA takes four batch entries per grid-stride sweep; an entry copies its source row if it is the last one
+ *  naming that table row */
 template <int kLanes>
 __global__ void __launch_bounds__(256)
 IndexFillCopyKernel(float *dst, int64_t ld_dst, const int32_t *last, const int32_t *index, const float *src,
                     int64_t ld_src, uint32_t n, uint32_t items, int32_t k) {
-  for (uint32_t y = blockIdx.x; y < n; y += gridDim.x) {
-    const int32_t j = index[y];
-    if (j < 0 || j >= k || last[j] != static_cast<int32_t>(y)) continue;
-    const float *in = src + y * ld_src;
-    float *out = dst + j * ld_dst;
+  constexpr int kRows = 4;  // batch entries per sweep: their index look-ups and row loads overlap
+  for (uint32_t y0 = blockIdx.x * kRows; y0 < n; y0 += gridDim.x * kRows) {
+    int32_t j[kRows];
+    bool live[kRows];
+#pragma unroll
+    for (int r = 0; r < kRows; ++r) j[r] = y0 + r < n ? index[y0 + r] : -1;
+#pragma unroll
+    for (int r = 0; r < kRows; ++r) live[r] = j[r] >= 0 && j[r] < k && last[j[r]] == static_cast<int32_t>(y0 + r);
     for (uint32_t i = threadIdx.x; i < items; i += 256) {
-      if (kLanes == 4) {
-        reinterpret_cast<float4 *>(out)[i] = __ldcs(reinterpret_cast<const float4 *>(in) + i);
-      } else {
-        out[i] = __ldcs(in + i);
+      float v[kRows][kLanes];
+#pragma unroll
+      for (int r = 0; r < kRows; ++r) {
+        if (!live[r]) continue;
+        const float *in = src + (y0 + r) * ld_src;
+        if (kLanes == 4) {
+          const float4 p = __ldcs(reinterpret_cast<const float4 *>(in) + i);
+          v[r][0] = p.x, v[r][1 % kLanes] = p.y, v[r][2 % kLanes] = p.z, v[r][3 % kLanes] = p.w;
+        } else {
+          v[r][0] = __ldcs(in + i);
+        }
+      }
+#pragma unroll
+      for (int r = 0; r < kRows; ++r) {
+        if (!live[r]) continue;
+        float *out = dst + j[r] * ld_dst;
+        if (kLanes == 4) {
+          __stcs(reinterpret_cast<float4 *>(out) + i,
+                 make_float4(v[r][0], v[r][1 % kLanes], v[r][2 % kLanes], v[r][3 % kLanes]));
+        } else {
+          __stcs(out + i, v[r][0]);
+        }
       }
     }
   }
@@ -349,7 +371,8 @@ inline void IndexFillLaunch(float *dst, int64_t ld_dst, const int32_t *index, co
   const bool vec = width % 4 == 0 && ld_src % 4 == 0 && ld_dst % 4 == 0 &&
                    reinterpret_cast<uintptr_t>(src) % 16 == 0 && reinterpret_cast<uintptr_t>(dst) % 16 == 0;
   const int cap = gpu_rt::CurrentDevice().sm_count * 8;
-  const int grid = n < cap ? static_cast<int>(n) : cap;
+  const int64_t sweeps = (n + 3) / 4;  // IndexFillCopyKernel takes four batch entries per sweep
+  const int grid = sweeps < cap ? static_cast<int>(sweeps) : cap;
   if (vec) {
     IndexFillCopyKernel<4><<<grid, 256, 0, stream>>>(dst, ld_dst, last, index, src, ld_src, un,
                                                     static_cast<uint32_t>(width / 4), static_cast<int32_t>(k));

@@ -441,6 +441,131 @@ void ORC(vectorized_sort)(float *values, int32_t *segments, int64_t n) {
   free(perm); free(tmp); free(v2); free(s2);
 }
 
+/* ---- index-remapping expressions: every Plan::Eval(i, j) of the reference restated on the
+        flattened (rows, last extent) view that MapExp walks (tensor_cpu-inl.h:143-201) ---- */
+
+void ORC(remap_shape)(int id, int64_t n, int64_t c, int64_t h, int64_t w, int64_t p0, int64_t p1,
+                      int64_t o[4]) {
+  o[0] = n; o[1] = c; o[2] = h; o[3] = w;
+  switch (id) {
+    case 0: case 5: case 7: o[1] = h; o[2] = c; break;
+    case 1: o[1] = p1 - p0; break;
+    case 2: o[3] = p1 - p0; break;
+    case 3: o[1] = 2 * c; break;
+    case 4: o[3] = 2 * w; break;
+    case 6: o[1] = w; o[3] = c; break;
+    case 8: o[0] = w; o[1] = c; o[2] = n; o[3] = h; break;
+    case 9: o[2] = h + 2 * p0; o[3] = w + 2 * p1; break;
+    case 10: case 11: o[2] = p0; o[3] = p1; break;
+    case 15: o[0] = 2 * n; break;
+    default: break;
+  }
+}
+
+/* A(row, col) of a dense tensor whose last extent is `w` */
+#define AT(p, w, row, col) ((p)[(int64_t)(row) * (w) + (col)])
+
+/* extension/pad.h:84-95 on a source of `sh` x `sw` planes */
+static float pad_eval(const float *A, int64_t sh, int64_t sw, int64_t py, int64_t px, int64_t i, int64_t j) {
+  const int64_t nh = sh + 2 * py;
+  const int64_t y = i % nh, cc = i / nh;
+  if (y < py || j < px) return 0.0f;
+  const int64_t hh = y - py, ww = j - px;
+  return (hh < sh && ww < sw) ? AT(A, sw, cc * sh + hh, ww) : 0.0f;
+}
+
+void ORC(remap_case)(int id, float *dst, const float *A, const float *B, int64_t n, int64_t c,
+                     int64_t h, int64_t w, int64_t p0, int64_t p1) {
+  int64_t o[4];
+  ORC(remap_shape)(id, n, c, h, w, p0, p1, o);
+  const int64_t rows = o[0] * o[1] * o[2], cols = o[3];
+  if (id == 14) memcpy(dst, B, (size_t)(n * c * h * w) * sizeof(float));
+#pragma omp parallel for
+  for (int64_t i = 0; i < rows; ++i) {
+    for (int64_t j = 0; j < cols; ++j) {
+      float v = 0.0f;
+      int store = 1;
+      switch (id) {
+        case 0: {  /* reshape.h:58-61: linear offset re-split by the source's last extent */
+          const int64_t idx = i * cols + j;
+          v = AT(A, w, idx / w, idx % w);
+        } break;
+        case 1: {  /* slice.h:101-109, dimslice = 1: height = h */
+          const int64_t y = i % h, t = i / h, ch = p1 - p0;
+          const int64_t cc = t % ch + p0, b = t / ch;
+          v = AT(A, w, (b * c + cc) * h + y, j);
+        } break;
+        case 2:  /* slice.h:132-134: last dimension */
+          v = AT(A, w, i, j + p0);
+          break;
+        case 3: {  /* concat.h:120-132, dimcat = 1 */
+          const int64_t y = i % h, t = i / h;
+          const int64_t cc = t % (2 * c), b = t / (2 * c);
+          v = cc < c ? AT(A, w, (b * c + cc) * h + y, j) : AT(B, w, (b * c + cc - c) * h + y, j);
+        } break;
+        case 4:  /* concat.h:163-169: last dimension */
+          v = j < w ? AT(A, w, i, j) : AT(B, w, i, j - w);
+          break;
+        case 5: {  /* swapaxis.h:72-84, a1 = 2, a2 = 1: shapey = 1, shapez = c(out axis 2), shapec = 1, shapen = h */
+          const int64_t z = i % c, t = i / c;
+          const int64_t nn = t % h, b = t / h;
+          v = AT(A, w, (b * c + z) * h + nn, j);
+        } break;
+        case 6: {  /* swapaxis.h:97-103, a1 = 3, a2 = 1: out (n, w, h, c); shapex = c, shapey = h, shapez = w */
+          const int64_t y = i % h, t = i / h;
+          const int64_t z = t % w, b = t / w;
+          v = AT(A, w, (b * c + j) * h + y, z);
+        } break;
+        case 7: case 8: {  /* transpose.h:64-72 */
+          const int64_t ss[4] = {c * h * w, h * w, w, 1};  /* dense strides of the source */
+          const int ax[2][4] = {{0, 2, 1, 3}, {3, 1, 0, 2}};
+          const int *a = ax[id - 7];
+          int64_t idx = j * ss[a[3]], r = i;
+          for (int k = 2; k >= 0; --k) {
+            idx += (r % o[k]) * ss[a[k]];
+            r /= o[k];
+          }
+          v = AT(A, w, idx / w, idx % w);
+        } break;
+        case 9:
+          v = pad_eval(A, h, w, p0, p1, i, j);
+          break;
+        case 10: case 11: {  /* crop.h:96-103 */
+          const int64_t ph = id == 10 ? (h - p0) / 2 : h - p0, pw = id == 10 ? (w - p1) / 2 : w - p1;
+          const int64_t y = i % p0, cc = i / p0;
+          v = AT(A, w, cc * h + y + ph, j + pw);
+        } break;
+        case 12:  /* mirror.h:51-53 */
+          v = AT(A, w, i, w - j - 1);
+          break;
+        case 13: {  /* flip.h:99-107, dim = 1: trailing = h*w, stride = c */
+          int64_t idx = i * w + j;
+          const int64_t low = idx % (h * w);
+          int64_t high = idx / (h * w);
+          const int64_t x = high % c;
+          high /= c;
+          idx = (high * c + c - 1 - x) * (h * w) + low;
+          v = AT(A, w, idx / w, idx % w);
+        } break;
+        case 14: {  /* destination rows (b, cc, y) with cc in [p0, p1) are overwritten */
+          const int64_t cc = (i / h) % c;
+          if (cc >= p0 && cc < p1) v = AT(A, w, i, j) + 1.0f;
+          else store = 0;
+        } break;
+        case 15: {  /* first n images receive B, the following n receive A */
+          v = i < n * c * h ? AT(B, w, i, j) : AT(A, w, i - n * c * h, j);
+        } break;
+        default: {  /* 16: centred crop of the padded tensor gives A back */
+          const int64_t nh = h + 2 * p0;
+          const int64_t y = i % h, cc = i / h;
+          v = pad_eval(A, h, w, p0, p1, cc * nh + y + p0, j + p1) + AT(A, w, i, w - j - 1);
+        } break;
+      }
+      if (store) dst[i * cols + j] = v;
+    }
+  }
+}
+
 int ORC(num_threads)(void) {
 #ifdef _OPENMP
   return omp_get_max_threads();

@@ -132,6 +132,34 @@ void ORC(index_fill)(float *dst, const int32_t *index, const float *src, int64_t
    two stable pair sorts (tensor_cpu-inl.h:562-567) */
 void ORC(vectorized_sort)(float *values, int32_t *segments, int64_t n);
 
+/*
+ * Index-remapping expressions evaluated through MapExp, on dense fp32 tensors A and B of shape
+ * (n, c, h, w); p0, p1 are per-case parameters.  `dst` is dense with the case's result shape,
+ * which remap_shape() reports.
+ *    0  dst = reshape(A, Shape4(n, h, c, w))                    extension/reshape.h
+ *    1  dst = slice<1>(A, p0, p1)                               extension/slice.h
+ *    2  dst = slice<3>(A, p0, p1)
+ *    3  dst = concat<1>(A, B)                                   extension/concat.h
+ *    4  dst = concat<3>(A, B)
+ *    5  dst = swapaxis<2, 1>(A)                                 extension/swapaxis.h
+ *    6  dst = swapaxis<3, 1>(A)
+ *    7  dst = transpose(A, Shape4(0, 2, 1, 3))                  extension/transpose.h
+ *    8  dst = transpose(A, Shape4(3, 1, 0, 2))
+ *    9  dst = pad(A, p0, p1)                                    extension/pad.h
+ *   10  dst = crop(A, Shape2(p0, p1))                           extension/crop.h (centred)
+ *   11  dst = crop(A, Shape2(p0, p1), h - p0, w - p1)
+ *   12  dst = mirror(A)                                         extension/mirror.h
+ *   13  dst = flip(A, 1)                                        extension/flip.h
+ *   14  dst = B;  slice<1>(dst, p0, p1) = slice<1>(A, p0, p1) + 1.0f      (slice as l-value)
+ *   15  concat<1>(dst[0:n], dst[n:2n]) = F<op::identity>(concat<1>(B, A))   dst is (2n, c, h, w) (concat as l-value)
+ *   16  dst = crop(pad(A, p0, p1), Shape2(h, w)) + mirror(A)    (nesting)
+ */
+#define ORC_NUM_REMAP_CASES 17
+void ORC(remap_shape)(int id, int64_t n, int64_t c, int64_t h, int64_t w, int64_t p0, int64_t p1,
+                      int64_t out_shape[4]);
+void ORC(remap_case)(int id, float *dst, const float *A, const float *B, int64_t n, int64_t c,
+                     int64_t h, int64_t w, int64_t p0, int64_t p1);
+
 /* number of OpenMP threads the library will use (for cpu_baseline.cores) */
 int ORC(num_threads)(void);
 

@@ -230,6 +230,64 @@ void ref_vectorized_sort(float *values, int32_t *segments, int64_t n) {
   VectorizedSort(v, s);
 }
 
+void ref_remap_shape(int id, int64_t n, int64_t c, int64_t h, int64_t w, int64_t p0, int64_t p1,
+                     int64_t o[4]) {
+  /* shapes come from the reference's own expression objects */
+  float dummy = 0.0f;
+  T4 a = img(&dummy, n, c, h, w, w);
+  Shape<4> s = a.shape_;
+  switch (id) {
+    case 0: s = reshape(a, Shape4(n, h, c, w)).shape_; break;
+    case 1: s = slice<1>(a, p0, p1).shape_; break;
+    case 2: s = slice<3>(a, p0, p1).shape_; break;
+    case 3: s = concat<1>(a, a).shape_; break;
+    case 4: s = concat<3>(a, a).shape_; break;
+    case 5: s = swapaxis<2, 1>(a).shape_; break;
+    case 6: s = swapaxis<3, 1>(a).shape_; break;
+    case 7: s = transpose(a, Shape4(0, 2, 1, 3)).shape_; break;
+    case 8: s = transpose(a, Shape4(3, 1, 0, 2)).shape_; break;
+    case 9: s = pad(a, p0, p1).shape_; break;
+    case 10: s = crop(a, Shape2(p0, p1)).shape_; break;
+    case 11: s = crop(a, Shape2(p0, p1), h - p0, w - p1).shape_; break;
+    case 15: s[0] = 2 * n; break;
+    default: break;
+  }
+  for (int i = 0; i < 4; ++i) o[i] = s[i];
+}
+
+void ref_remap_case(int id, float *dst, const float *A, const float *B, int64_t n, int64_t c,
+                    int64_t h, int64_t w, int64_t p0, int64_t p1) {
+  int64_t o[4];
+  ref_remap_shape(id, n, c, h, w, p0, p1, o);
+  T4 a = img(A, n, c, h, w, w), b = img(B, n, c, h, w, w);
+  T4 d = img(dst, o[0], o[1], o[2], o[3], o[3]);
+  switch (id) {
+    case 0: d = reshape(a, Shape4(n, h, c, w)); break;
+    case 1: d = slice<1>(a, p0, p1); break;
+    case 2: d = slice<3>(a, p0, p1); break;
+    case 3: d = concat<1>(a, b); break;
+    case 4: d = concat<3>(a, b); break;
+    case 5: d = swapaxis<2, 1>(a); break;
+    case 6: d = swapaxis<3, 1>(a); break;
+    case 7: d = transpose(a, Shape4(0, 2, 1, 3)); break;
+    case 8: d = transpose(a, Shape4(3, 1, 0, 2)); break;
+    case 9: d = pad(a, p0, p1); break;
+    case 10: d = crop(a, Shape2(p0, p1)); break;
+    case 11: d = crop(a, Shape2(p0, p1), h - p0, w - p1); break;
+    case 12: d = mirror(a); break;
+    case 13: d = flip(a, 1); break;
+    case 14:
+      Copy(d, b);
+      slice<1>(d, p0, p1) = slice<1>(a, p0, p1) + 1.0f;
+      break;
+    case 15: {
+      T4 d1 = img(dst, n, c, h, w, w), d2 = img(dst + n * c * h * w, n, c, h, w, w);
+      concat<1>(d1, d2) = F<op::identity>(concat<1>(b, a));
+    } break;
+    default: d = crop(pad(a, p0, p1), Shape2(h, w)) + mirror(a); break;
+  }
+}
+
 int ref_num_threads(void) {
 #ifdef _OPENMP
   return omp_get_max_threads();

@@ -162,10 +162,45 @@ class Checker:
                                i64(_ld(dst)), i64(_ld(src)))
         return dst
 
+    def remap_shape(self, cid, shape, p0=0, p1=0):
+        out = (i64 * 4)()
+        n, c, h, w = shape
+        self._fn("remap_shape")(C.c_int(cid), i64(n), i64(c), i64(h), i64(w), i64(p0), i64(p1), out)
+        return tuple(int(v) for v in out)
+
+    def remap_case(self, cid, A, B, p0=0, p1=0, fill=0.0):
+        """Evaluates index-remapping case `cid` on dense (n, c, h, w) inputs; returns the result."""
+        assert A.flags.c_contiguous and B.flags.c_contiguous and A.shape == B.shape
+        n, c, h, w = A.shape
+        dst = np.full(self.remap_shape(cid, A.shape, p0, p1), np.float32(fill), dtype=np.float32)
+        self._fn("remap_case")(C.c_int(cid), _fp(dst), _fp(A), _fp(B), i64(n), i64(c), i64(h), i64(w), i64(p0),
+                               i64(p1))
+        return dst
+
     def vectorized_sort(self, values, segments):
         assert values.flags.c_contiguous
         self._fn("vectorized_sort")(_fp(values), _ip(segments), i64(values.shape[0]))
         return values, segments
+
+
+NUM_REMAP_CASES = 17
+
+
+def remap_params(cid, shape):
+    """Valid (p0, p1) pairs for index-remapping case `cid` on an (n, c, h, w) input: ranges that
+    touch the borders, unaligned and 4-aligned boundaries."""
+    n, c, h, w = shape
+    if cid in (1, 14):
+        cand = {(0, c), (1, c), (0, max(1, c - 1)), (c // 2, c), (min(4, c - 1), c)}
+        return sorted(p for p in cand if p[0] < p[1])
+    if cid == 2:
+        cand = {(0, w), (1, w), (0, max(1, w - 1)), (min(4, w - 1), w), (w // 2, w)}
+        return sorted(p for p in cand if p[0] < p[1])
+    if cid in (9, 16):
+        return [(0, 0), (1, 2), (2, 4), (3, 0)]
+    if cid in (10, 11):
+        return sorted({(h, w), (1, 1), (max(1, h - 2), max(1, w - 8)), (max(1, h - 1), max(1, w - 3))})
+    return [(0, 0)]
 
 
 _cache = {}

@@ -389,6 +389,34 @@ def test_vectorized_sort(lib, n, nseg):
     assert np.array_equal(host(gs), ws)
 
 
+@pytest.mark.parametrize("cid", range(cc.NUM_REMAP_CASES))
+@pytest.mark.parametrize("shape", [(2, 3, 4, 5), (3, 8, 16, 64), (2, 5, 7, 33), (1, 4, 8, 128), (2, 2, 3, 1),
+                                   (4, 12, 20, 24)])
+def test_remap_expressions(lib, cid, shape):
+    """Index-remapping expressions are data movement: bit-exact, on the 128-bit path (aligned
+    widths and boundaries) and on the element path alike."""
+    rng = np.random.default_rng(cid * 1000 + sum(shape))
+    A = rng.uniform(-1, 1, shape).astype(np.float32)
+    B = rng.uniform(-1, 1, shape).astype(np.float32)
+    for p0, p1 in cc.remap_params(cid, shape):
+        want = orc.remap_case(cid, A, B, p0, p1, fill=9.0)
+        assert lib.remap_shape(cid, shape, p0, p1) == want.shape
+        got = lib.remap_case(cid, torch.full(want.shape, 9.0, device="cuda"), dev(A), dev(B), p0, p1)
+        assert_bits(host(got), want)
+
+
+def test_remap_argument_errors(lib):
+    import ctypes as C
+    z = torch.zeros(2, 3, 4, 5, device="cuda")
+    p = C.c_void_p(z.data_ptr())
+    st, msg = lib.status("msb_remap_case_f32", 1, p, p, p, 2, 3, 4, 5, 2, 9, None)   # slice beyond the channels
+    assert st == 2 and "slice" in msg.lower()
+    st, msg = lib.status("msb_remap_case_f32", 10, p, p, p, 2, 3, 4, 5, 7, 2, None)  # crop taller than the image
+    assert st == 2 and "height" in msg
+    st, _ = lib.status("msb_remap_case_f32", 99, p, p, p, 2, 3, 4, 5, 0, 0, None)
+    assert st == 1
+
+
 def test_errors_are_status_codes(lib):
     import ctypes as C
     z = torch.zeros(4, 4, device="cuda")

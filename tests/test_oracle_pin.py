@@ -208,6 +208,42 @@ def test_index_fill_and_vectorized_sort_match_reference():
         assert np.array_equal(out[0][0][seg == s], np.sort(vals[seg == s]))
 
 
+@needs_ref
+@pytest.mark.parametrize("cid", range(cc.NUM_REMAP_CASES))
+@pytest.mark.parametrize("shape", [(2, 3, 4, 5), (1, 8, 6, 16), (3, 5, 1, 7), (2, 2, 3, 1)])
+def test_remap_cases_match_reference(cid, shape):
+    rng = np.random.default_rng(cid * 100 + sum(shape))
+    A, B = rnd(rng, shape), rnd(rng, shape)
+    for p0, p1 in cc.remap_params(cid, shape):
+        assert orc.remap_shape(cid, shape, p0, p1) == ref.remap_shape(cid, shape, p0, p1)
+        res = [lib.remap_case(cid, A, B, p0, p1, fill=9.0) for lib in (orc, ref)]
+        assert same_bits(*res), (cid, p0, p1)
+
+
+def test_remap_known_answers():
+    A = np.arange(2 * 3 * 2 * 4, dtype=np.float32).reshape(2, 3, 2, 4)
+    B = -A
+    assert np.array_equal(orc.remap_case(0, A, B), A.reshape(2, 2, 3, 4))
+    assert np.array_equal(orc.remap_case(1, A, B, 1, 3), A[:, 1:3])
+    assert np.array_equal(orc.remap_case(2, A, B, 1, 4), A[..., 1:4])
+    assert np.array_equal(orc.remap_case(3, A, B), np.concatenate([A, B], axis=1))
+    assert np.array_equal(orc.remap_case(4, A, B), np.concatenate([A, B], axis=3))
+    assert np.array_equal(orc.remap_case(5, A, B), A.swapaxes(1, 2))
+    assert np.array_equal(orc.remap_case(6, A, B), A.swapaxes(1, 3))
+    assert np.array_equal(orc.remap_case(7, A, B), A.transpose(0, 2, 1, 3))
+    assert np.array_equal(orc.remap_case(8, A, B), A.transpose(3, 1, 0, 2))
+    assert np.array_equal(orc.remap_case(9, A, B, 1, 2), np.pad(A, ((0, 0), (0, 0), (1, 1), (2, 2))))
+    assert np.array_equal(orc.remap_case(10, A, B, 2, 2), A[:, :, :, 1:3])
+    assert np.array_equal(orc.remap_case(11, A, B, 1, 3), A[:, :, 1:, 1:])
+    assert np.array_equal(orc.remap_case(12, A, B), A[..., ::-1])
+    assert np.array_equal(orc.remap_case(13, A, B), A[:, ::-1])
+    want = B.copy()
+    want[:, 1:3] = A[:, 1:3] + 1
+    assert np.array_equal(orc.remap_case(14, A, B, 1, 3), want)
+    assert np.array_equal(orc.remap_case(15, A, B), np.concatenate([B, A], axis=0))
+    assert np.array_equal(orc.remap_case(16, A, B, 1, 2), A + A[..., ::-1])
+
+
 def test_softmax3d_and_index_fill_known_answers():
     # constant columns normalise to 1/classes; the gradient subtracts one at the label's class
     p = orc.softmax3d(np.zeros((2, 8, 3), np.float32), np.full((2, 8, 3), 2.5, np.float32))
