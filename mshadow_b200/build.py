@@ -26,6 +26,14 @@ TARGETS = [
 ]
 
 
+# the headers evaluated on Tensor<cpu> by the host compiler alone (tests of the plans' index arithmetic)
+HOST_FLAGS = ["-std=c++17", "-O2", "-fPIC", "-shared", "-ffp-contract=off", "-DMSHADOW_USE_CUDA=0",
+              "-DDMLC_LOG_FATAL_THROW=1", "-I" + os.path.join(HERE, "include")]
+HOST_TARGETS = [
+    (os.path.join(ROOT, "tests", "cxx", "libmsb_host_suite.so"), [os.path.join(ROOT, "tests", "cxx", "host_suite.cc")]),
+]
+
+
 def _nvcc():
     exe = shutil.which("nvcc") or "/usr/local/cuda/bin/nvcc"
     if not os.path.exists(exe):
@@ -53,6 +61,15 @@ def build_all(force=False, verbose=True):
         if not force and not _stale(out, srcs + deps_common):
             continue
         cmd = [_nvcc()] + NVCC_FLAGS + ["-o", out] + srcs
+        if verbose:
+            print("[build]", " ".join(cmd), flush=True)
+        subprocess.check_call(cmd)
+    for out, srcs in HOST_TARGETS:
+        if not all(os.path.exists(s) for s in srcs):
+            continue
+        if not force and not _stale(out, srcs + deps_common):
+            continue
+        cmd = [shutil.which("g++") or "g++"] + HOST_FLAGS + ["-o", out] + srcs
         if verbose:
             print("[build]", " ".join(cmd), flush=True)
         subprocess.check_call(cmd)

@@ -521,9 +521,11 @@ class Plan<PaddingExp<SrcExp, DType, srcdim>, DType> {
   MSHADOW_XINLINE DType Eval(index_t i, index_t j) const {
     uint32_t c;
     const uint32_t y = by_new_height_.DivMod(i, &c);
-    // unsigned wrap-around turns "above / left of the image" into a huge value: one comparison per axis
-    const index_t h = y - pad_y_, w = j - pad_x_;
-    return (h < src_height_ && w < src_width_) ? src_.Eval(c * src_height_ + h, w) : static_cast<DType>(0);
+    // in unsigned arithmetic "above / left of the image" wraps to a huge value: one comparison per axis
+    const uint32_t h = y - static_cast<uint32_t>(pad_y_), w = static_cast<uint32_t>(j) - static_cast<uint32_t>(pad_x_);
+    return (h < static_cast<uint32_t>(src_height_) && w < static_cast<uint32_t>(src_width_))
+               ? src_.Eval(c * src_height_ + h, w)
+               : static_cast<DType>(0);
   }
 
  private:

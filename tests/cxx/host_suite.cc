@@ -1,0 +1,90 @@
+/*
+ * Host-side conformance library: the engine's headers evaluated on Tensor<cpu>, compiled by
+ * g++ without CUDA.  An expression plan's Eval(y, x) is the same code on both devices, so the
+ * index arithmetic of every index-remapping plan can be checked here, on a machine without a
+ * GPU, against the CPU oracle.  Test code only; not part of the product library.
+ */
+#include <cstdint>
+#include <cstring>
+#include <string>
+
+#include "mshadow/tensor.h"
+
+using namespace mshadow;        // NOLINT(*)
+using namespace mshadow::expr;  // NOLINT(*)
+
+namespace {
+typedef Tensor<cpu, 4, float> H4;
+std::string g_error;
+
+inline H4 Img(const float *p, int64_t n, int64_t c, int64_t h, int64_t w) {
+  return H4(const_cast<float *>(p), Shape4(n, c, h, w), static_cast<index_t>(w), nullptr);
+}
+
+Shape<4> RemapShape(int id, int64_t n, int64_t c, int64_t h, int64_t w, int64_t p0, int64_t p1) {
+  const H4 a = Img(nullptr, n, c, h, w);
+  switch (id) {
+    case 0: return reshape(a, Shape4(n, h, c, w)).shape_;
+    case 1: return slice<1>(a, p0, p1).shape_;
+    case 2: return slice<3>(a, p0, p1).shape_;
+    case 3: return concat<1>(a, a).shape_;
+    case 4: return concat<3>(a, a).shape_;
+    case 5: return swapaxis<2, 1>(a).shape_;
+    case 6: return swapaxis<3, 1>(a).shape_;
+    case 7: return transpose(a, Shape4(0, 2, 1, 3)).shape_;
+    case 8: return transpose(a, Shape4(3, 1, 0, 2)).shape_;
+    case 9: return pad(a, p0, p1).shape_;
+    case 10: return crop(a, Shape2(p0, p1)).shape_;
+    case 11: return crop(a, Shape2(p0, p1), h - p0, w - p1).shape_;
+    case 15: return Shape4(2 * n, c, h, w);
+    default: return a.shape_;
+  }
+}
+}  // namespace
+
+extern "C" {
+
+const char *hostmsb_last_error(void) { return g_error.c_str(); }
+
+/* the cases of msb_remap_case_f32, on host memory; returns 0, or 1 when a CHECK of the engine fired */
+int hostmsb_remap_case(int id, float *dst, const float *A, const float *B, int64_t n, int64_t c, int64_t h,
+                       int64_t w, int64_t p0, int64_t p1, int64_t *out_shape) {
+  try {
+    const Shape<4> o = RemapShape(id, n, c, h, w, p0, p1);
+    for (int i = 0; i < 4; ++i) out_shape[i] = o[i];
+    if (dst == nullptr) return 0;  // shape query
+    const H4 a = Img(A, n, c, h, w), b = Img(B, n, c, h, w);
+    H4 d = Img(dst, o[0], o[1], o[2], o[3]);
+    switch (id) {
+      case 0: d = reshape(a, Shape4(n, h, c, w)); break;
+      case 1: d = slice<1>(a, p0, p1); break;
+      case 2: d = slice<3>(a, p0, p1); break;
+      case 3: d = concat<1>(a, b); break;
+      case 4: d = concat<3>(a, b); break;
+      case 5: d = swapaxis<2, 1>(a); break;
+      case 6: d = swapaxis<3, 1>(a); break;
+      case 7: d = transpose(a, Shape4(0, 2, 1, 3)); break;
+      case 8: d = transpose(a, Shape4(3, 1, 0, 2)); break;
+      case 9: d = pad(a, p0, p1); break;
+      case 10: d = crop(a, Shape2(p0, p1)); break;
+      case 11: d = crop(a, Shape2(p0, p1), h - p0, w - p1); break;
+      case 12: d = mirror(a); break;
+      case 13: d = flip(a, 1); break;
+      case 14:
+        std::memcpy(dst, B, sizeof(float) * n * c * h * w);
+        slice<1>(d, p0, p1) = slice<1>(a, p0, p1) + 1.0f;
+        break;
+      case 15: {
+        H4 d1 = Img(dst, n, c, h, w), d2 = Img(dst + n * c * h * w, n, c, h, w);
+        concat<1>(d1, d2) = F<op::identity>(concat<1>(b, a));
+      } break;
+      default: d = crop(pad(a, p0, p1), Shape2(h, w)) + mirror(a); break;
+    }
+  } catch (const std::exception &e) {
+    g_error = e.what();
+    return 1;
+  }
+  return 0;
+}
+
+}  // extern "C"

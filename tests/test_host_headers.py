@@ -1,0 +1,63 @@
+"""The engine's headers on Tensor<cpu>, compiled by g++ alone, against the CPU oracle.
+
+An expression plan's Eval(y, x) is the same code on the host and in the element-at-a-time GPU
+kernel, so the index arithmetic of the index-remapping plans (reciprocal division included) is
+checked here without a GPU.  tests/cxx/libmsb_host_suite.so is built by mshadow_b200/build.py.
+"""
+import ctypes as C
+import os
+
+import numpy as np
+import pytest
+
+import cpu_checkers as cc
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+PATH = os.path.join(ROOT, "tests", "cxx", "libmsb_host_suite.so")
+orc = cc.load("orc")
+i64 = C.c_int64
+f32p = C.POINTER(C.c_float)
+
+
+@pytest.fixture(scope="module")
+def host():
+    if not os.path.exists(PATH):
+        import mshadow_b200.build as b
+        b.build_all(verbose=False)
+    dll = C.CDLL(PATH)
+    dll.hostmsb_last_error.restype = C.c_char_p
+    return dll
+
+
+def run(dll, cid, A, B, p0, p1, fill=9.0):
+    n, c, h, w = A.shape
+    shape = (i64 * 4)()
+    assert dll.hostmsb_remap_case(cid, None, None, None, i64(n), i64(c), i64(h), i64(w), i64(p0), i64(p1), shape) == 0
+    dst = np.full(tuple(int(v) for v in shape), np.float32(fill), np.float32)
+    st = dll.hostmsb_remap_case(cid, dst.ctypes.data_as(f32p), A.ctypes.data_as(f32p), B.ctypes.data_as(f32p), i64(n),
+                                i64(c), i64(h), i64(w), i64(p0), i64(p1), shape)
+    assert st == 0, dll.hostmsb_last_error()
+    return dst
+
+
+@pytest.mark.parametrize("cid", range(cc.NUM_REMAP_CASES))
+@pytest.mark.parametrize("shape", [(2, 3, 4, 5), (1, 8, 6, 16), (3, 5, 1, 7), (2, 2, 3, 1), (2, 7, 9, 12)])
+def test_remap_plans_on_the_host(host, cid, shape):
+    rng = np.random.default_rng(cid * 100 + sum(shape))
+    A = rng.uniform(-1, 1, shape).astype(np.float32)
+    B = rng.uniform(-1, 1, shape).astype(np.float32)
+    for p0, p1 in cc.remap_params(cid, shape):
+        want = orc.remap_case(cid, A, B, p0, p1, fill=9.0)
+        got = run(host, cid, A, B, p0, p1)
+        assert got.shape == want.shape
+        assert np.array_equal(got.view(np.uint32), want.view(np.uint32)), (cid, p0, p1)
+
+
+def test_expression_checks_fire_on_the_host(host):
+    A = np.zeros((2, 3, 4, 5), np.float32)
+    shape = (i64 * 4)()
+    assert host.hostmsb_remap_case(1, None, None, None, i64(2), i64(3), i64(4), i64(5), i64(2), i64(9), shape) == 1
+    assert b"slice" in host.hostmsb_last_error().lower()
+    assert host.hostmsb_remap_case(10, None, None, None, i64(2), i64(3), i64(4), i64(5), i64(7), i64(2), shape) == 1
+    assert b"height" in host.hostmsb_last_error()
+    del A
