@@ -20,9 +20,11 @@ NVCC_FLAGS = [
 
 TARGETS = [
     (os.path.join(HERE, "libmshadow_b200.so"),
-     [os.path.join(HERE, "csrc", "capi.cu"), os.path.join(HERE, "csrc", "noalloc.cu")]),
+     [os.path.join(HERE, "csrc", "capi.cu"), os.path.join(HERE, "csrc", "noalloc.cu")], []),
     (os.path.join(ROOT, "tests", "cxx", "libmsb_api_suite.so"),
-     [os.path.join(ROOT, "tests", "cxx", "api_suite.cu")]),
+     [os.path.join(ROOT, "tests", "cxx", "api_suite.cu")], []),
+    # the multi-GPU synchronisation model; the only part that needs NCCL
+    (os.path.join(HERE, "libmshadow_b200_ps.so"), [os.path.join(HERE, "csrc", "ps_capi.cu")], ["-lnccl"]),
 ]
 
 
@@ -55,12 +57,12 @@ def _stale(out, deps):
 
 def build_all(force=False, verbose=True):
     deps_common = [os.path.join(HERE, "include"), os.path.join(ROOT, "include")]
-    for out, srcs in TARGETS:
+    for out, srcs, extra in TARGETS:
         if not all(os.path.exists(s) for s in srcs):
             continue
         if not force and not _stale(out, srcs + deps_common):
             continue
-        cmd = [_nvcc()] + NVCC_FLAGS + ["-o", out] + srcs
+        cmd = [_nvcc()] + NVCC_FLAGS + ["-o", out] + srcs + extra
         if verbose:
             print("[build]", " ".join(cmd), flush=True)
         subprocess.check_call(cmd)

@@ -1,0 +1,137 @@
+/*
+ * C ABI around mshadow::ps::NcclModel<float> (see mshadow_b200_ps.h for the contract).
+ * A separate shared object, so that the single-GPU library carries no NCCL dependency.
+ */
+#include "mshadow_b200_ps.h"
+
+#include <cstdio>
+#include <string>
+
+#include "mshadow-ps/mshadow_ps.h"
+
+using namespace mshadow;  // NOLINT(*)
+
+namespace {
+
+thread_local std::string g_ps_error;
+
+int FailPs(const std::string &msg) {
+  g_ps_error = msg;
+  return 1;
+}
+
+typedef ps::NcclModel<float> Model;
+
+/*! \brief the caller's matrix as a tensor on the caller's stream */
+struct View {
+  Stream<gpu> stream;
+  Tensor<gpu, 2, float> tensor;
+  View(const float *p, int64_t rows, int64_t cols, int64_t ld, void *s)
+      : tensor(const_cast<float *>(p), Shape2(rows, cols), static_cast<index_t>(ld), NULL) {
+    stream.stream_ = static_cast<cudaStream_t>(s);
+    tensor.stream_ = &stream;
+  }
+};
+
+bool ShapeOk(int64_t rows, int64_t cols, int64_t ld) {
+  return rows >= 0 && cols >= 0 && ld >= cols && rows < (int64_t(1) << 31) && cols < (int64_t(1) << 31) &&
+         rows * cols < (int64_t(1) << 31);
+}
+
+}  // namespace
+
+#define PS_BEGIN try {
+#define PS_END                      \
+  }                                 \
+  catch (const std::exception &e) { \
+    return FailPs(e.what());        \
+  }                                 \
+  return 0;
+
+extern "C" {
+
+const char *msb_ps_last_error(void) { return g_ps_error.c_str(); }
+
+int msb_ps_new_unique_id(char *hex, int64_t capacity) {
+  if (hex == NULL || capacity < 2 * NCCL_UNIQUE_ID_BYTES + 1) return FailPs("msb_ps_new_unique_id: buffer too small");
+  PS_BEGIN
+  const std::string s = Model::NewUniqueIdHex();
+  snprintf(hex, static_cast<size_t>(capacity), "%s", s.c_str());
+  PS_END
+}
+
+int msb_ps_create(int rank, int world, const char *id_hex, int device, msb_ps_t *out) {
+  if (out == NULL) return FailPs("msb_ps_create: null pointer");
+  if (world < 1 || rank < 0 || rank >= world) return FailPs("msb_ps_create: rank outside [0, world)");
+  if (world > 1 && id_hex == NULL) return FailPs("msb_ps_create: an identifier is needed for more than one process");
+  Model *m = NULL;
+  try {
+    m = new Model();
+    char num[32];
+    snprintf(num, sizeof(num), "%d", rank);
+    m->SetParam("rank", num);
+    snprintf(num, sizeof(num), "%d", world);
+    m->SetParam("world_size", num);
+    if (id_hex != NULL) m->SetParam("nccl_id", id_hex);
+    m->Init(std::vector<int>(1, device));
+  } catch (const std::exception &e) {
+    delete m;
+    return FailPs(e.what());
+  }
+  *out = m;
+  return 0;
+}
+
+int msb_ps_destroy(msb_ps_t model) {
+  PS_BEGIN
+  delete static_cast<Model *>(model);
+  PS_END
+}
+
+int msb_ps_init_key(msb_ps_t model, int key, int64_t rows, int64_t cols) {
+  if (model == NULL) return FailPs("msb_ps_init_key: null model");
+  if (!ShapeOk(rows, cols, cols)) return FailPs("msb_ps_init_key: extent out of range");
+  PS_BEGIN
+  int dev = 0;
+  MSHADOW_CUDA_CALL(cudaGetDevice(&dev));
+  static_cast<Model *>(model)->InitKey(Shape2(rows, cols), key, dev);
+  PS_END
+}
+
+#define PS_TENSOR_CALL(NAME, CALL)                                                                    \
+  if (model == NULL || (data == NULL && rows * cols > 0)) return FailPs(NAME ": null pointer");      \
+  if (!ShapeOk(rows, cols, ld)) return FailPs(NAME ": extent out of range");                         \
+  PS_BEGIN                                                                                            \
+  int dev = 0;                                                                                        \
+  MSHADOW_CUDA_CALL(cudaGetDevice(&dev));                                                             \
+  View v(data, rows, cols, ld, stream);                                                               \
+  static_cast<Model *>(model)->CALL;                                                                  \
+  PS_END
+
+int msb_ps_push(msb_ps_t model, const float *data, int64_t rows, int64_t cols, int64_t ld, int key, void *stream) {
+  PS_TENSOR_CALL("msb_ps_push", Push(v.tensor, key, dev))
+}
+
+int msb_ps_pull_req(msb_ps_t model, float *data, int64_t rows, int64_t cols, int64_t ld, int key, void *stream) {
+  PS_TENSOR_CALL("msb_ps_pull_req", PullReq(v.tensor, key, dev))
+}
+
+int msb_ps_pull_wait(msb_ps_t model, int key) {
+  if (model == NULL) return FailPs("msb_ps_pull_wait: null model");
+  PS_BEGIN
+  int dev = 0;
+  MSHADOW_CUDA_CALL(cudaGetDevice(&dev));
+  static_cast<Model *>(model)->PullWait(key, dev);
+  PS_END
+}
+
+int msb_ps_set_weight(msb_ps_t model, float *data, int64_t rows, int64_t cols, int64_t ld, int key, void *stream) {
+  PS_TENSOR_CALL("msb_ps_set_weight", SetWeight(v.tensor, key, dev))
+}
+
+int msb_ps_check_weight(msb_ps_t model, const float *data, int64_t rows, int64_t cols, int64_t ld, int key,
+                        void *stream) {
+  PS_TENSOR_CALL("msb_ps_check_weight", CheckWeight(v.tensor, key, dev))
+}
+
+}  // extern "C"

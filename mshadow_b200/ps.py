@@ -1,0 +1,114 @@
+"""ctypes binding of libmshadow_b200_ps.so (include/mshadow_b200_ps.h): the multi-GPU
+synchronisation model with the interface of dmlc/mshadow's mshadow-ps ISharedModel, one process
+per GPU, sums by NCCL all-reduce.  Used by the tests and by multi-process examples; C++ users
+include mshadow-ps/mshadow_ps.h instead.  There is no fallback when the library is missing.
+"""
+import ctypes as C
+import os
+import re
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(HERE, "libmshadow_b200_ps.so")
+HEADER_PATH = os.path.join(os.path.dirname(HERE), "include", "mshadow_b200_ps.h")
+
+vp, i64, cint = C.c_void_p, C.c_int64, C.c_int
+
+_SIGNATURES = {
+    "msb_ps_new_unique_id": [C.c_char_p, i64],
+    "msb_ps_create": [cint, cint, C.c_char_p, cint, C.POINTER(vp)],
+    "msb_ps_destroy": [vp],
+    "msb_ps_init_key": [vp, cint, i64, i64],
+    "msb_ps_push": [vp, vp, i64, i64, i64, cint, vp],
+    "msb_ps_pull_req": [vp, vp, i64, i64, i64, cint, vp],
+    "msb_ps_pull_wait": [vp, cint],
+    "msb_ps_set_weight": [vp, vp, i64, i64, i64, cint, vp],
+    "msb_ps_check_weight": [vp, vp, i64, i64, i64, cint, vp],
+}
+
+
+def declared_symbols():
+    text = open(HEADER_PATH).read()
+    return sorted(set(re.findall(r"\b(msb_ps_[a-z0-9_]+)\s*\(", text)))
+
+
+class PsError(RuntimeError):
+    pass
+
+
+_dll = None
+
+
+def dll():
+    global _dll
+    if _dll is None:
+        if not os.path.exists(LIB_PATH):
+            raise FileNotFoundError("%s not found: build it with `python -m mshadow_b200.build`" % LIB_PATH)
+        _dll = C.CDLL(LIB_PATH)
+        _dll.msb_ps_last_error.restype = C.c_char_p
+        for name, argtypes in _SIGNATURES.items():
+            fn = getattr(_dll, name)
+            fn.argtypes = argtypes
+            fn.restype = cint
+    return _dll
+
+
+def _check(status):
+    if status != 0:
+        raise PsError(dll().msb_ps_last_error().decode("utf-8", "replace"))
+
+
+def new_unique_id():
+    """Group identifier for a new set of processes; create on one rank, hand to the others."""
+    buf = C.create_string_buffer(300)
+    _check(dll().msb_ps_new_unique_id(buf, 300))
+    return buf.value.decode("ascii")
+
+
+def _mat(t):
+    """(pointer, rows, cols, leading dimension) of a tensor viewed as a matrix over its last axis."""
+    assert t.dim() >= 1 and (t.stride(-1) == 1 or t.shape[-1] <= 1)
+    cols = t.shape[-1]
+    rows = t.numel() // cols if cols else 0
+    ld = t.stride(-2) if t.dim() >= 2 else cols
+    return vp(t.data_ptr()), rows, cols, ld
+
+
+class SharedModel:
+    """One process's handle on the model: mirrors ISharedModel (InitKey, Push, PullReq, PullWait,
+    SetWeight, CheckWeight) for fp32 device tensors of the GPU it was created on."""
+
+    def __init__(self, rank=0, world=1, unique_id=None, device=0):
+        self.handle = vp()
+        uid = unique_id.encode("ascii") if unique_id is not None else None
+        _check(dll().msb_ps_create(rank, world, uid, device, C.byref(self.handle)))
+
+    def close(self):
+        if self.handle:
+            _check(dll().msb_ps_destroy(self.handle))
+            self.handle = vp()
+
+    def init_key(self, key, shape):
+        cols = shape[-1]
+        rows = 1
+        for s in shape[:-1]:
+            rows *= s
+        _check(dll().msb_ps_init_key(self.handle, key, rows, cols))
+
+    def push(self, tensor, key, stream=None):
+        p, rows, cols, ld = _mat(tensor)
+        _check(dll().msb_ps_push(self.handle, p, rows, cols, ld, key, stream))
+
+    def pull_req(self, tensor, key, stream=None):
+        p, rows, cols, ld = _mat(tensor)
+        _check(dll().msb_ps_pull_req(self.handle, p, rows, cols, ld, key, stream))
+
+    def pull_wait(self, key):
+        _check(dll().msb_ps_pull_wait(self.handle, key))
+
+    def set_weight(self, tensor, key, stream=None):
+        p, rows, cols, ld = _mat(tensor)
+        _check(dll().msb_ps_set_weight(self.handle, p, rows, cols, ld, key, stream))
+
+    def check_weight(self, tensor, key, stream=None):
+        p, rows, cols, ld = _mat(tensor)
+        _check(dll().msb_ps_check_weight(self.handle, p, rows, cols, ld, key, stream))
