@@ -22,7 +22,11 @@
  *     aligned widths, slices and concatenations on an aligned boundary, swaps and permutations
  *     that leave the last dimension in place, aligned crops, mirror) the plan also serves
  *     EvalPack, so that expressions containing it stay on the 128-bit kernel.  The run-time half
- *     of that decision is in PackAlign.
+ *     of that decision is in PackAlign;
+ *   - `dst = transpose(tensor, axes)` and `dst = swapaxis<last, a>(tensor)` on dense fp32/any-type
+ *     GPU tensors, when the permutation moves the last axis, run in a dedicated kernel that turns
+ *     64 x 64 tiles round in shared memory (gpu/transpose.cuh) instead of reading the source with a
+ *     large stride.
  */
 #ifndef MSHADOW_EXTENSION_REMAP_H_
 #define MSHADOW_EXTENSION_REMAP_H_
@@ -31,6 +35,11 @@
 
 #include "../engine/check.h"
 #include "../engine/fastdiv.h"
+#if MSHADOW_USE_CUDA && defined(__CUDACC__)
+#include <type_traits>
+
+#include "../gpu/transpose.cuh"
+#endif
 
 namespace mshadow {
 namespace expr {
@@ -735,5 +744,60 @@ class Plan<FlipExp<SrcExp, Device, DType, srcdim>, DType> {
 };
 
 }  // namespace expr
+
+#if MSHADOW_USE_CUDA && defined(__CUDACC__)
+namespace cuda {
+
+namespace remapdetail {
+/*! \brief tiled kernel when tensors are dense and have at most five dimensions, else the generic route */
+template <typename DType, int dim, typename E>
+inline void PermuteOrGeneric(Tensor<gpu, dim, DType> *dst, const E &e, const Tensor<gpu, dim, DType> &src,
+                             const Shape<dim> &axes, Shape<dim> dshape, cudaStream_t stream, std::true_type) {
+  if (src.CheckContiguous() && dst->CheckContiguous() && dst->dptr_ != src.dptr_ &&
+      TiledPermuteLaunch<DType, dim>(dst->dptr_, src.dptr_, src.shape_, axes, stream)) {
+    return;
+  }
+  MapGeneric<sv::saveto, DType>(dst, e, dshape, stream);
+}
+template <typename DType, int dim, typename E>
+inline void PermuteOrGeneric(Tensor<gpu, dim, DType> *dst, const E &e, const Tensor<gpu, dim, DType> &,
+                             const Shape<dim> &, Shape<dim> dshape, cudaStream_t stream, std::false_type) {
+  MapGeneric<sv::saveto, DType>(dst, e, dshape, stream);
+}
+}  // namespace remapdetail
+
+// `dst = transpose(tensor, axes)`: permutations that move the last axis go through shared-memory tiles
+template <typename DType, int dim>
+struct MapDispatch<sv::saveto, Tensor<gpu, dim, DType>, expr::TransposeExExp<Tensor<gpu, dim, DType>, DType, dim>, DType,
+                   dim> {
+  typedef expr::TransposeExExp<Tensor<gpu, dim, DType>, DType, dim> E;
+  inline static void Run(Tensor<gpu, dim, DType> *dst, const E &e, Shape<dim> dshape, cudaStream_t stream) {
+    if (e.axes_[dim - 1] != static_cast<index_t>(dim - 1)) {
+      remapdetail::PermuteOrGeneric<DType, dim>(dst, e, e.src_, e.axes_, dshape, stream,
+                                                std::integral_constant<bool, (dim >= 2 && dim <= 5)>());
+    } else {
+      MapGeneric<sv::saveto, DType>(dst, e, dshape, stream);
+    }
+  }
+};
+
+// `dst = swapaxis<last, a2>(tensor)`
+template <typename DType, int dim, int a2>
+struct MapDispatch<sv::saveto, Tensor<gpu, dim, DType>, expr::SwapAxisExp<Tensor<gpu, dim, DType>, DType, dim, 1, a2>,
+                   DType, dim> {
+  typedef expr::SwapAxisExp<Tensor<gpu, dim, DType>, DType, dim, 1, a2> E;
+  inline static void Run(Tensor<gpu, dim, DType> *dst, const E &e, Shape<dim> dshape, cudaStream_t stream) {
+    Shape<dim> axes;
+    for (int k = 0; k < dim; ++k) axes[k] = k;
+    axes[dim - 1] = a2;
+    axes[a2] = dim - 1;
+    remapdetail::PermuteOrGeneric<DType, dim>(dst, e, e.src_, axes, dshape, stream,
+                                              std::integral_constant<bool, (dim >= 2 && dim <= 5)>());
+  }
+};
+
+}  // namespace cuda
+#endif  // MSHADOW_USE_CUDA && __CUDACC__
+
 }  // namespace mshadow
 #endif  // MSHADOW_EXTENSION_REMAP_H_

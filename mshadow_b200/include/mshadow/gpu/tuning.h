@@ -57,4 +57,8 @@
 #define MSHADOW_B200_REDHIGH_DEPTH 4  // channel reduce: 16-byte groups in flight per thread
 #endif
 
+#ifndef MSHADOW_B200_TRANSPOSE_TILE
+#define MSHADOW_B200_TRANSPOSE_TILE 64  // edge of the shared-memory tile of axis permutations (32: 62 %, 64: 90 %)
+#endif
+
 #endif  // MSHADOW_GPU_TUNING_H_
