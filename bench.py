@@ -397,7 +397,7 @@ def kernel_cases(lib, torch, small=False):
            lambda: lib.ch_unpool(G4, X4, P4, gP4, 5, reducer=1), 10)
     del X4, P4, gP4, G4
     # softmax over the middle axis (per-pixel classification shape: 21 classes, 256x256 positions)
-    b3, c3, n3 = (16 if small else 64), 21, 256 * 256
+    b3, c3, n3 = (32 if small else 64), 21, 256 * 256
     L3 = torch.randn(b3, c3, n3, device=dev, generator=g) * 2
     P3 = torch.empty_like(L3)
     yield ("softmax3d", "Softmax 3-D (%d,%d,%d)" % (b3, c3, n3), 8 * L3.numel(), L3.numel(),
