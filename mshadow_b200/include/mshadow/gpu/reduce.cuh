@@ -177,8 +177,8 @@ ReduceKeepLowestKernel(DPlan dst, const SPlan src, uint32_t rows, uint32_t cols,
 #pragma unroll
   for (int l = 0; l < kLanes; ++l) {
     if (x + l < cols) {
-      DType sum = __ldcg(partial + x + l);
-      for (unsigned k = 1; k < nclusters; ++k) Reducer::Reduce(sum, __ldcg(partial + static_cast<size_t>(k) * cols + x + l));
+      DType sum = gpu_rt::LoadCg(partial + x + l);
+      for (unsigned k = 1; k < nclusters; ++k) Reducer::Reduce(sum, gpu_rt::LoadCg(partial + static_cast<size_t>(k) * cols + x + l));
       Saver::Save(dst.REval(0, x + l), DType(sum * scale));
     }
   }
@@ -260,8 +260,8 @@ ReduceKeepHighDimKernel(DPlan dst, const SPlan src, uint32_t outer, uint32_t cha
   __threadfence();
   if (atomicAdd(&tickets[c], 1u) != nclusters - 1) return;
   __threadfence();
-  DType sum = __ldcg(partial + c);
-  for (unsigned k = 1; k < nclusters; ++k) Reducer::Reduce(sum, __ldcg(partial + static_cast<size_t>(k) * channels + c));
+  DType sum = gpu_rt::LoadCg(partial + c);
+  for (unsigned k = 1; k < nclusters; ++k) Reducer::Reduce(sum, gpu_rt::LoadCg(partial + static_cast<size_t>(k) * channels + c));
   Saver::Save(dst.REval(0, c), DType(sum * scale));
   tickets[c] = 0;  // ready for the next launch
 }

@@ -240,6 +240,36 @@ struct FastDiv {
 
 inline int CeilDiv(int64_t a, int64_t b) { return static_cast<int>((a + b - 1) / b); }
 
+#ifdef __CUDACC__
+/*!
+ * \brief load that bypasses L1 (data written by other CTAs of the same launch), for any element
+ *  type of 1, 2, 4, 8 or 16 bytes; the intrinsic itself only knows the built-in types
+ */
+template <typename T>
+__device__ __forceinline__ T LoadCg(const T *p) {
+  static_assert(sizeof(T) == 1 || sizeof(T) == 2 || sizeof(T) == 4 || sizeof(T) == 8 || sizeof(T) == 16,
+                "LoadCg: unsupported element size");
+  T r;
+  if (sizeof(T) == 1) {
+    const unsigned char v = __ldcg(reinterpret_cast<const unsigned char *>(p));
+    memcpy(&r, &v, sizeof(T) == 1 ? 1 : 0);
+  } else if (sizeof(T) == 2) {
+    const unsigned short v = __ldcg(reinterpret_cast<const unsigned short *>(p));
+    memcpy(&r, &v, sizeof(T) == 2 ? 2 : 0);
+  } else if (sizeof(T) == 4) {
+    const unsigned int v = __ldcg(reinterpret_cast<const unsigned int *>(p));
+    memcpy(&r, &v, sizeof(T) == 4 ? 4 : 0);
+  } else if (sizeof(T) == 8) {
+    const unsigned long long v = __ldcg(reinterpret_cast<const unsigned long long *>(p));
+    memcpy(&r, &v, sizeof(T) == 8 ? 8 : 0);
+  } else {
+    const uint4 v = __ldcg(reinterpret_cast<const uint4 *>(p));
+    memcpy(&r, &v, sizeof(T) == 16 ? 16 : 0);
+  }
+  return r;
+}
+#endif
+
 }  // namespace gpu_rt
 
 template <>

@@ -15,6 +15,7 @@
 #include <string>
 
 #include "./base.h"
+#include "./half.h"
 #include "./expression.h"
 
 namespace mshadow {

@@ -27,6 +27,10 @@ struct addone_square {
 struct maximum_op {
   MSHADOW_XINLINE static float Map(float a, float b) { return a > b ? a : b; }
 };
+// the same written for binary16 operands
+struct maximum_half {
+  MSHADOW_XINLINE static mshadow::half::half_t Map(mshadow::half::half_t a, mshadow::half::half_t b) { return a > b ? a : b; }
+};
 
 template <int dim>
 void Upload(Tensor<gpu, dim, float> dst, const float *host, Stream<gpu> *s) {
@@ -226,6 +230,47 @@ int RunCase(int id, const float *a, const float *b, float *out, int rows, int co
       FreeSpace(&C);
       break;
     }
+    case 14: {  // binary16 tensors: eight elements per 16-byte group, every operation rounded to half
+      typedef mshadow::half::half_t H;
+      const size_t n = static_cast<size_t>(rows) * cols;
+      Tensor<gpu, 2, H> A = NewTensor<gpu>(Shape2(rows, cols), H(0.0f), true, st);
+      Tensor<gpu, 2, H> B = NewTensor<gpu>(Shape2(rows, cols), H(0.0f), true, st);
+      Tensor<gpu, 2, H> C = NewTensor<gpu>(Shape2(rows, cols), H(0.0f), true, st);
+      std::vector<H> ha(n), hb(n), hc(n);
+      for (size_t i = 0; i < n; ++i) ha[i] = H(a[i]), hb[i] = H(b[i]);
+      Copy(A, Tensor<cpu, 2, H>(ha.data(), A.shape_), st);
+      Copy(B, Tensor<cpu, 2, H>(hb.data(), B.shape_), st);
+      C = A * B + A * H(0.5f) - B / (A * A + H(2.0f));  // scalars are written in the element type, as in the reference
+      C += F<maximum_half>(A, B);
+      Copy(Tensor<cpu, 2, H>(hc.data(), C.shape_), C, st);
+      st->Wait();
+      for (size_t i = 0; i < n; ++i) out[i] = static_cast<float>(hc[i]);
+      FreeSpace(&A);
+      FreeSpace(&B);
+      FreeSpace(&C);
+      break;
+    }
+    case 15: {  // casts between float and binary16 tensors, and a half reduction with an exact reducer
+      typedef mshadow::half::half_t H;
+      Tensor<gpu, 2, float> A = NewTensor<gpu>(Shape2(rows, cols), 0.0f, true, st);
+      Tensor<gpu, 2, H> Ah = NewTensor<gpu>(Shape2(rows, cols), H(0.0f), true, st);
+      Tensor<gpu, 2, float> C = NewTensor<gpu>(Shape2(rows, cols), 0.0f, true, st);
+      Tensor<gpu, 1, H> colmax = NewTensor<gpu>(Shape1(cols), H(0.0f), true, st);
+      Tensor<gpu, 1, float> colmax_f = NewTensor<gpu>(Shape1(cols), 0.0f, true, st);
+      Upload(A, a, st);
+      Ah = tcast<H>(A);
+      C = tcast<float>(Ah) * 2.0f;
+      colmax = reduce_except_dim<1, red::maximum>(Ah);
+      colmax_f = tcast<float>(colmax);
+      Download(out, C, st);
+      Download(out + static_cast<size_t>(rows) * cols, colmax_f, st);
+      FreeSpace(&A);
+      FreeSpace(&Ah);
+      FreeSpace(&C);
+      FreeSpace(&colmax);
+      FreeSpace(&colmax_f);
+      break;
+    }
     default:
       rc = -1;
   }
@@ -245,4 +290,4 @@ extern "C" int msb_api_suite_run(int id, const float *a, const float *b, float *
     return -2;
   }
 }
-extern "C" int msb_api_suite_num_cases(void) { return 14; }
+extern "C" int msb_api_suite_num_cases(void) { return 16; }

@@ -46,6 +46,22 @@ extern "C" {
 
 const char *hostmsb_last_error(void) { return g_error.c_str(); }
 
+/* binary16 conversions of mshadow::half::half_t as the host performs them */
+void hostmsb_half_from_float(const float *src, uint16_t *dst, int64_t n) {
+  for (int64_t i = 0; i < n; ++i) dst[i] = mshadow::half::half_t(src[i]).half_;
+}
+void hostmsb_half_to_float(const uint16_t *src, float *dst, int64_t n) {
+  for (int64_t i = 0; i < n; ++i) dst[i] = static_cast<float>(mshadow::half::half_t::Binary(src[i]));
+}
+/* dst = a * b + a * 0.5 - b / (a * a + 2) on binary16 host tensors, every operation rounded to half */
+void hostmsb_half_expr(const uint16_t *a, const uint16_t *b, uint16_t *dst, int64_t rows, int64_t cols) {
+  typedef mshadow::half::half_t H;
+  Tensor<cpu, 2, H> A(reinterpret_cast<H *>(const_cast<uint16_t *>(a)), Shape2(rows, cols));
+  Tensor<cpu, 2, H> B(reinterpret_cast<H *>(const_cast<uint16_t *>(b)), Shape2(rows, cols));
+  Tensor<cpu, 2, H> D(reinterpret_cast<H *>(dst), Shape2(rows, cols));
+  D = A * B + A * H(0.5f) - B / (A * A + H(2.0f));
+}
+
 /* the cases of msb_remap_case_f32, on host memory; returns 0, or 1 when a CHECK of the engine fired */
 int hostmsb_remap_case(int id, float *dst, const float *A, const float *B, int64_t n, int64_t c, int64_t h,
                        int64_t w, int64_t p0, int64_t p1, int64_t *out_shape) {

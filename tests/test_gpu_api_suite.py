@@ -169,3 +169,23 @@ def test_shape_mismatch_raises(run, data):
     a, b = data
     rc, _ = run(13, a, b, 1)
     assert rc == 100
+
+
+def test_half_precision_expression(run, data):
+    """binary16 tensors: numpy's float16 arithmetic rounds every operation to half, as the engine does."""
+    a, b = data
+    rc, out = run(14, a, b, ROWS * COLS)
+    ah, bh = a.astype(np.float16), b.astype(np.float16)
+    want = ah * bh + ah * np.float16(0.5) - bh / (ah * ah + np.float16(2.0))
+    want = want + np.maximum(ah, bh)
+    assert rc == 0
+    assert np.array_equal(out.reshape(ROWS, COLS).astype(np.float16).view(np.uint16), want.view(np.uint16))
+
+
+def test_half_casts_and_exact_reduction(run, data):
+    a, b = data
+    rc, out = run(15, a, b, ROWS * COLS + COLS)
+    ah = a.astype(np.float16)
+    assert rc == 0
+    assert bits_equal(out[:ROWS * COLS].reshape(ROWS, COLS), ah.astype(np.float32) * np.float32(2))
+    assert bits_equal(out[ROWS * COLS:], ah.max(axis=0).astype(np.float32))

@@ -61,3 +61,42 @@ def test_expression_checks_fire_on_the_host(host):
     assert host.hostmsb_remap_case(10, None, None, None, i64(2), i64(3), i64(4), i64(5), i64(7), i64(2), shape) == 1
     assert b"height" in host.hostmsb_last_error()
     del A
+
+
+def test_half_conversions_match_ieee_binary16(host):
+    """half_t's host conversions against numpy's float16: every bit pattern one way, a dense
+    sample of floats (ties, subnormals, overflow, signed zeros) the other way."""
+    u16p = C.POINTER(C.c_uint16)
+    bits = np.arange(65536, dtype=np.uint16)
+    as_float = np.zeros(65536, np.float32)
+    host.hostmsb_half_to_float(bits.ctypes.data_as(u16p), as_float.ctypes.data_as(f32p), i64(65536))
+    want = bits.view(np.float16).astype(np.float32)
+    finite = ~np.isnan(want)
+    assert np.array_equal(as_float[finite].view(np.uint32), want[finite].view(np.uint32))
+    assert np.isnan(as_float[~finite]).all()
+    rng = np.random.default_rng(5)
+    samples = [rng.uniform(-70000, 70000, 200000), rng.uniform(-1e-4, 1e-4, 200000), rng.standard_normal(200000),
+               np.array([0.0, -0.0, 65504.0, 65519.99, 65520.0, 1e9, -1e9, 2.0 ** -24, 2.0 ** -25, 2.0 ** -25 * 1.0001,
+                         2.0 ** -14, np.inf, -np.inf])]
+    # every midpoint between neighbouring halves (the ties) and its float neighbours
+    pos = np.arange(0, 0x7C00, dtype=np.uint16).view(np.float16).astype(np.float64)
+    mid = ((pos[:-1] + pos[1:]) / 2).astype(np.float32)
+    samples += [mid, np.nextafter(mid, np.float32(np.inf)), np.nextafter(mid, np.float32(-np.inf)), -mid]
+    x = np.concatenate([np.asarray(s, dtype=np.float32) for s in samples])
+    got = np.zeros(x.size, np.uint16)
+    host.hostmsb_half_from_float(x.ctypes.data_as(f32p), got.ctypes.data_as(u16p), i64(x.size))
+    with np.errstate(over="ignore"):
+        want16 = x.astype(np.float16).view(np.uint16)
+    assert np.array_equal(got, want16)
+
+
+def test_half_expression_on_the_host(host):
+    u16p = C.POINTER(C.c_uint16)
+    rng = np.random.default_rng(6)
+    a = rng.uniform(-1, 1, (7, 33)).astype(np.float16)
+    b = rng.uniform(-1, 1, (7, 33)).astype(np.float16)
+    out = np.zeros((7, 33), np.uint16)
+    host.hostmsb_half_expr(a.view(np.uint16).ctypes.data_as(u16p), b.view(np.uint16).ctypes.data_as(u16p),
+                           out.ctypes.data_as(u16p), i64(7), i64(33))
+    want = a * b + a * np.float16(0.5) - b / (a * a + np.float16(2.0))
+    assert np.array_equal(out, want.view(np.uint16))
