@@ -442,6 +442,115 @@ def kernel_table(lib, torch, peak, only=None, small=False, iters=None, warm=None
 
 
 # --------------------------------------------------------------------------------------
+# embedding backward with the table sharded by rows (strong scaling; --workload embed_sharded)
+# --------------------------------------------------------------------------------------
+def embed_sharded_arm(args, torch, lib, dist, rank, world, dev):
+    """AddTakeGradLargeBatch on a 262144 x 1024 table whose rows are spread over the ranks, for the
+    same 2^20 Zipf(1.1) indices at every N (total work fixed).  The source rows are replicated on
+    every rank, the sorted index list is routed on the host before the timed region (its time is
+    reported separately).  Two ownership schemes are timed:
+      contiguous   rank r owns a contiguous range of rows; every row keeps its accumulation order
+      cyclic_hot   row i is owned by rank i % N and the 64 most frequent rows are handled by all
+                   ranks: each sums the hot entries of its slice of the batch into a 64 x 1024
+                   table, one NCCL all-reduce combines them, owners add their rows
+    Time per step = max over ranks (CUDA events); rank 0 prints one JSON line."""
+    from mshadow_b200 import sharding
+    k, d, nidx, hot_count = 262144, 1024, 1 << 20, 64
+    p = (np.arange(k) + 1.0) ** -1.1
+    idx = np.random.default_rng(5).choice(k, size=nidx, p=p / p.sum()).astype(np.int32)
+    order = np.argsort(idx, kind="stable").astype(np.int32)
+    keys = idx[order]
+    g = torch.Generator(device=dev)
+    g.manual_seed(1)
+    src = torch.randn(nidx, d, device=dev, generator=g)
+    steps, warm = max(3, min(args.steps, 30)), max(3, min(args.warmup, 5))
+
+    def timed(fn):
+        for _ in range(warm):
+            fn()
+        if dist is not None:
+            dist.barrier()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(steps):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        t = torch.tensor([e0.elapsed_time(e1) / steps], device=dev, dtype=torch.float64)
+        if dist is not None:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    def spread(count):
+        c = torch.tensor([float(count)], device=dev, dtype=torch.float64)
+        hi = c.clone()
+        if dist is not None:
+            dist.all_reduce(hi, op=dist.ReduceOp.MAX)
+        return int(hi.item())
+
+    def checksum(table):
+        s = table.double().sum().reshape(1)
+        if dist is not None:
+            dist.all_reduce(s)
+        return float(s.item())
+
+    out = {}
+    # contiguous ranges
+    t0 = time.perf_counter()
+    lk, lo, rb, re = sharding.route_sorted_indices(keys, order, k, rank, world)
+    route_ms = (time.perf_counter() - t0) * 1e3
+    shard = torch.zeros(re - rb, d, device=dev)
+    dk, do = torch.from_numpy(lk).to(dev), torch.from_numpy(lo).to(dev)
+    if lk.size:
+        lib.addtakegrad_largebatch(shard, dk, do, src)
+    ref_sum = checksum(shard)
+    ms = timed(lambda: lib.addtakegrad_largebatch(shard, dk, do, src) if lk.size else None)
+    out["contiguous"] = {"ms_per_step": ms, "max_entries_on_a_rank": spread(lk.size), "host_routing_ms": route_ms}
+    del shard, dk, do
+    # cyclic ownership, hot rows replicated
+    t0 = time.perf_counter()
+    hot = sharding.hot_rows(keys, hot_count)
+    tk, to, hk, ho = sharding.route_cyclic_with_hot_rows(keys, order, nidx, rank, world, hot)
+    route_ms = (time.perf_counter() - t0) * 1e3
+    rows_mine = (k - rank + world - 1) // world
+    shard = torch.zeros(rows_mine, d, device=dev)
+    dtk, dto = torch.from_numpy(tk).to(dev), torch.from_numpy(to).to(dev)
+    dhk, dho = torch.from_numpy(hk).to(dev), torch.from_numpy(ho).to(dev)
+    partial = torch.zeros(max(1, hot.size), d, device=dev)
+    mine = np.nonzero(hot % world == rank)[0]
+    mine_pos = torch.from_numpy(mine.astype(np.int64)).to(dev)
+    mine_rows = torch.from_numpy((hot[mine] // world).astype(np.int32)).to(dev)
+
+    def hot_step():
+        if tk.size:
+            lib.addtakegrad_largebatch(shard, dtk, dto, src)
+        partial.zero_()
+        if hk.size:
+            lib.addtakegrad_largebatch(partial, dhk, dho, src)
+        if dist is not None:
+            dist.all_reduce(partial)
+        if mine.size:
+            lib.addtakegrad(shard, mine_rows, partial.index_select(0, mine_pos))
+
+    hot_step()
+    hot_sum = checksum(shard)
+    ms = timed(hot_step)
+    out["cyclic_hot"] = {"ms_per_step": ms, "hot_rows": int(hot.size), "max_entries_on_a_rank": spread(tk.size + hk.size),
+                         "host_routing_ms": route_ms, "allreduce_bytes": int(hot.size) * d * 4}
+    if rank == 0:
+        best = min(v["ms_per_step"] for v in out.values())
+        line = {"metric": "AddTakeGradLargeBatch 262144x1024 table sharded by rows, 2^20 Zipf(1.1) indices, fp32",
+                "value": nidx * d / (best * 1e-3) / 1e9, "unit": "Gelem/s", "n_gpus": world, "steps": steps,
+                "warmup": warm, "ms_per_step": best, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+                "dtype": "f32", "data": "synthetic", "config": {"workload": "embed_sharded", "source_rows": "replicated",
+                                                               "index_routing": "host, outside the timed region"},
+                "schemes": out,
+                "checksum_rel_diff_between_schemes": abs(hot_sum - ref_sum) / max(1e-30, abs(ref_sum))}
+        print(json.dumps(line), flush=True)
+
+
+# --------------------------------------------------------------------------------------
 # our arm
 # --------------------------------------------------------------------------------------
 def main():
@@ -457,6 +566,9 @@ def main():
                     help="run one kernel of the table alone (map, keep_highdim, keep_lowest, softmax, softmax_grad, "
                          "pool, unpool, chpool, addtakegrad) for --steps launches after --warmup; for profiling")
     ap.add_argument("--small", action="store_true", help="with --only: reduced size that still exceeds L2")
+    ap.add_argument("--workload", default="reductions", choices=["reductions", "embed_sharded"],
+                    help="reductions: the headline workload; embed_sharded: AddTakeGradLargeBatch with the table "
+                         "sharded by rows over the ranks (strong scaling, see embed_sharded_arm)")
     args = ap.parse_args()
     if args.only is not None:
         import torch
@@ -492,6 +604,11 @@ def main():
     lib.init(local_rank)
     dev = torch.device("cuda", local_rank)
     peak, peak_kind = measured_peak()
+    if args.workload == "embed_sharded":
+        embed_sharded_arm(args, torch, lib, dist, rank, world, dev)
+        if dist is not None:
+            dist.destroy_process_group()
+        return
 
     (p4, h4), (pm, hm) = make_host_inputs(lib, rank)
     T = torch.empty(C2A_SHAPE, device=dev)
