@@ -48,6 +48,20 @@ FALLBACK_HBM_GBS = 6650.0
 NCU_TRAFFIC_KEEP_LOWEST = 4 * 268.45e6 + 4.2e6
 
 
+# where the JSON line goes; main() re-points it at the real stdout after moving fd 1 to stderr (see claim_stdout)
+OUT = sys.stdout
+
+
+def claim_stdout():
+    """Keeps stdout for the one JSON line: returns a file on the original fd 1 and points fd 1 at
+    stderr, so that banners which libraries write to stdout (NCCL prints its version there) do
+    not end up next to the result."""
+    sys.stdout.flush()
+    real = os.fdopen(os.dup(1), "w")
+    os.dup2(2, 1)
+    return real
+
+
 def measured_peak():
     path = os.path.join(ROOT, "MEASURED_PEAKS.json")
     try:
@@ -519,7 +533,8 @@ def embed_sharded_arm(args, torch, lib, dist, rank, world, dev):
     dhk, dho = torch.from_numpy(hk).to(dev), torch.from_numpy(ho).to(dev)
     partial = torch.zeros(max(1, hot.size), d, device=dev)
     mine = np.nonzero(hot % world == rank)[0]
-    mine_pos = torch.from_numpy(mine.astype(np.int64)).to(dev)
+    # my hot rows as a (sorted local row, position in `partial`) list: one more sorted scatter-add
+    mine_pos = torch.from_numpy(mine.astype(np.int32)).to(dev)
     mine_rows = torch.from_numpy((hot[mine] // world).astype(np.int32)).to(dev)
 
     def hot_step():
@@ -531,7 +546,7 @@ def embed_sharded_arm(args, torch, lib, dist, rank, world, dev):
         if dist is not None:
             dist.all_reduce(partial)
         if mine.size:
-            lib.addtakegrad(shard, mine_rows, partial.index_select(0, mine_pos))
+            lib.addtakegrad_largebatch(shard, mine_rows, mine_pos, partial)
 
     hot_step()
     hot_sum = checksum(shard)
@@ -547,7 +562,7 @@ def embed_sharded_arm(args, torch, lib, dist, rank, world, dev):
                                                                "index_routing": "host, outside the timed region"},
                 "schemes": out,
                 "checksum_rel_diff_between_schemes": abs(hot_sum - ref_sum) / max(1e-30, abs(ref_sum))}
-        print(json.dumps(line), flush=True)
+        print(json.dumps(line), file=OUT, flush=True)
 
 
 # --------------------------------------------------------------------------------------
@@ -597,6 +612,8 @@ def main():
     torch.cuda.set_device(local_rank)
     dist = None
     if world > 1:
+        global OUT
+        OUT = claim_stdout()
         import torch.distributed as dist
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
@@ -773,7 +790,7 @@ def main():
             del T, M
             torch.cuda.empty_cache()
             line["kernels"] = kernel_table(lib, torch, peak)
-    print(json.dumps(line), flush=True)
+    print(json.dumps(line), file=OUT, flush=True)
     if dist is not None:
         dist.destroy_process_group()
 
