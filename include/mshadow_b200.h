@@ -233,6 +233,24 @@ int msb_remap_shape(int id, int64_t n, int64_t c, int64_t h, int64_t w, int64_t 
 int msb_remap_case_f32(int id, float *dst, const float *A, const float *B, int64_t n, int64_t c,
                        int64_t h, int64_t w, int64_t p0, int64_t p1, msb_stream_t stream);
 
+/*
+ * Index-selecting expressions evaluated by MapExp on dense fp32 matrices A and B (rows x cols);
+ * idx_r: `rows` integers in [0, rows) stored as floats, idx_c: `rows` integers in [0, cols).
+ * Result (rows x cols) unless noted:
+ *    0  dst = take(idx_r, A)                                  mshadow/extension/take.h
+ *    1  dst = one_hot_encode(idx_c, cols)                     mshadow/extension/one_hot.h
+ *    2  dst = mat_choose_row_element(A, idx_c)     (rows)     mshadow/extension/choose.h
+ *    3  dst = mat_fill_row_element(A, B[0:rows], idx_c)       mshadow/extension/fill.h
+ *    4  dst = mask(idx_c, A)                                  mshadow/extension/mask.h
+ *    5  dst = upsampling_nearest(A, p0)   (rows*p0, cols*p0)  mshadow/extension/spatial_upsampling_nearest.h
+ *    6  dst = take_grad(idx_r, A, rows)                       mshadow/extension/take_grad.h
+ *    7  dst = take(idx_r, A) * B + one_hot_encode(idx_c, cols)
+ * Index values outside their range are not checked (they are not in the reference either).
+ */
+int msb_select_case_f32(int id, float *dst, const float *A, const float *B, const float *idx_r,
+                        const float *idx_c, int64_t rows, int64_t cols, int64_t p0,
+                        msb_stream_t stream);
+
 /* Softmax(Tensor<gpu,3>): softmax over the middle axis of (batch, classes, positions);
    ld_* = pitch of the last axis: mshadow/tensor_gpu-inl.h:163-167 */
 int msb_softmax3d_f32(float *dst, const float *src, int64_t batch, int64_t classes, int64_t npos,

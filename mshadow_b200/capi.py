@@ -70,6 +70,7 @@ _SIGNATURES = {
     "msb_index_fill_f32_i32": [vp, vp, vp, i64, i64, i64, vp],
     "msb_remap_shape": [cint, i64, i64, i64, i64, i64, i64, vp],
     "msb_remap_case_f32": [cint, vp, vp, vp, i64, i64, i64, i64, i64, i64, vp],
+    "msb_select_case_f32": [cint, vp, vp, vp, vp, vp, i64, i64, i64, vp],
     "msb_softmax3d_f32": [vp, vp, i64, i64, i64, i64, i64, vp],
     "msb_softmax_grad3d_f32": [vp, vp, vp, i64, i64, i64, i64, i64, i64, cint, f32, f32, vp],
 }
@@ -251,6 +252,12 @@ class Library:
     def remap_case(self, cid, dst, A, B, p0=0, p1=0, stream=None):
         n, c, h, w = A.shape
         self.call("msb_remap_case_f32", cid, _ptr(dst), _ptr(A), _ptr(B), n, c, h, w, p0, p1, stream)
+        return dst
+
+    def select_case(self, cid, dst, A, B, idx_r, idx_c, p0=1, stream=None):
+        rows, cols = A.shape
+        self.call("msb_select_case_f32", cid, _ptr(dst), _ptr(A), _ptr(B), _ptr(idx_r), _ptr(idx_c), rows, cols, p0,
+                  stream)
         return dst
 
     def vectorized_sort(self, values, segments, stream=None):

@@ -595,6 +595,37 @@ int msb_remap_case_f32(int id, float *dst, const float *A, const float *B, int64
   MSB_GUARD_END
 }
 
+int msb_select_case_f32(int id, float *dst, const float *A, const float *B, const float *idx_r, const float *idx_c,
+                        int64_t rows, int64_t cols, int64_t p0, msb_stream_t stream) {
+  MSB_REQUIRE(id >= 0 && id <= 7, MSB_ERR_ARGUMENT, "unknown expression id");
+  MSB_REQUIRE(rows > 0 && cols > 0 && FitsIndex(rows) && FitsIndex(cols) && FitsIndex(rows * cols) && p0 >= 1 &&
+                  (id != 5 || FitsIndex(rows * cols * p0 * p0)),
+              MSB_ERR_SHAPE, "extent out of range");
+  MSB_REQUIRE(dst && A && B && idx_r && idx_c, MSB_ERR_ARGUMENT, "null pointer");
+  MSB_GUARD_BEGIN
+  BorrowedStream st(stream);
+  const G2 a = Mat(A, rows, cols, cols, st.get()), b = Mat(B, rows, cols, cols, st.get());
+  const G1 ir = Vec(idx_r, rows, st.get()), ic = Vec(idx_c, rows, st.get()), val = Vec(B, rows, st.get());
+  G2 d = Mat(dst, rows, cols, cols, st.get());
+  switch (id) {
+    case 0: d = take(ir, a); break;
+    case 1: d = one_hot_encode(ic, cols); break;
+    case 2: {
+      G1 d1 = Vec(dst, rows, st.get());
+      d1 = mat_choose_row_element(a, ic);
+    } break;
+    case 3: d = mat_fill_row_element(a, val, ic); break;
+    case 4: d = mask(ic, a); break;
+    case 5: {
+      G2 up = Mat(dst, rows * p0, cols * p0, cols * p0, st.get());
+      up = upsampling_nearest(a, p0);
+    } break;
+    case 6: d = take_grad(ir, a, rows); break;
+    default: d = take(ir, a) * b + one_hot_encode(ic, cols); break;
+  }
+  MSB_GUARD_END
+}
+
 int msb_vectorized_sort_f32_i32(float *values, int32_t *segments, int64_t n, msb_stream_t stream) {
   MSB_REQUIRE(FitsIndex(n), MSB_ERR_SHAPE, "extent out of range");
   if (n == 0) return MSB_OK;

@@ -9,4 +9,5 @@
 #include "./extension/reduceto1d.h"
 #include "./extension/pooling.h"
 #include "./extension/remap.h"
+#include "./extension/select.h"
 #endif  // MSHADOW_EXTENSION_H_

@@ -566,6 +566,50 @@ void ORC(remap_case)(int id, float *dst, const float *A, const float *B, int64_t
   }
 }
 
+/* ---- index-selecting expressions: the Plan::Eval bodies of extension/{take, one_hot, choose, fill,
+        mask, spatial_upsampling_nearest, take_grad}.h ---- */
+
+void ORC(select_case)(int id, float *dst, const float *A, const float *B, const float *idx_r,
+                      const float *idx_c, int64_t rows, int64_t cols, int64_t p0) {
+  if (id == 2) {  /* choose.h:50-53: a vector result, element y = A(y, idx_c[y]) */
+    for (int64_t y = 0; y < rows; ++y) dst[y] = AT(A, cols, y, (int64_t)idx_c[y]);
+    return;
+  }
+  const int64_t orows = id == 5 ? rows * p0 : rows, ocols = id == 5 ? cols * p0 : cols;
+#pragma omp parallel for
+  for (int64_t y = 0; y < orows; ++y) {
+    for (int64_t x = 0; x < ocols; ++x) {
+      float v;
+      switch (id) {
+        case 0:  /* take.h:48-51 */
+          v = AT(A, cols, (int64_t)idx_r[y], x);
+          break;
+        case 1:  /* one_hot.h:47-50 */
+          v = (float)(x == (int64_t)idx_c[y]);
+          break;
+        case 3:  /* fill.h:55-62 */
+          v = (int64_t)idx_c[y] == x ? B[y] : AT(A, cols, y, x);
+          break;
+        case 4:  /* mask.h:47-49 */
+          v = AT(A, cols, y, x) * idx_c[y];
+          break;
+        case 5:  /* spatial_upsampling_nearest.h:50-57 with one plane */
+          v = AT(A, cols, y / p0, x / p0);
+          break;
+        case 6: {  /* take_grad.h:52-60: the whole batch is walked for every element, in order */
+          v = 0.0f;
+          for (int64_t i = 0; i < rows; ++i)
+            if ((int64_t)idx_r[i] == y) v += AT(A, cols, i, x);
+        } break;
+        default:  /* 7 */
+          v = AT(A, cols, (int64_t)idx_r[y], x) * AT(B, cols, y, x) + (float)(x == (int64_t)idx_c[y]);
+          break;
+      }
+      dst[y * ocols + x] = v;
+    }
+  }
+}
+
 int ORC(num_threads)(void) {
 #ifdef _OPENMP
   return omp_get_max_threads();

@@ -160,6 +160,23 @@ void ORC(remap_shape)(int id, int64_t n, int64_t c, int64_t h, int64_t w, int64_
 void ORC(remap_case)(int id, float *dst, const float *A, const float *B, int64_t n, int64_t c,
                      int64_t h, int64_t w, int64_t p0, int64_t p1);
 
+/*
+ * Index-selecting expressions evaluated through MapExp on dense fp32 matrices A and B
+ * (rows x cols).  idx_r holds `rows` integers in [0, rows) stored as floats, idx_c `rows`
+ * integers in [0, cols); p0 is a per-case parameter.  Result shape: (rows, cols) unless noted.
+ *    0  dst = take(idx_r, A)                                   extension/take.h
+ *    1  dst = one_hot_encode(idx_c, cols)                      extension/one_hot.h
+ *    2  dst = mat_choose_row_element(A, idx_c)      (rows)     extension/choose.h
+ *    3  dst = mat_fill_row_element(A, B[0:rows], idx_c)        extension/fill.h (B flat, first `rows` values)
+ *    4  dst = mask(idx_c, A)                                   extension/mask.h (row y scaled by idx_c[y])
+ *    5  dst = upsampling_nearest(A, p0)    (rows*p0, cols*p0)  extension/spatial_upsampling_nearest.h
+ *    6  dst = take_grad(idx_r, A, rows)                        extension/take_grad.h
+ *    7  dst = take(idx_r, A) * B + one_hot_encode(idx_c, cols)
+ */
+#define ORC_NUM_SELECT_CASES 8
+void ORC(select_case)(int id, float *dst, const float *A, const float *B, const float *idx_r,
+                      const float *idx_c, int64_t rows, int64_t cols, int64_t p0);
+
 /* number of OpenMP threads the library will use (for cpu_baseline.cores) */
 int ORC(num_threads)(void);
 

@@ -288,6 +288,29 @@ void ref_remap_case(int id, float *dst, const float *A, const float *B, int64_t 
   }
 }
 
+void ref_select_case(int id, float *dst, const float *A, const float *B, const float *idx_r,
+                     const float *idx_c, int64_t rows, int64_t cols, int64_t p0) {
+  T2 a = mat(A, rows, cols, cols), b = mat(B, rows, cols, cols);
+  T1 ir = vec(idx_r, rows), ic = vec(idx_c, rows), val = vec(B, rows);
+  T2 d = mat(dst, rows, cols, cols);
+  switch (id) {
+    case 0: d = take(ir, a); break;
+    case 1: d = one_hot_encode(ic, cols); break;
+    case 2: {
+      T1 d1 = vec(dst, rows);
+      d1 = mat_choose_row_element(a, ic);
+    } break;
+    case 3: d = mat_fill_row_element(a, val, ic); break;
+    case 4: d = mask(ic, a); break;
+    case 5: {
+      T2 up = mat(dst, rows * p0, cols * p0, cols * p0);
+      up = upsampling_nearest(a, p0);
+    } break;
+    case 6: d = take_grad(ir, a, rows); break;
+    default: d = take(ir, a) * b + one_hot_encode(ic, cols); break;
+  }
+}
+
 int ref_num_threads(void) {
 #ifdef _OPENMP
   return omp_get_max_threads();

@@ -177,6 +177,14 @@ class Checker:
                                i64(p1))
         return dst
 
+    def select_case(self, cid, A, B, idx_r, idx_c, p0=1):
+        """Evaluates index-selecting case `cid` on dense (rows, cols) inputs; returns the result."""
+        rows, cols = A.shape
+        dst = np.full(select_shape(cid, rows, cols, p0), np.float32(9.0), dtype=np.float32)
+        self._fn("select_case")(C.c_int(cid), _fp(dst), _fp(A), _fp(B), _fp(idx_r), _fp(idx_c), i64(rows), i64(cols),
+                                i64(p0))
+        return dst
+
     def vectorized_sort(self, values, segments):
         assert values.flags.c_contiguous
         self._fn("vectorized_sort")(_fp(values), _ip(segments), i64(values.shape[0]))
@@ -184,6 +192,25 @@ class Checker:
 
 
 NUM_REMAP_CASES = 17
+NUM_SELECT_CASES = 8
+
+
+def select_shape(cid, rows, cols, p0=1):
+    """Result shape of index-selecting case `cid` (see oracle.h)."""
+    if cid == 2:
+        return (rows,)
+    if cid == 5:
+        return (rows * p0, cols * p0)
+    return (rows, cols)
+
+
+def select_inputs(rng, rows, cols):
+    """(A, B, idx_r, idx_c): matrices and index vectors (integers stored as floats, with repeats)."""
+    A = rng.uniform(-1, 1, (rows, cols)).astype(np.float32)
+    B = rng.uniform(-1, 1, (rows, cols)).astype(np.float32)
+    idx_r = rng.integers(0, rows, rows).astype(np.float32)
+    idx_c = rng.integers(0, cols, rows).astype(np.float32)
+    return A, B, idx_r, idx_c
 
 
 def remap_params(cid, shape):

@@ -46,6 +46,39 @@ extern "C" {
 
 const char *hostmsb_last_error(void) { return g_error.c_str(); }
 
+/* the cases of msb_select_case_f32, on host memory; returns 0, or 1 when a CHECK of the engine fired */
+int hostmsb_select_case(int id, float *dst, const float *A, const float *B, const float *idx_r, const float *idx_c,
+                        int64_t rows, int64_t cols, int64_t p0) {
+  typedef Tensor<cpu, 2, float> H2;
+  typedef Tensor<cpu, 1, float> H1;
+  try {
+    const H2 a(const_cast<float *>(A), Shape2(rows, cols)), b(const_cast<float *>(B), Shape2(rows, cols));
+    const H1 ir(const_cast<float *>(idx_r), Shape1(rows)), ic(const_cast<float *>(idx_c), Shape1(rows));
+    const H1 val(const_cast<float *>(B), Shape1(rows));
+    H2 d(dst, Shape2(rows, cols));
+    switch (id) {
+      case 0: d = take(ir, a); break;
+      case 1: d = one_hot_encode(ic, cols); break;
+      case 2: {
+        H1 d1(dst, Shape1(rows));
+        d1 = mat_choose_row_element(a, ic);
+      } break;
+      case 3: d = mat_fill_row_element(a, val, ic); break;
+      case 4: d = mask(ic, a); break;
+      case 5: {
+        H2 up(dst, Shape2(rows * p0, cols * p0));
+        up = upsampling_nearest(a, p0);
+      } break;
+      case 6: d = take_grad(ir, a, rows); break;
+      default: d = take(ir, a) * b + one_hot_encode(ic, cols); break;
+    }
+  } catch (const std::exception &e) {
+    g_error = e.what();
+    return 1;
+  }
+  return 0;
+}
+
 /* binary16 conversions of mshadow::half::half_t as the host performs them */
 void hostmsb_half_from_float(const float *src, uint16_t *dst, int64_t n) {
   for (int64_t i = 0; i < n; ++i) dst[i] = mshadow::half::half_t(src[i]).half_;

@@ -405,6 +405,21 @@ def test_remap_expressions(lib, cid, shape):
         assert_bits(host(got), want)
 
 
+@pytest.mark.parametrize("cid", range(cc.NUM_SELECT_CASES))
+@pytest.mark.parametrize("rows,cols", [(5, 7), (16, 64), (1, 1), (33, 12), (300, 1024), (257, 130)])
+def test_select_expressions(lib, cid, rows, cols):
+    """take / one_hot_encode / mat_choose_row_element / mat_fill_row_element / mask / upsampling_nearest /
+    take_grad: bit-exact (take_grad adds in batch order on both sides)."""
+    if cid == 6 and rows * cols > 40000:
+        rows = 64  # the expression form walks the whole batch for every element
+    rng = np.random.default_rng(cid * 1000 + rows + cols)
+    A, B, ir, ic = cc.select_inputs(rng, rows, cols)
+    for p0 in ((1, 2, 3) if cid == 5 else (1,)):
+        want = orc.select_case(cid, A, B, ir, ic, p0)
+        got = lib.select_case(cid, torch.full(want.shape, 9.0, device="cuda"), dev(A), dev(B), dev(ir), dev(ic), p0)
+        assert_bits(host(got), want)
+
+
 def test_remap_argument_errors(lib):
     import ctypes as C
     z = torch.zeros(2, 3, 4, 5, device="cuda")

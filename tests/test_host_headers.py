@@ -100,3 +100,17 @@ def test_half_expression_on_the_host(host):
                            out.ctypes.data_as(u16p), i64(7), i64(33))
     want = a * b + a * np.float16(0.5) - b / (a * a + np.float16(2.0))
     assert np.array_equal(out, want.view(np.uint16))
+
+
+@pytest.mark.parametrize("cid", range(cc.NUM_SELECT_CASES))
+@pytest.mark.parametrize("rows,cols", [(5, 7), (16, 64), (1, 1), (33, 12)])
+def test_select_plans_on_the_host(host, cid, rows, cols):
+    rng = np.random.default_rng(cid * 100 + rows + cols)
+    A, B, ir, ic = cc.select_inputs(rng, rows, cols)
+    for p0 in ((1, 2, 3) if cid == 5 else (1,)):
+        want = orc.select_case(cid, A, B, ir, ic, p0)
+        got = np.full(want.shape, np.float32(9.0), np.float32)
+        st = host.hostmsb_select_case(cid, got.ctypes.data_as(f32p), A.ctypes.data_as(f32p), B.ctypes.data_as(f32p),
+                                      ir.ctypes.data_as(f32p), ic.ctypes.data_as(f32p), i64(rows), i64(cols), i64(p0))
+        assert st == 0, host.hostmsb_last_error()
+        assert np.array_equal(got.view(np.uint32), want.view(np.uint32)), (cid, p0)

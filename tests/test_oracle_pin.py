@@ -220,6 +220,35 @@ def test_remap_cases_match_reference(cid, shape):
         assert same_bits(*res), (cid, p0, p1)
 
 
+@needs_ref
+@pytest.mark.parametrize("cid", range(cc.NUM_SELECT_CASES))
+@pytest.mark.parametrize("rows,cols", [(5, 7), (16, 64), (1, 1), (33, 12)])
+def test_select_cases_match_reference(cid, rows, cols):
+    rng = np.random.default_rng(cid * 100 + rows + cols)
+    A, B, ir, ic = cc.select_inputs(rng, rows, cols)
+    for p0 in ((1, 2, 3) if cid == 5 else (1,)):
+        res = [lib.select_case(cid, A, B, ir, ic, p0) for lib in (orc, ref)]
+        assert same_bits(*res), (cid, p0)
+
+
+def test_select_known_answers():
+    A = np.arange(12, dtype=np.float32).reshape(3, 4)
+    B = -A
+    ir, ic = np.array([2, 0, 2], np.float32), np.array([3, 0, 1], np.float32)
+    assert np.array_equal(orc.select_case(0, A, B, ir, ic), A[[2, 0, 2]])
+    assert np.array_equal(orc.select_case(1, A, B, ir, ic), np.eye(4, dtype=np.float32)[[3, 0, 1]])
+    assert np.array_equal(orc.select_case(2, A, B, ir, ic), np.array([3, 4, 9], np.float32))
+    want = A.copy()
+    want[0, 3], want[1, 0], want[2, 1] = B.reshape(-1)[:3]
+    assert np.array_equal(orc.select_case(3, A, B, ir, ic), want)
+    assert np.array_equal(orc.select_case(4, A, B, ir, ic), A * ic[:, None])
+    assert np.array_equal(orc.select_case(5, A, B, ir, ic, 2), A.repeat(2, axis=0).repeat(2, axis=1))
+    want = np.zeros_like(A)
+    want[2] = A[0] + A[2]
+    want[0] = A[1]
+    assert np.array_equal(orc.select_case(6, A, B, ir, ic), want)
+
+
 def test_remap_known_answers():
     A = np.arange(2 * 3 * 2 * 4, dtype=np.float32).reshape(2, 3, 2, 4)
     B = -A
