@@ -438,6 +438,15 @@ def kernel_cases(lib, torch, small=False):
         yield ("remap_%d" % cid, "%s %s" % (name, rs), 8 * RA.numel(), RA.numel(),
                lambda cid=cid: lib.remap_case(cid, RD, RA, RB), 10)
     del RA, RB, RD
+    # embedding look-up (the forward of AddTakeGrad): rows of a table gathered by an index vector
+    tr, tc = (65536, 1024) if small else (262144, 1024)
+    TA = torch.randn(tr, tc, device=dev, generator=g)
+    TD = torch.empty_like(TA)
+    tidx = torch.randint(0, tr, (tr,), device=dev, generator=g).float()
+    tic = torch.zeros(tr, device=dev)
+    yield ("take", "take(index, table) %d rows of %d from a %dx%d table" % (tr, tc, tr, tc), 8 * tr * tc + 4 * tr,
+           tr * tc, lambda: lib.select_case(0, TD, TA, TA, tidx, tic), 10)
+    del TA, TD, tidx, tic
     torch.cuda.empty_cache()
 
 
@@ -537,22 +546,38 @@ def embed_sharded_arm(args, torch, lib, dist, rank, world, dev):
     mine_pos = torch.from_numpy(mine.astype(np.int32)).to(dev)
     mine_rows = torch.from_numpy((hot[mine] // world).astype(np.int32)).to(dev)
 
-    def hot_step():
+    def hot_step(stream=None):
         if tk.size:
-            lib.addtakegrad_largebatch(shard, dtk, dto, src)
+            lib.addtakegrad_largebatch(shard, dtk, dto, src, stream=stream)
         partial.zero_()
         if hk.size:
-            lib.addtakegrad_largebatch(partial, dhk, dho, src)
+            lib.addtakegrad_largebatch(partial, dhk, dho, src, stream=stream)
         if dist is not None:
             dist.all_reduce(partial)
         if mine.size:
-            lib.addtakegrad_largebatch(shard, mine_rows, mine_pos, partial)
+            lib.addtakegrad_largebatch(shard, mine_rows, mine_pos, partial, stream=stream)
 
     hot_step()
     hot_sum = checksum(shard)
     ms = timed(hot_step)
     out["cyclic_hot"] = {"ms_per_step": ms, "hot_rows": int(hot.size), "max_entries_on_a_rank": spread(tk.size + hk.size),
                          "host_routing_ms": route_ms, "allreduce_bytes": int(hot.size) * d * 4}
+    # the same step captured once into a CUDA graph: its dozen dependent launches (two multi-level
+    # segmented sums, the clear, the all-reduce, the scatter-add) are then issued by one graph launch
+    # instead of one host call each.  The library's scratch buffers are per stream, so the warm-up
+    # runs on the capture stream before the capture starts (nothing may allocate inside it).
+    side = torch.cuda.Stream(device=dev)
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        for _ in range(3):
+            hot_step(side.cuda_stream)
+    side.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph, stream=side):
+        hot_step(side.cuda_stream)
+    torch.cuda.current_stream().wait_stream(side)
+    ms = timed(graph.replay)
+    out["cyclic_hot_graph"] = {"ms_per_step": ms, "hot_rows": int(hot.size)}
     if rank == 0:
         best = min(v["ms_per_step"] for v in out.values())
         line = {"metric": "AddTakeGradLargeBatch 262144x1024 table sharded by rows, 2^20 Zipf(1.1) indices, fp32",
