@@ -184,6 +184,27 @@ class Tickets {
     }
     return slot.ptr;
   }
+  /*! \brief release the counters of one stream on the current device (all: every array) */
+  static void Release(bool all, cudaStream_t stream) {
+    int dev = 0;
+    if (!all) MSHADOW_CUDA_CALL(cudaGetDevice(&dev));
+    std::lock_guard<std::mutex> lock(Mutex());
+    auto &table = Table();
+    for (auto it = table.begin(); it != table.end();) {
+      if (all || (it->first.first == dev && it->first.second == stream)) {
+        if (it->second.ptr != nullptr) {
+          int cur = 0;
+          cudaGetDevice(&cur);
+          cudaSetDevice(it->first.first);
+          cudaFree(it->second.ptr);
+          cudaSetDevice(cur);
+        }
+        it = table.erase(it);
+      } else {
+        ++it;
+      }
+    }
+  }
 
  private:
   struct Slot {
@@ -285,6 +306,7 @@ inline void InitTensorEngine<gpu>(int dev_id) {
 template <>
 inline void ShutdownTensorEngine<gpu>() {
   gpu_rt::Scratch::Release(true, 0);
+  gpu_rt::Tickets::Release(true, 0);
 }
 template <>
 inline void SetDevice<gpu>(int devid) {
@@ -305,6 +327,7 @@ template <>
 inline void DeleteStream<gpu>(Stream<gpu> *stream) {
   if (stream == NULL) return;
   gpu_rt::Scratch::Release(false, stream->stream_);
+  gpu_rt::Tickets::Release(false, stream->stream_);
   MSHADOW_CUDA_CALL(cudaStreamDestroy(stream->stream_));
   delete stream;
 }
