@@ -18,14 +18,12 @@
  *     hundred thousand columns wide) is rejected with MSB_ERR_SHAPE before anything is
  *     launched.
  *   - the first call on each device looks up the array's device address
- *     (cudaGetSymbolAddress, also for a small array of ticket counters) and the SM count.
- *     That first call is a set-up call: make it before starting any stream capture.  Later
- *     calls only launch kernels.
+ *     (cudaGetSymbolAddress) and the SM count.  That first call is a set-up call: make it
+ *     before starting any stream capture.  Later calls only launch kernels.
  *   - all calls share the one array, also across streams.  Nothing in it has to start at
  *     zero (each launch overwrites exactly the rows it later reads), so stale contents are
  *     harmless, but two calls that execute on the GPU at the same time overwrite each
- *     other's partial rows and disturb each other's ticket counters (which every launch
- *     leaves at zero).  Serialise them: one stream, or events between streams.
+ *     other's partial rows.  Serialise them: one stream, or events between streams.
  *   - no cudaMalloc, cudaFree or other allocating routine is called, on the host or for
  *     the device; inputs and outputs are the caller's.
  * The arithmetic, launch geometry and result are those of msb_reduce_keep_lowest_f32 with
@@ -50,15 +48,10 @@ const int kMaxDevices = 64;
 // In host code this name is only a handle for the runtime's symbol table, never a device
 // address: kernels receive the pointer that cudaGetSymbolAddress returns for it.
 static __device__ __align__(256) float g_noalloc_scratch[kNoAllocScratchFloats];
-// Ticket counters with which the clusters of a launch find the one that finishes last; part of
-// the same fixed device image, zero at load and left at zero by every launch.
-const uint32_t kNoAllocMaxColumnTiles = 4096;
-static __device__ __align__(256) unsigned g_noalloc_tickets[kNoAllocMaxColumnTiles];
 
 struct PerDevice {
   bool ready;
   float *scratch;
-  unsigned *tickets;
   uint32_t slots_vec;     // resident CTAs of the 128-bit kernel on this device
   uint32_t slots_scalar;  // ... and of the element-at-a-time kernel
 };
@@ -84,9 +77,6 @@ int SetUpDevice(int dev, PerDevice *out) {
     float *ptr = nullptr;
     cudaError_t err = cudaGetSymbolAddress(reinterpret_cast<void **>(&ptr), g_noalloc_scratch);
     if (err != cudaSuccess || ptr == nullptr) return FailNoAlloc(MSB_ERR_CUDA, cudaGetErrorString(err));
-    unsigned *tickets = nullptr;
-    err = cudaGetSymbolAddress(reinterpret_cast<void **>(&tickets), g_noalloc_tickets);
-    if (err != cudaSuccess || tickets == nullptr) return FailNoAlloc(MSB_ERR_CUDA, cudaGetErrorString(err));
     int sms = 0, per_sm_vec = 0, per_sm_scalar = 0;
     err = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
     if (err != cudaSuccess || sms <= 0) return FailNoAlloc(MSB_ERR_CUDA, cudaGetErrorString(err));
@@ -98,7 +88,6 @@ int SetUpDevice(int dev, PerDevice *out) {
                                                           mshadow::cuda::kRedLowThreads, 0);
     if (err != cudaSuccess) return FailNoAlloc(MSB_ERR_CUDA, cudaGetErrorString(err));
     g_dev[dev].scratch = ptr;
-    g_dev[dev].tickets = tickets;
     g_dev[dev].slots_vec = static_cast<uint32_t>(per_sm_vec < 1 ? 1 : per_sm_vec) * sms;
     g_dev[dev].slots_scalar = static_cast<uint32_t>(per_sm_scalar < 1 ? 1 : per_sm_scalar) * sms;
     g_dev[dev].ready = true;
@@ -135,11 +124,8 @@ extern "C" int msb_reduce_keep_lowest_sum_f32_noalloc(float *dst, const float *s
   if (sp.clusters > 1) {
     if (static_cast<size_t>(sp.clusters) * static_cast<size_t>(cols) > kNoAllocScratchFloats)
       return FailNoAlloc(MSB_ERR_SHAPE, "input needs more than the 1 MiB built-in scratch; use msb_reduce_keep_lowest_f32");
-    if (col_tiles > kNoAllocMaxColumnTiles)
-      return FailNoAlloc(MSB_ERR_SHAPE, "input is wider than the built-in ticket array allows; use msb_reduce_keep_lowest_f32");
     partial = pd.scratch;
   }
-  unsigned *tickets = partial != nullptr ? pd.tickets : nullptr;
   Stream<gpu> st;
   st.stream_ = static_cast<cudaStream_t>(stream);
   const Tensor<gpu, 1, float> d(dst, Shape1(cols), static_cast<index_t>(cols), &st);
@@ -161,10 +147,16 @@ extern "C" int msb_reduce_keep_lowest_sum_f32_noalloc(float *dst, const float *s
   const uint32_t urows = static_cast<uint32_t>(rows), ucols = static_cast<uint32_t>(cols);
   cudaError_t err;
   if (vec) {
-    err = cudaLaunchKernelEx(&cfg, MSB_NOALLOC_KERNEL(4), dplan, splan, urows, ucols, sp.per_chunk, scale, partial, tickets);
+    err = cudaLaunchKernelEx(&cfg, MSB_NOALLOC_KERNEL(4), dplan, splan, urows, ucols, sp.per_chunk, scale, partial);
   } else {
-    err = cudaLaunchKernelEx(&cfg, MSB_NOALLOC_KERNEL(1), dplan, splan, urows, ucols, sp.per_chunk, scale, partial, tickets);
+    err = cudaLaunchKernelEx(&cfg, MSB_NOALLOC_KERNEL(1), dplan, splan, urows, ucols, sp.per_chunk, scale, partial);
   }
   if (err != cudaSuccess) return FailNoAlloc(MSB_ERR_CUDA, cudaGetErrorString(err));
+  if (partial != nullptr) {
+    mshadow::cuda::ReduceFinishKernel<sv::saveto, red::sum, float, DPlan>
+        <<<(ucols + 255) / 256, 256, 0, st.stream_>>>(dplan, partial, sp.clusters, ucols, scale);
+    err = cudaPeekAtLastError();
+    if (err != cudaSuccess) return FailNoAlloc(MSB_ERR_CUDA, cudaGetErrorString(err));
+  }
   return MSB_OK;
 }

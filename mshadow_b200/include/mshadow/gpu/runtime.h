@@ -160,68 +160,6 @@ class Scratch {
 };
 
 /*!
- * \brief zero-initialised counters, one array per (device, stream), with which the CTAs of a
- *  launch find out which of them finishes last.  Kernels leave every counter at zero again,
- *  so the array is cleared only when it is (re)allocated.
- */
-class Tickets {
- public:
-  static unsigned *Get(cudaStream_t stream, size_t count) {
-    int dev = 0;
-    MSHADOW_CUDA_CALL(cudaGetDevice(&dev));
-    std::lock_guard<std::mutex> lock(Mutex());
-    Slot &slot = Table()[std::make_pair(dev, stream)];
-    if (slot.count < count) {
-      if (slot.ptr != nullptr) {
-        MSHADOW_CUDA_CALL(cudaStreamSynchronize(stream));
-        MSHADOW_CUDA_CALL(cudaFree(slot.ptr));
-        slot.ptr = nullptr;
-      }
-      size_t want = count < 4096 ? 4096 : count * 2;
-      MSHADOW_CUDA_CALL(cudaMalloc(&slot.ptr, want * sizeof(unsigned)));
-      MSHADOW_CUDA_CALL(cudaMemsetAsync(slot.ptr, 0, want * sizeof(unsigned), stream));
-      slot.count = want;
-    }
-    return slot.ptr;
-  }
-  /*! \brief release the counters of one stream on the current device (all: every array) */
-  static void Release(bool all, cudaStream_t stream) {
-    int dev = 0;
-    if (!all) MSHADOW_CUDA_CALL(cudaGetDevice(&dev));
-    std::lock_guard<std::mutex> lock(Mutex());
-    auto &table = Table();
-    for (auto it = table.begin(); it != table.end();) {
-      if (all || (it->first.first == dev && it->first.second == stream)) {
-        if (it->second.ptr != nullptr) {
-          int cur = 0;
-          cudaGetDevice(&cur);
-          cudaSetDevice(it->first.first);
-          cudaFree(it->second.ptr);
-          cudaSetDevice(cur);
-        }
-        it = table.erase(it);
-      } else {
-        ++it;
-      }
-    }
-  }
-
- private:
-  struct Slot {
-    unsigned *ptr = nullptr;
-    size_t count = 0;
-  };
-  static std::mutex &Mutex() {
-    static std::mutex mu;
-    return mu;
-  }
-  static std::map<std::pair<int, cudaStream_t>, Slot> &Table() {
-    static std::map<std::pair<int, cudaStream_t>, Slot> table;
-    return table;
-  }
-};
-
-/*!
  * \brief one int per device in which a kernel records that a bounded wait gave up
  *  (see gpu/tma.cuh); allocated on first use, lives as long as the process
  */
@@ -306,7 +244,6 @@ inline void InitTensorEngine<gpu>(int dev_id) {
 template <>
 inline void ShutdownTensorEngine<gpu>() {
   gpu_rt::Scratch::Release(true, 0);
-  gpu_rt::Tickets::Release(true, 0);
 }
 template <>
 inline void SetDevice<gpu>(int devid) {
@@ -327,7 +264,6 @@ template <>
 inline void DeleteStream<gpu>(Stream<gpu> *stream) {
   if (stream == NULL) return;
   gpu_rt::Scratch::Release(false, stream->stream_);
-  gpu_rt::Tickets::Release(false, stream->stream_);
   MSHADOW_CUDA_CALL(cudaStreamDestroy(stream->stream_));
   delete stream;
 }
