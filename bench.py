@@ -447,6 +447,17 @@ def kernel_cases(lib, torch, small=False):
     yield ("take", "take(index, table) %d rows of %d from a %dx%d table" % (tr, tc, tr, tc), 8 * tr * tc + 4 * tr,
            tr * tc, lambda: lib.select_case(0, TD, TA, TA, tidx, tic), 10)
     del TA, TD, tidx, tic
+    # patch -> column (im2col) of a (64, 64, 56, 56) batch with 3 x 3 patches, stride 1: the matrix is nine
+    # times the image (minus the border), so the write dominates
+    pn = 8 if small else 64
+    PI = torch.rand(pn, 64, 56, 56, device=dev, generator=g)
+    PM = torch.empty(9 * 64, 54 * 54 * pn, device=dev)
+    yield ("unpack_patch2col", "unpack_patch2col 3x3/1 (%d,64,56,56)" % pn, 4 * PI.numel() + 4 * PM.numel(), PM.numel(),
+           lambda: lib.unpack_patch2col(PM, PI, 3, 3, 1, 1), 10)
+    PG = torch.empty_like(PI)
+    yield ("pack_col2patch", "pack_col2patch 3x3/1 (%d,64,56,56)" % pn, 4 * PI.numel() + 4 * PM.numel(), PM.numel(),
+           lambda: lib.pack_col2patch(PG, PM, 3, 3, 1, 1), 10)
+    del PI, PM, PG
     torch.cuda.empty_cache()
 
 

@@ -251,6 +251,20 @@ int msb_select_case_f32(int id, float *dst, const float *A, const float *B, cons
                         const float *idx_c, int64_t rows, int64_t cols, int64_t p0,
                         msb_stream_t stream);
 
+/*
+ * Patch <-> column conversion for convolutions on a dense (n, c, h, w) image:
+ *   mat = unpack_patch2col(img, psy, psx, sy, sx, dy, dx)      mshadow/extension/unpack_patch2col.h
+ *   img = pack_col2patch(mat, imshape, psy, psx, sy, sx, dy, dx)   mshadow/extension/pack_col2patch.h
+ * with patch size (psy, psx), stride (sy, sx) and dilation (dy, dx).  The matrix is dense,
+ * (psy*psx*c) x (oh*ow*n) with oh = (h - (dy*(psy-1)+1))/sy + 1 and ow likewise.
+ */
+int msb_unpack_patch2col_f32(float *mat, const float *img, int64_t n, int64_t c, int64_t h,
+                             int64_t w, int psy, int psx, int sy, int sx, int dy, int dx,
+                             msb_stream_t stream);
+int msb_pack_col2patch_f32(float *img, const float *mat, int64_t n, int64_t c, int64_t h,
+                           int64_t w, int psy, int psx, int sy, int sx, int dy, int dx,
+                           msb_stream_t stream);
+
 /* Softmax(Tensor<gpu,3>): softmax over the middle axis of (batch, classes, positions);
    ld_* = pitch of the last axis: mshadow/tensor_gpu-inl.h:163-167 */
 int msb_softmax3d_f32(float *dst, const float *src, int64_t batch, int64_t classes, int64_t npos,

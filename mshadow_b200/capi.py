@@ -71,6 +71,8 @@ _SIGNATURES = {
     "msb_remap_shape": [cint, i64, i64, i64, i64, i64, i64, vp],
     "msb_remap_case_f32": [cint, vp, vp, vp, i64, i64, i64, i64, i64, i64, vp],
     "msb_select_case_f32": [cint, vp, vp, vp, vp, vp, i64, i64, i64, vp],
+    "msb_unpack_patch2col_f32": [vp, vp, i64, i64, i64, i64, cint, cint, cint, cint, cint, cint, vp],
+    "msb_pack_col2patch_f32": [vp, vp, i64, i64, i64, i64, cint, cint, cint, cint, cint, cint, vp],
     "msb_softmax3d_f32": [vp, vp, i64, i64, i64, i64, i64, vp],
     "msb_softmax_grad3d_f32": [vp, vp, vp, i64, i64, i64, i64, i64, i64, cint, f32, f32, vp],
 }
@@ -259,6 +261,16 @@ class Library:
         self.call("msb_select_case_f32", cid, _ptr(dst), _ptr(A), _ptr(B), _ptr(idx_r), _ptr(idx_c), rows, cols, p0,
                   stream)
         return dst
+
+    def unpack_patch2col(self, mat, img, psy, psx, sy, sx, dy=1, dx=1, stream=None):
+        n, c, h, w = img.shape
+        self.call("msb_unpack_patch2col_f32", _ptr(mat), _ptr(img), n, c, h, w, psy, psx, sy, sx, dy, dx, stream)
+        return mat
+
+    def pack_col2patch(self, img, mat, psy, psx, sy, sx, dy=1, dx=1, stream=None):
+        n, c, h, w = img.shape
+        self.call("msb_pack_col2patch_f32", _ptr(img), _ptr(mat), n, c, h, w, psy, psx, sy, sx, dy, dx, stream)
+        return img
 
     def vectorized_sort(self, values, segments, stream=None):
         self.call("msb_vectorized_sort_f32_i32", _ptr(values), _ptr(segments), values.shape[0], stream)

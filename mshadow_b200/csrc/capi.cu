@@ -626,6 +626,42 @@ int msb_select_case_f32(int id, float *dst, const float *A, const float *B, cons
   MSB_GUARD_END
 }
 
+namespace {
+inline bool PatchArgsOk(int64_t n, int64_t c, int64_t h, int64_t w, int psy, int psx, int sy, int sx, int dy, int dx) {
+  if (n <= 0 || c <= 0 || h <= 0 || w <= 0 || psy <= 0 || psx <= 0 || sy <= 0 || sx <= 0 || dy <= 0 || dx <= 0) return false;
+  if (!FitsIndex(n * c) || !FitsIndex(n * c * h) || !FitsIndex(n * c * h * w)) return false;
+  if (dy * (psy - 1) + 1 > h || dx * (psx - 1) + 1 > w) return false;
+  const int64_t oh = (h - (dy * (psy - 1) + 1)) / sy + 1, ow = (w - (dx * (psx - 1) + 1)) / sx + 1;
+  return FitsIndex(static_cast<int64_t>(psy) * psx * c) && FitsIndex(oh * ow * n) &&
+         FitsIndex(static_cast<int64_t>(psy) * psx * c * oh * ow * n);
+}
+}  // namespace
+
+int msb_unpack_patch2col_f32(float *mat, const float *img, int64_t n, int64_t c, int64_t h, int64_t w, int psy, int psx,
+                             int sy, int sx, int dy, int dx, msb_stream_t stream) {
+  MSB_REQUIRE(PatchArgsOk(n, c, h, w, psy, psx, sy, sx, dy, dx), MSB_ERR_SHAPE, "extent out of range");
+  MSB_REQUIRE(mat && img, MSB_ERR_ARGUMENT, "null pointer");
+  MSB_GUARD_BEGIN
+  BorrowedStream st(stream);
+  const int64_t oh = (h - (dy * (psy - 1) + 1)) / sy + 1, ow = (w - (dx * (psx - 1) + 1)) / sx + 1;
+  G2 m = Mat(mat, static_cast<int64_t>(psy) * psx * c, oh * ow * n, oh * ow * n, st.get());
+  m = unpack_patch2col(Img(img, n, c, h, w, st.get()), psy, psx, sy, sx, dy, dx);
+  MSB_GUARD_END
+}
+
+int msb_pack_col2patch_f32(float *img, const float *mat, int64_t n, int64_t c, int64_t h, int64_t w, int psy, int psx,
+                           int sy, int sx, int dy, int dx, msb_stream_t stream) {
+  MSB_REQUIRE(PatchArgsOk(n, c, h, w, psy, psx, sy, sx, dy, dx), MSB_ERR_SHAPE, "extent out of range");
+  MSB_REQUIRE(mat && img, MSB_ERR_ARGUMENT, "null pointer");
+  MSB_GUARD_BEGIN
+  BorrowedStream st(stream);
+  const int64_t oh = (h - (dy * (psy - 1) + 1)) / sy + 1, ow = (w - (dx * (psx - 1) + 1)) / sx + 1;
+  G4 d = Img(img, n, c, h, w, st.get());
+  d = pack_col2patch(Mat(mat, static_cast<int64_t>(psy) * psx * c, oh * ow * n, oh * ow * n, st.get()), d.shape_, psy,
+                     psx, sy, sx, dy, dx);
+  MSB_GUARD_END
+}
+
 int msb_vectorized_sort_f32_i32(float *values, int32_t *segments, int64_t n, msb_stream_t stream) {
   MSB_REQUIRE(FitsIndex(n), MSB_ERR_SHAPE, "extent out of range");
   if (n == 0) return MSB_OK;

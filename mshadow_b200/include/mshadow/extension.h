@@ -10,4 +10,5 @@
 #include "./extension/pooling.h"
 #include "./extension/remap.h"
 #include "./extension/select.h"
+#include "./extension/patch.h"
 #endif  // MSHADOW_EXTENSION_H_

@@ -610,6 +610,47 @@ void ORC(select_case)(int id, float *dst, const float *A, const float *B, const 
   }
 }
 
+/* ---- patch <-> column (extension/unpack_patch2col.h:115-133, pack_col2patch.h:108-140) ---- */
+
+void ORC(unpack_patch2col)(float *mat, const float *img, int64_t n, int64_t c, int64_t h, int64_t w,
+                           int psy, int psx, int sy, int sx, int dy, int dx) {
+  const int64_t oh = (h - (dy * (psy - 1) + 1)) / sy + 1, ow = (w - (dx * (psx - 1) + 1)) / sx + 1;
+  const int64_t rows = (int64_t)psy * psx * c, cols = oh * ow * n;
+#pragma omp parallel for
+  for (int64_t i = 0; i < rows; ++i) {
+    const int64_t x_offset = i % psx * dx, idivp = i / psx;
+    const int64_t y_offset = idivp % psy * dy, ch = idivp / psy;
+    for (int64_t j = 0; j < cols; ++j) {
+      const int64_t x = (j % ow) * sx + x_offset, jdivw = j / ow;
+      const int64_t y = (jdivw % oh) * sy + y_offset, ni = jdivw / oh;
+      mat[i * cols + j] = (x < w && y < h) ? img[((ni * c + ch) * h + y) * w + x] : 0.0f;
+    }
+  }
+}
+
+void ORC(pack_col2patch)(float *img, const float *mat, int64_t n, int64_t c, int64_t h, int64_t w,
+                         int psy, int psx, int sy, int sx, int dy, int dx) {
+  const int64_t oh = (h - (dy * (psy - 1) + 1)) / sy + 1, ow = (w - (dx * (psx - 1) + 1)) / sx + 1;
+  const int64_t cols = oh * ow * n;
+  const int64_t psy_d = dy * (psy - 1) + 1, psx_d = dx * (psx - 1) + 1;
+#pragma omp parallel for
+  for (int64_t i = 0; i < n * c * h; ++i) {
+    const int64_t y = i % h, idivh = i / h;
+    const int64_t ch = idivh % c, ni = idivh / c;
+    for (int64_t x = 0; x < w; ++x) {
+      const int64_t py_min = y < psy_d ? y % dy : (y - psy_d + sy) / sy;
+      const int64_t px_min = x < psx_d ? x % dx : (x - psx_d + sx) / sx;
+      const int64_t py_max = imin((y + sy) / sy, oh), px_max = imin((x + sx) / sx, ow);
+      float res = 0.0f;
+      for (int64_t py = py_min; py < py_max; py += dy)
+        for (int64_t px = px_min; px < px_max; px += dx)
+          res += mat[((ch * psy + (y - py * sy) / dy) * psx + (x - px * sx) / dx) * cols +
+                     (ni * oh + py) * ow + px];
+      img[i * w + x] = res;
+    }
+  }
+}
+
 int ORC(num_threads)(void) {
 #ifdef _OPENMP
   return omp_get_max_threads();

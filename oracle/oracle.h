@@ -177,6 +177,16 @@ void ORC(remap_case)(int id, float *dst, const float *A, const float *B, int64_t
 void ORC(select_case)(int id, float *dst, const float *A, const float *B, const float *idx_r,
                       const float *idx_c, int64_t rows, int64_t cols, int64_t p0);
 
+/*
+ * Patch <-> column conversion on a dense (n, c, h, w) image (extension/unpack_patch2col.h:115-133,
+ * extension/pack_col2patch.h:108-140).  With oh = (h - (dy*(psy-1)+1))/sy + 1 and ow likewise, the
+ * matrix is (psy*psx*c) x (oh*ow*n), dense.
+ */
+void ORC(unpack_patch2col)(float *mat, const float *img, int64_t n, int64_t c, int64_t h, int64_t w,
+                           int psy, int psx, int sy, int sx, int dy, int dx);
+void ORC(pack_col2patch)(float *img, const float *mat, int64_t n, int64_t c, int64_t h, int64_t w,
+                         int psy, int psx, int sy, int sx, int dy, int dx);
+
 /* number of OpenMP threads the library will use (for cpu_baseline.cores) */
 int ORC(num_threads)(void);
 

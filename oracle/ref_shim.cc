@@ -311,6 +311,20 @@ void ref_select_case(int id, float *dst, const float *A, const float *B, const f
   }
 }
 
+void ref_unpack_patch2col(float *matp, const float *imgp, int64_t n, int64_t c, int64_t h, int64_t w,
+                          int psy, int psx, int sy, int sx, int dy, int dx) {
+  const int64_t oh = (h - (dy * (psy - 1) + 1)) / sy + 1, ow = (w - (dx * (psx - 1) + 1)) / sx + 1;
+  T2 m = mat(matp, (int64_t)psy * psx * c, oh * ow * n, oh * ow * n);
+  m = unpack_patch2col(img(imgp, n, c, h, w, w), psy, psx, sy, sx, dy, dx);
+}
+
+void ref_pack_col2patch(float *imgp, const float *matp, int64_t n, int64_t c, int64_t h, int64_t w,
+                        int psy, int psx, int sy, int sx, int dy, int dx) {
+  const int64_t oh = (h - (dy * (psy - 1) + 1)) / sy + 1, ow = (w - (dx * (psx - 1) + 1)) / sx + 1;
+  T4 d = img(imgp, n, c, h, w, w);
+  d = pack_col2patch(mat(matp, (int64_t)psy * psx * c, oh * ow * n, oh * ow * n), d.shape_, psy, psx, sy, sx, dy, dx);
+}
+
 int ref_num_threads(void) {
 #ifdef _OPENMP
   return omp_get_max_threads();

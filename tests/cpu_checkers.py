@@ -185,6 +185,21 @@ class Checker:
                                 i64(p0))
         return dst
 
+    def unpack_patch2col(self, img, psy, psx, sy, sx, dy=1, dx=1):
+        n, c, h, w = img.shape
+        mat = np.full(patch_matrix_shape(img.shape, psy, psx, sy, sx, dy, dx), np.float32(9.0), np.float32)
+        self._fn("unpack_patch2col")(_fp(mat), _fp(img), i64(n), i64(c), i64(h), i64(w), C.c_int(psy), C.c_int(psx),
+                                     C.c_int(sy), C.c_int(sx), C.c_int(dy), C.c_int(dx))
+        return mat
+
+    def pack_col2patch(self, mat, imshape, psy, psx, sy, sx, dy=1, dx=1):
+        n, c, h, w = imshape
+        assert mat.shape == patch_matrix_shape(imshape, psy, psx, sy, sx, dy, dx) and mat.flags.c_contiguous
+        img = np.full(imshape, np.float32(9.0), np.float32)
+        self._fn("pack_col2patch")(_fp(img), _fp(mat), i64(n), i64(c), i64(h), i64(w), C.c_int(psy), C.c_int(psx),
+                                   C.c_int(sy), C.c_int(sx), C.c_int(dy), C.c_int(dx))
+        return img
+
     def vectorized_sort(self, values, segments):
         assert values.flags.c_contiguous
         self._fn("vectorized_sort")(_fp(values), _ip(segments), i64(values.shape[0]))
@@ -193,6 +208,20 @@ class Checker:
 
 NUM_REMAP_CASES = 17
 NUM_SELECT_CASES = 8
+
+
+def patch_matrix_shape(imshape, psy, psx, sy, sx, dy=1, dx=1):
+    """Shape of unpack_patch2col's result for an (n, c, h, w) image."""
+    n, c, h, w = imshape
+    oh = (h - (dy * (psy - 1) + 1)) // sy + 1
+    ow = (w - (dx * (psx - 1) + 1)) // sx + 1
+    return (psy * psx * c, oh * ow * n)
+
+
+# (image shape, patch y, patch x, stride y, stride x, dilate y, dilate x)
+PATCH_CASES = [((2, 3, 6, 6), 3, 3, 1, 1, 1, 1), ((1, 2, 7, 9), 3, 2, 2, 1, 1, 1), ((2, 1, 8, 8), 2, 2, 2, 2, 1, 1),
+               ((1, 3, 9, 11), 3, 3, 1, 2, 2, 2), ((2, 2, 5, 5), 5, 5, 1, 1, 1, 1), ((1, 1, 10, 7), 2, 3, 3, 2, 2, 1),
+               ((3, 4, 12, 16), 3, 3, 2, 2, 1, 1)]
 
 
 def select_shape(cid, rows, cols, p0=1):

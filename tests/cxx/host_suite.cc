@@ -79,6 +79,27 @@ int hostmsb_select_case(int id, float *dst, const float *A, const float *B, cons
   return 0;
 }
 
+/* patch <-> column conversion on host memory; direction 0 = unpack (img -> mat), 1 = pack (mat -> img) */
+int hostmsb_patch(int direction, float *dst, const float *src, int64_t n, int64_t c, int64_t h, int64_t w, int psy,
+                  int psx, int sy, int sx, int dy, int dx) {
+  typedef Tensor<cpu, 2, float> H2;
+  try {
+    const int64_t oh = (h - (dy * (psy - 1) + 1)) / sy + 1, ow = (w - (dx * (psx - 1) + 1)) / sx + 1;
+    const Shape<2> mshape = Shape2(static_cast<index_t>(psy) * psx * c, oh * ow * n);
+    if (direction == 0) {
+      H2 m(dst, mshape);
+      m = unpack_patch2col(Img(src, n, c, h, w), psy, psx, sy, sx, dy, dx);
+    } else {
+      H4 d = Img(dst, n, c, h, w);
+      d = pack_col2patch(H2(const_cast<float *>(src), mshape), d.shape_, psy, psx, sy, sx, dy, dx);
+    }
+  } catch (const std::exception &e) {
+    g_error = e.what();
+    return 1;
+  }
+  return 0;
+}
+
 /* binary16 conversions of mshadow::half::half_t as the host performs them */
 void hostmsb_half_from_float(const float *src, uint16_t *dst, int64_t n) {
   for (int64_t i = 0; i < n; ++i) dst[i] = mshadow::half::half_t(src[i]).half_;

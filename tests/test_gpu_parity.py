@@ -420,6 +420,23 @@ def test_select_expressions(lib, cid, rows, cols):
         assert_bits(host(got), want)
 
 
+@pytest.mark.parametrize("case", cc.PATCH_CASES + [((4, 16, 28, 28), 3, 3, 1, 1, 1, 1), ((2, 8, 31, 33), 5, 5, 2, 2, 1, 1),
+                                                   ((2, 3, 20, 20), 3, 3, 1, 1, 2, 2)])
+def test_patch_conversions(lib, case):
+    """unpack_patch2col is data movement (bit-exact); pack_col2patch adds the covering patches in the
+    reference's order (bit-exact as well)."""
+    shape, psy, psx, sy, sx, dy, dx = case
+    rng = np.random.default_rng(sum(shape) + psy * 7 + sx)
+    img = rng.uniform(-1, 1, shape).astype(np.float32)
+    want = orc.unpack_patch2col(img, psy, psx, sy, sx, dy, dx)
+    got = lib.unpack_patch2col(torch.full(want.shape, 9.0, device="cuda"), dev(img), psy, psx, sy, sx, dy, dx)
+    assert_bits(host(got), want)
+    grad = rng.uniform(-1, 1, want.shape).astype(np.float32)
+    want_img = orc.pack_col2patch(grad, shape, psy, psx, sy, sx, dy, dx)
+    got_img = lib.pack_col2patch(torch.full(shape, 9.0, device="cuda"), dev(grad), psy, psx, sy, sx, dy, dx)
+    assert_bits(host(got_img), want_img)
+
+
 def test_remap_argument_errors(lib):
     import ctypes as C
     z = torch.zeros(2, 3, 4, 5, device="cuda")

@@ -114,3 +114,21 @@ def test_select_plans_on_the_host(host, cid, rows, cols):
                                       ir.ctypes.data_as(f32p), ic.ctypes.data_as(f32p), i64(rows), i64(cols), i64(p0))
         assert st == 0, host.hostmsb_last_error()
         assert np.array_equal(got.view(np.uint32), want.view(np.uint32)), (cid, p0)
+
+
+@pytest.mark.parametrize("case", cc.PATCH_CASES)
+def test_patch_plans_on_the_host(host, case):
+    shape, psy, psx, sy, sx, dy, dx = case
+    n, c, h, w = shape
+    rng = np.random.default_rng(sum(shape) + psy * 7 + sx)
+    img = rng.uniform(-1, 1, shape).astype(np.float32)
+    want = orc.unpack_patch2col(img, psy, psx, sy, sx, dy, dx)
+    got = np.full(want.shape, np.float32(9.0), np.float32)
+    args = (i64(n), i64(c), i64(h), i64(w), psy, psx, sy, sx, dy, dx)
+    assert host.hostmsb_patch(0, got.ctypes.data_as(f32p), img.ctypes.data_as(f32p), *args) == 0
+    assert np.array_equal(got.view(np.uint32), want.view(np.uint32))
+    grad = rng.uniform(-1, 1, want.shape).astype(np.float32)
+    want_img = orc.pack_col2patch(grad, shape, psy, psx, sy, sx, dy, dx)
+    got_img = np.full(shape, np.float32(9.0), np.float32)
+    assert host.hostmsb_patch(1, got_img.ctypes.data_as(f32p), grad.ctypes.data_as(f32p), *args) == 0
+    assert np.array_equal(got_img.view(np.uint32), want_img.view(np.uint32))

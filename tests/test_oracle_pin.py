@@ -231,6 +231,29 @@ def test_select_cases_match_reference(cid, rows, cols):
         assert same_bits(*res), (cid, p0)
 
 
+@needs_ref
+@pytest.mark.parametrize("case", cc.PATCH_CASES)
+def test_patch_conversions_match_reference(case):
+    shape, psy, psx, sy, sx, dy, dx = case
+    rng = np.random.default_rng(sum(shape) + psy * 7 + sx)
+    img = rnd(rng, shape)
+    mats = [lib.unpack_patch2col(img, psy, psx, sy, sx, dy, dx) for lib in (orc, ref)]
+    assert same_bits(*mats)
+    grad = rnd(rng, mats[0].shape)
+    backs = [lib.pack_col2patch(grad, shape, psy, psx, sy, sx, dy, dx) for lib in (orc, ref)]
+    assert same_bits(*backs)
+
+
+def test_patch_conversions_known_answers():
+    # 1 x 1 x 3 x 3 image, 2 x 2 patches, stride 1: four patches, rows (ky, kx), columns (oy, ox)
+    img = np.arange(9, dtype=np.float32).reshape(1, 1, 3, 3)
+    mat = orc.unpack_patch2col(img, 2, 2, 1, 1)
+    assert np.array_equal(mat, np.array([[0, 1, 3, 4], [1, 2, 4, 5], [3, 4, 6, 7], [4, 5, 7, 8]], np.float32))
+    # packing ones back counts how many patches cover each pixel
+    cover = orc.pack_col2patch(np.ones_like(mat), img.shape, 2, 2, 1, 1)
+    assert np.array_equal(cover[0, 0], np.array([[1, 2, 1], [2, 4, 2], [1, 2, 1]], np.float32))
+
+
 def test_select_known_answers():
     A = np.arange(12, dtype=np.float32).reshape(3, 4)
     B = -A
