@@ -29,6 +29,7 @@ namespace cuda {
 
 const int kMapThreads = MSHADOW_B200_MAP_THREADS;
 const int kMapUnroll = MSHADOW_B200_MAP_UNROLL;
+const int kMapScalarUnroll = MSHADOW_B200_MAP_SCALAR_UNROLL;
 /*! \brief resident CTAs per SM that the grid is sized for */
 const int kMapCtasPerSM = 8;
 
@@ -84,11 +85,11 @@ MapScalarKernel(DPlan dst, const SPlan src, uint32_t rows, uint32_t cols, gpu_rt
   const uint32_t total = rows * cols;
   const uint32_t step = gridDim.x * kMapThreads;
   for (uint32_t base = blockIdx.x * kMapThreads + threadIdx.x; base < total;
-       base += step * kMapUnroll) {
-    DType val[kMapUnroll];
-    uint32_t ys[kMapUnroll], xs[kMapUnroll];
+       base += step * kMapScalarUnroll) {
+    DType val[kMapScalarUnroll];
+    uint32_t ys[kMapScalarUnroll], xs[kMapScalarUnroll];
 #pragma unroll
-    for (int u = 0; u < kMapUnroll; ++u) {
+    for (int u = 0; u < kMapScalarUnroll; ++u) {
       const uint32_t i = base + u * step;
       if (i < total) {
         const uint32_t y = row_of_elem.Quot(i);
@@ -99,7 +100,7 @@ MapScalarKernel(DPlan dst, const SPlan src, uint32_t rows, uint32_t cols, gpu_rt
       }
     }
 #pragma unroll
-    for (int u = 0; u < kMapUnroll; ++u) {
+    for (int u = 0; u < kMapScalarUnroll; ++u) {
       if (base + u * step < total) Saver::Save(dst.REval(ys[u], xs[u]), val[u]);
     }
   }

@@ -13,6 +13,9 @@
 #define MSHADOW_B200_MAP_UNROLL 1  // 16-byte groups per thread and sweep; 1 keeps the sweep linear in memory
                                    // (measured: 1 -> 94 %, 2 or 4 -> 87 %, 8 -> 60 % of copy bandwidth)
 #endif
+#ifndef MSHADOW_B200_MAP_SCALAR_UNROLL
+#define MSHADOW_B200_MAP_SCALAR_UNROLL 1  // elements per thread and sweep of the element-at-a-time kernel
+#endif
 #ifndef MSHADOW_B200_SEG_CHUNK
 #define MSHADOW_B200_SEG_CHUNK 64  // sorted entries per CTA of the segmented sum (32: 81 %, 64: 87 %, 128: 81 %)
 #endif

@@ -132,3 +132,63 @@ def test_patch_plans_on_the_host(host, case):
     got_img = np.full(shape, np.float32(9.0), np.float32)
     assert host.hostmsb_patch(1, got_img.ctypes.data_as(f32p), grad.ctypes.data_as(f32p), *args) == 0
     assert np.array_equal(got_img.view(np.uint32), want_img.view(np.uint32))
+
+
+def _numpy_remap(cid, A, B, p0, p1):
+    """numpy's own formulation of the remap cases that have one (independent of the C oracle)."""
+    n, c, h, w = A.shape
+    if cid == 0:
+        return A.reshape(n, h, c, w)
+    if cid == 1:
+        return A[:, p0:p1]
+    if cid == 2:
+        return A[..., p0:p1]
+    if cid == 3:
+        return np.concatenate([A, B], axis=1)
+    if cid == 4:
+        return np.concatenate([A, B], axis=3)
+    if cid == 5:
+        return A.swapaxes(1, 2)
+    if cid == 6:
+        return A.swapaxes(1, 3)
+    if cid == 7:
+        return A.transpose(0, 2, 1, 3)
+    if cid == 8:
+        return A.transpose(3, 1, 0, 2)
+    if cid == 9:
+        return np.pad(A, ((0, 0), (0, 0), (p0, p0), (p1, p1)))
+    if cid == 12:
+        return A[..., ::-1]
+    if cid == 13:
+        return A[:, ::-1]
+    if cid == 16:
+        return A + A[..., ::-1]
+    return None
+
+
+def test_remap_plans_against_numpy_on_random_shapes(host):
+    hyp = pytest.importorskip("hypothesis")
+    st = hyp.strategies
+
+    @hyp.settings(max_examples=120, deadline=None)
+    @hyp.given(st.integers(1, 4), st.integers(1, 9), st.integers(1, 9), st.integers(1, 20),
+               st.sampled_from([0, 1, 2, 3, 4, 5, 6, 7, 8, 9, 12, 13, 16]), st.integers(0, 3), st.integers(0, 5),
+               st.integers(0, 2 ** 31 - 1))
+    def check(n, c, h, w, cid, a, b, seed):
+        rng = np.random.default_rng(seed)
+        A = rng.uniform(-1, 1, (n, c, h, w)).astype(np.float32)
+        B = rng.uniform(-1, 1, (n, c, h, w)).astype(np.float32)
+        if cid == 1:
+            p0 = a % c
+            p1 = p0 + 1 + b % (c - p0)
+        elif cid == 2:
+            p0 = a % w
+            p1 = p0 + 1 + b % (w - p0)
+        else:
+            p0, p1 = a, b
+        want = np.ascontiguousarray(_numpy_remap(cid, A, B, p0, p1))
+        got = run(host, cid, A, B, p0, p1)
+        assert got.shape == want.shape
+        assert np.array_equal(got.view(np.uint32), want.view(np.uint32))
+
+    check()
