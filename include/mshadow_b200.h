@@ -265,6 +265,30 @@ int msb_pack_col2patch_f32(float *img, const float *mat, int64_t n, int64_t c, i
                            int64_t w, int psy, int psx, int sy, int sx, int dy, int dx,
                            msb_stream_t stream);
 
+/*
+ * Expressions addressed by an axis number or a begin/end box, evaluated by MapExp on a dense fp32
+ * tensor A of shape (n, c, h, w); p0 and p1 are per-case parameters:
+ *    0  dst = range(p0, p0 + p1, 0.5f, 2)            (1-d)        mshadow/extension/range.h
+ *    1  dst = range(p0 + p1, p0, -1.5f, 1)           (1-d)
+ *    2  dst = slice(A, begin, end)                                mshadow/extension/slice_ex.h
+ *         begin = (p0 % n, p1 % c, p0 % h, p1 % w), end = (n, c, begin_h + (h - begin_h + 1) / 2, w)
+ *    3  dst = A * 2;  slice(dst, begin, end) = slice(A, begin, end) + 1
+ *    4  dst = reduce_with_axis<red::sum, false>(A, p0)   (3-d)    mshadow/extension/reduce_with_axis.h
+ *    5  dst = reduce_with_axis<red::maximum, true>(A, p0)     (position of the maximum along axis p0)
+ *    6  dst = reduce_keepdim<red::minimum, false>(A, p0)
+ *    7  dst = broadcast_with_axis(A3, p0 - 1, p1), A3 = A seen as (n*c, h, w)   mshadow/extension/broadcast_with_axis.h
+ *    8  dst = broadcast_keepdim(slice<1>(A, 0, 1), 1, p1)         -> (n, p1, h, w)
+ *    9  dst = broadcast_to(S, (n, p0, h, p1)), S = the first n*h elements of A seen as (n, 1, h, 1)
+ *   10  dst = broadcast_multi_axes(S, axes (0, 2), sizes (p0, p1)), S = the first c*w elements of A
+ *         seen as (1, c, 1, w)                                    -> (p0, c, p1, w)
+ * msb_axis_shape reports the extents of the (dense) result: *out_ndim of them in out_shape[0..3],
+ * the rest 1.  Parameters outside a case's domain return MSB_ERR_SHAPE.
+ */
+int msb_axis_shape(int id, int64_t n, int64_t c, int64_t h, int64_t w, int64_t p0, int64_t p1,
+                   int64_t *out_shape, int *out_ndim);
+int msb_axis_case_f32(int id, float *dst, const float *A, int64_t n, int64_t c, int64_t h, int64_t w,
+                      int64_t p0, int64_t p1, msb_stream_t stream);
+
 /* Softmax(Tensor<gpu,3>): softmax over the middle axis of (batch, classes, positions);
    ld_* = pitch of the last axis: mshadow/tensor_gpu-inl.h:163-167 */
 int msb_softmax3d_f32(float *dst, const float *src, int64_t batch, int64_t classes, int64_t npos,

@@ -69,6 +69,8 @@ _SIGNATURES = {
     "msb_vectorized_sort_f32_i32": [vp, vp, i64, vp],
     "msb_index_fill_f32_i32": [vp, vp, vp, i64, i64, i64, vp],
     "msb_remap_shape": [cint, i64, i64, i64, i64, i64, i64, vp],
+    "msb_axis_shape": [cint, i64, i64, i64, i64, i64, i64, vp, vp],
+    "msb_axis_case_f32": [cint, vp, vp, i64, i64, i64, i64, i64, i64, vp],
     "msb_remap_case_f32": [cint, vp, vp, vp, i64, i64, i64, i64, i64, i64, vp],
     "msb_select_case_f32": [cint, vp, vp, vp, vp, vp, i64, i64, i64, vp],
     "msb_unpack_patch2col_f32": [vp, vp, i64, i64, i64, i64, cint, cint, cint, cint, cint, cint, vp],
@@ -254,6 +256,17 @@ class Library:
     def remap_case(self, cid, dst, A, B, p0=0, p1=0, stream=None):
         n, c, h, w = A.shape
         self.call("msb_remap_case_f32", cid, _ptr(dst), _ptr(A), _ptr(B), n, c, h, w, p0, p1, stream)
+        return dst
+
+    def axis_shape(self, cid, shape, p0=0, p1=1):
+        out, ndim = (i64 * 4)(), C.c_int(0)
+        n, c, h, w = shape
+        self.call("msb_axis_shape", cid, n, c, h, w, p0, p1, C.cast(out, vp), C.cast(C.pointer(ndim), vp))
+        return tuple(int(v) for v in out[:ndim.value])
+
+    def axis_case(self, cid, dst, A, p0=0, p1=1, stream=None):
+        n, c, h, w = A.shape
+        self.call("msb_axis_case_f32", cid, _ptr(dst), _ptr(A), n, c, h, w, p0, p1, stream)
         return dst
 
     def select_case(self, cid, dst, A, B, idx_r, idx_c, p0=1, stream=None):

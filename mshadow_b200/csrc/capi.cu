@@ -14,6 +14,7 @@
 
 #include "mshadow/tensor.h"
 #include "mshadow/gpu/math.h"
+#include "./axis_cases.h"
 
 using namespace mshadow;        // NOLINT(*)
 using namespace mshadow::expr;  // NOLINT(*)
@@ -659,6 +660,27 @@ int msb_pack_col2patch_f32(float *img, const float *mat, int64_t n, int64_t c, i
   G4 d = Img(img, n, c, h, w, st.get());
   d = pack_col2patch(Mat(mat, static_cast<int64_t>(psy) * psx * c, oh * ow * n, oh * ow * n, st.get()), d.shape_, psy,
                      psx, sy, sx, dy, dx);
+  MSB_GUARD_END
+}
+
+int msb_axis_shape(int id, int64_t n, int64_t c, int64_t h, int64_t w, int64_t p0, int64_t p1, int64_t *out_shape,
+                   int *out_ndim) {
+  MSB_REQUIRE(id >= 0 && id < msb_axis::kNumCases, MSB_ERR_ARGUMENT, "unknown expression id");
+  MSB_REQUIRE(msb_axis::ArgsOk(id, n, c, h, w, p0, p1), MSB_ERR_SHAPE, "extent or parameter out of range");
+  MSB_REQUIRE(out_shape != nullptr && out_ndim != nullptr, MSB_ERR_ARGUMENT, "null pointer");
+  MSB_GUARD_BEGIN
+  *out_ndim = msb_axis::ResultShape<gpu>(id, n, c, h, w, p0, p1, out_shape);
+  MSB_GUARD_END
+}
+
+int msb_axis_case_f32(int id, float *dst, const float *A, int64_t n, int64_t c, int64_t h, int64_t w, int64_t p0,
+                      int64_t p1, msb_stream_t stream) {
+  MSB_REQUIRE(id >= 0 && id < msb_axis::kNumCases, MSB_ERR_ARGUMENT, "unknown expression id");
+  MSB_REQUIRE(msb_axis::ArgsOk(id, n, c, h, w, p0, p1), MSB_ERR_SHAPE, "extent or parameter out of range");
+  MSB_REQUIRE(dst && (A || id < 2), MSB_ERR_ARGUMENT, "null pointer");
+  MSB_GUARD_BEGIN
+  BorrowedStream st(stream);
+  msb_axis::Run<gpu>(id, dst, A, n, c, h, w, p0, p1, st.get());
   MSB_GUARD_END
 }
 

@@ -11,4 +11,5 @@
 #include "./extension/remap.h"
 #include "./extension/select.h"
 #include "./extension/patch.h"
+#include "./extension/axis.h"
 #endif  // MSHADOW_EXTENSION_H_

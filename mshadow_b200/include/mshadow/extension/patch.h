@@ -88,12 +88,51 @@ class Plan<UnpackPatchToColXExp<SrcExp, DType, srcdim>, DType> {
     }
     return DType(0.0f);
   }
+#ifdef __CUDACC__
+  /*!
+   * \brief a 16-byte group of one matrix row: row and first column are split once, the following
+   *  columns step (ox, oy, n) forward; the image needs no alignment since it is read by element
+   */
+  __device__ __forceinline__ Pack<DType> EvalPack(index_t i, index_t j) const {
+    uint32_t idivp, c, jdivw, n;
+    const uint32_t x_offset = by_psize_x_.DivMod(i, &idivp) * pdilate_x_;
+    const uint32_t y_offset = by_psize_y_.DivMod(idivp, &c) * pdilate_y_;
+    uint32_t ox = by_o_width_.DivMod(j, &jdivw);
+    uint32_t oy = by_o_height_.DivMod(jdivw, &n);
+    Pack<DType> r;
+#pragma unroll
+    for (int l = 0; l < Pack<DType>::kLanes; ++l) {
+      const uint32_t x = ox * pstride_x_ + x_offset, y = oy * pstride_y_ + y_offset;
+      r.v[l] = (x < static_cast<uint32_t>(i_width_) && y < static_cast<uint32_t>(i_height_))
+                   ? src_.Eval((n * i_channel_ + c) * i_height_ + y, x)
+                   : DType(0.0f);
+      if (++ox == by_o_width_.div) {
+        ox = 0;
+        if (++oy == by_o_height_.div) {
+          oy = 0;
+          ++n;
+        }
+      }
+    }
+    return r;
+  }
+#endif
 
  private:
   Plan<SrcExp, DType> src_;
   const FastDiv by_psize_x_, by_psize_y_;
   const index_t pstride_y_, pstride_x_, pdilate_y_, pdilate_x_, i_channel_, i_height_, i_width_;
   const FastDiv by_o_height_, by_o_width_;
+};
+
+// served in 16-byte groups whatever the image's alignment (the image is read by element)
+template <typename SrcExp, typename DType, int srcdim>
+struct PackInfo<UnpackPatchToColXExp<SrcExp, DType, srcdim> > {
+  static const bool kPass = true;
+};
+template <typename SrcExp, typename DType, int srcdim>
+struct PackAlign<UnpackPatchToColXExp<SrcExp, DType, srcdim> > {
+  inline static bool Check(const UnpackPatchToColXExp<SrcExp, DType, srcdim> &) { return true; }
 };
 
 // ------------------------------------------------------------------------------------------
@@ -175,12 +214,59 @@ class Plan<PackColToPatchXExp<SrcExp, DType, dstdim>, DType> {
     }
     return res;
   }
+#ifdef __CUDACC__
+  /*!
+   * \brief a 16-byte group of one image row: the row index and the range of patch rows are worked
+   *  out once; every lane keeps the addition order of Eval
+   */
+  __device__ __forceinline__ Pack<DType> EvalPack(index_t i, index_t j) const {
+    uint32_t idivh, n, q;
+    const uint32_t y = by_height_.DivMod(i, &idivh);
+    const uint32_t c = by_channel_.DivMod(idivh, &n);
+    const uint32_t sy = by_stride_y_.div, sx = by_stride_x_.div, dy = by_dilate_y_.div, dx = by_dilate_x_.div;
+    const uint32_t psize_y_dilate = dy * (psize_y_ - 1) + 1, psize_x_dilate = dx * (psize_x_ - 1) + 1;
+    const uint32_t py_min = y < psize_y_dilate ? by_dilate_y_.DivMod(y, &q) : by_stride_y_.Quot(y - psize_y_dilate + sy);
+    uint32_t py_max = by_stride_y_.Quot(y + sy);
+    if (py_max > static_cast<uint32_t>(o_height_)) py_max = o_height_;
+    uint32_t px_min[Pack<DType>::kLanes], px_max[Pack<DType>::kLanes];
+    Pack<DType> r;
+#pragma unroll
+    for (int l = 0; l < Pack<DType>::kLanes; ++l) {
+      const uint32_t x = j + l;
+      px_min[l] = x < psize_x_dilate ? by_dilate_x_.DivMod(x, &q) : by_stride_x_.Quot(x - psize_x_dilate + sx);
+      px_max[l] = by_stride_x_.Quot(x + sx);
+      if (px_max[l] > static_cast<uint32_t>(o_width_)) px_max[l] = o_width_;
+      r.v[l] = static_cast<DType>(0);
+    }
+    for (uint32_t py = py_min; py < py_max; py += dy) {
+      const uint32_t krow = (c * psize_y_ + by_dilate_y_.Quot(y - py * sy)) * psize_x_;
+      const uint32_t col = (n * o_height_ + py) * o_width_;
+#pragma unroll
+      for (int l = 0; l < Pack<DType>::kLanes; ++l) {
+        const uint32_t x = j + l;
+        for (uint32_t px = px_min[l]; px < px_max[l]; px += dx) {
+          r.v[l] = detail::AddRN<DType>(r.v[l], src_.Eval(krow + by_dilate_x_.Quot(x - px * sx), col + px));
+        }
+      }
+    }
+    return r;
+  }
+#endif
 
  private:
   Plan<SrcExp, DType> src_;
   const index_t psize_y_, psize_x_;
   const FastDiv by_stride_y_, by_stride_x_, by_channel_, by_dilate_y_, by_dilate_x_, by_height_;
   const index_t o_height_, o_width_;
+};
+
+template <typename SrcExp, typename DType, int dstdim>
+struct PackInfo<PackColToPatchXExp<SrcExp, DType, dstdim> > {
+  static const bool kPass = true;
+};
+template <typename SrcExp, typename DType, int dstdim>
+struct PackAlign<PackColToPatchXExp<SrcExp, DType, dstdim> > {
+  inline static bool Check(const PackColToPatchXExp<SrcExp, DType, dstdim> &) { return true; }
 };
 
 }  // namespace expr

@@ -1,0 +1,5 @@
+/* Kept so that `#include <mshadow/extension/reduce_with_axis.h>` keeps working; see axis.h. */
+#ifndef MSHADOW_EXTENSION_COMPAT_REDUCE_WITH_AXIS_H_
+#define MSHADOW_EXTENSION_COMPAT_REDUCE_WITH_AXIS_H_
+#include "./axis.h"
+#endif

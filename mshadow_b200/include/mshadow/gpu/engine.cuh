@@ -38,12 +38,30 @@ template <typename Saver, typename DType, typename R, typename E, int dim>
 inline void Go(R *dst, const E &exp, Shape<dim> dshape, cudaStream_t stream, std::false_type) {
   MapPlanScalar<Saver, DType>(expr::MakePlan(*dst), expr::MakePlan(exp), dshape.FlatTo2D(), stream);
 }
+// the expression only knows Eval(y, x) but the destination can be written 16 bytes at a time:
+// groups are assembled from element evaluations (one row split and one wide store per group)
+template <typename Saver, typename DType, typename R, typename E, int dim>
+inline void GoHybrid(R *dst, const E &exp, Shape<dim> dshape, cudaStream_t stream, std::true_type) {
+  if (expr::PackAlign<R>::Check(*dst)) {
+    MapPlanPacked<Saver, DType, false>(expr::MakePlan(*dst), expr::MakePlan(exp), dshape.FlatTo2D(), false, stream);
+  } else {
+    MapPlanScalar<Saver, DType>(expr::MakePlan(*dst), expr::MakePlan(exp), dshape.FlatTo2D(), stream);
+  }
+}
+template <typename Saver, typename DType, typename R, typename E, int dim>
+inline void GoHybrid(R *dst, const E &exp, Shape<dim> dshape, cudaStream_t stream, std::false_type) {
+  MapPlanScalar<Saver, DType>(expr::MakePlan(*dst), expr::MakePlan(exp), dshape.FlatTo2D(), stream);
+}
 }  // namespace mapdetail
 
 template <typename Saver, typename DType, typename R, typename E, int dim>
 inline void MapGeneric(R *dst, const E &exp, Shape<dim> dshape, cudaStream_t stream) {
-  mapdetail::Go<Saver, DType>(dst, exp, dshape, stream,
-                              std::integral_constant<bool, expr::PackInfo<E>::kPass && expr::PackInfo<R>::kPass>());
+  constexpr bool kSrcPack = expr::PackInfo<E>::kPass, kDstPack = expr::PackInfo<R>::kPass;
+  if constexpr (kSrcPack || !MSHADOW_B200_MAP_HYBRID) {
+    mapdetail::Go<Saver, DType>(dst, exp, dshape, stream, std::integral_constant<bool, kSrcPack && kDstPack>());
+  } else {
+    mapdetail::GoHybrid<Saver, DType>(dst, exp, dshape, stream, std::integral_constant<bool, kDstPack>());
+  }
 }
 
 template <typename Saver, typename R, typename E, typename DType, int dim>

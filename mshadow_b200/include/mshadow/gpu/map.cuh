@@ -33,7 +33,11 @@ const int kMapScalarUnroll = MSHADOW_B200_MAP_SCALAR_UNROLL;
 /*! \brief resident CTAs per SM that the grid is sized for */
 const int kMapCtasPerSM = 8;
 
-template <typename Saver, typename DPlan, typename SPlan, typename DType>
+/*!
+ * \tparam kSrcPack the source plan serves 16-byte groups (EvalPack); if false the group is put
+ *  together from kLanes element evaluations and only the destination is accessed 128 bits wide
+ */
+template <typename Saver, typename DPlan, typename SPlan, typename DType, bool kSrcPack = true>
 __global__ void __launch_bounds__(kMapThreads)
 MapPackKernel(DPlan dst, const SPlan src, uint32_t rows, uint32_t cols, uint32_t packs_per_row,
               gpu_rt::FastDiv row_of_pack) {
@@ -52,7 +56,13 @@ MapPackKernel(DPlan dst, const SPlan src, uint32_t rows, uint32_t cols, uint32_t
         const uint32_t x = (i - y * packs_per_row) * kLanes;
         ys[u] = y;
         xs[u] = x;
-        expr::Pack<DType> v = src.EvalPack(y, x);
+        expr::Pack<DType> v;
+        if constexpr (kSrcPack) {
+          v = src.EvalPack(y, x);
+        } else {
+#pragma unroll
+          for (int l = 0; l < kLanes; ++l) v.v[l] = src.Eval(y, x + l);
+        }
         if (!std::is_same<Saver, sv::saveto>::value) {
           expr::Pack<DType> d = dst.EvalPack(y, x);
 #pragma unroll
@@ -129,7 +139,7 @@ inline int MapGridSize(int64_t work_items, Kernel kernel) {
  * \brief launch the 128-bit path.  `flat` says that all operands are dense and the
  *  expression is position-independent, so the matrix is walked as a single row.
  */
-template <typename Saver, typename DType, typename DPlan, typename SPlan>
+template <typename Saver, typename DType, bool kSrcPack = true, typename DPlan, typename SPlan>
 inline void MapPlanPacked(DPlan dplan, const SPlan &splan, Shape<2> dshape, bool flat,
                           cudaStream_t stream) {
   constexpr int kLanes = expr::Pack<DType>::kLanes;
@@ -143,7 +153,7 @@ inline void MapPlanPacked(DPlan dplan, const SPlan &splan, Shape<2> dshape, bool
   }
   const uint32_t ppr = cols / kLanes;
   const int64_t work = static_cast<int64_t>(rows) * (ppr == 0 ? 1 : ppr);
-  auto kernel = MapPackKernel<Saver, DPlan, SPlan, DType>;
+  auto kernel = MapPackKernel<Saver, DPlan, SPlan, DType, kSrcPack>;
   kernel<<<MapGridSize(work, kernel), kMapThreads, 0, stream>>>(dplan, splan, rows, cols, ppr,
                                                                 gpu_rt::FastDiv(ppr == 0 ? 1 : ppr));
   MSHADOW_CUDA_POST_KERNEL_CHECK(MapPackKernel);

@@ -16,6 +16,9 @@
 #ifndef MSHADOW_B200_MAP_SCALAR_UNROLL
 #define MSHADOW_B200_MAP_SCALAR_UNROLL 1  // elements per thread and sweep of the element-at-a-time kernel
 #endif
+#ifndef MSHADOW_B200_MAP_HYBRID
+#define MSHADOW_B200_MAP_HYBRID 0  // expressions without EvalPack: assemble 16-byte groups from element evaluations
+#endif
 #ifndef MSHADOW_B200_SEG_CHUNK
 #define MSHADOW_B200_SEG_CHUNK 64  // sorted entries per CTA of the segmented sum (32: 81 %, 64: 87 %, 128: 81 %)
 #endif

@@ -651,6 +651,144 @@ void ORC(pack_col2patch)(float *img, const float *mat, int64_t n, int64_t c, int
   }
 }
 
+/* ---- expressions addressed by axis or box ---- */
+
+/* begin and end of the box of cases 2 and 3 */
+static void axis_box(int64_t n, int64_t c, int64_t h, int64_t w, int64_t p0, int64_t p1, int64_t b[4], int64_t e[4]) {
+  b[0] = p0 % n; b[1] = p1 % c; b[2] = p0 % h; b[3] = p1 % w;
+  e[0] = n; e[1] = c; e[2] = b[2] + (h - b[2] + 1) / 2; e[3] = w;
+}
+
+int ORC(axis_shape)(int id, int64_t n, int64_t c, int64_t h, int64_t w, int64_t p0, int64_t p1, int64_t o[4]) {
+  const int64_t s[4] = {n, c, h, w};
+  int64_t b[4], e[4];
+  o[0] = o[1] = o[2] = o[3] = 1;
+  switch (id) {
+    case 0:  /* range.h:79-83: repeat * ceil((stop - start) / step) in double */
+      o[0] = 2 * (int64_t)ceil(((double)(float)(p0 + p1) - (double)(float)p0) / 0.5);
+      return 1;
+    case 1:
+      o[0] = (int64_t)ceil(((double)(float)p0 - (double)(float)(p0 + p1)) / -1.5);
+      return 1;
+    case 2:
+      axis_box(n, c, h, w, p0, p1, b, e);
+      for (int k = 0; k < 4; ++k) o[k] = e[k] - b[k];
+      return 4;
+    case 3:
+      for (int k = 0; k < 4; ++k) o[k] = s[k];
+      return 4;
+    case 4: case 5:  /* reduce_with_axis.h:39-48: the axis is dropped */
+      for (int k = 0, m = 0; k < 4; ++k) if (k != p0) o[m++] = s[k];
+      return 3;
+    case 6:  /* reduce_with_axis.h:49-55: the axis keeps extent 1 */
+      for (int k = 0; k < 4; ++k) o[k] = k == p0 ? 1 : s[k];
+      return 4;
+    case 7: {  /* broadcast_with_axis.h:46-53: a new axis of extent p1 behind axis p0 - 1 of (n*c, h, w) */
+      const int64_t s3[3] = {n * c, h, w};
+      for (int k = 0, m = 0; k < 4; ++k) o[k] = k == p0 ? p1 : s3[m++];
+      return 4;
+    }
+    case 8: o[0] = n; o[1] = p1; o[2] = h; o[3] = w; return 4;
+    case 9: o[0] = n; o[1] = p0; o[2] = h; o[3] = p1; return 4;
+    default: o[0] = p0; o[1] = c; o[2] = p1; o[3] = w; return 4;
+  }
+}
+
+void ORC(axis_case)(int id, float *dst, const float *A, int64_t n, int64_t c, int64_t h, int64_t w, int64_t p0,
+                    int64_t p1) {
+  int64_t o[4], b[4], e[4];
+  const int ndim = ORC(axis_shape)(id, n, c, h, w, p0, p1, o);
+  const int64_t s[4] = {n, c, h, w};
+  const int64_t cols = o[ndim - 1];
+  int64_t rows = 1;
+  for (int k = 0; k + 1 < ndim; ++k) rows *= o[k];
+  axis_box(n, c, h, w, p0, p1, b, e);
+  if (id == 3) {
+    for (int64_t i = 0; i < n * c * h * w; ++i) dst[i] = A[i] * 2.0f;
+    /* slice_ex.h:112-121: the same row/column mapping, written through */
+    const int64_t bs[4] = {e[0] - b[0], e[1] - b[1], e[2] - b[2], e[3] - b[3]};
+    for (int64_t i = 0; i < bs[0] * bs[1] * bs[2]; ++i) {
+      int64_t idx = 0, stride = 1, r = i;
+      for (int k = 2; k >= 0; --k) {
+        idx += stride * (r % bs[k] + b[k]);
+        r /= bs[k];
+        stride *= s[k];
+      }
+      for (int64_t j = 0; j < bs[3]; ++j) AT(dst, w, idx, j + b[3]) = AT(A, w, idx, j + b[3]) + 1.0f;
+    }
+    return;
+  }
+  /* reductions (cases 4-6): trailing = product of the extents behind the axis, size = the axis' extent */
+  int64_t trailing = 1, size = 1;
+  if (id >= 4 && id <= 6) {
+    size = s[p0];
+    for (int64_t k = p0 + 1; k < 4; ++k) trailing *= s[k];
+  }
+#pragma omp parallel for
+  for (int64_t i = 0; i < rows; ++i) {
+    for (int64_t j = 0; j < cols; ++j) {
+      const int64_t lin = i * cols + j;
+      float v = 0.0f;
+      switch (id) {
+        case 0:  /* range.h:53-55 */
+          v = (float)p0 + (float)((int)j / 2) * 0.5f;
+          break;
+        case 1:
+          v = (float)(p0 + p1) + (float)((int)j / 1) * -1.5f;
+          break;
+        case 2: {  /* slice_ex.h:101-111 */
+          int64_t idx = 0, stride = 1, r = i;
+          for (int k = 2; k >= 0; --k) {
+            idx += stride * (r % o[k] + b[k]);
+            r /= o[k];
+            stride *= s[k];
+          }
+          v = AT(A, w, idx, j + b[3]);
+        } break;
+        case 4: case 5: case 6: {  /* reduce_with_axis.h:103-127 */
+          const int64_t x = lin / trailing, y = lin % trailing;
+          float res = id == 4 ? 0.0f : (id == 5 ? -FLT_MAX : FLT_MAX);
+          int64_t pos = 0;
+          for (int64_t k = 0; k < size; ++k) {
+            const int64_t z = (x * size + k) * trailing + y;
+            const float a = AT(A, w, z / w, z % w), before = res;
+            if (id == 4) res += a;
+            else if (id == 5) res = res < a ? a : res;
+            else res = a < res ? a : res;
+            if (before != res) pos = k;
+          }
+          v = id == 5 ? (float)(int)pos : res;
+        } break;
+        case 7: {  /* broadcast_with_axis.h:205-210: source (n*c, h, w), last extent w */
+          int64_t tr = 1;
+          const int64_t s3[3] = {n * c, h, w};
+          for (int64_t k = p0; k < 3; ++k) tr *= s3[k];
+          const int64_t x = lin / tr / p1, y = lin % tr, z = x * tr + y;
+          v = AT(A, w, z / w, z % w);
+        } break;
+        case 8: {  /* source slice<1>(A, 0, 1) = (n, 1, h, w): trailing h*w, last extent w; slice.h:101-109 */
+          const int64_t tr = h * w, x = lin / tr / p1, y = lin % tr, z = x * tr + y;
+          const int64_t srow = z / w, scol = z % w;  /* row (b, 0, yy) of the slice is row (b*c + 0)*h + yy of A */
+          v = AT(A, w, (srow / h) * c * h + srow % h, scol);
+        } break;
+        case 9: {  /* broadcast_with_axis.h:229-238: axes (1, 3) of (n, 1, h, 1), trailings (h*p1, 1), last extent 1 */
+          int64_t idx = lin;
+          idx = (idx / (h * p1) / p0) * (h * p1) + idx % (h * p1);
+          idx = (idx / 1 / p1) * 1 + idx % 1;
+          v = A[idx];
+        } break;
+        default: {  /* axes (0, 2) of (1, c, 1, w): trailings (c*p1*w, w), last extent w */
+          int64_t idx = lin;
+          idx = (idx / (c * p1 * w) / p0) * (c * p1 * w) + idx % (c * p1 * w);
+          idx = (idx / w / p1) * w + idx % w;
+          v = A[idx];
+        } break;
+      }
+      dst[lin] = v;
+    }
+  }
+}
+
 int ORC(num_threads)(void) {
 #ifdef _OPENMP
   return omp_get_max_threads();

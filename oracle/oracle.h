@@ -187,6 +187,31 @@ void ORC(unpack_patch2col)(float *mat, const float *img, int64_t n, int64_t c, i
 void ORC(pack_col2patch)(float *img, const float *mat, int64_t n, int64_t c, int64_t h, int64_t w,
                          int psy, int psx, int sy, int sx, int dy, int dx);
 
+/*
+ * Expressions addressed by an axis number or a begin/end box, evaluated through MapExp on a dense
+ * fp32 tensor A of shape (n, c, h, w); p0, p1 are per-case parameters.  `dst` is dense with the
+ * case's result shape; axis_shape() writes its extents to out_shape (unused entries 1) and
+ * returns their number.
+ *    0  dst = range(p0, p0 + p1, 0.5f, 2)              (1-d)       extension/range.h
+ *    1  dst = range(p0 + p1, p0, -1.5f, 1)             (1-d)
+ *    2  dst = slice(A, begin, end)                                 extension/slice_ex.h
+ *         begin = (p0 % n, p1 % c, p0 % h, p1 % w), end = (n, c, begin_h + (h - begin_h + 1) / 2, w)
+ *    3  dst = A * 2;  slice(dst, begin, end) = slice(A, begin, end) + 1    (the box as l-value)
+ *    4  dst = reduce_with_axis<red::sum, false>(A, p0)  (3-d)      extension/reduce_with_axis.h
+ *    5  dst = reduce_with_axis<red::maximum, true>(A, p0)   (position of the maximum along the axis)
+ *    6  dst = reduce_keepdim<red::minimum, false>(A, p0)  (4-d, extent 1 at p0)
+ *    7  dst = broadcast_with_axis(A3, p0 - 1, p1), A3 = A seen as (n*c, h, w)   extension/broadcast_with_axis.h
+ *    8  dst = broadcast_keepdim(slice<1>(A, 0, 1), 1, p1)  -> (n, p1, h, w)
+ *    9  dst = broadcast_to(S, (n, p0, h, p1)), S = the first n*h elements of A seen as (n, 1, h, 1)
+ *   10  dst = broadcast_multi_axes(S, axes (0, 2), sizes (p0, p1)), S = the first c*w elements of A
+ *         seen as (1, c, 1, w)  -> (p0, c, p1, w)
+ */
+#define ORC_NUM_AXIS_CASES 11
+int ORC(axis_shape)(int id, int64_t n, int64_t c, int64_t h, int64_t w, int64_t p0, int64_t p1,
+                    int64_t out_shape[4]);
+void ORC(axis_case)(int id, float *dst, const float *A, int64_t n, int64_t c, int64_t h, int64_t w,
+                    int64_t p0, int64_t p1);
+
 /* number of OpenMP threads the library will use (for cpu_baseline.cores) */
 int ORC(num_threads)(void);
 

@@ -325,6 +325,103 @@ void ref_pack_col2patch(float *imgp, const float *matp, int64_t n, int64_t c, in
   d = pack_col2patch(mat(matp, (int64_t)psy * psx * c, oh * ow * n, oh * ow * n), d.shape_, psy, psx, sy, sx, dy, dx);
 }
 
+extern "C++" {
+namespace {
+/* stand-in for the callers' dynamic shape type that broadcast_multi_axes / broadcast_to are templated on */
+struct DynShape {
+  std::vector<index_t> v;
+  DynShape() {}
+  template <typename It>
+  DynShape(It b, It e) : v(b, e) {}
+  index_t ndim() const { return static_cast<index_t>(v.size()); }
+  index_t operator[](size_t i) const { return v[i]; }
+};
+inline std::ostream &operator<<(std::ostream &os, const DynShape &s) {
+  for (size_t i = 0; i < s.v.size(); ++i) os << (i ? "," : "(") << s.v[i];
+  return os << ")";
+}
+inline void axis_box(int64_t n, int64_t c, int64_t h, int64_t w, int64_t p0, int64_t p1, Shape<4> *b, Shape<4> *e) {
+  *b = Shape4(p0 % n, p1 % c, p0 % h, p1 % w);
+  *e = Shape4(n, c, (*b)[2] + (h - (*b)[2] + 1) / 2, w);
+}
+template <int dim>
+inline Tensor<cpu, dim, float> dense(const float *p, Shape<dim> s) {
+  return Tensor<cpu, dim, float>(const_cast<float *>(p), s, s[dim - 1], NULL);
+}
+template <int dim>
+inline int put_shape(Shape<dim> s, int64_t o[4]) {
+  for (int i = 0; i < 4; ++i) o[i] = i < dim ? s[i] : 1;
+  return dim;
+}
+}  // namespace
+}  // extern "C++"
+
+int ref_axis_shape(int id, int64_t n, int64_t c, int64_t h, int64_t w, int64_t p0, int64_t p1, int64_t o[4]) {
+  /* shapes come from the reference's own expression objects */
+  float dummy = 0.0f;
+  T4 a = img(&dummy, n, c, h, w, w);
+  Shape<4> b, e;
+  axis_box(n, c, h, w, p0, p1, &b, &e);
+  std::vector<index_t> ax(2), sz(2);
+  switch (id) {
+    case 0: return put_shape(ShapeCheck<1, RangeExp<float> >::Check(range<float>(p0, p0 + p1, 0.5f, 2)), o);
+    case 1: return put_shape(ShapeCheck<1, RangeExp<float> >::Check(range<float>(p0 + p1, p0, -1.5f, 1)), o);
+    case 2: return put_shape(slice(a, b, e).shape_, o);
+    case 3: return put_shape(a.shape_, o);
+    case 4: return put_shape(reduce_with_axis<red::sum, false>(a, p0).shape_, o);
+    case 5: return put_shape(reduce_with_axis<red::maximum, true>(a, p0).shape_, o);
+    case 6: return put_shape(reduce_keepdim<red::minimum, false>(a, p0).shape_, o);
+    case 7: return put_shape(broadcast_with_axis(dense(&dummy, Shape3(n * c, h, w)), p0 - 1, p1).shape_, o);
+    case 8: return put_shape(broadcast_keepdim(slice<1>(a, 0, 1), 1, p1).shape_, o);
+    case 9: {
+      sz.resize(4);
+      sz[0] = n; sz[1] = p0; sz[2] = h; sz[3] = p1;
+      return put_shape(broadcast_to(dense(&dummy, Shape4(n, 1, h, 1)), DynShape(sz.begin(), sz.end())).shape_, o);
+    }
+    default:
+      ax[0] = 0; ax[1] = 2; sz[0] = p0; sz[1] = p1;
+      return put_shape(broadcast_multi_axes(dense(&dummy, Shape4(1, c, 1, w)), DynShape(ax.begin(), ax.end()),
+                                            DynShape(sz.begin(), sz.end())).shape_, o);
+  }
+}
+
+void ref_axis_case(int id, float *dst, const float *A, int64_t n, int64_t c, int64_t h, int64_t w, int64_t p0,
+                   int64_t p1) {
+  int64_t o[4];
+  ref_axis_shape(id, n, c, h, w, p0, p1, o);
+  T4 a = img(A, n, c, h, w, w);
+  T4 d4 = dense(dst, Shape4(o[0], o[1], o[2], o[3]));
+  Tensor<cpu, 3, float> d3 = dense(dst, Shape3(o[0], o[1], o[2]));
+  T1 d1 = vec(dst, o[0]);
+  Shape<4> b, e;
+  axis_box(n, c, h, w, p0, p1, &b, &e);
+  std::vector<index_t> ax(2), sz(2);
+  switch (id) {
+    case 0: d1 = range<float>(p0, p0 + p1, 0.5f, 2); break;
+    case 1: d1 = range<float>(p0 + p1, p0, -1.5f, 1); break;
+    case 2: d4 = slice(a, b, e); break;
+    case 3:
+      d4 = a * 2.0f;
+      slice(d4, b, e) = slice(a, b, e) + 1.0f;
+      break;
+    case 4: d3 = reduce_with_axis<red::sum, false>(a, p0); break;
+    case 5: d3 = reduce_with_axis<red::maximum, true>(a, p0); break;
+    case 6: d4 = reduce_keepdim<red::minimum, false>(a, p0); break;
+    case 7: d4 = broadcast_with_axis(dense(A, Shape3(n * c, h, w)), p0 - 1, p1); break;
+    case 8: d4 = broadcast_keepdim(slice<1>(a, 0, 1), 1, p1); break;
+    case 9:
+      sz.resize(4);
+      sz[0] = n; sz[1] = p0; sz[2] = h; sz[3] = p1;
+      d4 = broadcast_to(dense(A, Shape4(n, 1, h, 1)), DynShape(sz.begin(), sz.end()));
+      break;
+    default:
+      ax[0] = 0; ax[1] = 2; sz[0] = p0; sz[1] = p1;
+      d4 = broadcast_multi_axes(dense(A, Shape4(1, c, 1, w)), DynShape(ax.begin(), ax.end()),
+                                DynShape(sz.begin(), sz.end()));
+      break;
+  }
+}
+
 int ref_num_threads(void) {
 #ifdef _OPENMP
   return omp_get_max_threads();

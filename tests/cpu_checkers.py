@@ -177,6 +177,22 @@ class Checker:
                                i64(p1))
         return dst
 
+    def axis_shape(self, cid, shape, p0=0, p1=1):
+        out = (i64 * 4)()
+        n, c, h, w = shape
+        fn = self._fn("axis_shape")
+        fn.restype = C.c_int
+        ndim = fn(C.c_int(cid), i64(n), i64(c), i64(h), i64(w), i64(p0), i64(p1), out)
+        return tuple(int(v) for v in out[:ndim])
+
+    def axis_case(self, cid, A, p0=0, p1=1):
+        """Evaluates axis/box-addressed case `cid` on a dense (n, c, h, w) input; returns the result."""
+        assert A.flags.c_contiguous
+        n, c, h, w = A.shape
+        dst = np.full(self.axis_shape(cid, A.shape, p0, p1), np.float32(9.0), dtype=np.float32)
+        self._fn("axis_case")(C.c_int(cid), _fp(dst), _fp(A), i64(n), i64(c), i64(h), i64(w), i64(p0), i64(p1))
+        return dst
+
     def select_case(self, cid, A, B, idx_r, idx_c, p0=1):
         """Evaluates index-selecting case `cid` on dense (rows, cols) inputs; returns the result."""
         rows, cols = A.shape
@@ -257,6 +273,25 @@ def remap_params(cid, shape):
     if cid in (10, 11):
         return sorted({(h, w), (1, 1), (max(1, h - 2), max(1, w - 8)), (max(1, h - 1), max(1, w - 3))})
     return [(0, 0)]
+
+
+NUM_AXIS_CASES = 11
+
+
+def axis_params(cid, shape):
+    """Valid (p0, p1) pairs for axis/box-addressed case `cid` on an (n, c, h, w) input."""
+    n, c, h, w = shape
+    if cid in (0, 1):
+        return [(0, 1), (3, 7), (-5, 12), (100, 64)]
+    if cid in (2, 3):
+        return [(0, 0), (1, 1), (2, 4), (5, 3)]
+    if cid in (4, 5, 6):
+        return [(axis, 0) for axis in range(4)]
+    if cid == 7:
+        return [(axis, size) for axis in range(4) for size in (1, 3)]
+    if cid == 8:
+        return [(0, 1), (0, 4), (0, 7)]
+    return [(1, 1), (2, 3), (4, 4), (3, 1), (1, 5)]
 
 
 _cache = {}

@@ -9,6 +9,7 @@
 #include <string>
 
 #include "mshadow/tensor.h"
+#include "../../mshadow_b200/csrc/axis_cases.h"
 
 using namespace mshadow;        // NOLINT(*)
 using namespace mshadow::expr;  // NOLINT(*)
@@ -114,6 +115,21 @@ void hostmsb_half_expr(const uint16_t *a, const uint16_t *b, uint16_t *dst, int6
   Tensor<cpu, 2, H> B(reinterpret_cast<H *>(const_cast<uint16_t *>(b)), Shape2(rows, cols));
   Tensor<cpu, 2, H> D(reinterpret_cast<H *>(dst), Shape2(rows, cols));
   D = A * B + A * H(0.5f) - B / (A * A + H(2.0f));
+}
+
+/* the cases of msb_axis_case_f32, on host memory (dst == NULL: shape query only); returns 0, 1 when a CHECK of
+   the engine fired, 2 when the arguments are outside the case's domain */
+int hostmsb_axis_case(int id, float *dst, const float *A, int64_t n, int64_t c, int64_t h, int64_t w, int64_t p0,
+                      int64_t p1, int64_t *out_shape, int *out_ndim) {
+  if (id < 0 || id >= msb_axis::kNumCases || !msb_axis::ArgsOk(id, n, c, h, w, p0, p1)) return 2;
+  try {
+    *out_ndim = msb_axis::ResultShape<cpu>(id, n, c, h, w, p0, p1, out_shape);
+    if (dst != nullptr) msb_axis::Run<cpu>(id, dst, A, n, c, h, w, p0, p1, static_cast<Stream<cpu> *>(nullptr));
+  } catch (const std::exception &e) {
+    g_error = e.what();
+    return 1;
+  }
+  return 0;
 }
 
 /* the cases of msb_remap_case_f32, on host memory; returns 0, or 1 when a CHECK of the engine fired */

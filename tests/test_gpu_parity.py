@@ -437,6 +437,32 @@ def test_patch_conversions(lib, case):
     assert_bits(host(got_img), want_img)
 
 
+@pytest.mark.parametrize("cid", range(cc.NUM_AXIS_CASES))
+@pytest.mark.parametrize("shape", [(2, 3, 4, 5), (3, 8, 16, 64), (2, 5, 7, 33), (1, 4, 8, 128), (2, 2, 3, 1),
+                                   (4, 12, 20, 24)])
+def test_axis_expressions(lib, cid, shape):
+    """range / slice(begin, end) / reduce_with_axis / reduce_keepdim / broadcast_with_axis / broadcast_keepdim /
+    broadcast_to / broadcast_multi_axes: bit-exact (the reductions add along their axis in order on both sides)."""
+    rng = np.random.default_rng(cid * 1000 + sum(shape))
+    A = rng.uniform(-1, 1, shape).astype(np.float32)
+    if cid == 5:
+        A[0, 0] = A[-1, -1]  # ties: the reported position must be the reference's
+    for p0, p1 in cc.axis_params(cid, shape):
+        want = orc.axis_case(cid, A, p0, p1)
+        assert lib.axis_shape(cid, shape, p0, p1) == want.shape
+        got = lib.axis_case(cid, torch.full(want.shape, 9.0, device="cuda"), dev(A), p0, p1)
+        assert_bits(host(got), want)
+
+
+def test_axis_argument_errors(lib):
+    import ctypes as C
+    z = torch.zeros(2, 3, 4, 5, device="cuda")
+    p = C.c_void_p(z.data_ptr())
+    assert lib.status("msb_axis_case_f32", 4, p, p, 2, 3, 4, 5, 4, 0, None)[0] == 2    # no such axis
+    assert lib.status("msb_axis_case_f32", 0, p, p, 2, 3, 4, 5, 0, 0, None)[0] == 2    # an empty range
+    assert lib.status("msb_axis_case_f32", 11, p, p, 2, 3, 4, 5, 0, 1, None)[0] == 1   # no such case
+
+
 def test_remap_argument_errors(lib):
     import ctypes as C
     z = torch.zeros(2, 3, 4, 5, device="cuda")

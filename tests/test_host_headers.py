@@ -116,6 +116,41 @@ def test_select_plans_on_the_host(host, cid, rows, cols):
         assert np.array_equal(got.view(np.uint32), want.view(np.uint32)), (cid, p0)
 
 
+def run_axis(dll, cid, A, p0, p1):
+    n, c, h, w = A.shape
+    shape, ndim = (i64 * 4)(), C.c_int(0)
+    dims = (i64(n), i64(c), i64(h), i64(w), i64(p0), i64(p1))
+    st = dll.hostmsb_axis_case(cid, None, None, *dims, shape, C.byref(ndim))
+    if st != 0:
+        return st, None
+    dst = np.full(tuple(int(v) for v in shape[:ndim.value]), np.float32(9.0), np.float32)
+    st = dll.hostmsb_axis_case(cid, dst.ctypes.data_as(f32p), A.ctypes.data_as(f32p), *dims, shape, C.byref(ndim))
+    return st, dst
+
+
+@pytest.mark.parametrize("cid", range(cc.NUM_AXIS_CASES))
+@pytest.mark.parametrize("shape", [(2, 3, 4, 5), (1, 8, 6, 16), (3, 5, 1, 7), (2, 2, 3, 1), (2, 7, 9, 12)])
+def test_axis_plans_on_the_host(host, cid, shape):
+    rng = np.random.default_rng(cid * 100 + sum(shape))
+    A = rng.uniform(-1, 1, shape).astype(np.float32)
+    if cid == 5:
+        A[0, 0] = A[-1, -1]
+    for p0, p1 in cc.axis_params(cid, shape):
+        want = orc.axis_case(cid, A, p0, p1)
+        st, got = run_axis(host, cid, A, p0, p1)
+        assert st == 0, host.hostmsb_last_error()
+        assert got.shape == want.shape
+        assert np.array_equal(got.view(np.uint32), want.view(np.uint32)), (cid, p0, p1)
+
+
+def test_axis_arguments_outside_the_domain_are_refused(host):
+    A = np.zeros((2, 3, 4, 5), np.float32)
+    assert run_axis(host, 4, A, 4, 0)[0] == 2   # no such axis
+    assert run_axis(host, 0, A, 0, 0)[0] == 2   # an empty range
+    assert run_axis(host, 7, A, 0, 0)[0] == 2   # a broadcast extent of zero
+    assert run_axis(host, 11, A, 0, 1)[0] == 2  # no such case
+
+
 @pytest.mark.parametrize("case", cc.PATCH_CASES)
 def test_patch_plans_on_the_host(host, case):
     shape, psy, psx, sy, sx, dy, dx = case

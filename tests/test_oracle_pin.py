@@ -221,6 +221,45 @@ def test_remap_cases_match_reference(cid, shape):
 
 
 @needs_ref
+@pytest.mark.parametrize("cid", range(cc.NUM_AXIS_CASES))
+@pytest.mark.parametrize("shape", [(2, 3, 4, 5), (1, 8, 6, 16), (3, 5, 1, 7), (2, 2, 3, 1)])
+def test_axis_cases_match_reference(cid, shape):
+    rng = np.random.default_rng(cid * 100 + sum(shape))
+    A = rnd(rng, shape)
+    if cid == 5:
+        A[0, 0] = A[-1, -1]  # ties along every axis: the position reported must be the reference's
+    for p0, p1 in cc.axis_params(cid, shape):
+        assert orc.axis_shape(cid, shape, p0, p1) == ref.axis_shape(cid, shape, p0, p1)
+        res = [lib.axis_case(cid, A, p0, p1) for lib in (orc, ref)]
+        assert same_bits(*res), (cid, p0, p1)
+
+
+def test_axis_known_answers():
+    rng = np.random.default_rng(5)
+    A = rnd(rng, (2, 3, 4, 5))
+    assert np.array_equal(orc.axis_case(0, A, 3, 2), np.repeat(np.float32(3) + np.arange(4, dtype=np.float32) * 0.5, 2))
+    assert np.array_equal(orc.axis_case(1, A, 3, 4), np.array([7, 5.5, 4], dtype=np.float32))
+    assert np.array_equal(orc.axis_case(2, A, 1, 2), A[1:, 2:, 1:3, 2:])
+    want = A * 2
+    want[1:, 2:, 1:3, 2:] = A[1:, 2:, 1:3, 2:] + 1
+    assert np.array_equal(orc.axis_case(3, A, 1, 2), want)
+    for axis in range(4):
+        seq = np.zeros(np.delete(A.shape, axis), dtype=np.float32)
+        for k in range(A.shape[axis]):
+            seq = seq + np.take(A, k, axis=axis)  # the reference adds along the axis in order
+        assert np.array_equal(orc.axis_case(4, A, axis), seq)
+        assert np.array_equal(orc.axis_case(5, A, axis), A.argmax(axis=axis).astype(np.float32))
+        assert np.array_equal(orc.axis_case(6, A, axis), A.min(axis=axis, keepdims=True))
+        A3 = A.reshape(6, 4, 5)
+        assert np.array_equal(orc.axis_case(7, A, axis, 3), np.repeat(np.expand_dims(A3, axis), 3, axis=axis))
+    assert np.array_equal(orc.axis_case(8, A, 0, 4), np.repeat(A[:, :1], 4, axis=1))
+    S = A.ravel()[:8].reshape(2, 1, 4, 1)
+    assert np.array_equal(orc.axis_case(9, A, 3, 2), np.broadcast_to(S, (2, 3, 4, 2)))
+    S = A.ravel()[:15].reshape(1, 3, 1, 5)
+    assert np.array_equal(orc.axis_case(10, A, 2, 3), np.broadcast_to(S, (2, 3, 3, 5)))
+
+
+@needs_ref
 @pytest.mark.parametrize("cid", range(cc.NUM_SELECT_CASES))
 @pytest.mark.parametrize("rows,cols", [(5, 7), (16, 64), (1, 1), (33, 12)])
 def test_select_cases_match_reference(cid, rows, cols):
