@@ -342,6 +342,41 @@ struct ExpEngine {
   }
 };
 
+// ----------------------------------------------------------------------------------------
+// LaneInfo<E>::kPass: every node of E is a cheap, side-effect free Eval(y, x) (arithmetic and
+// index remapping, no loop over other elements).  For such an expression without EvalPack the
+// map kernel still writes the destination in 16-byte groups, each put together from element
+// evaluations.  Expressions whose Eval walks many elements (reductions, take_grad) stay out:
+// one thread would serialise several such walks.  Unknown (user-defined) expressions default
+// to false.
+// ----------------------------------------------------------------------------------------
+template <typename E>
+struct LaneInfo {
+  static const bool kPass = false;
+};
+template <typename T, typename SrcExp, int dim, typename DType>
+struct LaneInfo<MakeTensorExp<T, SrcExp, dim, DType> > : public LaneInfo<T> {};
+template <typename DType>
+struct LaneInfo<ScalarExp<DType> > {
+  static const bool kPass = true;
+};
+template <typename Device, int dim, typename DType>
+struct LaneInfo<Tensor<Device, dim, DType> > {
+  static const bool kPass = true;
+};
+template <typename DstDType, typename SrcDType, typename EType, int etype>
+struct LaneInfo<TypecastExp<DstDType, SrcDType, EType, etype> > : public LaneInfo<EType> {};
+template <typename OP, typename TA, typename DType, int etype>
+struct LaneInfo<UnaryMapExp<OP, TA, DType, etype> > : public LaneInfo<TA> {};
+template <typename OP, typename TA, typename TB, typename DType, int etype>
+struct LaneInfo<BinaryMapExp<OP, TA, TB, DType, etype> > {
+  static const bool kPass = LaneInfo<TA>::kPass && LaneInfo<TB>::kPass;
+};
+template <typename OP, typename TA, typename TB, typename TC, typename DType, int etype>
+struct LaneInfo<TernaryMapExp<OP, TA, TB, TC, DType, etype> > {
+  static const bool kPass = LaneInfo<TA>::kPass && LaneInfo<TB>::kPass && LaneInfo<TC>::kPass;
+};
+
 }  // namespace expr
 
 #if MSHADOW_USE_CUDA

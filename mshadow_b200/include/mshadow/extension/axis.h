@@ -485,6 +485,18 @@ class Plan<BroadcastWithMultiAxesExp<SrcExp, DType, dimsrc>, DType> {
   FastDiv by_trailing_[dimsrc], by_size_[dimsrc];
 };
 
+// cheap per-element plans; the reductions stay out (their Eval walks a whole axis)
+template <typename DType>
+struct LaneInfo<RangeExp<DType> > {
+  static const bool kPass = true;
+};
+template <typename SrcExp, typename Device, typename DType, int srcdim>
+struct LaneInfo<SliceExExp<SrcExp, Device, DType, srcdim> > : public LaneInfo<SrcExp> {};
+template <typename SrcExp, typename DType, int dimsrc, int dimdst>
+struct LaneInfo<BroadcastWithAxisExp<SrcExp, DType, dimsrc, dimdst> > : public LaneInfo<SrcExp> {};
+template <typename SrcExp, typename DType, int dimsrc>
+struct LaneInfo<BroadcastWithMultiAxesExp<SrcExp, DType, dimsrc> > : public LaneInfo<SrcExp> {};
+
 }  // namespace expr
 }  // namespace mshadow
 #endif  // MSHADOW_EXTENSION_AXIS_H_

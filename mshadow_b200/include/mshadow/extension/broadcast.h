@@ -90,6 +90,8 @@ struct PackAlign<Broadcast1DExp<SrcExp, DType, dimdst, dimdst_m_cast> > {
     return PackAlign<SrcExp>::Check(e.src_);
   }
 };
+template <typename SrcExp, typename DType, int dimdst, int dimdst_m_cast>
+struct LaneInfo<Broadcast1DExp<SrcExp, DType, dimdst, dimdst_m_cast> > : public LaneInfo<SrcExp> {};
 
 }  // namespace expr
 }  // namespace mshadow

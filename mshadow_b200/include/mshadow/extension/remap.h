@@ -743,6 +743,28 @@ class Plan<FlipExp<SrcExp, Device, DType, srcdim>, DType> {
   const FastDiv by_stride_j_, by_trailing_, by_stride_;
 };
 
+// every plan of this file is pure index arithmetic around its source's Eval
+template <typename SrcExp, typename DType, int dimdst, int dimsrc>
+struct LaneInfo<ReshapeExp<SrcExp, DType, dimdst, dimsrc> > : public LaneInfo<SrcExp> {};
+template <typename SrcExp, typename Device, typename DType, int srcdim, int dimsrc_m_slice>
+struct LaneInfo<SliceExp<SrcExp, Device, DType, srcdim, dimsrc_m_slice> > : public LaneInfo<SrcExp> {};
+template <typename LhsExp, typename RhsExp, typename Device, typename DType, int srcdim, int dimsrc_m_cat>
+struct LaneInfo<ConcatExp<LhsExp, RhsExp, Device, DType, srcdim, dimsrc_m_cat> > {
+  static const bool kPass = LaneInfo<LhsExp>::kPass && LaneInfo<RhsExp>::kPass;
+};
+template <typename SrcExp, typename DType, int dimsrc, int m_a1, int a2>
+struct LaneInfo<SwapAxisExp<SrcExp, DType, dimsrc, m_a1, a2> > : public LaneInfo<SrcExp> {};
+template <typename SrcExp, typename DType, int dimsrc>
+struct LaneInfo<TransposeExExp<SrcExp, DType, dimsrc> > : public LaneInfo<SrcExp> {};
+template <typename SrcExp, typename DType, int srcdim>
+struct LaneInfo<PaddingExp<SrcExp, DType, srcdim> > : public LaneInfo<SrcExp> {};
+template <typename SrcExp, typename DType, int srcdim>
+struct LaneInfo<CroppingExp<SrcExp, DType, srcdim> > : public LaneInfo<SrcExp> {};
+template <typename SrcExp, typename DType, int srcdim>
+struct LaneInfo<MirroringExp<SrcExp, DType, srcdim> > : public LaneInfo<SrcExp> {};
+template <typename SrcExp, typename Device, typename DType, int srcdim>
+struct LaneInfo<FlipExp<SrcExp, Device, DType, srcdim> > : public LaneInfo<SrcExp> {};
+
 }  // namespace expr
 
 #if MSHADOW_USE_CUDA && defined(__CUDACC__)

@@ -418,6 +418,28 @@ class Plan<UpSamplingNearestExp<SrcExp, DType, srcdim>, DType> {
   const index_t src_height_;
 };
 
+// one or two look-ups per element; take_grad stays out (its Eval walks the whole batch)
+template <typename IndexExp, typename SrcExp, typename DType>
+struct LaneInfo<TakeExp<IndexExp, SrcExp, DType> > {
+  static const bool kPass = LaneInfo<IndexExp>::kPass && LaneInfo<SrcExp>::kPass;
+};
+template <typename IndexExp, typename DType>
+struct LaneInfo<OneHotEncodeExp<IndexExp, DType> > : public LaneInfo<IndexExp> {};
+template <typename SrcExp, typename IndexExp, typename DType>
+struct LaneInfo<MatChooseRowElementExp<SrcExp, IndexExp, DType> > {
+  static const bool kPass = LaneInfo<IndexExp>::kPass && LaneInfo<SrcExp>::kPass;
+};
+template <typename SrcExp, typename ValExp, typename IndexExp, typename DType>
+struct LaneInfo<MatFillRowElementExp<SrcExp, ValExp, IndexExp, DType> > {
+  static const bool kPass = LaneInfo<IndexExp>::kPass && LaneInfo<SrcExp>::kPass && LaneInfo<ValExp>::kPass;
+};
+template <typename IndexExp, typename SrcExp, typename DType>
+struct LaneInfo<MaskExp<IndexExp, SrcExp, DType> > {
+  static const bool kPass = LaneInfo<IndexExp>::kPass && LaneInfo<SrcExp>::kPass;
+};
+template <typename SrcExp, typename DType, int srcdim>
+struct LaneInfo<UpSamplingNearestExp<SrcExp, DType, srcdim> > : public LaneInfo<SrcExp> {};
+
 }  // namespace expr
 }  // namespace mshadow
 #endif  // MSHADOW_EXTENSION_SELECT_H_

@@ -21,47 +21,36 @@
 namespace mshadow {
 namespace cuda {
 
-namespace mapdetail {
-// the expression type supports 16-byte evaluation: decide per call from pointers and strides
-template <typename Saver, typename DType, typename R, typename E, int dim>
-inline void Go(R *dst, const E &exp, Shape<dim> dshape, cudaStream_t stream, std::true_type) {
-  const Shape<2> flat = dshape.FlatTo2D();
-  if (expr::PackAlign<E>::Check(exp) && expr::PackAlign<R>::Check(*dst)) {
-    const bool one_row = expr::FlatInfo<E>::kPass && expr::FlatInfo<R>::kPass && expr::FlatCheck<E>::Check(exp) &&
-                         expr::FlatCheck<R>::Check(*dst);
-    MapPlanPacked<Saver, DType>(expr::MakePlan(*dst), expr::MakePlan(exp), flat, one_row, stream);
-  } else {
-    MapPlanScalar<Saver, DType>(expr::MakePlan(*dst), expr::MakePlan(exp), flat, stream);
-  }
-}
-template <typename Saver, typename DType, typename R, typename E, int dim>
-inline void Go(R *dst, const E &exp, Shape<dim> dshape, cudaStream_t stream, std::false_type) {
-  MapPlanScalar<Saver, DType>(expr::MakePlan(*dst), expr::MakePlan(exp), dshape.FlatTo2D(), stream);
-}
-// the expression only knows Eval(y, x) but the destination can be written 16 bytes at a time:
-// groups are assembled from element evaluations (one row split and one wide store per group)
-template <typename Saver, typename DType, typename R, typename E, int dim>
-inline void GoHybrid(R *dst, const E &exp, Shape<dim> dshape, cudaStream_t stream, std::true_type) {
-  if (expr::PackAlign<R>::Check(*dst)) {
-    MapPlanPacked<Saver, DType, false>(expr::MakePlan(*dst), expr::MakePlan(exp), dshape.FlatTo2D(), false, stream);
-  } else {
-    MapPlanScalar<Saver, DType>(expr::MakePlan(*dst), expr::MakePlan(exp), dshape.FlatTo2D(), stream);
-  }
-}
-template <typename Saver, typename DType, typename R, typename E, int dim>
-inline void GoHybrid(R *dst, const E &exp, Shape<dim> dshape, cudaStream_t stream, std::false_type) {
-  MapPlanScalar<Saver, DType>(expr::MakePlan(*dst), expr::MakePlan(exp), dshape.FlatTo2D(), stream);
-}
-}  // namespace mapdetail
-
+/*!
+ * \brief the generic route of `dst <Saver>= exp`, decided per call:
+ *  1. expression and destination both serve 16-byte groups and all pointers, strides and slice
+ *     boundaries are aligned: the 128-bit kernel (walked as one long row where every operand is
+ *     dense and the expression position-independent);
+ *  2. only the destination does, and the expression is cheap per element (expr::LaneInfo): the
+ *     128-bit kernel with groups assembled from element evaluations, which keeps one index
+ *     split and one wide store per four floats;
+ *  3. otherwise one element per thread.
+ */
 template <typename Saver, typename DType, typename R, typename E, int dim>
 inline void MapGeneric(R *dst, const E &exp, Shape<dim> dshape, cudaStream_t stream) {
-  constexpr bool kSrcPack = expr::PackInfo<E>::kPass, kDstPack = expr::PackInfo<R>::kPass;
-  if constexpr (kSrcPack || !MSHADOW_B200_MAP_HYBRID) {
-    mapdetail::Go<Saver, DType>(dst, exp, dshape, stream, std::integral_constant<bool, kSrcPack && kDstPack>());
-  } else {
-    mapdetail::GoHybrid<Saver, DType>(dst, exp, dshape, stream, std::integral_constant<bool, kDstPack>());
+  const Shape<2> flat = dshape.FlatTo2D();
+  if constexpr (expr::PackInfo<R>::kPass) {
+    if (expr::PackAlign<R>::Check(*dst)) {
+      if constexpr (expr::PackInfo<E>::kPass) {
+        if (expr::PackAlign<E>::Check(exp)) {
+          const bool one_row = expr::FlatInfo<E>::kPass && expr::FlatInfo<R>::kPass && expr::FlatCheck<E>::Check(exp) &&
+                               expr::FlatCheck<R>::Check(*dst);
+          MapPlanPacked<Saver, DType>(expr::MakePlan(*dst), expr::MakePlan(exp), flat, one_row, stream);
+          return;
+        }
+      }
+      if constexpr (expr::LaneInfo<E>::kPass && MSHADOW_B200_MAP_HYBRID) {
+        MapPlanPacked<Saver, DType, false>(expr::MakePlan(*dst), expr::MakePlan(exp), flat, false, stream);
+        return;
+      }
+    }
   }
+  MapPlanScalar<Saver, DType>(expr::MakePlan(*dst), expr::MakePlan(exp), flat, stream);
 }
 
 template <typename Saver, typename R, typename E, typename DType, int dim>
