@@ -19,6 +19,9 @@
 
 #include "../engine/check.h"
 #include "../engine/fastdiv.h"
+#if MSHADOW_USE_CUDA && defined(__CUDACC__)
+#include "../gpu/patch.cuh"
+#endif
 
 namespace mshadow {
 namespace expr {
@@ -270,5 +273,56 @@ struct PackAlign<PackColToPatchXExp<SrcExp, DType, dstdim> > {
 };
 
 }  // namespace expr
+
+#if MSHADOW_USE_CUDA && defined(__CUDACC__)
+namespace cuda {
+
+// `mat <Saver>= unpack_patch2col(tensor, ...)`: planes staged in shared memory where they fit
+template <typename Saver, typename DType, int srcdim>
+struct MapDispatch<Saver, Tensor<gpu, 2, DType>, expr::UnpackPatchToColXExp<Tensor<gpu, srcdim, DType>, DType, srcdim>,
+                   DType, 2> {
+  typedef expr::UnpackPatchToColXExp<Tensor<gpu, srcdim, DType>, DType, srcdim> E;
+  inline static void Run(Tensor<gpu, 2, DType> *dst, const E &e, Shape<2> dshape, cudaStream_t stream) {
+    const Tensor<gpu, srcdim, DType> &img = e.img_;
+    if (PatchPlaneFits(e.i_height_, e.i_width_, sizeof(DType))) {
+      PatchGeom g;
+      g.channels = e.i_channel_; g.h = e.i_height_; g.w = e.i_width_;
+      g.psy = e.psize_y_; g.psx = e.psize_x_; g.sy = e.pstride_y_; g.sx = e.pstride_x_;
+      g.dy = e.pdilate_y_; g.dx = e.pdilate_x_;
+      g.oh = (g.h - (g.dy * (g.psy - 1) + 1)) / g.sy + 1;
+      g.ow = (g.w - (g.dx * (g.psx - 1) + 1)) / g.sx + 1;
+      UnpackPatchLaunch<Saver, DType>(dst->dptr_, dst->stride_, img.dptr_, img.stride_,
+                                      img.shape_.ProdShape(0, srcdim - 2), g, stream);
+    } else {
+      MapGeneric<Saver, DType>(dst, e, dshape, stream);
+    }
+  }
+};
+
+// `img <Saver>= pack_col2patch(matrix, ...)` without dilation
+template <typename Saver, typename DType, int dstdim>
+struct MapDispatch<Saver, Tensor<gpu, dstdim, DType>, expr::PackColToPatchXExp<Tensor<gpu, 2, DType>, DType, dstdim>,
+                   DType, dstdim> {
+  typedef expr::PackColToPatchXExp<Tensor<gpu, 2, DType>, DType, dstdim> E;
+  inline static void Run(Tensor<gpu, dstdim, DType> *dst, const E &e, Shape<dstdim> dshape, cudaStream_t stream) {
+    const Tensor<gpu, 2, DType> &mat = e.src_;
+    if (e.pdilate_y_ == 1 && e.pdilate_x_ == 1 && PackPatchSupported(dshape[dstdim - 2], dshape[dstdim - 1])) {
+      PatchGeom g;
+      g.channels = dshape[dstdim - 3]; g.h = dshape[dstdim - 2]; g.w = dshape[dstdim - 1];
+      g.psy = e.psize_y_; g.psx = e.psize_x_; g.sy = e.pstride_y_; g.sx = e.pstride_x_;
+      g.dy = 1; g.dx = 1;
+      g.oh = (g.h - g.psy) / g.sy + 1;
+      g.ow = (g.w - g.psx) / g.sx + 1;
+      PackPatchLaunch<Saver, DType>(dst->dptr_, dst->stride_, mat.dptr_, mat.stride_, dshape.ProdShape(0, dstdim - 2), g,
+                                    stream);
+    } else {
+      MapGeneric<Saver, DType>(dst, e, dshape, stream);
+    }
+  }
+};
+
+}  // namespace cuda
+#endif  // MSHADOW_USE_CUDA && __CUDACC__
+
 }  // namespace mshadow
 #endif  // MSHADOW_EXTENSION_PATCH_H_

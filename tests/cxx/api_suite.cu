@@ -271,6 +271,26 @@ int RunCase(int id, const float *a, const float *b, float *out, int rows, int co
       FreeSpace(&colmax_f);
       break;
     }
+    case 16: {  // guide/neuralnet/convnet.cu style: patches of a 3-d image to columns and back, accumulating savers
+      const Shape<3> s3 = Shape3(2, 24, rows * cols / 48);
+      Tensor<gpu, 3, float> A = NewTensor<gpu>(s3, 0.0f, false, st), G = NewTensor<gpu>(s3, 0.0f, false, st);
+      Upload(A, a, st);
+      Upload(G, b, st);
+      const index_t oh = s3[1] - 2, ow = s3[2] - 2;
+      Tensor<gpu, 2, float> M = NewTensor<gpu>(Shape2(3 * 3 * 2, oh * ow), 1.0f, false, st);
+      M += unpack_patch2col(A, 3, 3, 1, 1);
+      G -= pack_col2patch(M, G.shape_, 3, 3, 1, 1);
+      const index_t oh2 = (s3[1] - 4) / 2 + 1, ow2 = s3[2] - 1;  // 4 x 2 patches, stride (2, 1)
+      Tensor<gpu, 2, float> M2 = NewTensor<gpu>(Shape2(4 * 2 * 2, oh2 * ow2), 0.0f, false, st);
+      M2 = unpack_patch2col(A, 4, 2, 2, 1, 1, 1);
+      G += pack_col2patch(M2, G.shape_, 4, 2, 2, 1, 1, 1);
+      Download(out, G, st);
+      FreeSpace(&A);
+      FreeSpace(&G);
+      FreeSpace(&M);
+      FreeSpace(&M2);
+      break;
+    }
     default:
       rc = -1;
   }

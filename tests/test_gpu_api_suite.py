@@ -189,3 +189,18 @@ def test_half_casts_and_exact_reduction(run, data):
     assert rc == 0
     assert bits_equal(out[:ROWS * COLS].reshape(ROWS, COLS), ah.astype(np.float32) * np.float32(2))
     assert bits_equal(out[ROWS * COLS:], ah.max(axis=0).astype(np.float32))
+
+
+def test_patch_columns_with_accumulating_savers(run, data):
+    """unpack_patch2col / pack_col2patch on a 3-d image with +=, -= (the dedicated kernels take any saver),
+    unit stride with a compile-time patch size and a strided 4 x 2 patch."""
+    a, b = data
+    rc, out = run(16, a, b, ROWS * COLS)
+    shape = (1, 2, 24, ROWS * COLS // 48)
+    img, g = a.reshape(shape), b.reshape(shape)
+    orc = cc.load("orc")
+    m = np.float32(1) + orc.unpack_patch2col(img, 3, 3, 1, 1, 1, 1)
+    g = g - orc.pack_col2patch(m, shape, 3, 3, 1, 1, 1, 1)
+    m2 = orc.unpack_patch2col(img, 4, 2, 2, 1, 1, 1)
+    g = g + orc.pack_col2patch(m2, shape, 4, 2, 2, 1, 1, 1)
+    assert rc == 0 and bits_equal(out.reshape(shape), g)

@@ -421,7 +421,14 @@ def test_select_expressions(lib, cid, rows, cols):
 
 
 @pytest.mark.parametrize("case", cc.PATCH_CASES + [((4, 16, 28, 28), 3, 3, 1, 1, 1, 1), ((2, 8, 31, 33), 5, 5, 2, 2, 1, 1),
-                                                   ((2, 3, 20, 20), 3, 3, 1, 1, 2, 2)])
+                                                   ((2, 3, 20, 20), 3, 3, 1, 1, 2, 2),
+                                                   # planes large enough for the staged kernels: odd widths,
+                                                   # strides that leave border pixels uncovered, dilation,
+                                                   # and a plane that needs nearly all shared memory
+                                                   ((2, 5, 28, 30), 5, 3, 2, 1, 1, 1), ((1, 4, 32, 32), 2, 2, 2, 2, 1, 1),
+                                                   ((2, 2, 23, 29), 3, 3, 1, 2, 2, 2), ((3, 2, 41, 20), 4, 4, 3, 3, 1, 1),
+                                                   ((2, 3, 24, 24), 1, 1, 1, 1, 1, 1), ((1, 2, 224, 224), 7, 7, 2, 2, 1, 1),
+                                                   ((1, 1, 250, 250), 3, 3, 1, 1, 1, 1)])
 def test_patch_conversions(lib, case):
     """unpack_patch2col is data movement (bit-exact); pack_col2patch adds the covering patches in the
     reference's order (bit-exact as well)."""
