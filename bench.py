@@ -437,6 +437,21 @@ def kernel_cases(lib, torch, small=False):
     for cid, name in ((7, "transpose(A,(0,2,1,3))"), (6, "swapaxis<3,1>(A)"), (12, "mirror(A)")):
         yield ("remap_%d" % cid, "%s %s" % (name, rs), 8 * RA.numel(), RA.numel(),
                lambda cid=cid: lib.remap_case(cid, RD, RA, RB), 10)
+    # a plan without 16-byte evaluation (zero padding): groups assembled from element evaluations
+    RP = torch.empty(lib.remap_shape(9, rs, 2, 4), device=dev)
+    yield ("remap_9", "pad(A, 2, 4) %s" % (rs,), 4 * RA.numel() + 4 * RP.numel(), RP.numel(),
+           lambda: lib.remap_case(9, RP, RA, RB, 2, 4), 10)
+    del RP
+    # folding and repeating an axis: sum over the channels, and a new axis of extent 2 behind the first
+    RS = torch.empty(lib.axis_shape(4, rs, 1, 0), device=dev)
+    yield ("axis_4", "reduce_with_axis<sum>(A, 1) %s" % (rs,), 4 * RA.numel() + 4 * RS.numel(), RA.numel(),
+           lambda: lib.axis_case(4, RS, RA, 1, 0), 10)
+    del RS, RD
+    RW = torch.empty(lib.axis_shape(7, rs, 1, 2), device=dev)
+    yield ("axis_7", "broadcast_with_axis(A3, 0, 2) %s" % (rs,), 4 * RA.numel() + 4 * RW.numel(), RW.numel(),
+           lambda: lib.axis_case(7, RW, RA, 1, 2), 10)
+    del RW
+    RD = None
     del RA, RB, RD
     # embedding look-up (the forward of AddTakeGrad): rows of a table gathered by an index vector
     tr, tc = (65536, 1024) if small else (262144, 1024)

@@ -20,6 +20,7 @@
 #include <utility>
 
 #include "../tensor.h"
+#include "../engine/fastdiv.h"
 #include "./tuning.h"
 
 namespace mshadow {
@@ -179,23 +180,8 @@ inline int *StatusWord() {
   return it->second;
 }
 
-/*! \brief exact division of a non-negative 31-bit number by a fixed divisor, without a divide */
-struct FastDiv {
-  uint32_t mul;
-  uint32_t shift;
-  uint32_t div;
-  FastDiv() : mul(0), shift(0), div(1) {}
-  explicit FastDiv(uint32_t d) : div(d) {
-    // q = (n * mul) >> (31 + ceil(log2 d)) is exact for all n < 2^31 (round-up method)
-    uint32_t lg = 0;
-    while ((1ull << lg) < d) ++lg;
-    shift = 31 + lg;
-    mul = static_cast<uint32_t>(((1ull << shift) + d - 1) / d);
-  }
-  MSHADOW_XINLINE uint32_t Quot(uint32_t n) const {
-    return div == 1 ? n : static_cast<uint32_t>((static_cast<uint64_t>(n) * mul) >> shift);
-  }
-};
+/*! \brief exact division of an index by a divisor fixed per launch, without a divide instruction */
+typedef expr::FastDiv FastDiv;
 
 inline int CeilDiv(int64_t a, int64_t b) { return static_cast<int>((a + b - 1) / b); }
 

@@ -117,6 +117,26 @@ void hostmsb_half_expr(const uint16_t *a, const uint16_t *b, uint16_t *dst, int6
   D = A * B + A * H(0.5f) - B / (A * A + H(2.0f));
 }
 
+/* reciprocal division against `/` and `%`: returns the number of (divisor, number) pairs that disagree */
+int64_t hostmsb_fastdiv_mismatches(const uint32_t *divisors, int64_t ndiv, const uint32_t *numbers, int64_t nnum) {
+  int64_t bad = 0;
+  for (int64_t i = 0; i < ndiv; ++i) {
+    const FastDiv f(divisors[i]);
+    const uint32_t d = divisors[i];
+    for (int64_t j = 0; j < nnum + 6; ++j) {
+      // the caller's numbers, and for every divisor its own multiples and their neighbours
+      const uint64_t around = static_cast<uint64_t>(d) * ((1u << 31) / d);
+      const uint32_t n = j < nnum ? numbers[j]
+                                  : static_cast<uint32_t>(j - nnum < 3 ? d - 1 + (j - nnum) : around - 2 + (j - nnum - 3));
+      if (n >= (1u << 31)) continue;
+      uint32_t q;
+      const uint32_t r = f.DivMod(n, &q);
+      bad += (q != n / d) || (r != n % d) || (f.Quot(n) != n / d);
+    }
+  }
+  return bad;
+}
+
 /* the cases of msb_axis_case_f32, on host memory (dst == NULL: shape query only); returns 0, 1 when a CHECK of
    the engine fired, 2 when the arguments are outside the case's domain */
 int hostmsb_axis_case(int id, float *dst, const float *A, int64_t n, int64_t c, int64_t h, int64_t w, int64_t p0,

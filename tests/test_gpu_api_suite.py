@@ -198,6 +198,7 @@ def test_patch_columns_with_accumulating_savers(run, data):
     rc, out = run(16, a, b, ROWS * COLS)
     shape = (1, 2, 24, ROWS * COLS // 48)
     img, g = a.reshape(shape), b.reshape(shape)
+    import cpu_checkers as cc
     orc = cc.load("orc")
     m = np.float32(1) + orc.unpack_patch2col(img, 3, 3, 1, 1, 1, 1)
     g = g - orc.pack_col2patch(m, shape, 3, 3, 1, 1, 1, 1)

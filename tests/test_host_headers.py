@@ -227,3 +227,21 @@ def test_remap_plans_against_numpy_on_random_shapes(host):
         assert np.array_equal(got.view(np.uint32), want.view(np.uint32))
 
     check()
+
+
+def test_reciprocal_division_is_exact(host):
+    """expr::FastDiv (multiply-high, add, shift) against / and % for every index below 2^31 that
+    matters: small and large divisors, powers of two and their neighbours, multiples of the divisor
+    and their neighbours, and random numbers."""
+    rng = np.random.default_rng(11)
+    divisors = np.unique(np.concatenate([
+        np.arange(1, 2050), 2 ** np.arange(1, 31), 2 ** np.arange(2, 31) - 1, 2 ** np.arange(1, 31) + 1,
+        np.array([3, 7, 54, 56, 641, 2916, 3136, 65521, 186624, 746496, 2 ** 31 - 1]),
+        rng.integers(1, 2 ** 31, 2000)])).astype(np.uint32)
+    numbers = np.concatenate([np.arange(0, 4100), 2 ** 31 - 1 - np.arange(0, 4100), 2 ** np.arange(0, 31),
+                              2 ** np.arange(1, 31) - 1, rng.integers(0, 2 ** 31, 20000)]).astype(np.uint32)
+    host.hostmsb_fastdiv_mismatches.restype = C.c_int64
+    u32p = C.POINTER(C.c_uint32)
+    bad = host.hostmsb_fastdiv_mismatches(divisors.ctypes.data_as(u32p), i64(divisors.size),
+                                          numbers.ctypes.data_as(u32p), i64(numbers.size))
+    assert bad == 0
