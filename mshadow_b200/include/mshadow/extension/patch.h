@@ -306,7 +306,9 @@ struct MapDispatch<Saver, Tensor<gpu, dstdim, DType>, expr::PackColToPatchXExp<T
   typedef expr::PackColToPatchXExp<Tensor<gpu, 2, DType>, DType, dstdim> E;
   inline static void Run(Tensor<gpu, dstdim, DType> *dst, const E &e, Shape<dstdim> dshape, cudaStream_t stream) {
     const Tensor<gpu, 2, DType> &mat = e.src_;
-    if (e.pdilate_y_ == 1 && e.pdilate_x_ == 1 && PackPatchSupported(dshape[dstdim - 2], dshape[dstdim - 1])) {
+    const bool offsets_fit = static_cast<int64_t>(mat.size(0)) * mat.stride_ < (int64_t(1) << 31);
+    if (e.pdilate_y_ == 1 && e.pdilate_x_ == 1 && offsets_fit &&
+        PackPatchSupported(dshape[dstdim - 2], dshape[dstdim - 1])) {
       PatchGeom g;
       g.channels = dshape[dstdim - 3]; g.h = dshape[dstdim - 2]; g.w = dshape[dstdim - 1];
       g.psy = e.psize_y_; g.psx = e.psize_x_; g.sy = e.pstride_y_; g.sx = e.pstride_x_;

@@ -67,14 +67,53 @@ UnpackPatchPlaneKernel(DType *__restrict__ mat, int64_t ld_mat, const DType *__r
   }
   __syncthreads();
   const uint32_t row_step = g.sy * g.w;
+  constexpr uint32_t kGroup = 16 / sizeof(DType);
+  struct alignas(16) Group {
+    DType v[kGroup];
+  };
+  // runs that start and end on 16-byte boundaries leave in 16-byte groups: one index split and one
+  // store per group (the kernel is bound by instruction issue, not by memory)
+  const bool wide = MSHADOW_B200_UNPACK_WIDE && seg % kGroup == 0 && ld_mat % kGroup == 0 &&
+                    reinterpret_cast<uintptr_t>(mat) % 16 == 0;
   for (uint32_t ky = 0, k = 0; ky < g.psy; ++ky) {
     for (uint32_t kx = 0; kx < g.psx; ++kx, ++k) {
       DType *out = mat + (static_cast<int64_t>(c) * g.psy * g.psx + k) * ld_mat + static_cast<int64_t>(n) * seg;
       const uint32_t off = ky * g.dy * g.w + kx * g.dx;
+      if (wide) {
+#pragma unroll 2
+        for (uint32_t e = threadIdx.x * kGroup; e < seg; e += kPatchThreads * kGroup) {
+          const uint32_t oy = by_ow.Quot(e);
+          uint32_t ox = e - oy * g.ow, at = off + oy * row_step + ox * g.sx;
+          Group grp;
+          if (ox + kGroup <= g.ow) {
+#pragma unroll
+            for (uint32_t l = 0; l < kGroup; ++l) grp.v[l] = plane[at + l * g.sx];
+          } else {  // the group runs over the end of a patch row
+#pragma unroll
+            for (uint32_t l = 0; l < kGroup; ++l) {
+              grp.v[l] = plane[at];
+              at += g.sx;
+              if (++ox == g.ow) {
+                ox = 0;
+                at += row_step - g.ow * g.sx;
+              }
+            }
+          }
+          Group *dst = reinterpret_cast<Group *>(out + e);
+          if (!std::is_same<Saver, sv::saveto>::value) {
+            Group old = *dst;
+#pragma unroll
+            for (uint32_t l = 0; l < kGroup; ++l) Saver::Save(old.v[l], grp.v[l]);
+            grp = old;
+          }
+          *dst = grp;
+        }
+      } else {
 #pragma unroll 4
-      for (uint32_t e = threadIdx.x; e < seg; e += kPatchThreads) {
-        const uint32_t oy = by_ow.Quot(e);
-        Saver::Save(out[e], plane[off + oy * row_step + (e - oy * g.ow) * g.sx]);
+        for (uint32_t e = threadIdx.x; e < seg; e += kPatchThreads) {
+          const uint32_t oy = by_ow.Quot(e);
+          Saver::Save(out[e], plane[off + oy * row_step + (e - oy * g.ow) * g.sx]);
+        }
       }
     }
   }
@@ -96,19 +135,20 @@ PackPatchKernel(DType *__restrict__ img, int64_t ld_img, const DType *__restrict
   const uint32_t p = blockIdx.x;
   const uint32_t n = by_channels.Quot(p), c = p - n * g.channels;
   const uint32_t y = by_w.Quot(i), x = i - y * g.w;
-  // first run of the plane, at the columns of image n
-  const DType *in = mat + static_cast<int64_t>(c) * psy * psx * ld_mat + static_cast<int64_t>(n) * g.oh * g.ow;
+  // the matrix has fewer than 2^31 elements (the launcher checks), so element offsets from its base
+  // fit 32 bits; `first` is the plane's first run at the columns of image n
+  const uint32_t ld = static_cast<uint32_t>(ld_mat);
+  const uint32_t first = c * psy * psx * ld + n * g.oh * g.ow;
   DType res = static_cast<DType>(0);
   if constexpr (kUnit) {
-    const DType *at = in + (y * g.ow + x);  // tap (ky, kx) lies k * ld_mat - ky * ow - kx further on
+    const uint32_t at = first + y * g.ow + x;  // tap (ky, kx) lies k * ld - ky * ow - kx, a launch constant, further on
 #pragma unroll
     for (uint32_t ky = psy; ky-- > 0;) {
       const bool row_ok = y - ky < g.oh;  // unsigned: also false for y < ky
 #pragma unroll
       for (uint32_t kx = psx; kx-- > 0;) {
         if (row_ok && x - kx < g.ow) {
-          res = detail::AddRN<DType>(
-              res, gpu_rt::LoadCg(at + (static_cast<int64_t>(ky * psx + kx) * ld_mat - static_cast<int64_t>(ky * g.ow + kx))));
+          res = detail::AddRN<DType>(res, gpu_rt::LoadCg(mat + (at + ((ky * psx + kx) * ld - (ky * g.ow + kx)))));
         }
       }
     }
@@ -121,7 +161,7 @@ PackPatchKernel(DType *__restrict__ img, int64_t ld_img, const DType *__restrict
       for (uint32_t kx = psx; kx-- > 0;) {
         uint32_t px;
         if (row_ok && x >= kx && by_sx.DivMod(x - kx, &px) == 0 && px < g.ow) {
-          res = detail::AddRN<DType>(res, gpu_rt::LoadCg(in + static_cast<int64_t>(ky * psx + kx) * ld_mat + py * g.ow + px));
+          res = detail::AddRN<DType>(res, gpu_rt::LoadCg(mat + (first + (ky * psx + kx) * ld + py * g.ow + px)));
         }
       }
     }

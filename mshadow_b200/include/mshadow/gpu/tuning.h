@@ -48,6 +48,9 @@
 #ifndef MSHADOW_B200_UNPOOL_SMEM_KB
 #define MSHADOW_B200_UNPOOL_SMEM_KB 74  // staged planes per CTA, backward pooling
 #endif
+#ifndef MSHADOW_B200_UNPACK_WIDE
+#define MSHADOW_B200_UNPACK_WIDE 1  // unpack_patch2col: 16-byte stores where the runs are aligned
+#endif
 #ifndef MSHADOW_B200_SMGRAD_UNROLL
 #define MSHADOW_B200_SMGRAD_UNROLL 1  // as for the map kernel: 1 -> 102 %, 2 -> 95-97 %, 4 -> 94 % of copy bandwidth
 #endif
