@@ -453,6 +453,14 @@ def kernel_cases(lib, torch, small=False):
     del RW
     RD = None
     del RA, RB, RD
+    # complex product of two interleaved (re, im) matrices
+    cr, ccn = (4096, 8192) if small else (8192, 8192)
+    CA = torch.rand(cr, ccn, device=dev, generator=g)
+    CB = torch.rand(cr, ccn, device=dev, generator=g)
+    CD = torch.empty_like(CA)
+    yield ("complex_0", "complex_mul_cc %dx%d floats" % (cr, ccn), 12 * CA.numel(), CA.numel(),
+           lambda: lib.complex_case(0, CD, CA, CB), 10)
+    del CA, CB, CD
     # embedding look-up (the forward of AddTakeGrad): rows of a table gathered by an index vector
     tr, tc = (65536, 1024) if small else (262144, 1024)
     TA = torch.randn(tr, tc, device=dev, generator=g)

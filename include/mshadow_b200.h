@@ -289,6 +289,20 @@ int msb_axis_shape(int id, int64_t n, int64_t c, int64_t h, int64_t w, int64_t p
 int msb_axis_case_f32(int id, float *dst, const float *A, int64_t n, int64_t c, int64_t h, int64_t w,
                       int64_t p0, int64_t p1, msb_stream_t stream);
 
+/*
+ * Complex arithmetic (mshadow/extension/complex.h) evaluated by MapExp.  A and B are dense fp32
+ * matrices of rows x cols floats read as rows x cols/2 complex numbers (re, im interleaved); Ah and
+ * Bh are the first rows*cols/2 floats of the same buffers read as real rows x cols/2 matrices.
+ * cols must be a multiple of 4.  dst is dense, rows x cols unless noted:
+ *    0  complex_mul_cc(A, B)      1  complex_mul_cr(A, Bh)     2  complex_mul_rc(Ah, B)
+ *    3  complex_div_cc(A, B)      4  complex_div_cr(A, Bh)     5  complex_div_rc(Ah, B)
+ *    6  conj(A)                   7  complex_exchange(A)       8  complex_pad_imag(Ah)
+ *    9  complex_toreal(A)        10  complex_abs_square(A)    11  complex_sum_real_imag(A)   (rows x cols/2)
+ *   12  complex_mul_cc(conj(A), B) + complex_pad_imag(complex_abs_square(B)) * 0.5f
+ */
+int msb_complex_case_f32(int id, float *dst, const float *A, const float *B, int64_t rows,
+                         int64_t cols, msb_stream_t stream);
+
 /* Softmax(Tensor<gpu,3>): softmax over the middle axis of (batch, classes, positions);
    ld_* = pitch of the last axis: mshadow/tensor_gpu-inl.h:163-167 */
 int msb_softmax3d_f32(float *dst, const float *src, int64_t batch, int64_t classes, int64_t npos,

@@ -69,6 +69,7 @@ _SIGNATURES = {
     "msb_vectorized_sort_f32_i32": [vp, vp, i64, vp],
     "msb_index_fill_f32_i32": [vp, vp, vp, i64, i64, i64, vp],
     "msb_remap_shape": [cint, i64, i64, i64, i64, i64, i64, vp],
+    "msb_complex_case_f32": [cint, vp, vp, vp, i64, i64, vp],
     "msb_axis_shape": [cint, i64, i64, i64, i64, i64, i64, vp, vp],
     "msb_axis_case_f32": [cint, vp, vp, i64, i64, i64, i64, i64, i64, vp],
     "msb_remap_case_f32": [cint, vp, vp, vp, i64, i64, i64, i64, i64, i64, vp],
@@ -256,6 +257,11 @@ class Library:
     def remap_case(self, cid, dst, A, B, p0=0, p1=0, stream=None):
         n, c, h, w = A.shape
         self.call("msb_remap_case_f32", cid, _ptr(dst), _ptr(A), _ptr(B), n, c, h, w, p0, p1, stream)
+        return dst
+
+    def complex_case(self, cid, dst, A, B, stream=None):
+        rows, cols = A.shape
+        self.call("msb_complex_case_f32", cid, _ptr(dst), _ptr(A), _ptr(B), rows, cols, stream)
         return dst
 
     def axis_shape(self, cid, shape, p0=0, p1=1):

@@ -15,6 +15,7 @@
 #include "mshadow/tensor.h"
 #include "mshadow/gpu/math.h"
 #include "./axis_cases.h"
+#include "./complex_cases.h"
 
 using namespace mshadow;        // NOLINT(*)
 using namespace mshadow::expr;  // NOLINT(*)
@@ -681,6 +682,17 @@ int msb_axis_case_f32(int id, float *dst, const float *A, int64_t n, int64_t c, 
   MSB_GUARD_BEGIN
   BorrowedStream st(stream);
   msb_axis::Run<gpu>(id, dst, A, n, c, h, w, p0, p1, st.get());
+  MSB_GUARD_END
+}
+
+int msb_complex_case_f32(int id, float *dst, const float *A, const float *B, int64_t rows, int64_t cols,
+                         msb_stream_t stream) {
+  MSB_REQUIRE(id >= 0 && id < msb_complex::kNumCases, MSB_ERR_ARGUMENT, "unknown expression id");
+  MSB_REQUIRE(msb_complex::ArgsOk(id, rows, cols), MSB_ERR_SHAPE, "extent out of range (cols must be a multiple of 4)");
+  MSB_REQUIRE(dst && A && B, MSB_ERR_ARGUMENT, "null pointer");
+  MSB_GUARD_BEGIN
+  BorrowedStream st(stream);
+  msb_complex::Run<gpu>(id, dst, A, B, rows, cols, st.get());
   MSB_GUARD_END
 }
 

@@ -12,4 +12,5 @@
 #include "./extension/select.h"
 #include "./extension/patch.h"
 #include "./extension/axis.h"
+#include "./extension/complex.h"
 #endif  // MSHADOW_EXTENSION_H_

@@ -789,6 +789,50 @@ void ORC(axis_case)(int id, float *dst, const float *A, int64_t n, int64_t c, in
   }
 }
 
+/* ---- complex arithmetic: extension/complex.h:17-112 (operators), :370-489 (which operand elements feed
+        column x: the pair (x & ~1, x | 1) of a complex operand, element x / 2 of a real one) ---- */
+
+static float cmul_part(int imag, float ar, float ai, float br, float bi) {
+  return imag ? ar * bi + br * ai : ar * br - ai * bi;
+}
+static float cdiv_part(int imag, float ar, float ai, float br, float bi) {
+  return imag ? (br * ai - ar * bi) / (br * br + bi * bi) : (ar * br + ai * bi) / (br * br + bi * bi);
+}
+
+void ORC(complex_case)(int id, float *dst, const float *A, const float *B, int64_t rows, int64_t cols) {
+  const int64_t half = cols / 2, ocols = (id >= 9 && id <= 11) ? half : cols;
+#pragma omp parallel for
+  for (int64_t y = 0; y < rows; ++y) {
+    const float *a = A + y * cols, *b = B + y * cols;  /* complex rows */
+    const float *ah = A + y * half, *bh = B + y * half; /* real rows */
+    for (int64_t x = 0; x < ocols; ++x) {
+      const int64_t re = x & ~(int64_t)1, im = re + 1, h = x / 2;
+      const int imag = (int)(x & 1);
+      float v;
+      switch (id) {
+        case 0: v = cmul_part(imag, a[re], a[im], b[re], b[im]); break;
+        case 1: v = cmul_part(imag, a[re], a[im], bh[h], 0.0f); break;
+        case 2: v = cmul_part(imag, ah[h], 0.0f, b[re], b[im]); break;
+        case 3: v = cdiv_part(imag, a[re], a[im], b[re], b[im]); break;
+        case 4: v = cdiv_part(imag, a[re], a[im], bh[h], 0.0f); break;
+        case 5: v = cdiv_part(imag, ah[h], 0.0f, b[re], b[im]); break;
+        case 6: v = imag ? -a[im] : a[re]; break;
+        case 7: v = imag ? a[re] : a[im]; break;
+        case 8: v = imag ? 0.0f : ah[h]; break;
+        case 9: v = a[2 * x]; break;
+        case 10: v = a[2 * x] * a[2 * x] + a[2 * x + 1] * a[2 * x + 1]; break;
+        case 11: v = a[2 * x] + a[2 * x + 1]; break;
+        default: {
+          const float prod = cmul_part(imag, a[re], -a[im], b[re], b[im]);
+          const float pad = imag ? 0.0f : b[2 * h] * b[2 * h] + b[2 * h + 1] * b[2 * h + 1];
+          v = prod + pad * 0.5f;
+        } break;
+      }
+      dst[y * ocols + x] = v;
+    }
+  }
+}
+
 int ORC(num_threads)(void) {
 #ifdef _OPENMP
   return omp_get_max_threads();

@@ -212,6 +212,20 @@ int ORC(axis_shape)(int id, int64_t n, int64_t c, int64_t h, int64_t w, int64_t 
 void ORC(axis_case)(int id, float *dst, const float *A, int64_t n, int64_t c, int64_t h, int64_t w,
                     int64_t p0, int64_t p1);
 
+/*
+ * Complex arithmetic (extension/complex.h) evaluated through MapExp.  A and B are dense fp32
+ * matrices of rows x cols floats, read as rows x cols/2 complex numbers (re, im interleaved);
+ * Ah and Bh are the first rows*cols/2 floats of the same buffers read as real rows x cols/2
+ * matrices.  cols must be a multiple of 4.  Result rows x cols unless noted:
+ *    0  complex_mul_cc(A, B)      1  complex_mul_cr(A, Bh)     2  complex_mul_rc(Ah, B)
+ *    3  complex_div_cc(A, B)      4  complex_div_cr(A, Bh)     5  complex_div_rc(Ah, B)
+ *    6  conj(A)                   7  complex_exchange(A)       8  complex_pad_imag(Ah)
+ *    9  complex_toreal(A)        10  complex_abs_square(A)    11  complex_sum_real_imag(A)   (rows x cols/2)
+ *   12  complex_mul_cc(conj(A), B) + complex_pad_imag(complex_abs_square(B)) * 0.5f
+ */
+#define ORC_NUM_COMPLEX_CASES 13
+void ORC(complex_case)(int id, float *dst, const float *A, const float *B, int64_t rows, int64_t cols);
+
 /* number of OpenMP threads the library will use (for cpu_baseline.cores) */
 int ORC(num_threads)(void);
 

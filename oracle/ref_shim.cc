@@ -422,6 +422,27 @@ void ref_axis_case(int id, float *dst, const float *A, int64_t n, int64_t c, int
   }
 }
 
+void ref_complex_case(int id, float *dst, const float *A, const float *B, int64_t rows, int64_t cols) {
+  T2 a = mat(A, rows, cols, cols), b = mat(B, rows, cols, cols);
+  T2 ah = mat(A, rows, cols / 2, cols / 2), bh = mat(B, rows, cols / 2, cols / 2);
+  T2 d = mat(dst, rows, cols, cols), dh = mat(dst, rows, cols / 2, cols / 2);
+  switch (id) {
+    case 0: d = complex_mul_cc(a, b); break;
+    case 1: d = complex_mul_cr(a, bh); break;
+    case 2: d = complex_mul_rc(ah, b); break;
+    case 3: d = complex_div_cc(a, b); break;
+    case 4: d = complex_div_cr(a, bh); break;
+    case 5: d = complex_div_rc(ah, b); break;
+    case 6: d = conj(a); break;
+    case 7: d = complex_exchange(a); break;
+    case 8: d = complex_pad_imag(ah); break;
+    case 9: dh = complex_toreal(a); break;
+    case 10: dh = complex_abs_square(a); break;
+    case 11: dh = complex_sum_real_imag(a); break;
+    default: d = complex_mul_cc(conj(a), b) + complex_pad_imag(complex_abs_square(b)) * 0.5f; break;
+  }
+}
+
 int ref_num_threads(void) {
 #ifdef _OPENMP
   return omp_get_max_threads();

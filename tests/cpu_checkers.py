@@ -193,6 +193,14 @@ class Checker:
         self._fn("axis_case")(C.c_int(cid), _fp(dst), _fp(A), i64(n), i64(c), i64(h), i64(w), i64(p0), i64(p1))
         return dst
 
+    def complex_case(self, cid, A, B):
+        """Evaluates complex-arithmetic case `cid` on dense (rows, cols) inputs (re, im interleaved)."""
+        assert A.flags.c_contiguous and B.flags.c_contiguous and A.shape == B.shape and A.shape[1] % 4 == 0
+        rows, cols = A.shape
+        dst = np.full((rows, cols // 2 if 9 <= cid <= 11 else cols), np.float32(9.0), dtype=np.float32)
+        self._fn("complex_case")(C.c_int(cid), _fp(dst), _fp(A), _fp(B), i64(rows), i64(cols))
+        return dst
+
     def select_case(self, cid, A, B, idx_r, idx_c, p0=1):
         """Evaluates index-selecting case `cid` on dense (rows, cols) inputs; returns the result."""
         rows, cols = A.shape
@@ -276,6 +284,7 @@ def remap_params(cid, shape):
 
 
 NUM_AXIS_CASES = 11
+NUM_COMPLEX_CASES = 13
 
 
 def axis_params(cid, shape):

@@ -10,6 +10,7 @@
 
 #include "mshadow/tensor.h"
 #include "../../mshadow_b200/csrc/axis_cases.h"
+#include "../../mshadow_b200/csrc/complex_cases.h"
 
 using namespace mshadow;        // NOLINT(*)
 using namespace mshadow::expr;  // NOLINT(*)
@@ -115,6 +116,32 @@ void hostmsb_half_expr(const uint16_t *a, const uint16_t *b, uint16_t *dst, int6
   Tensor<cpu, 2, H> B(reinterpret_cast<H *>(const_cast<uint16_t *>(b)), Shape2(rows, cols));
   Tensor<cpu, 2, H> D(reinterpret_cast<H *>(dst), Shape2(rows, cols));
   D = A * B + A * H(0.5f) - B / (A * A + H(2.0f));
+}
+
+/* the cases of msb_complex_case_f32, on host memory; returns 0, 1 when a CHECK of the engine fired, 2 when the
+   arguments are outside the domain */
+int hostmsb_complex_case(int id, float *dst, const float *A, const float *B, int64_t rows, int64_t cols) {
+  if (!msb_complex::ArgsOk(id, rows, cols)) return 2;
+  try {
+    msb_complex::Run<cpu>(id, dst, A, B, rows, cols, static_cast<Stream<cpu> *>(nullptr));
+  } catch (const std::exception &e) {
+    g_error = e.what();
+    return 1;
+  }
+  return 0;
+}
+
+/* a complex product of operands whose widths do not match: the shape rule must fire */
+int hostmsb_complex_shape_error(void) {
+  float buf[24] = {0};
+  Tensor<cpu, 2, float> a(buf, Shape2(2, 6)), b(buf, Shape2(2, 4)), d(buf + 12, Shape2(2, 6));
+  try {
+    d = complex_mul_cr(a, b);  // a real operand must be half as wide as the complex one
+  } catch (const std::exception &e) {
+    g_error = e.what();
+    return 1;
+  }
+  return 0;
 }
 
 /* reciprocal division against `/` and `%`: returns the number of (divisor, number) pairs that disagree */

@@ -461,6 +461,19 @@ def test_axis_expressions(lib, cid, shape):
         assert_bits(host(got), want)
 
 
+@pytest.mark.parametrize("cid", range(cc.NUM_COMPLEX_CASES))
+@pytest.mark.parametrize("rows,cols", [(3, 4), (5, 16), (7, 36), (64, 1024), (33, 260)])
+def test_complex_expressions(lib, cid, rows, cols):
+    """complex_mul / complex_div in their cc, cr, rc forms, conj, exchange, pad_imag, toreal, abs_square,
+    sum_real_imag: every product, sum and quotient rounded on its own, so bit-exact."""
+    rng = np.random.default_rng(cid * 1000 + rows + cols)
+    A = rng.uniform(-1, 1, (rows, cols)).astype(np.float32)
+    B = rng.uniform(-1, 1, (rows, cols)).astype(np.float32)
+    want = orc.complex_case(cid, A, B)
+    got = lib.complex_case(cid, torch.full(want.shape, 9.0, device="cuda"), dev(A), dev(B))
+    assert_bits(host(got), want)
+
+
 def test_axis_argument_errors(lib):
     import ctypes as C
     z = torch.zeros(2, 3, 4, 5, device="cuda")

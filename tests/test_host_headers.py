@@ -143,6 +143,28 @@ def test_axis_plans_on_the_host(host, cid, shape):
         assert np.array_equal(got.view(np.uint32), want.view(np.uint32)), (cid, p0, p1)
 
 
+@pytest.mark.parametrize("cid", range(cc.NUM_COMPLEX_CASES))
+@pytest.mark.parametrize("rows,cols", [(3, 4), (5, 16), (1, 8), (7, 36)])
+def test_complex_plans_on_the_host(host, cid, rows, cols):
+    rng = np.random.default_rng(cid * 100 + rows + cols)
+    A = rng.uniform(-1, 1, (rows, cols)).astype(np.float32)
+    B = rng.uniform(-1, 1, (rows, cols)).astype(np.float32)
+    want = orc.complex_case(cid, A, B)
+    got = np.full(want.shape, np.float32(9.0), np.float32)
+    st = host.hostmsb_complex_case(cid, got.ctypes.data_as(f32p), A.ctypes.data_as(f32p), B.ctypes.data_as(f32p),
+                                   i64(rows), i64(cols))
+    assert st == 0, host.hostmsb_last_error()
+    assert np.array_equal(got.view(np.uint32), want.view(np.uint32)), cid
+
+
+def test_complex_shape_rules(host):
+    z = np.zeros((2, 6), np.float32)
+    p = z.ctypes.data_as(f32p)
+    assert host.hostmsb_complex_case(0, p, p, p, i64(2), i64(6)) == 2  # cols not a multiple of 4
+    assert host.hostmsb_complex_shape_error() == 1
+    assert b"CR" in host.hostmsb_last_error()
+
+
 def test_axis_arguments_outside_the_domain_are_refused(host):
     A = np.zeros((2, 3, 4, 5), np.float32)
     assert run_axis(host, 4, A, 4, 0)[0] == 2   # no such axis

@@ -234,6 +234,36 @@ def test_axis_cases_match_reference(cid, shape):
         assert same_bits(*res), (cid, p0, p1)
 
 
+@needs_ref
+@pytest.mark.parametrize("cid", range(cc.NUM_COMPLEX_CASES))
+@pytest.mark.parametrize("rows,cols", [(3, 4), (5, 16), (1, 8), (7, 36)])
+def test_complex_cases_match_reference(cid, rows, cols):
+    rng = np.random.default_rng(cid * 100 + rows + cols)
+    A, B = rnd(rng, (rows, cols)), rnd(rng, (rows, cols))
+    res = [lib.complex_case(cid, A, B) for lib in (orc, ref)]
+    assert same_bits(*res), cid
+
+
+def test_complex_known_answers():
+    rng = np.random.default_rng(9)
+    A, B = rnd(rng, (4, 12)), rnd(rng, (4, 12))
+    za = A[:, 0::2].astype(np.complex128) + 1j * A[:, 1::2]
+    zb = B[:, 0::2].astype(np.complex128) + 1j * B[:, 1::2]
+
+    def inter(z):
+        out = np.empty((z.shape[0], z.shape[1] * 2))
+        out[:, 0::2], out[:, 1::2] = z.real, z.imag
+        return out
+
+    ah, bh = A.ravel()[:24].reshape(4, 6).astype(np.float64), B.ravel()[:24].reshape(4, 6).astype(np.float64)
+    want = {0: inter(za * zb), 1: inter(za * bh), 2: inter(ah * zb), 3: inter(za / zb), 4: inter(za / bh),
+            5: inter(ah / zb), 6: inter(za.conj()), 7: inter(za.imag + 1j * za.real), 8: inter(ah + 0j),
+            9: za.real, 10: np.abs(za) ** 2, 11: za.real + za.imag,
+            12: inter(za.conj() * zb + 0.5 * np.abs(zb) ** 2)}
+    for cid, w in want.items():
+        np.testing.assert_allclose(orc.complex_case(cid, A, B), w, rtol=2e-5, atol=1e-6, err_msg=str(cid))
+
+
 def test_axis_known_answers():
     rng = np.random.default_rng(5)
     A = rnd(rng, (2, 3, 4, 5))
