@@ -73,8 +73,9 @@ UnpackPatchPlaneKernel(DType *__restrict__ mat, int64_t ld_mat, const DType *__r
   };
   // runs that start and end on 16-byte boundaries leave in 16-byte groups: one index split and one
   // store per group (the kernel is bound by instruction issue, not by memory)
-  const bool wide = MSHADOW_B200_UNPACK_WIDE && seg % kGroup == 0 && ld_mat % kGroup == 0 &&
+  const bool wide = MSHADOW_B200_UNPACK_WIDE && seg % kGroup == 0 && ld_mat % kGroup == 0 && g.ow >= kGroup &&
                     reinterpret_cast<uintptr_t>(mat) % 16 == 0;
+  const uint32_t next_row = row_step - g.ow * g.sx;  // added to a plane index that passed the end of a patch row
   for (uint32_t ky = 0, k = 0; ky < g.psy; ++ky) {
     for (uint32_t kx = 0; kx < g.psx; ++kx, ++k) {
       DType *out = mat + (static_cast<int64_t>(c) * g.psy * g.psx + k) * ld_mat + static_cast<int64_t>(n) * seg;
@@ -83,21 +84,13 @@ UnpackPatchPlaneKernel(DType *__restrict__ mat, int64_t ld_mat, const DType *__r
 #pragma unroll 2
         for (uint32_t e = threadIdx.x * kGroup; e < seg; e += kPatchThreads * kGroup) {
           const uint32_t oy = by_ow.Quot(e);
-          uint32_t ox = e - oy * g.ow, at = off + oy * row_step + ox * g.sx;
+          const uint32_t ox = e - oy * g.ow, at = off + oy * row_step + ox * g.sx;
           Group grp;
-          if (ox + kGroup <= g.ow) {
+          // a group may run over the end of its patch row (at most once: ow >= kGroup); no branch, since
+          // nearly every warp holds such a group and would execute both sides
 #pragma unroll
-            for (uint32_t l = 0; l < kGroup; ++l) grp.v[l] = plane[at + l * g.sx];
-          } else {  // the group runs over the end of a patch row
-#pragma unroll
-            for (uint32_t l = 0; l < kGroup; ++l) {
-              grp.v[l] = plane[at];
-              at += g.sx;
-              if (++ox == g.ow) {
-                ox = 0;
-                at += row_step - g.ow * g.sx;
-              }
-            }
+          for (uint32_t l = 0; l < kGroup; ++l) {
+            grp.v[l] = plane[at + l * g.sx + (ox + l >= g.ow ? next_row : 0u)];
           }
           Group *dst = reinterpret_cast<Group *>(out + e);
           if (!std::is_same<Saver, sv::saveto>::value) {
@@ -142,13 +135,31 @@ PackPatchKernel(DType *__restrict__ img, int64_t ld_img, const DType *__restrict
   DType res = static_cast<DType>(0);
   if constexpr (kUnit) {
     const uint32_t at = first + y * g.ow + x;  // tap (ky, kx) lies k * ld - ky * ow - kx, a launch constant, further on
+    if constexpr (PSY > 0 && PSX > 0) {
+      // all loads of the element first (predicated, independent), then the adds in the reference's order
+      DType v[PSY * PSX];
+      bool ok[PSY * PSX];
 #pragma unroll
-    for (uint32_t ky = psy; ky-- > 0;) {
-      const bool row_ok = y - ky < g.oh;  // unsigned: also false for y < ky
+      for (uint32_t ky = 0; ky < PSY; ++ky) {
+        const bool row_ok = y - ky < g.oh;  // unsigned: also false for y < ky
 #pragma unroll
-      for (uint32_t kx = psx; kx-- > 0;) {
-        if (row_ok && x - kx < g.ow) {
-          res = detail::AddRN<DType>(res, gpu_rt::LoadCg(mat + (at + ((ky * psx + kx) * ld - (ky * g.ow + kx)))));
+        for (uint32_t kx = 0; kx < PSX; ++kx) {
+          const uint32_t k = ky * PSX + kx;
+          ok[k] = row_ok && x - kx < g.ow;
+          v[k] = ok[k] ? gpu_rt::LoadCg(mat + (at + (k * ld - (ky * g.ow + kx)))) : static_cast<DType>(0);
+        }
+      }
+#pragma unroll
+      for (int k = PSY * PSX - 1; k >= 0; --k) {
+        if (ok[k]) res = detail::AddRN<DType>(res, v[k]);
+      }
+    } else {
+      for (uint32_t ky = psy; ky-- > 0;) {
+        const bool row_ok = y - ky < g.oh;
+        for (uint32_t kx = psx; kx-- > 0;) {
+          if (row_ok && x - kx < g.ow) {
+            res = detail::AddRN<DType>(res, gpu_rt::LoadCg(mat + (at + ((ky * psx + kx) * ld - (ky * g.ow + kx)))));
+          }
         }
       }
     }
