@@ -370,11 +370,30 @@ class Plan<BroadcastWithAxisExp<SrcExp, DType, dimsrc, dimdst>, DType> {
     const uint32_t col = by_last_.DivMod(by_size_.Quot(t) * by_trailing_.div + inner, &row);
     return src_.Eval(row, col);
   }
+#ifdef __CUDACC__
+  /*! \brief a group stays inside one (outer, repeat) block when every extent involved is a multiple of the group */
+  __device__ __forceinline__ Pack<DType> EvalPack(index_t i, index_t j) const {
+    uint32_t t, row;
+    const uint32_t inner = by_trailing_.DivMod(i * dst_last_ + j, &t);
+    const uint32_t col = by_last_.DivMod(by_size_.Quot(t) * by_trailing_.div + inner, &row);
+    return src_.EvalPack(row, col);
+  }
+#endif
 
  private:
   Plan<SrcExp, DType> src_;
   const index_t dst_last_;
   const FastDiv by_trailing_, by_size_, by_last_;
+};
+
+template <typename SrcExp, typename DType, int dimsrc, int dimdst>
+struct PackInfo<BroadcastWithAxisExp<SrcExp, DType, dimsrc, dimdst> > : public PackInfo<SrcExp> {};
+template <typename SrcExp, typename DType, int dimsrc, int dimdst>
+struct PackAlign<BroadcastWithAxisExp<SrcExp, DType, dimsrc, dimdst> > {
+  inline static bool Check(const BroadcastWithAxisExp<SrcExp, DType, dimsrc, dimdst> &e) {
+    const index_t lanes = Pack<DType>::kLanes;
+    return e.trailing_ % lanes == 0 && e.last_ % lanes == 0 && e.dst_last_ % lanes == 0 && PackAlign<SrcExp>::Check(e.src_);
+  }
 };
 
 // ------------------------------------------------------------------------------------------
