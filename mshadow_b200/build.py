@@ -56,7 +56,7 @@ def _stale(out, deps):
 
 
 def build_all(force=False, verbose=True):
-    deps_common = [os.path.join(HERE, "include"), os.path.join(ROOT, "include")]
+    deps_common = [os.path.join(HERE, "include"), os.path.join(ROOT, "include"), os.path.join(HERE, "csrc")]
     for out, srcs, extra in TARGETS:
         if not all(os.path.exists(s) for s in srcs):
             continue

@@ -240,10 +240,46 @@ class Plan<ComplexBinaryMapExp<calctype, OP, TA, TB, DType, etype>, DType> {
     const DType bi = calctype == op::complex::kBinaryCR ? zero : rhs_.Eval(y, im);
     return (x & 1) == 0 ? OP::RealMap(ar, ai, br, bi) : OP::ImagMap(ar, ai, br, bi);
   }
+#ifdef __CUDACC__
+  /*! \brief complex x complex only: a 16-byte group holds whole (re, im) pairs of both operands */
+  __device__ __forceinline__ Pack<DType> EvalPack(index_t y, index_t x) const {
+    const Pack<DType> a = lhs_.EvalPack(y, x), b = rhs_.EvalPack(y, x);
+    Pack<DType> r;
+#pragma unroll
+    for (int p = 0; p < Pack<DType>::kLanes; p += 2) {
+      r.v[p] = OP::RealMap(a.v[p], a.v[p + 1], b.v[p], b.v[p + 1]);
+      r.v[p + 1] = OP::ImagMap(a.v[p], a.v[p + 1], b.v[p], b.v[p + 1]);
+    }
+    return r;
+  }
+#endif
 
  private:
   Plan<TA, DType> lhs_;
   Plan<TB, DType> rhs_;
+};
+
+// complex x complex reads both operands at the result's own positions: 16-byte groups, and one
+// long row where the operands are dense (widths are even, so parity survives the flattening)
+template <typename OP, typename TA, typename TB, typename DType, int etype>
+struct PackInfo<ComplexBinaryMapExp<op::complex::kBinaryCC, OP, TA, TB, DType, etype> > {
+  static const bool kPass = PackInfo<TA>::kPass && PackInfo<TB>::kPass;
+};
+template <typename OP, typename TA, typename TB, typename DType, int etype>
+struct PackAlign<ComplexBinaryMapExp<op::complex::kBinaryCC, OP, TA, TB, DType, etype> > {
+  inline static bool Check(const ComplexBinaryMapExp<op::complex::kBinaryCC, OP, TA, TB, DType, etype> &e) {
+    return PackAlign<TA>::Check(e.lhs_) && PackAlign<TB>::Check(e.rhs_);
+  }
+};
+template <typename OP, typename TA, typename TB, typename DType, int etype>
+struct FlatInfo<ComplexBinaryMapExp<op::complex::kBinaryCC, OP, TA, TB, DType, etype> > {
+  static const bool kPass = FlatInfo<TA>::kPass && FlatInfo<TB>::kPass;
+};
+template <typename OP, typename TA, typename TB, typename DType, int etype>
+struct FlatCheck<ComplexBinaryMapExp<op::complex::kBinaryCC, OP, TA, TB, DType, etype> > {
+  inline static bool Check(const ComplexBinaryMapExp<op::complex::kBinaryCC, OP, TA, TB, DType, etype> &e) {
+    return FlatCheck<TA>::Check(e.lhs_) && FlatCheck<TB>::Check(e.rhs_);
+  }
 };
 
 template <int calctype, typename OP, typename TA, int etype, typename DType>
