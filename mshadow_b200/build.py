@@ -23,6 +23,9 @@ TARGETS = [
      [os.path.join(HERE, "csrc", "capi.cu"), os.path.join(HERE, "csrc", "noalloc.cu")], []),
     (os.path.join(ROOT, "tests", "cxx", "libmsb_api_suite.so"),
      [os.path.join(ROOT, "tests", "cxx", "api_suite.cu")], []),
+    # the checked build of the engine (tensor leaves refuse and record accesses outside their storage)
+    (os.path.join(ROOT, "tests", "cxx", "libmsb_bounds_suite.so"),
+     [os.path.join(ROOT, "tests", "cxx", "bounds_suite.cu")], ["-DMSHADOW_B200_CHECK_BOUNDS=1"]),
     # the multi-GPU synchronisation model; the only part that needs NCCL
     (os.path.join(HERE, "libmshadow_b200_ps.so"), [os.path.join(HERE, "csrc", "ps_capi.cu")], ["-lnccl"]),
 ]

@@ -51,6 +51,46 @@ __device__ __forceinline__ void StoreStream(DType *p, const Pack<DType> &v) {
   __stcs(reinterpret_cast<int4 *>(p), *reinterpret_cast<const int4 *>(&v));
 }
 #endif
+
+/*
+ * Checked build (-DMSHADOW_B200_CHECK_BOUNDS=1), the stand-in for a memory checker while
+ * developing an expression plan: every access that a tensor leaf serves on the GPU is compared
+ * with the extent of the tensor's storage.  An access outside it is not performed: a load yields
+ * zero, a store is dropped, the first offending offset is recorded, and the kernel carries on,
+ * so the context stays usable and nothing faults.  gpu_rt::TakeBoundsViolation() reads and clears
+ * the record.  The record lives once per translation unit.  Off by default: the checks cost a
+ * compare per access and 8 bytes per leaf in the kernel arguments.
+ */
+#ifndef MSHADOW_B200_CHECK_BOUNDS
+#define MSHADOW_B200_CHECK_BOUNDS 0
+#endif
+#if MSHADOW_B200_CHECK_BOUNDS && defined(__CUDACC__)
+struct BoundsRecord {
+  int hit;                 // 0: clean
+  int width;               // elements of the refused access
+  long long offset, limit;  // element offset from the tensor's base, and the storage extent
+};
+static __device__ BoundsRecord g_bounds_record;
+static __device__ long long g_bounds_sink[2];  // where refused l-value references point
+static __device__ long long g_bounds_zero[2];  // what refused loads read (never written: all-zero bits)
+__device__ __forceinline__ bool BoundsOk(long long offset, int width, long long limit) {
+  if (offset >= 0 && offset + width <= limit) return true;
+  if (atomicCAS(&g_bounds_record.hit, 0, 1) == 0) {
+    g_bounds_record.width = width;
+    g_bounds_record.offset = offset;
+    g_bounds_record.limit = limit;
+  }
+  return false;
+}
+template <typename DType>
+__device__ __forceinline__ DType &BoundsSink() {
+  return *reinterpret_cast<DType *>(g_bounds_sink);
+}
+template <typename DType>
+__device__ __forceinline__ const DType &BoundsZero() {
+  return *reinterpret_cast<const DType *>(g_bounds_zero);
+}
+#endif
 }  // namespace plandetail
 
 /*!
@@ -87,17 +127,37 @@ class Plan<MakeTensorExp<SubType, SrcExp, dim, DType>, DType> {
 };
 
 // ---- tensor leaf ----
+#if MSHADOW_B200_CHECK_BOUNDS && defined(__CUDA_ARCH__)
+#define MSHADOW_B200_BOUNDS_(offset, width, refused) \
+  if (!plandetail::BoundsOk(offset, width, limit_)) refused
+#else
+#define MSHADOW_B200_BOUNDS_(offset, width, refused)
+#endif
+
 template <typename Device, int dim, typename DType>
 class Plan<Tensor<Device, dim, DType>, DType> {
  public:
-  explicit Plan(const Tensor<Device, dim, DType> &t) : dptr_(t.dptr_), stride_(t.stride_) {}
-  MSHADOW_XINLINE DType &REval(index_t y, index_t x) { return dptr_[Offset(y, x)]; }
-  MSHADOW_XINLINE const DType &Eval(index_t y, index_t x) const { return dptr_[Offset(y, x)]; }
+  explicit Plan(const Tensor<Device, dim, DType> &t) : dptr_(t.dptr_), stride_(t.stride_) {
+#if MSHADOW_B200_CHECK_BOUNDS && defined(__CUDACC__)
+    const Shape<2> flat = t.shape_.FlatTo2D();  // storage runs to the end of the last row
+    limit_ = flat[0] == 0 ? 0 : static_cast<long long>(flat[0] - 1) * t.stride_ + flat[1];
+#endif
+  }
+  MSHADOW_XINLINE DType &REval(index_t y, index_t x) {
+    MSHADOW_B200_BOUNDS_(Offset(y, x), 1, return plandetail::BoundsSink<DType>());
+    return dptr_[Offset(y, x)];
+  }
+  MSHADOW_XINLINE const DType &Eval(index_t y, index_t x) const {
+    MSHADOW_B200_BOUNDS_(Offset(y, x), 1, return plandetail::BoundsZero<DType>());
+    return dptr_[Offset(y, x)];
+  }
 #ifdef __CUDACC__
   __device__ __forceinline__ Pack<DType> EvalPack(index_t y, index_t x) const {
+    MSHADOW_B200_BOUNDS_(Offset(y, x), Pack<DType>::kLanes, return Pack<DType>());
     return plandetail::LoadStream(dptr_ + Offset(y, x));
   }
   __device__ __forceinline__ void StorePack(index_t y, index_t x, const Pack<DType> &v) {
+    MSHADOW_B200_BOUNDS_(Offset(y, x), Pack<DType>::kLanes, return);
     plandetail::StoreStream(dptr_ + Offset(y, x), v);
   }
 #endif
@@ -110,24 +170,40 @@ class Plan<Tensor<Device, dim, DType>, DType> {
   }
   DType *dptr_;
   index_t stride_;
+#if MSHADOW_B200_CHECK_BOUNDS && defined(__CUDACC__)
+  long long limit_;
+#endif
 };
 
 // ---- 1-d tensor leaf: a single row ----
 template <typename Device, typename DType>
 class Plan<Tensor<Device, 1, DType>, DType> {
  public:
-  explicit Plan(const Tensor<Device, 1, DType> &t) : dptr_(t.dptr_) {}
-  MSHADOW_XINLINE DType &REval(index_t, index_t x) { return dptr_[x]; }
-  MSHADOW_XINLINE const DType &Eval(index_t, index_t x) const { return dptr_[x]; }
+  explicit Plan(const Tensor<Device, 1, DType> &t) : dptr_(t.dptr_) {
+#if MSHADOW_B200_CHECK_BOUNDS && defined(__CUDACC__)
+    limit_ = t.shape_[0];
+#endif
+  }
+  MSHADOW_XINLINE DType &REval(index_t, index_t x) {
+    MSHADOW_B200_BOUNDS_(x, 1, return plandetail::BoundsSink<DType>());
+    return dptr_[x];
+  }
+  MSHADOW_XINLINE const DType &Eval(index_t, index_t x) const {
+    MSHADOW_B200_BOUNDS_(x, 1, return plandetail::BoundsZero<DType>());
+    return dptr_[x];
+  }
 #ifdef __CUDACC__
   __device__ __forceinline__ Pack<DType> EvalPack(index_t, index_t x) const {
+    MSHADOW_B200_BOUNDS_(x, Pack<DType>::kLanes, return Pack<DType>());
     return plandetail::LoadStream(dptr_ + x);
   }
   /*! \brief cached variant for operands that every row re-reads (broadcast sources) */
   __device__ __forceinline__ Pack<DType> EvalPackCached(index_t x) const {
+    MSHADOW_B200_BOUNDS_(x, Pack<DType>::kLanes, return Pack<DType>());
     return plandetail::LoadCached(dptr_ + x);
   }
   __device__ __forceinline__ void StorePack(index_t, index_t x, const Pack<DType> &v) {
+    MSHADOW_B200_BOUNDS_(x, Pack<DType>::kLanes, return);
     plandetail::StoreStream(dptr_ + x, v);
   }
 #endif
@@ -135,6 +211,9 @@ class Plan<Tensor<Device, 1, DType>, DType> {
 
  private:
   DType *dptr_;
+#if MSHADOW_B200_CHECK_BOUNDS && defined(__CUDACC__)
+  long long limit_;
+#endif
 };
 
 // ---- scalar ----

@@ -160,6 +160,27 @@ class Scratch {
   }
 };
 
+#if MSHADOW_B200_CHECK_BOUNDS && defined(__CUDACC__)
+/*!
+ * \brief checked build: the first access that a tensor leaf refused on the current device since
+ *  the last call (this translation unit's kernels), after waiting for the device; clears the record.
+ * \return true if there was one; then *offset is the element offset from the tensor's base,
+ *  *width the number of elements of the access and *limit the extent of the tensor's storage
+ */
+inline bool TakeBoundsViolation(long long *offset, int *width, long long *limit) {
+  expr::plandetail::BoundsRecord rec;
+  MSHADOW_CUDA_CALL(cudaDeviceSynchronize());
+  MSHADOW_CUDA_CALL(cudaMemcpyFromSymbol(&rec, expr::plandetail::g_bounds_record, sizeof(rec)));
+  if (rec.hit == 0) return false;
+  const expr::plandetail::BoundsRecord clean = {0, 0, 0, 0};
+  MSHADOW_CUDA_CALL(cudaMemcpyToSymbol(expr::plandetail::g_bounds_record, &clean, sizeof(clean)));
+  *offset = rec.offset;
+  *width = rec.width;
+  *limit = rec.limit;
+  return true;
+}
+#endif
+
 /*!
  * \brief one int per device in which a kernel records that a bounded wait gave up
  *  (see gpu/tma.cuh); allocated on first use, lives as long as the process

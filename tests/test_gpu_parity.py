@@ -474,6 +474,33 @@ def test_complex_expressions(lib, cid, rows, cols):
     assert_bits(host(got), want)
 
 
+def test_results_do_not_depend_on_the_run(lib):
+    """No atomics and no arrival-order folds anywhere: floating-point sums are bit-identical from run
+    to run (cluster and chunk partials are always combined in index order), also while other kernels
+    share the GPU."""
+    g = torch.Generator(device="cuda").manual_seed(3)
+    M = torch.randn(20000, 1536, device="cuda", generator=g)
+    T4 = torch.randn(96, 40, 28, 28, device="cuda", generator=g)
+    L = torch.randn(300, 32000, device="cuda", generator=g)
+    k, d, n = 5000, 512, 60000
+    idx = (torch.rand(n, device="cuda", generator=g) ** 3 * k).to(torch.int32)  # skewed: long runs of hot rows
+    src = torch.randn(n, d, device="cuda", generator=g)
+
+    def once():
+        out = [lib.reduce_keep_lowest(torch.zeros(1536, device="cuda"), M),
+               lib.reduce_keep_highdim(torch.zeros(40, device="cuda"), T4),
+               lib.softmax(torch.empty_like(L), L),
+               lib.addtakegrad(torch.zeros(k, d, device="cuda"), idx, src)]
+        return [host(t) for t in out]
+
+    first = once()
+    noise = torch.randn(4096, 4096, device="cuda")
+    for _ in range(3):
+        noise = noise * 1.0001  # unrelated work in flight changes the scheduling of the next kernels
+        for a, b in zip(first, once()):
+            assert_bits(a, b)
+
+
 def test_axis_argument_errors(lib):
     import ctypes as C
     z = torch.zeros(2, 3, 4, 5, device="cuda")
