@@ -65,6 +65,11 @@ int msb_stream_create(msb_stream_t *out);
 int msb_stream_destroy(msb_stream_t stream);
 int msb_stream_wait(msb_stream_t stream);
 int msb_stream_idle(msb_stream_t stream, int *idle);
+/* Self-test of the failure path that every kernel with a device-side wait relies on (no counterpart
+   in the reference, whose kernels do not wait): one thread waits, bounded by limit_ms (1..1000), on a
+   barrier that nothing signals, gives up, and marks the device status word.  The next msb_stream_wait
+   on the stream must then return MSB_ERR_TIMEOUT, and the device stays usable. */
+int msb_selftest_bounded_wait(int limit_ms, msb_stream_t stream);
 
 /* ---- memory ------------------------------------------------------------------------ */
 

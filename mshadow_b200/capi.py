@@ -45,6 +45,7 @@ _SIGNATURES = {
     "msb_stream_destroy": [vp],
     "msb_stream_wait": [vp],
     "msb_stream_idle": [vp, C.POINTER(cint)],
+    "msb_selftest_bounded_wait": [cint, vp],
     "msb_alloc_space": [C.POINTER(vp), C.POINTER(i64), i64, i64, i64, cint],
     "msb_free_space": [vp],
     "msb_alloc_host": [C.POINTER(vp), i64],

@@ -179,6 +179,25 @@ int msb_stream_wait(msb_stream_t stream) {
   }
   return MSB_OK;
 }
+namespace {
+__global__ void WaitThatNothingSignalsKernel(int *status, unsigned long long limit_ns) {
+  __shared__ uint64_t bar;
+  mshadow::cuda::tma::BarrierInit(&bar, 1);  // one arrival expected; none will come
+  if (!mshadow::cuda::tma::WaitBounded(&bar, 0, limit_ns)) {
+    atomicExch(status, mshadow::cuda::tma::kStatusBulkCopyTimeout);
+  }
+}
+}  // namespace
+
+int msb_selftest_bounded_wait(int limit_ms, msb_stream_t stream) {
+  MSB_REQUIRE(limit_ms >= 1 && limit_ms <= 1000, MSB_ERR_ARGUMENT, "limit_ms must be within 1..1000");
+  MSB_GUARD_BEGIN
+  WaitThatNothingSignalsKernel<<<1, 1, 0, static_cast<cudaStream_t>(stream)>>>(
+      gpu_rt::StatusWord(), static_cast<unsigned long long>(limit_ms) * 1000000ull);
+  MSHADOW_CUDA_POST_KERNEL_CHECK(WaitThatNothingSignalsKernel);
+  MSB_GUARD_END
+}
+
 int msb_stream_idle(msb_stream_t stream, int *idle) {
   MSB_REQUIRE(idle != nullptr, MSB_ERR_ARGUMENT, "null output");
   const cudaError_t err = cudaStreamQuery(static_cast<cudaStream_t>(stream));

@@ -8,9 +8,9 @@
  * addresses 16-byte aligned, byte count a multiple of 16.  Copies never leave the issuing
  * CTA's own shared memory and always read this GPU's own global memory.
  *
- * Every wait is bounded: after kWaitSpins unsuccessful polls WaitBounded() gives up and
- * reports false, and the caller records kStatusBulkCopyTimeout in the device status word
- * instead of computing on missing data.
+ * Every wait is bounded: after one second (or kWaitSpins unsuccessful polls, whichever comes
+ * first) WaitBounded() gives up and reports false, and the caller records
+ * kStatusBulkCopyTimeout in the device status word instead of computing on missing data.
  */
 #ifndef MSHADOW_GPU_TMA_CUH_
 #define MSHADOW_GPU_TMA_CUH_
@@ -23,6 +23,7 @@ namespace tma {
 
 const int kStatusBulkCopyTimeout = 1;
 const uint32_t kWaitSpins = 1u << 20;
+const uint64_t kWaitNanos = 1000000000ull;  // one second: a staged copy completes in microseconds
 
 __device__ __forceinline__ uint32_t SharedAddr(const void *p) {
   return static_cast<uint32_t>(__cvta_generic_to_shared(p));
@@ -66,10 +67,26 @@ __device__ __forceinline__ bool BarrierTest(uint64_t *bar, uint32_t parity) {
   return done != 0;
 }
 
-/*! \brief wait for the phase with the given parity; false if it did not complete in time */
-__device__ __forceinline__ bool WaitBounded(uint64_t *bar, uint32_t parity) {
-  for (uint32_t spin = 0; spin < kWaitSpins; ++spin) {
+/*! \brief nanoseconds of the device-wide timer */
+__device__ __forceinline__ uint64_t GlobalNanos() {
+  uint64_t t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+
+/*!
+ * \brief wait for the phase with the given parity; false if it did not complete within
+ *  `limit_ns` (looked at every 64 polls, a poll may itself block for a while) or kWaitSpins polls
+ */
+__device__ __forceinline__ bool WaitBounded(uint64_t *bar, uint32_t parity, uint64_t limit_ns = kWaitNanos) {
+  uint64_t start = 0;  // the clock is first read after 64 polls: a wait that succeeds quickly never reads it
+  for (uint32_t spin = 1; spin <= kWaitSpins; ++spin) {
     if (BarrierTest(bar, parity)) return true;
+    if ((spin & 63u) == 0) {
+      const uint64_t now = GlobalNanos();
+      if (start == 0) start = now;
+      else if (now - start > limit_ns) return false;
+    }
   }
   return false;
 }

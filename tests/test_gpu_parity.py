@@ -501,6 +501,24 @@ def test_results_do_not_depend_on_the_run(lib):
             assert_bits(a, b)
 
 
+def test_a_wait_that_nothing_signals_gives_up_and_is_reported(lib):
+    """The failure path behind every device-side wait: a bounded wait on a barrier that nothing signals
+    runs out, marks the status word, the next stream wait reports MSB_ERR_TIMEOUT (6), the mark is
+    cleared and the device keeps working.  No fault, trap or endless loop is involved."""
+    import time
+    assert lib.status("msb_selftest_bounded_wait", 0, None)[0] == 1      # limit outside 1..1000
+    t0 = time.time()
+    assert lib.status("msb_selftest_bounded_wait", 30, None)[0] == 0
+    st, msg = lib.status("msb_stream_wait", None)
+    assert st == 6 and "bounded wait" in msg
+    assert time.time() - t0 < 5.0                                         # the wait ended near its 30 ms limit
+    assert lib.status("msb_stream_wait", None)[0] == 0                   # reported once
+    x = torch.arange(12, dtype=torch.float32, device="cuda").reshape(3, 4)
+    got = lib.reduce_keep_lowest(torch.zeros(4, device="cuda"), x)
+    lib.stream_wait(None)
+    assert np.array_equal(host(got), host(x).sum(0))
+
+
 def test_axis_argument_errors(lib):
     import ctypes as C
     z = torch.zeros(2, 3, 4, 5, device="cuda")
