@@ -11,8 +11,13 @@
  *                    thread) and stores afterwards.  Rows whose length is not a multiple of
  *                    the group width finish with a scalar tail.  Dense operands are walked
  *                    as one long row, which removes the (y,x) split altogether.
- *   MapScalarKernel  the general fallback for plans that only know Eval(y,x) (index
- *                    remapping extension expressions, misaligned or odd-pitched tensors).
+ *                    With kSrcPack = false the same kernel serves expressions that only know
+ *                    Eval(y,x) but are cheap per element (expr::LaneInfo): a thread puts its
+ *                    group together from kLanes element evaluations, so the index split and
+ *                    the store are still paid once per 16 bytes.
+ *   MapScalarKernel  the general fallback: plans that only know Eval(y,x) and walk other
+ *                    elements per result (axis reductions), user-defined expressions,
+ *                    misaligned or odd-pitched destinations.
  * Both are grid-stride loops over a grid sized to the number of SMs; (y,x) is recovered
  * from the linear work index by multiplication with a precomputed reciprocal.
  *

@@ -291,6 +291,45 @@ int RunCase(int id, const float *a, const float *b, float *out, int rows, int co
       FreeSpace(&M2);
       break;
     }
+    case 17: {  // the same round trip on pitched tensors (row pitch != width), 16-byte-aligned runs
+      const Shape<3> s3 = Shape3(2, 12, 68);  // wide enough for AllocSpace to pitch the rows; out has one extra slot
+      Tensor<gpu, 3, float> A = NewTensor<gpu>(s3, 0.0f, true, st), G = NewTensor<gpu>(s3, 0.0f, true, st);
+      Tensor<cpu, 3, float> ha(const_cast<float *>(a), s3), hb(const_cast<float *>(b), s3), hout(out, s3);
+      Copy(A, ha, st);
+      Copy(G, hb, st);
+      Tensor<gpu, 2, float> M = NewTensor<gpu>(Shape2(3 * 3 * 2, 10 * 66), 1.0f, true, st);
+      M += unpack_patch2col(A, 3, 3, 1, 1);
+      G -= pack_col2patch(M, G.shape_, 3, 3, 1, 1);
+      Copy(hout, G, st);
+      st->Wait();
+      out[s3.Size()] = static_cast<float>(A.stride_ != s3[2]) + 2.0f * static_cast<float>(M.stride_ != M.size(1));
+      FreeSpace(&A);
+      FreeSpace(&G);
+      FreeSpace(&M);
+      break;
+    }
+    case 18: {  // the patch kernels are templates over the element type: binary64
+      const Shape<3> s3 = Shape3(2, 24, 26);
+      Tensor<gpu, 3, float> Af = NewTensor<gpu>(s3, 0.0f, false, st), Gf = NewTensor<gpu>(s3, 0.0f, false, st);
+      Tensor<cpu, 3, float> ha(const_cast<float *>(a), s3), hb(const_cast<float *>(b), s3), hout(out, s3);
+      Copy(Af, ha, st);
+      Copy(Gf, hb, st);
+      Tensor<gpu, 3, double> A = NewTensor<gpu>(s3, 0.0, false, st), G = NewTensor<gpu>(s3, 0.0, false, st);
+      A = tcast<double>(Af);
+      G = tcast<double>(Gf);
+      Tensor<gpu, 2, double> M = NewTensor<gpu>(Shape2(3 * 3 * 2, 22 * 24), 0.0, false, st);
+      M = unpack_patch2col(A, 3, 3, 1, 1);
+      G += pack_col2patch(M, G.shape_, 3, 3, 1, 1);
+      Gf = tcast<float>(G);
+      Copy(hout, Gf, st);
+      st->Wait();
+      FreeSpace(&Af);
+      FreeSpace(&Gf);
+      FreeSpace(&A);
+      FreeSpace(&G);
+      FreeSpace(&M);
+      break;
+    }
     default:
       rc = -1;
   }

@@ -205,3 +205,29 @@ def test_patch_columns_with_accumulating_savers(run, data):
     m2 = orc.unpack_patch2col(img, 4, 2, 2, 1, 1, 1)
     g = g + orc.pack_col2patch(m2, shape, 4, 2, 2, 1, 1, 1)
     assert rc == 0 and bits_equal(out.reshape(shape), g)
+
+
+def test_patch_columns_on_pitched_tensors(run):
+    """Row pitch != width on the image and on the matrix; the runs are 16-byte aligned, so the matrix
+    leaves the kernel in 16-byte groups."""
+    import cpu_checkers as cc
+    orc = cc.load("orc")
+    rng = np.random.default_rng(21)
+    shape = (1, 2, 12, 68)
+    a, b = (rng.uniform(-1, 1, shape).astype(np.float32) for _ in range(2))
+    rc, out = run(17, a, b, a.size + 1)
+    assert rc == 0 and out[-1] == 3.0  # both the image and the matrix were pitched
+    m = np.float32(1) + orc.unpack_patch2col(a, 3, 3, 1, 1, 1, 1)
+    assert bits_equal(out[:-1].reshape(shape), b - orc.pack_col2patch(m, shape, 3, 3, 1, 1, 1, 1))
+
+
+def test_patch_columns_in_double_precision(run):
+    import cpu_checkers as cc
+    orc = cc.load("orc")
+    rng = np.random.default_rng(22)
+    shape = (1, 2, 24, 26)
+    a, b = (rng.uniform(-1, 1, shape).astype(np.float32) for _ in range(2))
+    rc, out = run(18, a, b, a.size)
+    want = b.astype(np.float64) + orc.pack_col2patch(orc.unpack_patch2col(a, 3, 3, 1, 1, 1, 1), shape, 3, 3, 1, 1, 1, 1)
+    assert rc == 0
+    np.testing.assert_allclose(out.reshape(shape), want, rtol=2e-6, atol=2e-6)
