@@ -80,7 +80,7 @@ template <typename Reducer, int KY, int KX, int SY, int SX>
 __global__ void __launch_bounds__(kPoolThreads)
 PoolPlanesKernel(float *dst, const float *src, uint32_t planes, uint32_t h, uint32_t w, uint32_t ph, uint32_t pw,
                  PoolGeom g, int64_t ld_src, int64_t ld_dst, uint32_t gplanes, gpu_rt::FastDiv div_pw,
-                 gpu_rt::FastDiv div_ph, int *status) {
+                 gpu_rt::FastDiv div_ph, gpu_rt::FastDiv div_pairs, int *status) {
   extern __shared__ __align__(16) float tile[];
   __shared__ uint64_t bar;
   const int ky = KY > 0 ? KY : g.ky, kx = KX > 0 ? KX : g.kx;
@@ -108,6 +108,49 @@ PoolPlanesKernel(float *dst, const float *src, uint32_t planes, uint32_t h, uint
       __syncthreads();
     }
     const uint32_t nout = np * ph * pw;
+    if ((KX == 3 || KX == 2) && SX == 2 && KY > 0 && MSHADOW_B200_POOL_PAIRS && (w & 3u) == 0) {
+      // two adjacent outputs per thread: their windows span columns x0 .. x0+4 (x0+3 for 2-wide windows)
+      // with x0 a multiple of four, so each window row is one 16-byte and at most one 4-byte
+      // shared-memory load instead of six 4-byte loads, and the index split is paid once per pair: the
+      // one-output loop below keeps the issue slots 70 % busy, i.e. it is bound by instructions.  (The
+      // launcher only takes shapes in which no window is clipped.)  Values enter each output's
+      // reduction in the same order as below.
+      const uint32_t pairs_per_row = (pw + 1) >> 1;
+      const uint32_t npairs = np * ph * pairs_per_row;
+      for (uint32_t o = threadIdx.x; o < npairs; o += kPoolThreads) {
+        const uint32_t row = div_pairs.Quot(o);
+        const uint32_t px = (o - row * pairs_per_row) * 2;
+        const uint32_t p = div_ph.Quot(row);
+        const uint32_t py = row - p * ph;
+        const float *at = tile + p * h * w + py * SY * w + px * 2;
+        const bool second = px + 1 < pw;
+        float r0, r1;
+        Reducer::SetInitValue(r0);
+        Reducer::SetInitValue(r1);
+#pragma unroll
+        for (int dy = 0; dy < (KY > 0 ? KY : 1); ++dy) {
+          const float4 v = *reinterpret_cast<const float4 *>(at + dy * w);
+          Reducer::Reduce(r0, v.x);
+          Reducer::Reduce(r0, v.y);
+          if (KX == 3) {
+            const float e = second ? at[dy * w + 4] : 0.0f;
+            Reducer::Reduce(r0, v.z);
+            Reducer::Reduce(r1, v.z);
+            Reducer::Reduce(r1, v.w);
+            Reducer::Reduce(r1, e);
+          } else {
+            Reducer::Reduce(r1, v.z);
+            Reducer::Reduce(r1, v.w);
+          }
+        }
+        float *out = dst + (static_cast<int64_t>(first) * ph + row) * ld_dst + px;
+        out[0] = r0;
+        if (second) out[1] = r1;
+      }
+      tma::FenceAsyncShared();
+      __syncthreads();
+      continue;
+    }
     for (uint32_t o = threadIdx.x; o < nout; o += kPoolThreads) {
       const uint32_t row = div_pw.Quot(o);  // plane-local output row index: p * ph + py
       const uint32_t px = o - row * pw;
@@ -600,7 +643,8 @@ inline void PoolPlanesLaunch(float *dst, const float *src, int64_t planes, int64
                                            static_cast<int>(kPoolSmemBudget)));                                   \
     kernel<<<grid, kPoolThreads, smem, stream>>>(dst, src, static_cast<uint32_t>(planes), static_cast<uint32_t>(h), \
                                                 static_cast<uint32_t>(w), ph, pw, g, ld_src, ld_dst, gp,          \
-                                                gpu_rt::FastDiv(pw), gpu_rt::FastDiv(ph), status);                \
+                                                gpu_rt::FastDiv(pw), gpu_rt::FastDiv(ph),                         \
+                                                gpu_rt::FastDiv((pw + 1) / 2), status);                           \
   }
   if (ky == 3 && kx == 3 && sy == 2 && sx == 2) MSHADOW_B200_POOL_LAUNCH_(3, 3, 2, 2)
   else if (ky == 2 && kx == 2 && sy == 2 && sx == 2) MSHADOW_B200_POOL_LAUNCH_(2, 2, 2, 2)

@@ -216,7 +216,9 @@ def test_softmax_grad(lib, mode, rows, cols, pad):
 
 POOL_CASES = [(5, 6, 6, 2, 2, 2, 2, 0), (5, 13, 11, 3, 3, 2, 2, 0), (3, 8, 9, 3, 2, 1, 3, 3), (2, 7, 7, 7, 7, 1, 1, 0),
               (4, 10, 10, 2, 2, 3, 3, 0), (9, 56, 56, 3, 3, 2, 2, 0), (8, 27, 27, 3, 3, 2, 2, 0),
-              (70, 12, 12, 2, 2, 2, 2, 0), (3, 130, 120, 5, 4, 3, 2, 0)]
+              (70, 12, 12, 2, 2, 2, 2, 0), (3, 130, 120, 5, 4, 3, 2, 0),
+              # 3 x 3 / 2 on widths that are multiples of four (two outputs per thread), dense and pitched
+              (6, 20, 24, 3, 3, 2, 2, 4), (33, 9, 8, 3, 3, 2, 2, 0), (2, 64, 128, 3, 3, 2, 2, 0)]
 
 
 @pytest.mark.parametrize("reducer", [0, 1, 2])
