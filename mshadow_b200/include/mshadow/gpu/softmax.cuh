@@ -431,7 +431,8 @@ inline void SoftmaxGradLaunch(float *dst, const float *src, const float *label, 
 // neighbouring threads take neighbouring positions.
 // ----------------------------------------------------------------------------------------
 
-const int kSoftmax3DThreads = 128;
+const int kSoftmax3DThreads = MSHADOW_B200_SM3D_THREADS;
+constexpr int kSoftmax3DDepth = MSHADOW_B200_SM3D_DEPTH;
 
 /*!
  * \brief one CTA = one image y and a tile of kThreads * kLanes positions; thread t owns kLanes
@@ -456,7 +457,7 @@ Softmax3DKernel(float *dst, const float *src, uint32_t classes, uint32_t npos, u
   float m[kLanes], s[kLanes];
 #pragma unroll
   for (int l = 0; l < kLanes; ++l) m[l] = -FLT_MAX, s[l] = 0.0f;
-#pragma unroll 4
+#pragma unroll kSoftmax3DDepth
   for (uint32_t x = 0; x < classes; ++x) {
     float v[kLanes];
     if (kLanes == 4) {

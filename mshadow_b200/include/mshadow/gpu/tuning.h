@@ -58,6 +58,14 @@
 #define MSHADOW_B200_SMGRAD_UNROLL 1  // as for the map kernel: 1 -> 102 %, 2 -> 95-97 %, 4 -> 94 % of copy bandwidth
 #endif
 
+#ifndef MSHADOW_B200_SM3D_THREADS
+#define MSHADOW_B200_SM3D_THREADS 128  // softmax over the middle axis: threads per CTA, 4 positions each
+                                       // (64: 78.5 %, 128: 77.3 %, 256: 71.0 % of copy bandwidth, 21 classes)
+#endif
+#ifndef MSHADOW_B200_SM3D_DEPTH
+#define MSHADOW_B200_SM3D_DEPTH 4  // classes loaded ahead per thread in the first pass (4: 77.3 %, 8: 71.0 %, 21: 78.5 %)
+#endif
+
 #ifndef MSHADOW_B200_REDLOW_THREADS
 #define MSHADOW_B200_REDLOW_THREADS 128  // column reduce: threads per CTA (4 columns each)
 #endif
