@@ -79,6 +79,13 @@
 #define MSHADOW_B200_REDHIGH_DEPTH 4  // channel reduce: 16-byte groups in flight per thread
 #endif
 
+#ifndef MSHADOW_B200_REDLOW_CHUNKS
+#define MSHADOW_B200_REDLOW_CHUNKS 0  // column reduce: row chunks per column tile; 0 = chosen per shape
+#endif
+#ifndef MSHADOW_B200_REDHIGH_CHUNKS
+#define MSHADOW_B200_REDHIGH_CHUNKS 0  // channel reduce: chunks of the outer axis per channel; 0 = fill whole waves
+#endif
+
 #ifndef MSHADOW_B200_TRANSPOSE_TILE
 #define MSHADOW_B200_TRANSPOSE_TILE 64  // edge of the shared-memory tile of axis permutations (32: 62 %, 64: 90 %)
 #endif
