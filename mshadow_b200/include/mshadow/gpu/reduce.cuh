@@ -389,7 +389,30 @@ inline Split PlanKeepLowest(uint32_t rows, uint32_t col_tiles, uint32_t slots) {
   if (kmax < 1) kmax = 1;
   if (kmax > 4096) kmax = 4096;
   uint32_t pick = 0;
-  if (static_cast<uint64_t>(col_tiles) * kmax > slots) {
+  // Few, long CTAs first.  Every CTA streams its own band of rows, so the number of CTAs in flight is
+  // the number of DRAM streams; measured on 65536 x 4096 (8 column tiles, 148 SMs, 16 CTAs resident
+  // per SM): 128 chunks = 1024 CTAs, seven per SM, 98 % of copy bandwidth; 256 chunks 96 %; 288 chunks
+  // (what filling one wave of resident CTAs to 95 % picks) 93 %; 296 chunks = every slot taken 86 %;
+  // 64 chunks (3.5 per SM, unbalanced) 84 %.  So: about MSHADOW_B200_REDLOW_CTAS_PER_SM CTAs per SM,
+  // a multiple of the cluster size, nudged downwards until the SMs carry equal numbers of CTAs.
+  const uint32_t sms = static_cast<uint32_t>(gpu_rt::CurrentDevice().sm_count);
+  const uint64_t target = static_cast<uint64_t>(MSHADOW_B200_REDLOW_CTAS_PER_SM) * sms;
+  if (static_cast<uint64_t>(col_tiles) * kmax >= target && target / col_tiles >= static_cast<uint64_t>(kRedMaxCluster)) {
+    uint32_t k0 = static_cast<uint32_t>(target / col_tiles);
+    k0 -= k0 % kRedMaxCluster;
+    double best_balance = 0.0;
+    for (uint32_t k = k0; k >= static_cast<uint32_t>(kRedMaxCluster) && 2 * k >= k0; k -= kRedMaxCluster) {
+      const uint64_t ctas = static_cast<uint64_t>(col_tiles) * k;
+      const uint64_t per_sm = (ctas + sms - 1) / sms;
+      const double balance = static_cast<double>(ctas) / static_cast<double>(per_sm * sms);
+      if (balance > best_balance + 1e-9) {
+        best_balance = balance;
+        pick = k;
+      }
+      if (balance >= 0.97) break;
+    }
+  }
+  if (pick == 0 && static_cast<uint64_t>(col_tiles) * kmax > slots) {
     for (uint32_t k = kRedMaxCluster; k <= kmax && pick == 0; k += kRedMaxCluster) {
       const uint64_t ctas = static_cast<uint64_t>(col_tiles) * k;
       if (ctas * 20 < static_cast<uint64_t>(slots) * 19) continue;  // under 95 % of one wave

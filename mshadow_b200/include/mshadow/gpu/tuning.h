@@ -79,6 +79,9 @@
 #define MSHADOW_B200_REDHIGH_DEPTH 4  // channel reduce: 16-byte groups in flight per thread
 #endif
 
+#ifndef MSHADOW_B200_REDLOW_CTAS_PER_SM
+#define MSHADOW_B200_REDLOW_CTAS_PER_SM 7  // column reduce: CTAs (= DRAM streams) per SM aimed for on large inputs
+#endif
 #ifndef MSHADOW_B200_REDLOW_CHUNKS
 #define MSHADOW_B200_REDLOW_CHUNKS 0  // column reduce: row chunks per column tile; 0 = chosen per shape
 #endif
