@@ -86,8 +86,16 @@ int msb_free_host(void *ptr);
    forms: mshadow/tensor_gpu-inl.h:57-92.  Honours both strides. */
 int msb_copy_2d(void *dst, int64_t ld_dst, const void *src, int64_t ld_src, int64_t rows,
                 int64_t cols, int64_t elem_size, int kind, msb_stream_t stream);
-/* Scratch buffer of at least `bytes` for work on `stream`; owned by the library. */
+/* Scratch buffer of at least `bytes` for the caller's own work on `stream`; owned by the library
+   (one per device and stream, grown on demand, released by msb_stream_destroy / msb_shutdown).
+   It is not the buffer the operators use internally, so calls to them leave its contents alone.
+   The pointer stays valid until the next msb_workspace call on the same stream that asks for
+   more (the buffer is then replaced after the stream has drained). */
 int msb_workspace(msb_stream_t stream, int64_t bytes, void **out);
+/* No counterpart in the reference: bytes of device memory the library currently holds for `stream`
+   on the current device, as the operators' internal scratch and as the caller's workspace.  Lets
+   an integrator see when (and that) the library allocated on its behalf. */
+int msb_scratch_bytes(msb_stream_t stream, int64_t *engine_bytes, int64_t *caller_bytes);
 
 /* ---- element-wise expressions (MapExp): mshadow/tensor_gpu-inl.h:101-116 -------------
    Expression plans are C++ templates; these are fixed fp32 instantiations compiled from the

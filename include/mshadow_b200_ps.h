@@ -33,6 +33,27 @@ int msb_ps_new_unique_id(char *hex, int64_t capacity);
 int msb_ps_create(int rank, int world, const char *id_hex, int device, msb_ps_t *out);
 int msb_ps_destroy(msb_ps_t model);
 
+/* A second model behind the same interface, for small tensors whose exchange is bound by latency
+   (a few thousand partial sums per step): mshadow::ps::PeerModel.  Push stores the tensor straight
+   into a window of every other GPU's memory over NVLink and raises a flag there; PullReq waits for
+   all flags (at most wait_limit_ms, then msb_ps_pull_wait fails and the destination is left
+   unchanged) and adds the contributions in rank order, so that every rank receives the same bits.
+   It replaces the same LocalModel path (mshadow-ps/ps_local-inl.h:443-461, 625-662, 700-736:
+   device -> host copy, sum on a CPU thread, host -> device copy).
+   window_bytes, depth, wait_limit_ms: 0 selects the defaults (16 MiB, 4 slots, 2000 ms); a key of
+   n floats takes depth * world * n * 4 bytes of the window.  With depth d a rank may push at most
+   d/2 - 1 steps of a key ahead of pulling them.
+   Set-up: every rank creates its model, obtains its handle (128 hexadecimal digits and a
+   terminating zero; capacity at least 129), the application gathers the handles of all ranks in
+   rank order into one string and gives it to msb_ps_peer_connect on every rank.  world 1 needs no
+   connect.  The tensor calls below (init_key, push, pull_req, pull_wait, set_weight, check_weight,
+   destroy) serve both models; the application lets all ranks reach a barrier of its own before
+   it destroys a peer model. */
+int msb_ps_peer_create(int rank, int world, int device, int64_t window_bytes, int depth, int wait_limit_ms,
+                       msb_ps_t *out);
+int msb_ps_peer_handle(msb_ps_t model, char *hex, int64_t capacity);
+int msb_ps_peer_connect(msb_ps_t model, const char *all_handles_hex);
+
 /* ISharedModel::InitKey(Shape2(rows, cols), key, device) */
 int msb_ps_init_key(msb_ps_t model, int key, int64_t rows, int64_t cols);
 /* ISharedModel::Push: contribute `data` to the sum under `key`; ordered after the work already

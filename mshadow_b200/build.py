@@ -58,27 +58,35 @@ def _stale(out, deps):
     return False
 
 
-def build_all(force=False, verbose=True):
+def build_all(force=False, verbose=True, only=None):
+    """Builds every stale target; independent targets compile side by side.  `only` restricts the
+    build to targets whose output file name contains that text."""
+    from concurrent.futures import ThreadPoolExecutor
     deps_common = [os.path.join(HERE, "include"), os.path.join(ROOT, "include"), os.path.join(HERE, "csrc")]
+    cmds = []
     for out, srcs, extra in TARGETS:
-        if not all(os.path.exists(s) for s in srcs):
+        if not all(os.path.exists(s) for s in srcs) or (only and only not in os.path.basename(out)):
             continue
         if not force and not _stale(out, srcs + deps_common):
             continue
-        cmd = [_nvcc()] + NVCC_FLAGS + ["-o", out] + srcs + extra
-        if verbose:
-            print("[build]", " ".join(cmd), flush=True)
-        subprocess.check_call(cmd)
+        cmds.append([_nvcc()] + NVCC_FLAGS + ["-o", out] + srcs + extra)
     for out, srcs in HOST_TARGETS:
-        if not all(os.path.exists(s) for s in srcs):
+        if not all(os.path.exists(s) for s in srcs) or (only and only not in os.path.basename(out)):
             continue
         if not force and not _stale(out, srcs + deps_common):
             continue
-        cmd = [shutil.which("g++") or "g++"] + HOST_FLAGS + ["-o", out] + srcs
+        cmds.append([shutil.which("g++") or "g++"] + HOST_FLAGS + ["-o", out] + srcs)
+
+    def run(cmd):
         if verbose:
             print("[build]", " ".join(cmd), flush=True)
         subprocess.check_call(cmd)
+
+    if cmds:
+        with ThreadPoolExecutor(max_workers=min(len(cmds), os.cpu_count() or 1)) as pool:
+            list(pool.map(run, cmds))
 
 
 if __name__ == "__main__":
-    build_all(force="--force" in sys.argv)
+    build_all(force="--force" in sys.argv,
+              only=next((a.split("=", 1)[1] for a in sys.argv if a.startswith("--only=")), None))

@@ -52,6 +52,7 @@ _SIGNATURES = {
     "msb_free_host": [vp],
     "msb_copy_2d": [vp, i64, vp, i64, i64, i64, i64, cint, vp],
     "msb_workspace": [vp, i64, C.POINTER(vp)],
+    "msb_scratch_bytes": [vp, C.POINTER(i64), C.POINTER(i64)],
     "msb_expr_case_f32": [cint, vp, vp, vp, vp, vp, i64, i64, i64, i64, i64, i64, vp],
     "msb_reduce_keep_lowest_f32": [vp, vp, i64, i64, i64, f32, cint, cint, vp],
     "msb_reduce_keep_lowest_sum_f32_noalloc": [vp, vp, i64, i64, i64, f32, vp],
@@ -157,6 +158,18 @@ class Library:
 
     def free_host(self, p):
         self.call("msb_free_host", vp(p))
+
+    def workspace(self, nbytes, stream=None):
+        """Device address of the caller's scratch buffer of `stream` (at least `nbytes`)."""
+        p = vp()
+        self.call("msb_workspace", stream, nbytes, C.byref(p))
+        return p.value
+
+    def scratch_bytes(self, stream=None):
+        """(engine, caller): bytes the library holds for `stream` as internal scratch and as workspace."""
+        a, b = i64(), i64()
+        self.call("msb_scratch_bytes", stream, C.byref(a), C.byref(b))
+        return a.value, b.value
 
     def copy_2d(self, dst, ld_dst, src, ld_src, rows, cols, kind, elem_size=4, stream=None):
         self.call("msb_copy_2d", _ptr(dst), ld_dst, _ptr(src), ld_src, rows, cols, elem_size, kind, stream)

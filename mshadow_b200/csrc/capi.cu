@@ -55,6 +55,8 @@ inline G3 Planes(const float *p, int64_t n, int64_t h, int64_t w, int64_t ld, St
 }
 
 inline bool FitsIndex(int64_t v) { return v >= 0 && v <= 0x7fffffffLL; }
+/*! \brief a leading dimension covers its row and fits the 32-bit stride field of a Tensor */
+inline bool LdOk(int64_t ld, int64_t width) { return ld >= width && FitsIndex(ld); }
 
 // user-style functors for the exported expression cases (cf. guide/defop.cpp of the reference)
 struct clip_mul {
@@ -166,16 +168,28 @@ int msb_stream_destroy(msb_stream_t stream) {
   MSB_GUARD_END
 }
 int msb_stream_wait(msb_stream_t stream) {
-  const cudaError_t err = cudaStreamSynchronize(static_cast<cudaStream_t>(stream));
-  if (err != cudaSuccess) return Fail(MSB_ERR_CUDA, cudaGetErrorString(err));
-  // a kernel whose bounded wait ran out leaves a mark in the device status word
-  int flag = 0;
-  int *word = mshadow::cuda::pooldetail::StatusWord();
-  if (cudaMemcpy(&flag, word, sizeof(int), cudaMemcpyDeviceToHost) != cudaSuccess)
-    return Fail(MSB_ERR_CUDA, "cannot read device status word");
-  if (flag != 0) {
-    cudaMemset(word, 0, sizeof(int));
-    return Fail(MSB_ERR_TIMEOUT, "a device-side bounded wait gave up (status " + std::to_string(flag) + ")");
+  // A kernel whose bounded wait ran out leaves a mark in the device's status word.  The word is
+  // read on the waited stream itself (into page-locked memory), so that waiting on one stream does
+  // not wait for work on the others.
+  MSB_TRACE_RANGE_
+  try {
+    const cudaStream_t s = static_cast<cudaStream_t>(stream);
+    int *word = gpu_rt::StatusWord();
+    int *seen = gpu_rt::StatusMirror();
+    *seen = 0;
+    MSHADOW_CUDA_CALL(cudaMemcpyAsync(seen, word, sizeof(int), cudaMemcpyDeviceToHost, s));
+    const cudaError_t err = cudaStreamSynchronize(s);
+    if (err != cudaSuccess) return Fail(MSB_ERR_CUDA, cudaGetErrorString(err));
+    const int flag = *seen;
+    if (flag != 0) {
+      MSHADOW_CUDA_CALL(cudaMemsetAsync(word, 0, sizeof(int), s));
+      MSHADOW_CUDA_CALL(cudaStreamSynchronize(s));
+      return Fail(MSB_ERR_TIMEOUT, "a device-side bounded wait gave up (status " + std::to_string(flag) + ")");
+    }
+  } catch (const dmlc::Error &e) {
+    return Fail(MSB_ERR_CUDA, e.what());
+  } catch (const std::exception &e) {
+    return Fail(MSB_ERR_MEMORY, e.what());
   }
   return MSB_OK;
 }
@@ -240,7 +254,7 @@ int msb_free_host(void *ptr) {
 int msb_copy_2d(void *dst, int64_t ld_dst, const void *src, int64_t ld_src, int64_t rows, int64_t cols,
                 int64_t elem_size, int kind, msb_stream_t stream) {
   MSB_REQUIRE(kind >= 1 && kind <= 3, MSB_ERR_ARGUMENT, "kind must be 1 (h2d), 2 (d2h) or 3 (d2d)");
-  MSB_REQUIRE(rows >= 0 && cols >= 0 && ld_dst >= cols && ld_src >= cols, MSB_ERR_SHAPE, "bad extents");
+  MSB_REQUIRE(rows >= 0 && cols >= 0 && LdOk(ld_dst, cols) && LdOk(ld_src, cols), MSB_ERR_SHAPE, "bad extents");
   if (rows == 0 || cols == 0) return MSB_OK;
   MSB_REQUIRE(dst != nullptr && src != nullptr, MSB_ERR_ARGUMENT, "null pointer");
   const cudaMemcpyKind k =
@@ -257,7 +271,16 @@ int msb_copy_2d(void *dst, int64_t ld_dst, const void *src, int64_t ld_src, int6
 int msb_workspace(msb_stream_t stream, int64_t bytes, void **out) {
   MSB_REQUIRE(out != nullptr && bytes >= 0, MSB_ERR_ARGUMENT, "bad argument");
   MSB_GUARD_BEGIN
-  *out = gpu_rt::Scratch::Get(static_cast<cudaStream_t>(stream), static_cast<size_t>(bytes));
+  // the caller's buffer is not the one the operators park their partial results in
+  *out = gpu_rt::Scratch::Get(static_cast<cudaStream_t>(stream), static_cast<size_t>(bytes), gpu_rt::Scratch::kCaller);
+  MSB_GUARD_END
+}
+
+int msb_scratch_bytes(msb_stream_t stream, int64_t *engine_bytes, int64_t *caller_bytes) {
+  MSB_REQUIRE(engine_bytes != nullptr && caller_bytes != nullptr, MSB_ERR_ARGUMENT, "null output");
+  MSB_GUARD_BEGIN
+  *engine_bytes = static_cast<int64_t>(gpu_rt::Scratch::Held(static_cast<cudaStream_t>(stream), gpu_rt::Scratch::kEngine));
+  *caller_bytes = static_cast<int64_t>(gpu_rt::Scratch::Held(static_cast<cudaStream_t>(stream), gpu_rt::Scratch::kCaller));
   MSB_GUARD_END
 }
 
@@ -266,7 +289,7 @@ int msb_expr_case_f32(int id, float *dst, const float *A, const float *B, const 
                       msb_stream_t stream) {
   MSB_REQUIRE(id >= 0 && id <= 9, MSB_ERR_ARGUMENT, "unknown expression id");
   MSB_REQUIRE(FitsIndex(rows) && FitsIndex(cols) && FitsIndex(rows * cols), MSB_ERR_SHAPE, "extent out of range");
-  MSB_REQUIRE(ld_dst >= cols && ld_a >= cols && ld_b >= cols && ld_c >= cols, MSB_ERR_SHAPE, "stride < width");
+  MSB_REQUIRE(LdOk(ld_dst, cols) && LdOk(ld_a, cols) && LdOk(ld_b, cols) && LdOk(ld_c, cols), MSB_ERR_SHAPE, "stride < width");
   if (rows == 0 || cols == 0) return MSB_OK;
   MSB_REQUIRE(dst && A && B && C && bias, MSB_ERR_ARGUMENT, "null pointer");
   MSB_GUARD_BEGIN
@@ -292,7 +315,7 @@ int msb_expr_case_f32(int id, float *dst, const float *A, const float *B, const 
 int msb_reduce_keep_lowest_f32(float *dst, const float *src, int64_t rows, int64_t cols, int64_t ld, float scale,
                                int saver, int reducer, msb_stream_t stream) {
   MSB_REQUIRE(saver >= 0 && saver <= 4 && reducer >= 0 && reducer <= 2, MSB_ERR_ARGUMENT, "unknown selector");
-  MSB_REQUIRE(FitsIndex(rows) && FitsIndex(cols) && FitsIndex(rows * cols) && ld >= cols, MSB_ERR_SHAPE,
+  MSB_REQUIRE(FitsIndex(rows) && FitsIndex(cols) && FitsIndex(rows * cols) && LdOk(ld, cols), MSB_ERR_SHAPE,
               "extent out of range");
   MSB_REQUIRE(rows > 0, MSB_ERR_SHAPE, "can not reduce over empty tensor");
   if (cols == 0) return MSB_OK;
@@ -310,7 +333,7 @@ int msb_reduce_keep_lowest_f32(float *dst, const float *src, int64_t rows, int64
 int msb_reduce_keep_highdim_f32(float *dst, const float *src, int64_t n, int64_t c, int64_t h, int64_t w, int64_t ld,
                                 float scale, int saver, int reducer, msb_stream_t stream) {
   MSB_REQUIRE(saver >= 0 && saver <= 4 && reducer >= 0 && reducer <= 2, MSB_ERR_ARGUMENT, "unknown selector");
-  MSB_REQUIRE(FitsIndex(n) && FitsIndex(c) && FitsIndex(h) && FitsIndex(w) && ld >= w, MSB_ERR_SHAPE,
+  MSB_REQUIRE(FitsIndex(n) && FitsIndex(c) && FitsIndex(h) && FitsIndex(w) && LdOk(ld, w), MSB_ERR_SHAPE,
               "extent out of range");
   MSB_REQUIRE(FitsIndex(n * c) && FitsIndex(n * c * h) && FitsIndex(n * c * h * w), MSB_ERR_SHAPE, "tensor too large");
   if (c == 0) return MSB_OK;
@@ -327,7 +350,7 @@ int msb_reduce_keep_highdim_f32(float *dst, const float *src, int64_t n, int64_t
 
 int msb_softmax_f32(float *dst, const float *src, int64_t rows, int64_t cols, int64_t ld_dst, int64_t ld_src,
                     msb_stream_t stream) {
-  MSB_REQUIRE(FitsIndex(rows) && FitsIndex(cols) && ld_dst >= cols && ld_src >= cols, MSB_ERR_SHAPE,
+  MSB_REQUIRE(FitsIndex(rows) && FitsIndex(cols) && LdOk(ld_dst, cols) && LdOk(ld_src, cols), MSB_ERR_SHAPE,
               "extent out of range");
   if (rows == 0 || cols == 0) return MSB_OK;
   MSB_REQUIRE(dst && src, MSB_ERR_ARGUMENT, "null pointer");
@@ -341,7 +364,7 @@ int msb_softmax_grad_f32(float *dst, const float *src, const float *label, int64
                          int64_t ld_dst, int64_t ld_src, int mode, float ignore_label, float alpha,
                          msb_stream_t stream) {
   MSB_REQUIRE(mode >= 0 && mode <= 3, MSB_ERR_ARGUMENT, "mode must be 0..3");
-  MSB_REQUIRE(FitsIndex(rows) && FitsIndex(cols) && FitsIndex(rows * cols) && ld_dst >= cols && ld_src >= cols,
+  MSB_REQUIRE(FitsIndex(rows) && FitsIndex(cols) && FitsIndex(rows * cols) && LdOk(ld_dst, cols) && LdOk(ld_src, cols),
               MSB_ERR_SHAPE, "extent out of range");
   if (rows == 0 || cols == 0) return MSB_OK;
   MSB_REQUIRE(dst && src && label, MSB_ERR_ARGUMENT, "null pointer");
@@ -361,7 +384,7 @@ int msb_softmax_grad_f32(float *dst, const float *src, const float *label, int64
 
 int msb_softmax_grad_fused_f32(float *dst, const float *logits, const float *label, int64_t rows, int64_t cols,
                                int64_t ld_dst, int64_t ld_src, msb_stream_t stream) {
-  MSB_REQUIRE(FitsIndex(rows) && FitsIndex(cols) && ld_dst >= cols && ld_src >= cols, MSB_ERR_SHAPE,
+  MSB_REQUIRE(FitsIndex(rows) && FitsIndex(cols) && LdOk(ld_dst, cols) && LdOk(ld_src, cols), MSB_ERR_SHAPE,
               "extent out of range");
   if (rows == 0 || cols == 0) return MSB_OK;
   MSB_REQUIRE(dst && logits && label, MSB_ERR_ARGUMENT, "null pointer");
@@ -380,7 +403,7 @@ int msb_pool_f32(float *dst, const float *src, int64_t planes, int64_t h, int64_
               MSB_ERR_SHAPE, "extent out of range");
   MSB_REQUIRE(h >= ky && w >= kx, MSB_ERR_SHAPE, "PoolingExp: kernel must be smaller than image");
   const int64_t ph = (h - ky) / sy + 1, pw = (w - kx) / sx + 1;
-  MSB_REQUIRE(ld_src >= w && ld_dst >= pw, MSB_ERR_SHAPE, "stride < width");
+  MSB_REQUIRE(LdOk(ld_src, w) && LdOk(ld_dst, pw), MSB_ERR_SHAPE, "stride < width");
   if (planes == 0) return MSB_OK;
   MSB_REQUIRE(dst && src, MSB_ERR_ARGUMENT, "null pointer");
   MSB_GUARD_BEGIN
@@ -401,7 +424,7 @@ int msb_unpool_f32(float *dst, const float *src, const float *pooled, const floa
   MSB_REQUIRE(FitsIndex(planes) && FitsIndex(h) && FitsIndex(w) && FitsIndex(planes * h) && FitsIndex(planes * h * w) &&
                   FitsIndex(ph) && FitsIndex(pw),
               MSB_ERR_SHAPE, "extent out of range");
-  MSB_REQUIRE(ld_src >= w && ld_dst >= w && ld_pooled >= pw, MSB_ERR_SHAPE, "stride < width");
+  MSB_REQUIRE(LdOk(ld_src, w) && LdOk(ld_dst, w) && LdOk(ld_pooled, pw), MSB_ERR_SHAPE, "stride < width");
   if (planes == 0 || h * w == 0) return MSB_OK;
   MSB_REQUIRE(dst && src && (ph * pw == 0 || (pooled && gpooled)), MSB_ERR_ARGUMENT, "null pointer");
   MSB_GUARD_BEGIN
@@ -423,7 +446,7 @@ int msb_chpool_f32(float *dst, const float *src, int64_t n, int64_t c, int64_t h
                   FitsIndex(n * c * h * w),
               MSB_ERR_SHAPE, "extent out of range");
   MSB_REQUIRE(c >= nsize, MSB_ERR_SHAPE, "chpool: local size must be smaller than nchannels");
-  MSB_REQUIRE(ld_src >= w && ld_dst >= w, MSB_ERR_SHAPE, "stride < width");
+  MSB_REQUIRE(LdOk(ld_src, w) && LdOk(ld_dst, w), MSB_ERR_SHAPE, "stride < width");
   const int64_t co = (c - nsize + pad * 2 + 1) / stride;
   if (n * co * h * w == 0) return MSB_OK;
   MSB_REQUIRE(dst && src, MSB_ERR_ARGUMENT, "null pointer");
@@ -445,7 +468,7 @@ int msb_ch_unpool_f32(float *dst, const float *src, const float *pooled, const f
   MSB_REQUIRE(FitsIndex(n) && FitsIndex(c) && FitsIndex(pc) && FitsIndex(h) && FitsIndex(w) && FitsIndex(n * c * h) &&
                   FitsIndex(n * c * h * w) && FitsIndex(n * pc * h * w),
               MSB_ERR_SHAPE, "extent out of range");
-  MSB_REQUIRE(ld_src >= w && ld_dst >= w && ld_pooled >= w, MSB_ERR_SHAPE, "stride < width");
+  MSB_REQUIRE(LdOk(ld_src, w) && LdOk(ld_dst, w) && LdOk(ld_pooled, w), MSB_ERR_SHAPE, "stride < width");
   if (n * c * h * w == 0) return MSB_OK;
   {
     const int64_t top = (c - 1 + pad + stride) / stride;
@@ -465,7 +488,7 @@ int msb_ch_unpool_f32(float *dst, const float *src, const float *pooled, const f
 
 int msb_addtakegrad_f32_i32(float *dst, const int32_t *index, const float *src, int64_t k, int64_t d, int64_t nidx,
                             int64_t ld_dst, int64_t ld_src, msb_stream_t stream) {
-  MSB_REQUIRE(FitsIndex(k) && FitsIndex(d) && FitsIndex(nidx) && ld_dst >= d && ld_src >= d, MSB_ERR_SHAPE,
+  MSB_REQUIRE(FitsIndex(k) && FitsIndex(d) && FitsIndex(nidx) && LdOk(ld_dst, d) && LdOk(ld_src, d), MSB_ERR_SHAPE,
               "extent out of range");
   MSB_REQUIRE(k > 0 || nidx == 0, MSB_ERR_SHAPE, "empty table");
   if (nidx == 0 || d == 0) return MSB_OK;
@@ -504,7 +527,7 @@ int msb_sort_by_key_i32(int32_t *keys, int32_t *values, int64_t n, int ascend, m
 int msb_softmax3d_f32(float *dst, const float *src, int64_t batch, int64_t classes, int64_t npos, int64_t ld_dst,
                       int64_t ld_src, msb_stream_t stream) {
   MSB_REQUIRE(FitsIndex(batch) && FitsIndex(classes) && FitsIndex(npos) && FitsIndex(batch * classes) &&
-                  FitsIndex(batch * classes * npos) && ld_dst >= npos && ld_src >= npos,
+                  FitsIndex(batch * classes * npos) && LdOk(ld_dst, npos) && LdOk(ld_src, npos),
               MSB_ERR_SHAPE, "extent out of range");
   if (batch == 0 || classes == 0 || npos == 0) return MSB_OK;
   MSB_REQUIRE(dst && src, MSB_ERR_ARGUMENT, "null pointer");
@@ -522,7 +545,7 @@ int msb_softmax_grad3d_f32(float *dst, const float *src, const float *label, int
                            float ignore_label, float alpha, msb_stream_t stream) {
   MSB_REQUIRE(mode >= 0 && mode <= 3, MSB_ERR_ARGUMENT, "mode must be 0..3");
   MSB_REQUIRE(FitsIndex(batch) && FitsIndex(classes) && FitsIndex(npos) && FitsIndex(batch * classes) &&
-                  FitsIndex(batch * classes * npos) && ld_dst >= npos && ld_src >= npos && ld_label >= npos,
+                  FitsIndex(batch * classes * npos) && LdOk(ld_dst, npos) && LdOk(ld_src, npos) && LdOk(ld_label, npos),
               MSB_ERR_SHAPE, "extent out of range");
   if (batch == 0 || classes == 0 || npos == 0) return MSB_OK;
   MSB_REQUIRE(dst && src && label, MSB_ERR_ARGUMENT, "null pointer");

@@ -102,7 +102,8 @@ extern "C" int msb_reduce_keep_lowest_sum_f32_noalloc(float *dst, const float *s
                                                        int64_t ld, float scale, msb_stream_t stream) {
   using namespace mshadow;  // NOLINT(*)
   if (rows <= 0) return FailNoAlloc(MSB_ERR_SHAPE, "can not reduce over empty tensor");
-  if (cols < 0 || ld < cols || rows > 0x7fffffffLL || cols > 0x7fffffffLL || rows * cols > 0x7fffffffLL)
+  if (cols < 0 || ld < cols || ld > 0x7fffffffLL || rows > 0x7fffffffLL || cols > 0x7fffffffLL ||
+      rows * cols > 0x7fffffffLL)
     return FailNoAlloc(MSB_ERR_SHAPE, "extent out of range");
   if (cols == 0) return MSB_OK;
   if (dst == nullptr || src == nullptr) return FailNoAlloc(MSB_ERR_ARGUMENT, "null pointer");
@@ -113,6 +114,9 @@ extern "C" int msb_reduce_keep_lowest_sum_f32_noalloc(float *dst, const float *s
   const int rc = SetUpDevice(dev, &pd);
   if (rc != MSB_OK) return rc;
 
+  // Nothing below may leave through the C boundary as an exception: the planning helper and the
+  // plan constructors CHECK their arguments, and a failed CHECK throws in this build.
+  try {
   // same 128-bit eligibility rule and the same split as the allocating entry point
   const bool vec = cols % 4 == 0 && reinterpret_cast<uintptr_t>(src) % 16 == 0 && (rows == 1 || ld % 4 == 0);
   const int lanes = vec ? 4 : 1;
@@ -152,11 +156,16 @@ extern "C" int msb_reduce_keep_lowest_sum_f32_noalloc(float *dst, const float *s
     err = cudaLaunchKernelEx(&cfg, MSB_NOALLOC_KERNEL(1), dplan, splan, urows, ucols, sp.per_chunk, scale, partial);
   }
   if (err != cudaSuccess) return FailNoAlloc(MSB_ERR_CUDA, cudaGetErrorString(err));
+  gpu_rt::LaunchCounter().fetch_add(1, std::memory_order_relaxed);
   if (partial != nullptr) {
     mshadow::cuda::ReduceFinishKernel<sv::saveto, red::sum, float, DPlan>
         <<<(ucols + 255) / 256, 256, 0, st.stream_>>>(dplan, partial, sp.clusters, ucols, scale);
     err = cudaPeekAtLastError();
     if (err != cudaSuccess) return FailNoAlloc(MSB_ERR_CUDA, cudaGetErrorString(err));
+    gpu_rt::LaunchCounter().fetch_add(1, std::memory_order_relaxed);
+  }
+  } catch (const std::exception &e) {
+    return FailNoAlloc(MSB_ERR_SHAPE, e.what());
   }
   return MSB_OK;
 }

@@ -1,5 +1,7 @@
 /*
- * C ABI around mshadow::ps::NcclModel<float> (see mshadow_b200_ps.h for the contract).
+ * C ABI around mshadow::ps::NcclModel<float> and mshadow::ps::PeerModel<float> (see
+ * mshadow_b200_ps.h for the contract).  A handle is a pointer to the ISharedModel base, so the
+ * tensor calls are the same for both models.
  * A separate shared object, so that the single-GPU library carries no NCCL dependency.
  */
 #include "mshadow_b200_ps.h"
@@ -20,7 +22,9 @@ int FailPs(const std::string &msg) {
   return 1;
 }
 
-typedef ps::NcclModel<float> Model;
+typedef ps::ISharedModel<gpu, float> Model;
+typedef ps::NcclModel<float> NcclImpl;
+typedef ps::PeerModel<float> PeerImpl;
 
 /*! \brief the caller's matrix as a tensor on the caller's stream */
 struct View {
@@ -55,7 +59,7 @@ const char *msb_ps_last_error(void) { return g_ps_error.c_str(); }
 int msb_ps_new_unique_id(char *hex, int64_t capacity) {
   if (hex == NULL || capacity < 2 * NCCL_UNIQUE_ID_BYTES + 1) return FailPs("msb_ps_new_unique_id: buffer too small");
   PS_BEGIN
-  const std::string s = Model::NewUniqueIdHex();
+  const std::string s = NcclImpl::NewUniqueIdHex();
   snprintf(hex, static_cast<size_t>(capacity), "%s", s.c_str());
   PS_END
 }
@@ -64,9 +68,9 @@ int msb_ps_create(int rank, int world, const char *id_hex, int device, msb_ps_t 
   if (out == NULL) return FailPs("msb_ps_create: null pointer");
   if (world < 1 || rank < 0 || rank >= world) return FailPs("msb_ps_create: rank outside [0, world)");
   if (world > 1 && id_hex == NULL) return FailPs("msb_ps_create: an identifier is needed for more than one process");
-  Model *m = NULL;
+  NcclImpl *m = NULL;
   try {
-    m = new Model();
+    m = new NcclImpl();
     char num[32];
     snprintf(num, sizeof(num), "%d", rank);
     m->SetParam("rank", num);
@@ -78,8 +82,61 @@ int msb_ps_create(int rank, int world, const char *id_hex, int device, msb_ps_t 
     delete m;
     return FailPs(e.what());
   }
-  *out = m;
+  *out = static_cast<Model *>(m);
   return 0;
+}
+
+int msb_ps_peer_create(int rank, int world, int device, int64_t window_bytes, int depth, int wait_limit_ms,
+                       msb_ps_t *out) {
+  if (out == NULL) return FailPs("msb_ps_peer_create: null pointer");
+  if (world < 1 || rank < 0 || rank >= world) return FailPs("msb_ps_peer_create: rank outside [0, world)");
+  PeerImpl *m = NULL;
+  try {
+    m = new PeerImpl();
+    char num[32];
+    snprintf(num, sizeof(num), "%d", rank);
+    m->SetParam("rank", num);
+    snprintf(num, sizeof(num), "%d", world);
+    m->SetParam("world_size", num);
+    if (window_bytes > 0) {
+      snprintf(num, sizeof(num), "%lld", static_cast<long long>(window_bytes));
+      m->SetParam("window_bytes", num);
+    }
+    if (depth > 0) {
+      snprintf(num, sizeof(num), "%d", depth);
+      m->SetParam("depth", num);
+    }
+    if (wait_limit_ms > 0) {
+      snprintf(num, sizeof(num), "%d", wait_limit_ms);
+      m->SetParam("wait_limit_ms", num);
+    }
+    m->Init(std::vector<int>(1, device));
+  } catch (const std::exception &e) {
+    delete m;
+    return FailPs(e.what());
+  }
+  *out = static_cast<Model *>(m);
+  return 0;
+}
+
+int msb_ps_peer_handle(msb_ps_t model, char *hex, int64_t capacity) {
+  PeerImpl *m = dynamic_cast<PeerImpl *>(static_cast<Model *>(model));
+  if (m == NULL) return FailPs("msb_ps_peer_handle: not a peer model");
+  if (hex == NULL || capacity < 2 * ps::peerdetail::kHandleBytes + 1) return FailPs("msb_ps_peer_handle: buffer too small");
+  PS_BEGIN
+  const std::string s = m->ExportHandleHex();
+  snprintf(hex, static_cast<size_t>(capacity), "%s", s.c_str());
+  PS_END
+}
+
+int msb_ps_peer_connect(msb_ps_t model, const char *all_handles_hex) {
+  PeerImpl *m = dynamic_cast<PeerImpl *>(static_cast<Model *>(model));
+  if (m == NULL) return FailPs("msb_ps_peer_connect: not a peer model");
+  if (all_handles_hex == NULL) return FailPs("msb_ps_peer_connect: null pointer");
+  PS_BEGIN
+  m->SetParam("peer_handles", all_handles_hex);
+  m->Connect();
+  PS_END
 }
 
 int msb_ps_destroy(msb_ps_t model) {

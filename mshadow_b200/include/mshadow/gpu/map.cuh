@@ -128,14 +128,9 @@ MapScalarKernel(DPlan dst, const SPlan src, uint32_t rows, uint32_t cols, gpu_rt
  */
 template <typename Kernel>
 inline int MapGridSize(int64_t work_items, Kernel kernel) {
-  static int resident = 0;  // per kernel instantiation; the engine targets one device model
-  if (resident == 0) {
-    int per_sm = 0;
-    MSHADOW_CUDA_CALL(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, kMapThreads, 0));
-    if (per_sm < 1) per_sm = 1;
-    if (per_sm > kMapCtasPerSM) per_sm = kMapCtasPerSM;
-    resident = per_sm * gpu_rt::CurrentDevice().sm_count;
-  }
+  int per_sm = gpu_rt::ResidentPerSM(kernel, kMapThreads);
+  if (per_sm > kMapCtasPerSM) per_sm = kMapCtasPerSM;
+  const int resident = per_sm * gpu_rt::CurrentDevice().sm_count;
   const int want = gpu_rt::CeilDiv(work_items, static_cast<int64_t>(kMapThreads) * kMapUnroll);
   return want < 1 ? 1 : (want < resident ? want : resident);
 }

@@ -713,12 +713,8 @@ inline void ChannelPoolLaunch(float *dst, const float *src, int64_t n, int64_t c
     auto kernel = ChannelPoolKernel<Reducer, NS, LANES>;                                                       \
     /* cut the channel march into the number of segments that fills whole waves of resident CTAs; every      \
        segment costs NS-1 halo channels, so segments stay at least 8 windows long */                          \
-    static uint32_t slots = 0;                                                                                 \
-    if (slots == 0) {                                                                                          \
-      int per_sm = 0;                                                                                          \
-      MSHADOW_CUDA_CALL(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, kPoolThreads, 0));      \
-      slots = static_cast<uint32_t>(per_sm < 1 ? 1 : per_sm) * gpu_rt::CurrentDevice().sm_count;               \
-    }                                                                                                          \
+    const uint32_t slots = static_cast<uint32_t>(gpu_rt::ResidentPerSM(kernel, kPoolThreads)) *               \
+                           gpu_rt::CurrentDevice().sm_count;                                                   \
     uint32_t max_seg = static_cast<uint32_t>(c) / (8 * NS);                                                    \
     if (max_seg < 1) max_seg = 1;                                                                              \
     if (max_seg > 16) max_seg = 16;                                                                            \
@@ -803,12 +799,8 @@ inline void ChannelUnpoolLaunch(float *dst, const float *src, const float *poole
 #define MSHADOW_B200_CHUNPOOL_LAUNCH_(NS, LANES)                                                               \
   {                                                                                                            \
     auto kernel = ChannelUnpoolKernel<Reducer, NS, LANES>;                                                     \
-    static uint32_t slots = 0; /* resident CTAs of this instantiation */                                      \
-    if (slots == 0) {                                                                                          \
-      int per_sm = 0;                                                                                          \
-      MSHADOW_CUDA_CALL(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, kPoolThreads, 0));      \
-      slots = static_cast<uint32_t>(per_sm < 1 ? 1 : per_sm) * gpu_rt::CurrentDevice().sm_count;               \
-    }                                                                                                          \
+    const uint32_t slots = static_cast<uint32_t>(gpu_rt::ResidentPerSM(kernel, kPoolThreads)) *               \
+                           gpu_rt::CurrentDevice().sm_count;                                                   \
     /* channel segments that fill whole waves; each re-reads NS-1 halo channels of two tensors */            \
     uint32_t max_seg = static_cast<uint32_t>(c) / (8 * NS);                                                    \
     if (max_seg < 1) max_seg = 1;                                                                              \

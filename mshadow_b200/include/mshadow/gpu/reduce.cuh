@@ -440,10 +440,8 @@ inline Split PlanKeepLowest(uint32_t rows, uint32_t col_tiles, uint32_t slots) {
 /*! \brief CTAs of `kernel` that the current device keeps resident at once */
 template <typename Kernel>
 inline uint32_t ResidentCtas(Kernel kernel, int threads) {
-  int per_sm = 0;
-  MSHADOW_CUDA_CALL(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, threads, 0));
-  if (per_sm < 1) per_sm = 1;
-  return static_cast<uint32_t>(per_sm) * static_cast<uint32_t>(gpu_rt::CurrentDevice().sm_count);
+  return static_cast<uint32_t>(gpu_rt::ResidentPerSM(kernel, threads)) *
+         static_cast<uint32_t>(gpu_rt::CurrentDevice().sm_count);
 }
 }  // namespace reddetail
 
@@ -454,8 +452,7 @@ inline void ReduceKeepLowestLaunch(DPlan dplan, const SPlan &splan, Shape<2> esh
   const uint32_t rows = eshape[0], cols = eshape[1];
   const uint32_t col_tiles = gpu_rt::CeilDiv(cols, kRedLowThreads * kLanes);
   auto kernel = ReduceKeepLowestKernel<Saver, Reducer, kLanes, DType, DPlan, SPlan>;
-  static uint32_t slots = 0;  // per instantiation; the engine targets one device model
-  if (slots == 0) slots = reddetail::ResidentCtas(kernel, kRedLowThreads);
+  const uint32_t slots = reddetail::ResidentCtas(kernel, kRedLowThreads);
   const reddetail::Split sp = reddetail::PlanKeepLowest(rows, col_tiles, slots);
   DType *partial = nullptr;
   if (sp.clusters > 1) {
@@ -481,8 +478,7 @@ inline void ReduceKeepHighDimLaunch(DPlan dplan, const SPlan &splan, Shape<4> ps
   const uint32_t ppr = width / kLanes;
   auto kernel = ReduceKeepHighDimKernel<Saver, Reducer, kLanes, DType, DPlan, SPlan>;
   // whole waves of resident CTAs; at most 64 chunks, each at least one outer index
-  static uint32_t slots = 0;  // per instantiation; the engine targets one device model
-  if (slots == 0) slots = reddetail::ResidentCtas(kernel, kRedHighThreads);
+  const uint32_t slots = reddetail::ResidentCtas(kernel, kRedHighThreads);
   const reddetail::Split sp = reddetail::PlanSplitWaves(outer, channels, slots, 64);
   DType *partial = nullptr;
   if (sp.clusters > 1) {

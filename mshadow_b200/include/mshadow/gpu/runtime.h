@@ -98,17 +98,20 @@ inline const DeviceInfo &CurrentDevice() {
 }
 
 /*!
- * \brief scratch buffers, one per (device, stream), grown on demand and never shrunk.
+ * \brief scratch buffers, one per (device, stream, owner), grown on demand and never shrunk.
  *  Work that uses a buffer is ordered on its stream, so one buffer per stream is race-free;
- *  growing synchronises that stream before the old buffer is released.
+ *  growing synchronises that stream before the old buffer is released.  The engine's own
+ *  operators use owner kEngine; a buffer handed out to a caller (owner kCaller) is a different
+ *  one, so that no later operator on the stream overwrites or reallocates it.
  */
 class Scratch {
  public:
-  static void *Get(cudaStream_t stream, size_t bytes) {
+  enum Owner { kEngine = 0, kCaller = 1 };
+  static void *Get(cudaStream_t stream, size_t bytes, Owner owner = kEngine) {
     int dev = 0;
     MSHADOW_CUDA_CALL(cudaGetDevice(&dev));
     std::lock_guard<std::mutex> lock(Mutex());
-    Slot &slot = Table()[std::make_pair(dev, stream)];
+    Slot &slot = Table()[Key(dev, stream, owner)];
     if (slot.bytes < bytes) {
       if (slot.ptr != nullptr) {
         MSHADOW_CUDA_CALL(cudaStreamSynchronize(stream));
@@ -123,6 +126,14 @@ class Scratch {
     }
     return slot.ptr;
   }
+  /*! \brief bytes currently held for (current device, stream, owner); 0 if none */
+  static size_t Held(cudaStream_t stream, Owner owner = kEngine) {
+    int dev = 0;
+    MSHADOW_CUDA_CALL(cudaGetDevice(&dev));
+    std::lock_guard<std::mutex> lock(Mutex());
+    auto it = Table().find(Key(dev, stream, owner));
+    return it == Table().end() ? 0 : it->second.bytes;
+  }
   /*! \brief release the buffers of one stream on the current device (stream == all: every buffer) */
   static void Release(bool all, cudaStream_t stream) {
     int dev = 0;
@@ -130,11 +141,11 @@ class Scratch {
     std::lock_guard<std::mutex> lock(Mutex());
     auto &table = Table();
     for (auto it = table.begin(); it != table.end();) {
-      if (all || (it->first.first == dev && it->first.second == stream)) {
+      if (all || (it->first.dev == dev && it->first.stream == stream)) {
         if (it->second.ptr != nullptr) {
           int cur = 0;
           cudaGetDevice(&cur);
-          cudaSetDevice(it->first.first);
+          cudaSetDevice(it->first.dev);
           cudaFree(it->second.ptr);
           cudaSetDevice(cur);
         }
@@ -150,12 +161,23 @@ class Scratch {
     void *ptr = nullptr;
     size_t bytes = 0;
   };
+  struct Key {
+    int dev;
+    cudaStream_t stream;
+    int owner;
+    Key(int d, cudaStream_t s, int o) : dev(d), stream(s), owner(o) {}
+    bool operator<(const Key &b) const {
+      if (dev != b.dev) return dev < b.dev;
+      if (stream != b.stream) return stream < b.stream;
+      return owner < b.owner;
+    }
+  };
   static std::mutex &Mutex() {
     static std::mutex mu;
     return mu;
   }
-  static std::map<std::pair<int, cudaStream_t>, Slot> &Table() {
-    static std::map<std::pair<int, cudaStream_t>, Slot> table;
+  static std::map<Key, Slot> &Table() {
+    static std::map<Key, Slot> table;
     return table;
   }
 };
@@ -200,6 +222,42 @@ inline int *StatusWord() {
   }
   return it->second;
 }
+
+/*!
+ * \brief one page-locked int per host thread, into which msb-style waits copy the device's status
+ *  word on the stream they wait for; allocated on the thread's first use, lives as long as the process
+ */
+inline int *StatusMirror() {
+  thread_local int *mirror = nullptr;
+  if (mirror == nullptr) {
+    MSHADOW_CUDA_CALL(cudaHostAlloc(reinterpret_cast<void **>(&mirror), sizeof(int), cudaHostAllocPortable));
+  }
+  return mirror;
+}
+
+#ifdef __CUDACC__
+/*!
+ * \brief CTAs of `kernel` (with `threads` threads and `smem` bytes of dynamic shared memory) that
+ *  one SM of the current device keeps resident; at least 1.  Looked up once per (device, kernel)
+ *  and kept under a lock, so that host threads driving different devices can share the library.
+ */
+template <typename Kernel>
+inline int ResidentPerSM(Kernel kernel, int threads, size_t smem = 0) {
+  static std::mutex mu;
+  static std::map<std::pair<int, const void *>, int> cache;
+  int dev = 0;
+  MSHADOW_CUDA_CALL(cudaGetDevice(&dev));
+  const std::pair<int, const void *> key(dev, reinterpret_cast<const void *>(kernel));
+  std::lock_guard<std::mutex> lock(mu);
+  auto it = cache.find(key);
+  if (it == cache.end()) {
+    int per_sm = 0;
+    MSHADOW_CUDA_CALL(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, threads, smem));
+    it = cache.insert(std::make_pair(key, per_sm < 1 ? 1 : per_sm)).first;
+  }
+  return it->second;
+}
+#endif
 
 /*! \brief exact division of an index by a divisor fixed per launch, without a divide instruction */
 typedef expr::FastDiv FastDiv;

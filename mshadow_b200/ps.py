@@ -16,6 +16,9 @@ vp, i64, cint = C.c_void_p, C.c_int64, C.c_int
 _SIGNATURES = {
     "msb_ps_new_unique_id": [C.c_char_p, i64],
     "msb_ps_create": [cint, cint, C.c_char_p, cint, C.POINTER(vp)],
+    "msb_ps_peer_create": [cint, cint, cint, i64, cint, cint, C.POINTER(vp)],
+    "msb_ps_peer_handle": [vp, C.c_char_p, i64],
+    "msb_ps_peer_connect": [vp, C.c_char_p],
     "msb_ps_destroy": [vp],
     "msb_ps_init_key": [vp, cint, i64, i64],
     "msb_ps_push": [vp, vp, i64, i64, i64, cint, vp],
@@ -81,6 +84,10 @@ class SharedModel:
         self.handle = vp()
         uid = unique_id.encode("ascii") if unique_id is not None else None
         _check(dll().msb_ps_create(rank, world, uid, device, C.byref(self.handle)))
+        self._after_create()
+
+    def _after_create(self):
+        pass
 
     def close(self):
         if self.handle:
@@ -112,3 +119,27 @@ class SharedModel:
     def check_weight(self, tensor, key, stream=None):
         p, rows, cols, ld = _mat(tensor)
         _check(dll().msb_ps_check_weight(self.handle, p, rows, cols, ld, key, stream))
+
+
+class PeerModel(SharedModel):
+    """The peer-store model (mshadow::ps::PeerModel): same calls as SharedModel; the sum of a small
+    tensor is formed from direct stores into every GPU's window over NVLink, in rank order.
+
+    Set-up takes two steps because the ranks must learn each other's windows: create the model on
+    every rank, gather `handle()` of all ranks in rank order (any transport), `connect(handles)`."""
+
+    def __init__(self, rank=0, world=1, device=0, window_bytes=0, depth=0, wait_limit_ms=0):
+        self.handle = vp()
+        self.world = world
+        _check(dll().msb_ps_peer_create(rank, world, device, window_bytes, depth, wait_limit_ms,
+                                        C.byref(self.handle)))
+
+    def export_handle(self):
+        buf = C.create_string_buffer(200)
+        _check(dll().msb_ps_peer_handle(self.handle, buf, 200))
+        return buf.value.decode("ascii")
+
+    def connect(self, handles):
+        """`handles`: the export_handle() strings of all ranks, in rank order."""
+        assert len(handles) == self.world
+        _check(dll().msb_ps_peer_connect(self.handle, "".join(handles).encode("ascii")))

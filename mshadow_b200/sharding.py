@@ -69,6 +69,18 @@ def route_cyclic_with_hot_rows(sorted_keys, order, num_sources, rank, world, hot
     return tail_keys, tail_order, hot_keys, hot_order
 
 
+def rank_order_sum(parts):
+    """What the peer-store exchange (mshadow::ps::PeerModel) hands to every rank: the ranks'
+    contributions added one after the other in rank order, ((p0 + p1) + p2) + ..., each addition
+    rounded to the element type.  `parts` is a sequence of equally shaped numpy arrays, one per
+    rank.  Because every rank adds the same values in the same order, all ranks hold the same bits.
+    """
+    total = np.array(parts[0], copy=True)
+    for part in parts[1:]:
+        total = (total + part).astype(total.dtype)
+    return total
+
+
 def allreduce_sum(tensor):
     """In-place sum over all ranks of the default process group (NCCL on GPUs, gloo on CPU)."""
     import torch.distributed as dist

@@ -840,3 +840,11 @@ int ORC(num_threads)(void) {
   return 1;
 #endif
 }
+
+void ORC(set_num_threads)(int n) {
+#ifdef _OPENMP
+  if (n >= 1) omp_set_num_threads(n);
+#else
+  (void)n;
+#endif
+}

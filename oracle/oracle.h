@@ -228,6 +228,9 @@ void ORC(complex_case)(int id, float *dst, const float *A, const float *B, int64
 
 /* number of OpenMP threads the library will use (for cpu_baseline.cores) */
 int ORC(num_threads)(void);
+/* sets the number of OpenMP threads of later calls (n < 1: leave unchanged); a launcher may have
+ * exported OMP_NUM_THREADS=1 into the environment before this library was loaded */
+void ORC(set_num_threads)(int n);
 
 #ifdef __cplusplus
 }

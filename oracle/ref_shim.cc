@@ -451,4 +451,12 @@ int ref_num_threads(void) {
 #endif
 }
 
+void ref_set_num_threads(int n) {
+#ifdef _OPENMP
+  if (n >= 1) omp_set_num_threads(n);
+#else
+  (void)n;
+#endif
+}
+
 }  // extern "C"

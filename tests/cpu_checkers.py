@@ -52,6 +52,13 @@ class Checker:
     def num_threads(self):
         return int(self.lib[self.p + "num_threads"]())
 
+    def set_num_threads(self, n):
+        """OpenMP threads of later calls; overrides an OMP_NUM_THREADS that a launcher exported."""
+        f = self.lib[self.p + "set_num_threads"]
+        f.restype = None
+        f(C.c_int(int(n)))
+        return self.num_threads()
+
     # ---- elementwise -------------------------------------------------------------
     def expr_case(self, cid, dst, A, B, Cm, bias):
         rows, cols = dst.shape

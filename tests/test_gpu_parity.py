@@ -582,3 +582,28 @@ def test_memory_and_streams(lib):
     lib.free_host(hbuf)
     lib.free_space(p)
     lib.free_space(q)
+
+
+def test_workspace_survives_operators_on_the_same_stream(lib):
+    """The buffer msb_workspace hands out belongs to the caller: a column sum large enough to park
+    partial rows in the engine's own scratch (and, the first time, to allocate that scratch) on the
+    same stream must neither overwrite nor move it."""
+    s = lib.stream_create()
+    n = 1 << 16
+    w = lib.workspace(4 * n, stream=s)
+    assert w and lib.workspace(4 * n, stream=s) == w and lib.workspace(64, stream=s) == w
+    pattern = torch.arange(n, dtype=torch.float32, device="cuda")
+    lib.copy_2d(w, n, pattern, n, 1, n, 3, stream=s)
+    rng = np.random.default_rng(12)
+    M = rng.integers(-8, 9, (40000, 2048)).astype(np.float32)  # small integers: every sum is exact
+    got = lib.reduce_keep_lowest(torch.zeros(2048, device="cuda"), dev(M), stream=s)
+    idx = rng.integers(0, 300, 5000).astype(np.int32)
+    lib.addtakegrad(torch.zeros(300, 64, device="cuda"), dev(idx), dev(rng.standard_normal((5000, 64)).astype(np.float32)),
+                    stream=s)
+    back = torch.zeros(n, device="cuda")
+    lib.copy_2d(back, n, w, n, 1, n, 3, stream=s)
+    lib.stream_wait(s)
+    assert torch.equal(back, pattern)
+    assert_bits(host(got), M.sum(axis=0, dtype=np.float64).astype(np.float32))
+    assert lib.workspace(4 * n, stream=s) == w
+    lib.stream_destroy(s)

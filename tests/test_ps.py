@@ -1,4 +1,5 @@
-"""The multi-GPU synchronisation model (mshadow-ps interface over NCCL all-reduce).
+"""The multi-GPU synchronisation models (mshadow-ps interface): NCCL all-reduce, and direct
+peer stores over NVLink for small tensors.
 
 Without a GPU: the library loads, exports what include/mshadow_b200_ps.h declares and validates
 arguments.  With one GPU: a group of one process exercises the stream ordering, pitched tensors,
@@ -36,6 +37,10 @@ def test_ps_argument_errors_need_no_gpu():
     buf = C.create_string_buffer(8)
     assert ps.dll().msb_ps_new_unique_id(buf, 8) != 0
     assert ps.dll().msb_ps_pull_wait(None, 0) != 0
+    with pytest.raises(ps.PsError, match="rank outside"):
+        ps.PeerModel(rank=3, world=2)
+    assert ps.dll().msb_ps_peer_handle(None, buf, 8) != 0
+    assert ps.dll().msb_ps_peer_connect(None, b"00") != 0
 
 
 @pytest.mark.gpu
@@ -130,5 +135,190 @@ def test_two_processes_sum_over_nvlink(tmp_path):
     import torch.multiprocessing as mp
     world = 2
     mp.spawn(_worker, args=(world, str(tmp_path / "nccl_id"), str(tmp_path)), nprocs=world, join=True)
+    for r in range(world):
+        assert open(tmp_path / ("rank%d.txt" % r)).read() == "1"
+
+
+# ---- the peer-store model --------------------------------------------------------------------
+@pytest.mark.gpu
+def test_peer_model_alone_on_one_gpu_runs_its_kernels_and_slot_rotation():
+    """A group of one: the contribution goes through the window of this GPU (push kernel, flags,
+    pull kernel), step after step, so slots are reused several times; the sum of one is the data."""
+    if not torch.cuda.is_available():
+        pytest.skip("no CUDA device")
+    m = ps.PeerModel(rank=0, world=1, device=0, depth=4)
+    try:
+        m.init_key(0, (4608,))
+        m.init_key(1, (7, 33))            # odd sizes: element-wise path
+        m.init_key(2, (64, 1024))         # several CTAs per peer: ticket counter decides who publishes
+        g = torch.Generator(device="cuda")
+        g.manual_seed(5)
+        for step in range(11):
+            a = torch.randn(4608, device="cuda", generator=g)
+            out = torch.full((4608,), -7.0, device="cuda")
+            m.push(a, 0)
+            if step % 2:                  # one step pushed ahead of its pull is allowed with depth 4
+                b = torch.randn(4608, device="cuda", generator=g)
+                m.push(b, 0)
+                m.pull_req(out, 0)
+                m.pull_wait(0)
+                assert torch.equal(out, a)
+                m.pull_req(out, 0)
+                m.pull_wait(0)
+                assert torch.equal(out, b)
+            else:
+                m.pull_req(out, 0)
+                m.pull_wait(0)
+                assert torch.equal(out, a)
+            wide = torch.full((7, 40), -1.0, device="cuda")
+            view = wide[:, :33]
+            c = torch.randn(7, 33, device="cuda", generator=g)
+            view.copy_(c)
+            m.push(view, 1)               # rows 40 floats apart
+            m.pull_req(view, 1)
+            m.pull_wait(1)
+            assert torch.equal(view, c) and bool((wide[:, 33:] == -1.0).all())
+            d = torch.randn(64, 1024, device="cuda", generator=g)
+            o2 = torch.zeros_like(d)
+            m.push(d, 2)
+            m.pull_req(o2, 2)
+            m.pull_wait(2)
+            assert torch.equal(o2, d)
+        w = torch.randn(7, 33, device="cuda", generator=g)
+        keep = w.clone()
+        m.set_weight(w, 1)
+        m.check_weight(w, 1)
+        assert torch.equal(w, keep)
+        with pytest.raises(ps.PsError, match="shape differs"):
+            m.push(w, 0)
+        with pytest.raises(ps.PsError, match="nothing pushed"):
+            m.pull_req(torch.zeros(4608, device="cuda"), 0)
+        m.push(torch.zeros(4608, device="cuda"), 0)
+        m.push(torch.zeros(4608, device="cuda"), 0)
+        with pytest.raises(ps.PsError, match="too many steps"):
+            m.push(torch.zeros(4608, device="cuda"), 0)
+    finally:
+        torch.cuda.synchronize()
+        m.close()
+
+
+@pytest.mark.gpu
+def test_peer_model_pull_gives_up_when_a_peer_never_answers():
+    """A group of two whose second member does not exist: both handles name this rank's window, so
+    the flag of rank 1 is never set.  The pull kernel polls for the configured 30 ms, leaves the
+    destination alone and records a status; pull_wait reports it; the GPU carries on."""
+    if not torch.cuda.is_available():
+        pytest.skip("no CUDA device")
+    m = ps.PeerModel(rank=0, world=2, device=0, wait_limit_ms=30)
+    try:
+        h = m.export_handle()
+        assert len(h) == 128
+        m.connect([h, h])
+        m.init_key(0, (512,))
+        a = torch.ones(512, device="cuda")
+        out = torch.full((512,), 3.0, device="cuda")
+        m.push(a, 0)
+        m.pull_req(out, 0)
+        t0 = time.time()
+        with pytest.raises(ps.PsError, match="timeout"):
+            m.pull_wait(0)
+        assert time.time() - t0 < 5.0
+        assert bool((out == 3.0).all())
+        m.pull_wait(0)                    # the mark is cleared once reported
+        assert float((a + 1).sum().item()) == 1024.0
+    finally:
+        torch.cuda.synchronize()
+        m.close()
+
+
+def _exchange_handles(rank, world, handle, tmp):
+    with open(os.path.join(tmp, "h%d.tmp" % rank), "w") as f:
+        f.write(handle)
+    os.replace(os.path.join(tmp, "h%d.tmp" % rank), os.path.join(tmp, "h%d" % rank))
+    deadline = time.time() + 120
+    out = []
+    for r in range(world):
+        path = os.path.join(tmp, "h%d" % r)
+        while not os.path.exists(path):
+            if time.time() > deadline:
+                raise RuntimeError("no handle from rank %d" % r)
+            time.sleep(0.02)
+        out.append(open(path).read())
+    return out
+
+
+def _file_barrier(rank, world, tmp, name):
+    open(os.path.join(tmp, "%s.%d" % (name, rank)), "w").close()
+    deadline = time.time() + 120
+    while not all(os.path.exists(os.path.join(tmp, "%s.%d" % (name, r))) for r in range(world)):
+        if time.time() > deadline:
+            raise RuntimeError("barrier %s" % name)
+        time.sleep(0.02)
+
+
+def _peer_worker(rank, world, tmp):
+    from mshadow_b200 import sharding
+    torch.cuda.set_device(rank)
+    m = ps.PeerModel(rank=rank, world=world, device=rank, depth=4, wait_limit_ms=20000)
+    m.connect(_exchange_handles(rank, world, m.export_handle(), tmp))
+    m.init_key(0, (4608,))
+    m.init_key(1, (64, 1024))
+    ok = True
+
+    def data(r, step, shape):
+        g = torch.Generator()
+        g.manual_seed(1000 * step + r)
+        return torch.randn(shape, generator=g)
+
+    def want(step, shape):
+        return torch.from_numpy(sharding.rank_order_sum([data(r, step, shape).numpy() for r in range(world)]))
+
+    # steady state of a training loop: push step s + 1, then pull step s; ranks drift apart on purpose
+    steps = 40
+    outs = []
+    mine = [data(rank, s, (4608,)).cuda() for s in range(steps)]
+    m.push(mine[0], 0)
+    for s in range(steps):
+        if (s + rank) % 3 == 0:
+            torch.cuda._sleep(2000000)   # about a millisecond of delay on this rank's stream
+        if s + 1 < steps:
+            m.push(mine[s + 1], 0)
+        out = torch.zeros(4608, device="cuda")
+        m.pull_req(out, 0)
+        outs.append(out)
+    m.pull_wait(0)
+    for s in range(steps):
+        ok = ok and torch.equal(outs[s].cpu(), want(s, (4608,)))
+    # a larger tensor (several CTAs per peer), push and pull in turn
+    for s in range(6):
+        big = data(rank, 100 + s, (64, 1024)).cuda()
+        m.push(big, 1)
+        m.pull_req(big, 1)
+        m.pull_wait(1)
+        ok = ok and torch.equal(big.cpu(), want(100 + s, (64, 1024)))
+    w = torch.full((64, 1024), float(rank + 5), device="cuda")
+    m.set_weight(w, 1)
+    ok = ok and bool((w == 5.0).all())
+    m.check_weight(w, 1)
+    try:
+        m.check_weight(w + rank, 1)
+        caught = False
+    except ps.PsError:
+        caught = True
+    ok = ok and (caught == (rank != 0))
+    torch.cuda.synchronize()
+    _file_barrier(rank, world, tmp, "done")   # nobody frees a window that a peer may still write
+    m.close()
+    with open(os.path.join(tmp, "rank%d.txt" % rank), "w") as f:
+        f.write("1" if ok else "0")
+
+
+@pytest.mark.gpu
+def test_two_processes_exchange_by_peer_stores(tmp_path):
+    if not torch.cuda.is_available() or torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    import torch.multiprocessing as mp
+    world = 2
+    mp.spawn(_peer_worker, args=(world, str(tmp_path)), nprocs=world, join=True)
     for r in range(world):
         assert open(tmp_path / ("rank%d.txt" % r)).read() == "1"

@@ -31,8 +31,17 @@ def _worker(rank, world, port, tmpdir):
     full = orc.reduce_keep_highdim(np.zeros(6, np.float32), T)
     b, e = sharding.shard_range(T.shape[0], rank, world)
     part = orc.reduce_keep_highdim(np.zeros(6, np.float32), np.ascontiguousarray(T[b:e]))
-    total = sharding.allreduce_sum(torch.from_numpy(part)).numpy()
+    total = sharding.allreduce_sum(torch.from_numpy(part.copy())).numpy()
     ok_red = bool(np.allclose(total, full, rtol=1e-5, atol=1e-5 * np.sqrt(np.mean(full ** 2))))
+    # the peer-store exchange: every rank gathers all partial vectors and adds them in rank order,
+    # so the ranks agree bit for bit and stay within tolerance of the unsharded sum
+    gathered = [torch.zeros(6) for _ in range(world)]
+    dist.all_gather(gathered, torch.from_numpy(part))
+    ordered = sharding.rank_order_sum([g.numpy() for g in gathered])
+    theirs = [torch.zeros(6) for _ in range(world)]
+    dist.all_gather(theirs, torch.from_numpy(ordered))
+    ok_red = ok_red and all(np.array_equal(t.numpy().view(np.uint32), ordered.view(np.uint32)) for t in theirs)
+    ok_red = ok_red and bool(np.allclose(ordered, full, rtol=1e-5, atol=1e-5 * np.sqrt(np.mean(full ** 2))))
 
     k, d, n = 23, 12, 400
     idx = rng.integers(0, k, n).astype(np.int32)
