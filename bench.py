@@ -556,12 +556,13 @@ def kernel_table(lib, torch, peak, only=None, small=False, iters=None, warm=None
 # --------------------------------------------------------------------------------------
 # exchange of per-rank results (N > 1)
 # --------------------------------------------------------------------------------------
-def make_peer_model(dist, rank, world, local_rank):
+def make_peer_model(dist, rank, world, local_rank, own_stream=False):
     """mshadow::ps::PeerModel of this rank, connected to the others: key 0 carries the headline's
     4608 result floats, key 1 the 512 channel sums of the strong-scaling case, key 2 the partial
-    sums of the embedding table's hot rows.  The window handles travel through torch.distributed."""
+    sums of the embedding table's hot rows.  The window handles travel through torch.distributed.
+    own_stream: the model's kernels run on a stream of its own, beside the caller's."""
     from mshadow_b200 import ps
-    m = ps.PeerModel(rank=rank, world=world, device=local_rank, depth=4, wait_limit_ms=20000)
+    m = ps.PeerModel(rank=rank, world=world, device=local_rank, depth=4, wait_limit_ms=20000, own_stream=own_stream)
     if world > 1:
         handles = [None] * world
         dist.all_gather_object(handles, m.export_handle())
@@ -583,13 +584,22 @@ def gather_floats(torch, dist, dev, values):
 
 
 class Lagged:
-    """Push of step i, then pull of step i - 1: the wait for the peers hides behind a step's kernels."""
+    """Delivery of step i, then pull of step i - 1: the wait for the peers hides behind a step's
+    kernels.  The delivery is either a push kernel (step) or done by the reduction kernels
+    themselves through sinks (sinks, then delivered)."""
 
     def __init__(self, peer, key):
         self.peer, self.key, self.outstanding = peer, key, 0
 
     def step(self, src, dst):
         self.peer.push(src, self.key)
+        self.delivered(dst)
+
+    def sinks(self, *segments):
+        """One sink per (offset, count) segment of the step that the first segment opens."""
+        return [self.peer.next_sink(self.key, off, cnt) for off, cnt in segments]
+
+    def delivered(self, dst):
         self.outstanding += 1
         if self.outstanding > 1:
             self.peer.pull_req(dst, self.key)
@@ -602,8 +612,8 @@ class Lagged:
         self.peer.pull_wait(self.key)
 
 
-def exchange_variants(torch, lib, dist, peer, dev, T, M, outs, sums, steps):
-    """The headline step with four ways of combining the ranks' 4608 results, `steps` steps each,
+def exchange_variants(torch, lib, dist, peer, peer_side, dev, T, M, outs, sums, steps):
+    """The headline step with five ways of combining the ranks' 4608 results, `steps` steps each,
     CUDA events around every kernel: which exchange costs what, and what it does to the column sum
     that runs beside it.  Times are the maximum over the ranks."""
     o512s = [o[:C2A_SHAPE[1]] for o in outs]
@@ -614,9 +624,13 @@ def exchange_variants(torch, lib, dist, peer, dev, T, M, outs, sums, steps):
     def peer_lagged(j):
         lag.step(outs[j], sums[j ^ 1])
 
-    def peer_direct(j):
-        peer.push(outs[j], 0)
-        peer.pull_req(sums[j], 0)
+    lag_side = Lagged(peer_side, 0)
+
+    def peer_side_stream(j):
+        # the fence names the pull issued one step ago (step i - 2): behind it the buffers of step
+        # i + 1 are free, and nothing this step's push or pull does can hold up the main stream
+        peer_side.pull_fence(0)
+        lag_side.step(outs[j], sums[j ^ 1])
 
     def nccl_blocking(j):
         dist.all_reduce(outs[j])
@@ -633,16 +647,30 @@ def exchange_variants(torch, lib, dist, peer, dev, T, M, outs, sums, steps):
         before(0)
         before(1)
         lag.drain(sums[0])
-        peer.pull_wait(0)
+        lag_side.drain(sums[0])
+
+    def fused_lagged(j):
+        lag.delivered(sums[j ^ 1])
 
     result = {}
-    for name, combine in (("peer_stores_pull_lagging_one_step", peer_lagged), ("peer_stores_pull_at_once", peer_direct),
+    for name, combine in (("push_and_pull_kernels_on_the_models_own_stream", peer_side_stream),
+                          ("sinks_in_the_reductions_pull_lagging_one_step", fused_lagged),
+                          ("push_kernel_pull_lagging_one_step", peer_lagged),
                           ("nccl_allreduce_blocking", nccl_blocking), ("nccl_allreduce_overlapped", nccl_overlapped)):
-        def one(i):
+        fused = combine is fused_lagged
+
+        def one(i, ev=None):
             j = i & 1
             before(j)
-            lib.reduce_keep_highdim(o512s[j], T)
-            lib.reduce_keep_lowest(o4096s[j], M)
+            s_hi, s_lo = lag.sinks((0, C2A_SHAPE[1]), (C2A_SHAPE[1], C2B_SHAPE[1])) if fused else (None, None)
+            if ev is not None:
+                ev[0].record()
+            lib.reduce_keep_highdim(o512s[j], T, sink=s_hi)
+            if ev is not None:
+                ev[1].record()
+            lib.reduce_keep_lowest(o4096s[j], M, sink=s_lo)
+            if ev is not None:
+                ev[2].record()
             combine(j)
         for i in range(6):
             one(i)
@@ -653,14 +681,7 @@ def exchange_variants(torch, lib, dist, peer, dev, T, M, outs, sums, steps):
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record()
         for i in range(steps):
-            j = i & 1
-            before(j)
-            ev[i][0].record()
-            lib.reduce_keep_highdim(o512s[j], T)
-            ev[i][1].record()
-            lib.reduce_keep_lowest(o4096s[j], M)
-            ev[i][2].record()
-            combine(j)
+            one(i, ev[i])
         finish()
         e1.record()
         torch.cuda.synchronize()
@@ -730,7 +751,7 @@ def make_cyclic_hot_step(torch, lib, dist, peer, keys, order, src, rank, world, 
     return step, shard, info
 
 
-def sharded_block(args, torch, lib, dist, peer, rank, world, dev, peak):
+def sharded_block(args, torch, lib, dist, peer, peer_side, rank, world, dev, peak):
     """Every BASELINE tensor split on its leading dimension over the ranks (strong scaling: the total
     work is that of one GPU's config), inputs resident per rank before timing, launches back to
     back, time = the slowest rank.  A shard that would fit the 126 MB L2 is rotated through several
@@ -813,19 +834,35 @@ def sharded_block(args, torch, lib, dist, peer, rank, world, dev, peak):
     Ts = [torch.randn(imgs, 512, 28, 28, device=dev, generator=g) for _ in range(R)]
     part = [torch.zeros(512, device=dev) for _ in range(2)]
     total = [torch.zeros(512, device=dev) for _ in range(2)]
-    lag = Lagged(peer, 1) if world > 1 else None
+    lag = Lagged(peer_side, 1) if world > 1 else None
 
     def c2a(i):
+        # the reduction on the main stream; push of its 512 results and pull of the previous step's
+        # sum on the exchange model's own stream (the fence before them names the pull of step i - 2)
         j = i & 1
         lib.reduce_keep_highdim(part[j], Ts[i % R])
         if lag is not None:
+            peer_side.pull_fence(1)
             lag.step(part[j], total[j ^ 1])
 
     ms = timed(c2a, 200)
     if lag is not None:
         lag.drain(total[0])
     entry("C2a_sumall_except_dim", ms, 256 * 512 * 28 * 28, nb, R,
-          {"exchange": "512 floats per step by peer stores, pull lagging one step" if world > 1 else "none"})
+          {"exchange": "512 floats per step: push and pull kernels on the exchange model's own stream, pull lagging "
+                       "one step" if world > 1 else "none"})
+    if world > 1:
+        # the same with the reduction kernel delivering its results itself (sink) and the pull in-stream
+        lag2 = Lagged(peer, 1)
+
+        def c2a_sink(i):
+            j = i & 1
+            lib.reduce_keep_highdim(part[j], Ts[i % R], sink=lag2.sinks((0, 512))[0])
+            lag2.delivered(total[j ^ 1])
+
+        ms2 = timed(c2a_sink, 200)
+        lag2.drain(total[0])
+        out["C2a_sumall_except_dim"]["ms_with_sink_in_the_kernel_and_pull_in_stream"] = round(ms2, 5)
     if world > 1:
         # correctness of the exchange: the pulled sum equals the rank-order sum of the ranks' partials
         lib.reduce_keep_highdim(part[0], Ts[0])
@@ -1216,15 +1253,23 @@ def main():
     # the ranks' results are combined by peer stores; NCCL (through torch.distributed) carries the
     # barriers, the max-over-ranks of the timings and the window handles
     peer = make_peer_model(dist, rank, world, local_rank) if world > 1 else None
+    peer_side = make_peer_model(dist, rank, world, local_rank, own_stream=True) if world > 1 else None
     if args.workload == "embed_sharded":
         embed_sharded_arm(args, torch, lib, dist, peer, rank, world, dev)
         if dist is not None:
             dist.barrier()
             peer.close()
+            peer_side.close()
             dist.destroy_process_group()
         return
 
+    # The strong-scaling block and (N > 1) the comparison of exchange schemes run first: they are
+    # part of the job anyway, and the headline's short timed region then starts on a GPU that has
+    # been busy for a while instead of one that idled through the host-side set-up.
     (p4, h4), (pm, hm) = make_host_inputs(lib, rank)
+    sharded = None
+    if not args.no_sharded:
+        sharded = sharded_block(args, torch, lib, dist, peer, peer_side, rank, world, dev, peak)
     T = torch.empty(C2A_SHAPE, device=dev)
     M = torch.empty(C2B_SHAPE, device=dev)
     # both results of a step live in one buffer so that one exchange combines them; two buffers
@@ -1237,12 +1282,32 @@ def main():
     lib.copy_2d(T, n4, p4, n4, 1, n4, mshadow_b200.capi.H2D)
     lib.copy_2d(M, nm, pm, nm, 1, nm, mshadow_b200.capi.H2D)
     torch.cuda.synchronize()
-    lag = Lagged(peer, 0) if peer is not None else None
+    variants = None
+    if world > 1 and args.variant_steps > 0:
+        variants = exchange_variants(torch, lib, dist, peer, peer_side, dev, T, M, outs, sums, args.variant_steps)
+    lag = Lagged(peer_side, 0) if peer_side is not None else None
 
-    def combine(i):
-        # push of step i, then the pull of step i - 1 into sums[(i - 1) & 1]
+    def reductions(i, ev=None):
+        """Step i: both reductions into outs[i & 1]; then, on the exchange model's own stream and
+        beside the next step's reductions, the push of the 4608 results into every GPU's window and
+        the pull of step i - 1 (the sum over the ranks) into sums[(i - 1) & 1]."""
+        j = i & 1
+        if ev is not None:
+            ev[0].record()
+        lib.reduce_keep_highdim(o512s[j], T)
+        if ev is not None:
+            ev[1].record()
+        lib.reduce_keep_lowest(o4096s[j], M)
+        if ev is not None:
+            ev[2].record()
         if lag is not None:
-            lag.step(outs[i & 1], sums[(i & 1) ^ 1])
+            # The fence names the most recent pull, that of step i - 2: once it is done, so is the
+            # push that read outs[(i + 1) & 1], which the next step overwrites.  Placed here, before
+            # this step's push and pull are issued, it cannot make the main stream wait for them.
+            peer_side.pull_fence(0)
+            lag.step(outs[j], sums[j ^ 1])
+        if ev is not None:
+            ev[3].record()
 
     def barrier():
         if dist is not None:
@@ -1252,14 +1317,11 @@ def main():
     sampler = ClockSampler(local_rank)
     sampler.start()
     for i in range(args.warmup):
-        lib.reduce_keep_highdim(o512s[i & 1], T)
-        lib.reduce_keep_lowest(o4096s[i & 1], M)
-        combine(i)
+        reductions(i)
     barrier()
 
-    # timed region: events around the whole run and around each kernel of each step.  Every step
-    # issues its two reductions, one push and one pull (the pull of the step before: warm-up left
-    # one push outstanding), so K steps carry K complete exchanges.
+    # timed region: events around the whole run and around each kernel of each step; the end event
+    # follows the last step's pull, so K steps carry K complete exchanges
     k = args.steps
     e_start, e_end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     ev = [[torch.cuda.Event(enable_timing=True) for _ in range(4)] for _ in range(k)]
@@ -1267,18 +1329,13 @@ def main():
     sampler.window[0] = time.perf_counter()
     e_start.record()
     for s in range(k):
-        i = args.warmup + s
-        ev[s][0].record()
-        lib.reduce_keep_highdim(o512s[i & 1], T)
-        ev[s][1].record()
-        lib.reduce_keep_lowest(o4096s[i & 1], M)
-        ev[s][2].record()
-        combine(i)
-        ev[s][3].record()
+        reductions(args.warmup + s, ev[s])
+    if lag is not None:
+        peer_side.pull_fence(0)
     e_end.record()
     barrier()
     sampler.window[1] = time.perf_counter()
-    launches = lib.launch_count() - launches0 + (2 * k if lag is not None else 0)
+    launches = lib.launch_count() - launches0 + (2 * k if lag is not None else 0)  # + push and pull kernels
     if lag is not None:
         lag.drain(sums[(args.warmup + k - 1) & 1])
     seconds = e_start.elapsed_time(e_end) * 1e-3
@@ -1308,9 +1365,10 @@ def main():
         lib.reduce_keep_highdim(o512s[0], T)
         lib.reduce_keep_lowest(o4096s[0], M)
         res = outs[0]
-        if peer is not None:
-            peer.push(outs[0], 0)
-            peer.pull_req(sums[0], 0)
+        if peer_side is not None:
+            peer_side.push(outs[0], 0)
+            peer_side.pull_req(sums[0], 0)
+            peer_side.pull_fence(0)
             res = sums[0]
         lib.copy_2d(res_ptr, NRES, res, NRES, 1, NRES, mshadow_b200.capi.D2H)
         lib.stream_wait(None)
@@ -1330,25 +1388,16 @@ def main():
     e2e_value = ELEMS_PER_STEP * world * ke / e2e_seconds / 1e9
     sampler.stop_flag = True
     sampler.join(timeout=1.0)
-    if peer is not None:
-        peer.pull_wait(0)
+    if peer_side is not None:
+        peer_side.pull_wait(0)
 
-    variants = None
-    if world > 1 and args.variant_steps > 0:
-        variants = exchange_variants(torch, lib, dist, peer, dev, T, M, outs, sums, args.variant_steps)
     g1, g2 = o512s[0].cpu().numpy().copy(), o4096s[0].cpu().numpy().copy()
-    sharded = None
-    if not args.no_sharded:
-        del_T_M = world > 1  # the single-GPU run still needs them for the parity leg
-        if del_T_M:
-            del T, M
-            torch.cuda.empty_cache()
-        sharded = sharded_block(args, torch, lib, dist, peer, rank, world, dev, peak)
 
     if rank != 0:
         if dist is not None:
             dist.barrier()
             peer.close()
+            peer_side.close()
             dist.destroy_process_group()
         return
 
@@ -1361,7 +1410,8 @@ def main():
         "dtype": "f32", "data": "synthetic",
         "config": {"workload": WORKLOAD
                                + ("; the 4608 result floats of every step are stored into every GPU's window over NVLink "
-                                  "and added in rank order (mshadow::ps::PeerModel), the pull lagging one step"
+                                  "and added in rank order by two small kernels on the exchange model's own stream "
+                                  "(mshadow::ps::PeerModel), beside the next step's reductions"
                                   if world > 1 else ""),
                    "l2": "inputs (411 MB and 1074 MB) exceed the 126 MB L2; no flush needed",
                    "inputs": "N(0,1), seeded, generated on the host, resident in HBM before timing"},
@@ -1422,6 +1472,7 @@ def main():
     if dist is not None:
         dist.barrier()
         peer.close()
+        peer_side.close()
         dist.destroy_process_group()
 
 

@@ -30,6 +30,8 @@
 
 #include <stdint.h>
 
+#include "mshadow_b200_peer_sink.h"
+
 #ifdef __cplusplus
 extern "C" {
 #endif
@@ -144,6 +146,18 @@ int msb_reduce_keep_lowest_sum_f32_noalloc(float *dst, const float *src, int64_t
 int msb_reduce_keep_highdim_f32(float *dst, const float *src, int64_t n, int64_t c, int64_t h,
                                 int64_t w, int64_t ld, float scale, int saver, int reducer,
                                 msb_stream_t stream);
+/* The same two reductions with their results also delivered to the other GPUs of an exchange
+   group, from the threads that compute them (no second kernel): see mshadow_b200_peer_sink.h.
+   No counterpart in the reference.  `sink` may be NULL (then they are the calls above); it must
+   expect exactly cols (c) results.  The value delivered is scale * Reduce(...), i.e. what the
+   saver receives, whatever the saver does with dst. */
+int msb_reduce_keep_lowest_f32_sink(float *dst, const float *src, int64_t rows, int64_t cols, int64_t ld,
+                                    float scale, int saver, int reducer, const msb_peer_sink_t *sink,
+                                    msb_stream_t stream);
+int msb_reduce_keep_highdim_f32_sink(float *dst, const float *src, int64_t n, int64_t c, int64_t h, int64_t w,
+                                     int64_t ld, float scale, int saver, int reducer, const msb_peer_sink_t *sink,
+                                     msb_stream_t stream);
+
 
 /* ---- softmax family ----------------------------------------------------------------- */
 

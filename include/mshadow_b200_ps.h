@@ -16,6 +16,8 @@
 
 #include <stdint.h>
 
+#include "mshadow_b200_peer_sink.h"
+
 #ifdef __cplusplus
 extern "C" {
 #endif
@@ -33,26 +35,35 @@ int msb_ps_new_unique_id(char *hex, int64_t capacity);
 int msb_ps_create(int rank, int world, const char *id_hex, int device, msb_ps_t *out);
 int msb_ps_destroy(msb_ps_t model);
 
-/* A second model behind the same interface, for small tensors whose exchange is bound by latency
-   (a few thousand partial sums per step): mshadow::ps::PeerModel.  Push stores the tensor straight
-   into a window of every other GPU's memory over NVLink and raises a flag there; PullReq waits for
-   all flags (at most wait_limit_ms, then msb_ps_pull_wait fails and the destination is left
-   unchanged) and adds the contributions in rank order, so that every rank receives the same bits.
-   It replaces the same LocalModel path (mshadow-ps/ps_local-inl.h:443-461, 625-662, 700-736:
-   device -> host copy, sum on a CPU thread, host -> device copy).
-   window_bytes, depth, wait_limit_ms: 0 selects the defaults (16 MiB, 4 slots, 2000 ms); a key of
-   n floats takes depth * world * n * 4 bytes of the window.  With depth d a rank may push at most
-   d/2 - 1 steps of a key ahead of pulling them.
+/* A second model behind the same interface, for small fp32 tensors whose exchange is bound by
+   latency (a few thousand partial sums per step): mshadow::ps::PeerModel.  Push stores every
+   element, tagged with its step, straight into a window of every GPU's memory over NVLink;
+   PullReq reads the contributions of all ranks as they arrive (waiting at most wait_limit_ms,
+   then msb_ps_pull_wait fails) and adds them in rank order, so that every rank receives the same
+   bits.  It replaces the same LocalModel path (mshadow-ps/ps_local-inl.h:443-461, 625-662,
+   700-736: device -> host copy, sum on a CPU thread, host -> device copy).
+   window_bytes, depth, wait_limit_ms: 0 selects the defaults (64 MiB, 4 slots, 2000 ms); a key of
+   n floats takes depth * world * n * 8 bytes of the window.  With depth d a rank may push at most
+   d/2 - 1 steps of a key ahead of pulling them.  own_stream 0: push and pull kernels run on the
+   stream given with the call; 1: on a stream of the model, ordered behind the given stream by an
+   event at every call, so that the exchange runs beside the caller's next kernels (the caller
+   then leaves a pushed tensor alone until its step has been pulled, and uses msb_ps_pull_wait or
+   msb_ps_pull_fence before touching a result).
    Set-up: every rank creates its model, obtains its handle (128 hexadecimal digits and a
    terminating zero; capacity at least 129), the application gathers the handles of all ranks in
    rank order into one string and gives it to msb_ps_peer_connect on every rank.  world 1 needs no
    connect.  The tensor calls below (init_key, push, pull_req, pull_wait, set_weight, check_weight,
    destroy) serve both models; the application lets all ranks reach a barrier of its own before
-   it destroys a peer model. */
+   it destroys a peer model.
+   msb_ps_peer_next_sink takes the place of msb_ps_push when a reduction kernel delivers the
+   step's data itself: it returns the sink for `count` results starting at element `offset` of
+   the key's row.  The segment at offset 0 opens the step; the segments of a step must cover the
+   whole row before msb_ps_pull_req is called for it. */
 int msb_ps_peer_create(int rank, int world, int device, int64_t window_bytes, int depth, int wait_limit_ms,
-                       msb_ps_t *out);
+                       int own_stream, msb_ps_t *out);
 int msb_ps_peer_handle(msb_ps_t model, char *hex, int64_t capacity);
 int msb_ps_peer_connect(msb_ps_t model, const char *all_handles_hex);
+int msb_ps_peer_next_sink(msb_ps_t model, int key, int64_t offset, int64_t count, msb_peer_sink_t *out);
 
 /* ISharedModel::InitKey(Shape2(rows, cols), key, device) */
 int msb_ps_init_key(msb_ps_t model, int key, int64_t rows, int64_t cols);
@@ -65,6 +76,9 @@ int msb_ps_pull_req(msb_ps_t model, float *data, int64_t rows, int64_t cols, int
                     void *stream);
 /* ISharedModel::PullWait: block the host until the last pull of `key` has completed */
 int msb_ps_pull_wait(msb_ps_t model, int key);
+/* No counterpart in the reference: the device-side form of PullWait.  Work enqueued on `stream`
+   after this call runs after the last pull of `key`; the host does not block. */
+int msb_ps_pull_fence(msb_ps_t model, int key, void *stream);
 /* ISharedModel::SetWeight_: every process's `data` becomes that of rank 0 (synchronous) */
 int msb_ps_set_weight(msb_ps_t model, float *data, int64_t rows, int64_t cols, int64_t ld, int key,
                       void *stream);

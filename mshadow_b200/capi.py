@@ -57,6 +57,8 @@ _SIGNATURES = {
     "msb_reduce_keep_lowest_f32": [vp, vp, i64, i64, i64, f32, cint, cint, vp],
     "msb_reduce_keep_lowest_sum_f32_noalloc": [vp, vp, i64, i64, i64, f32, vp],
     "msb_reduce_keep_highdim_f32": [vp, vp, i64, i64, i64, i64, i64, f32, cint, cint, vp],
+    "msb_reduce_keep_lowest_f32_sink": [vp, vp, i64, i64, i64, f32, cint, cint, vp, vp],
+    "msb_reduce_keep_highdim_f32_sink": [vp, vp, i64, i64, i64, i64, i64, f32, cint, cint, vp, vp],
     "msb_softmax_f32": [vp, vp, i64, i64, i64, i64, vp],
     "msb_softmax_grad_f32": [vp, vp, vp, i64, i64, i64, i64, cint, f32, f32, vp],
     "msb_softmax_grad_fused_f32": [vp, vp, vp, i64, i64, i64, i64, vp],
@@ -181,8 +183,14 @@ class Library:
                   _ld(dst), _ld(A), _ld(B), _ld(Cm), stream)
         return dst
 
-    def reduce_keep_lowest(self, dst, src, scale=1.0, saver=0, reducer=0, stream=None):
+    def reduce_keep_lowest(self, dst, src, scale=1.0, saver=0, reducer=0, stream=None, sink=None):
+        """`sink`: a msb_peer_sink_t (ctypes structure) through which the results also reach the
+        other GPUs of an exchange group."""
         rows, cols = src.shape
+        if sink is not None:
+            self.call("msb_reduce_keep_lowest_f32_sink", _ptr(dst), _ptr(src), rows, cols, _ld(src), scale, saver,
+                      reducer, C.cast(C.pointer(sink), vp), stream)
+            return dst
         self.call("msb_reduce_keep_lowest_f32", _ptr(dst), _ptr(src), rows, cols, _ld(src), scale, saver,
                   reducer, stream)
         return dst
@@ -194,8 +202,12 @@ class Library:
                   stream)
         return dst
 
-    def reduce_keep_highdim(self, dst, src, scale=1.0, saver=0, reducer=0, stream=None):
+    def reduce_keep_highdim(self, dst, src, scale=1.0, saver=0, reducer=0, stream=None, sink=None):
         n, c, h, w = src.shape
+        if sink is not None:
+            self.call("msb_reduce_keep_highdim_f32_sink", _ptr(dst), _ptr(src), n, c, h, w, _ld(src), scale, saver,
+                      reducer, C.cast(C.pointer(sink), vp), stream)
+            return dst
         self.call("msb_reduce_keep_highdim_f32", _ptr(dst), _ptr(src), n, c, h, w, _ld(src), scale, saver,
                   reducer, stream)
         return dst

@@ -312,8 +312,34 @@ int msb_expr_case_f32(int id, float *dst, const float *A, const float *B, const 
   MSB_GUARD_END
 }
 
+static_assert(sizeof(msb_peer_sink_t) == sizeof(gpu_rt::PeerSink) && MSB_PEER_MAX_WORLD == gpu_rt::kPeerMaxWorld,
+              "msb_peer_sink_t must mirror gpu_rt::PeerSink");
+
+/*! \brief the C sink as the engine's; NULL or world 0 gives none */
+static bool ToPeerSink(const msb_peer_sink_t *in, gpu_rt::PeerSink *out) {
+  if (in == nullptr || in->world == 0) return true;
+  if (in->world < 0 || in->world > MSB_PEER_MAX_WORLD) return false;
+  for (int p = 0; p < in->world; ++p) {
+    if (in->row[p] == nullptr) return false;
+    out->row[p] = in->row[p];
+  }
+  out->tag = in->tag;
+  out->count = in->count;
+  out->world = in->world;
+  return true;
+}
+
 int msb_reduce_keep_lowest_f32(float *dst, const float *src, int64_t rows, int64_t cols, int64_t ld, float scale,
                                int saver, int reducer, msb_stream_t stream) {
+  return msb_reduce_keep_lowest_f32_sink(dst, src, rows, cols, ld, scale, saver, reducer, nullptr, stream);
+}
+
+int msb_reduce_keep_lowest_f32_sink(float *dst, const float *src, int64_t rows, int64_t cols, int64_t ld, float scale,
+                                    int saver, int reducer, const msb_peer_sink_t *csink, msb_stream_t stream) {
+  gpu_rt::PeerSink sink;
+  MSB_REQUIRE(ToPeerSink(csink, &sink), MSB_ERR_ARGUMENT, "malformed peer sink");
+  MSB_REQUIRE(sink.world == 0 || static_cast<int64_t>(sink.count) == cols, MSB_ERR_SHAPE,
+              "the peer sink expects a different number of results");
   MSB_REQUIRE(saver >= 0 && saver <= 4 && reducer >= 0 && reducer <= 2, MSB_ERR_ARGUMENT, "unknown selector");
   MSB_REQUIRE(FitsIndex(rows) && FitsIndex(cols) && FitsIndex(rows * cols) && LdOk(ld, cols), MSB_ERR_SHAPE,
               "extent out of range");
@@ -324,6 +350,7 @@ int msb_reduce_keep_lowest_f32(float *dst, const float *src, int64_t rows, int64
   BorrowedStream st(stream);
   const G1 d = Vec(dst, cols, st.get());
   const G2 s = Mat(src, rows, cols, ld, st.get());
+  gpu_rt::PeerSinkScope scope(sink.world > 0 ? &sink : nullptr);
   if (reducer == 0) KeepLowest<red::sum>(d, s, scale, saver);
   else if (reducer == 1) KeepLowest<red::maximum>(d, s, scale, saver);
   else KeepLowest<red::minimum>(d, s, scale, saver);
@@ -332,6 +359,16 @@ int msb_reduce_keep_lowest_f32(float *dst, const float *src, int64_t rows, int64
 
 int msb_reduce_keep_highdim_f32(float *dst, const float *src, int64_t n, int64_t c, int64_t h, int64_t w, int64_t ld,
                                 float scale, int saver, int reducer, msb_stream_t stream) {
+  return msb_reduce_keep_highdim_f32_sink(dst, src, n, c, h, w, ld, scale, saver, reducer, nullptr, stream);
+}
+
+int msb_reduce_keep_highdim_f32_sink(float *dst, const float *src, int64_t n, int64_t c, int64_t h, int64_t w,
+                                     int64_t ld, float scale, int saver, int reducer, const msb_peer_sink_t *csink,
+                                     msb_stream_t stream) {
+  gpu_rt::PeerSink sink;
+  MSB_REQUIRE(ToPeerSink(csink, &sink), MSB_ERR_ARGUMENT, "malformed peer sink");
+  MSB_REQUIRE(sink.world == 0 || static_cast<int64_t>(sink.count) == c, MSB_ERR_SHAPE,
+              "the peer sink expects a different number of results");
   MSB_REQUIRE(saver >= 0 && saver <= 4 && reducer >= 0 && reducer <= 2, MSB_ERR_ARGUMENT, "unknown selector");
   MSB_REQUIRE(FitsIndex(n) && FitsIndex(c) && FitsIndex(h) && FitsIndex(w) && LdOk(ld, w), MSB_ERR_SHAPE,
               "extent out of range");
@@ -342,6 +379,7 @@ int msb_reduce_keep_highdim_f32(float *dst, const float *src, int64_t n, int64_t
   BorrowedStream st(stream);
   const G1 d = Vec(dst, c, st.get());
   const G4 s = Img(src, n, c, h, w, ld, st.get());
+  gpu_rt::PeerSinkScope scope(sink.world > 0 ? &sink : nullptr);
   if (reducer == 0) KeepDim1<red::sum>(d, s, scale, saver);
   else if (reducer == 1) KeepDim1<red::maximum>(d, s, scale, saver);
   else KeepDim1<red::minimum>(d, s, scale, saver);

@@ -149,17 +149,20 @@ extern "C" int msb_reduce_keep_lowest_sum_f32_noalloc(float *dst, const float *s
   cfg.attrs = attr;
   cfg.numAttrs = 1;
   const uint32_t urows = static_cast<uint32_t>(rows), ucols = static_cast<uint32_t>(cols);
+  const gpu_rt::PeerSink no_sink;  // results stay on this GPU
   cudaError_t err;
   if (vec) {
-    err = cudaLaunchKernelEx(&cfg, MSB_NOALLOC_KERNEL(4), dplan, splan, urows, ucols, sp.per_chunk, scale, partial);
+    err = cudaLaunchKernelEx(&cfg, MSB_NOALLOC_KERNEL(4), dplan, splan, urows, ucols, sp.per_chunk, scale, partial,
+                             no_sink);
   } else {
-    err = cudaLaunchKernelEx(&cfg, MSB_NOALLOC_KERNEL(1), dplan, splan, urows, ucols, sp.per_chunk, scale, partial);
+    err = cudaLaunchKernelEx(&cfg, MSB_NOALLOC_KERNEL(1), dplan, splan, urows, ucols, sp.per_chunk, scale, partial,
+                             no_sink);
   }
   if (err != cudaSuccess) return FailNoAlloc(MSB_ERR_CUDA, cudaGetErrorString(err));
   gpu_rt::LaunchCounter().fetch_add(1, std::memory_order_relaxed);
   if (partial != nullptr) {
     mshadow::cuda::ReduceFinishKernel<sv::saveto, red::sum, float, DPlan>
-        <<<(ucols + 255) / 256, 256, 0, st.stream_>>>(dplan, partial, sp.clusters, ucols, scale);
+        <<<(ucols + 255) / 256, 256, 0, st.stream_>>>(dplan, partial, sp.clusters, ucols, scale, no_sink);
     err = cudaPeekAtLastError();
     if (err != cudaSuccess) return FailNoAlloc(MSB_ERR_CUDA, cudaGetErrorString(err));
     gpu_rt::LaunchCounter().fetch_add(1, std::memory_order_relaxed);

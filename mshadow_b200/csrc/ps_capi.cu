@@ -87,7 +87,7 @@ int msb_ps_create(int rank, int world, const char *id_hex, int device, msb_ps_t 
 }
 
 int msb_ps_peer_create(int rank, int world, int device, int64_t window_bytes, int depth, int wait_limit_ms,
-                       msb_ps_t *out) {
+                       int own_stream, msb_ps_t *out) {
   if (out == NULL) return FailPs("msb_ps_peer_create: null pointer");
   if (world < 1 || rank < 0 || rank >= world) return FailPs("msb_ps_peer_create: rank outside [0, world)");
   PeerImpl *m = NULL;
@@ -110,6 +110,7 @@ int msb_ps_peer_create(int rank, int world, int device, int64_t window_bytes, in
       snprintf(num, sizeof(num), "%d", wait_limit_ms);
       m->SetParam("wait_limit_ms", num);
     }
+    m->SetParam("own_stream", own_stream ? "1" : "0");
     m->Init(std::vector<int>(1, device));
   } catch (const std::exception &e) {
     delete m;
@@ -136,6 +137,23 @@ int msb_ps_peer_connect(msb_ps_t model, const char *all_handles_hex) {
   PS_BEGIN
   m->SetParam("peer_handles", all_handles_hex);
   m->Connect();
+  PS_END
+}
+
+int msb_ps_peer_next_sink(msb_ps_t model, int key, int64_t offset, int64_t count, msb_peer_sink_t *out) {
+  PeerImpl *m = dynamic_cast<PeerImpl *>(static_cast<Model *>(model));
+  if (m == NULL) return FailPs("msb_ps_peer_next_sink: not a peer model");
+  if (out == NULL) return FailPs("msb_ps_peer_next_sink: null pointer");
+  if (offset < 0 || count < 0 || offset + count >= (int64_t(1) << 31)) return FailPs("msb_ps_peer_next_sink: extent out of range");
+  static_assert(sizeof(msb_peer_sink_t) == sizeof(gpu_rt::PeerSink), "msb_peer_sink_t must mirror gpu_rt::PeerSink");
+  PS_BEGIN
+  int dev = 0;
+  MSHADOW_CUDA_CALL(cudaGetDevice(&dev));
+  const gpu_rt::PeerSink sink = m->NextSink(key, dev, static_cast<uint32_t>(offset), static_cast<uint32_t>(count));
+  for (int p = 0; p < MSB_PEER_MAX_WORLD; ++p) out->row[p] = sink.row[p];
+  out->tag = sink.tag;
+  out->count = sink.count;
+  out->world = sink.world;
   PS_END
 }
 
@@ -179,6 +197,17 @@ int msb_ps_pull_wait(msb_ps_t model, int key) {
   int dev = 0;
   MSHADOW_CUDA_CALL(cudaGetDevice(&dev));
   static_cast<Model *>(model)->PullWait(key, dev);
+  PS_END
+}
+
+int msb_ps_pull_fence(msb_ps_t model, int key, void *stream) {
+  if (model == NULL) return FailPs("msb_ps_pull_fence: null model");
+  PS_BEGIN
+  int dev = 0;
+  MSHADOW_CUDA_CALL(cudaGetDevice(&dev));
+  Stream<gpu> st;
+  st.stream_ = static_cast<cudaStream_t>(stream);
+  static_cast<Model *>(model)->PullFence(key, dev, &st);
   PS_END
 }
 

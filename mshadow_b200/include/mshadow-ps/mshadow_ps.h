@@ -137,6 +137,11 @@ class NcclModel : public ISharedModel<gpu, DType> {
     }
   }
 
+  virtual void PullFence(int key, int devid, Stream<gpu> *stream) {
+    Entry &e = this->Find(key, devid);
+    if (e.pull_pending) MSHADOW_CUDA_CALL(cudaStreamWaitEvent(Stream<gpu>::GetStream(stream), e.pull_done, 0));
+  }
+
   /*! \brief every rank's `data` becomes rank 0's */
   virtual void SetWeight_(Tensor<gpu, 2, DType> data, int key, int devid) {
     Entry &e = this->Find(key, devid);

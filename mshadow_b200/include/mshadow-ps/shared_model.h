@@ -33,6 +33,15 @@ class ISharedModel {
     this->InitKey_(shape.FlatTo2D(), key, devid);
   }
   virtual void PullWait(int key, int devid) = 0;
+  /*!
+   * \brief device-side PullWait: work enqueued on `stream` after this call runs after the last
+   *  pull of `key` has completed; the host does not block (an extension of the reference
+   *  interface, for consumers that stay on the GPU).  The default falls back to PullWait.
+   */
+  virtual void PullFence(int key, int devid, Stream<xpu> *stream) {
+    (void)stream;
+    this->PullWait(key, devid);
+  }
   template <int dim>
   inline void CheckWeight(Tensor<xpu, dim, DType> data, int key, int devid) {
     this->CheckWeight_(data.FlatTo2D(), key, devid);

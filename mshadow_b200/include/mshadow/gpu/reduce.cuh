@@ -15,12 +15,17 @@
  * second kernel folds in a fixed order.  Every combine order is fixed by the launch
  * geometry, so results are reproducible run to run.  Both kernels are bound by HBM
  * bandwidth: 4 bytes read per input element, nothing else of size.
+ *
+ * The thread that stores a final result can also hand it to the other GPUs of an exchange
+ * group (gpu_rt::PeerSink, see peer_sink.h): the value scale * Reduce(...) -- what the saver
+ * receives -- goes into every rank's exchange window by one 64-bit store per rank.
  */
 #ifndef MSHADOW_GPU_REDUCE_CUH_
 #define MSHADOW_GPU_REDUCE_CUH_
 
 #include <cooperative_groups.h>
 
+#include "./peer_sink.h"
 #include "./runtime.h"
 
 namespace mshadow {
@@ -120,7 +125,7 @@ __device__ __forceinline__ DType BlockReduce(DType v, DType *buf) {
 template <typename Saver, typename Reducer, int kLanes, typename DType, typename DPlan, typename SPlan>
 __global__ void __launch_bounds__(kRedLowThreads)
 ReduceKeepLowestKernel(DPlan dst, const SPlan src, uint32_t rows, uint32_t cols, uint32_t rows_per_chunk,
-                       DType scale, DType *partial) {
+                       DType scale, DType *partial, const gpu_rt::PeerSink sink) {
   __shared__ __align__(16) DType stage[kRedLowThreads * kLanes];
   cg::cluster_group cluster = cg::this_cluster();
   const uint32_t x = (blockIdx.x * kRedLowThreads + threadIdx.x) * kLanes;
@@ -174,7 +179,10 @@ ReduceKeepLowestKernel(DPlan dst, const SPlan src, uint32_t rows, uint32_t cols,
     if (!live) return;
 #pragma unroll
     for (int l = 0; l < kLanes; ++l) {
-      if (x + l < cols) Saver::Save(dst.REval(0, x + l), DType(acc[l] * scale));
+      if (x + l < cols) {
+        Saver::Save(dst.REval(0, x + l), DType(acc[l] * scale));
+        if (sink.world > 0) sink.Put(x + l, DType(acc[l] * scale));
+      }
     }
     return;
   }
@@ -195,11 +203,13 @@ ReduceKeepLowestKernel(DPlan dst, const SPlan src, uint32_t rows, uint32_t cols,
  *  launch, which only exists for inputs large enough to need several clusters per output.
  */
 template <typename Saver, typename Reducer, typename DType, typename DPlan>
-__global__ void ReduceFinishKernel(DPlan dst, const DType *partial, uint32_t nparts, uint32_t cols, DType scale) {
+__global__ void ReduceFinishKernel(DPlan dst, const DType *partial, uint32_t nparts, uint32_t cols, DType scale,
+                                   const gpu_rt::PeerSink sink) {
   const uint32_t x = blockIdx.x * blockDim.x + threadIdx.x;
   if (x >= cols) return;
   const DType sum = reddetail::FoldParked<Reducer>(partial + x, cols, nparts);
   Saver::Save(dst.REval(0, x), DType(sum * scale));
+  if (sink.world > 0) sink.Put(x, DType(sum * scale));
 }
 
 /*!
@@ -211,7 +221,7 @@ template <typename Saver, typename Reducer, int kLanes, typename DType, typename
 __global__ void __launch_bounds__(kRedHighThreads)
 ReduceKeepHighDimKernel(DPlan dst, const SPlan src, uint32_t outer, uint32_t channels, uint32_t inner_rows,
                         uint32_t packs_per_row, gpu_rt::FastDiv row_of_pack, gpu_rt::FastDiv plane_of_pack,
-                        uint32_t outer_per_chunk, DType scale, DType *partial) {
+                        uint32_t outer_per_chunk, DType scale, DType *partial, const gpu_rt::PeerSink sink) {
   __shared__ DType warp_buf[kRedHighThreads / 32];
   __shared__ DType cta_val;
   cg::cluster_group cluster = cg::this_cluster();
@@ -268,6 +278,7 @@ ReduceKeepHighDimKernel(DPlan dst, const SPlan src, uint32_t outer, uint32_t cha
   if (threadIdx.x != 0) return;
   if (partial == nullptr) {
     Saver::Save(dst.REval(0, c), DType(total * scale));
+    if (sink.world > 0) sink.Put(c, DType(total * scale));
     return;
   }
   // several clusters per channel: park the cluster's value for ReduceFinishKernel
@@ -437,6 +448,18 @@ inline Split PlanKeepLowest(uint32_t rows, uint32_t col_tiles, uint32_t slots) {
   return s;
 }
 
+/*! \brief the sink armed for this host thread's next reduction (peer_sink.h), checked against the launch */
+template <typename DType>
+inline gpu_rt::PeerSink TakePeerSink(uint32_t results) {
+  const gpu_rt::PeerSink *pending = gpu_rt::PendingPeerSink();
+  if (pending == nullptr || pending->world == 0) return gpu_rt::PeerSink();
+  gpu_rt::PendingPeerSink() = nullptr;  // one reduction per arming
+  CHECK_EQ(sizeof(DType), 4U) << "a peer sink carries 4-byte elements";
+  CHECK_EQ(pending->count, results) << "the peer sink expects " << pending->count << " results, the reduction gives "
+                                    << results;
+  return *pending;
+}
+
 /*! \brief CTAs of `kernel` that the current device keeps resident at once */
 template <typename Kernel>
 inline uint32_t ResidentCtas(Kernel kernel, int threads) {
@@ -454,17 +477,19 @@ inline void ReduceKeepLowestLaunch(DPlan dplan, const SPlan &splan, Shape<2> esh
   auto kernel = ReduceKeepLowestKernel<Saver, Reducer, kLanes, DType, DPlan, SPlan>;
   const uint32_t slots = reddetail::ResidentCtas(kernel, kRedLowThreads);
   const reddetail::Split sp = reddetail::PlanKeepLowest(rows, col_tiles, slots);
+  const gpu_rt::PeerSink sink = reddetail::TakePeerSink<DType>(cols);
+  const gpu_rt::PeerSink none;
   DType *partial = nullptr;
   if (sp.clusters > 1) {
     partial = static_cast<DType *>(
         gpu_rt::Scratch::Get(stream, static_cast<size_t>(sp.clusters) * cols * sizeof(DType)));
   }
   reddetail::LaunchClustered(kernel, dim3(col_tiles, sp.chunks), dim3(kRedLowThreads), sp.cluster, stream,
-                             dplan, splan, rows, cols, sp.per_chunk, scale, partial);
+                             dplan, splan, rows, cols, sp.per_chunk, scale, partial, partial == nullptr ? sink : none);
   MSHADOW_CUDA_POST_KERNEL_CHECK(ReduceKeepLowestKernel);
   if (partial != nullptr) {
     ReduceFinishKernel<Saver, Reducer, DType, DPlan>
-        <<<gpu_rt::CeilDiv(cols, 256), 256, 0, stream>>>(dplan, partial, sp.clusters, cols, scale);
+        <<<gpu_rt::CeilDiv(cols, 256), 256, 0, stream>>>(dplan, partial, sp.clusters, cols, scale, sink);
     MSHADOW_CUDA_POST_KERNEL_CHECK(ReduceFinishKernel);
   }
 }
@@ -480,6 +505,8 @@ inline void ReduceKeepHighDimLaunch(DPlan dplan, const SPlan &splan, Shape<4> ps
   // whole waves of resident CTAs; at most 64 chunks, each at least one outer index
   const uint32_t slots = reddetail::ResidentCtas(kernel, kRedHighThreads);
   const reddetail::Split sp = reddetail::PlanSplitWaves(outer, channels, slots, 64);
+  const gpu_rt::PeerSink sink = reddetail::TakePeerSink<DType>(channels);
+  const gpu_rt::PeerSink none;
   DType *partial = nullptr;
   if (sp.clusters > 1) {
     partial = static_cast<DType *>(
@@ -488,11 +515,12 @@ inline void ReduceKeepHighDimLaunch(DPlan dplan, const SPlan &splan, Shape<4> ps
   const uint32_t per_plane = inner_rows * ppr;
   reddetail::LaunchClustered(kernel, dim3(channels, sp.chunks), dim3(kRedHighThreads), sp.cluster, stream,
                              dplan, splan, outer, channels, inner_rows, ppr, gpu_rt::FastDiv(ppr),
-                             gpu_rt::FastDiv(per_plane == 0 ? 1 : per_plane), sp.per_chunk, scale, partial);
+                             gpu_rt::FastDiv(per_plane == 0 ? 1 : per_plane), sp.per_chunk, scale, partial,
+                             partial == nullptr ? sink : none);
   MSHADOW_CUDA_POST_KERNEL_CHECK(ReduceKeepHighDimKernel);
   if (partial != nullptr) {
     ReduceFinishKernel<Saver, Reducer, DType, DPlan>
-        <<<gpu_rt::CeilDiv(channels, 256), 256, 0, stream>>>(dplan, partial, sp.clusters, channels, scale);
+        <<<gpu_rt::CeilDiv(channels, 256), 256, 0, stream>>>(dplan, partial, sp.clusters, channels, scale, sink);
     MSHADOW_CUDA_POST_KERNEL_CHECK(ReduceFinishKernel);
   }
 }

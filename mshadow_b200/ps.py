@@ -16,9 +16,11 @@ vp, i64, cint = C.c_void_p, C.c_int64, C.c_int
 _SIGNATURES = {
     "msb_ps_new_unique_id": [C.c_char_p, i64],
     "msb_ps_create": [cint, cint, C.c_char_p, cint, C.POINTER(vp)],
-    "msb_ps_peer_create": [cint, cint, cint, i64, cint, cint, C.POINTER(vp)],
+    "msb_ps_peer_create": [cint, cint, cint, i64, cint, cint, cint, C.POINTER(vp)],
+    "msb_ps_pull_fence": [vp, cint, vp],
     "msb_ps_peer_handle": [vp, C.c_char_p, i64],
     "msb_ps_peer_connect": [vp, C.c_char_p],
+    "msb_ps_peer_next_sink": [vp, cint, i64, i64, vp],
     "msb_ps_destroy": [vp],
     "msb_ps_init_key": [vp, cint, i64, i64],
     "msb_ps_push": [vp, vp, i64, i64, i64, cint, vp],
@@ -36,6 +38,11 @@ def declared_symbols():
 
 class PsError(RuntimeError):
     pass
+
+
+class PeerSink(C.Structure):
+    """msb_peer_sink_t of include/mshadow_b200_peer_sink.h."""
+    _fields_ = [("row", C.c_void_p * 16), ("tag", C.c_uint32), ("count", C.c_uint32), ("world", C.c_int)]
 
 
 _dll = None
@@ -112,6 +119,10 @@ class SharedModel:
     def pull_wait(self, key):
         _check(dll().msb_ps_pull_wait(self.handle, key))
 
+    def pull_fence(self, key, stream=None):
+        """Later work on `stream` runs after the last pull of `key`; the host does not wait."""
+        _check(dll().msb_ps_pull_fence(self.handle, key, stream))
+
     def set_weight(self, tensor, key, stream=None):
         p, rows, cols, ld = _mat(tensor)
         _check(dll().msb_ps_set_weight(self.handle, p, rows, cols, ld, key, stream))
@@ -128,10 +139,10 @@ class PeerModel(SharedModel):
     Set-up takes two steps because the ranks must learn each other's windows: create the model on
     every rank, gather `handle()` of all ranks in rank order (any transport), `connect(handles)`."""
 
-    def __init__(self, rank=0, world=1, device=0, window_bytes=0, depth=0, wait_limit_ms=0):
+    def __init__(self, rank=0, world=1, device=0, window_bytes=0, depth=0, wait_limit_ms=0, own_stream=False):
         self.handle = vp()
         self.world = world
-        _check(dll().msb_ps_peer_create(rank, world, device, window_bytes, depth, wait_limit_ms,
+        _check(dll().msb_ps_peer_create(rank, world, device, window_bytes, depth, wait_limit_ms, int(own_stream),
                                         C.byref(self.handle)))
 
     def export_handle(self):
@@ -143,3 +154,10 @@ class PeerModel(SharedModel):
         """`handles`: the export_handle() strings of all ranks, in rank order."""
         assert len(handles) == self.world
         _check(dll().msb_ps_peer_connect(self.handle, "".join(handles).encode("ascii")))
+
+    def next_sink(self, key, offset, count):
+        """Sink for `count` results from element `offset` of the key's row in the step that the
+        segment at offset 0 opens; hand it to Library.reduce_keep_*(..., sink=...)."""
+        sink = PeerSink()
+        _check(dll().msb_ps_peer_next_sink(self.handle, key, offset, count, C.byref(sink)))
+        return sink

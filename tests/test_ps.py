@@ -142,15 +142,16 @@ def test_two_processes_sum_over_nvlink(tmp_path):
 # ---- the peer-store model --------------------------------------------------------------------
 @pytest.mark.gpu
 def test_peer_model_alone_on_one_gpu_runs_its_kernels_and_slot_rotation():
-    """A group of one: the contribution goes through the window of this GPU (push kernel, flags,
-    pull kernel), step after step, so slots are reused several times; the sum of one is the data."""
+    """A group of one: the contribution goes through the window of this GPU (push kernel, tagged
+    words, pull kernel), step after step, so slots are reused several times; the sum of one is the
+    data.  Then the same with reduction kernels delivering their results through sinks."""
     if not torch.cuda.is_available():
         pytest.skip("no CUDA device")
     m = ps.PeerModel(rank=0, world=1, device=0, depth=4)
     try:
         m.init_key(0, (4608,))
         m.init_key(1, (7, 33))            # odd sizes: element-wise path
-        m.init_key(2, (64, 1024))         # several CTAs per peer: ticket counter decides who publishes
+        m.init_key(2, (64, 1024))         # many CTAs
         g = torch.Generator(device="cuda")
         g.manual_seed(5)
         for step in range(11):
@@ -184,6 +185,27 @@ def test_peer_model_alone_on_one_gpu_runs_its_kernels_and_slot_rotation():
             m.pull_req(o2, 2)
             m.pull_wait(2)
             assert torch.equal(o2, d)
+        # reductions that deliver their own results: a column sum large enough to need the finishing
+        # kernel, a small one that does not, and a channel sum, as segments of one row
+        import mshadow_b200
+        lib = mshadow_b200.load()
+        lib.init(0)
+        m.init_key(3, (2048 + 48 + 24,))
+        for step in range(3):
+            big = torch.randn(30000, 2048, device="cuda", generator=g)
+            small = torch.randn(77, 48, device="cuda", generator=g)
+            img = torch.randn(5, 24, 6, 10, device="cuda", generator=g)
+            d1, d2, d3 = (torch.zeros(k, device="cuda") for k in (2048, 48, 24))
+            lib.reduce_keep_lowest(d1, big, scale=0.5, sink=m.next_sink(3, 0, 2048))
+            lib.reduce_keep_lowest(d2, small, sink=m.next_sink(3, 2048, 48))
+            lib.reduce_keep_highdim(d3, img, scale=2.0, saver=1, sink=m.next_sink(3, 2048 + 48, 24))
+            got = torch.zeros(2048 + 48 + 24, device="cuda")
+            m.pull_req(got, 3)
+            m.pull_wait(3)
+            # d3 was accumulated into (saver plusto) zeros, so it equals what was delivered
+            assert torch.equal(got, torch.cat([d1, d2, d3]))
+        with pytest.raises(mshadow_b200.MsbError, match="different number"):
+            lib.reduce_keep_lowest(d1, big, sink=m.next_sink(3, 2048, 48))   # a segment that opens no step
         w = torch.randn(7, 33, device="cuda", generator=g)
         keep = w.clone()
         m.set_weight(w, 1)
@@ -296,6 +318,24 @@ def _peer_worker(rank, world, tmp):
         m.pull_req(big, 1)
         m.pull_wait(1)
         ok = ok and torch.equal(big.cpu(), want(100 + s, (64, 1024)))
+    # reductions delivering their results themselves: every rank sums its own matrix, all receive
+    # the rank-order sum of the per-rank column sums
+    import mshadow_b200
+    lib = mshadow_b200.load()
+    lib.init(rank)
+    for s in range(4):
+        mat = data(rank, 200 + s, (9000, 4608)).cuda()
+        mine_sum = torch.zeros(4608, device="cuda")
+        lib.reduce_keep_lowest(mine_sum, mat, sink=m.next_sink(0, 0, 4608))
+        got = torch.zeros(4608, device="cuda")
+        m.pull_req(got, 0)
+        m.pull_wait(0)
+        parts = []
+        for r in range(world):
+            other = torch.zeros(4608, device="cuda")
+            lib.reduce_keep_lowest(other, data(r, 200 + s, (9000, 4608)).cuda())
+            parts.append(other.cpu().numpy())
+        ok = ok and torch.equal(got.cpu(), torch.from_numpy(sharding.rank_order_sum(parts)))
     w = torch.full((64, 1024), float(rank + 5), device="cuda")
     m.set_weight(w, 1)
     ok = ok and bool((w == 5.0).all())

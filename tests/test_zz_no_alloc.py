@@ -73,9 +73,13 @@ def test_two_calls_match_the_allocating_entry_point_and_allocate_nothing(lib, ro
         # the two entry points share kernels and launch geometry: identical results
         assert scaled_err(o, w) <= 1e-5
         assert np.array_equal(o.view(np.uint32), w.view(np.uint32))
-        # and both agree with the CPU evaluation within the tolerance of the other sum tests
-        ref = orc.reduce_keep_lowest(np.zeros(cols, np.float32), np.ascontiguousarray(src.cpu().numpy()), scale=scale)
-        assert scaled_err(o, ref) <= 1e-5
+        # and agree with the CPU: with a binary64 column sum always, with the oracle's binary32
+        # left-to-right sum where that sum's own rounding stays below the tolerance (few rows)
+        host = np.ascontiguousarray(src.cpu().numpy())
+        exact = (host.sum(axis=0, dtype=np.float64) * np.float64(np.float32(scale))).astype(np.float32)
+        assert scaled_err(o, exact) <= 1e-5
+        if rows <= 4096:
+            assert scaled_err(o, orc.reduce_keep_lowest(np.zeros(cols, np.float32), host, scale=scale)) <= 1e-5
 
 
 def test_oversized_input_is_rejected_without_launching(lib):
