@@ -427,6 +427,17 @@ def kernel_cases(lib, torch, small=False):
     yield ("chpool", "C4 chpool<sum> nsize 5 (%d,256,56,56)" % imgs, 8 * X.numel(), X.numel(),
            lambda: lib.chpool(G4, X4, 5), 20)
     del X, Pm, gP, G, X4, G4
+    # pooling of planes that do not fit shared memory (224 x 224): bands of rows instead of whole planes
+    pl = (8 if small else 64) * 64
+    XL = torch.rand(pl, 224, 224, device=dev, generator=g)
+    PL = torch.empty(pl, 111, 111, device=dev)
+    yield ("pool_large", "pool<max> 3x3/2 (%d,224,224) planes" % pl, 4 * XL.numel() + 4 * PL.numel(), XL.numel(),
+           lambda: lib.pool(PL, XL, 3, 3, 2, 2), 10)
+    gPL = torch.rand(pl, 111, 111, device=dev, generator=g)
+    GL = torch.empty_like(XL)
+    yield ("unpool_large", "unpool<max> 3x3/2 (%d,224,224) planes" % pl, 8 * XL.numel() + 8 * PL.numel(), XL.numel(),
+           lambda: lib.unpool(GL, XL, PL, gPL, 3, 3, 2, 2), 10)
+    del XL, PL, gPL, GL
     # C5: embedding backward
     k, d, nidx = (262144, 1024, 1 << 17) if small else (262144, 1024, 1 << 20)
     p = (np.arange(k) + 1.0) ** -1.1

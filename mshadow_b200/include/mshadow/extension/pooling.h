@@ -328,6 +328,14 @@ struct MapDispatch<sv::saveto, Tensor<gpu, dim, float>, expr::PoolingExp<Reducer
     if (standard_shape && PoolPlanesFit(e.src_height_, e.src_width_, ph, pw, false)) {
       PoolPlanesLaunch<Reducer>(dst->dptr_, src.dptr_, dshape.ProdShape(0, dim - 2), e.src_height_, e.src_width_,
                                 e.ksize_y_, e.ksize_x_, e.kstride_y_, e.kstride_x_, src.stride_, dst->stride_, stream);
+      return;
+    }
+    // planes beyond shared memory: bands of whole rows
+    const BandPlan bp = standard_shape ? PlanPoolBands(e.src_height_, e.src_width_, ph, e.ksize_y_, e.kstride_y_)
+                                       : BandPlan{0, 0, 0, 0, false};
+    if (bp.ok) {
+      PoolBandsLaunch<Reducer>(dst->dptr_, src.dptr_, dshape.ProdShape(0, dim - 2), e.src_height_, e.src_width_,
+                               e.ksize_y_, e.ksize_x_, e.kstride_y_, e.kstride_x_, src.stride_, dst->stride_, bp, stream);
     } else {
       MapGeneric<sv::saveto, float>(dst, e, dshape, stream);
     }
@@ -346,6 +354,15 @@ struct MapDispatch<sv::saveto, Tensor<gpu, dim, float>,
       UnpoolPlanesLaunch<Reducer>(dst->dptr_, src.dptr_, pooled.dptr_, grad.dptr_, dshape.ProdShape(0, dim - 2), h, w,
                                   e.pshape_y_, e.pshape_x_, e.ksize_y_, e.ksize_x_, e.kstride_y_, e.kstride_x_,
                                   src.stride_, pooled.stride_, dst->stride_, stream);
+      return;
+    }
+    const BandPlan bp = pooled.stride_ == grad.stride_
+                            ? PlanUnpoolBands(h, w, e.pshape_y_, e.pshape_x_, e.ksize_y_, e.kstride_y_)
+                            : BandPlan{0, 0, 0, 0, false};
+    if (bp.ok) {
+      UnpoolBandsLaunch<Reducer>(dst->dptr_, src.dptr_, pooled.dptr_, grad.dptr_, dshape.ProdShape(0, dim - 2), h, w,
+                                 e.pshape_y_, e.pshape_x_, e.ksize_y_, e.ksize_x_, e.kstride_y_, e.kstride_x_,
+                                 src.stride_, pooled.stride_, dst->stride_, bp, stream);
     } else {
       MapGeneric<sv::saveto, float>(dst, e, dshape, stream);
     }

@@ -316,6 +316,311 @@ UnpoolPlanesKernel(float *dst, const float *src, const float *pooled, const floa
   }
 }
 
+namespace pooldetail {
+/*!
+ * \brief bring the `count` floats that start at `first` into shared memory at tile + *off.
+ *  The bulk copy needs 16-byte aligned ends, so it fetches the 16-byte aligned window around the
+ *  range and *off tells where the range starts inside it (0..3); that is only done when the
+ *  window stays inside [lo_limit, hi_limit), the storage the caller vouches for.  Otherwise
+ *  all threads copy with plain loads and *off is 0.  Returns whether a bulk copy was issued (the
+ *  caller then waits on `bar`); `expect` accumulates the bytes announced to the barrier.
+ */
+__device__ __forceinline__ bool StageAround(float *tile, const float *first, uint32_t count, const float *lo_limit,
+                                            const float *hi_limit, bool allow_bulk, uint64_t *bar, uint32_t *off) {
+  const uintptr_t a = reinterpret_cast<uintptr_t>(first);
+  const uintptr_t lo = a & ~static_cast<uintptr_t>(15);
+  const uintptr_t hi = (a + static_cast<uintptr_t>(count) * 4 + 15) & ~static_cast<uintptr_t>(15);
+  const bool bulk = allow_bulk && count > 0 && lo >= reinterpret_cast<uintptr_t>(lo_limit) &&
+                    hi <= reinterpret_cast<uintptr_t>(hi_limit);
+  if (bulk) {
+    *off = static_cast<uint32_t>((a - lo) >> 2);
+    if (threadIdx.x == 0) tma::BulkLoad(tile, reinterpret_cast<const float *>(lo), static_cast<uint32_t>(hi - lo), bar);
+    return true;
+  }
+  *off = 0;
+  for (uint32_t i = threadIdx.x; i < count; i += blockDim.x) tile[i] = first[i];
+  return false;
+}
+/*! \brief bytes StageAround's bulk copy moves for this range */
+__device__ __forceinline__ uint32_t AroundBytes(const float *first, uint32_t count) {
+  const uintptr_t a = reinterpret_cast<uintptr_t>(first);
+  return static_cast<uint32_t>(((a + static_cast<uintptr_t>(count) * 4 + 15) & ~static_cast<uintptr_t>(15)) -
+                               (a & ~static_cast<uintptr_t>(15)));
+}
+/*! \brief whether StageAround would issue a bulk copy for this range */
+__device__ __forceinline__ bool AroundFits(const float *first, uint32_t count, const float *lo_limit,
+                                           const float *hi_limit) {
+  const uintptr_t a = reinterpret_cast<uintptr_t>(first);
+  return count > 0 && (a & ~static_cast<uintptr_t>(15)) >= reinterpret_cast<uintptr_t>(lo_limit) &&
+         ((a + static_cast<uintptr_t>(count) * 4 + 15) & ~static_cast<uintptr_t>(15)) <=
+             reinterpret_cast<uintptr_t>(hi_limit);
+}
+}  // namespace pooldetail
+
+/*!
+ * \brief spatial pooling of planes that do not fit shared memory.  The rows of a plane are
+ *  contiguous, so a band of whole rows is one contiguous range: work item = (plane, band of
+ *  `band_rows` output rows); the (band_rows - 1) * sy + ky input rows it reads are staged by one
+ *  bulk copy (the 16-byte aligned window around them; plain loads for pitched rows or at the
+ *  very ends of the tensor), windows are evaluated out of shared memory in the reference's
+ *  order, results leave coalesced.  Neighbouring bands re-read ky - sy rows.
+ *  Shared memory: ((band_rows - 1) * sy + ky) * w + 8 floats.
+ */
+template <typename Reducer, int KY, int KX, int SY, int SX>
+__global__ void __launch_bounds__(kPoolThreads)
+PoolBandsKernel(float *dst, const float *src, uint32_t planes, uint32_t h, uint32_t w, uint32_t ph, uint32_t pw,
+                PoolGeom g, int64_t ld_src, int64_t ld_dst, uint32_t band_rows, uint32_t bands,
+                gpu_rt::FastDiv div_bands, gpu_rt::FastDiv div_pw, gpu_rt::FastDiv div_pairs, int *status) {
+  extern __shared__ __align__(16) float tile[];
+  __shared__ uint64_t bar;
+  const int ky = KY > 0 ? KY : g.ky, kx = KX > 0 ? KX : g.kx;
+  const int sy = SY > 0 ? SY : g.sy, sx = SX > 0 ? SX : g.sx;
+  if (threadIdx.x == 0) tma::BarrierInit(&bar, 1);
+  __syncthreads();
+  uint32_t phase = 0;
+  const bool dense_in = ld_src == static_cast<int64_t>(w);
+  const float *src_end = src + static_cast<int64_t>(planes) * h * w;  // dense case only
+  const uint32_t items = planes * bands;
+  for (uint32_t item = blockIdx.x; item < items; item += gridDim.x) {
+    const uint32_t p = div_bands.Quot(item);
+    const uint32_t py0 = (item - p * bands) * band_rows;
+    const uint32_t npy = min(band_rows, ph - py0);
+    const uint32_t nrows = (npy - 1) * sy + ky;
+    const float *first = src + (static_cast<int64_t>(p) * h + py0 * sy) * ld_src;
+    uint32_t off = 0;
+    bool bulk = false;
+    if (dense_in) {
+      const bool fits = pooldetail::AroundFits(first, nrows * w, src, src_end);
+      if (fits && threadIdx.x == 0) tma::BarrierExpect(&bar, pooldetail::AroundBytes(first, nrows * w));
+      bulk = pooldetail::StageAround(tile, first, nrows * w, src, src_end, fits, &bar, &off);
+    } else {
+      pooldetail::StagePitched(tile, first, nrows, w, ld_src);
+    }
+    if (bulk) {
+      if (!tma::WaitBounded(&bar, phase)) {
+        if (threadIdx.x == 0) atomicExch(status, tma::kStatusBulkCopyTimeout);
+        tma::WaitBounded(&bar, phase);
+        return;
+      }
+      phase ^= 1;
+    } else {
+      __syncthreads();
+    }
+    const float *band = tile + off;
+    float *out_band = dst + (static_cast<int64_t>(p) * ph + py0) * ld_dst;
+    if ((KX == 3 || KX == 2) && SX == 2 && KY > 0 && MSHADOW_B200_POOL_PAIRS && (w & 3u) == 0 && (off & 3u) == 0) {
+      // two adjacent outputs per thread from 16-byte shared-memory loads, as in PoolPlanesKernel
+      const uint32_t pairs_per_row = (pw + 1) >> 1;
+      const uint32_t npairs = npy * pairs_per_row;
+      for (uint32_t o = threadIdx.x; o < npairs; o += kPoolThreads) {
+        const uint32_t lpy = div_pairs.Quot(o);
+        const uint32_t px = (o - lpy * pairs_per_row) * 2;
+        const float *at = band + lpy * SY * w + px * 2;
+        const bool second = px + 1 < pw;
+        float r0, r1;
+        Reducer::SetInitValue(r0);
+        Reducer::SetInitValue(r1);
+#pragma unroll
+        for (int dy = 0; dy < (KY > 0 ? KY : 1); ++dy) {
+          const float4 v = *reinterpret_cast<const float4 *>(at + dy * w);
+          Reducer::Reduce(r0, v.x);
+          Reducer::Reduce(r0, v.y);
+          if (KX == 3) {
+            const float e = second ? at[dy * w + 4] : 0.0f;
+            Reducer::Reduce(r0, v.z);
+            Reducer::Reduce(r1, v.z);
+            Reducer::Reduce(r1, v.w);
+            Reducer::Reduce(r1, e);
+          } else {
+            Reducer::Reduce(r1, v.z);
+            Reducer::Reduce(r1, v.w);
+          }
+        }
+        float *out = out_band + static_cast<int64_t>(lpy) * ld_dst + px;
+        out[0] = r0;
+        if (second) out[1] = r1;
+      }
+    } else {
+      const uint32_t nout = npy * pw;
+      for (uint32_t o = threadIdx.x; o < nout; o += kPoolThreads) {
+        const uint32_t lpy = div_pw.Quot(o);
+        const uint32_t px = o - lpy * pw;
+        const float *at = band + lpy * sy * w + px * sx;
+        float res;
+        Reducer::SetInitValue(res);
+        if (KY > 0) {
+#pragma unroll
+          for (int dy = 0; dy < (KY > 0 ? KY : 1); ++dy)
+#pragma unroll
+            for (int dx = 0; dx < (KX > 0 ? KX : 1); ++dx) Reducer::Reduce(res, at[dy * w + dx]);
+        } else {
+          for (int dy = 0; dy < ky; ++dy)
+            for (int dx = 0; dx < kx; ++dx) Reducer::Reduce(res, at[dy * w + dx]);
+        }
+        out_band[static_cast<int64_t>(lpy) * ld_dst + px] = res;
+      }
+    }
+    // all reads of the tile are done before the next band overwrites it
+    tma::FenceAsyncShared();
+    __syncthreads();
+  }
+}
+
+/*!
+ * \brief backward of spatial pooling for planes that do not fit shared memory: work item =
+ *  (plane, band of `band_rows` source rows).  The band of the source, and the rows of the pooled
+ *  plane and of its gradient whose windows reach into the band, are three contiguous ranges,
+ *  staged like the forward kernel's.  Sums run over the covering windows in py-outer / px-inner
+ *  order from zero with one rounding per product and per sum, as in UnpoolPlanesKernel.
+ *  Shared memory: band_rows * w + 2 * pooled_rows * pw + 24 floats, pooled_rows being the most
+ *  pooled rows any band needs.
+ */
+template <typename Reducer, int KY, int KX, int SY, int SX>
+__global__ void __launch_bounds__(kPoolThreads)
+UnpoolBandsKernel(float *dst, const float *src, const float *pooled, const float *gpooled, uint32_t planes,
+                  uint32_t h, uint32_t w, uint32_t ph, uint32_t pw, PoolGeom g, int64_t ld_src, int64_t ld_pooled,
+                  int64_t ld_dst, uint32_t band_rows, uint32_t bands, uint32_t pooled_rows_cap,
+                  gpu_rt::FastDiv div_bands, gpu_rt::FastDiv div_w, gpu_rt::FastDiv div_wq, gpu_rt::FastDiv div_sy,
+                  gpu_rt::FastDiv div_sx, int *status) {
+  extern __shared__ __align__(16) float tile[];
+  __shared__ uint64_t bar;
+  const uint32_t ky = KY > 0 ? KY : g.ky, kx = KX > 0 ? KX : g.kx;
+  const uint32_t sy = SY > 0 ? SY : g.sy, sx = SX > 0 ? SX : g.sx;
+  // three regions, each with room for the aligned window around its range
+  const uint32_t src_cap = ((band_rows * w + 3) & ~3u) + 8, pool_cap = ((pooled_rows_cap * pw + 3) & ~3u) + 8;
+  float *r_src = tile, *r_pool = tile + src_cap, *r_grad = r_pool + pool_cap;
+  if (threadIdx.x == 0) tma::BarrierInit(&bar, 1);
+  __syncthreads();
+  uint32_t phase = 0;
+  const bool dense = ld_src == static_cast<int64_t>(w) && ld_pooled == static_cast<int64_t>(pw);
+  const float *src_end = src + static_cast<int64_t>(planes) * h * w;
+  const float *pool_end = pooled + static_cast<int64_t>(planes) * ph * pw;
+  const float *grad_end = gpooled + static_cast<int64_t>(planes) * ph * pw;
+  constexpr bool kQuad = KY > 0 && KX > 0 && SY > 0 && SX > 0 && (4 % (SX > 0 ? SX : 1) == 0);
+  const bool vec_out = (ld_dst & 3) == 0 && reinterpret_cast<uintptr_t>(dst) % 16 == 0;
+  const uint32_t items = planes * bands;
+  for (uint32_t item = blockIdx.x; item < items; item += gridDim.x) {
+    const uint32_t p = div_bands.Quot(item);
+    const uint32_t y0 = (item - p * bands) * band_rows;
+    const uint32_t nrows = min(band_rows, h - y0);
+    // pooled rows whose windows reach rows y0 .. y0 + nrows - 1
+    const uint32_t py_lo = y0 < ky ? 0 : (SY > 0 ? (y0 - ky + sy) / sy : div_sy.Quot(y0 - ky + sy));
+    const uint32_t py_top = min(SY > 0 ? (y0 + nrows - 1 + sy) / sy : div_sy.Quot(y0 + nrows - 1 + sy), ph);
+    const uint32_t npr = py_top > py_lo ? py_top - py_lo : 0;
+    const float *g_src = src + (static_cast<int64_t>(p) * h + y0) * ld_src;
+    const float *g_pool = pooled + (static_cast<int64_t>(p) * ph + py_lo) * ld_pooled;
+    const float *g_grad = gpooled + (static_cast<int64_t>(p) * ph + py_lo) * ld_pooled;
+    uint32_t off_s = 0, off_p = 0, off_g = 0;
+    bool bulk = false;
+    if (dense) {
+      bulk = pooldetail::AroundFits(g_src, nrows * w, src, src_end) &&
+             (npr == 0 || (pooldetail::AroundFits(g_pool, npr * pw, pooled, pool_end) &&
+                           pooldetail::AroundFits(g_grad, npr * pw, gpooled, grad_end)));
+      if (bulk && threadIdx.x == 0) {
+        tma::BarrierExpect(&bar, pooldetail::AroundBytes(g_src, nrows * w) +
+                                     (npr == 0 ? 0u : pooldetail::AroundBytes(g_pool, npr * pw) +
+                                                          pooldetail::AroundBytes(g_grad, npr * pw)));
+      }
+      pooldetail::StageAround(r_src, g_src, nrows * w, src, src_end, bulk, &bar, &off_s);
+      if (npr > 0) {
+        pooldetail::StageAround(r_pool, g_pool, npr * pw, pooled, pool_end, bulk, &bar, &off_p);
+        pooldetail::StageAround(r_grad, g_grad, npr * pw, gpooled, grad_end, bulk, &bar, &off_g);
+      }
+    } else {
+      pooldetail::StagePitched(r_src, g_src, nrows, w, ld_src);
+      pooldetail::StagePitched(r_pool, g_pool, npr, pw, ld_pooled);
+      pooldetail::StagePitched(r_grad, g_grad, npr, pw, ld_pooled);
+    }
+    if (bulk) {
+      if (!tma::WaitBounded(&bar, phase)) {
+        if (threadIdx.x == 0) atomicExch(status, tma::kStatusBulkCopyTimeout);
+        tma::WaitBounded(&bar, phase);
+        return;
+      }
+      phase ^= 1;
+    } else {
+      __syncthreads();
+    }
+    const float *s_src = r_src + off_s;
+    // pooled row py of the plane sits at pp + (py - py_lo) * pw; fold the offset into the base
+    const float *pp = r_pool + off_p - static_cast<int64_t>(py_lo) * pw;
+    const float *gp = r_grad + off_g - static_cast<int64_t>(py_lo) * pw;
+    float *out_band = dst + (static_cast<int64_t>(p) * h + y0) * ld_dst;
+    if (kQuad && (w & 3u) == 0 && (off_s & 3u) == 0) {
+      constexpr int kSXs = SX > 0 ? SX : 1, kSYs = SY > 0 ? SY : 1;
+      constexpr int kOff = pooldetail::FloorDiv(kSXs - KX, kSXs);
+      constexpr int kCols = (3 / kSXs + 1) - kOff;
+      constexpr int kRows = (KY - 1) / kSYs + 1;
+      constexpr uint32_t kKYs = KY > 0 ? KY : 1;
+      const uint32_t wq = w >> 2;
+      const uint32_t nq = nrows * wq;
+      for (uint32_t it = threadIdx.x; it < nq; it += kPoolThreads) {
+        const uint32_t ly = div_wq.Quot(it);
+        const uint32_t xq = it - ly * wq;
+        const uint32_t y = y0 + ly;
+        const float4 sv4 = *reinterpret_cast<const float4 *>(s_src + ly * w + 4 * xq);
+        const float sv[4] = {sv4.x, sv4.y, sv4.z, sv4.w};
+        const int py_first = y < kKYs ? 0 : static_cast<int>((y - kKYs + kSYs) / kSYs);
+        const int py_hi = min(static_cast<int>((y + kSYs) / kSYs), static_cast<int>(ph));
+        const int pxb = static_cast<int>(xq) * (4 / kSXs) + kOff;
+        float val[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+#pragma unroll
+        for (int r = 0; r < kRows; ++r) {
+          const int py = py_first + r;
+          if (py < py_hi) {
+#pragma unroll
+            for (int cc = 0; cc < kCols; ++cc) {
+              const int px = pxb + cc;
+              if (px >= 0 && px < static_cast<int>(pw)) {
+                const float pv = pp[py * static_cast<int>(pw) + px];
+                const float gv = gp[py * static_cast<int>(pw) + px];
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                  const int lo = pooldetail::FloorDiv(i - KX + kSXs, kSXs) - kOff;
+                  const int hi = i / kSXs + 1 - kOff;
+                  if (cc >= lo && cc < hi) {
+                    val[i] = __fadd_rn(val[i], __fmul_rn(Reducer::PartialGrad(sv[i], pv), gv));
+                  }
+                }
+              }
+            }
+          }
+        }
+        float *out = out_band + static_cast<int64_t>(ly) * ld_dst + 4 * xq;
+        if (vec_out) {
+          __stcs(reinterpret_cast<float4 *>(out), make_float4(val[0], val[1], val[2], val[3]));
+        } else {
+          out[0] = val[0];
+          out[1] = val[1];
+          out[2] = val[2];
+          out[3] = val[3];
+        }
+      }
+    } else {
+      const uint32_t n = nrows * w;
+      for (uint32_t o = threadIdx.x; o < n; o += kPoolThreads) {
+        const uint32_t ly = div_w.Quot(o);
+        const uint32_t x = o - ly * w;
+        const uint32_t y = y0 + ly;
+        const float vsrc = s_src[o];
+        const uint32_t py_min = y < ky ? 0 : (SY > 0 ? (y - ky + sy) / sy : div_sy.Quot(y - ky + sy));
+        const uint32_t px_min = x < kx ? 0 : (SX > 0 ? (x - kx + sx) / sx : div_sx.Quot(x - kx + sx));
+        const uint32_t py_max = min(SY > 0 ? (y + sy) / sy : div_sy.Quot(y + sy), ph);
+        const uint32_t px_max = min(SX > 0 ? (x + sx) / sx : div_sx.Quot(x + sx), pw);
+        float val = 0.0f;
+        for (uint32_t py = py_min; py < py_max; ++py)
+          for (uint32_t px = px_min; px < px_max; ++px) {
+            const float pg = Reducer::PartialGrad(vsrc, pp[py * pw + px]);
+            val = __fadd_rn(val, __fmul_rn(pg, gp[py * pw + px]));
+          }
+        out_band[static_cast<int64_t>(ly) * ld_dst + x] = val;
+      }
+    }
+    tma::FenceAsyncShared();
+    __syncthreads();
+  }
+}
+
 /*!
  * \brief channel-window pooling with stride 1 and pad NSIZE/2 (the chpool(src, nsize) form).
  *  A thread owns kLanes adjacent pixels of one image and marches over the channels with the
@@ -687,6 +992,119 @@ inline void UnpoolPlanesLaunch(float *dst, const float *src, const float *pooled
   else MSHADOW_B200_UNPOOL_LAUNCH_(0, 0, 0, 0)
 #undef MSHADOW_B200_UNPOOL_LAUNCH_
   MSHADOW_CUDA_POST_KERNEL_CHECK(UnpoolPlanesKernel);
+}
+
+/*! \brief launch shape of the band kernels for planes beyond shared memory; ok == false: not applicable */
+struct BandPlan {
+  uint32_t band_rows, bands, pooled_rows;
+  size_t smem;
+  bool ok;
+};
+
+/*! \brief forward: as many output rows per band as the budget allows, bands of equal height */
+inline BandPlan PlanPoolBands(int64_t h, int64_t w, int64_t ph, int ky, int sy) {
+  BandPlan bp = {0, 0, 0, 0, false};
+  const uint64_t budget = static_cast<uint64_t>(MSHADOW_B200_POOL_BAND_SMEM_KB) * 1024;
+  if (h * w >= (int64_t(1) << 31) || ph < 1) return bp;
+  const uint64_t rows_cap = (budget - 64) / (static_cast<uint64_t>(w) * 4);
+  if (rows_cap < static_cast<uint64_t>(ky)) return bp;
+  const uint64_t out_cap = (rows_cap - ky) / sy + 1;
+  bp.bands = static_cast<uint32_t>((ph + out_cap - 1) / out_cap);
+  bp.band_rows = static_cast<uint32_t>((ph + bp.bands - 1) / bp.bands);
+  bp.bands = static_cast<uint32_t>((ph + bp.band_rows - 1) / bp.band_rows);
+  bp.smem = ((static_cast<size_t>(bp.band_rows - 1) * sy + ky) * w + 8) * 4;
+  bp.ok = true;
+  return bp;
+}
+
+/*! \brief backward: the fewest bands of source rows whose staged ranges fit the budget */
+inline BandPlan PlanUnpoolBands(int64_t h, int64_t w, int64_t ph, int64_t pw, int ky, int sy) {
+  BandPlan bp = {0, 0, 0, 0, false};
+  if (h * w >= (int64_t(1) << 31) || h < 1) return bp;
+  for (uint32_t bands = 1; bands <= static_cast<uint32_t>(h); ++bands) {
+    const uint32_t br = static_cast<uint32_t>((h + bands - 1) / bands);
+    uint32_t prc = 0;
+    for (uint32_t y0 = 0; y0 < static_cast<uint32_t>(h); y0 += br) {
+      const uint32_t nrows = static_cast<uint32_t>(h) - y0 < br ? static_cast<uint32_t>(h) - y0 : br;
+      const uint32_t lo = y0 < static_cast<uint32_t>(ky) ? 0 : (y0 - ky + sy) / sy;
+      uint32_t top = (y0 + nrows - 1 + sy) / sy;
+      if (top > static_cast<uint32_t>(ph)) top = static_cast<uint32_t>(ph);
+      if (top > lo && top - lo > prc) prc = top - lo;
+    }
+    const size_t smem = ((((static_cast<size_t>(br) * w + 3) & ~size_t(3)) + 8) +
+                         2 * (((static_cast<size_t>(prc) * pw + 3) & ~size_t(3)) + 8)) * 4;
+    if (smem <= kUnpoolSmemBudget) {
+      bp.band_rows = br;
+      bp.bands = static_cast<uint32_t>((h + br - 1) / br);
+      bp.pooled_rows = prc;
+      bp.smem = smem;
+      bp.ok = true;
+      return bp;
+    }
+    if (br == 1) break;
+  }
+  return bp;
+}
+
+template <typename Reducer>
+inline void PoolBandsLaunch(float *dst, const float *src, int64_t planes, int64_t h, int64_t w, int ky, int kx, int sy,
+                            int sx, int64_t ld_src, int64_t ld_dst, const BandPlan &bp, cudaStream_t stream) {
+  const uint32_t ph = static_cast<uint32_t>((h - ky) / sy + 1), pw = static_cast<uint32_t>((w - kx) / sx + 1);
+  if (planes == 0) return;
+  CHECK_LT(planes * static_cast<int64_t>(bp.bands), int64_t(1) << 31) << "pool: too many bands";
+  const uint32_t items = static_cast<uint32_t>(planes) * bp.bands;
+  const uint32_t cap = static_cast<uint32_t>(gpu_rt::CurrentDevice().sm_count) * 16;
+  const uint32_t grid = items < cap ? items : cap;
+  const PoolGeom g = {ky, kx, sy, sx};
+  int *status = pooldetail::StatusWord();
+#define MSHADOW_B200_POOL_BANDS_(KY, KX, SY, SX)                                                                  \
+  {                                                                                                               \
+    auto kernel = PoolBandsKernel<Reducer, KY, KX, SY, SX>;                                                       \
+    MSHADOW_CUDA_CALL(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,                   \
+                                           MSHADOW_B200_POOL_BAND_SMEM_KB * 1024));                               \
+    kernel<<<grid, kPoolThreads, bp.smem, stream>>>(dst, src, static_cast<uint32_t>(planes),                     \
+                                                   static_cast<uint32_t>(h), static_cast<uint32_t>(w), ph, pw, g, \
+                                                   ld_src, ld_dst, bp.band_rows, bp.bands,                        \
+                                                   gpu_rt::FastDiv(bp.bands), gpu_rt::FastDiv(pw),                \
+                                                   gpu_rt::FastDiv((pw + 1) / 2), status);                        \
+  }
+  if (ky == 3 && kx == 3 && sy == 2 && sx == 2) MSHADOW_B200_POOL_BANDS_(3, 3, 2, 2)
+  else if (ky == 2 && kx == 2 && sy == 2 && sx == 2) MSHADOW_B200_POOL_BANDS_(2, 2, 2, 2)
+  else MSHADOW_B200_POOL_BANDS_(0, 0, 0, 0)
+#undef MSHADOW_B200_POOL_BANDS_
+  MSHADOW_CUDA_POST_KERNEL_CHECK(PoolBandsKernel);
+}
+
+template <typename Reducer>
+inline void UnpoolBandsLaunch(float *dst, const float *src, const float *pooled, const float *gpooled, int64_t planes,
+                              int64_t h, int64_t w, int64_t ph, int64_t pw, int ky, int kx, int sy, int sx,
+                              int64_t ld_src, int64_t ld_pooled, int64_t ld_dst, const BandPlan &bp,
+                              cudaStream_t stream) {
+  if (planes == 0) return;
+  CHECK_LT(planes * static_cast<int64_t>(bp.bands), int64_t(1) << 31) << "unpool: too many bands";
+  const uint32_t items = static_cast<uint32_t>(planes) * bp.bands;
+  const uint32_t cap = static_cast<uint32_t>(gpu_rt::CurrentDevice().sm_count) * 16;
+  const uint32_t grid = items < cap ? items : cap;
+  const PoolGeom g = {ky, kx, sy, sx};
+  int *status = pooldetail::StatusWord();
+  const uint32_t uw = static_cast<uint32_t>(w);
+#define MSHADOW_B200_UNPOOL_BANDS_(KY, KX, SY, SX)                                                                \
+  {                                                                                                               \
+    auto kernel = UnpoolBandsKernel<Reducer, KY, KX, SY, SX>;                                                     \
+    MSHADOW_CUDA_CALL(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,                   \
+                                           static_cast<int>(kUnpoolSmemBudget)));                                 \
+    kernel<<<grid, kPoolThreads, bp.smem, stream>>>(                                                              \
+        dst, src, pooled, gpooled, static_cast<uint32_t>(planes), static_cast<uint32_t>(h), uw,                   \
+        static_cast<uint32_t>(ph), static_cast<uint32_t>(pw), g, ld_src, ld_pooled, ld_dst, bp.band_rows,         \
+        bp.bands, bp.pooled_rows, gpu_rt::FastDiv(bp.bands), gpu_rt::FastDiv(uw),                                 \
+        gpu_rt::FastDiv(uw / 4 > 0 ? uw / 4 : 1), gpu_rt::FastDiv(static_cast<uint32_t>(sy)),                     \
+        gpu_rt::FastDiv(static_cast<uint32_t>(sx)), status);                                                      \
+  }
+  if (ky == 3 && kx == 3 && sy == 2 && sx == 2) MSHADOW_B200_UNPOOL_BANDS_(3, 3, 2, 2)
+  else if (ky == 2 && kx == 2 && sy == 2 && sx == 2) MSHADOW_B200_UNPOOL_BANDS_(2, 2, 2, 2)
+  else MSHADOW_B200_UNPOOL_BANDS_(0, 0, 0, 0)
+#undef MSHADOW_B200_UNPOOL_BANDS_
+  MSHADOW_CUDA_POST_KERNEL_CHECK(UnpoolBandsKernel);
 }
 
 /*! \brief window sizes the register-ring channel kernel is instantiated for */

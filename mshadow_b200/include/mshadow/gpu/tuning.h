@@ -45,6 +45,9 @@
 #ifndef MSHADOW_B200_POOL_SMEM_KB
 #define MSHADOW_B200_POOL_SMEM_KB 28  // staged planes per CTA, forward pooling (14: 78 %, 28: 86 %, 56: 83 %)
 #endif
+#ifndef MSHADOW_B200_POOL_BAND_SMEM_KB
+#define MSHADOW_B200_POOL_BAND_SMEM_KB 48  // staged row band per CTA, forward pooling of planes beyond shared memory
+#endif
 #ifndef MSHADOW_B200_POOL_PAIRS
 #define MSHADOW_B200_POOL_PAIRS 1  // forward pooling 3 x 3 / 2: two adjacent outputs per thread from 16-byte loads
 #endif

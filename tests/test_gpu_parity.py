@@ -218,7 +218,12 @@ POOL_CASES = [(5, 6, 6, 2, 2, 2, 2, 0), (5, 13, 11, 3, 3, 2, 2, 0), (3, 8, 9, 3,
               (4, 10, 10, 2, 2, 3, 3, 0), (9, 56, 56, 3, 3, 2, 2, 0), (8, 27, 27, 3, 3, 2, 2, 0),
               (70, 12, 12, 2, 2, 2, 2, 0), (3, 130, 120, 5, 4, 3, 2, 0),
               # 3 x 3 / 2 on widths that are multiples of four (two outputs per thread), dense and pitched
-              (6, 20, 24, 3, 3, 2, 2, 4), (33, 9, 8, 3, 3, 2, 2, 0), (2, 64, 128, 3, 3, 2, 2, 0)]
+              (6, 20, 24, 3, 3, 2, 2, 4), (33, 9, 8, 3, 3, 2, 2, 0), (2, 64, 128, 3, 3, 2, 2, 0),
+              # planes beyond shared memory: bands of rows (aligned widths, odd widths whose bands start off a
+              # 16-byte boundary, a general window, pitched rows, a single plane, 2 x 2 windows)
+              (3, 112, 112, 3, 3, 2, 2, 0), (2, 224, 224, 3, 3, 2, 2, 0), (2, 513, 517, 3, 3, 2, 2, 0),
+              (1, 513, 517, 5, 4, 3, 2, 0), (3, 150, 131, 3, 3, 2, 2, 3), (1, 300, 260, 2, 2, 2, 2, 0),
+              (5, 97, 203, 3, 3, 1, 1, 0)]
 
 
 @pytest.mark.parametrize("reducer", [0, 1, 2])
