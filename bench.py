@@ -413,6 +413,14 @@ def kernel_cases(lib, torch, small=False):
     yield ("softmax_grad_fused", "Softmax+SoftmaxGrad fused %dx%d" % (r, c), 8 * r * c + 4 * r, r * c,
            lambda: lib.softmax_grad_fused(Gd, L, lab), 10)
     del L, P, Gd
+    # rows beyond one CTA's registers: held by a cluster of four CTAs (131072 columns), and rows beyond that
+    # (2^20 columns: one pass with a running max and sum, second read from the L2)
+    for key, (rl, cl) in (("softmax_long", (512, 1 << 17) if small else (2048, 1 << 17)),
+                          ("softmax_very_long", (16, 1 << 20) if small else (64, 1 << 20))):
+        LL = torch.randn(rl, cl, device=dev, generator=g) * 2
+        PLr = torch.empty(rl, cl, device=dev)
+        yield (key, "Softmax %dx%d" % (rl, cl), 8 * rl * cl, rl * cl, lambda: lib.softmax(PLr, LL), 10)
+        del LL, PLr
     # C4: pooling
     imgs = 32 if small else 256
     X = torch.rand(imgs * 256, 56, 56, device=dev, generator=g)

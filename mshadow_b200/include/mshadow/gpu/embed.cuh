@@ -27,12 +27,15 @@
 #include <cub/device/device_radix_sort.cuh>
 
 #include "./runtime.h"
+#include "./tma.cuh"
 
 namespace mshadow {
 namespace cuda {
 
 const uint32_t kSegChunk = MSHADOW_B200_SEG_CHUNK;
 const int kSegDepth = MSHADOW_B200_SEG_DEPTH;
+const uint32_t kSegRing = MSHADOW_B200_SEG_RING;       // source rows in flight per CTA of the staged kernel
+const uint32_t kSegSlab = 1024;                        // features per CTA: 256 threads x 4
 
 /*!
  * \brief one level of the chunked segmented sum.
@@ -147,6 +150,135 @@ SegmentSumKernel(float *dst, int64_t ld_dst, const int32_t *keys, const int32_t 
   flush(true);
 }
 
+/*!
+ * \brief the same level of the segmented sum with the source rows staged through shared memory.
+ *  SegmentSumKernel keeps kSegDepth 16-byte loads in flight per thread and then waits for them:
+ *  measured, its warps spend most of their time on those loads.  Here a producer warp issues
+ *  one bulk asynchronous copy per source row (a row's slab of up to 1024 features is contiguous
+ *  and 16-byte aligned) into a ring of kSegRing shared-memory slots, up to kSegRing rows ahead;
+ *  the eight consumer warps take the rows from shared memory in list order.  Each slot has a
+ *  `full` barrier (the copy has landed) and an `empty` barrier (every consumer warp has read
+ *  it), so no step synchronises the whole CTA.  Keys and row numbers of the chunk are brought
+ *  into shared memory once.  Arithmetic, run handling and results are SegmentSumKernel<4>'s.
+ *  Block: 256 consumer threads + one producer warp.  Dynamic shared memory: kSegRing * 4 KB.
+ *  (A template only so that the header can be included from several translation units.)
+ */
+template <int kRingSlots>
+__global__ void __launch_bounds__(288, MSHADOW_B200_SEG_MIN_CTAS)
+SegmentSumStagedKernel(float *dst, int64_t ld_dst, const int32_t *keys, const int32_t *rows, const float *src,
+                       int64_t ld_src, uint32_t n, uint32_t width, int32_t *part_keys, int32_t *part_rows,
+                       float *partials, int *status) {
+  extern __shared__ __align__(16) float ring[];
+  __shared__ uint64_t full[kSegRing], empty[kSegRing];
+  __shared__ int32_t s_keys[kSegChunk], s_rows[kSegChunk];
+  const uint32_t chunk = blockIdx.x;
+  const uint32_t begin = chunk * kSegChunk;
+  const uint32_t end = min(n, begin + kSegChunk);
+  const uint32_t cnt = end - begin;
+  const uint32_t col0 = blockIdx.y * kSegSlab;
+  const uint32_t slab_w = min(kSegSlab, width - col0);  // a multiple of 4
+  const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (threadIdx.x < kSegChunk) {
+    const uint32_t e = begin + threadIdx.x;
+    s_keys[threadIdx.x] = e < end ? keys[e] : 0;
+    s_rows[threadIdx.x] = e < end ? (rows != nullptr ? rows[e] : static_cast<int32_t>(e)) : -1;
+  }
+  if (threadIdx.x == 0) {
+    for (uint32_t j = 0; j < kSegRing; ++j) {
+      tma::BarrierInit(&full[j], 1);
+      tma::BarrierInit(&empty[j], 8);
+    }
+  }
+  __syncthreads();
+  if (warp == 8) {
+    // producer: one thread issues the copies in list order; a slot is refilled once the consumers
+    // have released the row it held (slots are released in the order they were filled)
+    if (lane != 0) return;
+    for (uint32_t e = 0; e < cnt; ++e) {
+      const uint32_t slot = e % kSegRing, use = e / kSegRing;
+      if (use > 0 && !tma::WaitBounded(&empty[slot], (use - 1) & 1u)) {
+        atomicExch(status, tma::kStatusBulkCopyTimeout);
+        return;
+      }
+      const int32_t r = s_rows[e];
+      if (r >= 0) {
+        tma::BarrierExpect(&full[slot], slab_w * 4u);
+        tma::BulkLoad(ring + static_cast<size_t>(slot) * kSegSlab, src + static_cast<int64_t>(r) * ld_src + col0,
+                      slab_w * 4u, &full[slot]);
+      } else {
+        // an entry without a source row still takes its turn on the slot: the consumers wait for
+        // `full` on every entry, so they can never release a slot twice before this thread has
+        // seen the first release
+        tma::BarrierArrive(&full[slot]);
+      }
+    }
+    return;
+  }
+  const uint32_t col = col0 + threadIdx.x * 4;
+  const bool active = threadIdx.x * 4 < slab_w;
+  const bool lead = blockIdx.y == 0 && threadIdx.x == 0;
+  const bool joins_prev = chunk > 0 && keys[begin - 1] == s_keys[0];
+  const bool joins_next = end < n && keys[end] == s_keys[cnt - 1];
+  if (lead && part_rows != nullptr) {
+    part_keys[2 * chunk] = s_keys[0];
+    part_keys[2 * chunk + 1] = s_keys[cnt - 1];
+    part_rows[2 * chunk] = -1;
+    part_rows[2 * chunk + 1] = -1;
+  }
+  int32_t cur = s_keys[0];
+  bool first_run = true, any = false;
+  float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+  auto flush = [&](bool last_run) {
+    const bool spans = (first_run && joins_prev) || (last_run && joins_next);
+    if (!spans) {
+      if (any && active) {
+        float *row = dst + static_cast<int64_t>(cur) * ld_dst + col;
+        float4 d = *reinterpret_cast<float4 *>(row);
+        d.x = __fadd_rn(d.x, acc[0]);
+        d.y = __fadd_rn(d.y, acc[1]);
+        d.z = __fadd_rn(d.z, acc[2]);
+        d.w = __fadd_rn(d.w, acc[3]);
+        *reinterpret_cast<float4 *>(row) = d;
+      }
+    } else if (any) {
+      const uint32_t slot = 2 * chunk + (first_run ? 0 : 1);
+      if (active) {
+        *reinterpret_cast<float4 *>(partials + static_cast<int64_t>(slot) * width + col) =
+            make_float4(acc[0], acc[1], acc[2], acc[3]);
+      }
+      if (lead) part_rows[slot] = static_cast<int32_t>(slot);
+    }
+  };
+  for (uint32_t e = 0; e < cnt; ++e) {
+    const uint32_t slot = e % kSegRing;
+    const int32_t k = s_keys[e], r = s_rows[e];
+    if (k != cur) {
+      flush(false);
+      cur = k;
+      first_run = false;
+      any = false;
+      acc[0] = acc[1] = acc[2] = acc[3] = 0.0f;
+    }
+    if (!tma::WaitBounded(&full[slot], (e / kSegRing) & 1u)) {
+      if (lane == 0) atomicExch(status, tma::kStatusBulkCopyTimeout);
+      return;
+    }
+    if (r >= 0) {
+      if (active) {
+        const float4 v = *reinterpret_cast<const float4 *>(ring + static_cast<size_t>(slot) * kSegSlab + threadIdx.x * 4);
+        acc[0] = __fadd_rn(acc[0], v.x);
+        acc[1] = __fadd_rn(acc[1], v.y);
+        acc[2] = __fadd_rn(acc[2], v.z);
+        acc[3] = __fadd_rn(acc[3], v.w);
+      }
+      any = true;
+    }
+    __syncwarp();
+    if (lane == 0) tma::BarrierArrive(&empty[slot]);
+  }
+  flush(true);
+}
+
 /*! \brief keys[i] = clip(index[i], 0, k-1), vals[i] = i */
 template <typename IndexType>
 __global__ void ClipIotaKernel(IndexType *keys, IndexType *vals, const IndexType *index, uint32_t n, IndexType k) {
@@ -213,7 +345,14 @@ inline void SegmentSumRun(float *dst, int64_t ld_dst, const int32_t *keys, const
     uint32_t threads = (items + 31) / 32 * 32;
     if (threads > 256) threads = 256;
     const dim3 grid(chunks[l], (items + threads - 1) / threads);
-    if (vec) {
+    if (vec && MSHADOW_B200_SEG_STAGED && width >= 256) {
+      // rows of a kilobyte and more: staged through shared memory by bulk copies
+      auto kernel = SegmentSumStagedKernel<static_cast<int>(kSegRing)>;
+      const size_t smem = static_cast<size_t>(kSegRing) * kSegSlab * sizeof(float);
+      MSHADOW_CUDA_CALL(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
+      kernel<<<dim3(chunks[l], (width + kSegSlab - 1) / kSegSlab), 288, smem, stream>>>(
+          dst, ld_dst, lkeys, lrows, lsrc, lld, entries[l], width, pk, pr, pp, gpu_rt::StatusWord());
+    } else if (vec) {
       SegmentSumKernel<4><<<grid, threads, 0, stream>>>(dst, ld_dst, lkeys, lrows, lsrc, lld, entries[l], width, pk,
                                                        pr, pp);
     } else {

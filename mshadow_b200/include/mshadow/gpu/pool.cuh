@@ -788,12 +788,15 @@ ChannelUnpoolKernel(float *dst, const float *src, const float *pooled, const flo
 /*!
  * \brief channel-window pooling with the channel planes staged through shared memory.
  *  Same arithmetic as ChannelPoolKernel (window kept in registers, channels added in
- *  ascending order), but the thread no longer waits on its own global loads: one thread
- *  issues a bulk asynchronous copy per channel plane (or plane tile) into a ring of `ring`
- *  shared-memory slots, `ring` channels ahead of the march, so a CTA keeps ring * tile bytes
- *  in flight at no register cost and reads memory in long contiguous pieces.
- *  CTA = (image, pixel tile) x channel segment; thread = 4 adjacent pixels.
- *  Dynamic shared memory: ring * tile_px floats.
+ *  ascending order), but no thread waits on its own global loads: a producer thread issues
+ *  one bulk asynchronous copy per channel plane (or plane tile) into a ring of `ring`
+ *  shared-memory slots, up to `ring` channels ahead of the march, so a CTA keeps
+ *  ring * tile bytes in flight at no register cost and reads memory in long contiguous pieces.
+ *  Every slot has two transaction barriers: `full` completes when the copy has landed,
+ *  `empty` when every consumer warp has read the slot (one arrival per warp).  Warps therefore
+ *  drift apart freely; nothing in the march synchronises the whole CTA.
+ *  CTA = (image, pixel tile) x channel segment; warps 0 .. n-2 consume, 4 adjacent pixels per
+ *  thread, the last warp produces.  Dynamic shared memory: ring * tile_px floats.
  */
 template <typename Reducer, int NSIZE>
 __global__ void __launch_bounds__(1024, 1)
@@ -802,7 +805,7 @@ ChannelPoolStagedKernel(float *dst, const float *src, uint32_t channels, uint32_
   constexpr int kPad = NSIZE / 2;
   constexpr uint32_t kMaxRing = 16;
   extern __shared__ __align__(16) float slots[];
-  __shared__ uint64_t bars[kMaxRing];
+  __shared__ uint64_t full[kMaxRing], empty[kMaxRing];
   const uint32_t image_idx = blockIdx.x / tiles_per_plane;
   const uint32_t tile_idx = blockIdx.x - image_idx * tiles_per_plane;
   const uint32_t px0 = tile_idx * tile_px;
@@ -813,28 +816,44 @@ ChannelPoolStagedKernel(float *dst, const float *src, uint32_t channels, uint32_
   const float *in = src + base;
   float *out = dst + base;
   const uint32_t nsteps = (c_end - c_begin) + 2 * kPad;  // channels c_begin-kPad .. c_end-1+kPad
-  const bool mine = threadIdx.x * 4 < len;
+  const uint32_t consumer_warps = (blockDim.x >> 5) - 1;
+  const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   if (threadIdx.x == 0) {
-    for (uint32_t j = 0; j < ring; ++j) tma::BarrierInit(&bars[j], 1);
+    for (uint32_t j = 0; j < ring; ++j) {
+      tma::BarrierInit(&full[j], 1);
+      tma::BarrierInit(&empty[j], consumer_warps);
+    }
   }
   __syncthreads();
-  auto issue = [&](uint32_t step) {  // called by thread 0 only
-    const int64_t ch = static_cast<int64_t>(c_begin) - kPad + step;
-    if (step < nsteps && ch >= 0 && ch < static_cast<int64_t>(channels)) {
-      const uint32_t slot = step % ring;
-      tma::BarrierExpect(&bars[slot], len * 4u);
-      tma::BulkLoad(slots + static_cast<size_t>(slot) * tile_px, in + ch * plane, len * 4u, &bars[slot]);
+  if (warp == consumer_warps) {
+    // producer: step s uses slot s % ring for the (s / ring)-th time, once the consumers have
+    // released its previous use
+    if (lane != 0) return;
+    for (uint32_t s = 0; s < nsteps; ++s) {
+      const uint32_t slot = s % ring, use = s / ring;
+      if (use > 0 && !tma::WaitBounded(&empty[slot], (use - 1) & 1u)) {
+        atomicExch(status, tma::kStatusBulkCopyTimeout);
+        return;
+      }
+      const int64_t ch = static_cast<int64_t>(c_begin) - kPad + s;
+      if (ch >= 0 && ch < static_cast<int64_t>(channels)) {
+        tma::BarrierExpect(&full[slot], len * 4u);
+        tma::BulkLoad(slots + static_cast<size_t>(slot) * tile_px, in + ch * plane, len * 4u, &full[slot]);
+      } else {
+        // a channel outside the tensor still takes its turn on the slot: the consumers wait for
+        // `full` at every step, so they can never release a slot twice before this thread has
+        // seen the first release
+        tma::BarrierArrive(&full[slot]);
+      }
     }
-  };
-  if (threadIdx.x == 0) {
-    for (uint32_t j = 0; j < ring; ++j) issue(j);
+    return;
   }
+  const bool mine = threadIdx.x * 4 < len;
   float init;
   Reducer::SetInitValue(init);
   float win[NSIZE][4];
 #pragma unroll
   for (int j = 0; j < NSIZE; ++j) win[j][0] = win[j][1] = win[j][2] = win[j][3] = init;
-  uint32_t phase_bits = 0;  // expected parity per ring slot; identical in every thread
   for (uint32_t s0 = 0; s0 < nsteps; s0 += NSIZE) {
 #pragma unroll
     for (int j = 0; j < NSIZE; ++j) {
@@ -843,20 +862,16 @@ ChannelPoolStagedKernel(float *dst, const float *src, uint32_t channels, uint32_
         const int64_t ch = static_cast<int64_t>(c_begin) - kPad + s;
         const uint32_t slot = s % ring;
         float4 v = make_float4(init, init, init, init);
-        if (ch >= 0 && ch < static_cast<int64_t>(channels)) {
-          if (!tma::WaitBounded(&bars[slot], (phase_bits >> slot) & 1u)) {
-            if (threadIdx.x == 0) atomicExch(status, tma::kStatusBulkCopyTimeout);
-            tma::WaitBounded(&bars[slot], (phase_bits >> slot) & 1u);
-            return;
-          }
-          phase_bits ^= 1u << slot;
-          if (mine) v = *reinterpret_cast<const float4 *>(slots + static_cast<size_t>(slot) * tile_px + threadIdx.x * 4);
+        if (!tma::WaitBounded(&full[slot], (s / ring) & 1u)) {
+          if (lane == 0) atomicExch(status, tma::kStatusBulkCopyTimeout);
+          return;
         }
-        __syncthreads();  // the slot has been read by everyone: refill it `ring` channels ahead
-        if (threadIdx.x == 0) {
-          tma::FenceAsyncShared();
-          issue(s + ring);
+        if (ch >= 0 && ch < static_cast<int64_t>(channels) && mine) {
+          v = *reinterpret_cast<const float4 *>(slots + static_cast<size_t>(slot) * tile_px + threadIdx.x * 4);
         }
+        // this warp is done with the slot (the producer counts one release per warp and step)
+        __syncwarp();
+        if (lane == 0) tma::BarrierArrive(&empty[slot]);
         win[j][0] = v.x;
         win[j][1] = v.y;
         win[j][2] = v.z;
@@ -1142,10 +1157,11 @@ inline void ChannelPoolLaunch(float *dst, const float *src, int64_t n, int64_t c
     kernel<<<dim3(tiles, nseg), kPoolThreads, 0, stream>>>(dst, src, static_cast<uint32_t>(c), plane, groups,  \
                                                             items, gpu_rt::FastDiv(groups), seg_len);          \
   }
-  // staged variant: planes (or plane tiles of at most 4096 pixels) ride through a shared-memory ring
-  const uint32_t tiles_per_plane = (plane + 4095) / 4096;
+  // staged variant: planes (or plane tiles of at most 3968 pixels: 31 consumer warps of 128 pixels and one
+  // producer warp make a 1024-thread CTA) ride through a shared-memory ring
+  const uint32_t tiles_per_plane = (plane + 3967) / 3968;
   const uint32_t tile_px = ((plane + tiles_per_plane - 1) / tiles_per_plane + 3) & ~3u;
-  const uint32_t st_threads = ((tile_px / 4) + 31) & ~31u;
+  const uint32_t st_threads = (((tile_px / 4) + 31) & ~31u) + 32;
   const bool staged = vec && MSHADOW_B200_CHPOOL_STAGED && c >= 2 * nsize &&
                       n * static_cast<int64_t>(tiles_per_plane) < (int64_t(1) << 31);
 #define MSHADOW_B200_CHPOOL_STAGED_LAUNCH_(NS)                                                                 \

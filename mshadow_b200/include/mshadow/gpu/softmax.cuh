@@ -5,9 +5,10 @@
  * which walks each row three times through global memory (20 bytes of traffic per element)
  * with 256 threads.  Here a CTA loads its row once into registers (up to 32 floats per
  * thread), finds the maximum, exponentiates and sums in registers, and writes the
- * normalised row once: 8 bytes per element, the algorithmic minimum.  Rows that do not fit
- * the register budget (more than 32768 columns) fall back to a three-sweep kernel whose
- * second and third sweeps mostly hit the L2 cache.
+ * normalised row once: 8 bytes per element, the algorithmic minimum.  Rows of more than 32768
+ * columns are held in the registers of a thread-block cluster (up to 8 x 32768 columns); rows
+ * beyond that are read once from HBM with a running (maximum, sum) pair per thread and a
+ * second time from the L2 for the normalisation.
  *
  * The arithmetic follows the reference's CPU definition (mshadow/tensor_cpu-inl.h:270-285):
  * exp(x - max) with true division by the sum.  The sum is formed pairwise (registers, warp
@@ -236,29 +237,227 @@ SoftmaxStagedKernel(float *dst, const float *src, const float *label, uint32_t r
   }
 }
 
-/*! \brief any row length: three sweeps over global memory, one CTA per row */
-template <int kThreads>
+/*!
+ * \brief rows of up to 8 x 32768 columns: the row is resident in the registers of a thread-block
+ *  CLUSTER.  grid.x = cluster size; CTA `rank` holds columns [rank * seg, (rank + 1) * seg), kItems
+ *  16-byte items per thread.  The CTAs agree on the row maximum and on the sum through distributed
+ *  shared memory (each publishes its value, all read all, in rank order), everything else is
+ *  SoftmaxRowKernel: one read of the row from HBM, one exp per element, one write.
+ *  A CTA loads, computes and stores in turn, so the launcher prefers 512-thread CTAs (two or
+ *  three per SM, whose phases overlap) whenever a cluster of eight of them covers the row.
+ */
+template <int kThreads, int kItems>
 __global__ void __launch_bounds__(kThreads)
-SoftmaxSweepKernel(float *dst, const float *src, const float *label, uint32_t rows, uint32_t cols, int64_t ld_dst,
-                   int64_t ld_src) {
+SoftmaxClusterRowKernel(float *dst, const float *src, const float *label, uint32_t rows, uint32_t cols,
+                        int64_t ld_dst, int64_t ld_src, uint32_t seg) {
   __shared__ float buf[32];
-  for (uint32_t y = blockIdx.x; y < rows; y += gridDim.x) {
-    const float *in = src + y * ld_src;
-    float *out = dst + y * ld_dst;
+  // published values alternate between two places from row to row: a CTA may still be reading
+  // row y's values when a faster one publishes row y + 1's, and by the time row y + 2 reuses the
+  // place every CTA has passed a cluster barrier of row y + 1
+  __shared__ float cta_max_buf[2], cta_sum_buf[2];
+  cg::cluster_group cluster = cg::this_cluster();
+  const unsigned csize = cluster.num_blocks(), crank = cluster.block_rank();
+  const uint32_t x0 = crank * seg;
+  const uint32_t x1 = min(cols, x0 + seg);
+  const uint32_t nitems = x1 > x0 ? (x1 - x0) / 4 : 0;  // cols and seg are multiples of 4
+  uint32_t flip = 0;
+  for (uint32_t y = blockIdx.y; y < rows; y += gridDim.y, flip ^= 1u) {
+    float &cta_max = cta_max_buf[flip];
+    float &cta_sum = cta_sum_buf[flip];
+    const float4 *in = reinterpret_cast<const float4 *>(src + y * ld_src + x0);
+    float4 *out = reinterpret_cast<float4 *>(dst + y * ld_dst + x0);
+    float v[kItems][4];
+#pragma unroll
+    for (int k = 0; k < kItems; ++k) {
+      const uint32_t item = threadIdx.x + k * kThreads;
+      if (item < nitems) {
+        const float4 p = __ldcs(in + item);
+        v[k][0] = p.x, v[k][1] = p.y, v[k][2] = p.z, v[k][3] = p.w;
+      } else {
+        v[k][0] = v[k][1] = v[k][2] = v[k][3] = -FLT_MAX;
+      }
+    }
     float m = -FLT_MAX;
-    for (uint32_t x = threadIdx.x; x < cols; x += kThreads) m = m < in[x] ? in[x] : m;
+#pragma unroll
+    for (int k = 0; k < kItems; ++k)
+#pragma unroll
+      for (int l = 0; l < 4; ++l) m = m < v[k][l] ? v[k][l] : m;
     m = smdetail::BlockAll<smdetail::MaxOp, kThreads>(m, buf);
+    if (threadIdx.x == 0) cta_max = m;
+    cluster.sync();
+    for (unsigned r = 0; r < csize; ++r) {
+      const float o = *cluster.map_shared_rank(&cta_max, r);
+      m = m < o ? o : m;
+    }
     float s = 0.0f;
-    for (uint32_t x = threadIdx.x; x < cols; x += kThreads) {
-      const float e = expf(__fsub_rn(in[x], m));
-      out[x] = e;
-      s = __fadd_rn(s, e);
+#pragma unroll
+    for (int k = 0; k < kItems; ++k) {
+      const bool in_row = threadIdx.x + k * kThreads < nitems;
+#pragma unroll
+      for (int l = 0; l < 4; ++l) {
+        v[k][l] = in_row ? expf(__fsub_rn(v[k][l], m)) : 0.0f;
+        s = __fadd_rn(s, v[k][l]);
+      }
     }
     s = smdetail::BlockAll<smdetail::SumOp, kThreads>(s, buf);
+    if (threadIdx.x == 0) cta_sum = s;
+    cluster.sync();
+    s = *cluster.map_shared_rank(&cta_sum, 0);
+    for (unsigned r = 1; r < csize; ++r) s = __fadd_rn(s, *cluster.map_shared_rank(&cta_sum, r));
+    const int hot = label != nullptr ? static_cast<int>(label[y]) - static_cast<int>(x0) : -1;
+    const float rcp = __frcp_rn(s);
+#pragma unroll
+    for (int k = 0; k < kItems; ++k) {
+      const uint32_t item = threadIdx.x + k * kThreads;
+      if (item < nitems) {
+        float q[4];
+#pragma unroll
+        for (int l = 0; l < 4; ++l) {
+          q[l] = smdetail::DivByReciprocal(v[k][l], s, rcp);
+          if (static_cast<int>(item * 4 + l) == hot) q[l] = __fsub_rn(q[l], 1.0f);
+        }
+        __stcs(out + item, make_float4(q[0], q[1], q[2], q[3]));
+      }
+    }
+  }
+  cluster.sync();  // no CTA leaves while others may still read its shared memory
+}
+
+namespace smdetail {
+/*! \brief running (maximum, sum of exp(x - maximum)) of a stream of values */
+struct MaxSum {
+  float m, s;
+};
+/*! \brief both streams as one: the sums are brought to the common maximum before they are added */
+__device__ __forceinline__ MaxSum Merge(MaxSum a, MaxSum b) {
+  MaxSum r;
+  r.m = a.m < b.m ? b.m : a.m;
+  r.s = __fadd_rn(__fmul_rn(a.s, expf(__fsub_rn(a.m, r.m))), __fmul_rn(b.s, expf(__fsub_rn(b.m, r.m))));
+  return r;
+}
+}  // namespace smdetail
+
+/*!
+ * \brief rows of any length, in particular those beyond the register budget of the kernels
+ *  above: ONE pass over HBM that keeps a running (maximum, sum) pair per thread -- when a new
+ *  maximum appears the sum so far is rescaled by exp(old - new) -- followed by a second read of
+ *  the row, which the L2 still holds (a row of 100 000 floats is 400 KB), to write
+ *  exp(x - max) / sum.  DRAM traffic is therefore the 8 bytes per element of the register
+ *  kernels, not the 20 of a max / exp-sum / normalise triple sweep.
+ *  A row is shared by the CTAs of a thread-block cluster (grid.x = cluster size, each CTA takes
+ *  a contiguous segment of the columns): few long rows would otherwise leave most SMs idle.
+ *  The CTAs exchange their pairs through distributed shared memory and every CTA merges them in
+ *  rank order, so all arrive at the same (max, sum).  exp(x - max) is evaluated with the row's
+ *  true maximum, exactly as the CPU evaluator does (mshadow/tensor_cpu-inl.h:270-285); only the
+ *  order of the additions in the sum differs.
+ */
+template <int kThreads, int kLanes>
+__global__ void __launch_bounds__(kThreads)
+SoftmaxOnlineKernel(float *dst, const float *src, const float *label, uint32_t rows, uint32_t cols, int64_t ld_dst,
+                    int64_t ld_src, uint32_t seg) {
+  __shared__ smdetail::MaxSum warp_pair[kThreads / 32];
+  __shared__ smdetail::MaxSum cta_pair;
+  cg::cluster_group cluster = cg::this_cluster();
+  const unsigned csize = cluster.num_blocks(), crank = cluster.block_rank();
+  const uint32_t x0 = crank * seg;
+  const uint32_t x1 = min(cols, x0 + seg);
+  for (uint32_t y = blockIdx.y; y < rows; y += gridDim.y) {
+    const float *in = src + y * ld_src;
+    float *out = dst + y * ld_dst;
+    smdetail::MaxSum acc = {-FLT_MAX, 0.0f};
+    constexpr int kDepth = 4;  // loads in flight per thread: 64 KB per CTA with 16-byte loads
+    for (uint32_t xb = x0 + threadIdx.x * kLanes; xb < x1; xb += kThreads * kLanes * kDepth) {
+      float v[kDepth][kLanes];
+#pragma unroll
+      for (int k = 0; k < kDepth; ++k) {
+        const uint32_t x = xb + k * kThreads * kLanes;
+        if (x < x1) {
+          if (kLanes == 4) {
+            const float4 p = __ldcg(reinterpret_cast<const float4 *>(in + x));  // the L2 keeps the row for the second read
+            v[k][0] = p.x, v[k][1 % kLanes] = p.y, v[k][2 % kLanes] = p.z, v[k][3 % kLanes] = p.w;
+          } else {
+            v[k][0] = __ldcg(in + x);
+          }
+        } else {
+#pragma unroll
+          for (int l = 0; l < kLanes; ++l) v[k][l] = -FLT_MAX;  // adds exp(-huge) = 0
+        }
+      }
+      float top = v[0][0];
+#pragma unroll
+      for (int k = 0; k < kDepth; ++k)
+#pragma unroll
+        for (int l = 0; l < kLanes; ++l) top = top < v[k][l] ? v[k][l] : top;
+      if (top > acc.m) {
+        acc.s = __fmul_rn(acc.s, expf(__fsub_rn(acc.m, top)));
+        acc.m = top;
+      }
+#pragma unroll
+      for (int k = 0; k < kDepth; ++k)
+#pragma unroll
+        for (int l = 0; l < kLanes; ++l) acc.s = __fadd_rn(acc.s, expf(__fsub_rn(v[k][l], acc.m)));
+    }
+    // warp, CTA, cluster
+#pragma unroll
+    for (int d = 16; d > 0; d >>= 1) {
+      smdetail::MaxSum o;
+      o.m = __shfl_xor_sync(0xffffffffu, acc.m, d);
+      o.s = __shfl_xor_sync(0xffffffffu, acc.s, d);
+      // lower lane first, so that both partners compute the same bits
+      acc = (threadIdx.x & d) ? smdetail::Merge(o, acc) : smdetail::Merge(acc, o);
+    }
+    if ((threadIdx.x & 31) == 0) warp_pair[threadIdx.x >> 5] = acc;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      smdetail::MaxSum t = warp_pair[0];
+      for (int wi = 1; wi < kThreads / 32; ++wi) t = smdetail::Merge(t, warp_pair[wi]);
+      cta_pair = t;
+    }
+    if (csize > 1) {
+      cluster.sync();
+    } else {
+      __syncthreads();
+    }
+    smdetail::MaxSum row = *cluster.map_shared_rank(&cta_pair, 0);
+    for (unsigned r = 1; r < csize; ++r) row = smdetail::Merge(row, *cluster.map_shared_rank(&cta_pair, r));
+    if (csize > 1) {
+      cluster.sync();  // every CTA has read the pairs before any of them is overwritten
+    } else {
+      __syncthreads();
+    }
     const int hot = label != nullptr ? static_cast<int>(label[y]) : -1;
-    for (uint32_t x = threadIdx.x; x < cols; x += kThreads) {
-      const float q = __fdiv_rn(out[x], s);
-      out[x] = static_cast<int>(x) == hot ? __fsub_rn(q, 1.0f) : q;
+    const float rcp = __frcp_rn(row.s);
+    for (uint32_t xb = x0 + threadIdx.x * kLanes; xb < x1; xb += kThreads * kLanes * kDepth) {
+      float v[kDepth][kLanes];
+#pragma unroll
+      for (int k = 0; k < kDepth; ++k) {
+        const uint32_t x = xb + k * kThreads * kLanes;
+        if (x < x1) {
+          if (kLanes == 4) {
+            const float4 p = __ldcs(reinterpret_cast<const float4 *>(in + x));  // last use of the row
+            v[k][0] = p.x, v[k][1 % kLanes] = p.y, v[k][2 % kLanes] = p.z, v[k][3 % kLanes] = p.w;
+          } else {
+            v[k][0] = __ldcs(in + x);
+          }
+        }
+      }
+#pragma unroll
+      for (int k = 0; k < kDepth; ++k) {
+        const uint32_t x = xb + k * kThreads * kLanes;
+        if (x < x1) {
+#pragma unroll
+          for (int l = 0; l < kLanes; ++l) {
+            const float q = smdetail::DivByReciprocal(expf(__fsub_rn(v[k][l], row.m)), row.s, rcp);
+            v[k][l] = static_cast<int>(x + l) == hot ? __fsub_rn(q, 1.0f) : q;
+          }
+          if (kLanes == 4) {
+            __stcs(reinterpret_cast<float4 *>(out + x),
+                   make_float4(v[k][0], v[k][1 % kLanes], v[k][2 % kLanes], v[k][3 % kLanes]));
+          } else {
+            __stcs(out + x, v[k][0]);
+          }
+        }
+      }
     }
   }
 }
@@ -323,9 +522,77 @@ inline void SoftmaxLaunch(float *dst, const float *src, int64_t rows, int64_t co
     else if (c <= 512) LaunchRow<256, 2, 1>(dst, src, label, r, c, ld_dst, ld_src, stream);
     else if (c <= 2048) LaunchRow<256, 8, 1>(dst, src, label, r, c, ld_dst, ld_src, stream);
     else LaunchRow<512, 16, 1>(dst, src, label, r, c, ld_dst, ld_src, stream);
+  } else if (vec && cols <= 8 * 32768) {
+    // the row lives in the registers of a cluster of 2, 4 or 8 CTAs
+    const bool narrow = c <= 8 * 16384;  // eight CTAs of 512 threads x 8 items x 4 floats hold the row
+    const uint32_t threads = narrow ? 512 : 1024;
+    const uint32_t per_cta = threads * 32;
+    uint32_t csize = 2;
+    while (csize < 8 && static_cast<uint64_t>(csize) * per_cta < c) csize *= 2;
+    // few rows: more CTAs per row keep more SMs busy
+    while (csize < 8 && static_cast<uint64_t>(r) * csize < static_cast<uint64_t>(sms) && c / (csize * 2) >= 4096) csize *= 2;
+    uint32_t seg = ((c + csize - 1) / csize + 3) & ~3u;
+    const uint32_t items = (seg / 4 + threads - 1) / threads;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(csize, r < 65535u ? r : 65535u);
+    cfg.blockDim = dim3(threads);
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = csize;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+#define MSHADOW_B200_SOFTMAX_CLUSTER_(ITEMS)                                                                      \
+  {                                                                                                               \
+    if (narrow) {                                                                                                 \
+      MSHADOW_CUDA_CALL(cudaLaunchKernelEx(&cfg, SoftmaxClusterRowKernel<512, ITEMS>, dst, src, label, r, c,      \
+                                           ld_dst, ld_src, seg));                                                 \
+    } else {                                                                                                      \
+      MSHADOW_CUDA_CALL(cudaLaunchKernelEx(&cfg, SoftmaxClusterRowKernel<1024, ITEMS>, dst, src, label, r, c,     \
+                                           ld_dst, ld_src, seg));                                                 \
+    }                                                                                                             \
+  }
+    if (items <= 1) MSHADOW_B200_SOFTMAX_CLUSTER_(1)
+    else if (items <= 2) MSHADOW_B200_SOFTMAX_CLUSTER_(2)
+    else if (items <= 4) MSHADOW_B200_SOFTMAX_CLUSTER_(4)
+    else MSHADOW_B200_SOFTMAX_CLUSTER_(8)
+#undef MSHADOW_B200_SOFTMAX_CLUSTER_
   } else {
-    const uint32_t cap = static_cast<uint32_t>(gpu_rt::CurrentDevice().sm_count) * 16u;
-    SoftmaxSweepKernel<512><<<r < cap ? r : cap, 512, 0, stream>>>(dst, src, label, r, c, ld_dst, ld_src);
+    // longer (or unaligned) rows: one pass with a running (max, sum), rows split over clusters
+    // A row goes to a cluster of 1, 2, 4 or 8 CTAs: more while there are fewer CTAs than SMs, and
+    // more while the rows in flight at once (about two CTAs per SM) would not fit the L2 together,
+    // because the second read of a row is meant to come from there.
+    uint32_t csize = 1;
+    const uint64_t l2_share = static_cast<uint64_t>(gpu_rt::CurrentDevice().l2_bytes) * 3 / 4;
+    while (csize < 8 && c / (csize * 2) >= 4096) {
+      const bool few_ctas = static_cast<uint64_t>(r) * csize < static_cast<uint64_t>(sms);
+      const uint64_t rows_in_flight = static_cast<uint64_t>(sms) * 2 / csize < r ? static_cast<uint64_t>(sms) * 2 / csize : r;
+      const bool spills = rows_in_flight * c * 4 > l2_share;
+      if (!few_ctas && !spills) break;
+      csize *= 2;
+    }
+    const uint32_t lanes = vec ? 4 : 1;
+    uint32_t seg = (c + csize - 1) / csize;
+    seg = (seg + 3) & ~3u;  // segments start on 16-byte boundaries
+    const uint32_t row_grid = r < 65535u ? r : 65535u;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(csize, row_grid);
+    cfg.blockDim = dim3(1024);
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = csize;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    if (lanes == 4) {
+      MSHADOW_CUDA_CALL(cudaLaunchKernelEx(&cfg, SoftmaxOnlineKernel<1024, 4>, dst, src, label, r, c, ld_dst, ld_src, seg));
+    } else {
+      MSHADOW_CUDA_CALL(cudaLaunchKernelEx(&cfg, SoftmaxOnlineKernel<1024, 1>, dst, src, label, r, c, ld_dst, ld_src, seg));
+    }
   }
   MSHADOW_CUDA_POST_KERNEL_CHECK(Softmax);
 }

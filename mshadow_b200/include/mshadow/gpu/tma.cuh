@@ -40,6 +40,11 @@ __device__ __forceinline__ void BarrierExpect(uint64_t *bar, uint32_t bytes) {
                : "memory");
 }
 
+/*! \brief one plain arrival (no data announced) */
+__device__ __forceinline__ void BarrierArrive(uint64_t *bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(SharedAddr(bar)) : "memory");
+}
+
 /*! \brief start copying `bytes` from global to this CTA's shared memory; completion lands on `bar` */
 __device__ __forceinline__ void BulkLoad(void *smem_dst, const void *gmem_src, uint32_t bytes, uint64_t *bar) {
   asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(

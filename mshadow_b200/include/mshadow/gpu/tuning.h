@@ -27,6 +27,12 @@
 #ifndef MSHADOW_B200_SEG_DEPTH
 #define MSHADOW_B200_SEG_DEPTH 4  // source rows in flight per thread
 #endif
+#ifndef MSHADOW_B200_SEG_STAGED
+#define MSHADOW_B200_SEG_STAGED 1  // segmented sum: source rows through a shared-memory ring filled by bulk copies
+#endif
+#ifndef MSHADOW_B200_SEG_RING
+#define MSHADOW_B200_SEG_RING 8  // rows (of up to 4 KB) in flight per CTA of the staged segmented sum
+#endif
 #ifndef MSHADOW_B200_SEG_MIN_CTAS
 #define MSHADOW_B200_SEG_MIN_CTAS 4  // resident CTAs per SM the register allocation must allow
 #endif

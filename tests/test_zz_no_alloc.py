@@ -66,9 +66,12 @@ def test_two_calls_match_the_allocating_entry_point_and_allocate_nothing(lib, ro
         held_before = lib.scratch_bytes(None)
         lib.reduce_keep_lowest_sum_noalloc(got, src, scale=scale)
         lib.stream_wait(None)
-        # neither the driver's view of free memory nor the library's scratch cache moved
-        assert torch.cuda.mem_get_info()[0] == free_before
+        # the library's scratch cache never moves; on the second call (the first one may make the
+        # driver load the kernels' code, which takes device memory of its own) neither does the
+        # driver's count of free memory
         assert lib.scratch_bytes(None) == held_before
+        if call == 1:
+            assert torch.cuda.mem_get_info()[0] == free_before
         w, o = want.cpu().numpy(), got.cpu().numpy()
         # the two entry points share kernels and launch geometry: identical results
         assert scaled_err(o, w) <= 1e-5
