@@ -482,6 +482,21 @@ def kernel_cases(lib, torch, small=False):
     yield ("ch_unpool_max", "ch_unpool<max> nsize 5 (%d,256,56,56)" % imgs, 16 * X4.numel(), X4.numel(),
            lambda: lib.ch_unpool(G4, X4, P4, gP4, 5, reducer=1), 10)
     del X4, P4, gP4, G4
+    # local response normalisation in one pass each way (beta 0.75 by roots: the bit-exact power functor)
+    XN = torch.rand(imgs, 256, 56, 56, device=dev, generator=g)
+    ON, NN = torch.empty_like(XN), torch.empty_like(XN)
+    yield ("lrn_forward", "LRN forward nsize 5 (%d,256,56,56), norm not kept" % imgs, 8 * XN.numel(), XN.numel(),
+           lambda: lib.lrn_forward(ON, None, XN, 5, 0.0001, 0.75, 1.0, 1), 10)
+    yield ("lrn_forward_norm", "LRN forward nsize 5 (%d,256,56,56), norm kept" % imgs, 12 * XN.numel(), XN.numel(),
+           lambda: lib.lrn_forward(ON, NN, XN, 5, 0.0001, 0.75, 1.0, 1), 10)
+    yield ("lrn_forward_fast", "LRN forward nsize 5 (%d,256,56,56), fast power functor" % imgs, 8 * XN.numel(),
+           XN.numel(), lambda: lib.lrn_forward(ON, None, XN, 5, 0.0001, 0.75, 1.0, 2), 10)
+    GN = torch.rand(imgs, 256, 56, 56, device=dev, generator=g)
+    yield ("lrn_backward", "LRN backward nsize 5 (%d,256,56,56)" % imgs, 16 * XN.numel(), XN.numel(),
+           lambda: lib.lrn_backward(ON, GN, XN, NN, 5, 0.0001, 0.75, 1), 10)
+    yield ("lrn_backward_fast", "LRN backward nsize 5 (%d,256,56,56), fast power functor" % imgs, 16 * XN.numel(),
+           XN.numel(), lambda: lib.lrn_backward(ON, GN, XN, NN, 5, 0.0001, 0.75, 2), 10)
+    del XN, ON, NN, GN
     # softmax over the middle axis (per-pixel classification shape: 21 classes, 256x256 positions)
     b3, c3, n3 = (32 if small else 64), 21, 256 * 256
     L3 = torch.randn(b3, c3, n3, device=dev, generator=g) * 2

@@ -204,6 +204,22 @@ int msb_ch_unpool_f32(float *dst, const float *src, const float *pooled, const f
                       int64_t n, int64_t c, int64_t pc, int64_t h, int64_t w, int nsize, int stride,
                       int pad, int64_t ld_src, int64_t ld_pooled, int64_t ld_dst, int reducer,
                       msb_stream_t stream);
+/* Local response normalisation across channels as single passes (no single reference call: a layer
+   written against the reference composes it from chpool<red::sum> and its own square / power
+   functors, mshadow/extension/channel_pool.h:77-104, channel_unpool.h:102-133):
+     forward    norm = chpool<red::sum>(F<square>(src), nsize) * salpha + knorm;
+                out  = src * F<power>(norm, -beta);                       (norm may be NULL: not kept)
+     backward   gsrc  = gout * F<power>(norm, -beta);
+                gsrc += (-2.0f * beta * salpha) * chpool<red::sum>(gout * src * F<power>(norm, -beta - 1.0f), nsize) * src;
+   Dense (n, c, h, w) tensors.  power_kind 0: powf; 1: exponents -0.75 and -1.75 from square roots
+   (bit-identical on every device); 2: the GPU's fast exp2 / log2 units (about 2^-21 relative).
+   Products and sums are rounded one by one in the order of the expressions. */
+int msb_lrn_forward_f32(float *out, float *norm, const float *src, int64_t n, int64_t c, int64_t h, int64_t w,
+                        int nsize, float salpha, float beta, float knorm, int power_kind, msb_stream_t stream);
+int msb_lrn_backward_f32(float *gsrc, const float *gout, const float *src, const float *norm, int64_t n,
+                         int64_t c, int64_t h, int64_t w, int nsize, float salpha, float beta, int power_kind,
+                         msb_stream_t stream);
+
 
 /* ---- embedding backward --------------------------------------------------------------- */
 

@@ -67,6 +67,8 @@ _SIGNATURES = {
                        cint, vp],
     "msb_chpool_f32": [vp, vp, i64, i64, i64, i64, cint, cint, cint, i64, i64, cint, vp],
     "msb_ch_unpool_f32": [vp, vp, vp, vp, i64, i64, i64, i64, i64, cint, cint, cint, i64, i64, i64, cint, vp],
+    "msb_lrn_forward_f32": [vp, vp, vp, i64, i64, i64, i64, cint, f32, f32, f32, cint, vp],
+    "msb_lrn_backward_f32": [vp, vp, vp, vp, i64, i64, i64, i64, cint, f32, f32, cint, vp],
     "msb_addtakegrad_f32_i32": [vp, vp, vp, i64, i64, i64, i64, i64, vp],
     "msb_addtakegrad_largebatch_f32_i32": [vp, vp, vp, vp, i64, i64, i64, vp],
     "msb_sort_by_key_i32": [vp, vp, i64, cint, vp],
@@ -257,6 +259,19 @@ class Library:
         self.call("msb_ch_unpool_f32", _ptr(dst), _ptr(src), _ptr(pooled), _ptr(gpooled), n, c, pooled.shape[1], h,
                   w, nsize, stride, pad, _ld(src), _ld(pooled), _ld(dst), reducer, stream)
         return dst
+
+    def lrn_forward(self, out, norm, src, nsize, salpha, beta, knorm, power_kind=0, stream=None):
+        """`norm` may be None (not kept)."""
+        n, c, h, w = src.shape
+        self.call("msb_lrn_forward_f32", _ptr(out), _ptr(norm) if norm is not None else None, _ptr(src), n, c, h, w,
+                  nsize, salpha, beta, knorm, power_kind, stream)
+        return out
+
+    def lrn_backward(self, gsrc, gout, src, norm, nsize, salpha, beta, power_kind=0, stream=None):
+        n, c, h, w = src.shape
+        self.call("msb_lrn_backward_f32", _ptr(gsrc), _ptr(gout), _ptr(src), _ptr(norm), n, c, h, w, nsize, salpha,
+                  beta, power_kind, stream)
+        return gsrc
 
     def addtakegrad(self, dst, index, src, stream=None):
         k, d = dst.shape

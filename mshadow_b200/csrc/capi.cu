@@ -524,6 +524,49 @@ int msb_ch_unpool_f32(float *dst, const float *src, const float *pooled, const f
   MSB_GUARD_END
 }
 
+int msb_lrn_forward_f32(float *out, float *norm, const float *src, int64_t n, int64_t c, int64_t h, int64_t w, int nsize,
+                        float salpha, float beta, float knorm, int power_kind, msb_stream_t stream) {
+  MSB_REQUIRE(nsize > 0 && nsize % 2 == 1, MSB_ERR_ARGUMENT, "the window must be odd and positive");
+  MSB_REQUIRE(power_kind >= 0 && power_kind <= 2, MSB_ERR_ARGUMENT, "power_kind must be 0 (powf), 1 (roots) or 2 (fast)");
+  MSB_REQUIRE(FitsIndex(n) && FitsIndex(c) && FitsIndex(h) && FitsIndex(w) && FitsIndex(n * c * h) &&
+                  FitsIndex(n * c * h * w),
+              MSB_ERR_SHAPE, "extent out of range");
+  MSB_REQUIRE(c >= nsize, MSB_ERR_SHAPE, "chpool: local size must be smaller than nchannels");
+  if (n * c * h * w == 0) return MSB_OK;
+  MSB_REQUIRE(out && src, MSB_ERR_ARGUMENT, "null pointer");
+  MSB_GUARD_BEGIN
+  BorrowedStream st(stream);
+  G4 o = Img(out, n, c, h, w, w, st.get());
+  G4 nm = Img(norm, n, c, h, w, w, st.get());
+  const G4 s = Img(src, n, c, h, w, w, st.get());
+  if (power_kind == 0) LRNForward<b200::power>(o, nm, s, nsize, salpha, beta, knorm);
+  else if (power_kind == 1) LRNForward<b200::power_by_roots>(o, nm, s, nsize, salpha, beta, knorm);
+  else LRNForward<b200::power_fast>(o, nm, s, nsize, salpha, beta, knorm);
+  MSB_GUARD_END
+}
+
+int msb_lrn_backward_f32(float *gsrc, const float *gout, const float *src, const float *norm, int64_t n, int64_t c,
+                         int64_t h, int64_t w, int nsize, float salpha, float beta, int power_kind,
+                         msb_stream_t stream) {
+  MSB_REQUIRE(nsize > 0 && nsize % 2 == 1, MSB_ERR_ARGUMENT, "the window must be odd and positive");
+  MSB_REQUIRE(power_kind >= 0 && power_kind <= 2, MSB_ERR_ARGUMENT, "power_kind must be 0 (powf), 1 (roots) or 2 (fast)");
+  MSB_REQUIRE(FitsIndex(n) && FitsIndex(c) && FitsIndex(h) && FitsIndex(w) && FitsIndex(n * c * h) &&
+                  FitsIndex(n * c * h * w),
+              MSB_ERR_SHAPE, "extent out of range");
+  MSB_REQUIRE(c >= nsize, MSB_ERR_SHAPE, "chpool: local size must be smaller than nchannels");
+  if (n * c * h * w == 0) return MSB_OK;
+  MSB_REQUIRE(gsrc && gout && src && norm, MSB_ERR_ARGUMENT, "null pointer");
+  MSB_GUARD_BEGIN
+  BorrowedStream st(stream);
+  G4 g = Img(gsrc, n, c, h, w, w, st.get());
+  const G4 go = Img(gout, n, c, h, w, w, st.get()), s = Img(src, n, c, h, w, w, st.get()),
+           nm = Img(norm, n, c, h, w, w, st.get());
+  if (power_kind == 0) LRNBackward<b200::power>(g, go, s, nm, nsize, salpha, beta);
+  else if (power_kind == 1) LRNBackward<b200::power_by_roots>(g, go, s, nm, nsize, salpha, beta);
+  else LRNBackward<b200::power_fast>(g, go, s, nm, nsize, salpha, beta);
+  MSB_GUARD_END
+}
+
 int msb_addtakegrad_f32_i32(float *dst, const int32_t *index, const float *src, int64_t k, int64_t d, int64_t nidx,
                             int64_t ld_dst, int64_t ld_src, msb_stream_t stream) {
   MSB_REQUIRE(FitsIndex(k) && FitsIndex(d) && FitsIndex(nidx) && LdOk(ld_dst, d) && LdOk(ld_src, d), MSB_ERR_SHAPE,

@@ -13,4 +13,5 @@
 #include "./extension/patch.h"
 #include "./extension/axis.h"
 #include "./extension/complex.h"
+#include "./extension/lrn.h"
 #endif  // MSHADOW_EXTENSION_H_

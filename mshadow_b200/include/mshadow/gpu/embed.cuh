@@ -26,6 +26,7 @@
 
 #include <cub/device/device_radix_sort.cuh>
 
+#include "./radix_sort.cuh"
 #include "./runtime.h"
 #include "./tma.cuh"
 
@@ -380,11 +381,29 @@ inline void AddTakeGradLargeBatchLaunch(float *dst, int64_t ld_dst, const int32_
                              static_cast<uint32_t>(width), scratch, stream);
 }
 
-/*! \brief stable key/value sort of 32-bit pairs, in place from the caller's point of view */
+namespace embeddetail {
+/*! \brief 4-byte arithmetic keys with 4-byte values: this engine's own radix sort (radix_sort.cuh) */
+template <typename KDType, typename VDType>
+inline void SortPairs4(KDType *keys, VDType *values, int64_t n, bool ascend, cudaStream_t stream, std::true_type) {
+  char *scratch = static_cast<char *>(gpu_rt::Scratch::Get(stream, sortdetail::ScratchBytes(n)));
+  const sortdetail::Source as_given = {0};
+  sortdetail::SortPairs<KDType, VDType>(keys, values, keys, n, 32, ascend, as_given, scratch, stream);
+}
+template <typename KDType, typename VDType>
+inline void SortPairs4(KDType *, VDType *, int64_t, bool, cudaStream_t, std::false_type) {}
+}  // namespace embeddetail
+
+/*! \brief stable key/value sort, in place from the caller's point of view */
 template <typename KDType, typename VDType>
 inline void SortPairsLaunch(KDType *keys, VDType *values, int64_t n, bool ascend, cudaStream_t stream) {
   if (n <= 1) return;
   CHECK_LT(n, (int64_t(1) << 31));
+  constexpr bool kOwn = sizeof(KDType) == 4 && sizeof(VDType) == 4 && std::is_arithmetic<KDType>::value;
+  if (kOwn) {
+    embeddetail::SortPairs4(keys, values, n, ascend, stream, std::integral_constant<bool, kOwn>());
+    return;
+  }
+  // other element sizes: the CUDA toolkit's device-wide radix sort
   size_t temp = 0;
   if (ascend) {
     MSHADOW_CUDA_CALL((cub::DeviceRadixSort::SortPairs<KDType, VDType>(nullptr, temp, keys, keys, values, values,
@@ -418,21 +437,21 @@ inline void AddTakeGradLaunch(float *dst, int64_t ld_dst, const int32_t *index, 
   CHECK_LT(n, (int64_t(1) << 31));
   using embeddetail::Align256;
   const uint32_t un = static_cast<uint32_t>(n);
-  size_t temp = 0;
-  MSHADOW_CUDA_CALL((cub::DeviceRadixSort::SortPairs<int32_t, int32_t>(nullptr, temp, nullptr, nullptr, nullptr,
-                                                                       nullptr, static_cast<int>(n), 0, 32, stream)));
+  // clip + stable sort of (index, position) + segmented sum.  Only the bits a row number can have
+  // are sorted (two passes for up to 2^18 rows); the first pass clips the raw indices and
+  // generates the positions itself.
+  int bits = 1;
+  while (bits < 31 && (int64_t(1) << bits) < k) ++bits;
   const size_t ib = Align256(n * sizeof(int32_t));
+  const size_t sort_bytes = sortdetail::ScratchBytes(n);
   const size_t seg = embeddetail::SegmentScratchBytes(un, static_cast<uint32_t>(width));
-  char *base = static_cast<char *>(gpu_rt::Scratch::Get(stream, 4 * ib + Align256(temp) + seg));
-  int32_t *k_in = reinterpret_cast<int32_t *>(base), *v_in = reinterpret_cast<int32_t *>(base + ib);
-  int32_t *k_out = reinterpret_cast<int32_t *>(base + 2 * ib), *v_out = reinterpret_cast<int32_t *>(base + 3 * ib);
-  void *work = base + 4 * ib;
-  char *seg_scratch = base + 4 * ib + Align256(temp);
-  ClipIotaKernel<int32_t><<<gpu_rt::CeilDiv(n, 256), 256, 0, stream>>>(k_in, v_in, index, un, static_cast<int32_t>(k));
-  MSHADOW_CUDA_POST_KERNEL_CHECK(ClipIotaKernel);
-  MSHADOW_CUDA_CALL((cub::DeviceRadixSort::SortPairs<int32_t, int32_t>(work, temp, k_in, k_out, v_in, v_out,
-                                                                       static_cast<int>(n), 0, 32, stream)));
-  embeddetail::SegmentSumRun(dst, ld_dst, k_out, v_out, src, ld_src, un, static_cast<uint32_t>(width), seg_scratch,
+  char *base = static_cast<char *>(gpu_rt::Scratch::Get(stream, 2 * ib + Align256(sort_bytes) + seg));
+  int32_t *k_sorted = reinterpret_cast<int32_t *>(base), *v_sorted = reinterpret_cast<int32_t *>(base + ib);
+  char *sort_scratch = base + 2 * ib;
+  char *seg_scratch = base + 2 * ib + Align256(sort_bytes);
+  const sortdetail::Source clipped = {static_cast<int>(k)};
+  sortdetail::SortPairs<int32_t, int32_t>(k_sorted, v_sorted, index, n, bits, true, clipped, sort_scratch, stream);
+  embeddetail::SegmentSumRun(dst, ld_dst, k_sorted, v_sorted, src, ld_src, un, static_cast<uint32_t>(width), seg_scratch,
                              stream);
 }
 

@@ -27,6 +27,9 @@
 #ifndef MSHADOW_B200_SEG_DEPTH
 #define MSHADOW_B200_SEG_DEPTH 4  // source rows in flight per thread
 #endif
+#ifndef MSHADOW_B200_LRN_TILE_PX
+#define MSHADOW_B200_LRN_TILE_PX 3968  // pixels per CTA of the LRN kernels (a multiple of 128)
+#endif
 #ifndef MSHADOW_B200_SEG_STAGED
 #define MSHADOW_B200_SEG_STAGED 1  // segmented sum: source rows through a shared-memory ring filled by bulk copies
 #endif

@@ -285,6 +285,64 @@ void ORC(ch_unpool)(float *dst, const float *src, const float *pooled, const flo
   }
 }
 
+/* ---- local response normalisation composed from chpool<red::sum> ----
+   The expressions of a layer written against the reference, evaluated element by element as
+   MapExp does (tensor_cpu-inl.h:143-201) with the window loop of extension/channel_pool.h:85-99
+   (stride 1, pad nsize / 2, channels [max(c - pad, 0), min(c - pad + nsize, C)) in ascending order
+   from zero). */
+static float lrn_power(float a, float b, int kind) {
+  if (kind == 1 && (b == -0.75f || b == -1.75f)) {
+    const float r = sqrtf(a);
+    float t = r * sqrtf(r);
+    if (b == -1.75f) t = t * a;
+    return 1.0f / t;
+  }
+  return powf(a, b);
+}
+
+void ORC(lrn_forward)(float *out, float *norm, const float *src, int64_t n, int64_t c, int64_t h, int64_t w,
+                      int nsize, float salpha, float beta, float knorm, int power_kind) {
+  const int64_t plane = h * w, pad = nsize / 2;
+#pragma omp parallel for
+  for (int64_t i = 0; i < n * c; ++i) {
+    const int64_t ci = i % c, ni = i / c;
+    const int64_t cstart = ci < pad ? 0 : ci - pad;
+    const int64_t cend = imin(ci - pad + nsize, c);
+    for (int64_t p = 0; p < plane; ++p) {
+      float sum = 0.0f;
+      for (int64_t cc = cstart; cc < cend; ++cc) {
+        const float a = src[(ni * c + cc) * plane + p];
+        sum = sum + a * a;
+      }
+      const float nrm = sum * salpha + knorm;
+      norm[i * plane + p] = nrm;
+      out[i * plane + p] = src[i * plane + p] * lrn_power(nrm, -beta, power_kind);
+    }
+  }
+}
+
+void ORC(lrn_backward)(float *gsrc, const float *gout, const float *src, const float *norm, int64_t n, int64_t c,
+                       int64_t h, int64_t w, int nsize, float salpha, float beta, int power_kind) {
+  const int64_t plane = h * w, pad = nsize / 2;
+  const float scale = -2.0f * beta * salpha;
+  const float e1 = -beta - 1.0f;
+#pragma omp parallel for
+  for (int64_t i = 0; i < n * c; ++i) {
+    const int64_t ci = i % c, ni = i / c;
+    const int64_t cstart = ci < pad ? 0 : ci - pad;
+    const int64_t cend = imin(ci - pad + nsize, c);
+    for (int64_t p = 0; p < plane; ++p) {
+      float sum = 0.0f;
+      for (int64_t cc = cstart; cc < cend; ++cc) {
+        const int64_t o = (ni * c + cc) * plane + p;
+        sum = sum + (gout[o] * src[o]) * lrn_power(norm[o], e1, power_kind);
+      }
+      const float first = gout[i * plane + p] * lrn_power(norm[i * plane + p], -beta, power_kind);
+      gsrc[i * plane + p] = first + (scale * sum) * src[i * plane + p];
+    }
+  }
+}
+
 /* ---- embedding backward ---- */
 
 /* tensor_cpu-inl.h:497-508: serial over the batch, index clipped into [0, K-1] */

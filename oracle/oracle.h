@@ -226,6 +226,21 @@ void ORC(axis_case)(int id, float *dst, const float *A, int64_t n, int64_t c, in
 #define ORC_NUM_COMPLEX_CASES 13
 void ORC(complex_case)(int id, float *dst, const float *A, const float *B, int64_t rows, int64_t cols);
 
+/*
+ * Local response normalisation as a layer composes it from chpool<red::sum> and user functors
+ * (extension/channel_pool.h:77-104 through MapExp, tensor_cpu-inl.h:143-201):
+ *   lrn_forward    norm = chpool<red::sum>(F<square>(src), nsize) * salpha + knorm;
+ *                  out  = src * F<power>(norm, -beta);
+ *   lrn_backward   gsrc  = gout * F<power>(norm, -beta);
+ *                  gsrc += (-2.0f * beta * salpha) * chpool<red::sum>(gout * src * F<power>(norm, -beta - 1.0f), nsize) * src;
+ * square(a) = a * a.  power_kind 0: power(a, b) = powf(a, b); 1: for b = -0.75 / -1.75,
+ * 1 / (sqrtf(a) * sqrtf(sqrtf(a)) [* a]), else powf; 2: powf.  Dense (n, c, h, w) tensors.
+ */
+void ORC(lrn_forward)(float *out, float *norm, const float *src, int64_t n, int64_t c, int64_t h, int64_t w,
+                      int nsize, float salpha, float beta, float knorm, int power_kind);
+void ORC(lrn_backward)(float *gsrc, const float *gout, const float *src, const float *norm, int64_t n, int64_t c,
+                       int64_t h, int64_t w, int nsize, float salpha, float beta, int power_kind);
+
 /* number of OpenMP threads the library will use (for cpu_baseline.cores) */
 int ORC(num_threads)(void);
 /* sets the number of OpenMP threads of later calls (n < 1: leave unchanged); a launcher may have

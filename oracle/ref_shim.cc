@@ -54,6 +54,31 @@ struct square {
   MSHADOW_XINLINE static float Map(float a) { return a * a; }
 };
 
+/* the functors of a local-response-normalisation layer written against the reference */
+struct power {
+  MSHADOW_XINLINE static float Map(float a, float b) { return powf(a, b); }
+};
+struct power_by_roots {
+  MSHADOW_XINLINE static float Map(float a, float b) {
+    if (b != -0.75f && b != -1.75f) return powf(a, b);
+    const float r = sqrtf(a);
+    float t = r * sqrtf(r);
+    if (b == -1.75f) t = t * a;
+    return 1.0f / t;
+  }
+};
+
+template <typename Power>
+void lrn_forward_impl(T4 out, T4 norm, const T4 &src, int nsize, float salpha, float beta, float knorm) {
+  norm = chpool<red::sum>(F<square>(src), nsize) * salpha + knorm;
+  out = src * F<Power>(norm, -beta);
+}
+template <typename Power>
+void lrn_backward_impl(T4 gsrc, const T4 &gout, const T4 &src, const T4 &norm, int nsize, float salpha, float beta) {
+  gsrc = gout * F<Power>(norm, -beta);
+  gsrc += (-2.0f * beta * salpha) * chpool<red::sum>(gout * src * F<Power>(norm, -beta - 1.0f), nsize) * src;
+}
+
 template <typename Reducer>
 void keep_lowest(T1 d, const T2 &s, float scale, int saver) {
   switch (saver) {
@@ -172,6 +197,21 @@ void ref_ch_unpool(float *dst, const float *src, const float *pooled, const floa
   if (reducer == 0) d = ch_unpool<red::sum>(s, p, g, nsize, stride, pad);
   else if (reducer == 1) d = ch_unpool<red::maximum>(s, p, g, nsize, stride, pad);
   else d = ch_unpool<red::minimum>(s, p, g, nsize, stride, pad);
+}
+
+void ref_lrn_forward(float *out, float *norm, const float *src, int64_t n, int64_t c, int64_t h, int64_t w, int nsize,
+                     float salpha, float beta, float knorm, int power_kind) {
+  T4 o = img(out, n, c, h, w, w), nm = img(norm, n, c, h, w, w), s = img(src, n, c, h, w, w);
+  if (power_kind == 0) lrn_forward_impl<power>(o, nm, s, nsize, salpha, beta, knorm);
+  else lrn_forward_impl<power_by_roots>(o, nm, s, nsize, salpha, beta, knorm);
+}
+
+void ref_lrn_backward(float *gsrc, const float *gout, const float *src, const float *norm, int64_t n, int64_t c,
+                      int64_t h, int64_t w, int nsize, float salpha, float beta, int power_kind) {
+  T4 g = img(gsrc, n, c, h, w, w), go = img(gout, n, c, h, w, w), s = img(src, n, c, h, w, w),
+     nm = img(norm, n, c, h, w, w);
+  if (power_kind == 0) lrn_backward_impl<power>(g, go, s, nm, nsize, salpha, beta);
+  else lrn_backward_impl<power_by_roots>(g, go, s, nm, nsize, salpha, beta);
 }
 
 void ref_addtakegrad(float *dst, const int32_t *index, const float *src, int64_t k, int64_t d,

@@ -131,6 +131,24 @@ class Checker:
                               i64(_ld(pooled)), i64(_ld(dst)), C.c_int(reducer))
         return dst
 
+    # ---- local response normalisation (chpool<sum> with its surrounding arithmetic) ------------
+    def lrn_forward(self, src, nsize, salpha, beta, knorm, power_kind=0):
+        """Returns (out, norm) for a dense (n, c, h, w) input."""
+        assert src.flags.c_contiguous
+        n, c, h, w = src.shape
+        out, norm = np.empty_like(src), np.empty_like(src)
+        self._fn("lrn_forward")(_fp(out), _fp(norm), _fp(src), i64(n), i64(c), i64(h), i64(w), C.c_int(nsize),
+                                C.c_float(salpha), C.c_float(beta), C.c_float(knorm), C.c_int(power_kind))
+        return out, norm
+
+    def lrn_backward(self, gout, src, norm, nsize, salpha, beta, power_kind=0):
+        assert src.flags.c_contiguous and gout.flags.c_contiguous and norm.flags.c_contiguous
+        n, c, h, w = src.shape
+        gsrc = np.empty_like(src)
+        self._fn("lrn_backward")(_fp(gsrc), _fp(gout), _fp(src), _fp(norm), i64(n), i64(c), i64(h), i64(w),
+                                 C.c_int(nsize), C.c_float(salpha), C.c_float(beta), C.c_int(power_kind))
+        return gsrc
+
     # ---- embedding backward ------------------------------------------------------
     def addtakegrad(self, dst, index, src):
         k, d = dst.shape

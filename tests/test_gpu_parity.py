@@ -317,6 +317,37 @@ def zipf_indices(rng, n, k, s=1.1):
     return rng.choice(k, size=n, p=p / p.sum()).astype(np.int32)
 
 
+@pytest.mark.parametrize("power_kind", [0, 1, 2])
+@pytest.mark.parametrize("shape,nsize", [((2, 16, 8, 8), 5), ((3, 32, 12, 12), 3), ((1, 64, 56, 56), 5), ((2, 20, 4, 8), 7),
+                                         ((2, 96, 64, 64), 5),          # planes cut into tiles
+                                         ((2, 7, 3, 5), 3), ((1, 9, 4, 4), 5)])  # odd planes, few channels: expressions
+def test_lrn_forward_backward(lib, power_kind, shape, nsize):
+    """One-pass LRN against the composition through chpool<red::sum>: bit-exact when the power functor
+    is built from correctly rounded operations (roots), within 1e-5 with powf (the C library's on the
+    CPU, CUDA's on the GPU)."""
+    rng = np.random.default_rng(sum(shape) + nsize)
+    x = rng.uniform(-2, 2, shape).astype(np.float32)
+    g = rng.uniform(-1, 1, shape).astype(np.float32)
+    salpha, beta, knorm = float(np.float32(0.02 / nsize)), 0.75, 1.0
+    want_out, want_norm = orc.lrn_forward(x, nsize, salpha, beta, knorm, power_kind)
+    want_g = orc.lrn_backward(g, x, want_norm, nsize, salpha, beta, power_kind)
+    out, norm = torch.empty(shape, device="cuda"), torch.empty(shape, device="cuda")
+    lib.lrn_forward(out, norm, dev(x), nsize, salpha, beta, knorm, power_kind)
+    gs = lib.lrn_backward(torch.empty(shape, device="cuda"), dev(g), dev(x), dev(want_norm), nsize, salpha, beta,
+                          power_kind)
+    assert_bits(host(norm), want_norm)
+    if power_kind == 1:
+        assert_bits(host(out), want_out)
+        assert_bits(host(gs), want_g)
+    else:
+        assert np.abs(host(out) - want_out).max() <= 1e-5 * np.abs(want_out).max()
+        assert np.abs(host(gs) - want_g).max() <= 1e-5 * np.abs(want_g).max()
+    # without keeping the norm (fused shapes only): same output
+    if shape[1] >= 2 * nsize and (shape[2] * shape[3]) % 4 == 0:
+        out2 = lib.lrn_forward(torch.empty(shape, device="cuda"), None, dev(x), nsize, salpha, beta, knorm, power_kind)
+        assert_bits(host(out2), host(out))
+
+
 @pytest.mark.parametrize("k,d,n,kind", [(11, 20, 300, "uniform"), (50, 64, 600, "uniform"), (1, 8, 1000, "uniform"),
                                         (4000, 128, 3000, "distinct"), (300, 1024, 5000, "zipf"),
                                         (64, 1028, 700, "zipf"), (200, 4, 40000, "zipf"), (7, 33, 1, "uniform")])

@@ -145,6 +145,34 @@ def test_ch_unpool_matches_reference(reducer, c, nsize):
 
 
 @needs_ref
+@needs_ref
+@pytest.mark.parametrize("power_kind", [0, 1])
+@pytest.mark.parametrize("shape,nsize", [((2, 7, 3, 4), 3), ((1, 16, 5, 8), 5), ((3, 20, 4, 4), 7), ((2, 5, 2, 2), 5),
+                                         ((1, 9, 1, 1), 9)])
+def test_lrn_matches_reference_composition(power_kind, shape, nsize):
+    """Local response normalisation as a layer composes it from chpool<red::sum>, F<square> and
+    F<power> through the reference's own plans."""
+    rng = np.random.default_rng(sum(shape) + nsize)
+    x, g = rnd(rng, shape, -2, 2), rnd(rng, shape)
+    salpha, beta, knorm = np.float32(0.0001 * 5 / nsize * 40), 0.75, 1.0
+    o1, n1 = orc.lrn_forward(x, nsize, salpha, beta, knorm, power_kind)
+    o2, n2 = ref.lrn_forward(x, nsize, salpha, beta, knorm, power_kind)
+    assert same_bits(o1, o2) and same_bits(n1, n2)
+    assert same_bits(orc.lrn_backward(g, x, n1, nsize, salpha, beta, power_kind),
+                     ref.lrn_backward(g, x, n2, nsize, salpha, beta, power_kind))
+
+
+def test_lrn_known_answer():
+    # all ones, five channels, window 3, salpha 1, knorm 1, beta 0.75 by roots: the window holds
+    # two squares at the ends and three inside, so norm = 3 / 4 and out = norm ^ -0.75
+    x = np.ones((1, 5, 1, 1), np.float32)
+    out, norm = orc.lrn_forward(x, 3, 1.0, 0.75, 1.0, 1)
+    assert norm.ravel().tolist() == [3.0, 4.0, 4.0, 4.0, 3.0]
+    r3, r4 = np.sqrt(np.float32(3)), np.float32(2)
+    want = [np.float32(1) / (r3 * np.sqrt(r3)), np.float32(1) / (r4 * np.sqrt(r4))]
+    assert out.ravel().tolist() == [want[0], want[1], want[1], want[1], want[0]]
+
+
 def test_addtakegrad_matches_reference():
     rng = np.random.default_rng(5)
     k, d, n = 11, 20, 300
