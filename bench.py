@@ -110,7 +110,7 @@ class ClockSampler(threading.Thread):
     def __init__(self, index, period=0.01):
         super().__init__(daemon=True)
         self.index, self.period = index, period
-        self.samples, self.stop_flag, self.window = [], False, [None, None]
+        self.samples, self.stop_flag, self.window, self.tail_window = [], False, [None, None], [None, None]
         self.ok = False
         try:
             import pynvml
@@ -142,13 +142,16 @@ class ClockSampler(threading.Thread):
             return {"sm_mhz": None, "sm_max_mhz": self.max_mhz, "reasons": [], "samples": 0}
         t0, t1 = self.window
         inside = [s for s in self.samples if t0 is not None and t0 <= s[0] <= t1]
-        use = inside if len(inside) >= 3 else self.samples
+        t2, t3 = self.tail_window
+        tail = [s for s in self.samples if t2 is not None and t2 <= s[0] <= t3]
+        use = inside if len(inside) >= 3 else (inside + tail if len(inside + tail) >= 3 else self.samples)
         mask = 0
         for s in use:
             mask |= s[2]
         reasons = [name for bit, name in self.REASONS.items() if mask & bit]
         return {"sm_mhz": float(np.median([s[1] for s in use])), "sm_max_mhz": self.max_mhz,
-                "reasons": reasons, "samples": len(use), "in_timed_region": len(inside)}
+                "reasons": reasons, "samples": len(use), "in_timed_region": len(inside),
+                "in_the_same_steps_continued_untimed": len(tail)}
 
 
 # --------------------------------------------------------------------------------------
@@ -369,6 +372,7 @@ def time_kernel(torch, fn, iters=20, warm=5):
         evs[i + 1].record()
     torch.cuda.synchronize()
     times = [evs[i].elapsed_time(evs[i + 1]) for i in range(iters)]
+    time_kernel.spread = (float(np.min(times)), float(np.max(times)))   # ms, of the launches just timed
     return float(np.median(times)) * 1e-3
 
 
@@ -571,6 +575,44 @@ def kernel_cases(lib, torch, small=False):
     torch.cuda.empty_cache()
 
 
+def launch_trace(lib, torch, key, small, launches, per_bin=20):
+    """One kernel launched `launches` times back to back, timed launch by launch, with the SM clock and
+    the throttle reasons sampled every 0.5 ms: per bin of `per_bin` launches the median time, the median
+    clock and the reasons seen.  Shows how a kernel's time moves with the clock over a long burst."""
+    sampler = ClockSampler(torch.cuda.current_device(), period=0.0005)
+    sampler.start()
+    bins = []
+    for k, label, nbytes, elems, fn, n_it in kernel_cases(lib, torch, small):
+        if k != key:
+            continue
+        for _ in range(3):
+            fn()
+        torch.cuda.synchronize()
+        for b in range(max(1, launches // per_bin)):
+            evs = [torch.cuda.Event(enable_timing=True) for _ in range(per_bin + 1)]
+            t0 = time.perf_counter()
+            evs[0].record()
+            for i in range(per_bin):
+                fn()
+                evs[i + 1].record()
+            torch.cuda.synchronize()
+            t1 = time.perf_counter()
+            ms = [evs[i].elapsed_time(evs[i + 1]) for i in range(per_bin)]
+            inside = [x for x in sampler.samples if t0 <= x[0] <= t1]
+            mask = 0
+            for x in inside:
+                mask |= x[2]
+            mhz = float(np.median([x[1] for x in inside])) if inside else None
+            bins.append({"launches": [b * per_bin, (b + 1) * per_bin - 1], "ms_median": round(float(np.median(ms)), 4),
+                         "ms_min": round(float(np.min(ms)), 4), "ms_max": round(float(np.max(ms)), 4), "sm_mhz": mhz,
+                         "ms_x_ghz": round(float(np.median(ms)) * mhz / 1e3, 4) if mhz else None,
+                         "reasons": [name for bit, name in ClockSampler.REASONS.items() if mask & bit]})
+        break
+    sampler.stop_flag = True
+    sampler.join(timeout=1.0)
+    return bins
+
+
 def kernel_table(lib, torch, peak, only=None, small=False, iters=None, warm=None):
     """Algorithmic GB/s of every kernel of the path (one GPU)."""
     rows = []
@@ -579,7 +621,8 @@ def kernel_table(lib, torch, peak, only=None, small=False, iters=None, warm=None
             continue
         seconds = time_kernel(torch, fn, iters=iters or n_it, warm=warm if warm is not None else 3)
         gbs = nbytes / seconds / 1e9
-        rows.append({"kernel": label, "key": key, "ms": seconds * 1e3, "GBps": round(gbs, 1),
+        rows.append({"kernel": label, "key": key, "ms": seconds * 1e3, "ms_min": round(time_kernel.spread[0], 5),
+                     "ms_max": round(time_kernel.spread[1], 5), "GBps": round(gbs, 1),
                      "frac_of_measured_peak": round(gbs / peak, 3), "frac_of_8TBps": round(gbs / NOMINAL_HBM_GBS, 3),
                      "Gelem_per_s": round(elems / seconds / 1e9, 2)})
     return rows
@@ -750,28 +793,55 @@ def make_cyclic_hot_step(torch, lib, dist, peer, keys, order, src, rank, world, 
     """Embedding backward with table row r owned by rank r % world and the HOT_ROWS most frequent
     rows summed by all ranks (see mshadow_b200/sharding.py).  Returns (step, shard, info).
     The hot rows' partial sums are combined through the peer-store exchange when `peer` is given,
-    else by one NCCL all-reduce."""
+    else by one NCCL all-reduce.  The rank's part of the sorted list is selected on the device
+    (msb_frequent_rows_i32, msb_route_cyclic_hot_i32) and checked against the host routing."""
     from mshadow_b200 import sharding
-    t0 = time.perf_counter()
-    hot = sharding.hot_rows(keys, HOT_ROWS)
-    tk, to, hk, ho = sharding.route_cyclic_with_hot_rows(keys, order, EMBED_N, rank, world, hot)
-    route_ms = (time.perf_counter() - t0) * 1e3
     rows_mine = (EMBED_K - rank + world - 1) // world
-    shard = torch.zeros(rows_mine, EMBED_D, device=dev)
-    dtk, dto = torch.from_numpy(tk).to(dev), torch.from_numpy(to).to(dev)
-    dhk, dho = torch.from_numpy(hk).to(dev), torch.from_numpy(ho).to(dev)
-    partial = torch.zeros(HOT_ROWS, EMBED_D, device=dev)
+    n = int(keys.size)
+    dk_all, do_all = torch.from_numpy(keys).to(dev), torch.from_numpy(order).to(dev)
+    hot_rows_dev = torch.zeros(HOT_ROWS, dtype=torch.int32, device=dev)
+    hot_counts_dev = torch.zeros(HOT_ROWS, dtype=torch.int32, device=dev)
+    out_keys = torch.empty(n, dtype=torch.int32, device=dev)
+    out_rows = torch.empty(n, dtype=torch.int32, device=dev)
+    totals = torch.zeros(2, dtype=torch.int32, device=dev)
+    b, e = sharding.shard_range(EMBED_N, rank, world)
+
+    def route_on_device():
+        lib.frequent_rows(hot_rows_dev, hot_counts_dev, dk_all)
+        found = hot_rows_dev.cpu().numpy()[hot_counts_dev.cpu().numpy() > 0]
+        hot_dev = torch.from_numpy(np.sort(found)).to(dev)
+        lib.route_cyclic_hot(out_keys, out_rows, totals, dk_all, do_all, hot_dev if found.size else None, world, rank,
+                             b, e, rows_mine)
+        nt, nh = (int(v) for v in totals.cpu().numpy())
+        return np.sort(found), nt, nh
+
+    route_on_device()                      # first call: scratch allocation, kernel loading
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    hot, nt, nh = route_on_device()
+    device_route_ms = (time.perf_counter() - t0) * 1e3
+    t0 = time.perf_counter()
+    hot_host = sharding.hot_rows(keys, HOT_ROWS)
+    tk, to, hk, ho = sharding.route_cyclic_with_hot_rows(keys, order, EMBED_N, rank, world, hot_host)
+    route_ms = (time.perf_counter() - t0) * 1e3
+    # One destination for both parts: the rank's table rows followed by the partial rows of the hot
+    # rows.  The tail list (local rows, ascending) followed by the hot list (positions offset by
+    # rows_mine) is again sorted, so ONE segmented sum serves both, with half the launches.
+    dkeys, dorder = out_keys[:nt + nh], out_rows[:nt + nh]
+    same = bool(np.array_equal(hot, hot_host) and nt == tk.size and nh == hk.size and
+                np.array_equal(dkeys.cpu().numpy(), np.concatenate([tk, hk + np.int32(rows_mine)])) and
+                np.array_equal(dorder.cpu().numpy(), np.concatenate([to, ho])))
+    ext = torch.zeros(rows_mine + HOT_ROWS, EMBED_D, device=dev)
+    shard, partial = ext[:rows_mine], ext[rows_mine:]
     mine = np.nonzero(hot % world == rank)[0]
     # my hot rows as a (sorted local row, position in `partial`) list: one more sorted scatter-add
     mine_pos = torch.from_numpy(mine.astype(np.int32)).to(dev)
     mine_rows = torch.from_numpy((hot[mine] // world).astype(np.int32)).to(dev)
 
     def step(stream=None):
-        if tk.size:
-            lib.addtakegrad_largebatch(shard, dtk, dto, src, stream=stream)
         partial.zero_()
-        if hk.size:
-            lib.addtakegrad_largebatch(partial, dhk, dho, src, stream=stream)
+        if dkeys.numel():
+            lib.addtakegrad_largebatch(ext, dkeys, dorder, src, stream=stream)
         if world > 1:
             if peer is not None:
                 peer.push(partial, 2, stream=stream)
@@ -781,7 +851,8 @@ def make_cyclic_hot_step(torch, lib, dist, peer, keys, order, src, rank, world, 
         if mine.size:
             lib.addtakegrad_largebatch(shard, mine_rows, mine_pos, partial, stream=stream)
 
-    info = {"hot_rows": int(hot.size), "entries_on_this_rank": int(tk.size + hk.size), "host_routing_ms": route_ms}
+    info = {"hot_rows": int(hot.size), "entries_on_this_rank": int(nt + nh), "host_routing_ms": route_ms,
+            "device_routing_ms": device_route_ms, "device_routing_equals_host_routing": same}
     return step, shard, info
 
 
@@ -922,9 +993,27 @@ def sharded_block(args, torch, lib, dist, peer, peer_side, rank, world, dev, pea
     if dist is not None:
         dist.all_reduce(most, op=dist.ReduceOp.MAX)
     total_bytes = 4 * EMBED_N * EMBED_D + 8 * EMBED_N + 8 * uniq * EMBED_D
+    # correctness: one step from a zero table against the unsharded call on this rank's own GPU
+    # (rows r, r + N, ...); the two differ only in the order the hot rows' entries are added
+    shard.zero_()
+    step()
+    if world > 1:
+        peer.pull_wait(2)
+    whole = torch.zeros(EMBED_K, EMBED_D, device=dev)
+    lib.addtakegrad_largebatch(whole, torch.from_numpy(keys).to(dev), torch.from_numpy(order).to(dev), src)
+    want = whole[rank::world]
+    scale = torch.maximum(want.abs(), want.pow(2).mean(dim=1, keepdim=True).sqrt()).clamp_min(1e-30)
+    worst = torch.tensor([float(((shard - want).abs() / scale).max().item())], device=dev, dtype=torch.float64)
+    if dist is not None:
+        dist.all_reduce(worst, op=dist.ReduceOp.MAX)
+    del whole, want, scale
     entry("C5_addtakegrad_cyclic_hot", ms, EMBED_N * EMBED_D, total_bytes / world, 1,
           {"hot_rows": info["hot_rows"], "max_entries_on_a_rank": int(most.item()),
-           "host_routing_ms_outside_timing": round(info["host_routing_ms"], 2), "source_rows": "replicated"})
+           "max_rel_diff_vs_unsharded_call": float(worst.item()), "within_1e-5": bool(worst.item() <= 1e-5),
+           "routing_ms_outside_timing": {"on_the_device_with_its_two_readbacks": round(info["device_routing_ms"], 3),
+                                         "numpy_on_the_host": round(info["host_routing_ms"], 2),
+                                         "same_lists": info["device_routing_equals_host_routing"]},
+           "source_rows": "replicated"})
     del src, shard
     torch.cuda.empty_cache()
     return out
@@ -1211,7 +1300,9 @@ def embed_sharded_arm(args, torch, lib, dist, peer, rank, world, dev):
             peer.pull_wait(2)
         out[name] = {"ms_per_step": ms, "hot_rows": info["hot_rows"],
                      "max_entries_on_a_rank": spread(info["entries_on_this_rank"]),
-                     "host_routing_ms": info["host_routing_ms"], "exchange_bytes": HOT_ROWS * EMBED_D * 4}
+                     "host_routing_ms": info["host_routing_ms"], "device_routing_ms": info["device_routing_ms"],
+                     "device_routing_equals_host_routing": info["device_routing_equals_host_routing"],
+                     "exchange_bytes": HOT_ROWS * EMBED_D * 4}
         del shard
     if rank == 0:
         best = min(v["ms_per_step"] for v in out.values())
@@ -1244,6 +1335,9 @@ def main():
                     help="run one kernel of the table alone (map, keep_highdim, keep_lowest, softmax, softmax_grad, "
                          "pool, unpool, chpool, addtakegrad, ...) for --steps launches after --warmup; for profiling")
     ap.add_argument("--small", action="store_true", help="with --only: reduced size that still exceeds L2")
+    ap.add_argument("--trace-launches", action="store_true",
+                    help="with --only: time --steps launches one by one and report them in bins of 20 beside the "
+                         "sampled SM clock and throttle reasons")
     ap.add_argument("--workload", default="reductions", choices=["reductions", "embed_sharded"],
                     help="reductions: the headline workload; embed_sharded: AddTakeGradLargeBatch with the table "
                          "sharded by rows over the ranks (strong scaling, see embed_sharded_arm)")
@@ -1254,6 +1348,10 @@ def main():
         lib = mshadow_b200.load()
         lib.init(0)
         peak, _ = measured_peak()
+        if args.trace_launches:
+            print(json.dumps({"only": args.only, "small": args.small,
+                              "launch_trace": launch_trace(lib, torch, args.only, args.small, args.steps)}), flush=True)
+            return
         print(json.dumps({"only": args.only, "small": args.small,
                           "kernels": kernel_table(lib, torch, peak, only=args.only, small=args.small,
                                                   iters=args.steps, warm=args.warmup)}), flush=True)
@@ -1350,6 +1448,7 @@ def main():
 
     sampler = ClockSampler(local_rank)
     sampler.start()
+    sampler.period = 0.002            # the timed region may last only milliseconds
     for i in range(args.warmup):
         reductions(i)
     barrier()
@@ -1370,20 +1469,33 @@ def main():
     barrier()
     sampler.window[1] = time.perf_counter()
     launches = lib.launch_count() - launches0 + (2 * k if lag is not None else 0)  # + push and pull kernels
-    if lag is not None:
-        lag.drain(sums[(args.warmup + k - 1) & 1])
     seconds = e_start.elapsed_time(e_end) * 1e-3
     t_high = float(np.mean([ev[s][0].elapsed_time(ev[s][1]) for s in range(k)])) * 1e-3
     t_low = float(np.mean([ev[s][1].elapsed_time(ev[s][2]) for s in range(k)])) * 1e-3
     t_xchg = float(np.mean([ev[s][2].elapsed_time(ev[s][3]) for s in range(k)])) * 1e-3
     per_rank = np.array(gather_floats(torch, dist, dev, [seconds, t_high, t_low, t_xchg]))
     seconds = float(per_rank[:, 0].max())
+    # One NVML query takes milliseconds, so a short timed region may hold no clock sample at all:
+    # the same steps carry on, untimed, for a fifth of a second (the same number on every rank),
+    # and the clock record says which samples fall where.
+    extra = int(min(5000, max(0, 0.2 / max(1e-6, seconds / k) - k)))
+    sampler.tail_window[0] = time.perf_counter()
+    for s in range(extra):
+        reductions(args.warmup + k + s)
+    if lag is not None:
+        peer_side.pull_fence(0)
+    barrier()
+    sampler.tail_window[1] = time.perf_counter()
+    k_done = k + extra
+    sampler.period = 0.01
+    if lag is not None:
+        lag.drain(sums[(args.warmup + k_done - 1) & 1])
     value = ELEMS_PER_STEP * world * k / seconds / 1e9
     exchange_ok = None
     if peer is not None:
         # the last step's sum over the ranks against the rank-order sum of the gathered results
         from mshadow_b200 import sharding
-        last = (args.warmup + k - 1) & 1
+        last = (args.warmup + k_done - 1) & 1
         parts = [torch.zeros(NRES, device=dev) for _ in range(world)]
         dist.all_gather(parts, outs[last])
         want = sharding.rank_order_sum([p.cpu().numpy() for p in parts])

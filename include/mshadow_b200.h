@@ -236,6 +236,25 @@ int msb_addtakegrad_largebatch_f32_i32(float *dst, const int32_t *sorted, const 
 /* SortByKey(keys, values, is_ascend), stable: mshadow/tensor_gpu-inl.h:231-235 */
 int msb_sort_by_key_i32(int32_t *keys, int32_t *values, int64_t n, int ascend,
                         msb_stream_t stream);
+/* The `count` most frequent keys of an ascending key list, most frequent first, equal counts in
+   ascending key order: rows_out[count], counts_out[count] (device memory).  Fewer distinct keys
+   than `count` leave trailing entries with counts_out == 0.  Host-side helper of the row-sharded
+   AddTakeGradLargeBatch (mshadow/tensor_gpu-inl.h:223-229 on one slice of the table per GPU);
+   the reference has no multi-GPU form of it. */
+int msb_frequent_rows_i32(int32_t *rows_out, int32_t *counts_out, const int32_t *sorted,
+                          int64_t n, int64_t count, msb_stream_t stream);
+/* This GPU's part of AddTakeGradLargeBatch's (sorted, index) lists when table row r lives on
+   GPU r % world as local row r / world and the rows listed in `hot` (ascending, <= 1024) are
+   summed by every GPU over the source rows [src_begin, src_end) it holds.  Writes, in list order,
+   first the entries of this GPU's rows with keys rewritten to local rows, then its hot entries
+   with keys hot_base + position in `hot`; totals[0], totals[1] (device words) receive the two
+   counts.  keys_out / rows_out need room for n entries.  With hot_base = number of local rows the
+   output is one ascending list for a single msb_addtakegrad_largebatch_f32_i32 call. */
+int msb_route_cyclic_hot_i32(int32_t *keys_out, int32_t *rows_out, uint32_t *totals,
+                             const int32_t *sorted, const int32_t *index, int64_t n,
+                             const int32_t *hot, int64_t hot_count, int world, int rank,
+                             int64_t src_begin, int64_t src_end, int64_t hot_base,
+                             msb_stream_t stream);
 /* VectorizedSort(values, segments): values sorted ascending inside each run of equal
    `segments` (ascending on entry), two stable pair sorts: mshadow/tensor.h:905-915,
    mshadow/tensor_cpu-inl.h:562-567 */

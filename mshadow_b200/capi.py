@@ -73,6 +73,8 @@ _SIGNATURES = {
     "msb_addtakegrad_largebatch_f32_i32": [vp, vp, vp, vp, i64, i64, i64, vp],
     "msb_sort_by_key_i32": [vp, vp, i64, cint, vp],
     "msb_vectorized_sort_f32_i32": [vp, vp, i64, vp],
+    "msb_frequent_rows_i32": [vp, vp, vp, i64, i64, vp],
+    "msb_route_cyclic_hot_i32": [vp, vp, vp, vp, vp, i64, vp, i64, cint, cint, i64, i64, i64, vp],
     "msb_index_fill_f32_i32": [vp, vp, vp, i64, i64, i64, vp],
     "msb_remap_shape": [cint, i64, i64, i64, i64, i64, i64, vp],
     "msb_complex_case_f32": [cint, vp, vp, vp, i64, i64, vp],
@@ -284,6 +286,18 @@ class Library:
         self.call("msb_addtakegrad_largebatch_f32_i32", _ptr(dst), _ptr(sorted_), _ptr(index), _ptr(src), k,
                   d, index.shape[0], stream)
         return dst
+
+    def frequent_rows(self, rows_out, counts_out, sorted_, stream=None):
+        self.call("msb_frequent_rows_i32", _ptr(rows_out), _ptr(counts_out), _ptr(sorted_), sorted_.shape[0],
+                  rows_out.shape[0], stream)
+        return rows_out, counts_out
+
+    def route_cyclic_hot(self, keys_out, rows_out, totals, sorted_, index, hot, world, rank, src_begin, src_end,
+                         hot_base, stream=None):
+        self.call("msb_route_cyclic_hot_i32", _ptr(keys_out), _ptr(rows_out), _ptr(totals), _ptr(sorted_), _ptr(index),
+                  sorted_.shape[0], _ptr(hot) if hot is not None else None, 0 if hot is None else hot.shape[0],
+                  world, rank, src_begin, src_end, hot_base, stream)
+        return keys_out, rows_out, totals
 
     def sort_by_key(self, keys, values, ascend=True, stream=None):
         self.call("msb_sort_by_key_i32", _ptr(keys), _ptr(values), keys.shape[0], int(ascend), stream)

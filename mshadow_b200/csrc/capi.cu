@@ -605,6 +605,48 @@ int msb_sort_by_key_i32(int32_t *keys, int32_t *values, int64_t n, int ascend, m
   MSB_GUARD_END
 }
 
+int msb_frequent_rows_i32(int32_t *rows_out, int32_t *counts_out, const int32_t *sorted, int64_t n, int64_t count,
+                          msb_stream_t stream) {
+  MSB_REQUIRE(FitsIndex(n) && count >= 0 && count <= n, MSB_ERR_SHAPE, "extent out of range");
+  if (count == 0) return MSB_OK;
+  MSB_REQUIRE(rows_out && counts_out && sorted, MSB_ERR_ARGUMENT, "null pointer");
+  MSB_GUARD_BEGIN
+  BorrowedStream st(stream);
+  cudaStream_t cs = Stream<gpu>::GetStream(st.get());
+  using mshadow::cuda::sortdetail::Align256;
+  const size_t ib = Align256(static_cast<size_t>(n) * 4);
+  const size_t sort_bytes = mshadow::cuda::sortdetail::ScratchBytes(n);
+  char *base = static_cast<char *>(mshadow::gpu_rt::Scratch::Get(cs, 2 * ib + sort_bytes));
+  int32_t *lens = reinterpret_cast<int32_t *>(base), *rows = reinterpret_cast<int32_t *>(base + ib);
+  mshadow::cuda::RunLengthLaunch(lens, rows, sorted, n, cs);
+  // run lengths in descending order, stable: equal counts stay in ascending row order
+  int bits = 1;
+  while (bits < 31 && (int64_t(1) << bits) <= n) ++bits;
+  const mshadow::cuda::sortdetail::Source as_given = {0};
+  mshadow::cuda::sortdetail::SortPairs<int32_t, int32_t>(lens, rows, lens, n, bits, false, as_given, base + 2 * ib, cs);
+  MSHADOW_CUDA_CALL(cudaMemcpyAsync(counts_out, lens, count * 4, cudaMemcpyDeviceToDevice, cs));
+  MSHADOW_CUDA_CALL(cudaMemcpyAsync(rows_out, rows, count * 4, cudaMemcpyDeviceToDevice, cs));
+  MSB_GUARD_END
+}
+
+int msb_route_cyclic_hot_i32(int32_t *keys_out, int32_t *rows_out, uint32_t *totals, const int32_t *sorted,
+                             const int32_t *index, int64_t n, const int32_t *hot, int64_t hot_count, int world,
+                             int rank, int64_t src_begin, int64_t src_end, int64_t hot_base, msb_stream_t stream) {
+  MSB_REQUIRE(FitsIndex(n) && FitsIndex(src_begin) && FitsIndex(src_end) && FitsIndex(hot_base) && hot_count >= 0 &&
+                  hot_count <= mshadow::cuda::routedetail::kMaxHot,
+              MSB_ERR_SHAPE, "extent out of range");
+  MSB_REQUIRE(world >= 1 && rank >= 0 && rank < world, MSB_ERR_ARGUMENT, "rank outside the group");
+  MSB_REQUIRE(totals, MSB_ERR_ARGUMENT, "null pointer");
+  MSB_REQUIRE(n == 0 || (keys_out && rows_out && sorted && index), MSB_ERR_ARGUMENT, "null pointer");
+  MSB_REQUIRE(hot_count == 0 || hot, MSB_ERR_ARGUMENT, "null pointer");
+  MSB_GUARD_BEGIN
+  BorrowedStream st(stream);
+  mshadow::cuda::RouteCyclicHotLaunch(keys_out, rows_out, totals, sorted, index, n, hot, static_cast<int>(hot_count),
+                                      world, rank, static_cast<int32_t>(src_begin), static_cast<int32_t>(src_end),
+                                      static_cast<int32_t>(hot_base), Stream<gpu>::GetStream(st.get()));
+  MSB_GUARD_END
+}
+
 int msb_softmax3d_f32(float *dst, const float *src, int64_t batch, int64_t classes, int64_t npos, int64_t ld_dst,
                       int64_t ld_src, msb_stream_t stream) {
   MSB_REQUIRE(FitsIndex(batch) && FitsIndex(classes) && FitsIndex(npos) && FitsIndex(batch * classes) &&

@@ -14,9 +14,12 @@
  * the key stays the same.  A run that lies wholly inside one chunk is added to its table
  * row directly.  A run that crosses a chunk boundary leaves one partial row per chunk in a
  * scratch matrix; those partial rows, keyed by table row and still in sorted order, are the
- * input of the same kernel one level up.  Levels shrink by a factor of kSegChunk / 2, so a
- * million entries take four launches, the last three tiny.  No atomics are used and every
- * addition order is fixed by the chunk geometry, so results are reproducible.
+ * input of the same kernel one level up.  The first level of a long list uses chunks of
+ * kSegChunk entries and is bound by bandwidth; the levels above it are a few CTAs each and bound
+ * by latency, so they use short chunks (kSegChunkUpper entries, shrinking a level by half that
+ * factor), all their rows in flight at once, and add to the table rows in batches.  A million
+ * entries take six launches, the last five a few microseconds each.  No atomics are used and
+ * every addition order is fixed by the chunk geometry, so results are reproducible.
  *
  * Traffic: each source row is read once (4*N*D bytes), each touched table row is read and
  * written once, partial rows add a few percent.  The kernel is bound by HBM bandwidth.
@@ -37,21 +40,33 @@ const uint32_t kSegChunk = MSHADOW_B200_SEG_CHUNK;
 const int kSegDepth = MSHADOW_B200_SEG_DEPTH;
 const uint32_t kSegRing = MSHADOW_B200_SEG_RING;       // source rows in flight per CTA of the staged kernel
 const uint32_t kSegSlab = 1024;                        // features per CTA: 256 threads x 4
+const int kSegDepthUpper = 8;                          // rows in flight per thread above the first level
+const uint32_t kSegChunkUpper = MSHADOW_B200_SEG_CHUNK_UPPER;  // entries per CTA above the first level
+const uint32_t kSegStagedMinChunks = MSHADOW_B200_SEG_STAGED_MIN_CHUNKS;
 
 /*!
  * \brief one level of the chunked segmented sum.
  *  keys[n] ascending; rows[n] (or identity when null) names the source row of each entry, a
  *  negative row contributes nothing.  part_keys / part_rows / partials receive two slots per
- *  chunk for the next level.  grid = (chunks, feature slabs).
+ *  chunk for the next level.  grid = (chunks, feature slabs).  kDepth source rows are in flight
+ *  per thread: kSegDepth on the first level, which is bound by bandwidth and wants many CTAs per
+ *  SM, kSegDepthUpper on the levels above it, which are a few CTAs each walking a list of partial
+ *  rows and are bound by the latency of those loads.
  */
-template <int kLanes>
-__global__ void __launch_bounds__(256, MSHADOW_B200_SEG_MIN_CTAS)
+template <int kLanes, int kDepth>
+__global__ void __launch_bounds__(256, kDepth > 4 ? 2 : MSHADOW_B200_SEG_MIN_CTAS)
 SegmentSumKernel(float *dst, int64_t ld_dst, const int32_t *keys, const int32_t *rows, const float *src,
-                 int64_t ld_src, uint32_t n, uint32_t width, int32_t *part_keys, int32_t *part_rows,
-                 float *partials) {
+                 int64_t ld_src, uint32_t n, uint32_t width, uint32_t chunk_len, int32_t *part_keys,
+                 int32_t *part_rows, float *partials) {
+  // With kDepth > 4 (the upper levels) the additions to table rows are batched: a run that ends
+  // inside a batch of kDepth entries is parked, and once the batch has been walked the table rows
+  // of all parked runs are loaded together, added to and stored.  Done one by one -- load, add,
+  // store at the moment the run ends -- a CTA walking 64 entries of 64 different rows spent 44 us
+  // on the 64 dependent round trips.
+  constexpr bool kBatched = kDepth > 4;
   const uint32_t chunk = blockIdx.x;
-  const uint32_t begin = chunk * kSegChunk;
-  const uint32_t end = min(n, begin + kSegChunk);
+  const uint32_t begin = chunk * chunk_len;
+  const uint32_t end = min(n, begin + chunk_len);
   const uint32_t col = (blockIdx.y * blockDim.x + threadIdx.x) * kLanes;
   const bool active = col < width;
   const bool lead = blockIdx.y == 0 && threadIdx.x == 0;
@@ -69,22 +84,31 @@ SegmentSumKernel(float *dst, int64_t ld_dst, const int32_t *keys, const int32_t 
 #pragma unroll
   for (int l = 0; l < kLanes; ++l) acc[l] = 0.0f;
 
-  // add a finished run to its table row, or park it in the scratch matrix if it continues
-  // in a neighbouring chunk
-  auto flush = [&](bool last_run) {
+  auto add_to_row = [&](float *row, const float (&a)[kLanes]) {
+    if (kLanes == 4) {
+      float4 d = *reinterpret_cast<float4 *>(row);
+      d.x = __fadd_rn(d.x, a[0]);
+      d.y = __fadd_rn(d.y, a[1 % kLanes]);
+      d.z = __fadd_rn(d.z, a[2 % kLanes]);
+      d.w = __fadd_rn(d.w, a[3 % kLanes]);
+      *reinterpret_cast<float4 *>(row) = d;
+    } else {
+      row[0] = __fadd_rn(row[0], a[0]);
+    }
+  };
+  // a finished run: parked in the scratch matrix if it continues in a neighbouring chunk, else
+  // added to its table row -- at once, or (park != nullptr) handed back to be added with its batch
+  auto flush = [&](bool last_run, float **park, float (*park_acc)[kLanes]) {
     const bool spans = (first_run && joins_prev) || (last_run && joins_next);
     if (!spans) {
       if (any && active) {
         float *row = dst + static_cast<int64_t>(cur) * ld_dst + col;
-        if (kLanes == 4) {
-          float4 d = *reinterpret_cast<float4 *>(row);
-          d.x = __fadd_rn(d.x, acc[0]);
-          d.y = __fadd_rn(d.y, acc[1 % kLanes]);
-          d.z = __fadd_rn(d.z, acc[2 % kLanes]);
-          d.w = __fadd_rn(d.w, acc[3 % kLanes]);
-          *reinterpret_cast<float4 *>(row) = d;
+        if (park != nullptr) {
+          *park = row;
+#pragma unroll
+          for (int l = 0; l < kLanes; ++l) (*park_acc)[l] = acc[l];
         } else {
-          row[0] = __fadd_rn(row[0], acc[0]);
+          add_to_row(row, acc);
         }
       }
     } else if (any) {
@@ -101,18 +125,18 @@ SegmentSumKernel(float *dst, int64_t ld_dst, const int32_t *keys, const int32_t 
     }
   };
 
-  for (uint32_t i = begin; i < end; i += kSegDepth) {
-    int32_t k[kSegDepth], r[kSegDepth];
-    float v[kSegDepth][kLanes];
+  for (uint32_t i = begin; i < end; i += kDepth) {
+    int32_t k[kDepth], r[kDepth];
+    float v[kDepth][kLanes];
 #pragma unroll
-    for (int u = 0; u < kSegDepth; ++u) {
+    for (int u = 0; u < kDepth; ++u) {
       const uint32_t e = i + u;
       const bool in = e < end;
       k[u] = in ? keys[e] : 0;
       r[u] = in ? (rows != nullptr ? rows[e] : static_cast<int32_t>(e)) : -1;
     }
 #pragma unroll
-    for (int u = 0; u < kSegDepth; ++u) {
+    for (int u = 0; u < kDepth; ++u) {
       if (r[u] >= 0 && active) {
         const float *p = src + static_cast<int64_t>(r[u]) * ld_src + col;
         if (kLanes == 4) {
@@ -129,11 +153,15 @@ SegmentSumKernel(float *dst, int64_t ld_dst, const int32_t *keys, const int32_t 
         for (int l = 0; l < kLanes; ++l) v[u][l] = 0.0f;
       }
     }
+    float *parked[kBatched ? kDepth : 1];
+    float parked_acc[kBatched ? kDepth : 1][kLanes];
 #pragma unroll
-    for (int u = 0; u < kSegDepth; ++u) {
+    for (int u = 0; u < (kBatched ? kDepth : 1); ++u) parked[u] = nullptr;
+#pragma unroll
+    for (int u = 0; u < kDepth; ++u) {
       if (i + u < end) {
         if (k[u] != cur) {
-          flush(false);
+          if (kBatched) flush(false, &parked[kBatched ? u : 0], &parked_acc[kBatched ? u : 0]); else flush(false, nullptr, nullptr);
           cur = k[u];
           first_run = false;
           any = false;
@@ -147,8 +175,39 @@ SegmentSumKernel(float *dst, int64_t ld_dst, const int32_t *keys, const int32_t 
         }
       }
     }
+    if (kBatched) {
+      // table rows of the runs that ended in this batch: all loads first, then the additions
+      float d[kDepth][kLanes];
+#pragma unroll
+      for (int u = 0; u < kDepth; ++u) {
+        if (parked[u] != nullptr) {
+          if (kLanes == 4) {
+            const float4 q = *reinterpret_cast<const float4 *>(parked[u]);
+            d[u][0] = q.x;
+            d[u][1 % kLanes] = q.y;
+            d[u][2 % kLanes] = q.z;
+            d[u][3 % kLanes] = q.w;
+          } else {
+            d[u][0] = parked[u][0];
+          }
+        }
+      }
+#pragma unroll
+      for (int u = 0; u < kDepth; ++u) {
+        if (parked[u] != nullptr) {
+          if (kLanes == 4) {
+            *reinterpret_cast<float4 *>(parked[u]) =
+                make_float4(__fadd_rn(d[u][0], parked_acc[u][0]), __fadd_rn(d[u][1 % kLanes], parked_acc[u][1 % kLanes]),
+                            __fadd_rn(d[u][2 % kLanes], parked_acc[u][2 % kLanes]),
+                            __fadd_rn(d[u][3 % kLanes], parked_acc[u][3 % kLanes]));
+          } else {
+            parked[u][0] = __fadd_rn(d[u][0], parked_acc[u][0]);
+          }
+        }
+      }
+    }
   }
-  flush(true);
+  flush(true, nullptr, nullptr);
 }
 
 /*!
@@ -229,6 +288,9 @@ SegmentSumStagedKernel(float *dst, int64_t ld_dst, const int32_t *keys, const in
   int32_t cur = s_keys[0];
   bool first_run = true, any = false;
   float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+  // (Loading the table row when a run ends and adding to it when the next one ends would hide the
+  // round trip, but the 16 registers it takes leave four CTAs per SM instead of five: measured
+  // 0.87 against 0.93 of the copy bandwidth.)
   auto flush = [&](bool last_run) {
     const bool spans = (first_run && joins_prev) || (last_run && joins_next);
     if (!spans) {
@@ -294,13 +356,23 @@ __global__ void ClipIotaKernel(IndexType *keys, IndexType *vals, const IndexType
 namespace embeddetail {
 inline size_t Align256(size_t b) { return (b + 255) / 256 * 256; }
 
-/*! \brief chunk counts of every level until one chunk remains */
-inline int Levels(uint32_t n, uint32_t (&entries)[8], uint32_t (&chunks)[8]) {
+const int kMaxLevels = 16;
+
+/*!
+ * \brief entries, chunk length and chunk count of every level until one chunk remains.
+ *  The first level of a long list uses chunks of kSegChunk entries (bandwidth: few, long CTAs);
+ *  the levels above it, and every level of a short list, use chunks of kSegChunkUpper entries:
+ *  they are bound by latency, and shorter chunks spread their rows over more CTAs.
+ */
+inline int Levels(uint32_t n, uint32_t (&entries)[kMaxLevels], uint32_t (&chunks)[kMaxLevels],
+                  uint32_t (&len)[kMaxLevels]) {
   int levels = 0;
   uint32_t cur = n;
-  while (levels < 8) {
+  const bool long_list = (n + kSegChunk - 1) / kSegChunk >= kSegStagedMinChunks;
+  while (levels < kMaxLevels) {
     entries[levels] = cur;
-    chunks[levels] = (cur + kSegChunk - 1) / kSegChunk;
+    len[levels] = (levels == 0 && long_list) ? kSegChunk : kSegChunkUpper;
+    chunks[levels] = (cur + len[levels] - 1) / len[levels];
     ++levels;
     if (chunks[levels - 1] <= 1) break;
     cur = 2 * chunks[levels - 1];
@@ -310,8 +382,8 @@ inline int Levels(uint32_t n, uint32_t (&entries)[8], uint32_t (&chunks)[8]) {
 
 /*! \brief bytes of scratch the levels below need (partial rows + their keys and row ids) */
 inline size_t SegmentScratchBytes(uint32_t n, uint32_t width) {
-  uint32_t entries[8], chunks[8];
-  const int levels = Levels(n, entries, chunks);
+  uint32_t entries[kMaxLevels], chunks[kMaxLevels], len[kMaxLevels];
+  const int levels = Levels(n, entries, chunks, len);
   size_t bytes = 0;
   for (int l = 0; l + 1 < levels; ++l) {
     bytes += Align256(2ull * chunks[l] * width * sizeof(float));
@@ -324,8 +396,8 @@ inline size_t SegmentScratchBytes(uint32_t n, uint32_t width) {
 inline void SegmentSumRun(float *dst, int64_t ld_dst, const int32_t *keys, const int32_t *rows, const float *src,
                           int64_t ld_src, uint32_t n, uint32_t width, char *scratch, cudaStream_t stream) {
   if (n == 0 || width == 0) return;
-  uint32_t entries[8], chunks[8];
-  const int levels = Levels(n, entries, chunks);
+  uint32_t entries[kMaxLevels], chunks[kMaxLevels], len[kMaxLevels];
+  const int levels = Levels(n, entries, chunks, len);
   const int32_t *lkeys = keys, *lrows = rows;
   const float *lsrc = src;
   int64_t lld = ld_src;
@@ -346,19 +418,29 @@ inline void SegmentSumRun(float *dst, int64_t ld_dst, const int32_t *keys, const
     uint32_t threads = (items + 31) / 32 * 32;
     if (threads > 256) threads = 256;
     const dim3 grid(chunks[l], (items + threads - 1) / threads);
-    if (vec && MSHADOW_B200_SEG_STAGED && width >= 256) {
-      // rows of a kilobyte and more: staged through shared memory by bulk copies
+    const bool long_chunks = len[l] == kSegChunk && kSegChunk != kSegChunkUpper;
+    if (vec && MSHADOW_B200_SEG_STAGED && width >= 256 && long_chunks) {
+      // rows of a kilobyte and more, enough chunks to fill the GPU: staged through shared memory by
+      // bulk copies.  (Measured on a list of 2039 chunks: the staged kernel took 32, 28 and 4.5 us
+      // for the three upper levels of 64, 2 and 1 chunks -- its in-order ring serves a lone CTA one
+      // row per 0.44 us -- which is why those levels use the register form.)
       auto kernel = SegmentSumStagedKernel<static_cast<int>(kSegRing)>;
       const size_t smem = static_cast<size_t>(kSegRing) * kSegSlab * sizeof(float);
       MSHADOW_CUDA_CALL(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
       kernel<<<dim3(chunks[l], (width + kSegSlab - 1) / kSegSlab), 288, smem, stream>>>(
           dst, ld_dst, lkeys, lrows, lsrc, lld, entries[l], width, pk, pr, pp, gpu_rt::StatusWord());
+    } else if (vec && long_chunks) {
+      SegmentSumKernel<4, kSegDepth><<<grid, threads, 0, stream>>>(dst, ld_dst, lkeys, lrows, lsrc, lld, entries[l],
+                                                                   width, len[l], pk, pr, pp);
     } else if (vec) {
-      SegmentSumKernel<4><<<grid, threads, 0, stream>>>(dst, ld_dst, lkeys, lrows, lsrc, lld, entries[l], width, pk,
-                                                       pr, pp);
+      SegmentSumKernel<4, kSegDepthUpper><<<grid, threads, 0, stream>>>(dst, ld_dst, lkeys, lrows, lsrc, lld,
+                                                                        entries[l], width, len[l], pk, pr, pp);
+    } else if (long_chunks) {
+      SegmentSumKernel<1, kSegDepth><<<grid, threads, 0, stream>>>(dst, ld_dst, lkeys, lrows, lsrc, lld, entries[l],
+                                                                   width, len[l], pk, pr, pp);
     } else {
-      SegmentSumKernel<1><<<grid, threads, 0, stream>>>(dst, ld_dst, lkeys, lrows, lsrc, lld, entries[l], width, pk,
-                                                       pr, pp);
+      SegmentSumKernel<1, kSegDepthUpper><<<grid, threads, 0, stream>>>(dst, ld_dst, lkeys, lrows, lsrc, lld,
+                                                                        entries[l], width, len[l], pk, pr, pp);
     }
     MSHADOW_CUDA_POST_KERNEL_CHECK(SegmentSumKernel);
     lkeys = pk;

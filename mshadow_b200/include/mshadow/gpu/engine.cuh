@@ -16,6 +16,7 @@
 #include "./embed.cuh"
 #include "./map.cuh"
 #include "./reduce.cuh"
+#include "./route.cuh"
 #include "./softmax.cuh"
 
 namespace mshadow {

@@ -876,7 +876,7 @@ ChannelPoolStagedKernel(float *dst, const float *src, uint32_t channels, uint32_
         win[j][1] = v.y;
         win[j][2] = v.z;
         win[j][3] = v.w;
-        if (s >= 2 * kPad && mine) {
+        if (s + 1 > 2 * kPad && mine) {
           // window of output channel ch - kPad: the last NSIZE loaded channels, oldest first
           float res[4] = {init, init, init, init};
 #pragma unroll

@@ -1,0 +1,252 @@
+/*
+ * Routing of a sorted (table row, source row) list to the GPU that owns the table rows, on the
+ * device.  Used when the table of AddTakeGradLargeBatch (mshadow/cuda/tensor_gpu-inl.cuh:619-672:
+ * dst[sorted[y]] += src[index[y]]) is spread over several GPUs with row r owned by GPU r % world
+ * and a short list of frequent ("hot") rows summed by every GPU over its slice of the batch.
+ *
+ *   RunLengthKernel      for every list entry that starts a run of equal keys: the run's length
+ *                        (0 for the other entries).  Sorting these lengths in descending order
+ *                        with the engine's stable radix sort puts the most frequent rows first,
+ *                        equal counts in ascending row order.
+ *   RouteCountKernel     per tile of the list, how many entries belong to this GPU's "tail" part
+ *                        (key not hot, key % world == rank) and to its "hot" part (key hot, source
+ *                        row inside [src_begin, src_end)).
+ *   RouteScanKernel      exclusive scan of the per-tile counts (one CTA), totals to `totals`.
+ *   RouteScatterKernel   writes the selected entries in list order: first the tail part with keys
+ *                        rewritten to local rows (key / world), then the hot part with keys
+ *                        rewritten to hot_base + position in the hot list.  Both parts are sorted,
+ *                        and every hot key is larger than every tail key when hot_base is the
+ *                        number of local rows, so the output is again one sorted list.
+ *
+ * The selection is stable, so each table row keeps its accumulation order.  All arithmetic is on
+ * 32-bit integers; results are exact.
+ */
+#ifndef MSHADOW_GPU_ROUTE_CUH_
+#define MSHADOW_GPU_ROUTE_CUH_
+
+#include "./runtime.h"
+
+namespace mshadow {
+namespace cuda {
+namespace routedetail {
+const int kThreads = 256;
+const int kItems = 8;                       // consecutive entries per thread
+const int kTile = kThreads * kItems;
+const int kMaxHot = 1024;                   // hot list length the kernels keep in shared memory
+
+struct Geometry {
+  int32_t world, rank;
+  int32_t src_begin, src_end;               // source rows held by this GPU (for the hot part)
+  int32_t hot_count, hot_base;
+};
+
+/*! \brief 0: tail entry of this GPU, 1: hot entry of this GPU, 2: not ours; `pos` = position in the hot list */
+__device__ __forceinline__ int Classify(int32_t key, int32_t row, const Geometry &g, const int32_t *s_hot, int32_t *pos) {
+  // lower bound of key in the ascending hot list
+  int lo = 0, hi = g.hot_count;
+  while (lo < hi) {
+    const int mid = (lo + hi) >> 1;
+    if (s_hot[mid] < key) lo = mid + 1; else hi = mid;
+  }
+  if (lo < g.hot_count && s_hot[lo] == key) {
+    *pos = lo;
+    return (row >= g.src_begin && row < g.src_end) ? 1 : 2;
+  }
+  return (key % g.world == g.rank) ? 0 : 2;
+}
+
+/*! \brief inclusive scan of one value per thread over a CTA of kThreads; returns this thread's exclusive prefix, total in *total */
+__device__ __forceinline__ uint32_t CtaExclusiveScan(uint32_t v, uint32_t *s_warp, uint32_t *total) {
+  const uint32_t lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  uint32_t inc = v;
+#pragma unroll
+  for (int d = 1; d < 32; d <<= 1) {
+    const uint32_t o = __shfl_up_sync(0xffffffffu, inc, d);
+    if (lane >= static_cast<uint32_t>(d)) inc += o;
+  }
+  if (lane == 31) s_warp[warp] = inc;
+  __syncthreads();
+  uint32_t base = 0, sum = 0;
+#pragma unroll
+  for (int w = 0; w < kThreads / 32; ++w) {
+    if (static_cast<uint32_t>(w) < warp) base += s_warp[w];
+    sum += s_warp[w];
+  }
+  *total = sum;
+  __syncthreads();
+  return base + inc - v;
+}
+}  // namespace routedetail
+
+/*! \brief lens[i] = length of the run of equal keys starting at i, 0 if i does not start one; rows[i] = keys[i] */
+template <int kDummy>
+__global__ void __launch_bounds__(256)
+RunLengthKernel(int32_t *lens, int32_t *rows, const int32_t *keys, uint32_t n) {
+  const uint32_t i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  const int32_t k = keys[i];
+  rows[i] = k;
+  if (i > 0 && keys[i - 1] == k) {
+    lens[i] = 0;
+    return;
+  }
+  // first position after i whose key differs: doubling steps, then bisection
+  uint32_t lo = i, step = 1;            // keys[lo] == k
+  uint32_t hi = n;                      // keys[hi] != k (or hi == n)
+  while (lo + step < n) {
+    if (keys[lo + step] != k) {
+      hi = lo + step;
+      break;
+    }
+    lo += step;
+    step <<= 1;
+  }
+  while (hi - lo > 1) {
+    const uint32_t mid = lo + ((hi - lo) >> 1);
+    if (keys[mid] == k) lo = mid; else hi = mid;
+  }
+  lens[i] = static_cast<int32_t>(hi - i);
+}
+
+/*! \brief counts[tile] = tail entries, counts[tiles + tile] = hot entries of this GPU in the tile */
+template <int kDummy>
+__global__ void __launch_bounds__(routedetail::kThreads)
+RouteCountKernel(uint32_t *counts, const int32_t *keys, const int32_t *rows, uint32_t n, const int32_t *hot,
+                 const routedetail::Geometry g) {
+  using namespace routedetail;
+  __shared__ int32_t s_hot[kMaxHot];
+  __shared__ uint32_t s_warp[kThreads / 32];
+  for (int j = threadIdx.x; j < g.hot_count; j += kThreads) s_hot[j] = hot[j];
+  __syncthreads();
+  const uint32_t first = blockIdx.x * kTile + threadIdx.x * kItems;
+  uint32_t mine = 0;                    // tail count in the low half, hot count in the high half
+#pragma unroll
+  for (int u = 0; u < kItems; ++u) {
+    const uint32_t e = first + u;
+    if (e < n) {
+      int32_t pos;
+      const int c = Classify(keys[e], rows[e], g, s_hot, &pos);
+      mine += c == 0 ? 1u : (c == 1 ? 65536u : 0u);
+    }
+  }
+  uint32_t total;
+  CtaExclusiveScan(mine, s_warp, &total);
+  if (threadIdx.x == 0) {
+    counts[blockIdx.x] = total & 0xffffu;
+    counts[gridDim.x + blockIdx.x] = total >> 16;
+  }
+}
+
+/*! \brief in-place exclusive scan of counts[0 .. 2*tiles) as two arrays of `tiles`; totals[0] = tail entries, totals[1] = hot entries */
+template <int kDummy>
+__global__ void __launch_bounds__(routedetail::kThreads)
+RouteScanKernel(uint32_t *counts, uint32_t tiles, uint32_t *totals) {
+  using namespace routedetail;
+  __shared__ uint32_t s_warp[kThreads / 32];
+  for (int part = 0; part < 2; ++part) {
+    uint32_t *c = counts + part * tiles;
+    uint32_t running = 0;
+    for (uint32_t t0 = 0; t0 < tiles; t0 += kThreads) {
+      const uint32_t t = t0 + threadIdx.x;
+      const uint32_t v = t < tiles ? c[t] : 0u;
+      uint32_t total;
+      const uint32_t ex = CtaExclusiveScan(v, s_warp, &total);
+      if (t < tiles) c[t] = running + ex;
+      running += total;
+    }
+    if (threadIdx.x == 0) totals[part] = running;
+  }
+}
+
+/*! \brief writes this GPU's entries: tail part at [0, totals[0]), hot part behind it */
+template <int kDummy>
+__global__ void __launch_bounds__(routedetail::kThreads)
+RouteScatterKernel(int32_t *out_keys, int32_t *out_rows, const uint32_t *bases, const uint32_t *totals,
+                   const int32_t *keys, const int32_t *rows, uint32_t n, const int32_t *hot,
+                   const routedetail::Geometry g) {
+  using namespace routedetail;
+  __shared__ int32_t s_hot[kMaxHot];
+  __shared__ uint32_t s_warp[kThreads / 32];
+  for (int j = threadIdx.x; j < g.hot_count; j += kThreads) s_hot[j] = hot[j];
+  __syncthreads();
+  const uint32_t first = blockIdx.x * kTile + threadIdx.x * kItems;
+  int32_t k[kItems], r[kItems], pos[kItems];
+  int cls[kItems];
+  uint32_t mine = 0;
+#pragma unroll
+  for (int u = 0; u < kItems; ++u) {
+    const uint32_t e = first + u;
+    cls[u] = 2;
+    pos[u] = 0;
+    if (e < n) {
+      k[u] = keys[e];
+      r[u] = rows[e];
+      cls[u] = Classify(k[u], r[u], g, s_hot, &pos[u]);
+      mine += cls[u] == 0 ? 1u : (cls[u] == 1 ? 65536u : 0u);
+    }
+  }
+  uint32_t total;
+  const uint32_t ex = CtaExclusiveScan(mine, s_warp, &total);
+  uint32_t at_tail = bases[blockIdx.x] + (ex & 0xffffu);
+  uint32_t at_hot = totals[0] + bases[gridDim.x + blockIdx.x] + (ex >> 16);
+#pragma unroll
+  for (int u = 0; u < kItems; ++u) {
+    if (cls[u] == 0) {
+      out_keys[at_tail] = k[u] / g.world;
+      out_rows[at_tail] = r[u];
+      ++at_tail;
+    } else if (cls[u] == 1) {
+      out_keys[at_hot] = g.hot_base + pos[u];
+      out_rows[at_hot] = r[u];
+      ++at_hot;
+    }
+  }
+}
+
+namespace routedetail {
+inline size_t Align256(size_t b) { return (b + 255) / 256 * 256; }
+inline uint32_t Tiles(int64_t n) { return static_cast<uint32_t>((n + kTile - 1) / kTile); }
+/*! \brief bytes of scratch RouteCyclicHotLaunch needs */
+inline size_t RouteScratchBytes(int64_t n) { return Align256(2ull * Tiles(n) * sizeof(uint32_t)); }
+}  // namespace routedetail
+
+/*!
+ * \brief this GPU's part of a sorted (key, source row) list under cyclic row ownership with hot rows.
+ *  out_keys / out_rows need room for n entries; totals (two device words) receives the number of
+ *  tail and of hot entries written.  `hot` is ascending, at most routedetail::kMaxHot long.
+ */
+inline void RouteCyclicHotLaunch(int32_t *out_keys, int32_t *out_rows, uint32_t *totals, const int32_t *keys,
+                                 const int32_t *rows, int64_t n, const int32_t *hot, int hot_count, int world, int rank,
+                                 int32_t src_begin, int32_t src_end, int32_t hot_base, cudaStream_t stream) {
+  using namespace routedetail;
+  CHECK_LT(n, (int64_t(1) << 31));
+  CHECK(hot_count >= 0 && hot_count <= kMaxHot) << "RouteCyclicHot: at most " << kMaxHot << " hot rows";
+  CHECK(world >= 1 && rank >= 0 && rank < world) << "RouteCyclicHot: rank outside the group";
+  if (n == 0) {
+    MSHADOW_CUDA_CALL(cudaMemsetAsync(totals, 0, 2 * sizeof(uint32_t), stream));
+    return;
+  }
+  const uint32_t tiles = Tiles(n);
+  uint32_t *counts = static_cast<uint32_t *>(gpu_rt::Scratch::Get(stream, RouteScratchBytes(n)));
+  const Geometry g = {world, rank, src_begin, src_end, hot_count, hot_base};
+  const uint32_t un = static_cast<uint32_t>(n);
+  RouteCountKernel<0><<<tiles, kThreads, 0, stream>>>(counts, keys, rows, un, hot, g);
+  MSHADOW_CUDA_POST_KERNEL_CHECK(RouteCountKernel);
+  RouteScanKernel<0><<<1, kThreads, 0, stream>>>(counts, tiles, totals);
+  MSHADOW_CUDA_POST_KERNEL_CHECK(RouteScanKernel);
+  RouteScatterKernel<0><<<tiles, kThreads, 0, stream>>>(out_keys, out_rows, counts, totals, keys, rows, un, hot, g);
+  MSHADOW_CUDA_POST_KERNEL_CHECK(RouteScatterKernel);
+}
+
+/*! \brief lens[i] = run length at run heads of the sorted list, 0 elsewhere; rows[i] = keys[i] */
+inline void RunLengthLaunch(int32_t *lens, int32_t *rows, const int32_t *keys, int64_t n, cudaStream_t stream) {
+  if (n == 0) return;
+  CHECK_LT(n, (int64_t(1) << 31));
+  RunLengthKernel<0><<<gpu_rt::CeilDiv(static_cast<uint32_t>(n), 256u), 256, 0, stream>>>(lens, rows, keys,
+                                                                                        static_cast<uint32_t>(n));
+  MSHADOW_CUDA_POST_KERNEL_CHECK(RunLengthKernel);
+}
+
+}  // namespace cuda
+}  // namespace mshadow
+#endif  // MSHADOW_GPU_ROUTE_CUH_

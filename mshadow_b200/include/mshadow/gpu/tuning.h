@@ -33,6 +33,12 @@
 #ifndef MSHADOW_B200_SEG_STAGED
 #define MSHADOW_B200_SEG_STAGED 1  // segmented sum: source rows through a shared-memory ring filled by bulk copies
 #endif
+#ifndef MSHADOW_B200_SEG_STAGED_MIN_CHUNKS
+#define MSHADOW_B200_SEG_STAGED_MIN_CHUNKS 296  // first-level chunks (two per SM) from which the staged form is used
+#endif
+#ifndef MSHADOW_B200_SEG_CHUNK_UPPER
+#define MSHADOW_B200_SEG_CHUNK_UPPER 16  // entries per CTA on the levels above the first, and on every level of a short list
+#endif
 #ifndef MSHADOW_B200_SEG_RING
 #define MSHADOW_B200_SEG_RING 8  // rows (of up to 4 KB) in flight per CTA of the staged segmented sum
 #endif

@@ -350,7 +350,11 @@ def test_lrn_forward_backward(lib, power_kind, shape, nsize):
 
 @pytest.mark.parametrize("k,d,n,kind", [(11, 20, 300, "uniform"), (50, 64, 600, "uniform"), (1, 8, 1000, "uniform"),
                                         (4000, 128, 3000, "distinct"), (300, 1024, 5000, "zipf"),
-                                        (64, 1028, 700, "zipf"), (200, 4, 40000, "zipf"), (7, 33, 1, "uniform")])
+                                        (64, 1028, 700, "zipf"), (200, 4, 40000, "zipf"), (7, 33, 1, "uniform"),
+                                        # long lists: the staged first level (rows of 1 KB and more), the register
+                                        # forms of the first level (narrow and odd-width rows), short-chunk levels above
+                                        (300, 1024, 30000, "zipf"), (5000, 256, 25000, "uniform"),
+                                        (90, 33, 25000, "zipf"), (3, 512, 20000, "uniform")])
 def test_addtakegrad_largebatch(lib, k, d, n, kind):
     rng = np.random.default_rng(k + d + n)
     if kind == "uniform":
@@ -391,6 +395,55 @@ def test_sort_by_key(lib, n, ascend):
     wk, wv = orc.sort_by_key(keys.copy(), vals.copy(), ascend)
     gk, gv = lib.sort_by_key(dev(keys), dev(vals), ascend)
     assert np.array_equal(host(gk), wk) and np.array_equal(host(gv), wv)
+
+
+@pytest.mark.parametrize("n,rows,count", [(1, 5, 1), (300, 7, 4), (5000, 40, 64), (70000, 3000, 64), (200000, 50000, 64)])
+def test_frequent_rows_match_the_host_selection(lib, n, rows, count):
+    """msb_frequent_rows_i32 against mshadow_b200.sharding.hot_rows: the same rows, exactly."""
+    from mshadow_b200 import sharding
+    rng = np.random.default_rng(n + count)
+    p = (np.arange(rows) + 1.0) ** -1.1
+    keys = np.sort(rng.choice(rows, size=n, p=p / p.sum()).astype(np.int32))
+    count = min(count, n)
+    out_rows = torch.zeros(count, dtype=torch.int32, device="cuda")
+    out_counts = torch.zeros(count, dtype=torch.int32, device="cuda")
+    lib.frequent_rows(out_rows, out_counts, dev(keys))
+    got_rows, got_counts = host(out_rows), host(out_counts)
+    uniq, counts = np.unique(keys, return_counts=True)
+    order = np.argsort(-counts, kind="stable")[:count]
+    valid = got_counts > 0
+    assert valid.sum() == min(count, uniq.size)
+    assert np.array_equal(got_rows[valid], uniq[order]) and np.array_equal(got_counts[valid], counts[order])
+    assert np.array_equal(np.sort(got_rows[valid]), sharding.hot_rows(keys, count))
+
+
+@pytest.mark.parametrize("n,rows,nhot", [(1, 5, 0), (300, 7, 2), (5000, 40, 8), (70000, 3000, 64), (200001, 50000, 64)])
+@pytest.mark.parametrize("world", [1, 2, 3, 8])
+def test_routing_on_the_device_matches_the_host_routing(lib, n, rows, nhot, world):
+    """msb_route_cyclic_hot_i32 against mshadow_b200.sharding.route_cyclic_with_hot_rows for every
+    rank of the group: the same entries in the same order, exactly."""
+    from mshadow_b200 import sharding
+    rng = np.random.default_rng(n + world)
+    p = (np.arange(rows) + 1.0) ** -1.1
+    idx = rng.choice(rows, size=n, p=p / p.sum()).astype(np.int32)
+    order = np.argsort(idx, kind="stable").astype(np.int32)
+    keys = idx[order]
+    hot = sharding.hot_rows(keys, nhot)
+    dk, do = dev(keys), dev(order)
+    dhot = dev(hot) if hot.size else None
+    for rank in range(world):
+        tk, to, hk, ho = sharding.route_cyclic_with_hot_rows(keys, order, n, rank, world, hot)
+        b, e = sharding.shard_range(n, rank, world)
+        rows_mine = (rows - rank + world - 1) // world
+        ok = torch.full((n,), -7, dtype=torch.int32, device="cuda")
+        oo = torch.full((n,), -7, dtype=torch.int32, device="cuda")
+        totals = torch.zeros(2, dtype=torch.int32, device="cuda")
+        lib.route_cyclic_hot(ok, oo, totals, dk, do, dhot, world, rank, b, e, rows_mine)
+        nt, nh = (int(v) for v in host(totals))
+        assert (nt, nh) == (tk.size, hk.size)
+        assert np.array_equal(host(ok)[:nt], tk) and np.array_equal(host(oo)[:nt], to)
+        assert np.array_equal(host(ok)[nt:nt + nh], hk + rows_mine) and np.array_equal(host(oo)[nt:nt + nh], ho)
+        assert np.all(host(ok)[nt + nh:] == -7)
 
 
 @pytest.mark.parametrize("batch,classes,npos,pad", [
