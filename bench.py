@@ -856,6 +856,87 @@ def make_cyclic_hot_step(torch, lib, dist, peer, keys, order, src, rank, world, 
     return step, shard, info
 
 
+def make_batch_sharded_step(torch, lib, dist, idx_all, src, rank, world, dev):
+    """Embedding backward when the SOURCE rows are spread over the ranks by batch position (rank r
+    holds rows [b, e) of the batch and their indices) and table row t lives on rank t % world.
+    Nothing is prepared outside the step: every call
+      1. builds a composite key (owner, local row) per local entry and sorts the entries by it
+         (this engine's radix sort), numbers the runs of equal keys (msb_run_index_i32),
+      2. sums the local source rows into a compact matrix with one partial row per distinct table
+         row (AddTakeGradLargeBatch with the run numbers as keys); the matrix is ordered by owner,
+      3. hands every owner its partial rows and their local row numbers (two NCCL all-to-alls with
+         uneven splits, after an all-to-all of the counts),
+      4. sorts what it received by row (stable: contributions to a row stay in rank order) and adds
+         it to its shard of the table (AddTakeGradLargeBatch again).
+    Returns (step, shard, info); info["phases"] holds the last call's split into routing (1 and the
+    count exchange), local sum (2), exchange (3) and owner's sum (4), from CUDA events."""
+    from mshadow_b200 import sharding
+    b, e = sharding.shard_range(EMBED_N, rank, world)
+    n_loc = e - b
+    kp = (EMBED_K + world - 1) // world
+    rows_mine = (EMBED_K - rank + world - 1) // world
+    idx = torch.from_numpy(np.ascontiguousarray(idx_all[b:e])).to(dev)
+    src_loc = src[b:e]
+    shard = torch.zeros(rows_mine, EMBED_D, device=dev)
+    iota = torch.arange(n_loc, dtype=torch.int32, device=dev)
+    pos = torch.empty_like(iota)
+    run_of, run_keys = torch.empty_like(iota), torch.empty_like(iota)
+    total = torch.zeros(1, dtype=torch.int32, device=dev)
+    partial = torch.empty(min(n_loc, EMBED_K), EMBED_D, device=dev)
+    edges = torch.arange(world + 1, dtype=torch.int32, device=dev) * kp
+    info = {"entries_on_this_rank": n_loc, "phases": {}}
+    ev = [torch.cuda.Event(enable_timing=True) for _ in range(5)]
+
+    def step():
+        ev[0].record()
+        ck = ((idx % world) * kp + idx // world).to(torch.int32)
+        pos.copy_(iota)
+        lib.sort_by_key(ck, pos)
+        lib.run_index(run_of, run_keys, total, ck)
+        u = int(total.item())
+        keys_u = run_keys[:u]
+        bounds = torch.searchsorted(keys_u, edges, right=False)
+        send = (bounds[1:] - bounds[:-1]).to(torch.int64)
+        recv = torch.empty_like(send)
+        if world > 1:
+            dist.all_to_all_single(recv, send)
+        else:
+            recv.copy_(send)
+        send_l, recv_l = send.tolist(), recv.tolist()
+        ev[1].record()
+        part = partial[:u]
+        part.zero_()
+        if u:
+            lib.addtakegrad_largebatch(part, run_of, pos, src_loc)
+        ev[2].record()
+        got = int(sum(recv_l))
+        local_rows = keys_u % kp                     # the owner's numbering of its rows
+        if world > 1:
+            rows_in = torch.empty(got, EMBED_D, device=dev)
+            keys_in = torch.empty(got, dtype=torch.int32, device=dev)
+            dist.all_to_all_single(rows_in, part, recv_l, send_l)
+            dist.all_to_all_single(keys_in, local_rows.contiguous(), recv_l, send_l)
+        else:
+            rows_in, keys_in = part, local_rows.clone()
+        ev[3].record()
+        if got:
+            order_in = torch.arange(got, dtype=torch.int32, device=dev)
+            lib.sort_by_key(keys_in, order_in)
+            lib.addtakegrad_largebatch(shard, keys_in, order_in, rows_in)
+        ev[4].record()
+        info["distinct_rows_in_the_local_batch"] = u
+        info["partial_rows_received"] = got
+        info["bytes_sent_to_other_ranks"] = int((u - send_l[rank]) * (EMBED_D * 4 + 4))
+
+    def phases():
+        torch.cuda.synchronize()
+        names = ("routing_sort_runs_counts", "local_sum", "exchange_of_partial_rows", "owner_sort_and_sum")
+        return {n: round(ev[i].elapsed_time(ev[i + 1]), 4) for i, n in enumerate(names)}
+
+    info["phases_fn"] = phases
+    return step, shard, info
+
+
 def sharded_block(args, torch, lib, dist, peer, peer_side, rank, world, dev, peak):
     """Every BASELINE tensor split on its leading dimension over the ranks (strong scaling: the total
     work is that of one GPU's config), inputs resident per rank before timing, launches back to
@@ -1014,7 +1095,43 @@ def sharded_block(args, torch, lib, dist, peer, peer_side, rank, world, dev, pea
                                          "numpy_on_the_host": round(info["host_routing_ms"], 2),
                                          "same_lists": info["device_routing_equals_host_routing"]},
            "source_rows": "replicated"})
-    del src, shard
+    del shard
+    # C5 with contiguous row ranges per rank (the plain scheme: rank 0 owns the head of the Zipf distribution)
+    lk, lo, rb, re_ = sharding.route_sorted_indices(keys, order, EMBED_K, rank, world)
+    shard_c = torch.zeros(re_ - rb, EMBED_D, device=dev)
+    dk, do = torch.from_numpy(lk).to(dev), torch.from_numpy(lo).to(dev)
+    ms_c = timed(lambda i: lib.addtakegrad_largebatch(shard_c, dk, do, src) if lk.size else None, 20)
+    most_c = torch.tensor([float(lk.size)], device=dev, dtype=torch.float64)
+    if dist is not None:
+        dist.all_reduce(most_c, op=dist.ReduceOp.MAX)
+    entry("C5_addtakegrad_contiguous_rows", ms_c, EMBED_N * EMBED_D, total_bytes / world, 1,
+          {"max_entries_on_a_rank": int(most_c.item()), "source_rows": "replicated",
+           "routing": "numpy on the host, outside the timed region"})
+    del shard_c, dk, do
+    # C5 again with the placement a data-parallel job has: source rows and indices sharded by batch position
+    step_b, shard_b, info_b = make_batch_sharded_step(torch, lib, dist, idx, src, rank, world, dev)
+    ms_b = timed(lambda i: step_b(), 10)
+    shard_b.zero_()
+    step_b()
+    ph = info_b["phases_fn"]()
+    whole = torch.zeros(EMBED_K, EMBED_D, device=dev)
+    lib.addtakegrad_largebatch(whole, torch.from_numpy(keys).to(dev), torch.from_numpy(order).to(dev), src)
+    want = whole[rank::world]
+    scale = torch.maximum(want.abs(), want.pow(2).mean(dim=1, keepdim=True).sqrt()).clamp_min(1e-30)
+    worst = torch.tensor([float(((shard_b - want).abs() / scale).max().item())], device=dev, dtype=torch.float64)
+    sent = torch.tensor([float(info_b["bytes_sent_to_other_ranks"])], device=dev, dtype=torch.float64)
+    if dist is not None:
+        dist.all_reduce(worst, op=dist.ReduceOp.MAX)
+        dist.all_reduce(sent, op=dist.ReduceOp.MAX)
+    del whole, want, scale
+    entry("C5_addtakegrad_source_sharded_by_batch", ms_b, EMBED_N * EMBED_D, total_bytes / world, 1,
+          {"placement": "source rows and indices sharded by batch position, table rows cyclic; sort, routing and "
+                        "exchange inside the timed step",
+           "exchange": "NCCL all-to-all of partial rows (uneven splits)" if world > 1 else "none",
+           "phases_ms_on_rank_0": ph, "distinct_rows_in_rank_0s_batch": info_b["distinct_rows_in_the_local_batch"],
+           "max_bytes_sent_by_a_rank": int(sent.item()),
+           "max_rel_diff_vs_unsharded_call": float(worst.item()), "within_1e-5": bool(worst.item() <= 1e-5)})
+    del src, shard_b
     torch.cuda.empty_cache()
     return out
 
@@ -1476,9 +1593,9 @@ def main():
     per_rank = np.array(gather_floats(torch, dist, dev, [seconds, t_high, t_low, t_xchg]))
     seconds = float(per_rank[:, 0].max())
     # One NVML query takes milliseconds, so a short timed region may hold no clock sample at all:
-    # the same steps carry on, untimed, for a fifth of a second (the same number on every rank),
+    # the same steps carry on, untimed, for a twentieth of a second (the same number on every rank),
     # and the clock record says which samples fall where.
-    extra = int(min(5000, max(0, 0.2 / max(1e-6, seconds / k) - k)))
+    extra = int(min(5000, max(0, 0.05 / max(1e-6, seconds / k) - k)))
     sampler.tail_window[0] = time.perf_counter()
     for s in range(extra):
         reductions(args.warmup + k + s)

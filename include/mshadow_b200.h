@@ -243,6 +243,13 @@ int msb_sort_by_key_i32(int32_t *keys, int32_t *values, int64_t n, int ascend,
    the reference has no multi-GPU form of it. */
 int msb_frequent_rows_i32(int32_t *rows_out, int32_t *counts_out, const int32_t *sorted,
                           int64_t n, int64_t count, msb_stream_t stream);
+/* Numbers the runs of equal keys of an ascending list: run_of[i] = 0, 1, ... for every entry,
+   run_keys[j] = the key of run j (room for n entries), total[0] (a device word) = number of
+   runs.  msb_addtakegrad_largebatch_f32_i32 with run_of in place of `sorted` sums into a compact
+   matrix of one row per distinct key: what a GPU hands to the owners of the table rows when
+   the source rows are spread over the GPUs by batch position. */
+int msb_run_index_i32(int32_t *run_of, int32_t *run_keys, uint32_t *total, const int32_t *sorted,
+                      int64_t n, msb_stream_t stream);
 /* This GPU's part of AddTakeGradLargeBatch's (sorted, index) lists when table row r lives on
    GPU r % world as local row r / world and the rows listed in `hot` (ascending, <= 1024) are
    summed by every GPU over the source rows [src_begin, src_end) it holds.  Writes, in list order,

@@ -74,6 +74,7 @@ _SIGNATURES = {
     "msb_sort_by_key_i32": [vp, vp, i64, cint, vp],
     "msb_vectorized_sort_f32_i32": [vp, vp, i64, vp],
     "msb_frequent_rows_i32": [vp, vp, vp, i64, i64, vp],
+    "msb_run_index_i32": [vp, vp, vp, vp, i64, vp],
     "msb_route_cyclic_hot_i32": [vp, vp, vp, vp, vp, i64, vp, i64, cint, cint, i64, i64, i64, vp],
     "msb_index_fill_f32_i32": [vp, vp, vp, i64, i64, i64, vp],
     "msb_remap_shape": [cint, i64, i64, i64, i64, i64, i64, vp],
@@ -291,6 +292,10 @@ class Library:
         self.call("msb_frequent_rows_i32", _ptr(rows_out), _ptr(counts_out), _ptr(sorted_), sorted_.shape[0],
                   rows_out.shape[0], stream)
         return rows_out, counts_out
+
+    def run_index(self, run_of, run_keys, total, sorted_, stream=None):
+        self.call("msb_run_index_i32", _ptr(run_of), _ptr(run_keys), _ptr(total), _ptr(sorted_), sorted_.shape[0], stream)
+        return run_of, run_keys, total
 
     def route_cyclic_hot(self, keys_out, rows_out, totals, sorted_, index, hot, world, rank, src_begin, src_end,
                          hot_base, stream=None):

@@ -629,6 +629,17 @@ int msb_frequent_rows_i32(int32_t *rows_out, int32_t *counts_out, const int32_t 
   MSB_GUARD_END
 }
 
+int msb_run_index_i32(int32_t *run_of, int32_t *run_keys, uint32_t *total, const int32_t *sorted, int64_t n,
+                      msb_stream_t stream) {
+  MSB_REQUIRE(FitsIndex(n), MSB_ERR_SHAPE, "extent out of range");
+  MSB_REQUIRE(total, MSB_ERR_ARGUMENT, "null pointer");
+  MSB_REQUIRE(n == 0 || (run_of && run_keys && sorted), MSB_ERR_ARGUMENT, "null pointer");
+  MSB_GUARD_BEGIN
+  BorrowedStream st(stream);
+  mshadow::cuda::RunIndexLaunch(run_of, run_keys, total, sorted, n, Stream<gpu>::GetStream(st.get()));
+  MSB_GUARD_END
+}
+
 int msb_route_cyclic_hot_i32(int32_t *keys_out, int32_t *rows_out, uint32_t *totals, const int32_t *sorted,
                              const int32_t *index, int64_t n, const int32_t *hot, int64_t hot_count, int world,
                              int rank, int64_t src_begin, int64_t src_end, int64_t hot_base, msb_stream_t stream) {

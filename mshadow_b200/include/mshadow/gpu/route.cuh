@@ -18,6 +18,12 @@
  *                        and every hot key is larger than every tail key when hot_base is the
  *                        number of local rows, so the output is again one sorted list.
  *
+ *   RunHeadCountKernel / RunHeadScanKernel / RunIndexKernel
+ *                        number the runs of equal keys (run_of[i], run_keys[j]): the key list of
+ *                        a segmented sum into a compact matrix with one row per distinct key, which
+ *                        is what a GPU sends to the owners when the SOURCE rows are spread over
+ *                        the GPUs by batch position.
+ *
  * The selection is stable, so each table row keeps its accumulation order.  All arithmetic is on
  * 32-bit integers; results are exact.
  */
@@ -203,6 +209,78 @@ RouteScatterKernel(int32_t *out_keys, int32_t *out_rows, const uint32_t *bases, 
   }
 }
 
+/*! \brief counts[tile] = entries of the tile that start a run of equal keys */
+template <int kDummy>
+__global__ void __launch_bounds__(routedetail::kThreads)
+RunHeadCountKernel(uint32_t *counts, const int32_t *keys, uint32_t n) {
+  using namespace routedetail;
+  __shared__ uint32_t s_warp[kThreads / 32];
+  const uint32_t first = blockIdx.x * kTile + threadIdx.x * kItems;
+  uint32_t mine = 0;
+#pragma unroll
+  for (int u = 0; u < kItems; ++u) {
+    const uint32_t e = first + u;
+    if (e < n && (e == 0 || keys[e - 1] != keys[e])) ++mine;
+  }
+  uint32_t total;
+  CtaExclusiveScan(mine, s_warp, &total);
+  if (threadIdx.x == 0) counts[blockIdx.x] = total;
+}
+
+/*! \brief in-place exclusive scan of counts[0 .. tiles); total[0] = sum */
+template <int kDummy>
+__global__ void __launch_bounds__(routedetail::kThreads)
+RunHeadScanKernel(uint32_t *counts, uint32_t tiles, uint32_t *total_out) {
+  using namespace routedetail;
+  __shared__ uint32_t s_warp[kThreads / 32];
+  uint32_t running = 0;
+  for (uint32_t t0 = 0; t0 < tiles; t0 += kThreads) {
+    const uint32_t t = t0 + threadIdx.x;
+    const uint32_t v = t < tiles ? counts[t] : 0u;
+    uint32_t total;
+    const uint32_t ex = CtaExclusiveScan(v, s_warp, &total);
+    if (t < tiles) counts[t] = running + ex;
+    running += total;
+  }
+  if (threadIdx.x == 0) total_out[0] = running;
+}
+
+/*! \brief run_of[i] = number of the run entry i belongs to (0, 1, ...); run_keys[j] = key of run j */
+template <int kDummy>
+__global__ void __launch_bounds__(routedetail::kThreads)
+RunIndexKernel(int32_t *run_of, int32_t *run_keys, const uint32_t *bases, const int32_t *keys, uint32_t n) {
+  using namespace routedetail;
+  __shared__ uint32_t s_warp[kThreads / 32];
+  const uint32_t first = blockIdx.x * kTile + threadIdx.x * kItems;
+  int32_t k[kItems];
+  bool head[kItems];
+  uint32_t mine = 0;
+#pragma unroll
+  for (int u = 0; u < kItems; ++u) {
+    const uint32_t e = first + u;
+    head[u] = false;
+    if (e < n) {
+      k[u] = keys[e];
+      head[u] = e == 0 || keys[e - 1] != k[u];
+      mine += head[u] ? 1u : 0u;
+    }
+  }
+  uint32_t total;
+  // runs that start before this thread's first entry, minus one: the run its first entry continues
+  uint32_t at = bases[blockIdx.x] + CtaExclusiveScan(mine, s_warp, &total);
+#pragma unroll
+  for (int u = 0; u < kItems; ++u) {
+    const uint32_t e = first + u;
+    if (e < n) {
+      if (head[u]) {
+        run_keys[at] = k[u];
+        ++at;
+      }
+      run_of[e] = static_cast<int32_t>(at - 1);
+    }
+  }
+}
+
 namespace routedetail {
 inline size_t Align256(size_t b) { return (b + 255) / 256 * 256; }
 inline uint32_t Tiles(int64_t n) { return static_cast<uint32_t>((n + kTile - 1) / kTile); }
@@ -236,6 +314,31 @@ inline void RouteCyclicHotLaunch(int32_t *out_keys, int32_t *out_rows, uint32_t 
   MSHADOW_CUDA_POST_KERNEL_CHECK(RouteScanKernel);
   RouteScatterKernel<0><<<tiles, kThreads, 0, stream>>>(out_keys, out_rows, counts, totals, keys, rows, un, hot, g);
   MSHADOW_CUDA_POST_KERNEL_CHECK(RouteScatterKernel);
+}
+
+/*!
+ * \brief numbers the runs of equal keys of an ascending list: run_of[i] in 0 .. runs-1 for every
+ *  entry, run_keys[j] the key of run j (room for n), total[0] (device word) the number of runs.
+ *  With run_of as the key list, a segmented sum lands in a compact matrix of one row per
+ *  distinct key instead of a table of all possible keys.
+ */
+inline void RunIndexLaunch(int32_t *run_of, int32_t *run_keys, uint32_t *total, const int32_t *keys, int64_t n,
+                           cudaStream_t stream) {
+  using namespace routedetail;
+  CHECK_LT(n, (int64_t(1) << 31));
+  if (n == 0) {
+    MSHADOW_CUDA_CALL(cudaMemsetAsync(total, 0, sizeof(uint32_t), stream));
+    return;
+  }
+  const uint32_t tiles = Tiles(n);
+  uint32_t *counts = static_cast<uint32_t *>(gpu_rt::Scratch::Get(stream, RouteScratchBytes(n)));
+  const uint32_t un = static_cast<uint32_t>(n);
+  RunHeadCountKernel<0><<<tiles, kThreads, 0, stream>>>(counts, keys, un);
+  MSHADOW_CUDA_POST_KERNEL_CHECK(RunHeadCountKernel);
+  RunHeadScanKernel<0><<<1, kThreads, 0, stream>>>(counts, tiles, total);
+  MSHADOW_CUDA_POST_KERNEL_CHECK(RunHeadScanKernel);
+  RunIndexKernel<0><<<tiles, kThreads, 0, stream>>>(run_of, run_keys, counts, keys, un);
+  MSHADOW_CUDA_POST_KERNEL_CHECK(RunIndexKernel);
 }
 
 /*! \brief lens[i] = run length at run heads of the sorted list, 0 elsewhere; rows[i] = keys[i] */

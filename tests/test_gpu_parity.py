@@ -417,6 +417,21 @@ def test_frequent_rows_match_the_host_selection(lib, n, rows, count):
     assert np.array_equal(np.sort(got_rows[valid]), sharding.hot_rows(keys, count))
 
 
+@pytest.mark.parametrize("n,rows", [(1, 5), (300, 7), (2048, 2048), (2049, 3), (70000, 3000), (200001, 50000)])
+def test_run_numbering_of_a_sorted_list(lib, n, rows):
+    """msb_run_index_i32 against numpy: run number of every entry, key of every run, number of runs."""
+    rng = np.random.default_rng(n + rows)
+    keys = np.sort(rng.integers(0, rows, n).astype(np.int32))
+    run_of = torch.full((n,), -7, dtype=torch.int32, device="cuda")
+    run_keys = torch.full((n,), -7, dtype=torch.int32, device="cuda")
+    total = torch.zeros(1, dtype=torch.int32, device="cuda")
+    lib.run_index(run_of, run_keys, total, dev(keys))
+    uniq, inverse = np.unique(keys, return_inverse=True)
+    assert int(host(total)[0]) == uniq.size
+    assert np.array_equal(host(run_of), inverse.astype(np.int32))
+    assert np.array_equal(host(run_keys)[:uniq.size], uniq) and np.all(host(run_keys)[uniq.size:] == -7)
+
+
 @pytest.mark.parametrize("n,rows,nhot", [(1, 5, 0), (300, 7, 2), (5000, 40, 8), (70000, 3000, 64), (200001, 50000, 64)])
 @pytest.mark.parametrize("world", [1, 2, 3, 8])
 def test_routing_on_the_device_matches_the_host_routing(lib, n, rows, nhot, world):
