@@ -846,7 +846,7 @@ def make_cyclic_hot_step(torch, lib, dist, peer, keys, order, src, rank, world, 
             if peer is not None:
                 peer.push(partial, 2, stream=stream)
                 peer.pull_req(partial, 2, stream=stream)
-            else:
+            elif dist is not None:
                 dist.all_reduce(partial)
         if mine.size:
             lib.addtakegrad_largebatch(shard, mine_rows, mine_pos, partial, stream=stream)
@@ -935,6 +935,101 @@ def make_batch_sharded_step(torch, lib, dist, idx_all, src, rank, world, dev):
 
     info["phases_fn"] = phases
     return step, shard, info
+
+
+def make_batch_sharded_peer_step(torch, lib, dist, idx_all, src, rank, world, local_rank, dev):
+    """The placement of make_batch_sharded_step with the exchange done by the segmented-sum kernel
+    itself: the sum of every run is stored straight into its row of a receive block in the OWNER's
+    memory (16-byte stores over NVLink into a window mapped with CUDA IPC), the owner's row numbers
+    beside it, and the counts travel as a small key of the peer-store exchange pushed behind those
+    kernels -- whoever has pulled that key finds the rows in place.  No library collective, no
+    send-side host synchronisation; the owner reads its counts back once per step to size its sum.
+    Receive blocks are double-buffered: a rank starts writing step i + 1 only after it has pulled
+    step i's counts, which every owner pushed after it had finished reading step i - 1.
+    Returns (step, shard, info, model)."""
+    from mshadow_b200 import ps, sharding
+    b, e = sharding.shard_range(EMBED_N, rank, world)
+    n_loc = e - b
+    kp = (EMBED_K + world - 1) // world
+    rows_mine = (EMBED_K - rank + world - 1) // world
+    slots = world * kp                                  # rows a rank can receive per step: kp from every sender
+    row_bytes, key_bytes = 2 * slots * EMBED_D * 4, 2 * slots * 4
+    m = ps.PeerModel(rank=rank, world=world, device=local_rank, depth=4, wait_limit_ms=20000,
+                     window_bytes=row_bytes + key_bytes + (1 << 20))
+    if world > 1:
+        handles = [None] * world
+        dist.all_gather_object(handles, m.export_handle())
+        m.connect(handles)
+    m.init_key(0, (world * world,))
+    off_rows, off_keys = m.reserve(row_bytes), m.reserve(key_bytes)
+    my_rows, my_keys = m.window(rank, off_rows), m.window(rank, off_keys)
+
+    def blocks(parity):
+        """Where this rank writes in every owner's window: sender `rank`'s kp rows of the given parity."""
+        at = (parity * world + rank) * kp
+        return ([m.window(q, off_rows) + at * EMBED_D * 4 for q in range(world)],
+                [m.window(q, off_keys) + at * 4 for q in range(world)])
+
+    targets = [blocks(0), blocks(1)]
+    idx = torch.from_numpy(np.ascontiguousarray(idx_all[b:e])).to(dev)
+    src_loc = src[b:e]
+    shard = torch.zeros(rows_mine, EMBED_D, device=dev)
+    iota = torch.arange(n_loc, dtype=torch.int32, device=dev)
+    pos, run_of, run_keys = torch.empty_like(iota), torch.empty_like(iota), torch.empty_like(iota)
+    total = torch.zeros(1, dtype=torch.int32, device=dev)
+    first = torch.zeros(world + 1, dtype=torch.int32, device=dev)
+    mine = torch.zeros(world * world, device=dev)
+    counts = torch.zeros(world * world, device=dev)
+    keys_all = torch.empty(slots, dtype=torch.int32, device=dev)
+    lane = torch.arange(kp, dtype=torch.int32, device=dev)
+    info = {"entries_on_this_rank": n_loc, "window_bytes": row_bytes + key_bytes + (1 << 20)}
+    ev = [torch.cuda.Event(enable_timing=True) for _ in range(4)]
+    state = {"step": 0}
+    from mshadow_b200 import capi as _capi
+
+    def step():
+        parity = state["step"] & 1
+        state["step"] += 1
+        row_blocks, key_blocks = targets[parity]
+        ev[0].record()
+        ck = ((idx % world) * kp + idx // world).to(torch.int32)
+        pos.copy_(iota)
+        lib.sort_by_key(ck, pos)
+        lib.run_index(run_of, run_keys, total, ck)
+        lib.run_bounds(first, run_keys, total, world, kp)
+        ev[1].record()
+        # sums of this rank's source rows, stored into the owners' memory; then the owners' row numbers
+        lib.take_sum_to_owners(row_blocks, first, run_of, pos, src_loc, world)
+        lib.run_keys_to_owners(key_blocks, first, run_keys, world, kp)
+        mine.zero_()
+        mine[rank * world:(rank + 1) * world] = (first[1:] - first[:-1]).float()
+        m.push(mine, 0)                      # behind the storing kernels on this stream: the completion signal
+        m.pull_req(counts, 0)
+        ev[2].record()
+        m.pull_wait(0)
+        got = counts.view(world, world)[:, rank].to(torch.int64).tolist()      # rows from every sender
+        lib.copy_2d(keys_all, slots, my_keys + parity * slots * 4, slots, 1, slots, _capi.D2D)
+        parts_k, parts_o = [], []
+        for r, c in enumerate(got):
+            if c:
+                parts_k.append(keys_all[r * kp:r * kp + c])
+                parts_o.append(lane[:c] + (parity * slots + r * kp))
+        if parts_k:
+            keys_in, order_in = torch.cat(parts_k), torch.cat(parts_o)
+            lib.sort_by_key(keys_in, order_in)
+            lib.call("msb_addtakegrad_largebatch_f32_i32", shard.data_ptr(), keys_in.data_ptr(), order_in.data_ptr(),
+                     my_rows, rows_mine, EMBED_D, keys_in.shape[0], None)
+        ev[3].record()
+        info["partial_rows_received"] = int(sum(got))
+
+    def phases():
+        torch.cuda.synchronize()
+        names = ("routing_sort_runs_bounds", "local_sum_stored_into_the_owners_and_signal", "owner_wait_sort_and_sum")
+        return {n: round(ev[i].elapsed_time(ev[i + 1]), 4) for i, n in enumerate(names)}
+
+    info["phases_fn"] = phases
+    info["first"] = first
+    return step, shard, info, m
 
 
 def sharded_block(args, torch, lib, dist, peer, peer_side, rank, world, dev, peak):
@@ -1131,7 +1226,35 @@ def sharded_block(args, torch, lib, dist, peer, peer_side, rank, world, dev, pea
            "phases_ms_on_rank_0": ph, "distinct_rows_in_rank_0s_batch": info_b["distinct_rows_in_the_local_batch"],
            "max_bytes_sent_by_a_rank": int(sent.item()),
            "max_rel_diff_vs_unsharded_call": float(worst.item()), "within_1e-5": bool(worst.item() <= 1e-5)})
-    del src, shard_b
+    del shard_b
+    # the same placement with the segmented-sum kernel storing its sums straight into the owners' memory
+    local_rank = dev.index if dev.index is not None else 0
+    step_p, shard_p, info_p, model_p = make_batch_sharded_peer_step(torch, lib, dist, idx, src, rank, world, local_rank, dev)
+    ms_p = timed(lambda i: step_p(), 10)
+    shard_p.zero_()
+    step_p()
+    ph = info_p["phases_fn"]()
+    f = info_p["first"].cpu().numpy()
+    stored = torch.tensor([float((f[world] - (f[rank + 1] - f[rank])) * (EMBED_D * 4 + 4))], device=dev, dtype=torch.float64)
+    whole = torch.zeros(EMBED_K, EMBED_D, device=dev)
+    lib.addtakegrad_largebatch(whole, torch.from_numpy(keys).to(dev), torch.from_numpy(order).to(dev), src)
+    want = whole[rank::world]
+    scale = torch.maximum(want.abs(), want.pow(2).mean(dim=1, keepdim=True).sqrt()).clamp_min(1e-30)
+    worst = torch.tensor([float(((shard_p - want).abs() / scale).max().item())], device=dev, dtype=torch.float64)
+    if dist is not None:
+        dist.all_reduce(worst, op=dist.ReduceOp.MAX)
+        dist.all_reduce(stored, op=dist.ReduceOp.MAX)
+        dist.barrier()
+    model_p.close()
+    del whole, want, scale
+    entry("C5_addtakegrad_source_sharded_by_batch_peer_stores", ms_p, EMBED_N * EMBED_D, total_bytes / world, 1,
+          {"placement": "as C5_addtakegrad_source_sharded_by_batch",
+           "exchange": "the segmented-sum kernel stores every run's sum into its owner's window over NVLink; counts "
+                       "through the peer-store exchange; no library collective" if world > 1 else "none (own window)",
+           "phases_ms_on_rank_0": ph, "max_bytes_stored_into_other_ranks": int(stored.item()),
+           "window_bytes_per_rank": info_p["window_bytes"],
+           "max_rel_diff_vs_unsharded_call": float(worst.item()), "within_1e-5": bool(worst.item() <= 1e-5)})
+    del src, shard_p
     torch.cuda.empty_cache()
     return out
 
@@ -1391,6 +1514,16 @@ def embed_sharded_arm(args, torch, lib, dist, peer, rank, world, dev):
             dist.all_reduce(s)
         return float(s.item())
 
+    if args.emulate_rank_of > 1 and world == 1:
+        # rank 0's step of a group of `emulate_rank_of` ranks, alone on this GPU and without the exchange:
+        # what the kernels of one shard cost (for launch lists; a single-rank command can be profiled)
+        w = args.emulate_rank_of
+        step, shard, info = make_cyclic_hot_step(torch, lib, None, None, keys, order, src, 0, w, dev)
+        ms = timed(step)
+        print(json.dumps({"workload": "embed_sharded", "emulated": "rank 0 of %d, no exchange" % w, "ms_per_step": ms,
+                          "entries_on_this_rank": info["entries_on_this_rank"], "steps": steps, "warmup": warm}),
+              file=OUT, flush=True)
+        return
     out = {}
     t0 = time.perf_counter()
     lk, lo, rb, re = sharding.route_sorted_indices(keys, order, EMBED_K, rank, world)
@@ -1455,6 +1588,9 @@ def main():
     ap.add_argument("--trace-launches", action="store_true",
                     help="with --only: time --steps launches one by one and report them in bins of 20 beside the "
                          "sampled SM clock and throttle reasons")
+    ap.add_argument("--emulate-rank-of", type=int, default=0,
+                    help="with --workload embed_sharded on one GPU: run rank 0's step of a group of this many ranks, "
+                         "without the exchange")
     ap.add_argument("--workload", default="reductions", choices=["reductions", "embed_sharded"],
                     help="reductions: the headline workload; embed_sharded: AddTakeGradLargeBatch with the table "
                          "sharded by rows over the ranks (strong scaling, see embed_sharded_arm)")

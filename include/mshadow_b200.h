@@ -250,6 +250,29 @@ int msb_frequent_rows_i32(int32_t *rows_out, int32_t *counts_out, const int32_t 
    the source rows are spread over the GPUs by batch position. */
 int msb_run_index_i32(int32_t *run_of, int32_t *run_keys, uint32_t *total, const int32_t *sorted,
                       int64_t n, msb_stream_t stream);
+/* The three calls below serve AddTakeGradLargeBatch when the SOURCE rows are spread over the GPUs
+   by batch position and table row t lives on GPU t % world as local row t / world.  A GPU sorts
+   its entries by the key (t % world) * per_owner + t / world, numbers the runs
+   (msb_run_index_i32), and then:
+   msb_run_bounds_i32: first[q] (device, world + 1 entries) = number of runs whose key is below
+     q * per_owner: the runs of owner q are first[q] .. first[q + 1] - 1.
+   msb_take_sum_to_owners_f32_i32: the sum of the source rows of run j is STORED into row
+     j - first[q] of row_blocks[q] (host array of `world` device addresses, 16-byte aligned, row
+     pitch d; an address may belong to another GPU's memory mapped into this process, see
+     msb_ps_peer_window: the kernel only stores there, 16 bytes at a time, each row once).
+   msb_run_keys_to_owners_i32: key_blocks[q][j - first[q]] = run key - q * per_owner, the owner's
+     own row number, beside the rows.
+   The owner then sorts what it received by row and adds it with
+   msb_addtakegrad_largebatch_f32_i32, its receive block as `src`.  The reference has no
+   multi-GPU form of this operator (mshadow/tensor_gpu-inl.h:223-229 serves one device). */
+int msb_run_bounds_i32(int32_t *first, const int32_t *run_keys, const uint32_t *total, int world,
+                       int64_t per_owner, msb_stream_t stream);
+int msb_run_keys_to_owners_i32(int32_t *const *key_blocks, const int32_t *first,
+                               const int32_t *run_keys, int64_t n, int world, int64_t per_owner,
+                               msb_stream_t stream);
+int msb_take_sum_to_owners_f32_i32(float *const *row_blocks, const int32_t *first,
+                                   const int32_t *run_of, const int32_t *index, const float *src,
+                                   int64_t d, int64_t nidx, int world, msb_stream_t stream);
 /* This GPU's part of AddTakeGradLargeBatch's (sorted, index) lists when table row r lives on
    GPU r % world as local row r / world and the rows listed in `hot` (ascending, <= 1024) are
    summed by every GPU over the source rows [src_begin, src_end) it holds.  Writes, in list order,

@@ -64,6 +64,17 @@ int msb_ps_peer_create(int rank, int world, int device, int64_t window_bytes, in
 int msb_ps_peer_handle(msb_ps_t model, char *hex, int64_t capacity);
 int msb_ps_peer_connect(msb_ps_t model, const char *all_handles_hex);
 int msb_ps_peer_next_sink(msb_ps_t model, int key, int64_t offset, int64_t count, msb_peer_sink_t *out);
+/* Regions of the windows for the caller's own kernels (bulk data that a kernel stores straight
+   into another GPU's memory, e.g. msb_addtakegrad_largebatch_store_f32_i32 with a destination in
+   the owner's window).  msb_ps_peer_reserve sets `bytes` of every rank's window aside and returns
+   their offset; all ranks make the same calls in the same order.  msb_ps_peer_window gives the
+   address, in this process, of byte `offset` of rank `rank`'s window (after connect); only plain
+   loads and stores of the caller's own kernels may use an address of another rank.  A key pushed
+   after the writing kernels, on the same stream, is the completion signal: whoever has pulled
+   that step finds the data in place.  The window (msb_ps_peer_create's window_bytes) must be
+   sized for keys and regions together. */
+int msb_ps_peer_reserve(msb_ps_t model, int64_t bytes, int64_t *offset);
+int msb_ps_peer_window(msb_ps_t model, int rank, int64_t offset, void **ptr);
 
 /* ISharedModel::InitKey(Shape2(rows, cols), key, device) */
 int msb_ps_init_key(msb_ps_t model, int key, int64_t rows, int64_t cols);

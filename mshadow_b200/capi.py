@@ -75,6 +75,9 @@ _SIGNATURES = {
     "msb_vectorized_sort_f32_i32": [vp, vp, i64, vp],
     "msb_frequent_rows_i32": [vp, vp, vp, i64, i64, vp],
     "msb_run_index_i32": [vp, vp, vp, vp, i64, vp],
+    "msb_run_bounds_i32": [vp, vp, vp, cint, i64, vp],
+    "msb_run_keys_to_owners_i32": [vp, vp, vp, i64, cint, i64, vp],
+    "msb_take_sum_to_owners_f32_i32": [vp, vp, vp, vp, vp, i64, i64, cint, vp],
     "msb_route_cyclic_hot_i32": [vp, vp, vp, vp, vp, i64, vp, i64, cint, cint, i64, i64, i64, vp],
     "msb_index_fill_f32_i32": [vp, vp, vp, i64, i64, i64, vp],
     "msb_remap_shape": [cint, i64, i64, i64, i64, i64, i64, vp],
@@ -296,6 +299,25 @@ class Library:
     def run_index(self, run_of, run_keys, total, sorted_, stream=None):
         self.call("msb_run_index_i32", _ptr(run_of), _ptr(run_keys), _ptr(total), _ptr(sorted_), sorted_.shape[0], stream)
         return run_of, run_keys, total
+
+    def run_bounds(self, first, run_keys, total, world, per_owner, stream=None):
+        self.call("msb_run_bounds_i32", _ptr(first), _ptr(run_keys), _ptr(total), world, per_owner, stream)
+        return first
+
+    @staticmethod
+    def _address_table(addresses):
+        table = (C.c_void_p * len(addresses))(*[int(a) for a in addresses])
+        return table
+
+    def run_keys_to_owners(self, key_blocks, first, run_keys, world, per_owner, stream=None):
+        """key_blocks: one device address per owner (ints; other GPUs' mapped memory allowed)."""
+        self.call("msb_run_keys_to_owners_i32", self._address_table(key_blocks), _ptr(first), _ptr(run_keys),
+                  run_keys.shape[0], world, per_owner, stream)
+
+    def take_sum_to_owners(self, row_blocks, first, run_of, index, src, world, stream=None):
+        """row_blocks: one device address per owner (ints; other GPUs' mapped memory allowed)."""
+        self.call("msb_take_sum_to_owners_f32_i32", self._address_table(row_blocks), _ptr(first), _ptr(run_of),
+                  _ptr(index), _ptr(src), src.shape[1], index.shape[0], world, stream)
 
     def route_cyclic_hot(self, keys_out, rows_out, totals, sorted_, index, hot, world, rank, src_begin, src_end,
                          hot_base, stream=None):

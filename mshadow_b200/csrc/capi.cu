@@ -640,6 +640,56 @@ int msb_run_index_i32(int32_t *run_of, int32_t *run_keys, uint32_t *total, const
   MSB_GUARD_END
 }
 
+int msb_run_bounds_i32(int32_t *first, const int32_t *run_keys, const uint32_t *total, int world, int64_t per_owner,
+                       msb_stream_t stream) {
+  MSB_REQUIRE(world >= 1 && world <= mshadow::cuda::routedetail::kMaxOwners, MSB_ERR_ARGUMENT, "1 to 16 owners");
+  MSB_REQUIRE(FitsIndex(per_owner) && per_owner >= 1 && FitsIndex(per_owner * world), MSB_ERR_SHAPE, "extent out of range");
+  MSB_REQUIRE(first && run_keys && total, MSB_ERR_ARGUMENT, "null pointer");
+  MSB_GUARD_BEGIN
+  BorrowedStream st(stream);
+  mshadow::cuda::RunBoundsLaunch(first, run_keys, total, world, static_cast<int32_t>(per_owner),
+                                 Stream<gpu>::GetStream(st.get()));
+  MSB_GUARD_END
+}
+
+int msb_run_keys_to_owners_i32(int32_t *const *key_blocks, const int32_t *first, const int32_t *run_keys, int64_t n,
+                               int world, int64_t per_owner, msb_stream_t stream) {
+  MSB_REQUIRE(world >= 1 && world <= mshadow::cuda::routedetail::kMaxOwners, MSB_ERR_ARGUMENT, "1 to 16 owners");
+  MSB_REQUIRE(FitsIndex(n) && FitsIndex(per_owner) && per_owner >= 1, MSB_ERR_SHAPE, "extent out of range");
+  MSB_REQUIRE(key_blocks && first && run_keys, MSB_ERR_ARGUMENT, "null pointer");
+  mshadow::cuda::routedetail::OwnerBlocks<int32_t> to;
+  for (int q = 0; q < mshadow::cuda::routedetail::kMaxOwners; ++q) to.base[q] = q < world ? key_blocks[q] : nullptr;
+  for (int q = 0; q < world; ++q) MSB_REQUIRE(to.base[q] != nullptr, MSB_ERR_ARGUMENT, "null block");
+  to.first = first;
+  to.world = world;
+  MSB_GUARD_BEGIN
+  BorrowedStream st(stream);
+  mshadow::cuda::RunKeysToOwnersLaunch(to, run_keys, n, static_cast<int32_t>(per_owner), Stream<gpu>::GetStream(st.get()));
+  MSB_GUARD_END
+}
+
+int msb_take_sum_to_owners_f32_i32(float *const *row_blocks, const int32_t *first, const int32_t *run_of,
+                                   const int32_t *index, const float *src, int64_t d, int64_t nidx, int world,
+                                   msb_stream_t stream) {
+  MSB_REQUIRE(world >= 1 && world <= mshadow::cuda::routedetail::kMaxOwners, MSB_ERR_ARGUMENT, "1 to 16 owners");
+  MSB_REQUIRE(FitsIndex(d) && FitsIndex(nidx), MSB_ERR_SHAPE, "extent out of range");
+  if (nidx == 0 || d == 0) return MSB_OK;
+  MSB_REQUIRE(row_blocks && first && run_of && index && src, MSB_ERR_ARGUMENT, "null pointer");
+  mshadow::cuda::routedetail::RowRoute route;
+  for (int q = 0; q < mshadow::cuda::routedetail::kMaxOwners; ++q) route.base[q] = q < world ? row_blocks[q] : nullptr;
+  for (int q = 0; q < world; ++q) {
+    MSB_REQUIRE(route.base[q] != nullptr, MSB_ERR_ARGUMENT, "null block");
+    MSB_REQUIRE(reinterpret_cast<uintptr_t>(route.base[q]) % 16 == 0, MSB_ERR_ARGUMENT, "blocks must be 16-byte aligned");
+  }
+  route.first = first;
+  route.world = world;
+  MSB_GUARD_BEGIN
+  BorrowedStream st(stream);
+  mshadow::cuda::AddTakeGradLargeBatchLaunch(nullptr, d, run_of, index, src, d, nidx, d, Stream<gpu>::GetStream(st.get()),
+                                             true, &route);
+  MSB_GUARD_END
+}
+
 int msb_route_cyclic_hot_i32(int32_t *keys_out, int32_t *rows_out, uint32_t *totals, const int32_t *sorted,
                              const int32_t *index, int64_t n, const int32_t *hot, int64_t hot_count, int world,
                              int rank, int64_t src_begin, int64_t src_end, int64_t hot_base, msb_stream_t stream) {

@@ -157,6 +157,24 @@ int msb_ps_peer_next_sink(msb_ps_t model, int key, int64_t offset, int64_t count
   PS_END
 }
 
+int msb_ps_peer_reserve(msb_ps_t model, int64_t bytes, int64_t *offset) {
+  PeerImpl *m = dynamic_cast<PeerImpl *>(static_cast<Model *>(model));
+  if (m == NULL) return FailPs("msb_ps_peer_reserve: not a peer model");
+  if (offset == NULL || bytes < 0) return FailPs("msb_ps_peer_reserve: bad argument");
+  PS_BEGIN
+  *offset = static_cast<int64_t>(m->ReserveRaw(static_cast<size_t>(bytes)));
+  PS_END
+}
+
+int msb_ps_peer_window(msb_ps_t model, int rank, int64_t offset, void **ptr) {
+  PeerImpl *m = dynamic_cast<PeerImpl *>(static_cast<Model *>(model));
+  if (m == NULL) return FailPs("msb_ps_peer_window: not a peer model");
+  if (ptr == NULL || offset < 0) return FailPs("msb_ps_peer_window: bad argument");
+  PS_BEGIN
+  *ptr = m->WindowOf(rank, static_cast<size_t>(offset));
+  PS_END
+}
+
 int msb_ps_destroy(msb_ps_t model) {
   PS_BEGIN
   delete static_cast<Model *>(model);

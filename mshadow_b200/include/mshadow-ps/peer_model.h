@@ -349,8 +349,32 @@ class PeerModel : public ISharedModel<gpu, DType> {
 #endif
   }
 
-  /*! \brief bytes of the window that InitKey has handed out so far */
+  /*! \brief bytes of the window that InitKey and ReserveRaw have handed out so far */
   size_t WindowUsed() const { return used_; }
+
+  /*!
+   * \brief sets `bytes` of every rank's window aside for the caller's own kernels and returns
+   *  their offset.  All ranks make the same calls in the same order, so the offset is the same
+   *  everywhere.  What travels through such a region, and how its readers learn that it has
+   *  arrived, is the caller's business; a key pushed after the writing kernels, on the same stream,
+   *  is a completion signal: its words are stored after those kernels have finished.
+   */
+  size_t ReserveRaw(size_t bytes) {
+    CHECK(ready_) << "PeerModel: Init has not been called";
+    const size_t offset = peerdetail::RoundUp(used_, 256);
+    CHECK_LE(offset + bytes, window_bytes_) << "PeerModel: a region of " << bytes << " bytes does not fit the window of "
+                                            << window_bytes_ << " bytes (SetParam(\"window_bytes\", ...) before Init)";
+    used_ = offset + bytes;
+    return offset;
+  }
+
+  /*! \brief address, in this process, of byte `offset` of rank p's window (plain loads and stores only) */
+  void *WindowOf(int p, size_t offset) const {
+    CHECK(connected_) << "PeerModel: Connect has not been called";
+    CHECK(p >= 0 && p < world_) << "PeerModel: rank " << p << " of " << world_;
+    CHECK_LE(offset, window_bytes_) << "PeerModel: offset beyond the window";
+    return peer_[p] + offset;
+  }
 
  protected:
   virtual void InitKey_(Shape<2> shape, int key, int devid) {

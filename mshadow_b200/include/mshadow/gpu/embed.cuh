@@ -30,6 +30,7 @@
 #include <cub/device/device_radix_sort.cuh>
 
 #include "./radix_sort.cuh"
+#include "./route.cuh"
 #include "./runtime.h"
 #include "./tma.cuh"
 
@@ -57,7 +58,9 @@ template <int kLanes, int kDepth>
 __global__ void __launch_bounds__(256, kDepth > 4 ? 2 : MSHADOW_B200_SEG_MIN_CTAS)
 SegmentSumKernel(float *dst, int64_t ld_dst, const int32_t *keys, const int32_t *rows, const float *src,
                  int64_t ld_src, uint32_t n, uint32_t width, uint32_t chunk_len, int32_t *part_keys,
-                 int32_t *part_rows, float *partials) {
+                 int32_t *part_rows, float *partials, int store, const routedetail::RowRoute route) {
+  // store != 0: a finished run's sum is stored into its table row instead of added to it (the
+  // row is not read; it may then live in another GPU's memory).
   // With kDepth > 4 (the upper levels) the additions to table rows are batched: a run that ends
   // inside a batch of kDepth entries is parked, and once the batch has been walked the table rows
   // of all parked runs are loaded together, added to and stored.  Done one by one -- load, add,
@@ -85,7 +88,13 @@ SegmentSumKernel(float *dst, int64_t ld_dst, const int32_t *keys, const int32_t 
   for (int l = 0; l < kLanes; ++l) acc[l] = 0.0f;
 
   auto add_to_row = [&](float *row, const float (&a)[kLanes]) {
-    if (kLanes == 4) {
+    if (store) {
+      if (kLanes == 4) {
+        *reinterpret_cast<float4 *>(row) = make_float4(a[0], a[1 % kLanes], a[2 % kLanes], a[3 % kLanes]);
+      } else {
+        row[0] = a[0];
+      }
+    } else if (kLanes == 4) {
       float4 d = *reinterpret_cast<float4 *>(row);
       d.x = __fadd_rn(d.x, a[0]);
       d.y = __fadd_rn(d.y, a[1 % kLanes]);
@@ -102,7 +111,7 @@ SegmentSumKernel(float *dst, int64_t ld_dst, const int32_t *keys, const int32_t 
     const bool spans = (first_run && joins_prev) || (last_run && joins_next);
     if (!spans) {
       if (any && active) {
-        float *row = dst + static_cast<int64_t>(cur) * ld_dst + col;
+        float *row = routedetail::RowOf(route, dst, ld_dst, cur) + col;
         if (park != nullptr) {
           *park = row;
 #pragma unroll
@@ -180,7 +189,9 @@ SegmentSumKernel(float *dst, int64_t ld_dst, const int32_t *keys, const int32_t 
       float d[kDepth][kLanes];
 #pragma unroll
       for (int u = 0; u < kDepth; ++u) {
-        if (parked[u] != nullptr) {
+#pragma unroll
+        for (int l = 0; l < kLanes; ++l) d[u][l] = 0.0f;
+        if (parked[u] != nullptr && !store) {
           if (kLanes == 4) {
             const float4 q = *reinterpret_cast<const float4 *>(parked[u]);
             d[u][0] = q.x;
@@ -197,11 +208,14 @@ SegmentSumKernel(float *dst, int64_t ld_dst, const int32_t *keys, const int32_t 
         if (parked[u] != nullptr) {
           if (kLanes == 4) {
             *reinterpret_cast<float4 *>(parked[u]) =
-                make_float4(__fadd_rn(d[u][0], parked_acc[u][0]), __fadd_rn(d[u][1 % kLanes], parked_acc[u][1 % kLanes]),
-                            __fadd_rn(d[u][2 % kLanes], parked_acc[u][2 % kLanes]),
-                            __fadd_rn(d[u][3 % kLanes], parked_acc[u][3 % kLanes]));
+                store ? make_float4(parked_acc[u][0], parked_acc[u][1 % kLanes], parked_acc[u][2 % kLanes],
+                                    parked_acc[u][3 % kLanes])
+                      : make_float4(__fadd_rn(d[u][0], parked_acc[u][0]),
+                                    __fadd_rn(d[u][1 % kLanes], parked_acc[u][1 % kLanes]),
+                                    __fadd_rn(d[u][2 % kLanes], parked_acc[u][2 % kLanes]),
+                                    __fadd_rn(d[u][3 % kLanes], parked_acc[u][3 % kLanes]));
           } else {
-            parked[u][0] = __fadd_rn(d[u][0], parked_acc[u][0]);
+            parked[u][0] = store ? parked_acc[u][0] : __fadd_rn(d[u][0], parked_acc[u][0]);
           }
         }
       }
@@ -227,7 +241,7 @@ template <int kRingSlots>
 __global__ void __launch_bounds__(288, MSHADOW_B200_SEG_MIN_CTAS)
 SegmentSumStagedKernel(float *dst, int64_t ld_dst, const int32_t *keys, const int32_t *rows, const float *src,
                        int64_t ld_src, uint32_t n, uint32_t width, int32_t *part_keys, int32_t *part_rows,
-                       float *partials, int *status) {
+                       float *partials, int *status, int store, const routedetail::RowRoute route) {
   extern __shared__ __align__(16) float ring[];
   __shared__ uint64_t full[kSegRing], empty[kSegRing];
   __shared__ int32_t s_keys[kSegChunk], s_rows[kSegChunk];
@@ -295,13 +309,17 @@ SegmentSumStagedKernel(float *dst, int64_t ld_dst, const int32_t *keys, const in
     const bool spans = (first_run && joins_prev) || (last_run && joins_next);
     if (!spans) {
       if (any && active) {
-        float *row = dst + static_cast<int64_t>(cur) * ld_dst + col;
-        float4 d = *reinterpret_cast<float4 *>(row);
-        d.x = __fadd_rn(d.x, acc[0]);
-        d.y = __fadd_rn(d.y, acc[1]);
-        d.z = __fadd_rn(d.z, acc[2]);
-        d.w = __fadd_rn(d.w, acc[3]);
-        *reinterpret_cast<float4 *>(row) = d;
+        float *row = routedetail::RowOf(route, dst, ld_dst, cur) + col;
+        if (store) {
+          *reinterpret_cast<float4 *>(row) = make_float4(acc[0], acc[1], acc[2], acc[3]);
+        } else {
+          float4 d = *reinterpret_cast<float4 *>(row);
+          d.x = __fadd_rn(d.x, acc[0]);
+          d.y = __fadd_rn(d.y, acc[1]);
+          d.z = __fadd_rn(d.z, acc[2]);
+          d.w = __fadd_rn(d.w, acc[3]);
+          *reinterpret_cast<float4 *>(row) = d;
+        }
       }
     } else if (any) {
       const uint32_t slot = 2 * chunk + (first_run ? 0 : 1);
@@ -394,7 +412,17 @@ inline size_t SegmentScratchBytes(uint32_t n, uint32_t width) {
 
 /*! \brief run all levels; `scratch` must hold SegmentScratchBytes(n, width) */
 inline void SegmentSumRun(float *dst, int64_t ld_dst, const int32_t *keys, const int32_t *rows, const float *src,
-                          int64_t ld_src, uint32_t n, uint32_t width, char *scratch, cudaStream_t stream) {
+                          int64_t ld_src, uint32_t n, uint32_t width, char *scratch, cudaStream_t stream,
+                          bool store = false, const routedetail::RowRoute *route = nullptr) {
+  const int st = store ? 1 : 0;
+  routedetail::RowRoute rt;
+  if (route != nullptr) {
+    rt = *route;
+  } else {
+    for (int q = 0; q < routedetail::kMaxOwners; ++q) rt.base[q] = nullptr;
+    rt.first = nullptr;
+    rt.world = 0;
+  }
   if (n == 0 || width == 0) return;
   uint32_t entries[kMaxLevels], chunks[kMaxLevels], len[kMaxLevels];
   const int levels = Levels(n, entries, chunks, len);
@@ -414,6 +442,7 @@ inline void SegmentSumRun(float *dst, int64_t ld_dst, const int32_t *keys, const
     }
     const bool vec = width % 4 == 0 && lld % 4 == 0 && ld_dst % 4 == 0 &&
                      reinterpret_cast<uintptr_t>(lsrc) % 16 == 0 && reinterpret_cast<uintptr_t>(dst) % 16 == 0;
+    // (a routed call passes dst == nullptr; its owners' blocks are checked for alignment by the caller)
     const uint32_t items = vec ? width / 4 : width;
     uint32_t threads = (items + 31) / 32 * 32;
     if (threads > 256) threads = 256;
@@ -428,19 +457,19 @@ inline void SegmentSumRun(float *dst, int64_t ld_dst, const int32_t *keys, const
       const size_t smem = static_cast<size_t>(kSegRing) * kSegSlab * sizeof(float);
       MSHADOW_CUDA_CALL(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
       kernel<<<dim3(chunks[l], (width + kSegSlab - 1) / kSegSlab), 288, smem, stream>>>(
-          dst, ld_dst, lkeys, lrows, lsrc, lld, entries[l], width, pk, pr, pp, gpu_rt::StatusWord());
+          dst, ld_dst, lkeys, lrows, lsrc, lld, entries[l], width, pk, pr, pp, gpu_rt::StatusWord(), st, rt);
     } else if (vec && long_chunks) {
       SegmentSumKernel<4, kSegDepth><<<grid, threads, 0, stream>>>(dst, ld_dst, lkeys, lrows, lsrc, lld, entries[l],
-                                                                   width, len[l], pk, pr, pp);
+                                                                   width, len[l], pk, pr, pp, st, rt);
     } else if (vec) {
       SegmentSumKernel<4, kSegDepthUpper><<<grid, threads, 0, stream>>>(dst, ld_dst, lkeys, lrows, lsrc, lld,
-                                                                        entries[l], width, len[l], pk, pr, pp);
+                                                                        entries[l], width, len[l], pk, pr, pp, st, rt);
     } else if (long_chunks) {
       SegmentSumKernel<1, kSegDepth><<<grid, threads, 0, stream>>>(dst, ld_dst, lkeys, lrows, lsrc, lld, entries[l],
-                                                                   width, len[l], pk, pr, pp);
+                                                                   width, len[l], pk, pr, pp, st, rt);
     } else {
       SegmentSumKernel<1, kSegDepthUpper><<<grid, threads, 0, stream>>>(dst, ld_dst, lkeys, lrows, lsrc, lld,
-                                                                        entries[l], width, len[l], pk, pr, pp);
+                                                                        entries[l], width, len[l], pk, pr, pp, st, rt);
     }
     MSHADOW_CUDA_POST_KERNEL_CHECK(SegmentSumKernel);
     lkeys = pk;
@@ -451,16 +480,21 @@ inline void SegmentSumRun(float *dst, int64_t ld_dst, const int32_t *keys, const
 }
 }  // namespace embeddetail
 
-/*! \brief dst[sorted[y]] += src[index[y]]; `sorted` ascending */
+/*!
+ * \brief dst[sorted[y]] += src[index[y]]; `sorted` ascending.  With store, the rows named by `sorted`
+ *  receive the sum itself (dst[r] = sum; rows not named stay as they are): every named row is
+ *  written exactly once and never read, so dst may be memory of another GPU.
+ */
 inline void AddTakeGradLargeBatchLaunch(float *dst, int64_t ld_dst, const int32_t *sorted, const int32_t *index,
                                         const float *src, int64_t ld_src, int64_t n, int64_t width,
-                                        cudaStream_t stream) {
+                                        cudaStream_t stream, bool store = false,
+                                        const routedetail::RowRoute *route = nullptr) {
   if (n == 0 || width == 0) return;
   CHECK_LT(n, (int64_t(1) << 31));
   const size_t bytes = embeddetail::SegmentScratchBytes(static_cast<uint32_t>(n), static_cast<uint32_t>(width));
   char *scratch = bytes == 0 ? nullptr : static_cast<char *>(gpu_rt::Scratch::Get(stream, bytes));
   embeddetail::SegmentSumRun(dst, ld_dst, sorted, index, src, ld_src, static_cast<uint32_t>(n),
-                             static_cast<uint32_t>(width), scratch, stream);
+                             static_cast<uint32_t>(width), scratch, stream, store, route);
 }
 
 namespace embeddetail {

@@ -16,7 +16,6 @@
 #include "./embed.cuh"
 #include "./map.cuh"
 #include "./reduce.cuh"
-#include "./route.cuh"
 #include "./softmax.cuh"
 
 namespace mshadow {

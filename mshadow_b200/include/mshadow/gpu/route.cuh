@@ -24,6 +24,12 @@
  *                        is what a GPU sends to the owners when the SOURCE rows are spread over
  *                        the GPUs by batch position.
  *
+ *   RunBoundsKernel / RunKeysToOwnersKernel, RowRoute
+ *                        with keys of the form owner * per_owner + local row the runs of one owner
+ *                        form a block; RowRoute tells the segmented sum (embed.cuh) to store the
+ *                        sum of run j into row j - first[owner] of a matrix in the OWNER's memory,
+ *                        and RunKeysToOwnersKernel stores the local row numbers beside them.
+ *
  * The selection is stable, so each table row keeps its accumulation order.  All arithmetic is on
  * 32-bit integers; results are exact.
  */
@@ -45,6 +51,38 @@ struct Geometry {
   int32_t src_begin, src_end;               // source rows held by this GPU (for the hot part)
   int32_t hot_count, hot_base;
 };
+
+const int kMaxOwners = 16;
+
+/*!
+ * \brief where the rows of a compact run numbering live when consecutive blocks of runs belong to
+ *  different owners: run j with first[q] <= j < first[q + 1] is row j - first[q] of the matrix at
+ *  base[q] (an address in owner q's memory as mapped into this process).  world == 0: not routed.
+ */
+template <typename T>
+struct OwnerBlocks {
+  T *base[kMaxOwners];
+  const int32_t *first;   // device array of world + 1 entries
+  int32_t world;
+};
+typedef OwnerBlocks<float> RowRoute;
+
+/*! \brief the owner of run j: the last q with first[q] <= j */
+__device__ __forceinline__ int OwnerOf(const int32_t *first, int world, int32_t j) {
+  int lo = 0, hi = world;               // first[lo] <= j < first[hi]
+  while (hi - lo > 1) {
+    const int mid = (lo + hi) >> 1;
+    if (first[mid] <= j) lo = mid; else hi = mid;
+  }
+  return lo;
+}
+
+/*! \brief address of row `run`: in the routed case inside its owner's block, else dst + run * ld */
+__device__ __forceinline__ float *RowOf(const RowRoute &r, float *dst, int64_t ld, int32_t run) {
+  if (r.world == 0) return dst + static_cast<int64_t>(run) * ld;
+  const int q = OwnerOf(r.first, r.world, run);
+  return r.base[q] + static_cast<int64_t>(run - r.first[q]) * ld;
+}
 
 /*! \brief 0: tail entry of this GPU, 1: hot entry of this GPU, 2: not ours; `pos` = position in the hot list */
 __device__ __forceinline__ int Classify(int32_t key, int32_t row, const Geometry &g, const int32_t *s_hot, int32_t *pos) {
@@ -281,6 +319,36 @@ RunIndexKernel(int32_t *run_of, int32_t *run_keys, const uint32_t *bases, const 
   }
 }
 
+/*!
+ * \brief first[q] = number of runs whose key is below q * per_owner, for q = 0 .. world: with keys
+ *  of the form owner * per_owner + local row, the block of runs of every owner.  One warp.
+ */
+template <int kDummy>
+__global__ void RunBoundsKernel(int32_t *first, const int32_t *run_keys, const uint32_t *total, int world,
+                                int32_t per_owner) {
+  const int q = threadIdx.x;
+  if (q > world) return;
+  const uint32_t runs = total[0];
+  const int64_t want = static_cast<int64_t>(q) * per_owner;
+  uint32_t lo = 0, hi = runs;           // lower bound of `want` in run_keys[0 .. runs)
+  while (lo < hi) {
+    const uint32_t mid = lo + ((hi - lo) >> 1);
+    if (run_keys[mid] < want) lo = mid + 1; else hi = mid;
+  }
+  first[q] = static_cast<int32_t>(lo);
+}
+
+/*! \brief hands every owner the local row numbers of its runs: to.base[q][j - first[q]] = run_keys[j] - q * per_owner */
+template <int kDummy>
+__global__ void __launch_bounds__(256)
+RunKeysToOwnersKernel(const routedetail::OwnerBlocks<int32_t> to, const int32_t *run_keys, int32_t per_owner) {
+  const int32_t runs = to.first[to.world];
+  for (int32_t j = blockIdx.x * blockDim.x + threadIdx.x; j < runs; j += gridDim.x * blockDim.x) {
+    const int q = routedetail::OwnerOf(to.first, to.world, j);
+    to.base[q][j - to.first[q]] = run_keys[j] - q * per_owner;
+  }
+}
+
 namespace routedetail {
 inline size_t Align256(size_t b) { return (b + 255) / 256 * 256; }
 inline uint32_t Tiles(int64_t n) { return static_cast<uint32_t>((n + kTile - 1) / kTile); }
@@ -339,6 +407,24 @@ inline void RunIndexLaunch(int32_t *run_of, int32_t *run_keys, uint32_t *total, 
   MSHADOW_CUDA_POST_KERNEL_CHECK(RunHeadScanKernel);
   RunIndexKernel<0><<<tiles, kThreads, 0, stream>>>(run_of, run_keys, counts, keys, un);
   MSHADOW_CUDA_POST_KERNEL_CHECK(RunIndexKernel);
+}
+
+/*! \brief first[0 .. world] (device): the block of runs of every owner, for run keys owner * per_owner + local row */
+inline void RunBoundsLaunch(int32_t *first, const int32_t *run_keys, const uint32_t *total, int world,
+                            int32_t per_owner, cudaStream_t stream) {
+  CHECK(world >= 1 && world <= routedetail::kMaxOwners) << "RunBounds: at most " << routedetail::kMaxOwners << " owners";
+  RunBoundsKernel<0><<<1, 32, 0, stream>>>(first, run_keys, total, world, per_owner);
+  MSHADOW_CUDA_POST_KERNEL_CHECK(RunBoundsKernel);
+}
+
+/*! \brief the owners' row numbers of all runs, stored into the owners' blocks (`n` bounds the number of runs) */
+inline void RunKeysToOwnersLaunch(const routedetail::OwnerBlocks<int32_t> &to, const int32_t *run_keys, int64_t n,
+                                  int32_t per_owner, cudaStream_t stream) {
+  if (n == 0) return;
+  unsigned grid = gpu_rt::CeilDiv(static_cast<uint32_t>(n), 256u);
+  if (grid > 1184u) grid = 1184u;
+  RunKeysToOwnersKernel<0><<<grid, 256, 0, stream>>>(to, run_keys, per_owner);
+  MSHADOW_CUDA_POST_KERNEL_CHECK(RunKeysToOwnersKernel);
 }
 
 /*! \brief lens[i] = run length at run heads of the sorted list, 0 elsewhere; rows[i] = keys[i] */

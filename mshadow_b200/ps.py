@@ -21,6 +21,8 @@ _SIGNATURES = {
     "msb_ps_peer_handle": [vp, C.c_char_p, i64],
     "msb_ps_peer_connect": [vp, C.c_char_p],
     "msb_ps_peer_next_sink": [vp, cint, i64, i64, vp],
+    "msb_ps_peer_reserve": [vp, i64, vp],
+    "msb_ps_peer_window": [vp, cint, i64, vp],
     "msb_ps_destroy": [vp],
     "msb_ps_init_key": [vp, cint, i64, i64],
     "msb_ps_push": [vp, vp, i64, i64, i64, cint, vp],
@@ -154,6 +156,19 @@ class PeerModel(SharedModel):
         """`handles`: the export_handle() strings of all ranks, in rank order."""
         assert len(handles) == self.world
         _check(dll().msb_ps_peer_connect(self.handle, "".join(handles).encode("ascii")))
+
+    def reserve(self, nbytes):
+        """Sets `nbytes` of every rank's window aside for the caller's own kernels; returns the offset
+        (the same on all ranks when all make the same calls in the same order)."""
+        off = C.c_int64(0)
+        _check(dll().msb_ps_peer_reserve(self.handle, nbytes, C.byref(off)))
+        return int(off.value)
+
+    def window(self, rank, offset=0):
+        """Address, in this process, of byte `offset` of rank `rank`'s window (after connect)."""
+        ptr = vp()
+        _check(dll().msb_ps_peer_window(self.handle, rank, offset, C.byref(ptr)))
+        return int(ptr.value or 0)
 
     def next_sink(self, key, offset, count):
         """Sink for `count` results from element `offset` of the key's row in the step that the

@@ -354,7 +354,10 @@ def test_lrn_forward_backward(lib, power_kind, shape, nsize):
                                         # long lists: the staged first level (rows of 1 KB and more), the register
                                         # forms of the first level (narrow and odd-width rows), short-chunk levels above
                                         (300, 1024, 30000, "zipf"), (5000, 256, 25000, "uniform"),
-                                        (90, 33, 25000, "zipf"), (3, 512, 20000, "uniform")])
+                                        (90, 33, 25000, "zipf"), (3, 512, 20000, "uniform"),
+                                        # short lists: every level in the short-chunk register form
+                                        (2, 1024, 512, "uniform"), (5, 64, 513, "uniform"), (1, 132, 100, "uniform"),
+                                        (40, 256, 37, "distinct"), (400, 12, 511, "zipf")])
 def test_addtakegrad_largebatch(lib, k, d, n, kind):
     rng = np.random.default_rng(k + d + n)
     if kind == "uniform":
@@ -430,6 +433,46 @@ def test_run_numbering_of_a_sorted_list(lib, n, rows):
     assert int(host(total)[0]) == uniq.size
     assert np.array_equal(host(run_of), inverse.astype(np.int32))
     assert np.array_equal(host(run_keys)[:uniq.size], uniq) and np.all(host(run_keys)[uniq.size:] == -7)
+
+
+@pytest.mark.parametrize("n,table_rows,d,world", [(1, 5, 8, 1), (300, 40, 20, 2), (5000, 300, 1024, 3),
+                                                 (30000, 5000, 256, 8), (40000, 64, 1024, 4)])
+def test_sums_stored_into_the_owners_blocks(lib, n, table_rows, d, world):
+    """The sender's half of the placement 'source rows sharded by batch position': entries sorted by
+    (owner, local row), runs numbered, owners' blocks found, every run's sum STORED into its row of
+    its owner's block and the local row number beside it.  The blocks here are all in this GPU's
+    memory; the sums are compared with the CPU evaluation of AddTakeGradLargeBatch on a zero table."""
+    rng = np.random.default_rng(n + world)
+    idx = zipf_indices(rng, n, table_rows)
+    src = rng.standard_normal((n, d)).astype(np.float32)
+    per_owner = (table_rows + world - 1) // world
+    ck = ((idx % world) * per_owner + idx // world).astype(np.int32)
+    pos = np.arange(n, dtype=np.int32)
+    dck, dpos = lib.sort_by_key(dev(ck), dev(pos), True)
+    run_of = torch.empty(n, dtype=torch.int32, device="cuda")
+    run_keys = torch.empty(n, dtype=torch.int32, device="cuda")
+    total = torch.zeros(1, dtype=torch.int32, device="cuda")
+    lib.run_index(run_of, run_keys, total, dck)
+    first = torch.full((world + 1,), -1, dtype=torch.int32, device="cuda")
+    lib.run_bounds(first, run_keys, total, world, per_owner)
+    uniq = np.unique(ck)
+    want_first = np.searchsorted(uniq, np.arange(world + 1) * per_owner).astype(np.int32)
+    assert np.array_equal(host(first), want_first)
+    rows = [torch.full((per_owner, d), 7.5, device="cuda") for _ in range(world)]
+    keys = [torch.full((per_owner,), -7, dtype=torch.int32, device="cuda") for _ in range(world)]
+    dsrc = dev(src)
+    lib.take_sum_to_owners([t.data_ptr() for t in rows], first, run_of, dpos, dsrc, world)
+    lib.run_keys_to_owners([t.data_ptr() for t in keys], first, run_keys, world, per_owner)
+    order = np.argsort(idx, kind="stable").astype(np.int32)
+    table = orc.addtakegrad_largebatch(np.zeros((table_rows, d), np.float32), idx[order], order, src)
+    for q in range(world):
+        cnt = int(want_first[q + 1] - want_first[q])
+        local = uniq[want_first[q]:want_first[q + 1]] - q * per_owner
+        assert np.array_equal(host(keys[q])[:cnt], local) and np.all(host(keys[q])[cnt:] == -7)
+        got = host(rows[q])
+        assert np.all(got[cnt:] == 7.5)                       # rows beyond the owner's runs stay untouched
+        if cnt:
+            assert_sum_close(got[:cnt], table[local * world + q], per_row=True)
 
 
 @pytest.mark.parametrize("n,rows,nhot", [(1, 5, 0), (300, 7, 2), (5000, 40, 8), (70000, 3000, 64), (200001, 50000, 64)])
