@@ -952,6 +952,7 @@ def make_batch_sharded_peer_step(torch, lib, dist, idx_all, src, rank, world, lo
     n_loc = e - b
     kp = (EMBED_K + world - 1) // world
     rows_mine = (EMBED_K - rank + world - 1) // world
+    key_bits, row_bits = max(1, int(world * kp - 1).bit_length()), max(1, int(kp - 1).bit_length())
     slots = world * kp                                  # rows a rank can receive per step: kp from every sender
     row_bytes, key_bytes = 2 * slots * EMBED_D * 4, 2 * slots * 4
     m = ps.PeerModel(rank=rank, world=world, device=local_rank, depth=4, wait_limit_ms=20000,
@@ -994,7 +995,7 @@ def make_batch_sharded_peer_step(torch, lib, dist, idx_all, src, rank, world, lo
         ev[0].record()
         ck = ((idx % world) * kp + idx // world).to(torch.int32)
         pos.copy_(iota)
-        lib.sort_by_key(ck, pos)
+        lib.sort_by_key(ck, pos, bits=key_bits)
         lib.run_index(run_of, run_keys, total, ck)
         lib.run_bounds(first, run_keys, total, world, kp)
         ev[1].record()
@@ -1016,7 +1017,7 @@ def make_batch_sharded_peer_step(torch, lib, dist, idx_all, src, rank, world, lo
                 parts_o.append(lane[:c] + (parity * slots + r * kp))
         if parts_k:
             keys_in, order_in = torch.cat(parts_k), torch.cat(parts_o)
-            lib.sort_by_key(keys_in, order_in)
+            lib.sort_by_key(keys_in, order_in, bits=row_bits)
             lib.call("msb_addtakegrad_largebatch_f32_i32", shard.data_ptr(), keys_in.data_ptr(), order_in.data_ptr(),
                      my_rows, rows_mine, EMBED_D, keys_in.shape[0], None)
         ev[3].record()

@@ -285,6 +285,12 @@ int msb_route_cyclic_hot_i32(int32_t *keys_out, int32_t *rows_out, uint32_t *tot
                              const int32_t *hot, int64_t hot_count, int world, int rank,
                              int64_t src_begin, int64_t src_end, int64_t hot_base,
                              msb_stream_t stream);
+/* SortByKey (ascending, stable) for keys known to lie in [0, 2^bits): only those bits are
+   sorted, in an even number of passes of at most nine bits (row numbers of a 2^18-row table:
+   two passes instead of the four of msb_sort_by_key_i32).  Keys outside the range give an
+   order by their low bits only. */
+int msb_sort_by_key_lowbits_i32(int32_t *keys, int32_t *values, int64_t n, int bits,
+                                msb_stream_t stream);
 /* VectorizedSort(values, segments): values sorted ascending inside each run of equal
    `segments` (ascending on entry), two stable pair sorts: mshadow/tensor.h:905-915,
    mshadow/tensor_cpu-inl.h:562-567 */

@@ -72,6 +72,7 @@ _SIGNATURES = {
     "msb_addtakegrad_f32_i32": [vp, vp, vp, i64, i64, i64, i64, i64, vp],
     "msb_addtakegrad_largebatch_f32_i32": [vp, vp, vp, vp, i64, i64, i64, vp],
     "msb_sort_by_key_i32": [vp, vp, i64, cint, vp],
+    "msb_sort_by_key_lowbits_i32": [vp, vp, i64, cint, vp],
     "msb_vectorized_sort_f32_i32": [vp, vp, i64, vp],
     "msb_frequent_rows_i32": [vp, vp, vp, i64, i64, vp],
     "msb_run_index_i32": [vp, vp, vp, vp, i64, vp],
@@ -326,8 +327,13 @@ class Library:
                   world, rank, src_begin, src_end, hot_base, stream)
         return keys_out, rows_out, totals
 
-    def sort_by_key(self, keys, values, ascend=True, stream=None):
-        self.call("msb_sort_by_key_i32", _ptr(keys), _ptr(values), keys.shape[0], int(ascend), stream)
+    def sort_by_key(self, keys, values, ascend=True, stream=None, bits=None):
+        """bits: the keys are known to lie in [0, 2^bits) (ascending only): fewer passes."""
+        if bits is not None:
+            assert ascend
+            self.call("msb_sort_by_key_lowbits_i32", _ptr(keys), _ptr(values), keys.shape[0], bits, stream)
+        else:
+            self.call("msb_sort_by_key_i32", _ptr(keys), _ptr(values), keys.shape[0], int(ascend), stream)
         return keys, values
 
     def remap_shape(self, cid, shape, p0=0, p1=0):

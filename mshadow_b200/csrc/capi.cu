@@ -605,6 +605,20 @@ int msb_sort_by_key_i32(int32_t *keys, int32_t *values, int64_t n, int ascend, m
   MSB_GUARD_END
 }
 
+int msb_sort_by_key_lowbits_i32(int32_t *keys, int32_t *values, int64_t n, int bits, msb_stream_t stream) {
+  MSB_REQUIRE(FitsIndex(n), MSB_ERR_SHAPE, "extent out of range");
+  MSB_REQUIRE(bits >= 1 && bits <= 31, MSB_ERR_ARGUMENT, "1 to 31 key bits");
+  if (n <= 1) return MSB_OK;
+  MSB_REQUIRE(keys && values, MSB_ERR_ARGUMENT, "null pointer");
+  MSB_GUARD_BEGIN
+  BorrowedStream st(stream);
+  cudaStream_t cs = Stream<gpu>::GetStream(st.get());
+  char *scratch = static_cast<char *>(mshadow::gpu_rt::Scratch::Get(cs, mshadow::cuda::sortdetail::ScratchBytes(n)));
+  const mshadow::cuda::sortdetail::Source as_given = {0};
+  mshadow::cuda::sortdetail::SortPairs<int32_t, int32_t>(keys, values, keys, n, bits, true, as_given, scratch, cs);
+  MSB_GUARD_END
+}
+
 int msb_frequent_rows_i32(int32_t *rows_out, int32_t *counts_out, const int32_t *sorted, int64_t n, int64_t count,
                           msb_stream_t stream) {
   MSB_REQUIRE(FitsIndex(n) && count >= 0 && count <= n, MSB_ERR_SHAPE, "extent out of range");

@@ -87,6 +87,7 @@ SegmentSumKernel(float *dst, int64_t ld_dst, const int32_t *keys, const int32_t 
 #pragma unroll
   for (int l = 0; l < kLanes; ++l) acc[l] = 0.0f;
 
+  routedetail::OwnerHint hint = {0, 0, 0};
   auto add_to_row = [&](float *row, const float (&a)[kLanes]) {
     if (store) {
       if (kLanes == 4) {
@@ -111,7 +112,7 @@ SegmentSumKernel(float *dst, int64_t ld_dst, const int32_t *keys, const int32_t 
     const bool spans = (first_run && joins_prev) || (last_run && joins_next);
     if (!spans) {
       if (any && active) {
-        float *row = routedetail::RowOf(route, dst, ld_dst, cur) + col;
+        float *row = routedetail::RowOf(route, dst, ld_dst, cur, &hint) + col;
         if (park != nullptr) {
           *park = row;
 #pragma unroll
@@ -309,7 +310,9 @@ SegmentSumStagedKernel(float *dst, int64_t ld_dst, const int32_t *keys, const in
     const bool spans = (first_run && joins_prev) || (last_run && joins_next);
     if (!spans) {
       if (any && active) {
-        float *row = routedetail::RowOf(route, dst, ld_dst, cur) + col;
+        // (no cached owner block here: its three registers would cost this kernel its fifth CTA per SM)
+        routedetail::OwnerHint look = {0, 0, 0};
+        float *row = routedetail::RowOf(route, dst, ld_dst, cur, &look) + col;
         if (store) {
           *reinterpret_cast<float4 *>(row) = make_float4(acc[0], acc[1], acc[2], acc[3]);
         } else {

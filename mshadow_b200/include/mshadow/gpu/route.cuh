@@ -77,11 +77,21 @@ __device__ __forceinline__ int OwnerOf(const int32_t *first, int world, int32_t 
   return lo;
 }
 
+/*! \brief the owner block a thread looked up last: consecutive runs mostly share it */
+struct OwnerHint {
+  int32_t lo, hi;   // runs lo .. hi - 1 belong to owner q (lo == hi: nothing cached)
+  int q;
+};
+
 /*! \brief address of row `run`: in the routed case inside its owner's block, else dst + run * ld */
-__device__ __forceinline__ float *RowOf(const RowRoute &r, float *dst, int64_t ld, int32_t run) {
+__device__ __forceinline__ float *RowOf(const RowRoute &r, float *dst, int64_t ld, int32_t run, OwnerHint *hint) {
   if (r.world == 0) return dst + static_cast<int64_t>(run) * ld;
-  const int q = OwnerOf(r.first, r.world, run);
-  return r.base[q] + static_cast<int64_t>(run - r.first[q]) * ld;
+  if (run < hint->lo || run >= hint->hi) {
+    hint->q = OwnerOf(r.first, r.world, run);
+    hint->lo = r.first[hint->q];
+    hint->hi = r.first[hint->q + 1];
+  }
+  return r.base[hint->q] + static_cast<int64_t>(run - hint->lo) * ld;
 }
 
 /*! \brief 0: tail entry of this GPU, 1: hot entry of this GPU, 2: not ours; `pos` = position in the hot list */

@@ -504,6 +504,16 @@ def test_routing_on_the_device_matches_the_host_routing(lib, n, rows, nhot, worl
         assert np.all(host(ok)[nt + nh:] == -7)
 
 
+@pytest.mark.parametrize("n,bits", [(2, 1), (1000, 7), (70000, 18), (70000, 19), (300000, 31)])
+def test_sort_by_key_on_the_significant_bits(lib, n, bits):
+    rng = np.random.default_rng(n + bits)
+    keys = rng.integers(0, 2 ** bits, n, dtype=np.int64).astype(np.int32)
+    vals = np.arange(n, dtype=np.int32)
+    order = np.argsort(keys, kind="stable")
+    gk, gv = lib.sort_by_key(dev(keys), dev(vals), True, bits=bits)
+    assert np.array_equal(host(gk), keys[order]) and np.array_equal(host(gv), vals[order])
+
+
 @pytest.mark.parametrize("batch,classes,npos,pad", [
     (1, 1, 1, 0), (2, 5, 7, 0), (3, 21, 64, 0), (2, 9, 33, 3), (2, 21, 1024, 0), (1, 19, 4100, 4),
     (2, 100, 512, 0),    # 128-bit tile too large for shared memory: one position per thread
