@@ -59,6 +59,7 @@ __global__ void __launch_bounds__(256, kDepth > 4 ? 2 : MSHADOW_B200_SEG_MIN_CTA
 SegmentSumKernel(float *dst, int64_t ld_dst, const int32_t *keys, const int32_t *rows, const float *src,
                  int64_t ld_src, uint32_t n, uint32_t width, uint32_t chunk_len, int32_t *part_keys,
                  int32_t *part_rows, float *partials, int store, const routedetail::RowRoute route) {
+  gpu_rt::GridDependencySync();
   // store != 0: a finished run's sum is stored into its table row instead of added to it (the
   // row is not read; it may then live in another GPU's memory).
   // With kDepth > 4 (the upper levels) the additions to table rows are batched: a run that ends
@@ -243,6 +244,7 @@ __global__ void __launch_bounds__(288, MSHADOW_B200_SEG_MIN_CTAS)
 SegmentSumStagedKernel(float *dst, int64_t ld_dst, const int32_t *keys, const int32_t *rows, const float *src,
                        int64_t ld_src, uint32_t n, uint32_t width, int32_t *part_keys, int32_t *part_rows,
                        float *partials, int *status, int store, const routedetail::RowRoute route) {
+  gpu_rt::GridDependencySync();
   extern __shared__ __align__(16) float ring[];
   __shared__ uint64_t full[kSegRing], empty[kSegRing];
   __shared__ int32_t s_keys[kSegChunk], s_rows[kSegChunk];
@@ -459,19 +461,19 @@ inline void SegmentSumRun(float *dst, int64_t ld_dst, const int32_t *keys, const
       auto kernel = SegmentSumStagedKernel<static_cast<int>(kSegRing)>;
       const size_t smem = static_cast<size_t>(kSegRing) * kSegSlab * sizeof(float);
       MSHADOW_CUDA_CALL(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
-      kernel<<<dim3(chunks[l], (width + kSegSlab - 1) / kSegSlab), 288, smem, stream>>>(
+      gpu_rt::LaunchAfterDrain(kernel, dim3(chunks[l], (width + kSegSlab - 1) / kSegSlab), dim3(288), smem, stream, 
           dst, ld_dst, lkeys, lrows, lsrc, lld, entries[l], width, pk, pr, pp, gpu_rt::StatusWord(), st, rt);
     } else if (vec && long_chunks) {
-      SegmentSumKernel<4, kSegDepth><<<grid, threads, 0, stream>>>(dst, ld_dst, lkeys, lrows, lsrc, lld, entries[l],
+      gpu_rt::LaunchAfterDrain(SegmentSumKernel<4, kSegDepth>, dim3(grid), dim3(threads), 0, stream, dst, ld_dst, lkeys, lrows, lsrc, lld, entries[l],
                                                                    width, len[l], pk, pr, pp, st, rt);
     } else if (vec) {
-      SegmentSumKernel<4, kSegDepthUpper><<<grid, threads, 0, stream>>>(dst, ld_dst, lkeys, lrows, lsrc, lld,
+      gpu_rt::LaunchAfterDrain(SegmentSumKernel<4, kSegDepthUpper>, dim3(grid), dim3(threads), 0, stream, dst, ld_dst, lkeys, lrows, lsrc, lld,
                                                                         entries[l], width, len[l], pk, pr, pp, st, rt);
     } else if (long_chunks) {
-      SegmentSumKernel<1, kSegDepth><<<grid, threads, 0, stream>>>(dst, ld_dst, lkeys, lrows, lsrc, lld, entries[l],
+      gpu_rt::LaunchAfterDrain(SegmentSumKernel<1, kSegDepth>, dim3(grid), dim3(threads), 0, stream, dst, ld_dst, lkeys, lrows, lsrc, lld, entries[l],
                                                                    width, len[l], pk, pr, pp, st, rt);
     } else {
-      SegmentSumKernel<1, kSegDepthUpper><<<grid, threads, 0, stream>>>(dst, ld_dst, lkeys, lrows, lsrc, lld,
+      gpu_rt::LaunchAfterDrain(SegmentSumKernel<1, kSegDepthUpper>, dim3(grid), dim3(threads), 0, stream, dst, ld_dst, lkeys, lrows, lsrc, lld,
                                                                         entries[l], width, len[l], pk, pr, pp, st, rt);
     }
     MSHADOW_CUDA_POST_KERNEL_CHECK(SegmentSumKernel);

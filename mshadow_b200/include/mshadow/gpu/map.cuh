@@ -47,6 +47,7 @@ __global__ void __launch_bounds__(kMapThreads)
 MapPackKernel(DPlan dst, const SPlan src, uint32_t rows, uint32_t cols, uint32_t packs_per_row,
               gpu_rt::FastDiv row_of_pack) {
   constexpr int kLanes = expr::Pack<DType>::kLanes;
+  gpu_rt::GridDependencySync();
   const uint32_t total = rows * packs_per_row;
   const uint32_t step = gridDim.x * kMapThreads;
   for (uint32_t base = blockIdx.x * kMapThreads + threadIdx.x; base < total;
@@ -97,6 +98,7 @@ MapPackKernel(DPlan dst, const SPlan src, uint32_t rows, uint32_t cols, uint32_t
 template <typename Saver, typename DPlan, typename SPlan, typename DType>
 __global__ void __launch_bounds__(kMapThreads)
 MapScalarKernel(DPlan dst, const SPlan src, uint32_t rows, uint32_t cols, gpu_rt::FastDiv row_of_elem) {
+  gpu_rt::GridDependencySync();
   const uint32_t total = rows * cols;
   const uint32_t step = gridDim.x * kMapThreads;
   for (uint32_t base = blockIdx.x * kMapThreads + threadIdx.x; base < total;
@@ -154,8 +156,8 @@ inline void MapPlanPacked(DPlan dplan, const SPlan &splan, Shape<2> dshape, bool
   const uint32_t ppr = cols / kLanes;
   const int64_t work = static_cast<int64_t>(rows) * (ppr == 0 ? 1 : ppr);
   auto kernel = MapPackKernel<Saver, DPlan, SPlan, DType, kSrcPack>;
-  kernel<<<MapGridSize(work, kernel), kMapThreads, 0, stream>>>(dplan, splan, rows, cols, ppr,
-                                                                gpu_rt::FastDiv(ppr == 0 ? 1 : ppr));
+  gpu_rt::LaunchAfterDrain(kernel, dim3(MapGridSize(work, kernel)), dim3(kMapThreads), 0, stream, dplan, splan, rows,
+                           cols, ppr, gpu_rt::FastDiv(ppr == 0 ? 1 : ppr));
   MSHADOW_CUDA_POST_KERNEL_CHECK(MapPackKernel);
 }
 
@@ -166,9 +168,9 @@ inline void MapPlanScalar(DPlan dplan, const SPlan &splan, Shape<2> dshape, cuda
   if (count == 0) return;
   CHECK_LT(count, (int64_t(1) << 31)) << "MapExp: tensor too large for 32-bit indexing";
   auto kernel = MapScalarKernel<Saver, DPlan, SPlan, DType>;
-  kernel<<<MapGridSize(count, kernel), kMapThreads, 0, stream>>>(
-      dplan, splan, static_cast<uint32_t>(dshape[0]), static_cast<uint32_t>(dshape[1]),
-      gpu_rt::FastDiv(static_cast<uint32_t>(dshape[1])));
+  gpu_rt::LaunchAfterDrain(kernel, dim3(MapGridSize(count, kernel)), dim3(kMapThreads), 0, stream, dplan, splan,
+                           static_cast<uint32_t>(dshape[0]), static_cast<uint32_t>(dshape[1]),
+                           gpu_rt::FastDiv(static_cast<uint32_t>(dshape[1])));
   MSHADOW_CUDA_POST_KERNEL_CHECK(MapScalarKernel);
 }
 

@@ -81,6 +81,7 @@ __global__ void __launch_bounds__(kPoolThreads)
 PoolPlanesKernel(float *dst, const float *src, uint32_t planes, uint32_t h, uint32_t w, uint32_t ph, uint32_t pw,
                  PoolGeom g, int64_t ld_src, int64_t ld_dst, uint32_t gplanes, gpu_rt::FastDiv div_pw,
                  gpu_rt::FastDiv div_ph, gpu_rt::FastDiv div_pairs, int *status) {
+  gpu_rt::GridDependencySync();
   extern __shared__ __align__(16) float tile[];
   __shared__ uint64_t bar;
   const int ky = KY > 0 ? KY : g.ky, kx = KX > 0 ? KX : g.kx;
@@ -188,6 +189,7 @@ UnpoolPlanesKernel(float *dst, const float *src, const float *pooled, const floa
                    uint32_t h, uint32_t w, uint32_t ph, uint32_t pw, PoolGeom g, int64_t ld_src, int64_t ld_pooled,
                    int64_t ld_dst, uint32_t gplanes, gpu_rt::FastDiv div_w, gpu_rt::FastDiv div_h,
                    gpu_rt::FastDiv div_sy, gpu_rt::FastDiv div_sx, gpu_rt::FastDiv div_wq, int *status) {
+  gpu_rt::GridDependencySync();
   extern __shared__ __align__(16) float tile[];
   __shared__ uint64_t bar;
   const uint32_t ky = KY > 0 ? KY : g.ky, kx = KX > 0 ? KX : g.kx;
@@ -371,6 +373,7 @@ __global__ void __launch_bounds__(kPoolThreads)
 PoolBandsKernel(float *dst, const float *src, uint32_t planes, uint32_t h, uint32_t w, uint32_t ph, uint32_t pw,
                 PoolGeom g, int64_t ld_src, int64_t ld_dst, uint32_t band_rows, uint32_t bands,
                 gpu_rt::FastDiv div_bands, gpu_rt::FastDiv div_pw, gpu_rt::FastDiv div_pairs, int *status) {
+  gpu_rt::GridDependencySync();
   extern __shared__ __align__(16) float tile[];
   __shared__ uint64_t bar;
   const int ky = KY > 0 ? KY : g.ky, kx = KX > 0 ? KX : g.kx;
@@ -482,6 +485,7 @@ UnpoolBandsKernel(float *dst, const float *src, const float *pooled, const float
                   int64_t ld_dst, uint32_t band_rows, uint32_t bands, uint32_t pooled_rows_cap,
                   gpu_rt::FastDiv div_bands, gpu_rt::FastDiv div_w, gpu_rt::FastDiv div_wq, gpu_rt::FastDiv div_sy,
                   gpu_rt::FastDiv div_sx, int *status) {
+  gpu_rt::GridDependencySync();
   extern __shared__ __align__(16) float tile[];
   __shared__ uint64_t bar;
   const uint32_t ky = KY > 0 ? KY : g.ky, kx = KX > 0 ? KX : g.kx;
@@ -634,6 +638,7 @@ template <typename Reducer, int NSIZE, int kLanes>
 __global__ void __launch_bounds__(kPoolThreads, MSHADOW_B200_CHPOOL_MIN_CTAS)
 ChannelPoolKernel(float *dst, const float *src, uint32_t channels, uint32_t plane, uint32_t groups_per_image,
                   uint32_t total_items, gpu_rt::FastDiv image_of_item, uint32_t seg_len) {
+  gpu_rt::GridDependencySync();
   constexpr int kPad = NSIZE / 2;
   constexpr int kAhead = MSHADOW_B200_CHPOOL_AHEAD;  // loads issued this many channels before they are needed
   constexpr int kRing = NSIZE + kAhead;
@@ -718,6 +723,7 @@ __global__ void __launch_bounds__(kPoolThreads, 2)
 ChannelUnpoolKernel(float *dst, const float *src, const float *pooled, const float *gpooled, uint32_t channels,
                     uint32_t plane, uint32_t groups_per_image, uint32_t total_items, gpu_rt::FastDiv image_of_item,
                     uint32_t seg_len) {
+  gpu_rt::GridDependencySync();
   constexpr int kPad = NSIZE / 2;
   // loads are issued this many channels before they are needed (for red::sum PartialGrad is the
   // constant 1, so the compiler drops the source and pooled rings and only the gradient is read)
@@ -802,6 +808,7 @@ template <typename Reducer, int NSIZE>
 __global__ void __launch_bounds__(1024, 1)
 ChannelPoolStagedKernel(float *dst, const float *src, uint32_t channels, uint32_t plane, uint32_t tile_px,
                         uint32_t tiles_per_plane, uint32_t seg_len, uint32_t ring, int *status) {
+  gpu_rt::GridDependencySync();
   constexpr int kPad = NSIZE / 2;
   constexpr uint32_t kMaxRing = 16;
   extern __shared__ __align__(16) float slots[];
@@ -961,7 +968,7 @@ inline void PoolPlanesLaunch(float *dst, const float *src, int64_t planes, int64
     auto kernel = PoolPlanesKernel<Reducer, KY, KX, SY, SX>;                                                      \
     MSHADOW_CUDA_CALL(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,                   \
                                            static_cast<int>(kPoolSmemBudget)));                                   \
-    kernel<<<grid, kPoolThreads, smem, stream>>>(dst, src, static_cast<uint32_t>(planes), static_cast<uint32_t>(h), \
+    gpu_rt::LaunchAfterDrain(kernel, dim3(grid), dim3(kPoolThreads), smem, stream, dst, src, static_cast<uint32_t>(planes), static_cast<uint32_t>(h), \
                                                 static_cast<uint32_t>(w), ph, pw, g, ld_src, ld_dst, gp,          \
                                                 gpu_rt::FastDiv(pw), gpu_rt::FastDiv(ph),                         \
                                                 gpu_rt::FastDiv((pw + 1) / 2), status);                           \
@@ -995,7 +1002,7 @@ inline void UnpoolPlanesLaunch(float *dst, const float *src, const float *pooled
     auto kernel = UnpoolPlanesKernel<Reducer, KY, KX, SY, SX>;                                                    \
     MSHADOW_CUDA_CALL(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,                   \
                                            static_cast<int>(kUnpoolSmemBudget)));                                 \
-    kernel<<<grid, kPoolThreads, smem, stream>>>(                                                                 \
+    gpu_rt::LaunchAfterDrain(kernel, dim3(grid), dim3(kPoolThreads), smem, stream,                                                                  \
         dst, src, pooled, gpooled, static_cast<uint32_t>(planes), static_cast<uint32_t>(h),                       \
         static_cast<uint32_t>(w), static_cast<uint32_t>(ph), static_cast<uint32_t>(pw), g, ld_src, ld_pooled,     \
         ld_dst, gp, gpu_rt::FastDiv(static_cast<uint32_t>(w)), gpu_rt::FastDiv(static_cast<uint32_t>(h)),         \
@@ -1077,7 +1084,7 @@ inline void PoolBandsLaunch(float *dst, const float *src, int64_t planes, int64_
     auto kernel = PoolBandsKernel<Reducer, KY, KX, SY, SX>;                                                       \
     MSHADOW_CUDA_CALL(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,                   \
                                            MSHADOW_B200_POOL_BAND_SMEM_KB * 1024));                               \
-    kernel<<<grid, kPoolThreads, bp.smem, stream>>>(dst, src, static_cast<uint32_t>(planes),                     \
+    gpu_rt::LaunchAfterDrain(kernel, dim3(grid), dim3(kPoolThreads), bp.smem, stream, dst, src, static_cast<uint32_t>(planes),                     \
                                                    static_cast<uint32_t>(h), static_cast<uint32_t>(w), ph, pw, g, \
                                                    ld_src, ld_dst, bp.band_rows, bp.bands,                        \
                                                    gpu_rt::FastDiv(bp.bands), gpu_rt::FastDiv(pw),                \
@@ -1108,7 +1115,7 @@ inline void UnpoolBandsLaunch(float *dst, const float *src, const float *pooled,
     auto kernel = UnpoolBandsKernel<Reducer, KY, KX, SY, SX>;                                                     \
     MSHADOW_CUDA_CALL(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,                   \
                                            static_cast<int>(kUnpoolSmemBudget)));                                 \
-    kernel<<<grid, kPoolThreads, bp.smem, stream>>>(                                                              \
+    gpu_rt::LaunchAfterDrain(kernel, dim3(grid), dim3(kPoolThreads), bp.smem, stream,                                                               \
         dst, src, pooled, gpooled, static_cast<uint32_t>(planes), static_cast<uint32_t>(h), uw,                   \
         static_cast<uint32_t>(ph), static_cast<uint32_t>(pw), g, ld_src, ld_pooled, ld_dst, bp.band_rows,         \
         bp.bands, bp.pooled_rows, gpu_rt::FastDiv(bp.bands), gpu_rt::FastDiv(uw),                                 \
@@ -1154,7 +1161,7 @@ inline void ChannelPoolLaunch(float *dst, const float *src, int64_t n, int64_t c
     const uint32_t segs = pooldetail::WaveFriendlySegments(tiles, max_seg, slots);                            \
     const uint32_t seg_len = (static_cast<uint32_t>(c) + segs - 1) / segs;                                     \
     const uint32_t nseg = (static_cast<uint32_t>(c) + seg_len - 1) / seg_len;                                  \
-    kernel<<<dim3(tiles, nseg), kPoolThreads, 0, stream>>>(dst, src, static_cast<uint32_t>(c), plane, groups,  \
+    gpu_rt::LaunchAfterDrain(kernel, dim3(tiles, nseg), dim3(kPoolThreads), 0, stream, dst, src, static_cast<uint32_t>(c), plane, groups,  \
                                                             items, gpu_rt::FastDiv(groups), seg_len);          \
   }
   // staged variant: planes (or plane tiles of at most 3968 pixels: 31 consumer warps of 128 pixels and one
@@ -1191,7 +1198,7 @@ inline void ChannelPoolLaunch(float *dst, const float *src, int64_t n, int64_t c
     }                                                                                                          \
     const uint32_t seg_len = (static_cast<uint32_t>(c) + segs - 1) / segs;                                     \
     const uint32_t nseg = (static_cast<uint32_t>(c) + seg_len - 1) / seg_len;                                  \
-    kernel<<<dim3(fixed, nseg), st_threads, smem, stream>>>(dst, src, static_cast<uint32_t>(c), plane, tile_px, \
+    gpu_rt::LaunchAfterDrain(kernel, dim3(fixed, nseg), dim3(st_threads), smem, stream, dst, src, static_cast<uint32_t>(c), plane, tile_px, \
                                                              tiles_per_plane, seg_len, ring,                   \
                                                              gpu_rt::StatusWord());                            \
   }
@@ -1242,7 +1249,7 @@ inline void ChannelUnpoolLaunch(float *dst, const float *src, const float *poole
     const uint32_t segs = pooldetail::WaveFriendlySegments(tiles, max_seg, slots);                            \
     const uint32_t seg_len = (static_cast<uint32_t>(c) + segs - 1) / segs;                                     \
     const uint32_t nseg = (static_cast<uint32_t>(c) + seg_len - 1) / seg_len;                                  \
-    kernel<<<dim3(tiles, nseg), kPoolThreads, 0, stream>>>(dst, src, pooled, gpooled, static_cast<uint32_t>(c), \
+    gpu_rt::LaunchAfterDrain(kernel, dim3(tiles, nseg), dim3(kPoolThreads), 0, stream, dst, src, pooled, gpooled, static_cast<uint32_t>(c), \
                                                             plane, groups, items, gpu_rt::FastDiv(groups),     \
                                                             seg_len);                                          \
   }

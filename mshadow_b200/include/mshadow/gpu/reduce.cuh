@@ -126,6 +126,7 @@ template <typename Saver, typename Reducer, int kLanes, typename DType, typename
 __global__ void __launch_bounds__(kRedLowThreads)
 ReduceKeepLowestKernel(DPlan dst, const SPlan src, uint32_t rows, uint32_t cols, uint32_t rows_per_chunk,
                        DType scale, DType *partial, const gpu_rt::PeerSink sink) {
+  gpu_rt::GridDependencySync();
   __shared__ __align__(16) DType stage[kRedLowThreads * kLanes];
   cg::cluster_group cluster = cg::this_cluster();
   const uint32_t x = (blockIdx.x * kRedLowThreads + threadIdx.x) * kLanes;
@@ -205,6 +206,7 @@ ReduceKeepLowestKernel(DPlan dst, const SPlan src, uint32_t rows, uint32_t cols,
 template <typename Saver, typename Reducer, typename DType, typename DPlan>
 __global__ void ReduceFinishKernel(DPlan dst, const DType *partial, uint32_t nparts, uint32_t cols, DType scale,
                                    const gpu_rt::PeerSink sink) {
+  gpu_rt::GridDependencySync();
   const uint32_t x = blockIdx.x * blockDim.x + threadIdx.x;
   if (x >= cols) return;
   const DType sum = reddetail::FoldParked<Reducer>(partial + x, cols, nparts);
@@ -222,6 +224,7 @@ __global__ void __launch_bounds__(kRedHighThreads)
 ReduceKeepHighDimKernel(DPlan dst, const SPlan src, uint32_t outer, uint32_t channels, uint32_t inner_rows,
                         uint32_t packs_per_row, gpu_rt::FastDiv row_of_pack, gpu_rt::FastDiv plane_of_pack,
                         uint32_t outer_per_chunk, DType scale, DType *partial, const gpu_rt::PeerSink sink) {
+  gpu_rt::GridDependencySync();
   __shared__ DType warp_buf[kRedHighThreads / 32];
   __shared__ DType cta_val;
   cg::cluster_group cluster = cg::this_cluster();
@@ -295,13 +298,16 @@ inline void LaunchClustered(Kernel kernel, dim3 grid, dim3 block, unsigned clust
   cfg.blockDim = block;
   cfg.dynamicSmemBytes = 0;
   cfg.stream = stream;
-  cudaLaunchAttribute attr[1];
+  cudaLaunchAttribute attr[2];
   attr[0].id = cudaLaunchAttributeClusterDimension;
   attr[0].val.clusterDim.x = 1;
   attr[0].val.clusterDim.y = cluster_y;
   attr[0].val.clusterDim.z = 1;
+  // the kernels begin with GridDependencySync(): see gpu_rt::LaunchAfterDrain
+  attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[1].val.programmaticStreamSerializationAllowed = MSHADOW_B200_EARLY_LAUNCH ? 1 : 0;
   cfg.attrs = attr;
-  cfg.numAttrs = 1;
+  cfg.numAttrs = 2;
   MSHADOW_CUDA_CALL(cudaLaunchKernelEx(&cfg, kernel, args...));
 }
 
@@ -488,8 +494,8 @@ inline void ReduceKeepLowestLaunch(DPlan dplan, const SPlan &splan, Shape<2> esh
                              dplan, splan, rows, cols, sp.per_chunk, scale, partial, partial == nullptr ? sink : none);
   MSHADOW_CUDA_POST_KERNEL_CHECK(ReduceKeepLowestKernel);
   if (partial != nullptr) {
-    ReduceFinishKernel<Saver, Reducer, DType, DPlan>
-        <<<gpu_rt::CeilDiv(cols, 256), 256, 0, stream>>>(dplan, partial, sp.clusters, cols, scale, sink);
+    gpu_rt::LaunchAfterDrain(ReduceFinishKernel<Saver, Reducer, DType, DPlan>, dim3(gpu_rt::CeilDiv(cols, 256)), dim3(256),
+                             0, stream, dplan, partial, sp.clusters, cols, scale, sink);
     MSHADOW_CUDA_POST_KERNEL_CHECK(ReduceFinishKernel);
   }
 }
@@ -519,8 +525,8 @@ inline void ReduceKeepHighDimLaunch(DPlan dplan, const SPlan &splan, Shape<4> ps
                              partial == nullptr ? sink : none);
   MSHADOW_CUDA_POST_KERNEL_CHECK(ReduceKeepHighDimKernel);
   if (partial != nullptr) {
-    ReduceFinishKernel<Saver, Reducer, DType, DPlan>
-        <<<gpu_rt::CeilDiv(channels, 256), 256, 0, stream>>>(dplan, partial, sp.clusters, channels, scale, sink);
+    gpu_rt::LaunchAfterDrain(ReduceFinishKernel<Saver, Reducer, DType, DPlan>, dim3(gpu_rt::CeilDiv(channels, 256)),
+                             dim3(256), 0, stream, dplan, partial, sp.clusters, channels, scale, sink);
     MSHADOW_CUDA_POST_KERNEL_CHECK(ReduceFinishKernel);
   }
 }

@@ -42,6 +42,44 @@ inline std::atomic<long long> &LaunchCounter() {
   }
 
 namespace mshadow {
+namespace gpu_rt {
+#ifdef __CUDACC__
+/*!
+ * \brief launch of a kernel that begins with GridDependencySync(): when the operation before it
+ *  in the stream is a kernel, its CTAs may be placed on the SMs while that kernel drains, run up
+ *  to GridDependencySync() and wait there until it has completed and its memory is visible.  The
+ *  launch gap between the two kernels (a few microseconds, a fifth of the time of a kernel that
+ *  processes an eighth of a benchmark tensor) overlaps the tail of the first.  Only kernels that
+ *  call GridDependencySync() before their first access to global memory may be launched this way.
+ */
+template <typename... KArgs, typename... Args>
+inline void LaunchAfterDrain(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                             Args... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = MSHADOW_B200_EARLY_LAUNCH ? 1 : 0;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  MSHADOW_CUDA_CALL(cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...));
+}
+
+/*! \brief lets the next kernel of the stream be placed early, then waits for the previous one: first statements of a kernel launched with LaunchAfterDrain */
+__device__ __forceinline__ void GridDependencySync() {
+#if MSHADOW_B200_EARLY_LAUNCH
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+#endif
+}
+#endif  // __CUDACC__
+}  // namespace gpu_rt
+}  // namespace mshadow
+
+namespace mshadow {
 
 /*! \brief execution queue of a CUDA device */
 template <>

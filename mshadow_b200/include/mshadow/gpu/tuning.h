@@ -6,6 +6,9 @@
 #ifndef MSHADOW_GPU_TUNING_H_
 #define MSHADOW_GPU_TUNING_H_
 
+#ifndef MSHADOW_B200_EARLY_LAUNCH
+#define MSHADOW_B200_EARLY_LAUNCH 1  // programmatic dependent launch for the kernels that support it
+#endif
 #ifndef MSHADOW_B200_MAP_THREADS
 #define MSHADOW_B200_MAP_THREADS 256  // threads per CTA of the element-wise kernels
 #endif
