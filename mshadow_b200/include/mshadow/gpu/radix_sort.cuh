@@ -76,6 +76,7 @@ template <typename K>
 __global__ void __launch_bounds__(kThreads)
 RadixCountKernel(const K *keys, uint32_t n, int shift, uint32_t mask, bool ascend, Source src, uint32_t *counts,
                  uint32_t tiles) {
+  gpu_rt::GridDependencySync();
   extern __shared__ uint32_t hist[];
   for (uint32_t d = threadIdx.x; d <= mask; d += kThreads) hist[d] = 0;
   __syncthreads();
@@ -106,6 +107,7 @@ RadixCountKernel(const K *keys, uint32_t n, int shift, uint32_t mask, bool ascen
 template <int kWarps>  // a template only so that the header can be included from several translation units
 __global__ void __launch_bounds__(kWarps * 32) RadixScanKernel(uint32_t *counts, uint32_t *total, uint32_t digits,
                                                                 uint32_t tiles) {
+  gpu_rt::GridDependencySync();
   const uint32_t lane = threadIdx.x & 31;
   const uint32_t d = blockIdx.x * kWarps + (threadIdx.x >> 5);
   if (d >= digits) return;
@@ -142,6 +144,7 @@ template <typename K, typename V>
 __global__ void __launch_bounds__(kThreads)
 RadixScatterKernel(const K *keys_in, const V *vals_in, K *keys_out, V *vals_out, uint32_t n, int shift, uint32_t mask,
                    bool ascend, Source src, const uint32_t *counts, const uint32_t *total, uint32_t tiles) {
+  gpu_rt::GridDependencySync();
   extern __shared__ uint32_t warp_count[];  // [16][digits], then digit_base[digits]
   __shared__ uint32_t warp_sum[16];
   const uint32_t digits = mask + 1;
@@ -259,11 +262,11 @@ inline void SortPairs(K *keys, V *vals, const K *raw, int64_t n, int bits, bool 
     if (width < 1) width = 1;  // a pass over no remaining bits still moves the data to the other buffer
     const uint32_t mask = (1u << width) - 1u;
     const uint32_t digits = mask + 1;
-    RadixCountKernel<K><<<tiles, kThreads, digits * 4, stream>>>(kin, un, shift, mask, ascend, from, counts, tiles);
+    gpu_rt::LaunchAfterDrain(RadixCountKernel<K>, dim3(tiles), dim3(kThreads), digits * 4, stream, kin, un, shift, mask, ascend, from, counts, tiles);
     MSHADOW_CUDA_POST_KERNEL_CHECK(RadixCountKernel);
-    RadixScanKernel<8><<<(digits + 7) / 8, 256, 0, stream>>>(counts, totals, digits, tiles);
+    gpu_rt::LaunchAfterDrain(RadixScanKernel<8>, dim3((digits + 7) / 8), dim3(256), 0, stream, counts, totals, digits, tiles);
     MSHADOW_CUDA_POST_KERNEL_CHECK(RadixScanKernel);
-    RadixScatterKernel<K, V><<<tiles, kThreads, 17 * digits * 4, stream>>>(kin, vin, kout, vout, un, shift, mask,
+    gpu_rt::LaunchAfterDrain(RadixScatterKernel<K, V>, dim3(tiles), dim3(kThreads), 17 * digits * 4, stream, kin, vin, kout, vout, un, shift, mask,
                                                                            ascend, from, counts, totals, tiles);
     MSHADOW_CUDA_POST_KERNEL_CHECK(RadixScatterKernel);
     // the next pass reads what this one wrote; only the first pass clips and generates

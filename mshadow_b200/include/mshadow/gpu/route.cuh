@@ -136,6 +136,7 @@ __device__ __forceinline__ uint32_t CtaExclusiveScan(uint32_t v, uint32_t *s_war
 template <int kDummy>
 __global__ void __launch_bounds__(256)
 RunLengthKernel(int32_t *lens, int32_t *rows, const int32_t *keys, uint32_t n) {
+  gpu_rt::GridDependencySync();
   const uint32_t i = blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= n) return;
   const int32_t k = keys[i];
@@ -167,6 +168,7 @@ template <int kDummy>
 __global__ void __launch_bounds__(routedetail::kThreads)
 RouteCountKernel(uint32_t *counts, const int32_t *keys, const int32_t *rows, uint32_t n, const int32_t *hot,
                  const routedetail::Geometry g) {
+  gpu_rt::GridDependencySync();
   using namespace routedetail;
   __shared__ int32_t s_hot[kMaxHot];
   __shared__ uint32_t s_warp[kThreads / 32];
@@ -195,6 +197,7 @@ RouteCountKernel(uint32_t *counts, const int32_t *keys, const int32_t *rows, uin
 template <int kDummy>
 __global__ void __launch_bounds__(routedetail::kThreads)
 RouteScanKernel(uint32_t *counts, uint32_t tiles, uint32_t *totals) {
+  gpu_rt::GridDependencySync();
   using namespace routedetail;
   __shared__ uint32_t s_warp[kThreads / 32];
   for (int part = 0; part < 2; ++part) {
@@ -218,6 +221,7 @@ __global__ void __launch_bounds__(routedetail::kThreads)
 RouteScatterKernel(int32_t *out_keys, int32_t *out_rows, const uint32_t *bases, const uint32_t *totals,
                    const int32_t *keys, const int32_t *rows, uint32_t n, const int32_t *hot,
                    const routedetail::Geometry g) {
+  gpu_rt::GridDependencySync();
   using namespace routedetail;
   __shared__ int32_t s_hot[kMaxHot];
   __shared__ uint32_t s_warp[kThreads / 32];
@@ -261,6 +265,7 @@ RouteScatterKernel(int32_t *out_keys, int32_t *out_rows, const uint32_t *bases, 
 template <int kDummy>
 __global__ void __launch_bounds__(routedetail::kThreads)
 RunHeadCountKernel(uint32_t *counts, const int32_t *keys, uint32_t n) {
+  gpu_rt::GridDependencySync();
   using namespace routedetail;
   __shared__ uint32_t s_warp[kThreads / 32];
   const uint32_t first = blockIdx.x * kTile + threadIdx.x * kItems;
@@ -279,6 +284,7 @@ RunHeadCountKernel(uint32_t *counts, const int32_t *keys, uint32_t n) {
 template <int kDummy>
 __global__ void __launch_bounds__(routedetail::kThreads)
 RunHeadScanKernel(uint32_t *counts, uint32_t tiles, uint32_t *total_out) {
+  gpu_rt::GridDependencySync();
   using namespace routedetail;
   __shared__ uint32_t s_warp[kThreads / 32];
   uint32_t running = 0;
@@ -297,6 +303,7 @@ RunHeadScanKernel(uint32_t *counts, uint32_t tiles, uint32_t *total_out) {
 template <int kDummy>
 __global__ void __launch_bounds__(routedetail::kThreads)
 RunIndexKernel(int32_t *run_of, int32_t *run_keys, const uint32_t *bases, const int32_t *keys, uint32_t n) {
+  gpu_rt::GridDependencySync();
   using namespace routedetail;
   __shared__ uint32_t s_warp[kThreads / 32];
   const uint32_t first = blockIdx.x * kTile + threadIdx.x * kItems;
@@ -336,6 +343,7 @@ RunIndexKernel(int32_t *run_of, int32_t *run_keys, const uint32_t *bases, const 
 template <int kDummy>
 __global__ void RunBoundsKernel(int32_t *first, const int32_t *run_keys, const uint32_t *total, int world,
                                 int32_t per_owner) {
+  gpu_rt::GridDependencySync();
   const int q = threadIdx.x;
   if (q > world) return;
   const uint32_t runs = total[0];
@@ -352,6 +360,7 @@ __global__ void RunBoundsKernel(int32_t *first, const int32_t *run_keys, const u
 template <int kDummy>
 __global__ void __launch_bounds__(256)
 RunKeysToOwnersKernel(const routedetail::OwnerBlocks<int32_t> to, const int32_t *run_keys, int32_t per_owner) {
+  gpu_rt::GridDependencySync();
   const int32_t runs = to.first[to.world];
   for (int32_t j = blockIdx.x * blockDim.x + threadIdx.x; j < runs; j += gridDim.x * blockDim.x) {
     const int q = routedetail::OwnerOf(to.first, to.world, j);
@@ -386,11 +395,11 @@ inline void RouteCyclicHotLaunch(int32_t *out_keys, int32_t *out_rows, uint32_t 
   uint32_t *counts = static_cast<uint32_t *>(gpu_rt::Scratch::Get(stream, RouteScratchBytes(n)));
   const Geometry g = {world, rank, src_begin, src_end, hot_count, hot_base};
   const uint32_t un = static_cast<uint32_t>(n);
-  RouteCountKernel<0><<<tiles, kThreads, 0, stream>>>(counts, keys, rows, un, hot, g);
+  gpu_rt::LaunchAfterDrain(RouteCountKernel<0>, dim3(tiles), dim3(kThreads), 0, stream, counts, keys, rows, un, hot, g);
   MSHADOW_CUDA_POST_KERNEL_CHECK(RouteCountKernel);
-  RouteScanKernel<0><<<1, kThreads, 0, stream>>>(counts, tiles, totals);
+  gpu_rt::LaunchAfterDrain(RouteScanKernel<0>, dim3(1), dim3(kThreads), 0, stream, counts, tiles, totals);
   MSHADOW_CUDA_POST_KERNEL_CHECK(RouteScanKernel);
-  RouteScatterKernel<0><<<tiles, kThreads, 0, stream>>>(out_keys, out_rows, counts, totals, keys, rows, un, hot, g);
+  gpu_rt::LaunchAfterDrain(RouteScatterKernel<0>, dim3(tiles), dim3(kThreads), 0, stream, out_keys, out_rows, counts, totals, keys, rows, un, hot, g);
   MSHADOW_CUDA_POST_KERNEL_CHECK(RouteScatterKernel);
 }
 
@@ -411,11 +420,11 @@ inline void RunIndexLaunch(int32_t *run_of, int32_t *run_keys, uint32_t *total, 
   const uint32_t tiles = Tiles(n);
   uint32_t *counts = static_cast<uint32_t *>(gpu_rt::Scratch::Get(stream, RouteScratchBytes(n)));
   const uint32_t un = static_cast<uint32_t>(n);
-  RunHeadCountKernel<0><<<tiles, kThreads, 0, stream>>>(counts, keys, un);
+  gpu_rt::LaunchAfterDrain(RunHeadCountKernel<0>, dim3(tiles), dim3(kThreads), 0, stream, counts, keys, un);
   MSHADOW_CUDA_POST_KERNEL_CHECK(RunHeadCountKernel);
-  RunHeadScanKernel<0><<<1, kThreads, 0, stream>>>(counts, tiles, total);
+  gpu_rt::LaunchAfterDrain(RunHeadScanKernel<0>, dim3(1), dim3(kThreads), 0, stream, counts, tiles, total);
   MSHADOW_CUDA_POST_KERNEL_CHECK(RunHeadScanKernel);
-  RunIndexKernel<0><<<tiles, kThreads, 0, stream>>>(run_of, run_keys, counts, keys, un);
+  gpu_rt::LaunchAfterDrain(RunIndexKernel<0>, dim3(tiles), dim3(kThreads), 0, stream, run_of, run_keys, counts, keys, un);
   MSHADOW_CUDA_POST_KERNEL_CHECK(RunIndexKernel);
 }
 
@@ -423,7 +432,7 @@ inline void RunIndexLaunch(int32_t *run_of, int32_t *run_keys, uint32_t *total, 
 inline void RunBoundsLaunch(int32_t *first, const int32_t *run_keys, const uint32_t *total, int world,
                             int32_t per_owner, cudaStream_t stream) {
   CHECK(world >= 1 && world <= routedetail::kMaxOwners) << "RunBounds: at most " << routedetail::kMaxOwners << " owners";
-  RunBoundsKernel<0><<<1, 32, 0, stream>>>(first, run_keys, total, world, per_owner);
+  gpu_rt::LaunchAfterDrain(RunBoundsKernel<0>, dim3(1), dim3(32), 0, stream, first, run_keys, total, world, per_owner);
   MSHADOW_CUDA_POST_KERNEL_CHECK(RunBoundsKernel);
 }
 
@@ -433,7 +442,7 @@ inline void RunKeysToOwnersLaunch(const routedetail::OwnerBlocks<int32_t> &to, c
   if (n == 0) return;
   unsigned grid = gpu_rt::CeilDiv(static_cast<uint32_t>(n), 256u);
   if (grid > 1184u) grid = 1184u;
-  RunKeysToOwnersKernel<0><<<grid, 256, 0, stream>>>(to, run_keys, per_owner);
+  gpu_rt::LaunchAfterDrain(RunKeysToOwnersKernel<0>, dim3(grid), dim3(256), 0, stream, to, run_keys, per_owner);
   MSHADOW_CUDA_POST_KERNEL_CHECK(RunKeysToOwnersKernel);
 }
 
@@ -441,7 +450,7 @@ inline void RunKeysToOwnersLaunch(const routedetail::OwnerBlocks<int32_t> &to, c
 inline void RunLengthLaunch(int32_t *lens, int32_t *rows, const int32_t *keys, int64_t n, cudaStream_t stream) {
   if (n == 0) return;
   CHECK_LT(n, (int64_t(1) << 31));
-  RunLengthKernel<0><<<gpu_rt::CeilDiv(static_cast<uint32_t>(n), 256u), 256, 0, stream>>>(lens, rows, keys,
+  gpu_rt::LaunchAfterDrain(RunLengthKernel<0>, dim3(gpu_rt::CeilDiv(static_cast<uint32_t>(n), 256u)), dim3(256), 0, stream, lens, rows, keys,
                                                                                         static_cast<uint32_t>(n));
   MSHADOW_CUDA_POST_KERNEL_CHECK(RunLengthKernel);
 }
