@@ -11,6 +11,7 @@ import ctypes as C
 import os
 import time
 
+import numpy as np
 import pytest
 
 from mshadow_b200 import ps
@@ -225,6 +226,36 @@ def test_peer_model_alone_on_one_gpu_runs_its_kernels_and_slot_rotation():
 
 
 @pytest.mark.gpu
+def test_peer_model_raw_regions():
+    """Regions of the window for the caller's own kernels: offsets follow the keys, are 256-byte
+    aligned and reproducible; addresses are base + offset; a region beyond the window is refused."""
+    if not torch.cuda.is_available():
+        pytest.skip("no CUDA device")
+    m = ps.PeerModel(rank=0, world=1, device=0, window_bytes=1 << 20)
+    try:
+        m.init_key(0, (100,))
+        a = m.reserve(1000)
+        b = m.reserve(4096)
+        assert a % 256 == 0 and b % 256 == 0 and b >= a + 1000
+        base = m.window(0, 0)
+        assert m.window(0, a) == base + a and m.window(0, b) == base + b
+        x = torch.arange(256, dtype=torch.float32, device="cuda")
+        import mshadow_b200
+        lib = mshadow_b200.load()
+        lib.init(0)
+        lib.copy_2d(m.window(0, b), 256, x, 256, 1, 256, mshadow_b200.capi.D2D)
+        y = torch.zeros(256, device="cuda")
+        lib.copy_2d(y, 256, m.window(0, b), 256, 1, 256, mshadow_b200.capi.D2D)
+        assert torch.equal(x, y)
+        with pytest.raises(ps.PsError):
+            m.reserve(2 << 20)
+        with pytest.raises(ps.PsError):
+            m.window(1, 0)
+    finally:
+        m.close()
+
+
+@pytest.mark.gpu
 def test_peer_model_pull_gives_up_when_a_peer_never_answers():
     """A group of two whose second member does not exist: both handles name this rank's window, so
     the flag of rank 1 is never set.  The pull kernel polls for the configured 30 ms, leaves the
@@ -336,6 +367,53 @@ def _peer_worker(rank, world, tmp):
             lib.reduce_keep_lowest(other, data(r, 200 + s, (9000, 4608)).cuda())
             parts.append(other.cpu().numpy())
         ok = ok and torch.equal(got.cpu(), torch.from_numpy(sharding.rank_order_sum(parts)))
+    # raw regions: every rank's segmented sum stores the sums of its runs straight into the owner's
+    # window (row t of the table lives on rank t % world), the row numbers beside them, and a small
+    # key pushed afterwards carries the counts and tells the owner that the rows have arrived
+    table_rows, d, n_loc = 500, 64, 3000
+    kp = (table_rows + world - 1) // world
+    m.init_key(2, (world * world,))
+    off_rows, off_keys = m.reserve(world * kp * d * 4), m.reserve(world * kp * 4)
+
+    def batch(r):
+        rng = np.random.default_rng(77 + r)
+        p = (np.arange(table_rows) + 1.0) ** -1.1
+        return (rng.choice(table_rows, size=n_loc, p=p / p.sum()).astype(np.int32),
+                rng.standard_normal((n_loc, d)).astype(np.float32))
+
+    idx, src = batch(rank)
+    ck = torch.from_numpy(((idx % world) * kp + idx // world).astype(np.int32)).cuda()
+    pos = torch.arange(n_loc, dtype=torch.int32, device="cuda")
+    lib.sort_by_key(ck, pos, bits=int(world * kp - 1).bit_length())
+    run_of, run_keys = torch.empty_like(pos), torch.empty_like(pos)
+    total = torch.zeros(1, dtype=torch.int32, device="cuda")
+    first = torch.zeros(world + 1, dtype=torch.int32, device="cuda")
+    lib.run_index(run_of, run_keys, total, ck)
+    lib.run_bounds(first, run_keys, total, world, kp)
+    lib.take_sum_to_owners([m.window(q, off_rows) + rank * kp * d * 4 for q in range(world)], first, run_of, pos,
+                           torch.from_numpy(src).cuda(), world)
+    lib.run_keys_to_owners([m.window(q, off_keys) + rank * kp * 4 for q in range(world)], first, run_keys, world, kp)
+    counts_mine = torch.zeros(world * world, device="cuda")
+    counts_mine[rank * world:(rank + 1) * world] = (first[1:] - first[:-1]).float()
+    counts = torch.zeros(world * world, device="cuda")
+    m.push(counts_mine, 2)
+    m.pull_req(counts, 2)
+    m.pull_wait(2)
+    got_counts = counts.view(world, world)[:, rank].cpu().numpy().astype(np.int64)
+    rows_in = torch.empty(world * kp, d, device="cuda")
+    keys_in = torch.empty(world * kp, dtype=torch.int32, device="cuda")
+    lib.copy_2d(rows_in, d, m.window(rank, off_rows), d, world * kp, d, mshadow_b200.capi.D2D)
+    lib.copy_2d(keys_in, world * kp, m.window(rank, off_keys), world * kp, 1, world * kp, mshadow_b200.capi.D2D)
+    rows_in, keys_in = rows_in.cpu().numpy(), keys_in.cpu().numpy()
+    for r in range(world):
+        ridx, rsrc = batch(r)
+        to_me = np.unique(ridx[ridx % world == rank])
+        ok = ok and int(got_counts[r]) == to_me.size
+        ok = ok and np.array_equal(keys_in[r * kp:r * kp + to_me.size], (to_me // world).astype(np.int32))
+        for j, t in enumerate(to_me):
+            want_row = rsrc[ridx == t].astype(np.float64).sum(axis=0)
+            err = np.abs(rows_in[r * kp + j] - want_row).max() / max(1e-30, np.abs(want_row).max())
+            ok = ok and err <= 1e-5
     w = torch.full((64, 1024), float(rank + 5), device="cuda")
     m.set_weight(w, 1)
     ok = ok and bool((w == 5.0).all())
