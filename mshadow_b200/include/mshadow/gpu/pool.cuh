@@ -903,6 +903,122 @@ ChannelPoolStagedKernel(float *dst, const float *src, uint32_t channels, uint32_
   }
 }
 
+/*!
+ * \brief backward pass of channel-window pooling for reducers whose gradient depends on the values
+ *  (maximum, minimum), with the planes staged through shared memory like ChannelPoolStagedKernel.
+ *  A ring slot holds the three planes of one channel (source, pooled, pooled gradient; the source
+ *  plane is left out for the halo channels of a segment).  Consumers keep the last NSIZE pooled
+ *  values and gradients of their four pixels in registers; the source value of the output channel,
+ *  loaded NSIZE / 2 steps earlier, is read from its slot, which is released that much later.
+ *  Arithmetic as in ChannelUnpoolKernel: val = 0, then val += PartialGrad(src, pooled) * gradient
+ *  over the window in ascending channel order, product and sum rounded one by one.
+ *  CTA = (image, pixel tile of at most kChUnpoolTilePx pixels) x channel segment; block = tile / 4
+ *  consumer threads + one producer warp; dynamic shared memory ring * 3 * tile_px floats.
+ */
+const uint32_t kChUnpoolTilePx = 3200;                       // 800 consumer threads: 78 registers each
+const int kChUnpoolMaxThreads = kChUnpoolTilePx / 4 + 32;
+
+template <typename Reducer, int NSIZE>
+__global__ void __launch_bounds__(kChUnpoolMaxThreads, 1)
+ChannelUnpoolStagedKernel(float *dst, const float *src, const float *pooled, const float *gpooled, uint32_t channels,
+                          uint32_t plane, uint32_t tile_px, uint32_t tiles_per_plane, uint32_t seg_len, uint32_t ring,
+                          int *status) {
+  gpu_rt::GridDependencySync();
+  constexpr int kPad = NSIZE / 2;
+  constexpr uint32_t kMaxRing = 16;
+  extern __shared__ __align__(16) float slots[];
+  __shared__ uint64_t full[kMaxRing], empty[kMaxRing];
+  const uint32_t image_idx = blockIdx.x / tiles_per_plane;
+  const uint32_t px0 = (blockIdx.x - image_idx * tiles_per_plane) * tile_px;
+  const uint32_t len = min(tile_px, plane - px0);
+  const uint32_t c_begin = blockIdx.y * seg_len;
+  const uint32_t c_end = min(channels, c_begin + seg_len);
+  const int64_t base = static_cast<int64_t>(image_idx) * channels * plane + px0;
+  const uint32_t nsteps = (c_end - c_begin) + 2 * kPad;
+  const uint32_t consumer_warps = (blockDim.x >> 5) - 1;
+  const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const size_t slot_floats = static_cast<size_t>(3) * tile_px;
+  if (threadIdx.x == 0) {
+    for (uint32_t j = 0; j < ring; ++j) {
+      tma::BarrierInit(&full[j], 1);
+      tma::BarrierInit(&empty[j], consumer_warps);
+    }
+  }
+  __syncthreads();
+  if (warp == consumer_warps) {
+    if (lane != 0) return;
+    for (uint32_t s = 0; s < nsteps; ++s) {
+      const uint32_t slot = s % ring, use = s / ring;
+      if (use > 0 && !tma::WaitBounded(&empty[slot], (use - 1) & 1u)) {
+        atomicExch(status, tma::kStatusBulkCopyTimeout);
+        return;
+      }
+      const int64_t ch = static_cast<int64_t>(c_begin) - kPad + s;
+      if (ch >= 0 && ch < static_cast<int64_t>(channels)) {
+        float *at = slots + slot * slot_floats;
+        const int64_t from = base + ch * plane;
+        // the source plane is needed only where this segment produces an output
+        const bool own = ch >= static_cast<int64_t>(c_begin) && ch < static_cast<int64_t>(c_end);
+        tma::BarrierExpect(&full[slot], (own ? 3u : 2u) * len * 4u);
+        if (own) tma::BulkLoad(at, src + from, len * 4u, &full[slot]);
+        tma::BulkLoad(at + tile_px, pooled + from, len * 4u, &full[slot]);
+        tma::BulkLoad(at + 2 * tile_px, gpooled + from, len * 4u, &full[slot]);
+      } else {
+        tma::BarrierArrive(&full[slot]);
+      }
+    }
+    return;
+  }
+  const bool mine = threadIdx.x * 4 < len;
+  float wp[NSIZE][4], wg[NSIZE][4];
+#pragma unroll
+  for (int j = 0; j < NSIZE; ++j) {
+#pragma unroll
+    for (int l = 0; l < 4; ++l) wp[j][l] = 0.0f, wg[j][l] = 0.0f;
+  }
+  for (uint32_t s0 = 0; s0 < nsteps; s0 += NSIZE) {
+#pragma unroll
+    for (int j = 0; j < NSIZE; ++j) {
+      const uint32_t s = s0 + j;
+      if (s < nsteps) {
+        const int64_t ch = static_cast<int64_t>(c_begin) - kPad + s;
+        const uint32_t slot = s % ring;
+        if (!tma::WaitBounded(&full[slot], (s / ring) & 1u)) {
+          if (lane == 0) atomicExch(status, tma::kStatusBulkCopyTimeout);
+          return;
+        }
+        // a channel outside the tensor enters as gradient +0, which adds nothing
+        float4 pv = make_float4(0.0f, 0.0f, 0.0f, 0.0f), gv = pv;
+        if (ch >= 0 && ch < static_cast<int64_t>(channels) && mine) {
+          const float *at = slots + slot * slot_floats + threadIdx.x * 4;
+          pv = *reinterpret_cast<const float4 *>(at + tile_px);
+          gv = *reinterpret_cast<const float4 *>(at + 2 * tile_px);
+        }
+        wp[j][0] = pv.x, wp[j][1] = pv.y, wp[j][2] = pv.z, wp[j][3] = pv.w;
+        wg[j][0] = gv.x, wg[j][1] = gv.y, wg[j][2] = gv.z, wg[j][3] = gv.w;
+        if (s >= 2 * kPad && mine) {
+          // output channel ch - kPad; its source values still sit in the slot of step s - kPad
+          const float4 xv = *reinterpret_cast<const float4 *>(slots + ((s - kPad) % ring) * slot_floats + threadIdx.x * 4);
+          const float xc[4] = {xv.x, xv.y, xv.z, xv.w};
+          float val[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+#pragma unroll
+          for (int u = 1; u <= NSIZE; ++u)
+#pragma unroll
+            for (int l = 0; l < 4; ++l) {
+              const float pg = Reducer::PartialGrad(xc[l], wp[(j + u) % NSIZE][l]);
+              val[l] = __fadd_rn(val[l], __fmul_rn(pg, wg[(j + u) % NSIZE][l]));
+            }
+          __stcs(reinterpret_cast<float4 *>(dst + base + (ch - kPad) * plane + threadIdx.x * 4),
+                 make_float4(val[0], val[1], val[2], val[3]));
+        }
+        // the slot of step s - kPad has now been read for the last time
+        __syncwarp();
+        if (s >= static_cast<uint32_t>(kPad) && lane == 0) tma::BarrierArrive(&empty[(s - kPad) % ring]);
+      }
+    }
+  }
+}
+
 // ------------------------------- host side ----------------------------------------------
 
 namespace pooldetail {
@@ -1245,6 +1361,56 @@ inline void ChannelUnpoolLaunch(float *dst, const float *src, const float *poole
   const bool vec = plane % 4 == 0 && reinterpret_cast<uintptr_t>(dst) % 16 == 0 &&
                    reinterpret_cast<uintptr_t>(src) % 16 == 0 && reinterpret_cast<uintptr_t>(pooled) % 16 == 0 &&
                    reinterpret_cast<uintptr_t>(gpooled) % 16 == 0;
+  // staged variant: three planes per ring slot; the ring has to hold the nsize / 2 slots kept back
+  // for the source values plus a few in flight inside 200 KB, so plane tiles shrink with the window
+  if (vec && MSHADOW_B200_CHUNPOOL_STAGED && nsize >= 3 && c >= 2 * nsize) {
+    const uint32_t least = static_cast<uint32_t>(nsize) / 2 + 3;
+    uint32_t max_tile = (200u * 1024u / (least * 12u)) & ~3u;
+    if (max_tile > kChUnpoolTilePx) max_tile = kChUnpoolTilePx;
+    const uint32_t tiles_per_plane = (plane + max_tile - 1) / max_tile;
+    const uint32_t tile_px = ((plane + tiles_per_plane - 1) / tiles_per_plane + 3) & ~3u;
+    const uint32_t st_threads = (((tile_px / 4) + 31) & ~31u) + 32;
+    const int64_t fixed64 = n * static_cast<int64_t>(tiles_per_plane);
+    if (tile_px >= 128 && fixed64 < (int64_t(1) << 31)) {
+      uint32_t ring = (200u * 1024u) / (tile_px * 12u);
+      if (ring > 16) ring = 16;
+      const size_t smem = static_cast<size_t>(ring) * tile_px * 12;
+      const uint32_t fixed = static_cast<uint32_t>(fixed64);
+#define MSHADOW_B200_CHUNPOOL_STAGED_LAUNCH_(NS)                                                               \
+  {                                                                                                            \
+    auto kernel = ChannelUnpoolStagedKernel<Reducer, NS>;                                                      \
+    MSHADOW_CUDA_CALL(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));  \
+    const uint32_t slots = static_cast<uint32_t>(gpu_rt::ResidentPerSM(kernel, st_threads, smem)) *            \
+                           gpu_rt::CurrentDevice().sm_count;                                                   \
+    /* segments: whole waves of resident CTAs, weighed against the NS-1 halo channels each one re-reads */    \
+    uint32_t segs = 1;                                                                                         \
+    double best = 0.0;                                                                                         \
+    for (uint32_t k = 1; k <= 16 && k * 2 * NS <= static_cast<uint32_t>(c); ++k) {                             \
+      const uint64_t ctas = static_cast<uint64_t>(fixed) * k;                                                  \
+      const uint64_t waves = (ctas + slots - 1) / slots;                                                       \
+      const double eff = static_cast<double>(ctas) / static_cast<double>(waves * slots) /                     \
+                         (1.0 + static_cast<double>((NS - 1) * k) / static_cast<double>(c));                   \
+      if (eff > best + 1e-9) {                                                                                 \
+        best = eff;                                                                                            \
+        segs = k;                                                                                              \
+      }                                                                                                        \
+    }                                                                                                          \
+    const uint32_t seg_len = (static_cast<uint32_t>(c) + segs - 1) / segs;                                     \
+    const uint32_t nseg = (static_cast<uint32_t>(c) + seg_len - 1) / seg_len;                                  \
+    gpu_rt::LaunchAfterDrain(kernel, dim3(fixed, nseg), dim3(st_threads), smem, stream, dst, src, pooled, gpooled, \
+                             static_cast<uint32_t>(c), plane, tile_px, tiles_per_plane, seg_len, ring,         \
+                             gpu_rt::StatusWord());                                                            \
+  }
+      switch (nsize) {
+        case 3: MSHADOW_B200_CHUNPOOL_STAGED_LAUNCH_(3) break;
+        case 5: MSHADOW_B200_CHUNPOOL_STAGED_LAUNCH_(5) break;
+        default: MSHADOW_B200_CHUNPOOL_STAGED_LAUNCH_(7) break;
+      }
+#undef MSHADOW_B200_CHUNPOOL_STAGED_LAUNCH_
+      MSHADOW_CUDA_POST_KERNEL_CHECK(ChannelUnpoolStagedKernel);
+      return;
+    }
+  }
   const uint32_t groups = plane / (vec ? 4 : 1);
   const int64_t items64 = n * static_cast<int64_t>(groups);
   CHECK_LT(items64, (int64_t(1) << 31)) << "ch_unpool: tensor too large for 32-bit indexing";

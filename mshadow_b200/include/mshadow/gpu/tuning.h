@@ -57,6 +57,9 @@
 #ifndef MSHADOW_B200_CHPOOL_STAGED
 #define MSHADOW_B200_CHPOOL_STAGED 1  // route dense 16-byte-aligned inputs through the shared-memory ring kernel
 #endif
+#ifndef MSHADOW_B200_CHUNPOOL_STAGED
+#define MSHADOW_B200_CHUNPOOL_STAGED 1  // ch_unpool of maximum / minimum: planes through a shared-memory ring (0.79 -> see pool.cuh)
+#endif
 #ifndef MSHADOW_B200_CHPOOL_RING_KB
 #define MSHADOW_B200_CHPOOL_RING_KB 100  // shared memory of the ring per CTA (two CTAs per SM)
 #endif
