@@ -715,14 +715,38 @@ constexpr int kSoftmax3DDepth = MSHADOW_B200_SM3D_DEPTH;
  *  parked in dst and read back, mostly from L2.  Each column is summed by one thread in class
  *  order, as mshadow/tensor_cpu-inl.h:474-495 does.
  */
-template <int kLanes, bool kStaged>
+template <int kLanes, bool kStaged, bool kBulk = false>
 __global__ void __launch_bounds__(kSoftmax3DThreads)
 Softmax3DKernel(float *dst, const float *src, uint32_t classes, uint32_t npos, uint32_t tiles, int64_t ld_dst,
-                int64_t ld_src) {
+                int64_t ld_src, int *status) {
   extern __shared__ __align__(16) float tile[];  // [classes][kThreads * kLanes]
   constexpr int kWidth = kSoftmax3DThreads * kLanes;
   const uint32_t y = blockIdx.x / tiles;
-  const uint32_t n = (blockIdx.x - y * tiles) * kWidth + threadIdx.x * kLanes;
+  const uint32_t n0 = (blockIdx.x - y * tiles) * kWidth;
+  const uint32_t n = n0 + threadIdx.x * kLanes;
+  // kBulk (16-byte aligned rows, four positions per thread): a tile that lies wholly inside the
+  // position axis is brought in by one bulk asynchronous copy per class row (kWidth contiguous
+  // floats each), all of them in flight at once on one barrier, instead of kSoftmax3DDepth loads
+  // per thread: 43 KB per CTA against 8 KB for 21 classes (0.77 -> see the launch site).
+  bool from_tile = false;
+  if (kBulk && kStaged && kLanes == 4) {
+    __shared__ uint64_t landed;
+    if (n0 + kWidth <= npos) {   // the same for all threads of the CTA
+      if (threadIdx.x == 0) tma::BarrierInit(&landed, 1);
+      __syncthreads();
+      if (threadIdx.x == 0) {
+        tma::BarrierExpect(&landed, classes * static_cast<uint32_t>(kWidth) * 4u);
+        const float *row = src + static_cast<int64_t>(y) * classes * ld_src + n0;
+        for (uint32_t x = 0; x < classes; ++x)
+          tma::BulkLoad(tile + static_cast<size_t>(x) * kWidth, row + x * ld_src, kWidth * 4u, &landed);
+      }
+      if (!tma::WaitBounded(&landed, 0u)) {
+        if ((threadIdx.x & 31) == 0) atomicExch(status, tma::kStatusBulkCopyTimeout);
+        return;
+      }
+      from_tile = true;
+    }
+  }
   if (n >= npos) return;  // no CTA-wide barrier below: every thread works on its own columns
   const float *in = src + static_cast<int64_t>(y) * classes * ld_src + n;
   float *out = dst + static_cast<int64_t>(y) * classes * ld_dst + n;
@@ -730,8 +754,17 @@ Softmax3DKernel(float *dst, const float *src, uint32_t classes, uint32_t npos, u
   float m[kLanes], s[kLanes];
 #pragma unroll
   for (int l = 0; l < kLanes; ++l) m[l] = -FLT_MAX, s[l] = 0.0f;
+  if (from_tile) {
+#pragma unroll 4
+    for (uint32_t x = 0; x < classes; ++x) {
+      const float4 p = *reinterpret_cast<const float4 *>(mine + x * kWidth);
+      const float v[4] = {p.x, p.y, p.z, p.w};
+#pragma unroll
+      for (int l = 0; l < kLanes; ++l) m[l] = m[l] < v[l % 4] ? v[l % 4] : m[l];
+    }
+  }
 #pragma unroll kSoftmax3DDepth
-  for (uint32_t x = 0; x < classes; ++x) {
+  for (uint32_t x = from_tile ? classes : 0; x < classes; ++x) {
     float v[kLanes];
     if (kLanes == 4) {
       const float4 p = __ldcs(reinterpret_cast<const float4 *>(in + x * ld_src));
@@ -798,17 +831,21 @@ inline void LaunchSoftmax3D(float *dst, const float *src, uint32_t batch, uint32
   const size_t limit = static_cast<size_t>(gpu_rt::CurrentDevice().max_smem_optin);
   const int64_t ctas = static_cast<int64_t>(batch) * tiles;
   CHECK_LT(ctas, (int64_t(1) << 31)) << "Softmax: too many tiles for one launch";
-  if (smem <= limit) {
-    auto kernel = Softmax3DKernel<kLanes, true>;
+  int *status = gpu_rt::StatusWord();
+  if (smem + 64 <= limit) {  // (the bulk variant has a few bytes of static shared memory beside the tile)
+    // bulk-copy staging where the class rows of a tile are 16-byte aligned pieces of at most 1 MB in all
+    const bool bulk = kLanes == 4 && ld_src % 4 == 0 && reinterpret_cast<uintptr_t>(src) % 16 == 0 &&
+                      smem < (size_t(1) << 20) && npos >= width;
+    auto kernel = bulk ? Softmax3DKernel<kLanes, true, true> : Softmax3DKernel<kLanes, true, false>;
     if (smem > 48 * 1024) {
       MSHADOW_CUDA_CALL(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                             static_cast<int>(limit)));
+                                             static_cast<int>(limit - 64)));
     }
     kernel<<<static_cast<unsigned>(ctas), kSoftmax3DThreads, smem, stream>>>(dst, src, classes, npos, tiles, ld_dst,
-                                                                            ld_src);
+                                                                            ld_src, status);
   } else {
     Softmax3DKernel<kLanes, false><<<static_cast<unsigned>(ctas), kSoftmax3DThreads, 0, stream>>>(
-        dst, src, classes, npos, tiles, ld_dst, ld_src);
+        dst, src, classes, npos, tiles, ld_dst, ld_src, status);
   }
   MSHADOW_CUDA_POST_KERNEL_CHECK(Softmax3D);
 }
@@ -825,8 +862,8 @@ inline void Softmax3DLaunch(float *dst, const float *src, int64_t batch, int64_t
   // narrow position axes keep one position per thread so that a tile is not mostly idle threads;
   // the same when only the one-lane tile of all classes fits shared memory
   const size_t limit = static_cast<size_t>(gpu_rt::CurrentDevice().max_smem_optin);
-  const bool wide_fits = static_cast<size_t>(classes) * kSoftmax3DThreads * 4 * sizeof(float) <= limit;
-  const bool narrow_fits = static_cast<size_t>(classes) * kSoftmax3DThreads * sizeof(float) <= limit;
+  const bool wide_fits = static_cast<size_t>(classes) * kSoftmax3DThreads * 4 * sizeof(float) + 64 <= limit;
+  const bool narrow_fits = static_cast<size_t>(classes) * kSoftmax3DThreads * sizeof(float) + 64 <= limit;
   if (vec && npos >= 4 * kSoftmax3DThreads && (wide_fits || !narrow_fits)) {
     smdetail::LaunchSoftmax3D<4>(dst, src, b, c, p, ld_dst, ld_src, stream);
   } else {
