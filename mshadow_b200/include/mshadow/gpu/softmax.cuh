@@ -175,6 +175,8 @@ SoftmaxStagedKernel(float *dst, const float *src, const float *label, uint32_t r
       return;
     }
     phase ^= 1;
+    // the row's label is fetched now, so that its round trip overlaps the two reductions
+    const float hot_f = label != nullptr ? __ldg(label + y) : -1.0f;
     float v[kItems][4];
 #pragma unroll
     for (int k = 0; k < kItems; ++k) {
@@ -214,7 +216,7 @@ SoftmaxStagedKernel(float *dst, const float *src, const float *label, uint32_t r
     }
     s = smdetail::BlockAll<smdetail::SumOp, kThreads>(s, buf);
     const float r = __frcp_rn(s);
-    const int hot = label != nullptr ? static_cast<int>(label[y]) : -1;
+    const int hot = label != nullptr ? static_cast<int>(hot_f) : -1;
     const int hot_item = hot >= 0 ? hot >> 2 : -1, hot_lane = hot & 3;
     float4 *out = reinterpret_cast<float4 *>(dst + y * ld_dst);
 #pragma unroll
