@@ -889,16 +889,32 @@ SoftmaxGrad3DKernel(float *dst, const float *src, const float *label, uint32_t t
     const uint32_t y = image_of_row.Quot(row);
     const int x = static_cast<int>(row - y * image_of_row.div);
     int k[kLanes];
-    bool any_live = false;
-#pragma unroll
-    for (int l = 0; l < kLanes; ++l) {
-      k[l] = static_cast<int>(__ldg(label + y * ld_label + n + l));
-      any_live |= !((mode & 2) && k[l] == ignore_label);
-    }
     float v[kLanes];
 #pragma unroll
     for (int l = 0; l < kLanes; ++l) v[l] = 0.0f;
-    if (any_live) {
+    // without an ignore label every position is live: the source is requested before the labels, so
+    // that the two round trips overlap instead of following one another
+    const bool may_skip = (mode & 2) != 0;
+    if (!may_skip) {
+      if (kLanes == 4) {
+        const float4 p = __ldcs(reinterpret_cast<const float4 *>(src + row * ld_src + n));
+        v[0] = p.x, v[1 % kLanes] = p.y, v[2 % kLanes] = p.z, v[3 % kLanes] = p.w;
+      } else {
+        v[0] = __ldcs(src + row * ld_src + n);
+      }
+    }
+    bool any_live = false;
+    if (kLanes == 4 && ld_label % 4 == 0 && reinterpret_cast<uintptr_t>(label) % 16 == 0) {
+      const float4 q = __ldg(reinterpret_cast<const float4 *>(label + y * ld_label + n));
+      k[0] = static_cast<int>(q.x), k[1 % kLanes] = static_cast<int>(q.y), k[2 % kLanes] = static_cast<int>(q.z),
+      k[3 % kLanes] = static_cast<int>(q.w);
+    } else {
+#pragma unroll
+      for (int l = 0; l < kLanes; ++l) k[l] = static_cast<int>(__ldg(label + y * ld_label + n + l));
+    }
+#pragma unroll
+    for (int l = 0; l < kLanes; ++l) any_live |= !(may_skip && k[l] == ignore_label);
+    if (any_live && may_skip) {
       if (kLanes == 4) {
         const float4 p = __ldcs(reinterpret_cast<const float4 *>(src + row * ld_src + n));
         v[0] = p.x, v[1 % kLanes] = p.y, v[2 % kLanes] = p.z, v[3 % kLanes] = p.w;
