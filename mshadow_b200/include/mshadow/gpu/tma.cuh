@@ -58,6 +58,11 @@ __device__ __forceinline__ void FenceAsyncShared() {
   asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
 }
 
+/*!
+ * \brief one potentially blocking test of the phase.  (With an explicit suspend-time hint of 20 us
+ *  the ring kernels were no faster -- LRN forward 0.349 -> 0.359 ms, softmax 1.305 -> 1.317 ms --
+ *  so the instruction's own time limit stays.)
+ */
 __device__ __forceinline__ bool BarrierTest(uint64_t *bar, uint32_t parity) {
   uint32_t done;
   asm volatile(
