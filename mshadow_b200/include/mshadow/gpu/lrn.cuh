@@ -78,8 +78,8 @@ LrnForwardKernel(float *dst, float *norm, const float *src, lrndetail::Geometry 
   __syncthreads();
   if (warp == consumer_warps) {
     if (lane != 0) return;
+    uint32_t slot = 0, use = 0;  // counted, not s % ring and s / ring: no divisions in the march
     for (uint32_t s = 0; s < nsteps; ++s) {
-      const uint32_t slot = s % g.ring, use = s / g.ring;
       if (use > 0 && !tma::WaitBounded(&empty[slot], (use - 1) & 1u)) {
         atomicExch(status, tma::kStatusBulkCopyTimeout);
         return;
@@ -91,6 +91,10 @@ LrnForwardKernel(float *dst, float *norm, const float *src, lrndetail::Geometry 
       } else {
         tma::BarrierArrive(&full[slot]);  // keeps the slot's turn: see ChannelPoolStagedKernel
       }
+      if (++slot == g.ring) {
+        slot = 0;
+        ++use;
+      }
     }
     return;
   }
@@ -99,15 +103,15 @@ LrnForwardKernel(float *dst, float *norm, const float *src, lrndetail::Geometry 
 #pragma unroll
   for (int j = 0; j < NSIZE; ++j) win[j][0] = win[j][1] = win[j][2] = win[j][3] = 0.0f;
   const float neg_beta = -beta;
+  uint32_t slot = 0, lap = 0;
   for (uint32_t s0 = 0; s0 < nsteps; s0 += NSIZE) {
 #pragma unroll
     for (int j = 0; j < NSIZE; ++j) {
       const uint32_t s = s0 + j;
       if (s < nsteps) {
         const int64_t ch = static_cast<int64_t>(c_begin) - kPad + s;
-        const uint32_t slot = s % g.ring;
         float4 v = make_float4(0.0f, 0.0f, 0.0f, 0.0f);  // a channel outside the tensor adds 0 * 0
-        if (!tma::WaitBounded(&full[slot], (s / g.ring) & 1u)) {
+        if (!tma::WaitBounded(&full[slot], lap & 1u)) {
           if (lane == 0) atomicExch(status, tma::kStatusBulkCopyTimeout);
           return;
         }
@@ -134,6 +138,10 @@ LrnForwardKernel(float *dst, float *norm, const float *src, lrndetail::Geometry 
           const int64_t at = base + (ch - kPad) * g.plane + threadIdx.x * 4;
           __stcs(reinterpret_cast<float4 *>(dst + at), make_float4(o[0], o[1], o[2], o[3]));
           if (norm != nullptr) __stcs(reinterpret_cast<float4 *>(norm + at), make_float4(nrm[0], nrm[1], nrm[2], nrm[3]));
+        }
+        if (++slot == g.ring) {
+          slot = 0;
+          ++lap;
         }
       }
     }
@@ -172,8 +180,8 @@ LrnBackwardKernel(float *gsrc, const float *gout, const float *src, const float 
   __syncthreads();
   if (warp == consumer_warps) {
     if (lane != 0) return;
+    uint32_t slot = 0, use = 0;
     for (uint32_t s = 0; s < nsteps; ++s) {
-      const uint32_t slot = s % g.ring, use = s / g.ring;
       if (use > 0 && !tma::WaitBounded(&empty[slot], (use - 1) & 1u)) {
         atomicExch(status, tma::kStatusBulkCopyTimeout);
         return;
@@ -189,6 +197,10 @@ LrnBackwardKernel(float *gsrc, const float *gout, const float *src, const float 
       } else {
         tma::BarrierArrive(&full[slot]);
       }
+      if (++slot == g.ring) {
+        slot = 0;
+        ++use;
+      }
     }
     return;
   }
@@ -197,14 +209,15 @@ LrnBackwardKernel(float *gsrc, const float *gout, const float *src, const float 
 #pragma unroll
   for (int j = 0; j < NSIZE; ++j) win[j][0] = win[j][1] = win[j][2] = win[j][3] = 0.0f;
   const float neg_beta = -beta, neg_beta_1 = -beta - 1.0f;
+  uint32_t slot = 0, lap = 0;  // ring position of step s, and of step s - kPad (the centre channel's slot)
+  uint32_t centre = 0;
   for (uint32_t s0 = 0; s0 < nsteps; s0 += NSIZE) {
 #pragma unroll
     for (int j = 0; j < NSIZE; ++j) {
       const uint32_t s = s0 + j;
       if (s < nsteps) {
         const int64_t ch = static_cast<int64_t>(c_begin) - kPad + s;
-        const uint32_t slot = s % g.ring;
-        if (!tma::WaitBounded(&full[slot], (s / g.ring) & 1u)) {
+        if (!tma::WaitBounded(&full[slot], lap & 1u)) {
           if (lane == 0) atomicExch(status, tma::kStatusBulkCopyTimeout);
           return;
         }
@@ -222,7 +235,7 @@ LrnBackwardKernel(float *gsrc, const float *gout, const float *src, const float 
         win[j][0] = t[0], win[j][1] = t[1], win[j][2] = t[2], win[j][3] = t[3];
         if (s >= 2 * kPad && mine) {
           // output channel ch - kPad; its own three values still sit in the slot of step s - kPad
-          const float *at = slots + ((s - kPad) % g.ring) * slot_floats + threadIdx.x * 4;
+          const float *at = slots + centre * slot_floats + threadIdx.x * 4;
           const float4 gv = *reinterpret_cast<const float4 *>(at);
           const float4 xv = *reinterpret_cast<const float4 *>(at + g.tile_px);
           const float4 nv = *reinterpret_cast<const float4 *>(at + 2 * g.tile_px);
@@ -241,7 +254,14 @@ LrnBackwardKernel(float *gsrc, const float *gout, const float *src, const float 
         }
         // the slot of step s - kPad has now been read for the last time
         __syncwarp();
-        if (s >= static_cast<uint32_t>(kPad) && lane == 0) tma::BarrierArrive(&empty[(s - kPad) % g.ring]);
+        if (s >= static_cast<uint32_t>(kPad)) {
+          if (lane == 0) tma::BarrierArrive(&empty[centre]);
+          if (++centre == g.ring) centre = 0;
+        }
+        if (++slot == g.ring) {
+          slot = 0;
+          ++lap;
+        }
       }
     }
   }

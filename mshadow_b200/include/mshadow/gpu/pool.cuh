@@ -841,8 +841,10 @@ ChannelPoolStagedKernel(float *dst, const float *src, uint32_t channels, uint32_
     // producer: step s uses slot s % ring for the (s / ring)-th time, once the consumers have
     // released its previous use
     if (lane != 0) return;
+    // (slot and lap are counted, not computed as s % ring and s / ring: with a run-time ring the two
+    // divisions per step were a third of the consumers' instructions)
+    uint32_t slot = 0, use = 0;
     for (uint32_t s = 0; s < nsteps; ++s) {
-      const uint32_t slot = s % ring, use = s / ring;
       if (use > 0 && !tma::WaitBounded(&empty[slot], (use - 1) & 1u)) {
         atomicExch(status, tma::kStatusBulkCopyTimeout);
         return;
@@ -857,6 +859,10 @@ ChannelPoolStagedKernel(float *dst, const float *src, uint32_t channels, uint32_
         // seen the first release
         tma::BarrierArrive(&full[slot]);
       }
+      if (++slot == ring) {
+        slot = 0;
+        ++use;
+      }
     }
     return;
   }
@@ -866,15 +872,15 @@ ChannelPoolStagedKernel(float *dst, const float *src, uint32_t channels, uint32_
   float win[NSIZE][4];
 #pragma unroll
   for (int j = 0; j < NSIZE; ++j) win[j][0] = win[j][1] = win[j][2] = win[j][3] = init;
+  uint32_t slot = 0, lap = 0;
   for (uint32_t s0 = 0; s0 < nsteps; s0 += NSIZE) {
 #pragma unroll
     for (int j = 0; j < NSIZE; ++j) {
       const uint32_t s = s0 + j;
       if (s < nsteps) {
         const int64_t ch = static_cast<int64_t>(c_begin) - kPad + s;
-        const uint32_t slot = s % ring;
         float4 v = make_float4(init, init, init, init);
-        if (!tma::WaitBounded(&full[slot], (s / ring) & 1u)) {
+        if (!tma::WaitBounded(&full[slot], lap & 1u)) {
           if (lane == 0) atomicExch(status, tma::kStatusBulkCopyTimeout);
           return;
         }
@@ -897,6 +903,10 @@ ChannelPoolStagedKernel(float *dst, const float *src, uint32_t channels, uint32_
             for (int l = 0; l < 4; ++l) Reducer::Reduce(res[l], win[(j + t) % NSIZE][l]);
           __stcs(reinterpret_cast<float4 *>(out + (ch - kPad) * plane + threadIdx.x * 4),
                  make_float4(res[0], res[1], res[2], res[3]));
+        }
+        if (++slot == ring) {
+          slot = 0;
+          ++lap;
         }
       }
     }
@@ -947,8 +957,8 @@ ChannelUnpoolStagedKernel(float *dst, const float *src, const float *pooled, con
   __syncthreads();
   if (warp == consumer_warps) {
     if (lane != 0) return;
+    uint32_t slot = 0, use = 0;  // counted, not s % ring and s / ring
     for (uint32_t s = 0; s < nsteps; ++s) {
-      const uint32_t slot = s % ring, use = s / ring;
       if (use > 0 && !tma::WaitBounded(&empty[slot], (use - 1) & 1u)) {
         atomicExch(status, tma::kStatusBulkCopyTimeout);
         return;
@@ -966,6 +976,10 @@ ChannelUnpoolStagedKernel(float *dst, const float *src, const float *pooled, con
       } else {
         tma::BarrierArrive(&full[slot]);
       }
+      if (++slot == ring) {
+        slot = 0;
+        ++use;
+      }
     }
     return;
   }
@@ -976,14 +990,14 @@ ChannelUnpoolStagedKernel(float *dst, const float *src, const float *pooled, con
 #pragma unroll
     for (int l = 0; l < 4; ++l) wp[j][l] = 0.0f, wg[j][l] = 0.0f;
   }
+  uint32_t slot = 0, lap = 0, centre = 0;  // ring position of step s, and of step s - kPad
   for (uint32_t s0 = 0; s0 < nsteps; s0 += NSIZE) {
 #pragma unroll
     for (int j = 0; j < NSIZE; ++j) {
       const uint32_t s = s0 + j;
       if (s < nsteps) {
         const int64_t ch = static_cast<int64_t>(c_begin) - kPad + s;
-        const uint32_t slot = s % ring;
-        if (!tma::WaitBounded(&full[slot], (s / ring) & 1u)) {
+        if (!tma::WaitBounded(&full[slot], lap & 1u)) {
           if (lane == 0) atomicExch(status, tma::kStatusBulkCopyTimeout);
           return;
         }
@@ -998,7 +1012,7 @@ ChannelUnpoolStagedKernel(float *dst, const float *src, const float *pooled, con
         wg[j][0] = gv.x, wg[j][1] = gv.y, wg[j][2] = gv.z, wg[j][3] = gv.w;
         if (s >= 2 * kPad && mine) {
           // output channel ch - kPad; its source values still sit in the slot of step s - kPad
-          const float4 xv = *reinterpret_cast<const float4 *>(slots + ((s - kPad) % ring) * slot_floats + threadIdx.x * 4);
+          const float4 xv = *reinterpret_cast<const float4 *>(slots + centre * slot_floats + threadIdx.x * 4);
           const float xc[4] = {xv.x, xv.y, xv.z, xv.w};
           float val[4] = {0.0f, 0.0f, 0.0f, 0.0f};
 #pragma unroll
@@ -1013,7 +1027,14 @@ ChannelUnpoolStagedKernel(float *dst, const float *src, const float *pooled, con
         }
         // the slot of step s - kPad has now been read for the last time
         __syncwarp();
-        if (s >= static_cast<uint32_t>(kPad) && lane == 0) tma::BarrierArrive(&empty[(s - kPad) % ring]);
+        if (s >= static_cast<uint32_t>(kPad)) {
+          if (lane == 0) tma::BarrierArrive(&empty[centre]);
+          if (++centre == ring) centre = 0;
+        }
+        if (++slot == ring) {
+          slot = 0;
+          ++lap;
+        }
       }
     }
   }
