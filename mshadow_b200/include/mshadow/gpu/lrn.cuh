@@ -104,19 +104,23 @@ LrnForwardKernel(float *dst, float *norm, const float *src, lrndetail::Geometry 
   for (int j = 0; j < NSIZE; ++j) win[j][0] = win[j][1] = win[j][2] = win[j][3] = 0.0f;
   const float neg_beta = -beta;
   uint32_t slot = 0, lap = 0;
+  // 32-bit bookkeeping: the channel of a step as an unsigned number (one before the tensor wraps and
+  // fails the one comparison), slot and output addresses advanced by additions
+  uint32_t ch = c_begin - kPad;
+  const float *my_slot = slots + threadIdx.x * 4;
+  int64_t at = base + static_cast<int64_t>(c_begin) * g.plane + threadIdx.x * 4;
   for (uint32_t s0 = 0; s0 < nsteps; s0 += NSIZE) {
 #pragma unroll
     for (int j = 0; j < NSIZE; ++j) {
       const uint32_t s = s0 + j;
       if (s < nsteps) {
-        const int64_t ch = static_cast<int64_t>(c_begin) - kPad + s;
         float4 v = make_float4(0.0f, 0.0f, 0.0f, 0.0f);  // a channel outside the tensor adds 0 * 0
         if (!tma::WaitBounded(&full[slot], lap & 1u)) {
           if (lane == 0) atomicExch(status, tma::kStatusBulkCopyTimeout);
           return;
         }
-        if (ch >= 0 && ch < static_cast<int64_t>(g.channels) && mine) {
-          v = *reinterpret_cast<const float4 *>(slots + static_cast<size_t>(slot) * g.tile_px + threadIdx.x * 4);
+        if (ch < g.channels && mine) {
+          v = *reinterpret_cast<const float4 *>(my_slot);
         }
         __syncwarp();
         if (lane == 0) tma::BarrierArrive(&empty[slot]);
@@ -135,13 +139,16 @@ LrnForwardKernel(float *dst, float *norm, const float *src, lrndetail::Geometry 
             nrm[l] = __fadd_rn(__fmul_rn(sum, salpha), knorm);
             o[l] = __fmul_rn(win[(j + 1 + kPad) % NSIZE][l], Power::Map(nrm[l], neg_beta));
           }
-          const int64_t at = base + (ch - kPad) * g.plane + threadIdx.x * 4;
           __stcs(reinterpret_cast<float4 *>(dst + at), make_float4(o[0], o[1], o[2], o[3]));
           if (norm != nullptr) __stcs(reinterpret_cast<float4 *>(norm + at), make_float4(nrm[0], nrm[1], nrm[2], nrm[3]));
+          at += g.plane;
         }
+        ++ch;
+        my_slot += g.tile_px;
         if (++slot == g.ring) {
           slot = 0;
           ++lap;
+          my_slot = slots + threadIdx.x * 4;
         }
       }
     }
@@ -211,19 +218,22 @@ LrnBackwardKernel(float *gsrc, const float *gout, const float *src, const float 
   const float neg_beta = -beta, neg_beta_1 = -beta - 1.0f;
   uint32_t slot = 0, lap = 0;  // ring position of step s, and of step s - kPad (the centre channel's slot)
   uint32_t centre = 0;
+  // 32-bit bookkeeping as in the forward kernel
+  uint32_t ch = c_begin - kPad;
+  const float *my_slot = slots + threadIdx.x * 4, *my_centre = my_slot;
+  float *my_out = gsrc + base + static_cast<int64_t>(c_begin) * g.plane + threadIdx.x * 4;
   for (uint32_t s0 = 0; s0 < nsteps; s0 += NSIZE) {
 #pragma unroll
     for (int j = 0; j < NSIZE; ++j) {
       const uint32_t s = s0 + j;
       if (s < nsteps) {
-        const int64_t ch = static_cast<int64_t>(c_begin) - kPad + s;
         if (!tma::WaitBounded(&full[slot], lap & 1u)) {
           if (lane == 0) atomicExch(status, tma::kStatusBulkCopyTimeout);
           return;
         }
         float t[4] = {0.0f, 0.0f, 0.0f, 0.0f};  // a channel outside the tensor adds nothing
-        if (ch >= 0 && ch < static_cast<int64_t>(g.channels) && mine) {
-          const float *at = slots + slot * slot_floats + threadIdx.x * 4;
+        if (ch < g.channels && mine) {
+          const float *at = my_slot;
           const float4 gv = *reinterpret_cast<const float4 *>(at);
           const float4 xv = *reinterpret_cast<const float4 *>(at + g.tile_px);
           const float4 nv = *reinterpret_cast<const float4 *>(at + 2 * g.tile_px);
@@ -235,7 +245,7 @@ LrnBackwardKernel(float *gsrc, const float *gout, const float *src, const float 
         win[j][0] = t[0], win[j][1] = t[1], win[j][2] = t[2], win[j][3] = t[3];
         if (s >= 2 * kPad && mine) {
           // output channel ch - kPad; its own three values still sit in the slot of step s - kPad
-          const float *at = slots + centre * slot_floats + threadIdx.x * 4;
+          const float *at = my_centre;
           const float4 gv = *reinterpret_cast<const float4 *>(at);
           const float4 xv = *reinterpret_cast<const float4 *>(at + g.tile_px);
           const float4 nv = *reinterpret_cast<const float4 *>(at + 2 * g.tile_px);
@@ -249,18 +259,25 @@ LrnBackwardKernel(float *gsrc, const float *gout, const float *src, const float 
             const float first = __fmul_rn(gc[l], Power::Map(nc[l], neg_beta));
             o[l] = __fadd_rn(first, __fmul_rn(__fmul_rn(scale, sum), xc[l]));
           }
-          __stcs(reinterpret_cast<float4 *>(gsrc + base + (ch - kPad) * g.plane + threadIdx.x * 4),
-                 make_float4(o[0], o[1], o[2], o[3]));
+          __stcs(reinterpret_cast<float4 *>(my_out), make_float4(o[0], o[1], o[2], o[3]));
+          my_out += g.plane;
         }
         // the slot of step s - kPad has now been read for the last time
         __syncwarp();
         if (s >= static_cast<uint32_t>(kPad)) {
           if (lane == 0) tma::BarrierArrive(&empty[centre]);
-          if (++centre == g.ring) centre = 0;
+          my_centre += slot_floats;
+          if (++centre == g.ring) {
+            centre = 0;
+            my_centre = slots + threadIdx.x * 4;
+          }
         }
+        ++ch;
+        my_slot += slot_floats;
         if (++slot == g.ring) {
           slot = 0;
           ++lap;
+          my_slot = slots + threadIdx.x * 4;
         }
       }
     }

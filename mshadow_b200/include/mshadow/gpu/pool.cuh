@@ -873,19 +873,24 @@ ChannelPoolStagedKernel(float *dst, const float *src, uint32_t channels, uint32_
 #pragma unroll
   for (int j = 0; j < NSIZE; ++j) win[j][0] = win[j][1] = win[j][2] = win[j][3] = init;
   uint32_t slot = 0, lap = 0;
+  // 32-bit bookkeeping in the march: the channel of step s as an unsigned number (a channel before
+  // the tensor wraps to a huge one and fails the one comparison), slot and output addresses advanced
+  // by additions
+  uint32_t ch = c_begin - kPad;
+  const float *my_slot = slots + threadIdx.x * 4;
+  float *my_out = out + static_cast<int64_t>(c_begin) * plane + threadIdx.x * 4;
   for (uint32_t s0 = 0; s0 < nsteps; s0 += NSIZE) {
 #pragma unroll
     for (int j = 0; j < NSIZE; ++j) {
       const uint32_t s = s0 + j;
       if (s < nsteps) {
-        const int64_t ch = static_cast<int64_t>(c_begin) - kPad + s;
         float4 v = make_float4(init, init, init, init);
         if (!tma::WaitBounded(&full[slot], lap & 1u)) {
           if (lane == 0) atomicExch(status, tma::kStatusBulkCopyTimeout);
           return;
         }
-        if (ch >= 0 && ch < static_cast<int64_t>(channels) && mine) {
-          v = *reinterpret_cast<const float4 *>(slots + static_cast<size_t>(slot) * tile_px + threadIdx.x * 4);
+        if (ch < channels && mine) {
+          v = *reinterpret_cast<const float4 *>(my_slot);
         }
         // this warp is done with the slot (the producer counts one release per warp and step)
         __syncwarp();
@@ -901,12 +906,15 @@ ChannelPoolStagedKernel(float *dst, const float *src, uint32_t channels, uint32_
           for (int t = 1; t <= NSIZE; ++t)
 #pragma unroll
             for (int l = 0; l < 4; ++l) Reducer::Reduce(res[l], win[(j + t) % NSIZE][l]);
-          __stcs(reinterpret_cast<float4 *>(out + (ch - kPad) * plane + threadIdx.x * 4),
-                 make_float4(res[0], res[1], res[2], res[3]));
+          __stcs(reinterpret_cast<float4 *>(my_out), make_float4(res[0], res[1], res[2], res[3]));
+          my_out += plane;
         }
+        ++ch;
+        my_slot += tile_px;
         if (++slot == ring) {
           slot = 0;
           ++lap;
+          my_slot = slots + threadIdx.x * 4;
         }
       }
     }
@@ -991,20 +999,24 @@ ChannelUnpoolStagedKernel(float *dst, const float *src, const float *pooled, con
     for (int l = 0; l < 4; ++l) wp[j][l] = 0.0f, wg[j][l] = 0.0f;
   }
   uint32_t slot = 0, lap = 0, centre = 0;  // ring position of step s, and of step s - kPad
+  // 32-bit bookkeeping: the channel of a step as an unsigned number (one before the tensor wraps and
+  // fails the one comparison), slot and output addresses advanced by additions
+  uint32_t ch = c_begin - kPad;
+  const float *my_slot = slots + threadIdx.x * 4, *my_centre = my_slot;
+  float *my_out = dst + base + static_cast<int64_t>(c_begin) * plane + threadIdx.x * 4;
   for (uint32_t s0 = 0; s0 < nsteps; s0 += NSIZE) {
 #pragma unroll
     for (int j = 0; j < NSIZE; ++j) {
       const uint32_t s = s0 + j;
       if (s < nsteps) {
-        const int64_t ch = static_cast<int64_t>(c_begin) - kPad + s;
         if (!tma::WaitBounded(&full[slot], lap & 1u)) {
           if (lane == 0) atomicExch(status, tma::kStatusBulkCopyTimeout);
           return;
         }
         // a channel outside the tensor enters as gradient +0, which adds nothing
         float4 pv = make_float4(0.0f, 0.0f, 0.0f, 0.0f), gv = pv;
-        if (ch >= 0 && ch < static_cast<int64_t>(channels) && mine) {
-          const float *at = slots + slot * slot_floats + threadIdx.x * 4;
+        if (ch < channels && mine) {
+          const float *at = my_slot;
           pv = *reinterpret_cast<const float4 *>(at + tile_px);
           gv = *reinterpret_cast<const float4 *>(at + 2 * tile_px);
         }
@@ -1012,7 +1024,7 @@ ChannelUnpoolStagedKernel(float *dst, const float *src, const float *pooled, con
         wg[j][0] = gv.x, wg[j][1] = gv.y, wg[j][2] = gv.z, wg[j][3] = gv.w;
         if (s >= 2 * kPad && mine) {
           // output channel ch - kPad; its source values still sit in the slot of step s - kPad
-          const float4 xv = *reinterpret_cast<const float4 *>(slots + centre * slot_floats + threadIdx.x * 4);
+          const float4 xv = *reinterpret_cast<const float4 *>(my_centre);
           const float xc[4] = {xv.x, xv.y, xv.z, xv.w};
           float val[4] = {0.0f, 0.0f, 0.0f, 0.0f};
 #pragma unroll
@@ -1022,18 +1034,25 @@ ChannelUnpoolStagedKernel(float *dst, const float *src, const float *pooled, con
               const float pg = Reducer::PartialGrad(xc[l], wp[(j + u) % NSIZE][l]);
               val[l] = __fadd_rn(val[l], __fmul_rn(pg, wg[(j + u) % NSIZE][l]));
             }
-          __stcs(reinterpret_cast<float4 *>(dst + base + (ch - kPad) * plane + threadIdx.x * 4),
-                 make_float4(val[0], val[1], val[2], val[3]));
+          __stcs(reinterpret_cast<float4 *>(my_out), make_float4(val[0], val[1], val[2], val[3]));
+          my_out += plane;
         }
         // the slot of step s - kPad has now been read for the last time
         __syncwarp();
         if (s >= static_cast<uint32_t>(kPad)) {
           if (lane == 0) tma::BarrierArrive(&empty[centre]);
-          if (++centre == ring) centre = 0;
+          my_centre += slot_floats;
+          if (++centre == ring) {
+            centre = 0;
+            my_centre = slots + threadIdx.x * 4;
+          }
         }
+        ++ch;
+        my_slot += slot_floats;
         if (++slot == ring) {
           slot = 0;
           ++lap;
+          my_slot = slots + threadIdx.x * 4;
         }
       }
     }
